@@ -1,0 +1,316 @@
+#!/usr/bin/env python
+"""Benchmark of the HBQ hot path on B200: one quantised linear layer.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (the reference's HBQ-E quant-GEMM configuration with partial-sum-quantised
+accumulation, config/hbq_e_psum_quant.yaml): X bf16 [4096, 4096] ~ N(0,1) with 0.5 % outlier
+channels x30, W bf16 [14336, 4096] ~ N(0, 0.02) (the Llama-3-8B MLP up-projection shape),
+synthetic and seeded.  The weight is fake-quantised once (static weight quantisation, not
+timed).  One step = HBQ-E activation quantize of X followed by the GEMM whose fp32 partial sums
+are INT8-quantised per (128 k, 32 n) block and accumulated in fp16.  The metric counts 2*M*N*K
+flops per step and nothing else.
+
+With N > 1 (torchrun, one rank per GPU) every rank runs its own batch X against the same W: the
+path shards over rows without any exchange, so the scaling is weak and no collective is on the
+data path; ranks only meet in the barriers around the timed region.
+
+`--impl reference` times the CPU restatement of the reference's path (oracle/, all host
+threads) on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+M, K, N = 4096, 4096, 14336
+GROUP_K, GROUP_N = 128, 32
+WORKLOAD = ("configs[1]: HBQ-E linear, X[4096,4096] (0.5% outlier channels x30) * W[14336,4096]^T, "
+            "act E2M2 / wgt E2M1, block 128, micro-block 32, accumulation fp16_quant(group 128, block 32)")
+ACT = dict(block_size=128, ebit=2, mbit=2, sc_ebit=5, sc_mbit=3, l2_block_size=32, l2_sc_bit=2, l2_scheme="SIG-1")
+WGT = dict(block_size=128, ebit=2, mbit=1, sc_ebit=5, sc_mbit=3, l2_block_size=32, l2_sc_bit=2, l2_scheme="Mix")
+# algorithmic HBM bytes per element of the activation quantize: 2 in + 2 fake-quantised out
+QUANT_BYTES_PER_ELEM = 4.0
+
+
+def make_inputs(rank: int):
+    import torch
+    g = torch.Generator().manual_seed(1000 + rank)
+    x = torch.randn(M, K, generator=g)
+    cols = torch.randperm(K, generator=torch.Generator().manual_seed(7))[: max(1, int(K * 0.005))]
+    x[:, cols] *= 30
+    w = 0.02 * torch.randn(N, K, generator=torch.Generator().manual_seed(1))
+    return x.to(torch.bfloat16), w.to(torch.bfloat16)
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as fh:
+            d = json.load(fh)
+        return {"hbm_gbs": d.get("hbm_gbs"), "tf_burst": d.get("bf16_tflops"),
+                "tf_sustained": d.get("bf16_tflops_sustained"), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tf_burst": 1590.0, "tf_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons of one GPU, sampled every 200 ms (read only)."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0])); smax.append(float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for n, v in zip(names, r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def cpu_baseline_sample(x_bf16, wq_f16, seconds_target: float = 15.0):
+    """The CPU oracle (a port of the reference's eager fp16 quantizer and of gemm.cu's INT8
+    partial-sum model) on a bounded row sample of the workload, all host threads."""
+    import numpy as np
+    import oracle as O
+    fa = O.Format(O.KIND_HBQ, ACT["ebit"], ACT["mbit"], 5, 3, 128, l2_block_size=32, l2_sc_bit=2, l2_scheme="SIG-1")
+    xh = x_bf16.to(dtype=__import__("torch").float16).numpy()
+    wt = np.ascontiguousarray(wq_f16.numpy().T)
+    rows = 8
+    t0 = time.perf_counter()
+    xq = O.quantize(xh[:rows], fa, want_codes=False)["deq"]
+    O.gemm(xq, wt, O.ACC_PSUM_INT8, GROUP_K, GROUP_N)
+    dt = time.perf_counter() - t0
+    rows = int(max(8, min(M, rows * seconds_target / max(dt, 1e-3)) // 8 * 8))
+    t0 = time.perf_counter()
+    xq = O.quantize(xh[:rows], fa, want_codes=False)["deq"]
+    O.gemm(xq, wt, O.ACC_PSUM_INT8, GROUP_K, GROUP_N)
+    dt = time.perf_counter() - t0
+    return {"value": 2.0 * rows * N * K / dt / 1e12, "unit": "TFLOP/s", "cores": O.num_threads(), "kind": "port",
+            "sample": f"{rows} of {M} rows of X through oracle HBQ-E quantize + INT8-psum GEMM vs full W, {dt:.1f} s"}
+
+
+def run_reference(args, rank: int, world: int):
+    """Reference arm: the CPU implementation of the path (oracle port; the reference's Python
+    quantizer cannot travel to the GPU box and its GEMM has no CPU implementation)."""
+    if rank != 0:
+        return
+    import numpy as np
+    import torch
+    import oracle as O
+    O.build()
+    x, w = make_inputs(0)
+    fw = O.Format(O.KIND_HBQ, 2, 1, 5, 3, 128, l2_block_size=32, l2_sc_bit=2, l2_scheme="Mix")
+    fa = O.Format(O.KIND_HBQ, 2, 2, 5, 3, 128, l2_block_size=32, l2_sc_bit=2, l2_scheme="SIG-1")
+    wq = O.quantize(w.to(torch.float16).numpy(), fw, want_codes=False)["deq"]
+    wt = np.ascontiguousarray(wq.T)
+    xh = x.to(torch.float16).numpy()
+    rows = 32            # per step: bounded sample so that K+W steps end within minutes
+
+    def step(i):
+        r0 = (i * rows) % M
+        xq = O.quantize(xh[r0:r0 + rows], fa, want_codes=False)["deq"]
+        return O.gemm(xq, wt, O.ACC_PSUM_INT8, GROUP_K, GROUP_N)
+
+    for i in range(args.warmup):
+        step(i)
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        step(args.warmup + i)
+    dt = (time.perf_counter() - t0) / args.steps
+    val = 2.0 * rows * N * K / dt / 1e12
+    sample = f"{rows} rows of X per step (of {M}), full W; oracle HBQ-E quantize + INT8-psum GEMM"
+    print(json.dumps({
+        "impl": "reference", "metric": "quant_gemm_tflops", "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": WORKLOAD},
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": O.num_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+
+
+def run_ours(args, rank: int, world: int, local_rank: int):
+    import torch
+    import torch.distributed as dist
+    import hbq_b200 as H
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    x_host, w_host = make_inputs(rank)
+    aq = H.HBQQuantizer(**ACT)
+    aq.out_dtype = torch.float16          # bf16 in, fp16 fake-quantised out: the GEMM's operand type
+    wq = H.HBQQuantizer(**WGT)
+    wq.out_dtype = torch.float16
+    lin = H.QLinear(K, N, bias=False, device=dev, dtype=torch.float16, check_finite=False)
+    lin.weight.data = wq.q(w_host.to(dev))                              # static weight quantisation (not timed)
+    lin.aq = aq
+    lin.ops = H.FP16AccumMatMul(group_size=GROUP_K, quant_block_size=GROUP_N)
+    x = x_host.to(dev)
+    torch.cuda.synchronize()
+
+    def step():
+        return lin(x)
+
+    for _ in range(max(args.warmup, 3)):
+        y = step()
+    barrier()
+    if H.gemm_status() != 0:
+        raise RuntimeError("tensor-core GEMM reported an expired wait")
+
+    # ---- timed region: K steps, device time, max over ranks ----
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    time.sleep(0.3)
+    l0 = H.launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev0.record()
+    for _ in range(args.steps):
+        y = step()
+    ev1.record()
+    barrier()
+    total_ms = ev0.elapsed_time(ev1)
+    launches = H.launch_count() - l0
+    clocks = sampler.stop()
+    if world > 1:
+        t = torch.tensor([total_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t.item())
+    ms_step = total_ms / args.steps
+    flops_step = 2.0 * M * N * K
+    value = flops_step * world / (ms_step * 1e-3) / 1e12
+
+    # ---- per-kernel device times (events on the launching stream, same steady state) ----
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+           for _ in range(args.steps)]
+    barrier()
+    for a, b, c in evs:
+        a.record()
+        xq_i = aq.q(x)
+        b.record()
+        lin.ops(xq_i, lin.weight)
+        c.record()
+    torch.cuda.synchronize()
+    q_ms = statistics.mean(a.elapsed_time(b) for a, b, c in evs)
+    g_ms = statistics.mean(b.elapsed_time(c) for a, b, c in evs)
+    peaks = measured_peaks()
+    g_tf = flops_step / (g_ms * 1e-3) / 1e12
+    q_gbs = M * K * QUANT_BYTES_PER_ELEM / (q_ms * 1e-3) / 1e9
+
+    # ---- end to end through the plugin API: pinned host X -> device -> layer -> host Y ----
+    x_pin = x_host.pin_memory()
+    y_pin = torch.empty((M, N), dtype=torch.float16).pin_memory()
+    x_dev = torch.empty_like(x)
+
+    def e2e_step():
+        x_dev.copy_(x_pin, non_blocking=True)
+        y_pin.copy_(lin(x_dev), non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_val = flops_step * world / (e2e_ms / args.steps * 1e-3) / 1e12
+    if H.gemm_status() != 0:
+        raise RuntimeError("tensor-core GEMM reported an expired wait")
+
+    if rank == 0:
+        cpu = None
+        if world == 1 and not args.no_cpu_baseline:
+            cpu = cpu_baseline_sample(x_host, lin.weight.data.cpu())
+        line = {
+            "metric": "quant_gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "global_rows": M * world, "parallelism": f"row-sharded x{world}, no collective",
+                       "l2": "no flush: per-step working set 266 MB (X 32 + Xq 32 + W 117 + Y 117) exceeds the 126 MB L2"},
+            "clocks": clocks,
+            "e2e": {"value": e2e_val, "unit": "TFLOP/s", "h2d_bytes_per_step": M * K * 2, "d2h_bytes_per_step": M * N * 2},
+            "gpu_launches": int(launches),
+            "roofline": {"bound": "tensor", "kernel": "gemm_tc_kernel<PSUM_INT8,32>", "achieved": g_tf,
+                         "peak": peaks["tf_sustained"], "unit": "TFLOP/s", "frac": g_tf / peaks["tf_sustained"],
+                         "peak_burst": peaks["tf_burst"], "frac_of_burst": g_tf / peaks["tf_burst"],
+                         "peak_source": peaks["source"], "ms_per_launch": g_ms, "traffic": None},
+            "quantize": {"kernel": "hbq_quantize_kernel<2> (HBQ-E act, bf16 in, fp16 fake-quant out)", "bound": "hbm",
+                         "achieved": q_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": q_gbs / peaks["hbm_gbs"],
+                         "ms_per_launch": q_ms, "bytes_per_elem": QUANT_BYTES_PER_ELEM},
+        }
+        if cpu is not None:
+            line["cpu_baseline"] = cpu
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+    else:
+        run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

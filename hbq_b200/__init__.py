@@ -1,0 +1,18 @@
+"""hbq_b200 -- B200 (sm_100a) implementation of HBQ's hot path: block quantize-dequantize and the
+GEMM with modelled low-precision accumulation, behind the reference's Python interface.
+
+Importing the package does not need a GPU; the CUDA library (``lib/libhbq_b200.so``, built by
+``python -m hbq_b200.build``) is loaded on first use and there is no fallback without it.
+"""
+from . import blockquant_ext  # noqa: F401
+from ._lib import HbqError, launch_count  # noqa: F401
+from .gemm import gemm, gemm_status  # noqa: F401
+from .module import QLinear  # noqa: F401
+from .ops import FP16AccumMatMul  # noqa: F401
+from .ptq import PTQConfig, load_quant_config  # noqa: F401
+from .quantizer import (HBQQuantizer, MXFPQuantizer, MXINTQuantizer, PackedTensor, _QBase,  # noqa: F401
+                        dequantize_packed, get_max_norm, get_min_norm, get_min_subnorm)
+
+__all__ = ["HBQQuantizer", "MXFPQuantizer", "MXINTQuantizer", "_QBase", "FP16AccumMatMul", "QLinear",
+           "PTQConfig", "load_quant_config", "blockquant_ext", "gemm", "gemm_status", "PackedTensor",
+           "dequantize_packed", "HbqError", "launch_count", "get_max_norm", "get_min_norm", "get_min_subnorm"]

@@ -1,0 +1,267 @@
+// C ABI of the library (declared in include/hbq_b200.h) and the packed-code dequantizer.
+#include "common.cuh"
+#include <atomic>
+#include <cstring>
+#include <cstdio>
+#include <math.h>
+
+namespace hbq {
+
+static std::atomic<long long> g_launches{0};
+static thread_local char g_last_cuda_error[256] = "";
+
+void note_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+int set_cuda_error(cudaError_t e, const char* where)
+{
+    snprintf(g_last_cuda_error, sizeof(g_last_cuda_error), "%s: %s", where, cudaGetErrorString(e));
+    return HBQ_ERR_CUDA;
+}
+
+// implemented in quantize.cu / gemm_simt.cu / gemm_tc.cu
+int quantize_launch(const void*, int, int64_t, int64_t, const hbq_format*, void*, int, const hbq_packed_out*,
+                    const float*, cudaStream_t);
+int fp_quant_launch(const void*, int64_t, int, int, int, int, int, void*, cudaStream_t);
+int64_t absmax_scratch_bytes();
+int absmax_launch(const void*, int, int64_t, float*, void*, cudaStream_t);
+int gemm_simt_launch(const void*, const void*, void*, int64_t, int64_t, int64_t, int, int, int, int,
+                     const void*, cudaStream_t);
+bool gemm_tc_eligible(int64_t, int64_t, int64_t, int, int, int);
+int gemm_tc_launch(const void*, const void*, void*, int64_t, int64_t, int64_t, int, int, int, const void*,
+                   cudaStream_t);
+int transpose_launch(const void*, void*, int64_t, int64_t, cudaStream_t);
+int gemm_tc_status(int*);
+int gemm_tc_status_reset();
+
+// ------------------------------------------------------------------------------------------
+// Packed codes -> fake-quantised fp16/bf16 tensor.
+// ------------------------------------------------------------------------------------------
+struct DqArgs {
+    hbq_packed_out in;
+    void* deq;
+    int64_t rows, K, Kp, total_chunks, cpr;
+    int out_bf16, nblk, code_bits, is_int, mbit, ebit, hbq, nl2, l2_block, l2_bits, l2_bytes;
+    float tab[2][16];
+};
+
+__global__ void __launch_bounds__(256) dequantize_kernel(const DqArgs a)
+{
+    const int64_t ci = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (ci >= a.total_chunks) return;
+    const int64_t row = ci / a.cpr, k0 = (ci % a.cpr) * 8;
+    if (k0 >= a.K) return;
+    const int64_t e0 = row * a.Kp + k0;
+    const int B = (int)(a.Kp / a.nblk);
+    const int64_t blk = row * a.nblk + k0 / B;
+    const float s = __half2float(bits_h((uint16_t)((uint16_t)a.in.scale_u8[blk] << 7)));
+    const __half sh = __float2half_rn(s);
+
+    uint32_t code[8];
+    if (a.code_bits <= 5) {
+        const uint32_t w = *reinterpret_cast<const uint32_t*>(a.in.codes + (e0 >> 1));
+        const uint32_t sb = (a.code_bits == 5) ? a.in.sign[e0 >> 3] : 0u;
+        #pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            code[j] = (w >> (4 * j)) & 0xFu;
+            if (a.code_bits == 5) code[j] |= ((sb >> j) & 1u) << 4;
+        }
+    } else {
+        const uint2 w = *reinterpret_cast<const uint2*>(a.in.codes + e0);
+        #pragma unroll
+        for (int j = 0; j < 8; ++j) code[j] = ((j < 4 ? w.x : w.y) >> (8 * (j & 3))) & 0xFFu;
+    }
+    const int scheme = (a.hbq && a.in.scheme) ? a.in.scheme[blk] : 0;
+    uint32_t l2w = 0;
+    if (a.hbq) {
+        const uint8_t* lp = a.in.l2_packed + blk * a.l2_bytes;
+        for (int b = 0; b < a.l2_bytes; ++b) l2w |= (uint32_t)lp[b] << (8 * b);
+    }
+    uint16_t* dp = reinterpret_cast<uint16_t*>(a.deq) + row * a.K + k0;
+    #pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        if (k0 + j >= a.K) break;
+        __half c;
+        if (a.is_int) {
+            int v = (int)code[j];
+            if (v >> (a.code_bits - 1)) v -= (1 << a.code_bits);
+            c = __int2half_rn(v);
+        } else {
+            const int nb = a.ebit + a.mbit;
+            const uint32_t sgn = (code[j] >> nb) & 1u, ef = (code[j] >> a.mbit) & ((1u << a.ebit) - 1u);
+            const uint32_t mf = code[j] & ((1u << a.mbit) - 1u);
+            const int bias = (1 << (a.ebit - 1)) - 1;
+            const float mag = ef == 0 ? ldexpf((float)mf, 1 - bias - a.mbit)
+                                      : ldexpf((float)((1u << a.mbit) + mf), (int)ef - bias - a.mbit);
+            c = __float2half_rn(sgn ? -mag : mag);
+        }
+        __half d;
+        if (a.hbq) {
+            const int u = (int)((k0 % B) + j) / a.l2_block;
+            const int idx = (l2w >> (u * a.l2_bits)) & ((1 << a.l2_bits) - 1);
+            d = __hmul(__hmul(c, __float2half_rn(a.tab[scheme][idx])), sh);
+        } else {
+            d = __hmul(c, sh);
+        }
+        dp[j] = a.out_bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(__half2float(d))) : h_bits(d);
+    }
+}
+
+static float h_rh(float f) { return __half2float(__float2half_rn(f)); }
+
+static int dequantize_launch(const hbq_packed_out* in, int64_t rows, int64_t K, const hbq_format* f,
+                             void* deq, int dtype, cudaStream_t stream)
+{
+    if (!in || !f || !deq || !in->codes || !in->scale_u8) return HBQ_ERR_ARG;
+    if (rows == 0 || K == 0) return HBQ_OK;
+    const int B = f->block_size;
+    DqArgs a;
+    memset(&a, 0, sizeof(a));
+    a.in = *in; a.deq = deq; a.rows = rows; a.K = K;
+    a.nblk = (int)((K + B - 1) / B); a.Kp = (int64_t)a.nblk * B; a.cpr = a.Kp / 8;
+    a.total_chunks = rows * a.cpr;
+    a.out_bf16 = dtype == HBQ_DTYPE_BF16;
+    a.is_int = f->kind == HBQ_KIND_MXINT;
+    a.ebit = f->ebit; a.mbit = f->mbit;
+    if (a.is_int) a.code_bits = f->mbit <= 4 ? 4 : 8;
+    else {
+        a.code_bits = 1 + f->ebit + f->mbit;
+        if (a.code_bits < 4) a.code_bits = 4;
+        if (a.code_bits > 5) a.code_bits = 8;
+    }
+    if (a.is_int && f->mbit != 4 && f->mbit != 8) return HBQ_ERR_UNSUPPORTED;
+    if (a.code_bits == 5 && !in->sign) return HBQ_ERR_ARG;
+    if (f->kind == HBQ_KIND_HBQ) {
+        a.hbq = 1; a.l2_block = f->l2_block_size; a.nl2 = B / f->l2_block_size; a.l2_bits = f->l2_sc_bit;
+        const int tb = a.nl2 * a.l2_bits;
+        if (tb != 8 && tb != 16 && tb != 32) return HBQ_ERR_UNSUPPORTED;
+        if (!in->l2_packed || (f->l2_scheme == HBQ_L2_MIX && !in->scheme)) return HBQ_ERR_ARG;
+        a.l2_bytes = tb / 8;
+        const int n = 1 << f->l2_sc_bit;
+        for (int i = 0; i < n; ++i) {
+            const float r = (float)i;
+            const float fp = h_rh(1.f + h_rh(r / (float)n)), fp10 = h_rh(1.f + h_rh(r / (float)(2 * n)));
+            switch (f->l2_scheme) {
+                case HBQ_L2_POT: a.tab[0][i] = exp2f(r); break;
+                case HBQ_L2_INT: a.tab[0][i] = r + 1.f; break;
+                case HBQ_L2_SIG1: a.tab[0][i] = 1.f + r / 2.f; break;
+                case HBQ_L2_FPM1: a.tab[0][i] = fp; break;
+                case HBQ_L2_FP1: a.tab[0][i] = h_rh(1.f + h_rh((r + 1.f) / (float)n)); break;
+                case HBQ_L2_FPM10: a.tab[0][i] = fp10; break;
+                case HBQ_L2_FPM100: a.tab[0][i] = h_rh(1.f + h_rh(r / (float)(4 * n))); break;
+                case HBQ_L2_MIX: a.tab[0][i] = fp; a.tab[1][i] = fp10; break;
+                default: return HBQ_ERR_ARG;
+            }
+        }
+    }
+    dequantize_kernel<<<(unsigned)((a.total_chunks + 255) / 256), 256, 0, stream>>>(a);
+    HBQ_LAUNCH_CHECK("dequantize_kernel");
+    return HBQ_OK;
+}
+
+}  // namespace hbq
+
+using namespace hbq;
+
+extern "C" {
+
+int hbq_quantize(const void* x, int dtype, int64_t rows, int64_t K, const hbq_format* fmt, void* deq,
+                 int deq_dtype, const hbq_packed_out* out, const float* tensor_amax, void* stream)
+{
+    return quantize_launch(x, dtype, rows, K, fmt, deq, deq_dtype, out, tensor_amax, (cudaStream_t)stream);
+}
+
+int hbq_absmax(const void* x, int dtype, int64_t n, float* amax, void* scratch, void* stream)
+{
+    return absmax_launch(x, dtype, n, amax, scratch, (cudaStream_t)stream);
+}
+int64_t hbq_absmax_scratch_bytes(void) { return absmax_scratch_bytes(); }
+
+int hbq_dequantize(const hbq_packed_out* in, int64_t rows, int64_t K, const hbq_format* fmt, void* deq,
+                   int dtype, void* stream)
+{
+    return dequantize_launch(in, rows, K, fmt, deq, dtype, (cudaStream_t)stream);
+}
+
+int hbq_fp_quant(const void* x, int64_t n, int ebit, int mbit, int allow_subnormal, int use_ceil,
+                 int elem_variant, void* out, void* stream)
+{
+    return fp_quant_launch(x, n, ebit, mbit, allow_subnormal, use_ceil, elem_variant, out, (cudaStream_t)stream);
+}
+
+static int check_gemm_args(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int mode,
+                           int group_k, int group_n)
+{
+    if (!A || !B || !C || M < 0 || N < 0 || K < 0) return HBQ_ERR_ARG;
+    if (mode < HBQ_ACC_FP32 || mode > HBQ_ACC_PSUM_E3M4) return HBQ_ERR_ARG;
+    if (mode >= HBQ_ACC_GROUPED && group_k <= 0) return HBQ_ERR_ARG;
+    if (mode >= HBQ_ACC_PSUM_INT8 && (group_n <= 0 || 64 % group_n != 0)) return HBQ_ERR_ARG;
+    return HBQ_OK;
+}
+
+int hbq_gemm_uses_tensor_cores(int64_t M, int64_t N, int64_t K, int b_is_nk, int mode, int group_k, int group_n)
+{
+    (void)b_is_nk;
+    return gemm_tc_eligible(M, N, K, mode, group_k, group_n) ? 1 : 0;
+}
+
+int64_t hbq_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int b_is_nk, int mode, int group_k, int group_n)
+{
+    if (b_is_nk || !gemm_tc_eligible(M, N, K, mode, group_k, group_n)) return 0;
+    return N * K * 2;
+}
+
+int hbq_gemm(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int b_is_nk, int mode,
+             int group_k, int group_n, const void* bias, void* workspace, int64_t workspace_bytes, void* stream)
+{
+    int rc = check_gemm_args(A, B, C, M, N, K, mode, group_k, group_n);
+    if (rc) return rc;
+    if (M == 0 || N == 0) return HBQ_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    const bool aligned = (((uintptr_t)A | (uintptr_t)B | (uintptr_t)C | (uintptr_t)bias) & 15) == 0;
+    if (K > 0 && aligned && gemm_tc_eligible(M, N, K, mode, group_k, group_n)) {
+        const void* W = B;
+        if (!b_is_nk) {
+            if (!workspace || workspace_bytes < N * K * 2 || ((uintptr_t)workspace & 15)) return HBQ_ERR_WORKSPACE;
+            rc = transpose_launch(B, workspace, K, N, st);
+            if (rc) return rc;
+            W = workspace;
+        }
+        return gemm_tc_launch(A, W, C, M, N, K, mode, group_k, group_n, bias, st);
+    }
+    return gemm_simt_launch(A, B, C, M, N, K, b_is_nk, mode, group_k, group_n, bias, st);
+}
+
+int hbq_gemm_simt(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int b_is_nk, int mode,
+                  int group_k, int group_n, const void* bias, void* stream)
+{
+    int rc = check_gemm_args(A, B, C, M, N, K, mode, group_k, group_n);
+    if (rc) return rc;
+    if (M == 0 || N == 0) return HBQ_OK;
+    return gemm_simt_launch(A, B, C, M, N, K, b_is_nk, mode, group_k, group_n, bias, (cudaStream_t)stream);
+}
+
+int hbq_gemm_status(int* status_host)
+{
+    if (!status_host) return HBQ_ERR_ARG;
+    return gemm_tc_status(status_host);
+}
+int hbq_gemm_status_reset(void) { return gemm_tc_status_reset(); }
+
+const char* hbq_error_string(int code)
+{
+    switch (code) {
+        case HBQ_OK: return "ok";
+        case HBQ_ERR_ARG: return "invalid argument";
+        case HBQ_ERR_UNSUPPORTED: return "format or shape not supported by the CUDA kernels";
+        case HBQ_ERR_CUDA: return "CUDA call failed (see hbq_last_cuda_error)";
+        case HBQ_ERR_ALIGN: return "pointer not 16-byte aligned";
+        case HBQ_ERR_WORKSPACE: return "workspace missing, too small or misaligned";
+        case HBQ_ERR_DEVICE: return "device error reported by a kernel";
+    }
+    return "unknown error";
+}
+const char* hbq_last_cuda_error(void) { return g_last_cuda_error; }
+int hbq_version(void) { return 100; }
+int64_t hbq_launch_count(void) { return (int64_t)g_launches.load(); }
+
+}  // extern "C"

@@ -1,0 +1,36 @@
+// Shared helpers of the hbq_b200 CUDA library (sm_100a only).
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include "../../include/hbq_b200.h"
+
+namespace hbq {
+
+// Bookkeeping shared by all translation units (defined in api.cu).
+void note_launch(int n = 1);
+int set_cuda_error(cudaError_t e, const char* where);
+
+#define HBQ_CUDA_TRY(expr)                                                     \
+    do {                                                                       \
+        cudaError_t _e = (expr);                                               \
+        if (_e != cudaSuccess) return ::hbq::set_cuda_error(_e, #expr);        \
+    } while (0)
+
+#define HBQ_LAUNCH_CHECK(what)                                                 \
+    do {                                                                       \
+        cudaError_t _e = cudaGetLastError();                                   \
+        if (_e != cudaSuccess) return ::hbq::set_cuda_error(_e, what);         \
+        ::hbq::note_launch();                                                  \
+    } while (0)
+
+__device__ __forceinline__ uint32_t h2_bits(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
+__device__ __forceinline__ __half2 bits_h2(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
+__device__ __forceinline__ uint16_t h_bits(__half h) { return __half_as_ushort(h); }
+__device__ __forceinline__ __half bits_h(uint16_t u) { return __ushort_as_half(u); }
+
+// Round an fp32 value to fp16 and back: the per-op rounding of a torch fp16 elementwise op.
+__device__ __forceinline__ float rh(float f) { return __half2float(__float2half_rn(f)); }
+
+}  // namespace hbq

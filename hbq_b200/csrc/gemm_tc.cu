@@ -1,0 +1,517 @@
+// tcgen05 / TMEM GEMM with the reference's accumulation models (blockquant_ext_src/gemm.cu).
+//
+// C[M,N] = A[M,K] * W[N,K]^T, fp16 operands (both K-major), fp16 output.
+//
+// The reference accumulates exact fp16xfp16 products in fp32 inside a K-chunk of `group_k`
+// and then folds the chunk's partial sum into an fp16 running sum, optionally after fake
+// quantising it (INT8 / E3M4 with a power-of-two scale per `group_n` columns).  Here each
+// K-chunk is one accumulation in tensor memory: kind::f16 MMAs with fp32 accumulators, the
+// first MMA of a chunk overwriting.  Two 128x256 fp32 accumulators (all 512 TMEM columns)
+// alternate, so the epilogue warps drain chunk c (tcgen05.ld -> round / quantise -> fp16 add
+// in registers) while the tensor core computes chunk c+1.
+//
+// One persistent CTA per SM, 320 threads:
+//   warp 0      TMA producer: 4-stage ring of {A 128x64, W 256x64} fp16 tiles, 128B swizzle
+//   warp 1      TMEM allocation and MMA issue (one lane)
+//   warps 2-9   epilogue: warp w owns TMEM lanes 32*(w%4).. and column half (w-2)/4
+// Every mbarrier wait is bounded: on expiry the kernel records a status word, all roles leave
+// their loops, TMEM is freed and the kernel returns.
+#include "common.cuh"
+#include <cuda.h>
+#include <math.h>
+
+namespace hbq {
+
+constexpr int BM = 128, BN = 256, BK = 64, NSTAGE = 4;
+constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int TC_THREADS = 320;
+constexpr int EPI_WARPS = 8;
+constexpr uint32_t SMEM_BYTES = NSTAGE * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
+
+__device__ int g_tc_status;   // 0 = ok; otherwise the code of the wait that expired
+
+// ---- PTX wrappers ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n .reg .pred p;\n"
+        " mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        " selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ unsigned long long gtime_ns()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait.  Returns false when the limit expired or another role already gave up.
+__device__ __noinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code)
+{
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = gtime_ns();
+    for (uint32_t it = 1;; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 63u) == 0u) {
+            if (*abort_flag) return false;
+            if (gtime_ns() - t0 > WAIT_LIMIT_NS) {
+                *abort_flag = 1;
+                atomicCAS(&g_tc_status, 0, code);
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_commit(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// 32 consecutive fp32 columns of this thread's TMEM lane
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, float* v)
+{
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    #pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor: K-major tile, 128-byte swizzle, rows 128 B apart, 8-row
+// groups 1024 B apart (SBO = 64 x 16 B), LBO = 1 (unused for swizzled K-major), version 1.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)64 << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// kind::f16: D fp32, A/B fp16, both K-major, M = 128, N = 256
+constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+
+// ---- epilogue arithmetic ---------------------------------------------------------------------
+// INT8 partial-sum fake quantisation of `n` consecutive columns (gemm.cu:1145-1152, 1198-1249):
+// scale = 2^(floor(log2 max|v|) - 6) (1 for an all-zero run), q = clamp(rint(v / scale), +-127).
+// v / scale is exact, so rint is one FMA against 1.5 * 2^23.  Non-finite partial sums are not
+// given the reference's special treatment.
+template <int GN>
+__device__ __forceinline__ void psum_int8_run(float* v)
+{
+    float mx = 0.f;
+    #pragma unroll
+    for (int i = 0; i < GN; ++i) mx = fmaxf(mx, fabsf(v[i]));
+    const uint32_t e = (__float_as_uint(mx) >> 23) & 0xFFu;
+    const float scale = mx > 0.f ? __uint_as_float((e - 6u) << 23) : 1.f;
+    const float inv = mx > 0.f ? __uint_as_float((260u - e) << 23) : 1.f;
+    #pragma unroll
+    for (int i = 0; i < GN; ++i) {
+        float q = __fmaf_rn(v[i], inv, 12582912.f) - 12582912.f;
+        q = fminf(fmaxf(q, -127.f), 127.f);
+        v[i] = q * scale;
+    }
+}
+
+__device__ float tc_e3m4(float x, float scale)
+{
+    const float sg = copysignf(1.f, x), a = fabsf(x);
+    if (a == 0.f) return copysignf(0.f, x);
+    const float y = __fdiv_rn(a, scale);
+    if (y < 0.5f * 0.015625f) return 0.f;
+    if (y >= 0.25f) {
+        int e = max(-2, min(3, ilogbf(y)));
+        float p = ldexpf(1.f, e);
+        float m = nearbyintf((__fdiv_rn(y, p) - 1.f) * 16.f);
+        if (m >= 16.f) { m = 0.f; ++e; if (e > 3) { e = 3; m = 15.f; } p = ldexpf(1.f, e); }
+        return sg * fminf((1.f + m * 0.0625f) * p, 15.5f) * scale;
+    }
+    const float m = nearbyintf(y * 64.f);
+    if (m <= 0.f) return 0.f;
+    if (m >= 16.f) return sg * 0.25f * scale;
+    return sg * (m * 0.0625f) * 0.25f * scale;
+}
+
+template <int GN>
+__device__ __forceinline__ void psum_e3m4_run(float* v)
+{
+    float mx = 0.f;
+    #pragma unroll
+    for (int i = 0; i < GN; ++i) mx = fmaxf(mx, fabsf(v[i]));
+    const float scale = mx > 0.f ? ldexpf(1.f, ilogbf(mx) - 3) : 1.f;
+    #pragma unroll
+    for (int i = 0; i < GN; ++i) v[i] = tc_e3m4(v[i], scale);
+}
+
+template <int MODE, int GN>
+__device__ __forceinline__ void psum_quant32(float* v)
+{
+    if (MODE == HBQ_ACC_PSUM_INT8) {
+        #pragma unroll
+        for (int c = 0; c < 32; c += GN) psum_int8_run<GN>(v + c);
+    } else if (MODE == HBQ_ACC_PSUM_E3M4) {
+        #pragma unroll
+        for (int c = 0; c < 32; c += GN) psum_e3m4_run<GN>(v + c);
+    }
+}
+
+struct TcArgs {
+    __half* C;
+    const __half* bias;
+    int M, N, K;
+    int tiles_m, tiles_n;
+    int k_stages;        // ceil(K / 64)
+    int chunk_k16;       // MMAs (K = 16 each) per accumulation chunk
+};
+
+// ---- the kernel ------------------------------------------------------------------------------
+template <int MODE, int GN>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+               const TcArgs args)
+{
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t tiles = (raw + 1023u) & ~1023u;                  // 1024-byte aligned tile ring
+    uint8_t* ctrl = smem_raw + (tiles - raw) + NSTAGE * STAGE_BYTES;
+    const uint32_t ctrl_u = tiles + NSTAGE * STAGE_BYTES;
+    // control block: full[4] empty[4] tmem_full[2] tmem_empty[2] (8 B each), tmem base, abort flag
+    const uint32_t bar_full = ctrl_u, bar_empty = ctrl_u + 8 * NSTAGE;
+    const uint32_t bar_tfull = ctrl_u + 16 * NSTAGE, bar_tempty = bar_tfull + 16;
+    uint32_t* tmem_base_smem = reinterpret_cast<uint32_t*>(ctrl + 16 * NSTAGE + 32);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(ctrl + 16 * NSTAGE + 40);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < NSTAGE; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(bar_tfull + 8 * b, 1); mbar_init(bar_tempty + 8 * b, EPI_WARPS); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;"
+                     ::"r"(smem_u32(tmem_base_smem)) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_base_smem;
+
+    const int total_tiles = args.tiles_m * args.tiles_n;
+    const int total_k16 = args.k_stages * (BK / 16);
+
+    if (warp == 0) {
+        // ================= TMA producer =================
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                const int m0 = (t % args.tiles_m) * BM, n0 = (t / args.tiles_m) * BN;
+                for (int ks = 0; ks < args.k_stages; ++ks) {
+                    if (!(ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, 1))) break;
+                    const uint32_t sa = tiles + stage * STAGE_BYTES, sb = sa + A_BYTES;
+                    mbar_expect_tx(bar_full + 8 * stage, STAGE_BYTES);
+                    tma_load_2d(sa, &mapA, ks * BK, m0, bar_full + 8 * stage);
+                    tma_load_2d(sb, &mapB, ks * BK, n0, bar_full + 8 * stage);
+                    if (++stage == NSTAGE) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ================= MMA issue =================
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            uint32_t chunk = 0;              // running chunk counter: buffer = chunk & 1
+            bool ok = true;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                int in_chunk = 0;
+                for (int ks = 0; ks < args.k_stages && ok; ++ks) {
+                    if (!(ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, 2))) break;
+                    tc_fence_after();
+                    const uint32_t sa = tiles + stage * STAGE_BYTES, sb = sa + A_BYTES;
+                    #pragma unroll
+                    for (int kk = 0; kk < BK / 16; ++kk) {
+                        const uint32_t buf = chunk & 1u;
+                        if (in_chunk == 0) {
+                            // the epilogue must have drained this accumulator's previous chunk
+                            if (!(ok = mbar_wait(bar_tempty + 8 * buf, ((chunk >> 1) & 1u) ^ 1u, abort_flag, 3))) break;
+                            tc_fence_after();
+                        }
+                        tc_mma_f16(tmem_base + buf * BN, umma_desc(sa + kk * 32), umma_desc(sb + kk * 32),
+                                   IDESC, in_chunk != 0);
+                        ++in_chunk;
+                        const int k16 = ks * (BK / 16) + kk;
+                        if (in_chunk == args.chunk_k16 || k16 + 1 == total_k16) {
+                            tc_commit(bar_tfull + 8 * buf);
+                            in_chunk = 0;
+                            ++chunk;
+                        }
+                    }
+                    if (!ok) break;
+                    tc_commit(bar_empty + 8 * stage);       // smem slot free once these MMAs retire
+                    if (++stage == NSTAGE) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else {
+        // ================= epilogue =================
+        const int ew = warp - 2;
+        const int quarter = warp & 3;            // TMEM lanes this warp may touch
+        const int chalf = ew >> 2;               // column half of the 256-wide tile
+        const int chunks_per_tile = (total_k16 + args.chunk_k16 - 1) / args.chunk_k16;
+        uint32_t chunk = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+            const int m0 = (t % args.tiles_m) * BM, n0 = (t / args.tiles_m) * BN;
+            __half2 acc[64];
+            #pragma unroll
+            for (int i = 0; i < 64; ++i) acc[i] = __float2half2_rn(0.f);
+            for (int c = 0; c < chunks_per_tile; ++c, ++chunk) {
+                const uint32_t buf = chunk & 1u;
+                ok = mbar_wait(bar_tfull + 8 * buf, (chunk >> 1) & 1u, abort_flag, 4);
+                ok = __all_sync(0xFFFFFFFFu, ok);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN + chalf * 128;
+                #pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    float v[32];
+                    tc_ld32(taddr + q * 32, v);
+                    if (q == 3) {
+                        // all of this warp's reads of the buffer are complete: hand it back
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
+                    }
+                    if (MODE >= HBQ_ACC_PSUM_INT8) psum_quant32<MODE, GN>(v);
+                    #pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const __half2 p = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+                        acc[q * 16 + i] = (MODE == HBQ_ACC_FP32) ? p : __hadd2(acc[q * 16 + i], p);
+                    }
+                }
+            }
+            if (!ok) break;
+            // ---- write the thread's row: 128 columns starting at n0 + chalf*128 ----
+            const int row = m0 + quarter * 32 + lane;
+            const int col0 = n0 + chalf * 128;
+            if (row < args.M) {
+                __half* cp = args.C + (int64_t)row * args.N + col0;
+                #pragma unroll
+                for (int g = 0; g < 16; ++g) {
+                    const int col = col0 + g * 8;
+                    if (col >= args.N) break;
+                    __half2 o[4] = {acc[4 * g], acc[4 * g + 1], acc[4 * g + 2], acc[4 * g + 3]};
+                    if (args.bias) {
+                        const uint4 bv = *reinterpret_cast<const uint4*>(args.bias + col);
+                        o[0] = __hadd2(o[0], bits_h2(bv.x)); o[1] = __hadd2(o[1], bits_h2(bv.y));
+                        o[2] = __hadd2(o[2], bits_h2(bv.z)); o[3] = __hadd2(o[3], bits_h2(bv.w));
+                    }
+                    *reinterpret_cast<uint4*>(cp + g * 8) =
+                        make_uint4(h2_bits(o[0]), h2_bits(o[1]), h2_bits(o[2]), h2_bits(o[3]));
+                }
+            }
+        }
+    }
+
+    // ---- teardown: every role arrives here, also after an expired wait ----
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        // let TMA copies that may still be in flight land before the CTA's smem is released
+        const unsigned long long t0 = gtime_ns();
+        while (gtime_ns() - t0 < 200000ull) { }
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
+    }
+}
+
+// ---- transpose [K,N] -> [N,K] ------------------------------------------------------------------
+__global__ void __launch_bounds__(256) transpose_kernel(const __half* __restrict__ in, __half* __restrict__ out,
+                                                        int R, int Ccols)
+{
+    __shared__ __half tile[64][66];
+    const int r0 = blockIdx.y * 64, c0 = blockIdx.x * 64;
+    for (int i = threadIdx.x; i < 64 * 64; i += 256) {
+        const int r = i / 64, c = i % 64;
+        if (r0 + r < R && c0 + c < Ccols) tile[r][c] = in[(int64_t)(r0 + r) * Ccols + c0 + c];
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < 64 * 64; i += 256) {
+        const int c = i / 64, r = i % 64;
+        if (r0 + r < R && c0 + c < Ccols) out[(int64_t)(c0 + c) * R + r0 + r] = tile[r][c];
+    }
+}
+
+// ---- host side -----------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn()
+{
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) == cudaSuccess &&
+            qr == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// fp16 row-major [rows, K] matrix, boxes of box_rows x 64 elements, 128-byte swizzle, zero fill
+static int make_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t K, int box_rows)
+{
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return HBQ_ERR_CUDA;
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? HBQ_OK : HBQ_ERR_CUDA;
+}
+
+bool gemm_tc_eligible(int64_t M, int64_t N, int64_t K, int mode, int group_k, int group_n)
+{
+    if (M <= 0 || N <= 0 || K <= 0 || M > (1ll << 30) || N > (1ll << 30) || K > (1ll << 30)) return false;
+    if ((K % 8) != 0 || (N % 8) != 0) return false;
+    if (mode == HBQ_ACC_FP16) return false;                 // the per-product fp16 chain has no tensor-core form
+    if (mode == HBQ_ACC_FP32) return true;
+    if (group_k < 16 || (group_k % 16) != 0) return false;
+    if (mode >= HBQ_ACC_PSUM_INT8 && !(group_n == 4 || group_n == 8 || group_n == 16 || group_n == 32)) return false;
+    return true;
+}
+
+template <int MODE, int GN>
+static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcArgs& args, int grid, cudaStream_t stream)
+{
+    // per device, and cheap: set on every launch rather than caching per process
+    HBQ_CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel<MODE, GN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    gemm_tc_kernel<MODE, GN><<<grid, TC_THREADS, SMEM_BYTES, stream>>>(ma, mb, args);
+    HBQ_LAUNCH_CHECK("gemm_tc_kernel");
+    return HBQ_OK;
+}
+
+int transpose_launch(const void* in, void* out, int64_t R, int64_t Ccols, cudaStream_t stream)
+{
+    const dim3 grid((unsigned)((Ccols + 63) / 64), (unsigned)((R + 63) / 64));
+    transpose_kernel<<<grid, 256, 0, stream>>>((const __half*)in, (__half*)out, (int)R, (int)Ccols);
+    HBQ_LAUNCH_CHECK("transpose_kernel");
+    return HBQ_OK;
+}
+
+// A [M,K], W [N,K], both fp16 row-major and 16-byte aligned.
+int gemm_tc_launch(const void* A, const void* W, void* C, int64_t M, int64_t N, int64_t K, int mode,
+                   int group_k, int group_n, const void* bias, cudaStream_t stream)
+{
+    if (!gemm_tc_eligible(M, N, K, mode, group_k, group_n)) return HBQ_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(C) |
+         reinterpret_cast<uintptr_t>(bias)) & 15)
+        return HBQ_ERR_ALIGN;
+    CUtensorMap ma, mb;
+    int rc = make_map(&ma, A, M, K, BM);
+    if (rc) return rc;
+    rc = make_map(&mb, W, N, K, BN);
+    if (rc) return rc;
+
+    TcArgs args;
+    args.C = (__half*)C; args.bias = (const __half*)bias;
+    args.M = (int)M; args.N = (int)N; args.K = (int)K;
+    args.tiles_m = (int)((M + BM - 1) / BM); args.tiles_n = (int)((N + BN - 1) / BN);
+    args.k_stages = (int)((K + BK - 1) / BK);
+    args.chunk_k16 = (mode == HBQ_ACC_FP32) ? args.k_stages * (BK / 16) : group_k / 16;
+
+    int dev = 0, sms = 0;
+    HBQ_CUDA_TRY(cudaGetDevice(&dev));
+    HBQ_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    const int64_t total = (int64_t)args.tiles_m * args.tiles_n;
+    const int grid = (int)(total < sms ? total : sms);
+
+    switch (mode) {
+        case HBQ_ACC_FP32: return launch_tc<HBQ_ACC_FP32, 32>(ma, mb, args, grid, stream);
+        case HBQ_ACC_GROUPED: return launch_tc<HBQ_ACC_GROUPED, 32>(ma, mb, args, grid, stream);
+        case HBQ_ACC_PSUM_INT8:
+            switch (group_n) {
+                case 4: return launch_tc<HBQ_ACC_PSUM_INT8, 4>(ma, mb, args, grid, stream);
+                case 8: return launch_tc<HBQ_ACC_PSUM_INT8, 8>(ma, mb, args, grid, stream);
+                case 16: return launch_tc<HBQ_ACC_PSUM_INT8, 16>(ma, mb, args, grid, stream);
+                default: return launch_tc<HBQ_ACC_PSUM_INT8, 32>(ma, mb, args, grid, stream);
+            }
+        case HBQ_ACC_PSUM_E3M4:
+            switch (group_n) {
+                case 4: return launch_tc<HBQ_ACC_PSUM_E3M4, 4>(ma, mb, args, grid, stream);
+                case 8: return launch_tc<HBQ_ACC_PSUM_E3M4, 8>(ma, mb, args, grid, stream);
+                case 16: return launch_tc<HBQ_ACC_PSUM_E3M4, 16>(ma, mb, args, grid, stream);
+                default: return launch_tc<HBQ_ACC_PSUM_E3M4, 32>(ma, mb, args, grid, stream);
+            }
+    }
+    return HBQ_ERR_ARG;
+}
+
+int gemm_tc_status(int* host_out)
+{
+    HBQ_CUDA_TRY(cudaMemcpyFromSymbol(host_out, g_tc_status, sizeof(int)));
+    return HBQ_OK;
+}
+int gemm_tc_status_reset()
+{
+    const int z = 0;
+    HBQ_CUDA_TRY(cudaMemcpyToSymbol(g_tc_status, &z, sizeof(int)));
+    return HBQ_OK;
+}
+
+}  // namespace hbq

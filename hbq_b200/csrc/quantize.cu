@@ -1,0 +1,842 @@
+// Block quantize-dequantize kernels: MXFP / NVFP / MXINT / HBQ (two-level scale).
+//
+// Reference semantics (src/quantizer.py): eager torch ops on fp16 tensors, i.e. every
+// elementwise op rounds its result to fp16 and reductions accumulate in fp32.  The kernels
+// reproduce that op by op with fp16 hardware arithmetic (one rounding per instruction) so the
+// fake-quantised tensor, the shared scales, the micro-scale indices and the scheme bits are
+// bit-identical to the reference's.
+//
+// Work decomposition: one thread owns 8 consecutive elements of a row (one 128-bit load);
+// the G = block_size/8 lanes that own one quantisation block reduce with warp shuffles, so a
+// tensor is read once from HBM and every output is written once.
+#include "common.cuh"
+#include <math.h>
+
+namespace hbq {
+
+// ------------------------------------------------------------------------------------------
+// Scalar building blocks (literal restatement of the reference's op chain; used for the shared
+// scale -- once per block -- and for element formats without a packed fast path).
+// ------------------------------------------------------------------------------------------
+
+__device__ __forceinline__ float sgnf(float x) { return x > 0.f ? 1.f : (x < 0.f ? -1.f : 0.f); }
+
+// floor(log2(t)) as evaluated on an fp16 tensor: log2 in fp32, rounded to fp16, then floor.
+__device__ __forceinline__ float log2_h(float t) { return rh(log2f(t)); }
+
+struct FpFmt {
+    int ebit, mbit, emax, emin;
+    float min_norm, thr, mant_shift, mant_max;
+};
+
+__host__ __device__ inline FpFmt make_fpfmt(int ebit, int mbit)
+{
+    FpFmt f;
+    f.ebit = ebit; f.mbit = mbit;
+    f.emax = (ebit == 5) ? 15 : (1 << (ebit - 1));
+    f.emin = 2 - (1 << (ebit - 1));
+    f.min_norm = (ebit == 1) ? 1.f : ldexpf(1.f, f.emin);
+    f.thr = f.min_norm - ldexpf(1.f, -(mbit + 1) + f.emin);
+    f.mant_shift = ldexpf(1.f, mbit);
+    f.mant_max = f.mant_shift - 1.f;
+    return f;
+}
+
+// make_fp_quant closure (src/quantizer.py:202-255; elem_variant = 1: the "+0.5004" rounding,
+// which the fp16 add sees as 0.50048828125) and the free function fp_quant
+// (src/quantizer.py:259-328; elem_variant = 0: "+0.5").  x holds an fp16 value.
+// *code receives {exp field, mantissa} as the detailed output defines them.
+__device__ float fpq_chain(float x, const FpFmt& f, bool allow_sub, bool use_ceil,
+                           bool elem_variant, int* code)
+{
+    const float ax = fabsf(x);
+    const bool is_zero = (x == 0.f);
+    const bool promote = (ax < f.min_norm) && (ax >= f.thr);
+    const bool below = (ax < f.thr) && !is_zero;
+    const bool sub = allow_sub && below;
+    const bool under = !allow_sub && below;
+
+    float e = floorf(log2_h(rh(ax + (is_zero ? 1.f : 0.f))));
+    e = fminf(fmaxf(e, (float)f.emin), (float)f.emax);
+    const float p2 = rh(exp2f(e));
+    const float sg = sgnf(x);
+    const float xs = rh(__fdiv_rn(x, p2));
+    const float mant = sub ? rh(xs * f.mant_shift) : rh(rh(xs - sg) * f.mant_shift);
+    const float am = fabsf(mant);
+    float mr;
+    if (use_ceil) mr = ceilf(am);
+    else mr = floorf(rh(am + (elem_variant ? 0.50048828125f : 0.5f)));
+    const bool overflow = (mr > f.mant_max) && (e != (float)f.emax);
+    mr = fminf(mr, f.mant_max);
+    if (is_zero || under || overflow || promote) mr = 0.f;
+    if (overflow) e += 1.f;
+    const float sm = sg * mr;
+    const float p2b = rh(exp2f(e));
+    float xq = sub ? rh(rh(__fdiv_rn(sm, f.mant_shift)) * p2b)
+                   : rh(rh(rh(__fdiv_rn(sm, f.mant_shift)) + sg) * p2b);
+    if (is_zero || under) xq = 0.f;
+    if (f.ebit == 4 && f.mbit == 3) xq = fminf(fmaxf(xq, -448.f), 448.f);
+    if (code) {
+        int ef = (int)e + ((1 << (f.ebit - 1)) - 1);
+        if (is_zero || under || sub) ef = 0;
+        *code = (ef << f.mbit) | (int)mr;
+    }
+    return xq;
+}
+
+// ------------------------------------------------------------------------------------------
+// Packed element quantizer for E2Mx (x = MB mantissa bits), two values per call.
+//
+// For |b| >= 1 the reference's mantissa rounding floor(fp16(m + 0.50048828125)) is exactly
+// round-half-up to MB mantissa bits with carry into the exponent, saturating at the format
+// maximum: an integer add + mask on the fp16 bit pattern.  Below 1 the reference computes
+// k = floor(fp16(|b| * 2^MB + 0.50048828125)) and returns k / 2^MB; one HFMA2 reproduces that
+// rounding literally (the product is exact), including the thresholds that sit 3 and 1 ulp
+// below the midpoints and the value 1.0 for [1 - 2^-(MB+1), 1).  E2M1 only: |b| = 0x39FF
+// gives k = 2 in the subnormal branch, which the reference turns into 0.
+// ZERO_SIGN: give b = -0 the reference's +0 result (the other callers only square it).
+// ------------------------------------------------------------------------------------------
+template <int MB, bool ZERO_SIGN>
+__device__ __forceinline__ __half2 q2_e2(__half2 b)
+{
+    constexpr uint32_t kHalf = (0x0200u >> MB) * 0x00010001u;
+    constexpr uint32_t kMask = ~(((0x0400u >> MB) - 1u) * 0x00010001u);
+    constexpr uint32_t kMax = (0x4400u | (((1u << MB) - 1u) << (10 - MB))) * 0x00010001u;
+    const uint32_t u = h2_bits(b);
+    const uint32_t a = u & 0x7FFF7FFFu;
+    uint32_t sgn = u & 0x80008000u;
+    const __half2 ab = bits_h2(a);
+    // normal range
+    const __half2 n = __hmin2(bits_h2((a + kHalf) & kMask), bits_h2(kMax));
+    // below 1
+    const __half2 v = __hfma2(ab, bits_h2(((uint32_t)(0x3C00u + (MB << 10))) * 0x00010001u),
+                              bits_h2(0x38013801u));
+    __half2 s = __hmul2(h2floor(v), bits_h2(((uint32_t)(0x3C00u - (MB << 10))) * 0x00010001u));
+    uint32_t sb = h2_bits(s);
+    if (MB == 1) sb &= ~__heq2_mask(ab, bits_h2(0x39FF39FFu));
+    const uint32_t m = __hge2_mask(ab, bits_h2(0x3C003C00u));
+    uint32_t r = (h2_bits(n) & m) | (sb & ~m);
+    if (ZERO_SIGN) sgn &= __hne2_mask(ab, bits_h2(0u));
+    return bits_h2(r | sgn);
+}
+
+// Code magnitudes {exp field, mantissa} of two quantised E2Mx values, one per 16-bit half.
+template <int MB>
+__device__ __forceinline__ uint32_t code2_e2(__half2 c)
+{
+    const uint32_t a = h2_bits(c) & 0x7FFF7FFFu;
+    const uint32_t nrm = ((a - 0x38003800u) >> (10 - MB)) & (((1u << (MB + 2)) - 1u) * 0x00010001u);
+    // below 1: k = c * 2^MB, read from the low mantissa bits of k + 1024
+    const __half2 k = __hfma2(bits_h2(a), bits_h2(((uint32_t)(0x3C00u + (MB << 10))) * 0x00010001u),
+                              bits_h2(0x64006400u));
+    const uint32_t sub = h2_bits(k) & 0x00FF00FFu;
+    const uint32_t m = __hge2_mask(bits_h2(a), bits_h2(0x3C003C00u));
+    return (nrm & m) | (sub & ~m);
+}
+
+// ------------------------------------------------------------------------------------------
+// Kernel arguments
+// ------------------------------------------------------------------------------------------
+struct QArgs {
+    const void* x;
+    void* deq;
+    hbq_packed_out out;
+    const float* tensor_amax;
+    int64_t rows, K, Kp;
+    int64_t cpr;            // 8-element chunks per (padded) row
+    int64_t total_chunks;
+    int in_bf16, out_bf16;
+    int aligned;            // 128-bit loads/stores are legal
+    int G;                  // lanes per block = block_size / 8
+    int nblk;
+    hbq_format f;
+    // HBQ
+    int nscheme, nc;
+    float tab[2][16];
+    float inv_tab[2][16];
+    float ele_max[2];
+    // scale
+    int scale_fast_e5m3;    // closed-form E5M3 round-half-up
+    int exact_div;          // use IEEE division for x / scale (scale mantissa wider than 4 bits)
+    float sc_lo, sc_hi;     // clip range of the FP scale
+    float elem_max;         // MXFP FP-scale divisor / MXINT FP-scale divisor
+    double pts_den;         // per-tensor scale: element max * scale max (src/quantizer.py:517-523)
+    int pot_emin, pot_emax, pot_sub;
+    int code_bits;          // bits per element code
+};
+
+struct Chunk {
+    __half2 h[4];
+};
+
+__device__ __forceinline__ Chunk load_chunk(const QArgs& a, int64_t row, int64_t k0)
+{
+    Chunk c;
+    if (k0 >= a.K) {
+        #pragma unroll
+        for (int p = 0; p < 4; ++p) c.h[p] = bits_h2(0u);
+        return c;
+    }
+    const int64_t off = row * a.K + k0;
+    if (a.aligned && k0 + 8 <= a.K) {
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(
+            reinterpret_cast<const uint16_t*>(a.x) + off));
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        if (!a.in_bf16) {
+            #pragma unroll
+            for (int p = 0; p < 4; ++p) c.h[p] = bits_h2(w[p]);
+        } else {
+            #pragma unroll
+            for (int p = 0; p < 4; ++p)
+                c.h[p] = __floats2half2_rn(__uint_as_float(w[p] << 16),
+                                           __uint_as_float(w[p] & 0xFFFF0000u));
+        }
+        return c;
+    }
+    const uint16_t* xp = reinterpret_cast<const uint16_t*>(a.x) + off;
+    float v[8];
+    #pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        uint16_t b = (k0 + j < a.K) ? xp[j] : (uint16_t)0;
+        v[j] = a.in_bf16 ? __uint_as_float((uint32_t)b << 16) : __half2float(bits_h(b));
+    }
+    #pragma unroll
+    for (int p = 0; p < 4; ++p) c.h[p] = __floats2half2_rn(v[2 * p], v[2 * p + 1]);
+    return c;
+}
+
+__device__ __forceinline__ void store_deq(const QArgs& a, int64_t row, int64_t k0, const __half2* d)
+{
+    if (!a.deq || k0 >= a.K) return;
+    uint32_t w[4];
+    if (!a.out_bf16) {
+        #pragma unroll
+        for (int p = 0; p < 4; ++p) w[p] = h2_bits(d[p]);
+    } else {
+        #pragma unroll
+        for (int p = 0; p < 4; ++p) {
+            const float2 f = __half22float2(d[p]);
+            __nv_bfloat162 b = __floats2bfloat162_rn(f.x, f.y);
+            w[p] = *reinterpret_cast<uint32_t*>(&b);
+        }
+    }
+    uint16_t* dp = reinterpret_cast<uint16_t*>(a.deq) + row * a.K + k0;
+    if (a.aligned && k0 + 8 <= a.K) {
+        *reinterpret_cast<uint4*>(dp) = make_uint4(w[0], w[1], w[2], w[3]);
+    } else {
+        #pragma unroll
+        for (int j = 0; j < 8; ++j)
+            if (k0 + j < a.K) dp[j] = (uint16_t)(w[j >> 1] >> ((j & 1) * 16));
+    }
+}
+
+// codes: mag[p] holds two code magnitudes (one per 16-bit half), sgn[p] the fp16 sign bits.
+// TWOS: integer elements, stored as two's complement of (sign, magnitude).
+template <bool TWOS>
+__device__ __forceinline__ void store_codes(const QArgs& a, int64_t row, int64_t k0,
+                                            const uint32_t* mag_in, const uint32_t* sgn)
+{
+    if (!a.out.codes) return;
+    uint32_t mag[4];
+    #pragma unroll
+    for (int p = 0; p < 4; ++p) {
+        mag[p] = mag_in[p];
+        if (TWOS) {
+            const uint32_t cm = (1u << a.code_bits) - 1u;
+            uint32_t lo = mag[p] & 0xFFFFu, hi = mag[p] >> 16;
+            if ((sgn[p] >> 15) & 1u) lo = (0u - lo) & cm;
+            if (sgn[p] >> 31) hi = (0u - hi) & cm;
+            mag[p] = lo | (hi << 16);
+        }
+    }
+    const int64_t e0 = row * a.Kp + k0;
+    const int bits = a.code_bits;
+    if (bits <= 5) {
+        uint32_t w = 0, sb = 0;
+        #pragma unroll
+        for (int p = 0; p < 4; ++p) {
+            uint32_t lo = mag[p] & 0xFFFFu, hi = mag[p] >> 16;
+            const uint32_t slo = (sgn[p] >> 15) & 1u, shi = sgn[p] >> 31;
+            if (bits == 4 && !TWOS) { lo |= slo << 3; hi |= shi << 3; }
+            w |= ((lo & 0xFu) | ((hi & 0xFu) << 4)) << (8 * p);
+            sb |= (slo | (shi << 1)) << (2 * p);
+        }
+        *reinterpret_cast<uint32_t*>(a.out.codes + (e0 >> 1)) = w;
+        if (bits == 5 && a.out.sign) a.out.sign[e0 >> 3] = (uint8_t)sb;
+    } else {
+        uint32_t w[2] = {0, 0};
+        #pragma unroll
+        for (int p = 0; p < 4; ++p) {
+            uint32_t lo = mag[p] & 0xFFFFu, hi = mag[p] >> 16;
+            if (!TWOS) {
+                lo |= ((sgn[p] >> 15) & 1u) << (bits - 1);
+                hi |= (sgn[p] >> 31) << (bits - 1);
+            }
+            w[p >> 1] |= ((lo & 0xFFu) | ((hi & 0xFFu) << 8)) << (16 * (p & 1));
+        }
+        *reinterpret_cast<uint2*>(a.out.codes + e0) = make_uint2(w[0], w[1]);
+    }
+}
+
+// (row, chunk-in-row) of a flat chunk index; 32-bit division when the tensor allows it.
+__device__ __forceinline__ void split_chunk(const QArgs& a, int64_t ci, int64_t& row, int64_t& c)
+{
+    if (a.total_chunks <= 0x7FFFFFFFll) {
+        const uint32_t r = (uint32_t)ci / (uint32_t)a.cpr;
+        row = r; c = (uint32_t)ci - r * (uint32_t)a.cpr;
+    } else { row = ci / a.cpr; c = ci % a.cpr; }
+}
+
+__device__ __forceinline__ float group_max(float v, int G)
+{
+    for (int off = G >> 1; off >= 1; off >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, off));
+    return v;
+}
+__device__ __forceinline__ float group_sum(float v, int lanes)
+{
+    for (int off = lanes >> 1; off >= 1; off >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off);
+    return v;
+}
+__device__ __forceinline__ uint32_t group_or(uint32_t v, int G)
+{
+    for (int off = G >> 1; off >= 1; off >>= 1) v |= __shfl_xor_sync(0xFFFFFFFFu, v, off);
+    return v;
+}
+
+__device__ __forceinline__ float chunk_absmax(const Chunk& c)
+{
+    __half2 m = __hmax2(bits_h2(h2_bits(c.h[0]) & 0x7FFF7FFFu), bits_h2(h2_bits(c.h[1]) & 0x7FFF7FFFu));
+    m = __hmax2(m, bits_h2(h2_bits(c.h[2]) & 0x7FFF7FFFu));
+    m = __hmax2(m, bits_h2(h2_bits(c.h[3]) & 0x7FFF7FFFu));
+    const float2 f = __half22float2(m);
+    return fmaxf(f.x, f.y);
+}
+
+// FP shared scale: clip to [sc_lo, sc_hi] then fp_quant (HBQQuantizer.quant_scale,
+// src/quantizer.py:735-739; MXFPQuantizer.get_shared_scale, src/quantizer.py:504-509).
+// For E5M3 without subnormals and without ceil the chain reduces to round-half-up of the
+// 3-bit mantissa on the fp16 pattern (checked over all fp16 inputs by the tests).
+__device__ __forceinline__ float quant_scale_fp(const QArgs& a, float s)
+{
+    s = fminf(fmaxf(s, a.sc_lo), a.sc_hi);
+    if (a.scale_fast_e5m3) {
+        const uint32_t b = (uint32_t)h_bits(__float2half_rn(s));
+        return __half2float(bits_h((uint16_t)((b + 0x40u) & 0xFF80u)));
+    }
+    const FpFmt sf = make_fpfmt(a.f.sc_ebit, a.f.sc_mbit);
+    return fpq_chain(s, sf, a.f.scale_allow_subnormal != 0, a.f.use_ceil != 0, false, nullptr);
+}
+
+// Power-of-two shared exponent (src/quantizer.py:395-407, 491-503): log2 evaluated in fp16.
+__device__ __forceinline__ float pot_scale(const QArgs& a, float amax, bool use_round)
+{
+    const float t = rh(amax + (amax == 0.f ? 6.103515625e-05f : 0.f));
+    const float l = log2_h(t);
+    float e = use_round ? rintf(l) : floorf(l);
+    e = rh(e - (float)a.pot_sub);
+    e = fminf(fmaxf(e, (float)a.pot_emin), (float)a.pot_emax);
+    return rh(exp2f(e));
+}
+
+__device__ __forceinline__ void store_scale(const QArgs& a, int64_t row, int64_t kb, float s)
+{
+    const uint16_t b = h_bits(__float2half_rn(s));
+    const int64_t i = row * a.nblk + kb;
+    if (a.out.scale_h) a.out.scale_h[i] = b;
+    if (a.out.scale_u8) a.out.scale_u8[i] = (uint8_t)(b >> 7);
+}
+
+// x / s rounded to fp16, for two values.  rs = 1/s correctly rounded.  The reciprocal form is
+// exact because s has at most 4 significant bits: the quotient of an 11-bit by a <=4-bit
+// integer never lies within 2^-16 (relative) of an fp16 rounding boundary unless it is
+// exactly representable, while the two fp32 roundings err by at most 2^-23.
+__device__ __forceinline__ __half2 div2_h(float x0, float x1, float s, float rs, bool exact)
+{
+    return exact ? __floats2half2_rn(__fdiv_rn(x0, s), __fdiv_rn(x1, s))
+                 : __floats2half2_rn(x0 * rs, x1 * rs);
+}
+
+// ------------------------------------------------------------------------------------------
+// MXFP / NVFP / MXINT kernel.  MB >= 0: E2M<MB> packed fast path; MB = -1: generic element
+// format through the literal chain; KIND = MXINT ignores MB.
+// ------------------------------------------------------------------------------------------
+template <int KIND, int MB>
+__global__ void __launch_bounds__(256) mx_quantize_kernel(const QArgs a)
+{
+    const int64_t ci = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const bool valid = ci < a.total_chunks;
+    int64_t row = 0, c = 0;
+    if (valid) split_chunk(a, ci, row, c);
+    const int64_t k0 = c * 8;
+    Chunk x;
+    if (valid) x = load_chunk(a, row, k0);
+    else { for (int p = 0; p < 4; ++p) x.h[p] = bits_h2(0u); }
+
+    // per-tensor scale (src/quantizer.py:516-524): the reference divides the fp16 tensor by a
+    // Python double, which torch evaluates as an fp32 division by float(scale) rounded to fp16
+    float tsf = 1.f;
+    if (KIND == HBQ_KIND_MXFP && a.f.per_tensor_scale) {
+        const float tmax = *a.tensor_amax;
+        if (tmax != 0.f) tsf = (float)((double)tmax / a.pts_den);
+        #pragma unroll
+        for (int p = 0; p < 4; ++p) {
+            const float2 f = __half22float2(x.h[p]);
+            x.h[p] = __floats2half2_rn(__fdiv_rn(f.x, tsf), __fdiv_rn(f.y, tsf));
+        }
+    }
+    const float amax = group_max(chunk_absmax(x), a.G);
+    float s;
+    if (KIND == HBQ_KIND_MXINT) {
+        if (a.f.sc_mbit == 0) s = pot_scale(a, amax, false);
+        else {
+            // quantise first, then clip from below only (src/quantizer.py:409-412)
+            const FpFmt sf = make_fpfmt(a.f.sc_ebit, a.f.sc_mbit);
+            s = fpq_chain(rh(__fdiv_rn(amax, a.elem_max)), sf, a.f.scale_allow_subnormal != 0,
+                          a.f.use_ceil != 0, false, nullptr);
+            s = fmaxf(s, a.sc_lo);
+        }
+    } else {
+        if (a.f.sc_mbit == 0) s = pot_scale(a, amax, a.f.use_round != 0);
+        else s = quant_scale_fp(a, rh(__fdiv_rn(amax, a.elem_max)));
+    }
+    const float rs = __frcp_rn(s);
+    const bool exact = a.exact_div != 0 || (KIND != HBQ_KIND_MXINT && MB < 0);
+    const __half2 s2 = __float2half2_rn(s);
+
+    __half2 d[4];
+    uint32_t mag[4], sg[4];
+    #pragma unroll
+    for (int p = 0; p < 4; ++p) {
+        const float2 xf = __half22float2(x.h[p]);
+        const __half2 y = div2_h(xf.x, xf.y, s, rs, exact);
+        __half2 q;
+        if (KIND == HBQ_KIND_MXINT) {
+            // sign(y) * floor(|y| + 0.5), clipped to [-2^(n-1), 2^(n-1)-1] (src/quantizer.py:421-422)
+            const uint32_t u = h2_bits(y);
+            const uint32_t ab = u & 0x7FFF7FFFu;
+            uint32_t sgn = u & 0x80008000u;
+            const __half2 k = h2floor(__hadd2(bits_h2(ab), bits_h2(0x38003800u)));
+            const float qmax = (float)((1 << (a.f.mbit - 1)) - 1);
+            const uint32_t lp = h2_bits(__float2half2_rn(qmax)), ln = h2_bits(__float2half2_rn(qmax + 1.f));
+            const uint32_t nm = (sgn >> 15) * 0xFFFFu;
+            const __half2 kc = __hmin2(k, bits_h2((lp & ~nm) | (ln & nm)));
+            sgn &= __hne2_mask(bits_h2(ab), bits_h2(0u));
+            q = bits_h2(h2_bits(kc) | sgn);
+            // integer code magnitude: k + 1024 keeps k in the low mantissa bits
+            mag[p] = h2_bits(__hadd2(kc, bits_h2(0x64006400u))) & 0x01FF01FFu;
+            sg[p] = sgn;
+        } else if (MB >= 0) {
+            q = q2_e2<(MB >= 0 ? MB : 1), true>(y);
+            mag[p] = code2_e2<(MB >= 0 ? MB : 1)>(q);
+            sg[p] = h2_bits(q) & 0x80008000u;
+        } else {
+            const FpFmt ef = make_fpfmt(a.f.ebit, a.f.mbit);
+            const float2 yf = __half22float2(y);
+            int c0, c1;
+            const float q0 = fpq_chain(yf.x, ef, true, false, true, &c0);
+            const float q1 = fpq_chain(yf.y, ef, true, false, true, &c1);
+            q = __floats2half2_rn(q0, q1);
+            mag[p] = (uint32_t)c0 | ((uint32_t)c1 << 16);
+            sg[p] = ((yf.x < 0.f) ? 0x8000u : 0u) | ((yf.y < 0.f) ? 0x80000000u : 0u);
+        }
+        d[p] = __hmul2(q, s2);
+        if (KIND == HBQ_KIND_MXFP && a.f.per_tensor_scale) {
+            const float2 f = __half22float2(d[p]);
+            d[p] = __floats2half2_rn(f.x * tsf, f.y * tsf);
+        }
+    }
+    if (!valid) return;
+    store_deq(a, row, k0, d);
+    store_codes<KIND == HBQ_KIND_MXINT>(a, row, k0, mag, sg);
+    if ((threadIdx.x & (a.G - 1)) == 0) store_scale(a, row, k0 / a.f.block_size, s);
+}
+
+// ------------------------------------------------------------------------------------------
+// HBQ kernel (HBQQuantizer.q, src/quantizer.py:741-859).
+//   per scheme s (1, or 2 for "Mix"):  l1_s = E5M3(clip(absmax / (elem_max * max T_s)))
+//   per micro-block: the candidate T_s[i] minimising fp16(sum fp16((x - deq_i)^2)), first wins
+//   "Mix": the scheme minimising fp16(sum over the block of the selected errors), first wins.
+// Pass 1 evaluates every candidate's error, pass 2 recomputes the winner (values + codes);
+// nothing but the winner is kept in registers, so the candidate count is a run-time value.
+// LPM = lanes per micro-block (l2_block_size / 8), 0 when l2_block_size = 4 (two per lane).
+// ------------------------------------------------------------------------------------------
+template <int MB>
+struct HbqEval {
+    // dequantised candidate for two elements: fp16(fp16(Q(fp16(a / t)) * t) * l1)
+    template <bool ZS>
+    static __device__ __forceinline__ __half2 deq2(float a0, float a1, float it, __half2 t2,
+                                                   __half2 l1_2, __half2* c_out)
+    {
+        const __half2 b = __floats2half2_rn(a0 * it, a1 * it);
+        const __half2 c = q2_e2<MB, ZS>(b);
+        if (c_out) *c_out = c;
+        return __hmul2(__hmul2(c, t2), l1_2);
+    }
+};
+
+template <int MB>
+__global__ void __launch_bounds__(256) hbq_quantize_kernel(const QArgs a)
+{
+    const int64_t ci = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const bool valid = ci < a.total_chunks;
+    int64_t row = 0, c = 0;
+    if (valid) split_chunk(a, ci, row, c);
+    const int64_t k0 = c * 8;
+    Chunk x;
+    if (valid) x = load_chunk(a, row, k0);
+    else { for (int p = 0; p < 4; ++p) x.h[p] = bits_h2(0u); }
+
+    const int L = a.f.l2_block_size;
+    const int lpm = L >> 3;                  // lanes per micro-block (0 => two micro-blocks per lane)
+    const float amax = group_max(chunk_absmax(x), a.G);
+
+    float xf[8];
+    #pragma unroll
+    for (int p = 0; p < 4; ++p) { const float2 f = __half22float2(x.h[p]); xf[2 * p] = f.x; xf[2 * p + 1] = f.y; }
+
+    __half2 best_d[4];
+    uint32_t best_mag[4], best_sg[4];
+    float best_l1 = 0.f, best_err = 0.f;
+    int best_s = 0, best_i0 = 0, best_i1 = 0;
+
+    for (int s = 0; s < a.nscheme; ++s) {
+        const float l1 = quant_scale_fp(a, rh(__fdiv_rn(amax, a.ele_max[s])));
+        const float rl1 = __frcp_rn(l1);
+        const __half2 l1_2 = __float2half2_rn(l1);
+        float af[8];
+        #pragma unroll
+        for (int p = 0; p < 4; ++p) {
+            const float2 f = __half22float2(div2_h(xf[2 * p], xf[2 * p + 1], l1, rl1, a.exact_div != 0));
+            af[2 * p] = f.x; af[2 * p + 1] = f.y;
+        }
+        // ---- pass 1: error of every candidate --------------------------------------------
+        float bE0 = 0.f, bE1 = 0.f;
+        int i0 = 0, i1 = 0;
+        for (int i = 0; i < a.nc; ++i) {
+            const float it = a.inv_tab[s][i];
+            const __half2 t2 = __float2half2_rn(a.tab[s][i]);
+            float acc0 = 0.f, acc1 = 0.f;
+            #pragma unroll
+            for (int p = 0; p < 4; ++p) {
+                const __half2 d = HbqEval<MB>::template deq2<false>(af[2 * p], af[2 * p + 1], it, t2, l1_2, nullptr);
+                const __half2 r = __hsub2(x.h[p], d);
+                const float2 e = __half22float2(__hmul2(r, r));
+                if (p < 2 || lpm != 0) { acc0 += e.x; acc0 += e.y; } else { acc1 += e.x; acc1 += e.y; }
+            }
+            float E0, E1;
+            if (lpm == 0) { E0 = rh(acc0); E1 = rh(acc1); }
+            else { E0 = rh(group_sum(acc0, lpm)); E1 = E0; }
+            if (i == 0 || E0 < bE0) { bE0 = E0; i0 = i; }
+            if (i == 0 || E1 < bE1) { bE1 = E1; i1 = i; }
+        }
+        // ---- pass 2: recompute the winners -------------------------------------------------
+        __half2 d[4];
+        uint32_t mag[4], sg[4];
+        float esum = 0.f;
+        #pragma unroll
+        for (int p = 0; p < 4; ++p) {
+            const int i = (p < 2) ? i0 : i1;
+            const float it = a.inv_tab[s][i];
+            const __half2 t2 = __float2half2_rn(a.tab[s][i]);
+            __half2 cq;
+            d[p] = HbqEval<MB>::template deq2<true>(af[2 * p], af[2 * p + 1], it, t2, l1_2, &cq);
+            mag[p] = code2_e2<MB>(cq);
+            sg[p] = h2_bits(cq) & 0x80008000u;
+            if (a.nscheme > 1) {
+                const __half2 r = __hsub2(x.h[p], d[p]);
+                const float2 e = __half22float2(__hmul2(r, r));
+                esum += e.x; esum += e.y;
+            }
+        }
+        float Es = 0.f;
+        if (a.nscheme > 1) Es = rh(group_sum(esum, a.G));
+        if (s == 0 || Es < best_err) {
+            best_err = Es; best_s = s; best_l1 = l1; best_i0 = i0; best_i1 = i1;
+            #pragma unroll
+            for (int p = 0; p < 4; ++p) { best_d[p] = d[p]; best_mag[p] = mag[p]; best_sg[p] = sg[p]; }
+        }
+    }
+
+    // ---- micro-scale indices ------------------------------------------------------------------
+    const int lig = threadIdx.x & (a.G - 1);       // lane in group
+    const int nl2 = a.f.block_size / L;
+    uint32_t l2word = 0;
+    if (lpm == 0) l2word = ((uint32_t)best_i0 | ((uint32_t)best_i1 << a.f.l2_sc_bit)) << (2 * lig * a.f.l2_sc_bit);
+    else if ((lig % lpm) == 0) l2word = (uint32_t)best_i0 << ((lig / lpm) * a.f.l2_sc_bit);
+    if (a.out.l2_packed) l2word = group_or(l2word, a.G);
+
+    if (!valid) return;
+    const int64_t kb = k0 / a.f.block_size;
+    store_deq(a, row, k0, best_d);
+    store_codes<false>(a, row, k0, best_mag, best_sg);
+    if (a.out.l2_idx) {
+        uint8_t* lp = a.out.l2_idx + (row * a.nblk + kb) * nl2;
+        if (lpm == 0) { lp[2 * lig] = (uint8_t)best_i0; lp[2 * lig + 1] = (uint8_t)best_i1; }
+        else if ((lig % lpm) == 0) lp[lig / lpm] = (uint8_t)best_i0;
+    }
+    if (lig == 0) {
+        store_scale(a, row, kb, best_l1);
+        if (a.out.scheme) a.out.scheme[row * a.nblk + kb] = (uint8_t)best_s;
+        if (a.out.l2_packed) {
+            const int nbytes = (nl2 * a.f.l2_sc_bit) >> 3;
+            uint8_t* lp = a.out.l2_packed + (row * a.nblk + kb) * nbytes;
+            if (nbytes == 4) *reinterpret_cast<uint32_t*>(lp) = l2word;
+            else if (nbytes == 2) *reinterpret_cast<uint16_t*>(lp) = (uint16_t)l2word;
+            else *lp = (uint8_t)l2word;
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// Element quantizer alone (test / utility entry point).
+// ------------------------------------------------------------------------------------------
+__global__ void fp_quant_kernel(const uint16_t* x, int64_t n, int ebit, int mbit, int allow_sub,
+                                int use_ceil, int elem_variant, uint16_t* out)
+{
+    const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 2;
+    if (i >= n) return;
+    const bool two = i + 1 < n;
+    const __half h0 = bits_h(x[i]), h1 = two ? bits_h(x[i + 1]) : __float2half(0.f);
+    __half2 r;
+    const bool fast = ebit == 2 && allow_sub && !use_ceil && elem_variant;
+    const __half2 b = __halves2half2(h0, h1);
+    if (fast && mbit == 1) r = q2_e2<1, true>(b);
+    else if (fast && mbit == 2) r = q2_e2<2, true>(b);
+    else if (fast && mbit == 3) r = q2_e2<3, true>(b);
+    else if (fast && mbit == 5) r = q2_e2<5, true>(b);
+    else {
+        const FpFmt f = make_fpfmt(ebit, mbit);
+        r = __floats2half2_rn(
+            fpq_chain(__half2float(h0), f, allow_sub != 0, use_ceil != 0, elem_variant != 0, nullptr),
+            fpq_chain(__half2float(h1), f, allow_sub != 0, use_ceil != 0, elem_variant != 0, nullptr));
+    }
+    out[i] = h_bits(__low2half(r));
+    if (two) out[i + 1] = h_bits(__high2half(r));
+}
+
+// ------------------------------------------------------------------------------------------
+// absmax (per-tensor scale support): two stages, partial maxima in caller-provided scratch.
+// ------------------------------------------------------------------------------------------
+constexpr int kAbsmaxBlocks = 1184;   // 8 x 148 SMs
+constexpr int kAbsmaxThreads = 256;
+
+__global__ void __launch_bounds__(kAbsmaxThreads)
+absmax_partial_kernel(const uint16_t* x, int64_t n, int in_bf16, float* partial)
+{
+    float m = 0.f;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    const int64_t nvec = ((reinterpret_cast<uintptr_t>(x) & 15) == 0) ? n / 8 : 0;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(x) + i);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        #pragma unroll
+        for (int p = 0; p < 4; ++p) {
+            float f0, f1;
+            if (in_bf16) { f0 = __uint_as_float(w[p] << 16); f1 = __uint_as_float(w[p] & 0xFFFF0000u); }
+            else { const float2 f = __half22float2(bits_h2(w[p])); f0 = f.x; f1 = f.y; }
+            m = fmaxf(m, fmaxf(fabsf(f0), fabsf(f1)));
+        }
+    }
+    for (int64_t i = nvec * 8 + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const float f = in_bf16 ? __uint_as_float((uint32_t)x[i] << 16) : __half2float(bits_h(x[i]));
+        m = fmaxf(m, fabsf(f));
+    }
+    m = group_max(m, 32);
+    __shared__ float sm[kAbsmaxThreads / 32];
+    if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = m;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        m = threadIdx.x < kAbsmaxThreads / 32 ? sm[threadIdx.x] : 0.f;
+        m = group_max(m, 32);
+        if (threadIdx.x == 0) partial[blockIdx.x] = m;
+    }
+}
+
+__global__ void __launch_bounds__(kAbsmaxThreads)
+absmax_final_kernel(const float* partial, int nparts, int in_bf16, float* amax)
+{
+    float m = 0.f;
+    for (int i = threadIdx.x; i < nparts; i += blockDim.x) m = fmaxf(m, partial[i]);
+    m = group_max(m, 32);
+    __shared__ float sm[kAbsmaxThreads / 32];
+    if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = m;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        m = threadIdx.x < kAbsmaxThreads / 32 ? sm[threadIdx.x] : 0.f;
+        m = group_max(m, 32);
+        // bf16 input is quantised in fp16: the maximum is that of the converted tensor
+        if (threadIdx.x == 0) *amax = in_bf16 ? rh(m) : m;
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// Host side
+// ------------------------------------------------------------------------------------------
+static float h_rh(float f) { return __half2float(__float2half_rn(f)); }
+
+static double h_max_norm(int ebit, int mbit)
+{
+    if (ebit == 0) return ldexp(1.0, mbit - 1) - 1;
+    if (ebit == 4 && mbit == 3) return 448.0;
+    const int emax = (ebit == 5) ? 15 : (1 << (ebit - 1));
+    return ldexp(1.0, emax) * (ldexp(1.0, mbit + 1) - 1) / ldexp(1.0, mbit);
+}
+static double h_min_norm(int ebit) { return ebit == 0 ? 0.0 : (ebit == 1 ? 1.0 : ldexp(1.0, 2 - (1 << (ebit - 1)))); }
+static double h_min_subnorm(int ebit, int mbit) { return ldexp(1.0, 2 - (1 << (ebit - 1)) - mbit); }
+
+// Micro-scale tables (src/quantizer.py:745-770), values as fp16 arithmetic produces them.
+static int l2_tables(int scheme, int bits, float tab[2][16])
+{
+    const int n = 1 << bits;
+    int ns = 1;
+    for (int i = 0; i < n; ++i) {
+        const float r = (float)i;
+        const float fp = h_rh(1.f + h_rh(r / (float)(1 << bits)));
+        const float fp10 = h_rh(1.f + h_rh(r / (float)(1 << (bits + 1))));
+        switch (scheme) {
+            case HBQ_L2_POT: tab[0][i] = h_rh(exp2f(r)); break;
+            case HBQ_L2_INT: tab[0][i] = h_rh(r + 1.f); break;
+            case HBQ_L2_SIG1: tab[0][i] = h_rh(1.f + h_rh(r / 2.f)); break;
+            case HBQ_L2_FPM1: tab[0][i] = fp; break;
+            case HBQ_L2_FP1: tab[0][i] = h_rh(1.f + h_rh(h_rh(r + 1.f) / (float)(1 << bits))); break;
+            case HBQ_L2_FPM10: tab[0][i] = fp10; break;
+            case HBQ_L2_FPM100: tab[0][i] = h_rh(1.f + h_rh(r / (float)(1 << (bits + 2)))); break;
+            case HBQ_L2_MIX: tab[0][i] = fp; tab[1][i] = fp10; ns = 2; break;
+            default: return -1;
+        }
+    }
+    return ns;
+}
+
+static bool is_pow2(int v) { return v > 0 && (v & (v - 1)) == 0; }
+
+int quantize_launch(const void* x, int dtype, int64_t rows, int64_t K, const hbq_format* f,
+                    void* deq, int deq_dtype, const hbq_packed_out* out, const float* tensor_amax,
+                    cudaStream_t stream)
+{
+    if (!x || !f || rows < 0 || K < 0) return HBQ_ERR_ARG;
+    if (dtype != HBQ_DTYPE_F16 && dtype != HBQ_DTYPE_BF16) return HBQ_ERR_UNSUPPORTED;
+    if (deq && deq_dtype != HBQ_DTYPE_F16 && deq_dtype != HBQ_DTYPE_BF16) return HBQ_ERR_UNSUPPORTED;
+    if (rows == 0 || K == 0) return HBQ_OK;
+    const int B = f->block_size;
+    if (!is_pow2(B) || B < 8 || B > 256) return HBQ_ERR_UNSUPPORTED;
+    const bool pts = f->kind == HBQ_KIND_MXFP && f->per_tensor_scale;    // the other kinds ignore it
+    if (pts && !tensor_amax) return HBQ_ERR_ARG;
+
+    QArgs a;
+    memset(&a, 0, sizeof(a));
+    a.x = x; a.deq = deq;
+    if (out) a.out = *out;
+    a.tensor_amax = tensor_amax;
+    a.rows = rows; a.K = K;
+    a.nblk = (int)((K + B - 1) / B);
+    a.Kp = (int64_t)a.nblk * B;
+    a.cpr = a.Kp / 8;
+    a.total_chunks = rows * a.cpr;
+    a.in_bf16 = dtype == HBQ_DTYPE_BF16;
+    a.out_bf16 = deq_dtype == HBQ_DTYPE_BF16;
+    a.aligned = (K % 8 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0) &&
+                (!deq || (reinterpret_cast<uintptr_t>(deq) & 15) == 0);
+    a.G = B / 8;
+    a.f = *f;
+    a.f.per_tensor_scale = pts;
+    a.scale_fast_e5m3 = (f->sc_ebit == 5 && f->sc_mbit == 3 && !f->use_ceil && !f->scale_allow_subnormal);
+    a.exact_div = f->sc_mbit > 4;
+    if (f->sc_mbit > 0) {
+        a.sc_lo = (float)(f->scale_allow_subnormal ? h_min_subnorm(f->sc_ebit, f->sc_mbit) : h_min_norm(f->sc_ebit));
+        a.sc_hi = (float)h_max_norm(f->sc_ebit, f->sc_mbit);
+    }
+    const dim3 block(256), grid((unsigned)((a.total_chunks + 255) / 256));
+
+    if (f->kind == HBQ_KIND_MXINT) {
+        if (f->mbit < 2 || f->mbit > 8) return HBQ_ERR_UNSUPPORTED;
+        a.code_bits = f->mbit <= 4 ? 4 : 8;
+        if (a.out.codes && f->mbit != 4 && f->mbit != 8) return HBQ_ERR_UNSUPPORTED;
+        a.elem_max = (float)h_max_norm(0, f->mbit);
+        a.pot_sub = f->mbit - 2; a.pot_emin = -14; a.pot_emax = 15;       // quantizer.py:403-405
+        mx_quantize_kernel<HBQ_KIND_MXINT, 0><<<grid, block, 0, stream>>>(a);
+        HBQ_LAUNCH_CHECK("mx_quantize_kernel<mxint>");
+        return HBQ_OK;
+    }
+    if (f->ebit < 1 || f->ebit > 5 || f->mbit < 0 || f->mbit > 7 || f->ebit + f->mbit > 7) return HBQ_ERR_UNSUPPORTED;
+    a.code_bits = 1 + f->ebit + f->mbit;
+    if (a.code_bits < 4) a.code_bits = 4;
+    if (a.code_bits > 5 && a.code_bits < 8) a.code_bits = 8;
+    a.elem_max = (float)h_max_norm(f->ebit, f->mbit);
+    const int fast_mb = (f->ebit == 2 && (f->mbit == 1 || f->mbit == 2 || f->mbit == 3 || f->mbit == 5)) ? f->mbit : -1;
+
+    if (f->kind == HBQ_KIND_MXFP) {
+        if (pts) {
+            a.pts_den = (double)a.elem_max * h_max_norm(f->sc_ebit, f->sc_mbit);
+        }
+        a.pot_sub = 1 << (f->ebit - 1);
+        a.pot_emin = 2 - (1 << (f->sc_ebit - 1)); a.pot_emax = (1 << (f->sc_ebit - 1)) - 1;   // quantizer.py:500-502
+        if (f->sc_mbit == 0 && (f->sc_ebit < 2 || f->sc_ebit > 8)) return HBQ_ERR_UNSUPPORTED;
+        switch (fast_mb) {
+            case 1: mx_quantize_kernel<HBQ_KIND_MXFP, 1><<<grid, block, 0, stream>>>(a); break;
+            case 2: mx_quantize_kernel<HBQ_KIND_MXFP, 2><<<grid, block, 0, stream>>>(a); break;
+            case 3: mx_quantize_kernel<HBQ_KIND_MXFP, 3><<<grid, block, 0, stream>>>(a); break;
+            case 5: mx_quantize_kernel<HBQ_KIND_MXFP, 5><<<grid, block, 0, stream>>>(a); break;
+            default: mx_quantize_kernel<HBQ_KIND_MXFP, -1><<<grid, block, 0, stream>>>(a); break;
+        }
+        HBQ_LAUNCH_CHECK("mx_quantize_kernel<mxfp>");
+        return HBQ_OK;
+    }
+    if (f->kind != HBQ_KIND_HBQ) return HBQ_ERR_ARG;
+    // HBQ
+    const int L = f->l2_block_size;
+    if (fast_mb < 0 || fast_mb == 5) return HBQ_ERR_UNSUPPORTED;          // element must be E2M1/2/3
+    if (f->sc_mbit == 0) return HBQ_ERR_UNSUPPORTED;
+    if (!is_pow2(L) || L < 4 || L > B || f->l2_sc_bit < 0 || f->l2_sc_bit > 4) return HBQ_ERR_UNSUPPORTED;
+    a.nc = 1 << f->l2_sc_bit;
+    a.nscheme = l2_tables(f->l2_scheme, f->l2_sc_bit, a.tab);
+    if (a.nscheme < 0) return HBQ_ERR_ARG;
+    for (int s = 0; s < a.nscheme; ++s) {
+        float tmax = a.tab[s][0];
+        for (int i = 0; i < a.nc; ++i) {
+            a.inv_tab[s][i] = 1.f / a.tab[s][i];
+            tmax = fmaxf(tmax, a.tab[s][i]);
+        }
+        a.ele_max[s] = h_rh(h_rh(a.elem_max) * tmax);                   // quantizer.py:775-777
+    }
+    if (a.out.l2_packed) {
+        const int tb = (B / L) * f->l2_sc_bit;
+        if (tb != 8 && tb != 16 && tb != 32) return HBQ_ERR_UNSUPPORTED;
+    }
+    switch (fast_mb) {
+        case 1: hbq_quantize_kernel<1><<<grid, block, 0, stream>>>(a); break;
+        case 2: hbq_quantize_kernel<2><<<grid, block, 0, stream>>>(a); break;
+        default: hbq_quantize_kernel<3><<<grid, block, 0, stream>>>(a); break;
+    }
+    HBQ_LAUNCH_CHECK("hbq_quantize_kernel");
+    return HBQ_OK;
+}
+
+int fp_quant_launch(const void* x, int64_t n, int ebit, int mbit, int allow_sub, int use_ceil,
+                    int elem_variant, void* out, cudaStream_t stream)
+{
+    if (!x || !out || n < 0 || ebit < 1 || ebit > 5 || mbit < 0 || mbit > 9) return HBQ_ERR_ARG;
+    if (n == 0) return HBQ_OK;
+    const int64_t pairs = (n + 1) / 2;
+    fp_quant_kernel<<<(unsigned)((pairs + 255) / 256), 256, 0, stream>>>(
+        (const uint16_t*)x, n, ebit, mbit, allow_sub, use_ceil, elem_variant, (uint16_t*)out);
+    HBQ_LAUNCH_CHECK("fp_quant_kernel");
+    return HBQ_OK;
+}
+
+int64_t absmax_scratch_bytes() { return (int64_t)kAbsmaxBlocks * sizeof(float); }
+
+int absmax_launch(const void* x, int dtype, int64_t n, float* amax, void* scratch, cudaStream_t stream)
+{
+    if (!x || !amax || !scratch || n < 0) return HBQ_ERR_ARG;
+    if (dtype != HBQ_DTYPE_F16 && dtype != HBQ_DTYPE_BF16) return HBQ_ERR_UNSUPPORTED;
+    absmax_partial_kernel<<<kAbsmaxBlocks, kAbsmaxThreads, 0, stream>>>(
+        (const uint16_t*)x, n, dtype == HBQ_DTYPE_BF16, (float*)scratch);
+    HBQ_LAUNCH_CHECK("absmax_partial_kernel");
+    absmax_final_kernel<<<1, kAbsmaxThreads, 0, stream>>>((const float*)scratch, kAbsmaxBlocks,
+                                                          dtype == HBQ_DTYPE_BF16, amax);
+    HBQ_LAUNCH_CHECK("absmax_final_kernel");
+    return HBQ_OK;
+}
+
+}  // namespace hbq

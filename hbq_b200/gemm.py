@@ -1,0 +1,53 @@
+"""``hbq_gemm`` for torch tensors: C = A @ B with one of the reference's accumulation models
+(blockquant_ext_src/gemm.cu)."""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import _lib
+from .quantizer import _ptr, _stream_ptr
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, mode: int, group_k: int = 0, group_n: int = 0,
+         bias: Optional[torch.Tensor] = None, b_is_nk: bool = False, force_simt: bool = False) -> torch.Tensor:
+    """``hbq_gemm``: a [M, K] fp16, b [K, N] (or [N, K] when ``b_is_nk``) fp16 -> [M, N] fp16."""
+    if a.dtype != torch.float16 or b.dtype != torch.float16:
+        raise RuntimeError("A must be fp16" if a.dtype != torch.float16 else "B must be fp16")
+    if a.dim() != 2 or b.dim() != 2:
+        raise RuntimeError("A and B must be 2D")
+    if not (a.is_cuda and b.is_cuda):
+        raise RuntimeError("A and B must be CUDA tensors")
+    if a.device != b.device:
+        raise RuntimeError("A and B must be on the same CUDA device")
+    M, K = a.shape
+    N = b.shape[0] if b_is_nk else b.shape[1]
+    if (b.shape[1] if b_is_nk else b.shape[0]) != K:
+        raise RuntimeError("A's K dimension must match B's K dimension")
+    a = a.contiguous()
+    b = b.contiguous()
+    if bias is not None:
+        bias = bias.to(device=a.device, dtype=torch.float16).contiguous()
+    c = torch.empty((M, N), dtype=torch.float16, device=a.device)
+    L = _lib.lib()
+    with torch.cuda.device(a.device):
+        stream = _stream_ptr(a.device)
+        if force_simt:
+            rc = L.hbq_gemm_simt(_ptr(a), _ptr(b), _ptr(c), M, N, K, int(b_is_nk), mode, group_k, group_n,
+                                 _ptr(bias), stream)
+        else:
+            ws_bytes = int(L.hbq_gemm_workspace_bytes(M, N, K, int(b_is_nk), mode, group_k, group_n))
+            ws = torch.empty(ws_bytes, dtype=torch.uint8, device=a.device) if ws_bytes else None
+            rc = L.hbq_gemm(_ptr(a), _ptr(b), _ptr(c), M, N, K, int(b_is_nk), mode, group_k, group_n,
+                            _ptr(bias), _ptr(ws), ws_bytes, stream)
+    _lib.check(rc, "hbq_gemm")
+    return c
+
+
+def gemm_status() -> int:
+    """Device status word of the tensor-core kernel (0 = ok); synchronises the device."""
+    v = ctypes.c_int(0)
+    _lib.check(_lib.lib().hbq_gemm_status(ctypes.byref(v)), "hbq_gemm_status")
+    return v.value

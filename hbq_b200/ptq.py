@@ -1,0 +1,154 @@
+"""YAML quantization config -> quantizer / GEMM-operator objects, with the keys and defaults of
+the reference's ``PTQ`` (src/ptq.py:29-105) and its factory methods (src/ptq.py:107-257,
+384-404).  The reference's model plumbing (Hugging Face module patching) is not reproduced;
+``apply_to_linear`` performs its per-layer steps on one ``QLinear``.
+"""
+from __future__ import annotations
+
+from typing import Any, Dict, Optional
+
+import torch
+
+from .module import QLinear
+from .ops import FP16AccumMatMul
+from .quantizer import HBQQuantizer, MXFPQuantizer, MXINTQuantizer, _QBase
+
+
+def load_quant_config(path: str) -> Dict[str, Any]:
+    import yaml
+    with open(path, "r") as fh:
+        return yaml.full_load(fh)
+
+
+class PTQConfig:
+    """Parsed quantization YAML (the second YAML of a reference run, config/README.md)."""
+
+    def __init__(self, quant_config: Dict[str, Any]):
+        self.quant_config = quant_config
+        q = quant_config.get("quantization", {})
+        b = quant_config.get("block_quant", {})
+        acc = quant_config.get("accumulation", {})
+        self.xqtype = q["xqtype"]
+        self.wqtype = q["wqtype"]
+        self.a_ebit = b.get("act_ebit", 0)
+        self.a_mbit = b.get("act_mbit", 0)
+        self.a_sc_ebit = b.get("act_sc_ebit", 0)
+        self.a_sc_mbit = b.get("act_sc_mbit", 8)
+        self.a_block_size = b.get("act_block_size", 32)
+        self.kv_block_size = b.get("kv_block_size", self.a_block_size)
+        self.a_per_tensor_scale = b.get("act_per_tensor_scale", False)
+        self.w_ebit = b.get("wgt_ebit", 0)
+        self.w_mbit = b.get("wgt_mbit", 0)
+        self.w_sc_ebit = b.get("wgt_sc_ebit", 0)
+        self.w_sc_mbit = b.get("wgt_sc_mbit", 8)
+        self.w_block_size = b.get("wgt_block_size", 32)
+        self.w_per_tensor_scale = b.get("wgt_per_tensor_scale", False)
+        self.scale_allow_subnormal = b.get("scale_allow_subnormal", True)
+        self.qk_mx_round = b.get("qk_mx_round", False)
+        self.act_scale_use_ceil = b.get("act_scale_use_ceil", False)
+        self.wgt_scale_use_ceil = b.get("wgt_scale_use_ceil", False)
+        self.wgt_l2_sc_bit = b.get("wgt_l2_sc_bit", 1)
+        self.wgt_l2_block_size = b.get("wgt_l2_block_size", 4)
+        self.wgt_l2_scheme = b.get("wgt_l2_scheme", "PoT")
+        self.act_l2_sc_bit = b.get("act_l2_sc_bit", 1)
+        self.act_l2_block_size = b.get("act_l2_block_size", 4)
+        self.act_l2_scheme = b.get("act_l2_scheme", "PoT")
+        self.quant_before_hadamard = q.get("quant_before_hadamard", False)
+        self.quant_before_silu = q.get("quant_before_silu", False)
+        self.quant_before_rms_norm = q.get("quant_before_rms_norm", False)
+        self.quant_embedding_layer = q.get("quant_embedding_layer", False)
+        self.quant_output_layer = q.get("quant_output_layer", False)
+        self.quant_attn_wgt = q.get("quant_attn_wgt", False)
+        self.quant_post_rope_q = q.get("quant_post_rope_q", False)
+        self.quant_4b_kv = q.get("quant_4b_kv", False)
+        self.quant_k_cache = q.get("quant_k_cache", False)
+        self.quant_v_cache = q.get("quant_v_cache", False)
+        self.accumulation_type = acc.get("type", "fp32")
+        self.accumulation_group_size = acc.get("group_size", 128)
+        self.accumulation_quant_block_size = acc.get("quant_block_size", 16)
+
+    # ---- src/ptq.py:107-157 ----
+    def map_wgt_quantizer(self, use_round: bool = False):
+        if self.wqtype == "mxfp":
+            return MXFPQuantizer(ebit=self.w_ebit, mbit=self.w_mbit, sc_ebit=self.w_sc_ebit, sc_mbit=self.w_sc_mbit,
+                                 block_size=self.w_block_size, per_tensor_scale=self.w_per_tensor_scale,
+                                 scale_allow_subnormal=self.scale_allow_subnormal, use_round=use_round,
+                                 use_ceil=self.wgt_scale_use_ceil)
+        if self.wqtype == "mxint":
+            return MXINTQuantizer(nbit=self.w_mbit, sc_ebit=self.w_sc_ebit, sc_mbit=self.w_sc_mbit,
+                                  block_size=self.w_block_size, scale_allow_subnormal=self.scale_allow_subnormal)
+        if self.wqtype == "hbq":
+            return HBQQuantizer(ebit=self.w_ebit, mbit=self.w_mbit, sc_ebit=self.w_sc_ebit, sc_mbit=self.w_sc_mbit,
+                                block_size=self.w_block_size, scale_allow_subnormal=self.scale_allow_subnormal,
+                                l2_block_size=self.wgt_l2_block_size, l2_sc_bit=self.wgt_l2_sc_bit,
+                                l2_scheme=self.wgt_l2_scheme)
+        if self.wqtype == "none":
+            return _QBase()
+        raise AssertionError(f"Invalid weight quantizer type: {self.wqtype}")
+
+    # ---- src/ptq.py:159-212 ----
+    def map_act_quantizer(self, use_round: bool = False):
+        if self.xqtype == "mxfp":
+            return MXFPQuantizer(ebit=self.a_ebit, mbit=self.a_mbit, sc_ebit=self.a_sc_ebit, sc_mbit=self.a_sc_mbit,
+                                 block_size=self.a_block_size, per_tensor_scale=self.a_per_tensor_scale,
+                                 scale_allow_subnormal=self.scale_allow_subnormal, use_round=use_round,
+                                 use_ceil=self.act_scale_use_ceil)
+        if self.xqtype == "mxint":
+            return MXINTQuantizer(nbit=self.a_mbit, sc_ebit=self.a_sc_ebit, sc_mbit=self.a_sc_mbit,
+                                  block_size=self.a_block_size, scale_allow_subnormal=self.scale_allow_subnormal)
+        if self.xqtype == "hbq":
+            return HBQQuantizer(ebit=self.a_ebit, mbit=self.a_mbit, sc_ebit=self.a_sc_ebit, sc_mbit=self.a_sc_mbit,
+                                block_size=self.a_block_size, scale_allow_subnormal=self.scale_allow_subnormal,
+                                l2_block_size=self.act_l2_block_size, l2_sc_bit=self.act_l2_sc_bit,
+                                l2_scheme=self.act_l2_scheme)
+        if self.xqtype == "none":
+            return _QBase()
+        raise AssertionError(f"Invalid activation quantizer type: {self.xqtype}")
+
+    # ---- src/ptq.py:214-257: 4-bit KV quantizer with the activation's scale settings ----
+    def map_4b_kv_quantizer(self, use_round: bool = False):
+        if self.xqtype == "mxfp":
+            return MXFPQuantizer(ebit=2, mbit=1, sc_ebit=self.a_sc_ebit, sc_mbit=self.a_sc_mbit,
+                                 block_size=self.kv_block_size, per_tensor_scale=self.a_per_tensor_scale,
+                                 scale_allow_subnormal=self.scale_allow_subnormal, use_round=use_round,
+                                 use_ceil=self.act_scale_use_ceil)
+        if self.xqtype == "mxint":
+            return MXINTQuantizer(nbit=4, sc_ebit=self.a_sc_ebit, sc_mbit=self.a_sc_mbit,
+                                  block_size=self.kv_block_size, scale_allow_subnormal=self.scale_allow_subnormal)
+        if self.xqtype == "hbq":
+            return HBQQuantizer(ebit=2, mbit=1, sc_ebit=self.a_sc_ebit, sc_mbit=self.a_sc_mbit,
+                                block_size=self.kv_block_size, scale_allow_subnormal=self.scale_allow_subnormal,
+                                l2_block_size=self.act_l2_block_size, l2_sc_bit=self.act_l2_sc_bit,
+                                l2_scheme=self.act_l2_scheme)
+        if self.xqtype == "none":
+            return _QBase()
+        raise AssertionError(f"Invalid activation quantizer type: {self.xqtype}")
+
+    def map_kv_quantizer(self):
+        """KV-cache quantizer as src/ptq.py:267-270 chooses it."""
+        if self.quant_4b_kv:
+            return self.map_4b_kv_quantizer(use_round=self.qk_mx_round)
+        return self.map_act_quantizer(use_round=self.qk_mx_round)
+
+    # ---- src/ptq.py:384-404 ----
+    def make_accum_op(self) -> Optional[FP16AccumMatMul]:
+        if self.accumulation_type == "fp32":
+            return None
+        if self.accumulation_type == "fp16":
+            return FP16AccumMatMul(group_size=self.accumulation_group_size)
+        if self.accumulation_type == "fp16_quant":
+            return FP16AccumMatMul(group_size=self.accumulation_group_size,
+                                   quant_block_size=self.accumulation_quant_block_size)
+        raise ValueError(f"Invalid accumulation type: {self.accumulation_type}")
+
+    @torch.no_grad()
+    def apply_to_linear(self, linear: QLinear, qk_proj: bool = False) -> QLinear:
+        """Inject quantizers, fake-quantise the weight once and set the GEMM operator: what
+        inject_quantizers / static_quant_wgt / replace_accum_kernel do to one layer
+        (src/ptq.py:259-290, 337-404).  ``qk_proj`` selects the q/k-projection rounding rule."""
+        use_round = self.qk_mx_round if qk_proj else False
+        linear.wq = self.map_wgt_quantizer(use_round=use_round)
+        linear.aq = self.map_act_quantizer(use_round=use_round)
+        linear.weight.data = linear.wq(linear.weight.data)
+        linear.ops = self.make_accum_op()
+        return linear

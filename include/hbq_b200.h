@@ -1,0 +1,160 @@
+/*
+ * hbq_b200 -- C ABI of the B200 (sm_100a) implementation of HBQ's hot path:
+ * block quantize-dequantize (MXFP / NVFP / MXINT / HBQ two-level) and the GEMM
+ * with modelled low-precision accumulation.
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer unless the name ends in _host;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream);
+ *   - the calls enqueue work and return; they never synchronise the device;
+ *   - return value 0 = success, negative = error (see hbq_error_string);
+ *   - no global state besides one device status word (hbq_gemm_status); calls are
+ *     re-entrant per stream.
+ *
+ * Each entry point names the reference interface it replaces (paths inside the
+ * HBQ repository).
+ */
+#ifndef HBQ_B200_H
+#define HBQ_B200_H
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- formats --------------------------------------------------------------------------- */
+
+enum { HBQ_KIND_MXFP = 0, HBQ_KIND_MXINT = 1, HBQ_KIND_HBQ = 2 };
+/* Index into HBQQuantizer.L2_SCHEME, src/quantizer.py:708 */
+enum { HBQ_L2_POT = 0, HBQ_L2_INT = 1, HBQ_L2_SIG1 = 2, HBQ_L2_FPM1 = 3,
+       HBQ_L2_FP1 = 4, HBQ_L2_FPM10 = 5, HBQ_L2_FPM100 = 6, HBQ_L2_MIX = 7 };
+enum { HBQ_DTYPE_F16 = 0, HBQ_DTYPE_BF16 = 1 };
+
+/* Constructor arguments of MXFPQuantizer / MXINTQuantizer / HBQQuantizer
+ * (src/quantizer.py:348-357, 431-443, 709-725), same meaning. */
+typedef struct hbq_format {
+    int32_t kind;                  /* HBQ_KIND_* */
+    int32_t ebit, mbit;            /* element format; MXINT: ebit = 0, mbit = nbit */
+    int32_t sc_ebit, sc_mbit;      /* shared scale; sc_mbit == 0 => power of two */
+    int32_t block_size;            /* 16..256, multiple of 8 */
+    int32_t scale_allow_subnormal;
+    int32_t use_round;             /* MXFP power-of-two scale: round(log2 max) instead of floor */
+    int32_t use_ceil;              /* FP scale: ceil its mantissa */
+    int32_t l2_block_size;         /* HBQ micro-block (4, 8, 16, ... block_size) */
+    int32_t l2_sc_bit;             /* HBQ: log2(number of micro-scale candidates), 0..4 */
+    int32_t l2_scheme;             /* HBQ_L2_* */
+    int32_t per_tensor_scale;      /* MXFP only (src/quantizer.py:516-524) */
+    int32_t reserved;
+} hbq_format;
+
+/* Optional outputs of hbq_quantize; any pointer may be NULL.
+ *   Kp = ceil(K / block_size) * block_size, nblk = Kp / block_size, nl2 = block_size / l2_block_size.
+ *   codes     element codes, row-major [rows, Kp]:
+ *               4-bit elements (E2M1, INT4): two per byte, element 2i in the low nibble;
+ *               5-bit elements (E2M2): low 4 bits {exp, mant} packed as above, sign bits in `sign`;
+ *               6..8-bit elements: one byte each ({sign, exp, mant} or two's complement).
+ *             FP code fields are those of make_fp_quant's detailed output
+ *             (src/quantizer.py:249-253): exponent biased by 2^(ebit-1)-1, 0 = subnormal.
+ *   sign      [rows, Kp/8] sign bit-plane for 5-bit elements, element i in bit (i % 8).
+ *   scale_u8  [rows, nblk] shared scale byte: bits 14..7 of its fp16 pattern, i.e. {exp5, mant3}
+ *             with bias 15 (E5M3) or the biased power-of-two exponent << 3.
+ *   scale_h   [rows, nblk] shared scale as fp16 (HBQQuantizer.shared_scale).
+ *   l2_packed [rows, nblk, nl2*l2_sc_bit/8] micro-scale indices, l2_sc_bit bits each, little
+ *             endian; needs nl2*l2_sc_bit to be 8, 16 or 32.
+ *   l2_idx    [rows, nblk, nl2] the same indices one per byte (HBQQuantizer.l2_scale).
+ *   scheme    [rows, nblk] chosen table of the "Mix" scheme (HBQQuantizer.blk_l2_scheme). */
+typedef struct hbq_packed_out {
+    uint8_t* codes;
+    uint8_t* sign;
+    uint8_t* scale_u8;
+    uint16_t* scale_h;
+    uint8_t* l2_packed;
+    uint8_t* l2_idx;
+    uint8_t* scheme;
+} hbq_packed_out;
+
+/* ---- quantize -------------------------------------------------------------------------- */
+
+/* Replaces _QBase.forward / MXFPQuantizer.q / MXINTQuantizer.q / HBQQuantizer.q
+ * (src/quantizer.py:343-345, 415-428, 513-539, 741-859) on a [rows, K] tensor quantised
+ * along K.  x has `dtype`, deq `deq_dtype`; bf16 input is converted to fp16 first, the
+ * arithmetic is the reference's fp16 arithmetic, and a bf16 deq is the fp16 result rounded to
+ * bf16.  deq (the fake-quantised tensor, same shape as x) and `out` may each be NULL.  `tensor_amax` is only read when fmt->per_tensor_scale is set: a device
+ * float holding max|x| of the whole tensor (see hbq_absmax). */
+int hbq_quantize(const void* x, int dtype, int64_t rows, int64_t K, const hbq_format* fmt,
+                 void* deq, int deq_dtype, const hbq_packed_out* out, const float* tensor_amax,
+                 void* stream);
+
+/* max|x| over n elements into *amax (device float, overwritten).  Replaces the
+ * `xg.abs().max().item()` of the per-tensor scale, src/quantizer.py:519.  `scratch` must
+ * hold at least hbq_absmax_scratch_bytes() bytes of device memory. */
+int hbq_absmax(const void* x, int dtype, int64_t n, float* amax, void* scratch, void* stream);
+int64_t hbq_absmax_scratch_bytes(void);
+
+/* Rebuilds the fake-quantised fp16 tensor [rows, K] from the packed outputs of
+ * hbq_quantize (codes, sign, scale_u8, l2_packed, scheme as the format needs them).
+ * No reference counterpart: the reference never stores codes (it keeps the fp16
+ * fake-quantised weight, src/ptq.py:349). */
+int hbq_dequantize(const hbq_packed_out* in, int64_t rows, int64_t K, const hbq_format* fmt,
+                   void* deq, int dtype, void* stream);
+
+/* Element quantizer alone over n values (fp16 in, fp16 out): make_fp_quant
+ * (src/quantizer.py:187-257) when elem_variant = 1, the free function fp_quant
+ * (src/quantizer.py:259-328) when 0. */
+int hbq_fp_quant(const void* x, int64_t n, int ebit, int mbit, int allow_subnormal,
+                 int use_ceil, int elem_variant, void* out, void* stream);
+
+/* ---- GEMM with modelled accumulation --------------------------------------------------- */
+
+enum { HBQ_ACC_FP32 = 0,       /* gemm_fp32_accum         blockquant_ext.cpp:21-29, gemm.cu:96-303 */
+       HBQ_ACC_FP16 = 1,       /* gemm_fp16_accum         blockquant_ext.cpp:31-39, gemm.cu:96-303 */
+       HBQ_ACC_GROUPED = 2,    /* gemm_fp16_grouped_accum blockquant_ext.cpp:41-49, gemm.cu:306-553 */
+       HBQ_ACC_PSUM_INT8 = 3,  /* gemm_blockquant_mxint8  blockquant_ext.cpp:64-71, gemm.cu:1154-1396 */
+       HBQ_ACC_PSUM_E3M4 = 4   /* gemm_blockquant_mxfp8   blockquant_ext.cpp:55-62, gemm.cu:752-1035 */ };
+
+/* C[M,N] = A[M,K] * B, fp16 in, fp16 out, row-major, with the accumulation model `mode`.
+ *   b_is_nk = 0: B is [K,N] (the layout the reference extension receives, ops.py:41);
+ *   b_is_nk = 1: B is W [N,K] as nn.Linear stores it -- no transpose is needed and this is
+ *                the fast path (FP16AccumMatMul.forward, src/ops.py:28-62).
+ *   group_k: K-chunk of the fp32 partial sum (modes 2-4); group_n: columns per partial-sum
+ *   quantisation block (modes 3-4).  `bias` [N] fp16 or NULL is added in fp16 after the
+ *   accumulation (src/ops.py:59-60).
+ *   `workspace` / `workspace_bytes`: device scratch, at least hbq_gemm_workspace_bytes(...)
+ *   (holds B transposed when b_is_nk = 0 and the tensor-core path is taken; may be NULL if 0). */
+int hbq_gemm(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
+             int b_is_nk, int mode, int group_k, int group_n, const void* bias,
+             void* workspace, int64_t workspace_bytes, void* stream);
+int64_t hbq_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int b_is_nk, int mode,
+                                 int group_k, int group_n);
+/* 1 if hbq_gemm would run the tcgen05 kernel for these arguments, 0 if the SIMT kernel. */
+int hbq_gemm_uses_tensor_cores(int64_t M, int64_t N, int64_t K, int b_is_nk, int mode,
+                               int group_k, int group_n);
+/* Force the SIMT kernel (exact sequential-fp32 model of gemm.cu) regardless of shape. */
+int hbq_gemm_simt(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
+                  int b_is_nk, int mode, int group_k, int group_n, const void* bias,
+                  void* stream);
+
+/* The tensor-core kernel bounds every wait on an mbarrier.  If one expires the kernel stops,
+ * frees its tensor memory and records which wait gave up in a device status word; the output
+ * of that call is then undefined.  hbq_gemm_status copies the word to the host (it
+ * synchronises the device); 0 = no wait has expired since the last reset.
+ * No reference counterpart (the reference kernels do not wait on anything). */
+int hbq_gemm_status(int* status_host);
+int hbq_gemm_status_reset(void);
+
+/* ---- misc ------------------------------------------------------------------------------ */
+
+const char* hbq_error_string(int code);
+/* Text of the last failing CUDA runtime/driver call on this thread ("" if none). */
+const char* hbq_last_cuda_error(void);
+int hbq_version(void);
+/* Kernels launched by this library since load (all threads); the benchmark reports it. */
+int64_t hbq_launch_count(void);
+
+enum { HBQ_OK = 0, HBQ_ERR_ARG = -1, HBQ_ERR_UNSUPPORTED = -2, HBQ_ERR_CUDA = -3,
+       HBQ_ERR_ALIGN = -4, HBQ_ERR_WORKSPACE = -5, HBQ_ERR_DEVICE = -6 };
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -275,7 +275,16 @@ int orc_quantize(const uint16_t* x, int64_t rows, int64_t K, const orc_format* f
     if (B <= 0 || B > 1024) return -1;
     if (f->kind == ORC_KIND_HBQ && (B % f->l2_block_size != 0 || B / f->l2_block_size > 128 ||
                                     f->l2_sc_bit > 4 || f->l2_sc_bit < 0)) return -1;
-    if (f->kind == ORC_KIND_MXFP && f->per_tensor_scale) return -2; /* host-level, not a block op */
+    /* per-tensor scale, MXFPQuantizer.q quantizer.py:516-524 and :534-535: the fp16 tensor is
+     * divided / multiplied by a Python double, which torch evaluates in fp32 with float(scale). */
+    float tsf = 1.f;
+    const int pts = (f->kind == ORC_KIND_MXFP && f->per_tensor_scale);
+    if (pts) {
+        float tmax = 0.f;
+        for (int64_t i = 0; i < rows * K; ++i) tmax = fmaxf(tmax, fabsf(h2f(x[i])));
+        if (tmax != 0.f)
+            tsf = (float)((double)tmax / (max_norm(f->ebit, f->mbit, 0) * max_norm(f->sc_ebit, f->sc_mbit, 0)));
+    }
     const int64_t nblk = (K + B - 1) / B;
     float tab[32]; int nscheme = 1;
     int nl2 = 0;
@@ -288,10 +297,12 @@ int orc_quantize(const uint16_t* x, int64_t rows, int64_t K, const orc_format* f
             const int64_t k0 = kb * B;
             const int valid = (int)((K - k0) < B ? (K - k0) : B);
             for (int j = 0; j < B; ++j) xb[j] = j < valid ? h2f(x[r * K + k0 + j]) : 0.f;
+            if (pts) for (int j = 0; j < B; ++j) xb[j] = rh(xb[j] / tsf);
             float s; uint8_t sch = 0;
             if (f->kind == ORC_KIND_MXFP) mxfp_block(xb, B, f, db, &s, cb);
             else if (f->kind == ORC_KIND_MXINT) mxint_block(xb, B, f, db, &s, cb);
             else hbq_block(xb, B, f, tab, nscheme, db, &s, ib, &sch, cb);
+            if (pts) for (int j = 0; j < B; ++j) db[j] = rh(db[j] * tsf);
             for (int j = 0; j < valid; ++j) deq[r * K + k0 + j] = f2h(db[j]);
             if (scale) scale[r * nblk + kb] = f2h(s);
             if (codes) memcpy(codes + (r * nblk + kb) * B, cb, (size_t)B);
