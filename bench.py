@@ -111,16 +111,15 @@ def cpu_baseline_sample(x_bf16, wq_f16, seconds_target: float = 15.0):
     fa = O.Format(O.KIND_HBQ, ACT["ebit"], ACT["mbit"], 5, 3, 128, l2_block_size=32, l2_sc_bit=2, l2_scheme="SIG-1")
     xh = x_bf16.to(dtype=__import__("torch").float16).numpy()
     wt = np.ascontiguousarray(wq_f16.numpy().T)
-    rows = 8
-    t0 = time.perf_counter()
-    xq = O.quantize(xh[:rows], fa, want_codes=False)["deq"]
-    O.gemm(xq, wt, O.ACC_PSUM_INT8, GROUP_K, GROUP_N)
-    dt = time.perf_counter() - t0
-    rows = int(max(8, min(M, rows * seconds_target / max(dt, 1e-3)) // 8 * 8))
-    t0 = time.perf_counter()
-    xq = O.quantize(xh[:rows], fa, want_codes=False)["deq"]
-    O.gemm(xq, wt, O.ACC_PSUM_INT8, GROUP_K, GROUP_N)
-    dt = time.perf_counter() - t0
+    rows, dt = 64, 0.0
+    while True:                      # grow the sample until it costs about seconds_target of CPU time
+        t0 = time.perf_counter()
+        xq = O.quantize(xh[:rows], fa, want_codes=False)["deq"]
+        O.gemm(xq, wt, O.ACC_PSUM_INT8, GROUP_K, GROUP_N)
+        dt = time.perf_counter() - t0
+        if dt >= 0.6 * seconds_target or rows >= M:
+            break
+        rows = int(min(M, max(rows * 2, rows * seconds_target / max(dt, 1e-3)) // 8 * 8))
     return {"value": 2.0 * rows * N * K / dt / 1e12, "unit": "TFLOP/s", "cores": O.num_threads(), "kind": "port",
             "sample": f"{rows} of {M} rows of X through oracle HBQ-E quantize + INT8-psum GEMM vs full W, {dt:.1f} s"}
 

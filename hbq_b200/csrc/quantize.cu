@@ -125,7 +125,9 @@ template <int MB>
 __device__ __forceinline__ uint32_t code2_e2(__half2 c)
 {
     const uint32_t a = h2_bits(c) & 0x7FFF7FFFu;
-    const uint32_t nrm = ((a - 0x38003800u) >> (10 - MB)) & (((1u << (MB + 2)) - 1u) * 0x00010001u);
+    // clamp below at 0.5 (0x3800) first so the packed subtraction cannot borrow across halves
+    const uint32_t an = h2_bits(__hmax2(bits_h2(a), bits_h2(0x38003800u)));
+    const uint32_t nrm = ((an - 0x38003800u) >> (10 - MB)) & (((1u << (MB + 2)) - 1u) * 0x00010001u);
     // below 1: k = c * 2^MB, read from the low mantissa bits of k + 1024
     const __half2 k = __hfma2(bits_h2(a), bits_h2(((uint32_t)(0x3C00u + (MB << 10))) * 0x00010001u),
                               bits_h2(0x64006400u));
