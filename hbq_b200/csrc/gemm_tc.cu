@@ -10,10 +10,13 @@
 // alternate, so the epilogue warps drain chunk c (tcgen05.ld -> round / quantise -> fp16 add
 // in registers) while the tensor core computes chunk c+1.
 //
-// One persistent CTA per SM, 320 threads:
+// One persistent CTA per SM, 576 threads:
 //   warp 0      TMA producer: 4-stage ring of {A 128x64, W 256x64} fp16 tiles, 128B swizzle
 //   warp 1      TMEM allocation and MMA issue (one lane)
-//   warps 2-9   epilogue: warp w owns TMEM lanes 32*(w%4).. and column half (w-2)/4
+//   warps 2-17  epilogue: warp w owns TMEM lanes 32*(w%4).. and the 64 columns (w-2)/4
+// The epilogue is the instruction-issue bottleneck (32768 fp32 values per 128-deep chunk against
+// 1024 tensor-pipe cycles), so its arithmetic is packed: fma.rn.f32x2 for the INT8 rounding,
+// cvt.rn.f16x2 and half2 min/max/add for the clamp and the fp16 accumulation.
 // Every mbarrier wait is bounded: on expiry the kernel records a status word, all roles leave
 // their loops, TMEM is freed and the kernel returns.
 #include "common.cuh"
@@ -24,8 +27,9 @@ namespace hbq {
 
 constexpr int BM = 128, BN = 256, BK = 64, NSTAGE = 4;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int TC_THREADS = 320;
-constexpr int EPI_WARPS = 8;
+constexpr int EPI_WARPS = 16;                       // 4 per TMEM lane quarter, 64 columns each
+constexpr int TC_THREADS = 64 + EPI_WARPS * 32;
+constexpr int EPI_COLS = BN / (EPI_WARPS / 4);
 constexpr uint32_t SMEM_BYTES = NSTAGE * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
 
@@ -107,16 +111,21 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, float* v)
     uint32_t r[32];
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr));
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
     #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// d = a * b + c on two fp32 lanes at once
+__device__ __forceinline__ void fma2(float& d0, float& d1, float a0, float a1, float b, float c)
+{
+    asm("{ .reg .b64 ra, rb, rc, rd;\n"
+        " mov.b64 ra, {%2, %3};\n mov.b64 rb, {%4, %4};\n mov.b64 rc, {%5, %5};\n"
+        " fma.rn.f32x2 rd, ra, rb, rc;\n mov.b64 {%0, %1}, rd; }"
+        : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b), "f"(c));
 }
 
 // Shared-memory matrix descriptor: K-major tile, 128-byte swizzle, rows 128 B apart, 8-row
@@ -140,19 +149,27 @@ constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)
 // v / scale is exact, so rint is one FMA against 1.5 * 2^23.  Non-finite partial sums are not
 // given the reference's special treatment.
 template <int GN>
-__device__ __forceinline__ void psum_int8_run(float* v)
+__device__ __forceinline__ void psum_int8_accumulate(const float* v, __half2* acc)
 {
     float mx = 0.f;
     #pragma unroll
-    for (int i = 0; i < GN; ++i) mx = fmaxf(mx, fabsf(v[i]));
+    for (int i = 0; i < GN; i += 2) mx = fmaxf(fmaxf(mx, fabsf(v[i])), fabsf(v[i + 1]));
     const uint32_t e = (__float_as_uint(mx) >> 23) & 0xFFu;
     const float scale = mx > 0.f ? __uint_as_float((e - 6u) << 23) : 1.f;
     const float inv = mx > 0.f ? __uint_as_float((260u - e) << 23) : 1.f;
+    constexpr float kMagic = 12582912.f;                 // 1.5 * 2^23: v*inv + kMagic rounds to an integer (RNE)
+    const float unmagic = -kMagic * scale;               // exact
+    // clamp to +-127 after the conversion to fp16: rounding is monotone, so
+    // min(fp16(q*s), fp16(127*s)) == fp16(min(q, 127)*s)
+    const __half2 lim = __float2half2_rn(127.f * scale);
+    const __half2 nlim = bits_h2(h2_bits(lim) ^ 0x80008000u);
     #pragma unroll
-    for (int i = 0; i < GN; ++i) {
-        float q = __fmaf_rn(v[i], inv, 12582912.f) - 12582912.f;
-        q = fminf(fmaxf(q, -127.f), 127.f);
-        v[i] = q * scale;
+    for (int i = 0; i < GN; i += 2) {
+        float t0, t1, o0, o1;
+        fma2(t0, t1, v[i], v[i + 1], inv, kMagic);
+        fma2(o0, o1, t0, t1, scale, unmagic);            // (t - kMagic) * scale, exact
+        const __half2 h = __hmin2(__hmax2(__floats2half2_rn(o0, o1), nlim), lim);
+        acc[i >> 1] = __hadd2(acc[i >> 1], h);
     }
 }
 
@@ -176,25 +193,33 @@ __device__ float tc_e3m4(float x, float scale)
 }
 
 template <int GN>
-__device__ __forceinline__ void psum_e3m4_run(float* v)
+__device__ __forceinline__ void psum_e3m4_accumulate(const float* v, __half2* acc)
 {
     float mx = 0.f;
     #pragma unroll
     for (int i = 0; i < GN; ++i) mx = fmaxf(mx, fabsf(v[i]));
     const float scale = mx > 0.f ? ldexpf(1.f, ilogbf(mx) - 3) : 1.f;
     #pragma unroll
-    for (int i = 0; i < GN; ++i) v[i] = tc_e3m4(v[i], scale);
+    for (int i = 0; i < GN; i += 2)
+        acc[i >> 1] = __hadd2(acc[i >> 1], __floats2half2_rn(tc_e3m4(v[i], scale), tc_e3m4(v[i + 1], scale)));
 }
 
+// Fold 32 fp32 partial sums (one TMEM load) of this thread's row into its fp16 running sums.
 template <int MODE, int GN>
-__device__ __forceinline__ void psum_quant32(float* v)
+__device__ __forceinline__ void fold_chunk(const float* v, __half2* acc)
 {
     if (MODE == HBQ_ACC_PSUM_INT8) {
         #pragma unroll
-        for (int c = 0; c < 32; c += GN) psum_int8_run<GN>(v + c);
+        for (int c = 0; c < 32; c += GN) psum_int8_accumulate<GN>(v + c, acc + (c >> 1));
     } else if (MODE == HBQ_ACC_PSUM_E3M4) {
         #pragma unroll
-        for (int c = 0; c < 32; c += GN) psum_e3m4_run<GN>(v + c);
+        for (int c = 0; c < 32; c += GN) psum_e3m4_accumulate<GN>(v + c, acc + (c >> 1));
+    } else {
+        #pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const __half2 p = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+            acc[i] = (MODE == HBQ_ACC_FP32) ? p : __hadd2(acc[i], p);
+        }
     }
 }
 
@@ -302,48 +327,43 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         // ================= epilogue =================
         const int ew = warp - 2;
         const int quarter = warp & 3;            // TMEM lanes this warp may touch
-        const int chalf = ew >> 2;               // column half of the 256-wide tile
+        const int cgrp = ew >> 2;                // which EPI_COLS columns of the 256-wide tile
         const int chunks_per_tile = (total_k16 + args.chunk_k16 - 1) / args.chunk_k16;
         uint32_t chunk = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
             const int m0 = (t % args.tiles_m) * BM, n0 = (t / args.tiles_m) * BN;
-            __half2 acc[64];
+            __half2 acc[EPI_COLS / 2];
             #pragma unroll
-            for (int i = 0; i < 64; ++i) acc[i] = __float2half2_rn(0.f);
+            for (int i = 0; i < EPI_COLS / 2; ++i) acc[i] = __float2half2_rn(0.f);
             for (int c = 0; c < chunks_per_tile; ++c, ++chunk) {
                 const uint32_t buf = chunk & 1u;
                 ok = mbar_wait(bar_tfull + 8 * buf, (chunk >> 1) & 1u, abort_flag, 4);
                 ok = __all_sync(0xFFFFFFFFu, ok);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN + chalf * 128;
+                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN + cgrp * EPI_COLS;
                 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
+                for (int h = 0; h < EPI_COLS / 32; ++h) {
                     float v[32];
-                    tc_ld32(taddr + q * 32, v);
-                    if (q == 3) {
-                        // all of this warp's reads of the buffer are complete: hand it back
+                    tc_ld32(taddr + h * 32, v);
+                    if (h == EPI_COLS / 32 - 1) {
+                        // this warp's reads of the accumulator are complete: hand it back to the MMA warp
                         tc_fence_before();
                         __syncwarp();
                         if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
                     }
-                    if (MODE >= HBQ_ACC_PSUM_INT8) psum_quant32<MODE, GN>(v);
-                    #pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        const __half2 p = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
-                        acc[q * 16 + i] = (MODE == HBQ_ACC_FP32) ? p : __hadd2(acc[q * 16 + i], p);
-                    }
+                    fold_chunk<MODE, GN>(v, acc + h * 16);
                 }
             }
             if (!ok) break;
-            // ---- write the thread's row: 128 columns starting at n0 + chalf*128 ----
+            // ---- write the thread's row: EPI_COLS columns starting at n0 + cgrp*EPI_COLS ----
             const int row = m0 + quarter * 32 + lane;
-            const int col0 = n0 + chalf * 128;
+            const int col0 = n0 + cgrp * EPI_COLS;
             if (row < args.M) {
                 __half* cp = args.C + (int64_t)row * args.N + col0;
                 #pragma unroll
-                for (int g = 0; g < 16; ++g) {
+                for (int g = 0; g < EPI_COLS / 8; ++g) {
                     const int col = col0 + g * 8;
                     if (col >= args.N) break;
                     __half2 o[4] = {acc[4 * g], acc[4 * g + 1], acc[4 * g + 2], acc[4 * g + 3]};
