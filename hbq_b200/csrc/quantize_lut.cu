@@ -1,0 +1,442 @@
+// HBQ activation quantize, table-driven variant (one scale scheme, up to 4 micro-scale candidates).
+//
+// The arithmetic variant in quantize.cu evaluates Q(fp16(a / t_i)) for every candidate t_i with
+// ~20 instructions per element pair and is instruction-issue bound at ~10 % of HBM bandwidth.
+// Here the observation is that, for a fixed format, fp16(Q(fp16(a / t_i)) * t_i) is a function of
+// the fp16 pattern of |a| = |x / l1| alone, monotone (bar one E2M1 exception), and saturated
+// above ~18.  Each CTA therefore builds, once, a shared-memory table indexed by that pattern
+// holding the four candidates' values as fp16; the per-element work becomes one 8-byte shared
+// load plus packed fp16 arithmetic in which the two halves of a half2 are two CANDIDATES:
+//   r = fma(-value, l1, |x|)  (= fp16(|x| - fp16(value * l1)), the product is exact)
+//   e = r * r                 (fp16, as the reference rounds it)
+//   acc += e                  (fp32, add.rn.f32.f16)
+// The table is filled from 60 thresholds that the host finds by bisection with an exact scalar
+// restatement of the element quantizer, so the kernel's results stay bit-identical to the
+// reference's (src/quantizer.py:741-859).
+#include "quantize_dev.cuh"
+#include <math.h>
+#include <string.h>
+
+namespace hbq {
+
+constexpr int LUT_MAX_CAND = 4;
+constexpr int LUT_MAX_LEVELS = 32;
+
+struct LutPlan {
+    int nlev;                                   // 2^(mbit+2) magnitudes of E2M<mbit>
+    int base, hi;                               // table covers |a| patterns [base, hi]; entry 0 = all zero
+    uint16_t thr[LUT_MAX_CAND][LUT_MAX_LEVELS]; // thr[i][k]: smallest |a| pattern whose level is >= k
+    uint16_t val[LUT_MAX_CAND][LUT_MAX_LEVELS]; // fp16 pattern of level_k * t_i
+    uint16_t zmax[LUT_MAX_CAND];                // largest |a| pattern with fp16(a / t_i) == 0
+    uint16_t hole[LUT_MAX_CAND][4];             // E2M1: |a| patterns with fp16(a / t_i) == 0x39FF (value 0)
+    int nhole[LUT_MAX_CAND];
+};
+
+// ---- exact host-side scalar arithmetic on fp16 patterns ------------------------------------------
+static double h2d(uint16_t b)
+{
+    const int e = (b >> 10) & 31, m = b & 1023;
+    const double v = e == 0 ? ldexp((double)m, -24) : ldexp((double)(1024 + m), e - 25);
+    return (b & 0x8000) ? -v : v;
+}
+// round a non-negative double to the nearest fp16 pattern (ties to even); saturates to infinity
+static uint16_t d2h(double v)
+{
+    if (!(v > 0.0)) return 0;
+    int ex;
+    frexp(v, &ex);                              // v = f * 2^ex, f in [0.5, 1)
+    int e = ex - 1;                             // floor(log2 v)
+    if (e < -14) e = -14;                       // subnormal range: fixed quantum 2^-24
+    const double q = ldexp(v, 10 - e);          // in units of the quantum
+    double r = nearbyint(q);                    // FE_TONEAREST: ties to even
+    if (e == -14 && r < 1024.0) return (uint16_t)r;
+    if (r >= 2048.0) { r = 1024.0; ++e; }
+    if (e > 15) return 0x7C00;
+    return (uint16_t)(((e + 15) << 10) | ((int)r - 1024));
+}
+
+// Level index (= code magnitude {exp, mant}) of the E2M<mb> element quantizer for |b| given as an
+// fp16 pattern: the closed form of make_fp_quant (src/quantizer.py:202-255) used by the kernels.
+// hole_as: what the E2M1 exception |b| = 0x39FF returns (the reference gives 0).
+static int e2_level(int mb, uint16_t b, int hole_as)
+{
+    const uint16_t a = b & 0x7FFF;
+    if (a >= 0x3C00) {
+        const uint16_t half = 0x0200 >> mb, mask = ~((0x0400 >> mb) - 1);
+        uint16_t n = (uint16_t)((a + half) & mask);
+        const uint16_t mx = 0x4400 | (((1u << mb) - 1u) << (10 - mb));
+        if (n > mx) n = mx;
+        return (n - 0x3800) >> (10 - mb);
+    }
+    if (mb == 1 && a == 0x39FF) return hole_as;
+    const uint16_t w = d2h(h2d(a) * (double)(1 << mb) + 0.50048828125);
+    return (int)floor(h2d(w));
+}
+static double e2_value(int mb, int level)
+{
+    const int ef = level >> mb, mf = level & ((1 << mb) - 1);
+    return ef == 0 ? (double)mf / (1 << mb) : (1.0 + (double)mf / (1 << mb)) * ldexp(1.0, ef - 1);
+}
+
+// Build the plan for element E2M<mb> and candidate micro-scales tab[0..nc).  Returns false when
+// the format does not fit the table kernel.
+bool lut_plan_build(int mb, const float* tab, int nc, LutPlan* p)
+{
+    if (mb < 1 || mb > 3 || nc < 1 || nc > LUT_MAX_CAND) return false;
+    memset(p, 0, sizeof(*p));
+    p->nlev = 1 << (mb + 2);
+    int lo = 0x7BFF, hi = 0;
+    for (int i = 0; i < LUT_MAX_CAND; ++i) {
+        const double t = tab[i < nc ? i : nc - 1];      // unused slots repeat the last candidate
+        if (!(t >= 1.0) || t > 64.0) return false;
+        auto level_of = [&](uint16_t u, int hole_as) { return e2_level(mb, d2h(h2d(u) / t), hole_as); };
+        for (int k = 1; k < p->nlev; ++k) {             // smallest u with level >= k (monotone version)
+            int a = 0, b = 0x7BFF;                      // invariant: level(a) < k <= level(b)
+            if (level_of((uint16_t)b, 2) < k) return false;
+            while (b - a > 1) {
+                const int mid = (a + b) >> 1;
+                if (level_of((uint16_t)mid, 2) >= k) b = mid; else a = mid;
+            }
+            p->thr[i][k] = (uint16_t)b;
+        }
+        for (int k = 0; k < p->nlev; ++k) {
+            const double v = e2_value(mb, k) * t;
+            const uint16_t hb = d2h(v);
+            if (h2d(hb) != v) return false;             // level * t must be exact in fp16
+            p->val[i][k] = hb;
+        }
+        int z = 0;
+        while (z < 0x0400 && d2h(h2d((uint16_t)(z + 1)) / t) == 0) ++z;
+        p->zmax[i] = (uint16_t)z;
+        if (mb == 1) {                                  // the E2M1 hole, mapped back to |a|
+            const int c = d2h(h2d(0x39FF) * t);
+            for (int u = c - 4; u <= c + 4; ++u)
+                if (u > 0 && d2h(h2d((uint16_t)u) / t) == 0x39FF && p->nhole[i] < 4)
+                    p->hole[i][p->nhole[i]++] = (uint16_t)u;
+        }
+        if (p->thr[i][1] < lo) lo = p->thr[i][1];
+        if (p->thr[i][p->nlev - 1] > hi) hi = p->thr[i][p->nlev - 1];
+    }
+    p->base = lo - 1;
+    p->hi = hi;
+    return p->base >= 1 && (p->hi - p->base + 1) <= 8191;   // byte offsets of the entries must fit 16 bits
+}
+
+
+// ---- kernel arguments -----------------------------------------------------------------------------
+struct LutArgs {
+    QArgs q;                  // tensor geometry, pointers and output selection (shared helpers use it)
+    LutPlan plan;
+    uint16_t rm[8];           // fp16(1 / m) for the eight E5M3 mantissas m = 1 + i/8
+    uint16_t rt[LUT_MAX_CAND];// fp16(1 / t_i), for the code extraction
+    float inv_ele_max;        // 1 / (element max * largest candidate), rounded to fp32
+    uint16_t big_l1;          // smallest l1 pattern with l1 * max value > 65504 (fp16 overflow of deq)
+    int lpm, log2lpm;         // lanes per micro-block (l2_block_size / 8) and its log2
+    int iters;                // chunks per thread
+    int64_t step_rows, step_chunks;   // one grid stride of chunks = step_rows rows + step_chunks chunks
+};
+
+constexpr int LUT_THREADS = 512;
+
+// acc_lo += lo(e), acc_hi += hi(e): fp32 accumulation of two fp16 values (one rounding each)
+__device__ __forceinline__ void add2_f32_f16(float& acc_lo, float& acc_hi, uint32_t e)
+{
+    asm("{ .reg .b16 lo, hi;\n mov.b32 {lo, hi}, %2;\n"
+        " add.rn.f32.f16 %0, lo, %0;\n add.rn.f32.f16 %1, hi, %1; }"
+        : "+f"(acc_lo), "+f"(acc_hi) : "r"(e));
+}
+
+// ---- the kernel -----------------------------------------------------------------------------------
+template <int MB, bool CODES>
+__global__ void __launch_bounds__(LUT_THREADS, 2) hbq_lut_kernel(const LutArgs a)
+{
+    extern __shared__ uint2 lut[];
+    const QArgs& q = a.q;
+    const int tid = threadIdx.x;
+
+    // -- build the table: entry e covers |a| pattern base + e and holds the 4 candidates' values.
+    //    Each thread walks its entries in increasing order, so every candidate's level only moves up.
+    __shared__ uint16_t s_thr[LUT_MAX_CAND][LUT_MAX_LEVELS + 1], s_val[LUT_MAX_CAND][LUT_MAX_LEVELS];
+    for (int i = tid; i < LUT_MAX_CAND * LUT_MAX_LEVELS; i += LUT_THREADS) {
+        const int c = i / LUT_MAX_LEVELS, k = i % LUT_MAX_LEVELS;
+        s_thr[c][k] = (k >= 1 && k < a.plan.nlev) ? a.plan.thr[c][k] : (uint16_t)0xFFFF;
+        s_val[c][k] = a.plan.val[c][k];
+        if (k == 0) s_thr[c][LUT_MAX_LEVELS] = 0xFFFF;
+    }
+    __syncthreads();
+    {
+        const int n = a.plan.hi - a.plan.base + 1;
+        int lvl[LUT_MAX_CAND] = {0, 0, 0, 0};
+        for (int e = tid; e < n; e += LUT_THREADS) {
+            const uint32_t u = (uint32_t)(a.plan.base + e);
+            uint32_t v[LUT_MAX_CAND];
+            #pragma unroll
+            for (int i = 0; i < LUT_MAX_CAND; ++i) {
+                while (u >= s_thr[i][lvl[i] + 1]) ++lvl[i];
+                uint32_t val = s_val[i][lvl[i]];
+                if (MB == 1)
+                    for (int h = 0; h < a.plan.nhole[i]; ++h)
+                        if (u == a.plan.hole[i][h]) val = 0;
+                v[i] = val;
+            }
+            lut[e] = make_uint2(v[0] | (v[1] << 16), v[2] | (v[3] << 16));
+        }
+    }
+    __syncthreads();
+
+    const int lane = tid & 31;
+    const int lig = tid & (q.G - 1);
+    const uint32_t base2 = (uint32_t)a.plan.base * 0x00010001u, hi2 = (uint32_t)a.plan.hi * 0x00010001u;
+    const int nl2 = q.f.block_size / q.f.l2_block_size;
+
+    int64_t ci = (int64_t)blockIdx.x * LUT_THREADS + tid;
+    int64_t row = 0, c = 0;
+    split_chunk(q, ci < q.total_chunks ? ci : 0, row, c);
+    for (int it = 0; it < a.iters; ++it, ci += (int64_t)gridDim.x * LUT_THREADS) {
+        if (it > 0) {                                          // advance (row, chunk-in-row) by one grid stride
+            row += a.step_rows; c += a.step_chunks;
+            if (c >= q.cpr) { c -= q.cpr; ++row; }
+        }
+        if (ci - lane >= q.total_chunks) break;                // warp-uniform
+        const bool valid = ci < q.total_chunks;
+        const int64_t k0 = c * 8;
+        Chunk x;
+        if (valid) x = load_chunk(q, row, k0);
+        else { for (int p = 0; p < 4; ++p) x.h[p] = bits_h2(0u); }
+
+        uint32_t sg[4], ax[4];
+        #pragma unroll
+        for (int p = 0; p < 4; ++p) { sg[p] = h2_bits(x.h[p]) & 0x80008000u; ax[p] = h2_bits(x.h[p]) & 0x7FFF7FFFu; }
+
+        // -- block maximum and the E5M3 shared scale (round-half-up of the 3-bit mantissa) --
+        uint32_t mx = h2_bits(__hmax2(__hmax2(bits_h2(ax[0]), bits_h2(ax[1])), __hmax2(bits_h2(ax[2]), bits_h2(ax[3]))));
+        for (int off = q.G >> 1; off >= 1; off >>= 1)
+            mx = h2_bits(__hmax2(bits_h2(mx), bits_h2(__shfl_xor_sync(0xFFFFFFFFu, mx, off))));
+        const uint32_t am16 = max(mx & 0xFFFFu, mx >> 16);
+        // amax / ele_max as a multiplication by the rounded reciprocal: exact after the fp16 rounding
+        // because ele_max has a short significand (same argument as div2_h)
+        const float sf = __half2float(bits_h((uint16_t)am16)) * a.inv_ele_max;
+        uint32_t sb = (uint32_t)h_bits(__float2half_rn(sf));
+        sb = min(max(sb, 0x0400u), 0x7B80u);
+        const uint32_t l1b = (sb + 0x40u) & 0xFF80u;
+
+        // -- a = fp16(|x| / l1): l1 = m * 2^e; |x| is pre-scaled so that the residual of the
+        //    division by m stays exact, then the quotient is scaled back (exact unless a < 2^-14) --
+        const int e5 = (int)(l1b >> 10) - 15;
+        const int s1 = min(15, 8 - e5);
+        const uint32_t pre2 = ((uint32_t)(s1 + 15) << 10) * 0x00010001u;
+        const uint32_t post2 = ((uint32_t)(15 - (s1 + e5)) << 10) * 0x00010001u;
+        const uint32_t nm2 = (0xBC00u | (l1b & 0x03FFu)) * 0x00010001u;          // -m
+        const uint32_t rm2 = (uint32_t)a.rm[(l1b >> 7) & 7u] * 0x00010001u;
+        const __half2 l1_2 = bits_h2(l1b * 0x00010001u), nl1_2 = bits_h2((l1b | 0x8000u) * 0x00010001u);
+        const bool big = l1b >= a.big_l1;
+
+        __half2 aa[4];
+        uint32_t w[4];
+        #pragma unroll
+        for (int p = 0; p < 4; ++p) {
+            const __half2 axs = __hmul2(bits_h2(ax[p]), bits_h2(pre2));
+            const __half2 q0 = __hmul2(axs, bits_h2(rm2));
+            const __half2 r = __hfma2(q0, bits_h2(nm2), axs);
+            const __half2 q1 = __hfma2(r, bits_h2(rm2), q0);
+            aa[p] = __hmul2(q1, bits_h2(post2));
+            // byte offset of the table entry (8 B each; at most 12288 entries, so it fits 16 bits)
+            w[p] = (h2_bits(__hmin2(__hmax2(aa[p], bits_h2(base2)), bits_h2(hi2))) - base2) << 3;
+        }
+
+        // -- every candidate's squared error, two candidates per half2 --
+        uint32_t ct01[8], ct23[8];
+        float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
+        if (!big) {
+            #pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int p = j >> 1;
+                const uint32_t off = (j & 1) ? (w[p] >> 16) : (w[p] & 0xFFFFu);
+                const uint2 ent = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(lut) + off);
+                ct01[j] = ent.x; ct23[j] = ent.y;
+                const __half2 axb = (j & 1) ? __high2half2(bits_h2(ax[p])) : __low2half2(bits_h2(ax[p]));
+                const __half2 r01 = __hfma2(bits_h2(ent.x), nl1_2, axb), r23 = __hfma2(bits_h2(ent.y), nl1_2, axb);
+                add2_f32_f16(acc0, acc1, h2_bits(__hmul2(r01, r01)));
+                add2_f32_f16(acc2, acc3, h2_bits(__hmul2(r23, r23)));
+            }
+        } else {
+            // value * l1 may overflow to infinity here: keep the product's own rounding
+            #pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int p = j >> 1;
+                const uint32_t off = (j & 1) ? (w[p] >> 16) : (w[p] & 0xFFFFu);
+                const uint2 ent = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(lut) + off);
+                ct01[j] = ent.x; ct23[j] = ent.y;
+                const __half2 axb = (j & 1) ? __high2half2(bits_h2(ax[p])) : __low2half2(bits_h2(ax[p]));
+                const __half2 r01 = __hsub2(axb, __hmul2(bits_h2(ent.x), l1_2));
+                const __half2 r23 = __hsub2(axb, __hmul2(bits_h2(ent.y), l1_2));
+                add2_f32_f16(acc0, acc1, h2_bits(__hmul2(r01, r01)));
+                add2_f32_f16(acc2, acc3, h2_bits(__hmul2(r23, r23)));
+            }
+        }
+        for (int off = a.lpm >> 1; off >= 1; off >>= 1) {
+            acc0 += __shfl_xor_sync(0xFFFFFFFFu, acc0, off); acc1 += __shfl_xor_sync(0xFFFFFFFFu, acc1, off);
+            acc2 += __shfl_xor_sync(0xFFFFFFFFu, acc2, off); acc3 += __shfl_xor_sync(0xFFFFFFFFu, acc3, off);
+        }
+        // first minimum of the fp16-rounded sums (non-negative fp16 patterns order like integers)
+        const uint32_t E01 = h2_bits(__floats2half2_rn(acc0, acc1)), E23 = h2_bits(__floats2half2_rn(acc2, acc3));
+        uint32_t bv = E01 & 0xFFFFu;
+        int best = 0;
+        if ((E01 >> 16) < bv) { bv = E01 >> 16; best = 1; }
+        if ((E23 & 0xFFFFu) < bv) { bv = E23 & 0xFFFFu; best = 2; }
+        if ((E23 >> 16) < bv) { bv = E23 >> 16; best = 3; }
+
+        // -- the winner's values, signs and (optionally) codes --
+        const uint32_t psel = (best & 1) ? 0x7632u : 0x5410u;
+        __half2 dq[4];
+        uint32_t mag[4], sgo[4], tiny[4];
+        #pragma unroll
+        for (int p = 0; p < 4; ++p) {
+            const uint32_t ra = best < 2 ? ct01[2 * p] : ct23[2 * p], rb = best < 2 ? ct01[2 * p + 1] : ct23[2 * p + 1];
+            const __half2 ctw = bits_h2(__byte_perm(ra, rb, psel));
+            const __half2 d = __hmul2(ctw, l1_2);
+            // negative inputs whose quotient a is tiny: candidates for the reference's "+0" rule below
+            tiny[p] = __hle2_mask(aa[p], bits_h2(0x00200020u)) & ((sg[p] >> 15) * 0xFFFFu);
+            const uint32_t s = sg[p];
+            dq[p] = bits_h2(h2_bits(d) | s);
+            sgo[p] = s;
+            if (CODES) mag[p] = code2_e2<MB>(__hmul2(ctw, bits_h2((uint32_t)a.rt[best] * 0x00010001u)));
+        }
+
+        // The reference returns +0 (not -0) when fp16(a / t) is exactly zero.  Deciding that needs
+        // the exact a for tiny quotients, where the scaled division above may be off: rare, so branch.
+        if (tiny[0] | tiny[1] | tiny[2] | tiny[3]) {
+            const float l1f = __half2float(bits_h((uint16_t)l1b)), t = q.tab[0][best < q.nc ? best : q.nc - 1];
+            #pragma unroll
+            for (int p = 0; p < 4; ++p)
+                #pragma unroll
+                for (int h = 0; h < 2; ++h)
+                    if ((tiny[p] >> (16 * h)) & 1u) {
+                        const float xf = __half2float(bits_h((uint16_t)(ax[p] >> (16 * h))));
+                        if (rh(__fdiv_rn(rh(__fdiv_rn(xf, l1f)), t)) == 0.f) {
+                            const uint32_t clr = ~(0x8000u << (16 * h));
+                            dq[p] = bits_h2(h2_bits(dq[p]) & clr);
+                            sgo[p] &= clr;
+                        }
+                    }
+        }
+
+        uint32_t l2word = 0;
+        const bool mb_leader = (lig & (a.lpm - 1)) == 0;         // first lane of its micro-block
+        const int mb_index = lig >> a.log2lpm;
+        if (mb_leader) l2word = (uint32_t)best << (mb_index * q.f.l2_sc_bit);
+        if (q.out.l2_packed) l2word = group_or(l2word, q.G);
+
+        if (!valid) continue;
+        const int64_t kb = c >> q.log2G;
+        store_deq(q, row, k0, dq);
+        if (CODES) store_codes<false>(q, row, k0, mag, sgo);
+        if (q.out.l2_idx && mb_leader) q.out.l2_idx[(row * q.nblk + kb) * nl2 + mb_index] = (uint8_t)best;
+        if (lig == 0) {
+            store_scale(q, row, kb, __half2float(bits_h((uint16_t)l1b)));
+            if (q.out.scheme) q.out.scheme[row * q.nblk + kb] = 0;
+            if (q.out.l2_packed) {
+                const int nbytes = (nl2 * q.f.l2_sc_bit) >> 3;
+                uint8_t* lp = q.out.l2_packed + (row * q.nblk + kb) * nbytes;
+                if (nbytes == 4) *reinterpret_cast<uint32_t*>(lp) = l2word;
+                else if (nbytes == 2) *reinterpret_cast<uint16_t*>(lp) = (uint16_t)l2word;
+                else *lp = (uint8_t)l2word;
+            }
+        }
+    }
+}
+
+// ---- host side ------------------------------------------------------------------------------------
+}  // namespace hbq
+#include <mutex>
+#include <vector>
+namespace hbq {
+
+struct CachedPlan {
+    int mb, nc;
+    float tab[LUT_MAX_CAND];
+    bool ok;
+    LutPlan plan;
+};
+static std::mutex g_plan_mutex;
+static std::vector<CachedPlan> g_plans;
+
+// Plans depend on the format only; building one costs ~2000 scalar quantizer evaluations.
+static bool get_plan(int mb, const float* tab, int nc, LutPlan* out)
+{
+    std::lock_guard<std::mutex> lock(g_plan_mutex);
+    for (const CachedPlan& c : g_plans)
+        if (c.mb == mb && c.nc == nc && memcmp(c.tab, tab, sizeof(float) * nc) == 0) {
+            if (c.ok) *out = c.plan;
+            return c.ok;
+        }
+    CachedPlan c;
+    memset(&c, 0, sizeof(c));
+    c.mb = mb; c.nc = nc;
+    memcpy(c.tab, tab, sizeof(float) * nc);
+    c.ok = lut_plan_build(mb, tab, nc, &c.plan);
+    if (g_plans.size() < 64) g_plans.push_back(c);
+    if (c.ok) *out = c.plan;
+    return c.ok;
+}
+
+template <int MB>
+static int launch_lut(const LutArgs& a, bool codes, int grid, size_t smem, cudaStream_t stream)
+{
+    if (codes) {
+        HBQ_CUDA_TRY(cudaFuncSetAttribute(hbq_lut_kernel<MB, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        hbq_lut_kernel<MB, true><<<grid, LUT_THREADS, smem, stream>>>(a);
+    } else {
+        HBQ_CUDA_TRY(cudaFuncSetAttribute(hbq_lut_kernel<MB, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        hbq_lut_kernel<MB, false><<<grid, LUT_THREADS, smem, stream>>>(a);
+    }
+    HBQ_LAUNCH_CHECK("hbq_lut_kernel");
+    return HBQ_OK;
+}
+
+// Runs the table kernel if the (already validated) HBQ arguments fit it.  *launched tells the
+// caller whether it did; when it did not, the arithmetic kernel must be used.
+int hbq_lut_try_launch(const QArgs& qa, int mb, cudaStream_t stream, bool* launched)
+{
+    *launched = false;
+    const int L = qa.f.l2_block_size;
+    if (qa.nscheme != 1 || qa.nc > LUT_MAX_CAND || !qa.scale_fast_e5m3 || L < 8 || mb < 1 || mb > 3) return HBQ_OK;
+    LutArgs a;
+    memset(&a, 0, sizeof(a));
+    if (!get_plan(mb, qa.tab[0], qa.nc, &a.plan)) return HBQ_OK;
+    a.q = qa;
+    a.lpm = L / 8;
+    while ((1 << a.log2lpm) < a.lpm) ++a.log2lpm;
+    for (int i = 0; i < 8; ++i) a.rm[i] = d2h(1.0 / (1.0 + i / 8.0));
+    double vmax = 0;
+    for (int i = 0; i < LUT_MAX_CAND; ++i) {
+        a.rt[i] = d2h(1.0 / (double)qa.tab[0][i < qa.nc ? i : qa.nc - 1]);
+        const double v = h2d(a.plan.val[i][a.plan.nlev - 1]);
+        if (v > vmax) vmax = v;
+    }
+    a.inv_ele_max = 1.f / qa.ele_max[0];
+    a.big_l1 = 0x7C00;
+    for (int pat = 0x0400; pat <= 0x7B80; pat += 0x80)
+        if (h2d((uint16_t)pat) * vmax > 65504.0) { a.big_l1 = (uint16_t)pat; break; }
+
+    int dev = 0, sms = 0;
+    HBQ_CUDA_TRY(cudaGetDevice(&dev));
+    HBQ_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    const int64_t need = (qa.total_chunks + LUT_THREADS - 1) / LUT_THREADS;
+    const int grid = (int)(need < 2 * sms ? need : 2 * sms);
+    a.iters = (int)((need + grid - 1) / grid);
+    a.step_rows = ((int64_t)grid * LUT_THREADS) / qa.cpr;
+    a.step_chunks = ((int64_t)grid * LUT_THREADS) % qa.cpr;
+    const size_t smem = (size_t)(a.plan.hi - a.plan.base + 1) * sizeof(uint2);
+    const bool codes = qa.out.codes != nullptr;
+    int rc;
+    switch (mb) {
+        case 1: rc = launch_lut<1>(a, codes, grid, smem, stream); break;
+        case 2: rc = launch_lut<2>(a, codes, grid, smem, stream); break;
+        default: rc = launch_lut<3>(a, codes, grid, smem, stream); break;
+    }
+    if (rc == HBQ_OK) *launched = true;
+    return rc;
+}
+
+}  // namespace hbq
