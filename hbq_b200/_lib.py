@@ -14,11 +14,13 @@ KIND_MXFP, KIND_MXINT, KIND_HBQ = 0, 1, 2
 DTYPE_F16, DTYPE_BF16 = 0, 1
 L2_SCHEMES = ["PoT", "INT", "SIG-1", "FP-1", "FP1", "FP-10", "FP-100", "Mix"]
 ACC_FP32, ACC_FP16, ACC_GROUPED, ACC_PSUM_INT8, ACC_PSUM_E3M4 = range(5)
+GEMM_NOALLOC_MAX_ELEMS = 4 * 1024 * 1024      # HBQ_GEMM_NOALLOC_MAX_ELEMS
 
 # every symbol include/hbq_b200.h declares
 EXPORTS = [
     "hbq_quantize", "hbq_absmax", "hbq_absmax_scratch_bytes", "hbq_dequantize", "hbq_fp_quant",
     "hbq_gemm", "hbq_gemm_workspace_bytes", "hbq_gemm_uses_tensor_cores", "hbq_gemm_simt",
+    "hbq_gemm_kn_noalloc",
     "hbq_gemm_status", "hbq_gemm_status_reset", "hbq_error_string", "hbq_last_cuda_error",
     "hbq_version", "hbq_launch_count",
 ]
@@ -63,6 +65,7 @@ def lib() -> ctypes.CDLL:
     L.hbq_fp_quant.argtypes = [vp, i64, ci, ci, ci, ci, ci, vp, vp]
     L.hbq_gemm.argtypes = [vp, vp, vp, i64, i64, i64, ci, ci, ci, ci, vp, vp, i64, vp]
     L.hbq_gemm_simt.argtypes = [vp, vp, vp, i64, i64, i64, ci, ci, ci, ci, vp, vp]
+    L.hbq_gemm_kn_noalloc.argtypes = [vp, vp, vp, i64, i64, i64, ci, ci, ci, vp, vp]
     L.hbq_gemm_workspace_bytes.argtypes = [i64, i64, i64, ci, ci, ci, ci]
     L.hbq_gemm_workspace_bytes.restype = i64
     L.hbq_gemm_uses_tensor_cores.argtypes = [i64, i64, i64, ci, ci, ci, ci]

@@ -257,6 +257,8 @@ const char* hbq_error_string(int code)
         case HBQ_ERR_ALIGN: return "pointer not 16-byte aligned";
         case HBQ_ERR_WORKSPACE: return "workspace missing, too small or misaligned";
         case HBQ_ERR_DEVICE: return "device error reported by a kernel";
+        case HBQ_ERR_TOO_LARGE: return "operand larger than the fixed scratch of the no-allocation entry point "
+                                       "(N*K > HBQ_GEMM_NOALLOC_MAX_ELEMS)";
     }
     return "unknown error";
 }

@@ -134,6 +134,25 @@ int hbq_gemm_simt(const void* A, const void* B, void* C, int64_t M, int64_t N, i
                   int b_is_nk, int mode, int group_k, int group_n, const void* bias,
                   void* stream);
 
+/* Same computation as hbq_gemm with b_is_nk = 0 (B is [K,N]), for callers that cannot hand over
+ * device scratch because they cannot allocate any: a plugin running inside a host framework
+ * whose memory pool it must not touch, a server that freezes its allocations after start-up,
+ * a latency-critical loop that cannot afford cudaMalloc's implicit synchronisation.  The
+ * transposed copy of B lives in an array inside the library image instead, so
+ *   - every GPU that loads the library holds HBQ_GEMM_NOALLOC_MAX_ELEMS * 2 bytes (8 MiB) for
+ *     the life of the process, and N*K above that limit returns HBQ_ERR_TOO_LARGE;
+ *   - the call itself performs no cudaMalloc / cudaFree and calls no allocating library routine;
+ *   - the first call on each device looks the array's device address up (with that device
+ *     current); make that first call before starting any stream capture;
+ *   - all calls share the one array, which keeps the previous call's contents: each call
+ *     rewrites the N*K values it reads, nothing needs to start at zero, but two calls that
+ *     overlap on the GPU (different streams) race on it -- keep them on one stream.
+ * This entry point has no counterpart in the reference, whose caller allocates the transposed
+ * weight with torch on every call (src/ops.py:41). */
+#define HBQ_GEMM_NOALLOC_MAX_ELEMS (4 * 1024 * 1024)
+int hbq_gemm_kn_noalloc(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
+                        int mode, int group_k, int group_n, const void* bias, void* stream);
+
 /* The tensor-core kernel bounds every wait on an mbarrier.  If one expires the kernel stops,
  * frees its tensor memory and records which wait gave up in a device status word; the output
  * of that call is then undefined.  hbq_gemm_status copies the word to the host (it
@@ -152,7 +171,8 @@ int hbq_version(void);
 int64_t hbq_launch_count(void);
 
 enum { HBQ_OK = 0, HBQ_ERR_ARG = -1, HBQ_ERR_UNSUPPORTED = -2, HBQ_ERR_CUDA = -3,
-       HBQ_ERR_ALIGN = -4, HBQ_ERR_WORKSPACE = -5, HBQ_ERR_DEVICE = -6 };
+       HBQ_ERR_ALIGN = -4, HBQ_ERR_WORKSPACE = -5, HBQ_ERR_DEVICE = -6,
+       HBQ_ERR_TOO_LARGE = -7 };
 
 #ifdef __cplusplus
 }
