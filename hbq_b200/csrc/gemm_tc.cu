@@ -10,10 +10,10 @@
 // alternate, so the epilogue warps drain chunk c (tcgen05.ld -> round / quantise -> fp16 add
 // in registers) while the tensor core computes chunk c+1.
 //
-// One persistent CTA per SM, 576 threads:
+// One persistent CTA per SM, 320 threads (576 with 16 epilogue warps):
 //   warp 0      TMA producer: 4-stage ring of {A 128x64, W 256x64} fp16 tiles, 128B swizzle
 //   warp 1      TMEM allocation and MMA issue (one lane)
-//   warps 2-17  epilogue: warp w owns TMEM lanes 32*(w%4).. and the 64 columns (w-2)/4
+//   warps 2-9   epilogue: warp w owns TMEM lanes 32*(w%4).. and the 128 columns (w-2)/4
 // The epilogue is the instruction-issue bottleneck (32768 fp32 values per 128-deep chunk against
 // 1024 tensor-pipe cycles), so its arithmetic is packed: fma.rn.f32x2 for the INT8 rounding,
 // cvt.rn.f16x2 and half2 min/max/add for the clamp and the fp16 accumulation.
@@ -22,16 +22,15 @@
 #include "common.cuh"
 #include <cuda.h>
 #include <math.h>
+#include <stdlib.h>
 
 namespace hbq {
 
 constexpr int BM = 128, BN = 256, BK = 64, NSTAGE = 4;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int EPI_WARPS = 16;                       // 4 per TMEM lane quarter, 64 columns each
-constexpr int TC_THREADS = 64 + EPI_WARPS * 32;
-constexpr int EPI_COLS = BN / (EPI_WARPS / 4);
+// Epilogue warps per CTA (template parameter EPW): 8 = two per TMEM lane quarter, 128 columns
+// each, TMEM loads double-buffered in registers; 16 = four per quarter, 64 columns each.
 constexpr uint32_t SMEM_BYTES = NSTAGE * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
 
 __device__ int g_tc_status;   // 0 = ok; otherwise the code of the wait that expired
 
@@ -60,28 +59,37 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n .reg .pred p;\n"
+        " mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        " selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ unsigned long long gtime_ns()
 {
     unsigned long long t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     return t;
 }
-// Bounded wait.  Returns false when the limit expired or another role already gave up.
-__device__ __noinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code)
+// Bounded wait.  Returns false when the limit expired or another role already gave up.  The
+// polls are non-suspending and the loop body is minimal: a poll of a completed barrier costs
+// ~160 cycles of the waiting thread, which matters for the single MMA-issuing thread.  The
+// iteration cap (2^23 polls, a fraction of a second at any clock) is the bound; the caller's
+// `code` tells hbq_gemm_status which wait gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code)
 {
-    if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = gtime_ns();
-    for (uint32_t it = 1;; ++it) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((it & 63u) == 0u) {
-            if (*abort_flag) return false;
-            if (gtime_ns() - t0 > WAIT_LIMIT_NS) {
-                *abort_flag = 1;
-                atomicCAS(&g_tc_status, 0, code);
-                return false;
-            }
-        }
+    #pragma unroll 1
+    for (uint32_t it = 0; it < (1u << 23); ++it) {
+        if (mbar_test(bar, parity)) return true;
+        if ((it & 127u) == 127u && *abort_flag) return false;
     }
+    *abort_flag = 1;
+    atomicCAS(&g_tc_status, 0, code);
+    return false;
 }
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar)
@@ -119,6 +127,24 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, float* v)
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// The same load split in two, so that a second load can be in flight while the first one's
+// values are consumed: issue, then (later) wait.  The wait names the registers as in/out operands
+// so that the compiler cannot move their consumers above it.
+__device__ __forceinline__ void tc_ld32_issue(uint32_t taddr, uint32_t* r)
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tc_ld_wait(uint32_t* r)
+{
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+        : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+        :: "memory");
+}
+
 // d = a * b + c on two fp32 lanes at once
 __device__ __forceinline__ void fma2(float& d0, float& d1, float a0, float a1, float b, float c)
 {
@@ -132,13 +158,9 @@ __device__ __forceinline__ void fma2(float& d0, float& d1, float a0, float a1, f
 // groups 1024 B apart (SBO = 64 x 16 B), LBO = 1 (unused for swizzled K-major), version 1.
 __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr)
 {
-    uint64_t d = 0;
-    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
-    d |= (uint64_t)1 << 16;
-    d |= (uint64_t)64 << 32;
-    d |= (uint64_t)1 << 46;
-    d |= (uint64_t)2 << 61;
-    return d;
+    constexpr uint32_t kHi = 64u | (1u << 14) | (2u << 29);          // SBO, version, SWIZZLE_128B
+    const uint32_t lo = ((saddr & 0x3FFFFu) >> 4) | (1u << 16);      // start address, LBO
+    return ((uint64_t)kHi << 32) | lo;
 }
 // kind::f16: D fp32, A/B fp16, both K-major, M = 128, N = 256
 constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
@@ -233,8 +255,8 @@ struct TcArgs {
 };
 
 // ---- the kernel ------------------------------------------------------------------------------
-template <int MODE, int GN>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+template <int MODE, int GN, int EPW>
+__global__ void __launch_bounds__(64 + EPW * 32, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                const TcArgs args)
 {
@@ -249,11 +271,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     uint32_t* tmem_base_smem = reinterpret_cast<uint32_t*>(ctrl + 16 * NSTAGE + 32);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(ctrl + 16 * NSTAGE + 40);
 
+    constexpr int EPI_COLS = BN / (EPW / 4);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < NSTAGE; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(bar_tfull + 8 * b, 1); mbar_init(bar_tempty + 8 * b, EPI_WARPS); }
+        for (int b = 0; b < 2; ++b) { mbar_init(bar_tfull + 8 * b, 1); mbar_init(bar_tempty + 8 * b, EPW); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -289,37 +312,76 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         }
     } else if (warp == 1) {
         // ================= MMA issue =================
+        // One thread feeds the tensor pipe; its serial latency per chunk (barrier polls ~160 cycles,
+        // commits ~130, MMA issues ~50 each) has to stay below the chunk's 1024 MMA cycles, so the
+        // polls of the next stage's / next chunk's barriers are issued before the MMAs and only
+        // consumed afterwards.
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
             uint32_t chunk = 0;              // running chunk counter: buffer = chunk & 1
             bool ok = true;
-            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-                int in_chunk = 0;
-                for (int ks = 0; ks < args.k_stages && ok; ++ks) {
-                    if (!(ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, 2))) break;
-                    tc_fence_after();
-                    const uint32_t sa = tiles + stage * STAGE_BYTES, sb = sa + A_BYTES;
-                    #pragma unroll
-                    for (int kk = 0; kk < BK / 16; ++kk) {
+            if ((args.chunk_k16 % (BK / 16)) == 0) {
+                // chunks are whole stages (group_k a multiple of 64, or the fp32 mode)
+                const int spc = args.chunk_k16 / (BK / 16);
+                bool full_pre = mbar_test(bar_full, 0);
+                bool tempty_pre = true;                       // first use of buffer 0 needs no wait
+                for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                    int sic = 0;                              // stage within the chunk
+                    for (int ks = 0; ks < args.k_stages; ++ks) {
                         const uint32_t buf = chunk & 1u;
-                        if (in_chunk == 0) {
-                            // the epilogue must have drained this accumulator's previous chunk
-                            if (!(ok = mbar_wait(bar_tempty + 8 * buf, ((chunk >> 1) & 1u) ^ 1u, abort_flag, 3))) break;
-                            tc_fence_after();
-                        }
-                        tc_mma_f16(tmem_base + buf * BN, umma_desc(sa + kk * 32), umma_desc(sb + kk * 32),
-                                   IDESC, in_chunk != 0);
-                        ++in_chunk;
-                        const int k16 = ks * (BK / 16) + kk;
-                        if (in_chunk == args.chunk_k16 || k16 + 1 == total_k16) {
+                        if (sic == 0 && !tempty_pre &&
+                            !(ok = mbar_wait(bar_tempty + 8 * buf, ((chunk >> 1) & 1u) ^ 1u, abort_flag, 3))) break;
+                        if (!full_pre && !(ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, 2))) break;
+                        tc_fence_after();
+                        // polls for what comes next: in flight while the MMAs below are issued
+                        const uint32_t nstage = (stage + 1 == NSTAGE) ? 0u : stage + 1, nphase = (stage + 1 == NSTAGE) ? phase ^ 1u : phase;
+                        full_pre = mbar_test(bar_full + 8 * nstage, nphase);
+                        if (sic == 0) tempty_pre = mbar_test(bar_tempty + 8 * (buf ^ 1u), (((chunk + 1) >> 1) & 1u) ^ 1u);
+                        const uint32_t sa = tiles + stage * STAGE_BYTES, sb = sa + A_BYTES;
+                        const uint32_t d_tmem = tmem_base + buf * BN;
+                        #pragma unroll
+                        for (int kk = 0; kk < BK / 16; ++kk)
+                            tc_mma_f16(d_tmem, umma_desc(sa + kk * 32), umma_desc(sb + kk * 32), IDESC,
+                                       (sic != 0 || kk != 0) ? 1u : 0u);
+                        tc_commit(bar_empty + 8 * stage);   // smem slot free once these MMAs retire
+                        if (++sic == spc || ks + 1 == args.k_stages) {
                             tc_commit(bar_tfull + 8 * buf);
-                            in_chunk = 0;
+                            sic = 0;
                             ++chunk;
                         }
+                        stage = nstage; phase = nphase;
                     }
-                    if (!ok) break;
-                    tc_commit(bar_empty + 8 * stage);       // smem slot free once these MMAs retire
-                    if (++stage == NSTAGE) { stage = 0; phase ^= 1u; }
+                }
+            } else {
+                // chunks smaller than a stage (group_k 16 / 32): general bookkeeping per MMA
+                for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                    int in_chunk = 0;
+                    for (int ks = 0; ks < args.k_stages && ok; ++ks) {
+                        if (!(ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, 2))) break;
+                        tc_fence_after();
+                        const uint32_t sa = tiles + stage * STAGE_BYTES, sb = sa + A_BYTES;
+                        #pragma unroll
+                        for (int kk = 0; kk < BK / 16; ++kk) {
+                            const uint32_t buf = chunk & 1u;
+                            if (in_chunk == 0) {
+                                // the epilogue must have drained this accumulator's previous chunk
+                                if (!(ok = mbar_wait(bar_tempty + 8 * buf, ((chunk >> 1) & 1u) ^ 1u, abort_flag, 3))) break;
+                                tc_fence_after();
+                            }
+                            tc_mma_f16(tmem_base + buf * BN, umma_desc(sa + kk * 32), umma_desc(sb + kk * 32),
+                                       IDESC, in_chunk != 0);
+                            ++in_chunk;
+                            const int k16 = ks * (BK / 16) + kk;
+                            if (in_chunk == args.chunk_k16 || k16 + 1 == total_k16) {
+                                tc_commit(bar_tfull + 8 * buf);
+                                in_chunk = 0;
+                                ++chunk;
+                            }
+                        }
+                        if (!ok) break;
+                        tc_commit(bar_empty + 8 * stage);
+                        if (++stage == NSTAGE) { stage = 0; phase ^= 1u; }
+                    }
                 }
             }
         }
@@ -343,17 +405,39 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN + cgrp * EPI_COLS;
-                #pragma unroll
-                for (int h = 0; h < EPI_COLS / 32; ++h) {
-                    float v[32];
-                    tc_ld32(taddr + h * 32, v);
-                    if (h == EPI_COLS / 32 - 1) {
-                        // this warp's reads of the accumulator are complete: hand it back to the MMA warp
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
+                if (EPW == 8) {
+                    // 4 loads of 32 columns, two register buffers: load h+1 flies while h is folded
+                    uint32_t ra[32], rb[32];
+                    tc_ld32_issue(taddr, ra);
+                    #pragma unroll
+                    for (int h = 0; h < 4; ++h) {
+                        uint32_t* cur = (h & 1) ? rb : ra;
+                        uint32_t* nxt = (h & 1) ? ra : rb;
+                        tc_ld_wait(cur);
+                        if (h < 3) tc_ld32_issue(taddr + (h + 1) * 32, nxt);
+                        else {
+                            // this warp's reads of the accumulator are complete: hand it back to the MMA warp
+                            tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
+                        }
+                        float v[32];
+                        #pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(cur[i]);
+                        fold_chunk<MODE, GN>(v, acc + h * 16);
                     }
-                    fold_chunk<MODE, GN>(v, acc + h * 16);
+                } else {
+                    #pragma unroll
+                    for (int h = 0; h < EPI_COLS / 32; ++h) {
+                        float v[32];
+                        tc_ld32(taddr + h * 32, v);
+                        if (h == EPI_COLS / 32 - 1) {
+                            tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
+                        }
+                        fold_chunk<MODE, GN>(v, acc + h * 16);
+                    }
                 }
             }
             if (!ok) break;
@@ -456,12 +540,28 @@ bool gemm_tc_eligible(int64_t M, int64_t N, int64_t K, int mode, int group_k, in
     return true;
 }
 
+// HBQ_TC_EPILOGUE_WARPS=8|16 selects the epilogue shape (tuning knob; default 8).
+static int epilogue_warps()
+{
+    static int v = 0;
+    if (!v) {
+        const char* e = getenv("HBQ_TC_EPILOGUE_WARPS");
+        v = (e && atoi(e) == 16) ? 16 : 8;
+    }
+    return v;
+}
+
 template <int MODE, int GN>
 static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcArgs& args, int grid, cudaStream_t stream)
 {
     // per device, and cheap: set on every launch rather than caching per process
-    HBQ_CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel<MODE, GN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    gemm_tc_kernel<MODE, GN><<<grid, TC_THREADS, SMEM_BYTES, stream>>>(ma, mb, args);
+    if (epilogue_warps() == 16) {
+        HBQ_CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel<MODE, GN, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        gemm_tc_kernel<MODE, GN, 16><<<grid, 64 + 16 * 32, SMEM_BYTES, stream>>>(ma, mb, args);
+    } else {
+        HBQ_CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel<MODE, GN, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        gemm_tc_kernel<MODE, GN, 8><<<grid, 64 + 8 * 32, SMEM_BYTES, stream>>>(ma, mb, args);
+    }
     HBQ_LAUNCH_CHECK("gemm_tc_kernel");
     return HBQ_OK;
 }
