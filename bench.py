@@ -110,6 +110,7 @@ def cpu_baseline_sample(x_bf16, wq_f16, seconds_target: float = 15.0):
     partial-sum model) on a bounded row sample of the workload, all host threads."""
     import numpy as np
     import oracle as O
+    O.use_all_cores()
     fa = O.Format(O.KIND_HBQ, ACT["ebit"], ACT["mbit"], 5, 3, 128, l2_block_size=32, l2_sc_bit=2, l2_scheme="SIG-1")
     xh = x_bf16.to(dtype=__import__("torch").float16).numpy()
     wt = np.ascontiguousarray(wq_f16.numpy().T)
@@ -135,6 +136,7 @@ def run_reference(args, rank: int, world: int):
     import torch
     import oracle as O
     O.build()
+    O.use_all_cores()
     x, w = make_inputs(0)
     fw = O.Format(O.KIND_HBQ, 2, 1, 5, 3, 128, l2_block_size=32, l2_sc_bit=2, l2_scheme="Mix")
     fa = O.Format(O.KIND_HBQ, 2, 2, 5, 3, 128, l2_block_size=32, l2_sc_bit=2, l2_scheme="SIG-1")

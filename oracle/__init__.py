@@ -162,3 +162,10 @@ def gemm(A, B, mode: int, group_k: int = 0, group_n: int = 0, rows=None) -> np.n
 
 def num_threads() -> int:
     return lib().orc_num_threads()
+
+
+def use_all_cores() -> int:
+    """Use every host core the process may run on (torchrun exports OMP_NUM_THREADS=1)."""
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib().orc_set_num_threads(int(n))
+    return num_threads()

@@ -433,6 +433,15 @@ int orc_gemm(const uint16_t* A, const uint16_t* B, uint16_t* C, int64_t M, int64
     return orc_gemm_rows(A, B, C, M, N, K, mode, group_k, group_n, 0, M);
 }
 
+void orc_set_num_threads(int n)
+{
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int orc_num_threads(void)
 {
 #ifdef _OPENMP

@@ -72,6 +72,8 @@ int orc_gemm_rows(const uint16_t* A, const uint16_t* B, uint16_t* C, int64_t M, 
                   int64_t K, int mode, int group_k, int group_n, int64_t m0, int64_t m1);
 
 int orc_num_threads(void);
+/* Launchers such as torchrun export OMP_NUM_THREADS=1; the CPU baseline sets its thread count itself. */
+void orc_set_num_threads(int n);
 
 #ifdef __cplusplus
 }
