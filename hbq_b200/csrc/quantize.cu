@@ -11,6 +11,7 @@
 // tensor is read once from HBM and every output is written once.
 #include "quantize_dev.cuh"
 #include <math.h>
+#include <mutex>
 
 namespace hbq {
 
@@ -199,6 +200,135 @@ __global__ void __launch_bounds__(256) mx_quantize_kernel(const QArgs a)
     store_deq(a, row, k0, d);
     store_codes<KIND == HBQ_KIND_MXINT>(a, row, k0, mag, sg);
     if ((threadIdx.x & (a.G - 1)) == 0) store_scale(a, row, c >> a.log2G, s);
+}
+
+// ------------------------------------------------------------------------------------------
+// Fast path of the same computation for the shipped MX / NV configurations: E2Mx or integer
+// elements with (a) a power-of-two scale whose exponent stays inside fp16's normal range or
+// (b) an E5M3 scale without subnormals / ceil.  Everything stays in packed fp16:
+//   (a) floor|round(log2(absmax)) evaluated on an fp16 tensor equals the exponent field of
+//       absmax, plus one when the mantissa reaches a per-exponent threshold (the 94 values just
+//       below a power of two for floor; the sqrt(2) point for round) -- a 32-entry table built by
+//       the host with the same log2f; x / 2^e is one exact HMUL2;
+//   (b) absmax / elem_max is a multiplication by the rounded reciprocal, the E5M3 rounding an
+//       add + mask on the pattern, and x / scale a pre-scaled two-step fp16 division (exact for
+//       every quotient >= 2^-14; smaller ones quantise to zero anyway).
+// CODES: also emit element codes (needs the extra extraction arithmetic).
+// ------------------------------------------------------------------------------------------
+template <int KIND, int MB, bool CODES>
+__global__ void __launch_bounds__(256) mx_fast_kernel(const QArgs a)
+{
+    // Grid-stride loop with the next chunk's load issued before the current one is processed, so
+    // every thread keeps a 16-byte load in flight while it computes.
+    const int lane = threadIdx.x & 31;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    int64_t ci = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    int64_t row = 0, c = 0;
+    split_chunk(a, ci < a.total_chunks ? ci : 0, row, c);
+    Chunk x;
+    if (ci < a.total_chunks) x = load_chunk(a, row, c * 8);
+    else { for (int p = 0; p < 4; ++p) x.h[p] = bits_h2(0u); }
+    for (; ci - lane < a.total_chunks; ci += stride) {
+    const bool valid = ci < a.total_chunks;
+    const int64_t k0 = c * 8;
+    const int64_t row_cur = row, c_cur = c;
+    // advance (row, chunk-in-row) by one grid stride and prefetch
+    row += a.step_rows; c += a.step_chunks;
+    if (c >= a.cpr) { c -= a.cpr; ++row; }
+    Chunk xn;
+    if (ci + stride < a.total_chunks) xn = load_chunk(a, row, c * 8);
+    else { for (int p = 0; p < 4; ++p) xn.h[p] = bits_h2(0u); }
+
+    uint32_t ax[4];
+    #pragma unroll
+    for (int p = 0; p < 4; ++p) ax[p] = h2_bits(x.h[p]) & 0x7FFF7FFFu;
+    uint32_t mx = h2_bits(__hmax2(__hmax2(bits_h2(ax[0]), bits_h2(ax[1])), __hmax2(bits_h2(ax[2]), bits_h2(ax[3]))));
+    for (int off = a.G >> 1; off >= 1; off >>= 1)
+        mx = h2_bits(__hmax2(bits_h2(mx), bits_h2(__shfl_xor_sync(0xFFFFFFFFu, mx, off))));
+    const uint32_t am16 = max(mx & 0xFFFFu, mx >> 16);
+
+    uint32_t sb;                       // fp16 pattern of the shared scale
+    __half2 y[4];
+    if (a.f.sc_mbit == 0) {
+        int g;                         // floor|round(log2(absmax)) as the reference's fp16 tensor op gives it
+        const int E = (int)(am16 >> 10);
+        if (am16 == 0) g = -14;        // log2(0 + 2^-14)
+        else if (E == 0) {             // subnormal maximum: rare, evaluate literally
+            const float l = log2_h(__half2float(bits_h((uint16_t)am16)));
+            g = (int)((KIND == HBQ_KIND_MXFP && a.f.use_round) ? rintf(l) : floorf(l));
+        } else g = E - 15 + ((am16 & 0x3FFu) >= a.pot_thr[E] ? 1 : 0);
+        const int e = min(max(g - a.pot_sub, a.pot_emin), a.pot_emax);       // within [-14, 15] on this path
+        sb = (uint32_t)(e + 15) << 10;
+        const uint32_t rs2 = (e == 15 ? 0x0200u : (uint32_t)(15 - e) << 10) * 0x00010001u;   // 2^-e
+        #pragma unroll
+        for (int p = 0; p < 4; ++p) y[p] = __hmul2(x.h[p], bits_h2(rs2));
+    } else {
+        const float sf = __half2float(bits_h((uint16_t)am16)) * a.inv_elem_max;
+        uint32_t t = (uint32_t)h_bits(__float2half_rn(sf));
+        t = min(max(t, 0x0400u), 0x7B80u);
+        sb = (t + 0x40u) & 0xFF80u;
+        const int e5 = (int)(sb >> 10) - 15;
+        const int s1 = min(15, 8 - e5);
+        const uint32_t pre2 = ((uint32_t)(s1 + 15) << 10) * 0x00010001u;
+        const uint32_t post2 = ((uint32_t)(15 - (s1 + e5)) << 10) * 0x00010001u;
+        const uint32_t nm2 = (0xBC00u | (sb & 0x03FFu)) * 0x00010001u;
+        const uint32_t rm2 = (uint32_t)a.rm[(sb >> 7) & 7u] * 0x00010001u;
+        #pragma unroll
+        for (int p = 0; p < 4; ++p) {
+            const __half2 xs = __hmul2(x.h[p], bits_h2(pre2));
+            const __half2 q0 = __hmul2(xs, bits_h2(rm2));
+            const __half2 r = __hfma2(q0, bits_h2(nm2), xs);
+            y[p] = __hmul2(__hfma2(r, bits_h2(rm2), q0), bits_h2(post2));
+        }
+        // quotients below 2^-14 may be off by an ulp, which can only matter for the sign of a zero
+        // result (the reference returns +0 when the quotient is exactly 0): redo those exactly
+        const float sfl = __half2float(bits_h((uint16_t)sb));
+        #pragma unroll
+        for (int p = 0; p < 4; ++p) {
+            const uint32_t tiny = __hle2_mask(bits_h2(h2_bits(y[p]) & 0x7FFF7FFFu), bits_h2(0x00200020u));
+            if (tiny) {
+                const float2 xf = __half22float2(x.h[p]);
+                const __half2 ex = __floats2half2_rn(__fdiv_rn(xf.x, sfl), __fdiv_rn(xf.y, sfl));
+                y[p] = bits_h2((h2_bits(y[p]) & ~tiny) | (h2_bits(ex) & tiny));
+            }
+        }
+    }
+    const __half2 s2 = bits_h2(sb * 0x00010001u);
+
+    __half2 d[4];
+    uint32_t mag[4], sg[4];
+    #pragma unroll
+    for (int p = 0; p < 4; ++p) {
+        __half2 q;
+        if (KIND == HBQ_KIND_MXINT) {
+            // sign(y) * floor(|y| + 0.5), clipped to [-2^(n-1), 2^(n-1)-1] (src/quantizer.py:421-422)
+            const uint32_t u = h2_bits(y[p]);
+            const uint32_t ab = u & 0x7FFF7FFFu;
+            uint32_t sgn = u & 0x80008000u;
+            // |y| + 0.5 capped at 1023 first (everything above the clip range behaves the same)
+            const __half2 k = floor_small_h2(__hmin2(__hadd2(bits_h2(ab), bits_h2(0x38003800u)), bits_h2(0x63FE63FEu)));
+            const uint32_t nm = (sgn >> 15) * 0xFFFFu;
+            const __half2 kc = __hmin2(k, bits_h2((a.int_lim_pos & ~nm) | (a.int_lim_neg & nm)));
+            sgn &= __hne2_mask(bits_h2(ab), bits_h2(0u));
+            q = bits_h2(h2_bits(kc) | sgn);
+            if (CODES) { mag[p] = h2_bits(__hadd2(kc, bits_h2(0x64006400u))) & 0x01FF01FFu; sg[p] = sgn; }
+        } else {
+            q = q2_e2<MB, true>(y[p]);
+            if (CODES) { mag[p] = code2_e2<MB>(q); sg[p] = h2_bits(q) & 0x80008000u; }
+        }
+        d[p] = __hmul2(q, s2);
+    }
+    if (valid) {
+        store_deq(a, row_cur, k0, d);
+        if (CODES) store_codes<KIND == HBQ_KIND_MXINT>(a, row_cur, k0, mag, sg);
+        if ((threadIdx.x & (a.G - 1)) == 0) {
+            const int64_t i = row_cur * a.nblk + (c_cur >> a.log2G);
+            if (a.out.scale_h) a.out.scale_h[i] = (uint16_t)sb;
+            if (a.out.scale_u8) a.out.scale_u8[i] = (uint8_t)(sb >> 7);
+        }
+    }
+    x = xn;
+    }   // grid-stride loop
 }
 
 // ------------------------------------------------------------------------------------------
@@ -463,6 +593,45 @@ static int l2_tables(int scheme, int bits, float tab[2][16])
 
 static bool is_pow2(int v) { return v > 0 && (v & (v - 1)) == 0; }
 
+// pot_thr[E] for the fast path: the smallest mantissa of an fp16 value with exponent field E whose
+// floor (or round) of the fp16-rounded log2 is E - 14 instead of E - 15; 1024 if there is none.
+static void build_pot_table(bool use_round, uint16_t thr[32])
+{
+    // computed once per process and rounding rule (30 x 1024 log2f evaluations)
+    static uint16_t cache[2][32];
+    static bool ready[2] = {false, false};
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    const int w = use_round ? 1 : 0;
+    if (!ready[w]) {
+        for (int E = 0; E < 32; ++E) cache[w][E] = 1024;
+        for (int E = 1; E <= 30; ++E) {
+            for (int m = 0; m < 1024; ++m) {
+                const float v = __half2float(__ushort_as_half((unsigned short)((E << 10) | m)));
+                const float l = h_rh(log2f(v));
+                const int g = (int)(use_round ? nearbyintf(l) : floorf(l));
+                if (g > E - 15) { cache[w][E] = (uint16_t)m; break; }
+            }
+        }
+        ready[w] = true;
+    }
+    memcpy(thr, cache[w], sizeof(cache[w]));
+}
+
+template <int KIND, int MB>
+static void launch_mx_fast(QArgs& a, dim3 grid, dim3 block, cudaStream_t stream)
+{
+    // at most 8 CTAs of 256 threads per SM (a full complement of warps), each looping over chunks
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if ((int64_t)grid.x > (int64_t)sms * 8) grid.x = (unsigned)(sms * 8);
+    const int64_t stride = (int64_t)grid.x * block.x;
+    a.step_rows = stride / a.cpr;
+    a.step_chunks = stride % a.cpr;
+    if (a.out.codes) mx_fast_kernel<KIND, MB, true><<<grid, block, 0, stream>>>(a);
+    else mx_fast_kernel<KIND, MB, false><<<grid, block, 0, stream>>>(a);
+}
+
 int quantize_launch(const void* x, int dtype, int64_t rows, int64_t K, const hbq_format* f,
                     void* deq, int deq_dtype, const hbq_packed_out* out, const float* tensor_amax,
                     cudaStream_t stream)
@@ -510,6 +679,15 @@ int quantize_launch(const void* x, int dtype, int64_t rows, int64_t K, const hbq
         if (a.out.codes && f->mbit != 4 && f->mbit != 8) return HBQ_ERR_UNSUPPORTED;
         a.elem_max = (float)h_max_norm(0, f->mbit);
         a.pot_sub = f->mbit - 2; a.pot_emin = -14; a.pot_emax = 15;       // quantizer.py:403-405
+        if (f->sc_mbit == 0) {
+            build_pot_table(false, a.pot_thr);
+            const float qmax = (float)((1 << (f->mbit - 1)) - 1);
+            a.int_lim_pos = (uint32_t)__half_as_ushort(__float2half_rn(qmax)) * 0x00010001u;
+            a.int_lim_neg = (uint32_t)__half_as_ushort(__float2half_rn(qmax + 1.f)) * 0x00010001u;
+            launch_mx_fast<HBQ_KIND_MXINT, 0>(a, grid, block, stream);
+            HBQ_LAUNCH_CHECK("mx_fast_kernel<mxint>");
+            return HBQ_OK;
+        }
         mx_quantize_kernel<HBQ_KIND_MXINT, 0><<<grid, block, 0, stream>>>(a);
         HBQ_LAUNCH_CHECK("mx_quantize_kernel<mxint>");
         return HBQ_OK;
@@ -529,6 +707,21 @@ int quantize_launch(const void* x, int dtype, int64_t rows, int64_t K, const hbq
         a.pot_sub = 1 << (f->ebit - 1);
         a.pot_emin = 2 - (1 << (f->sc_ebit - 1)); a.pot_emax = (1 << (f->sc_ebit - 1)) - 1;   // quantizer.py:500-502
         if (f->sc_mbit == 0 && (f->sc_ebit < 2 || f->sc_ebit > 8)) return HBQ_ERR_UNSUPPORTED;
+        const bool fast_scale = (f->sc_mbit == 0 && a.pot_emin >= -14 && a.pot_emax <= 15) ||
+                                (a.scale_fast_e5m3 != 0);
+        if (fast_mb >= 0 && !pts && fast_scale) {
+            if (f->sc_mbit == 0) build_pot_table(f->use_round != 0, a.pot_thr);
+            for (int i = 0; i < 8; ++i) a.rm[i] = __half_as_ushort(__float2half_rn(1.f / (1.f + i / 8.f)));
+            a.inv_elem_max = 1.f / a.elem_max;
+            switch (fast_mb) {
+                case 1: launch_mx_fast<HBQ_KIND_MXFP, 1>(a, grid, block, stream); break;
+                case 2: launch_mx_fast<HBQ_KIND_MXFP, 2>(a, grid, block, stream); break;
+                case 3: launch_mx_fast<HBQ_KIND_MXFP, 3>(a, grid, block, stream); break;
+                default: launch_mx_fast<HBQ_KIND_MXFP, 5>(a, grid, block, stream); break;
+            }
+            HBQ_LAUNCH_CHECK("mx_fast_kernel<mxfp>");
+            return HBQ_OK;
+        }
         switch (fast_mb) {
             case 1: mx_quantize_kernel<HBQ_KIND_MXFP, 1><<<grid, block, 0, stream>>>(a); break;
             case 2: mx_quantize_kernel<HBQ_KIND_MXFP, 2><<<grid, block, 0, stream>>>(a); break;

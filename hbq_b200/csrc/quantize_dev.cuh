@@ -17,6 +17,15 @@ namespace hbq {
 // gives k = 2 in the subnormal branch, which the reference turns into 0.
 // ZERO_SIGN: give b = -0 the reference's +0 result (the other callers only square it).
 // ------------------------------------------------------------------------------------------
+// floor of two fp16 values in [0, 1024) without a conversion instruction: adding 1024 rounds to the
+// nearest integer (ties to even) in the fp16 adder; subtract one where that rounded up.
+__device__ __forceinline__ __half2 floor_small_h2(__half2 v)
+{
+    const __half2 k1024 = bits_h2(0x64006400u);
+    const __half2 n = __hsub2(__hadd2(v, k1024), k1024);
+    return __hsub2(n, __hgt2(n, v));
+}
+
 template <int MB, bool ZERO_SIGN>
 __device__ __forceinline__ __half2 q2_e2(__half2 b)
 {
@@ -32,7 +41,7 @@ __device__ __forceinline__ __half2 q2_e2(__half2 b)
     // below 1
     const __half2 v = __hfma2(ab, bits_h2(((uint32_t)(0x3C00u + (MB << 10))) * 0x00010001u),
                               bits_h2(0x38013801u));
-    __half2 s = __hmul2(h2floor(v), bits_h2(((uint32_t)(0x3C00u - (MB << 10))) * 0x00010001u));
+    __half2 s = __hmul2(floor_small_h2(v), bits_h2(((uint32_t)(0x3C00u - (MB << 10))) * 0x00010001u));
     uint32_t sb = h2_bits(s);
     if (MB == 1) sb &= ~__heq2_mask(ab, bits_h2(0x39FF39FFu));
     const uint32_t m = __hge2_mask(ab, bits_h2(0x3C003C00u));
@@ -68,6 +77,7 @@ struct QArgs {
     int64_t rows, K, Kp;
     int64_t cpr;            // 8-element chunks per (padded) row
     int64_t total_chunks;
+    int64_t step_rows, step_chunks;   // one grid stride of chunks = step_rows rows + step_chunks chunks
     int in_bf16, out_bf16;
     int aligned;            // 128-bit loads/stores are legal
     int G;                  // lanes per block = block_size / 8
@@ -86,6 +96,10 @@ struct QArgs {
     float elem_max;         // MXFP FP-scale divisor / MXINT FP-scale divisor
     double pts_den;         // per-tensor scale: element max * scale max (src/quantizer.py:517-523)
     int pot_emin, pot_emax, pot_sub;
+    uint16_t pot_thr[32];   // per fp16 exponent field of absmax: smallest mantissa whose floor|round(log2) is one higher
+    uint16_t rm[8];         // fp16(1 / m) for the E5M3 mantissas m = 1 + i/8
+    float inv_elem_max;     // 1 / elem_max (fp32), for the E5M3 scale
+    uint32_t int_lim_pos, int_lim_neg;   // MXINT clip limits 2^(n-1)-1 and 2^(n-1) as packed fp16 pairs
     int code_bits;          // bits per stored element code (4, 5 or 8)
     int sign_bit;           // position of the sign in a byte code: ebit + mbit
 };
