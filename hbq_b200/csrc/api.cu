@@ -20,7 +20,7 @@ int set_cuda_error(cudaError_t e, const char* where)
 
 // implemented in quantize.cu / gemm_simt.cu / gemm_tc.cu
 int quantize_launch(const void*, int, int64_t, int64_t, const hbq_format*, void*, int, const hbq_packed_out*,
-                    const float*, cudaStream_t);
+                    const float*, cudaStream_t, const KvWriteOpts*);
 int fp_quant_launch(const void*, int64_t, int, int, int, int, int, void*, cudaStream_t);
 int64_t absmax_scratch_bytes();
 int absmax_launch(const void*, int, int64_t, float*, void*, cudaStream_t);
@@ -167,7 +167,30 @@ extern "C" {
 int hbq_quantize(const void* x, int dtype, int64_t rows, int64_t K, const hbq_format* fmt, void* deq,
                  int deq_dtype, const hbq_packed_out* out, const float* tensor_amax, void* stream)
 {
-    return quantize_launch(x, dtype, rows, K, fmt, deq, deq_dtype, out, tensor_amax, (cudaStream_t)stream);
+    return quantize_launch(x, dtype, rows, K, fmt, deq, deq_dtype, out, tensor_amax, (cudaStream_t)stream, nullptr);
+}
+
+int hbq_kv_write_k(const void* k, int dtype, int64_t B, int64_t T, int64_t H, int64_t D, const void* cos,
+                   const void* sin, int64_t rope_rows, const hbq_format* fmt, void* out, int out_dtype, void* stream)
+{
+    if (!fmt || B < 0 || T < 0 || H < 0 || D <= 0 || (cos != nullptr) != (sin != nullptr)) return HBQ_ERR_ARG;
+    if (B * T * H == 0) return HBQ_OK;
+    if (!out) return HBQ_ERR_ARG;
+    if (fmt->kind == HBQ_KIND_MXFP && fmt->per_tensor_scale) return HBQ_ERR_UNSUPPORTED;   // needs max|x| of the rotated tensor first
+    KvWriteOpts kv = {cos, sin, rope_rows, B, T, H, D, 0};
+    return quantize_launch(k, dtype, B * T * H, D, fmt, out, out_dtype, nullptr, nullptr, (cudaStream_t)stream, &kv);
+}
+
+int hbq_kv_write_v(const void* v, int dtype, int64_t B, int64_t T, int64_t H, int64_t D, const hbq_format* fmt,
+                   void* out, int out_dtype, void* stream)
+{
+    if (!fmt || B < 0 || T < 0 || H < 0 || D <= 0) return HBQ_ERR_ARG;
+    if (B * T * H == 0) return HBQ_OK;
+    if (!out) return HBQ_ERR_ARG;
+    KvWriteOpts kv = {nullptr, nullptr, 0, B, T, H, D, 1};
+    // rows / K only size the format checks here; the token-axis kernel takes its shape from kv
+    return quantize_launch(v, dtype, B * H * D, fmt->block_size, fmt, out, out_dtype, nullptr, nullptr,
+                           (cudaStream_t)stream, &kv);
 }
 
 int hbq_absmax(const void* x, int dtype, int64_t n, float* amax, void* scratch, void* stream)

@@ -12,6 +12,17 @@ namespace hbq {
 void note_launch(int n = 1);
 int set_cuda_error(cudaError_t e, const char* where);
 
+// Options of quantize_launch for the fused KV-cache writes.  K (and post-RoPE Q): rotary embedding on load
+// and the (b,t,h) -> (b,h,t) row permutation on store; rows = B*T*H, K = D.  V (v_axis != 0): blocks run
+// along the token axis of [B,T,H,D].
+struct KvWriteOpts {
+    const void* cos;
+    const void* sin;
+    int64_t rope_rows;        // rows of the cos/sin tables: B*T, or T when one table serves every batch
+    int64_t B, T, H, D;
+    int v_axis;
+};
+
 #define HBQ_CUDA_TRY(expr)                                                     \
     do {                                                                       \
         cudaError_t _e = (expr);                                               \

@@ -122,6 +122,7 @@ __global__ void __launch_bounds__(256) mx_quantize_kernel(const QArgs a)
     Chunk x;
     if (valid) x = load_chunk(a, row, k0);
     else { for (int p = 0; p < 4; ++p) x.h[p] = bits_h2(0u); }
+    if (a.rope_cos) rope_chunk(a, x, row, k0);
 
     // per-tensor scale (src/quantizer.py:516-524): the reference divides the fp16 tensor by a
     // Python double, which torch evaluates as an fp32 division by float(scale) rounded to fp16
@@ -197,9 +198,10 @@ __global__ void __launch_bounds__(256) mx_quantize_kernel(const QArgs a)
         }
     }
     if (!valid) return;
-    store_deq(a, row, k0, d);
-    store_codes<KIND == HBQ_KIND_MXINT>(a, row, k0, mag, sg);
-    if ((threadIdx.x & (a.G - 1)) == 0) store_scale(a, row, c >> a.log2G, s);
+    const int64_t orow = out_row(a, row);
+    store_deq(a, orow, k0, d);
+    store_codes<KIND == HBQ_KIND_MXINT>(a, orow, k0, mag, sg);
+    if ((threadIdx.x & (a.G - 1)) == 0) store_scale(a, orow, c >> a.log2G, s);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -239,6 +241,7 @@ __global__ void __launch_bounds__(256) mx_fast_kernel(const QArgs a)
     if (ci + stride < a.total_chunks) xn = load_chunk(a, row, c * 8);
     else { for (int p = 0; p < 4; ++p) xn.h[p] = bits_h2(0u); }
 
+    if (a.rope_cos) rope_chunk(a, x, valid ? row_cur : 0, k0);
     uint32_t ax[4];
     #pragma unroll
     for (int p = 0; p < 4; ++p) ax[p] = h2_bits(x.h[p]) & 0x7FFF7FFFu;
@@ -319,10 +322,11 @@ __global__ void __launch_bounds__(256) mx_fast_kernel(const QArgs a)
         d[p] = __hmul2(q, s2);
     }
     if (valid) {
-        store_deq(a, row_cur, k0, d);
-        if (CODES) store_codes<KIND == HBQ_KIND_MXINT>(a, row_cur, k0, mag, sg);
+        const int64_t orow = out_row(a, row_cur);
+        store_deq(a, orow, k0, d);
+        if (CODES) store_codes<KIND == HBQ_KIND_MXINT>(a, orow, k0, mag, sg);
         if ((threadIdx.x & (a.G - 1)) == 0) {
-            const int64_t i = row_cur * a.nblk + (c_cur >> a.log2G);
+            const int64_t i = orow * a.nblk + (c_cur >> a.log2G);
             if (a.out.scale_h) a.out.scale_h[i] = (uint16_t)sb;
             if (a.out.scale_u8) a.out.scale_u8[i] = (uint8_t)(sb >> 7);
         }
@@ -365,6 +369,7 @@ __global__ void __launch_bounds__(256) hbq_quantize_kernel(const QArgs a)
     Chunk x;
     if (valid) x = load_chunk(a, row, k0);
     else { for (int p = 0; p < 4; ++p) x.h[p] = bits_h2(0u); }
+    if (a.rope_cos) rope_chunk(a, x, row, k0);
 
     const int L = a.f.l2_block_size;
     const int lpm = L >> 3;                  // lanes per micro-block (0 => two micro-blocks per lane)
@@ -448,6 +453,7 @@ __global__ void __launch_bounds__(256) hbq_quantize_kernel(const QArgs a)
 
     if (!valid) return;
     const int64_t kb = c >> a.log2G;
+    row = out_row(a, row);
     store_deq(a, row, k0, best_d);
     store_codes<false>(a, row, k0, best_mag, best_sg);
     if (a.out.l2_idx) {
@@ -555,6 +561,9 @@ absmax_final_kernel(const float* partial, int nparts, int in_bf16, float* amax)
 // ------------------------------------------------------------------------------------------
 int hbq_lut_try_launch(const QArgs& qa, int mb, cudaStream_t stream, bool* launched);   // quantize_lut.cu
 
+int hbq_lut_v_launch(const QArgs& qa, int mb, const void* in, void* out, int in_bf16, int out_bf16,
+                     int64_t B, int64_t T, int64_t H, int64_t D, cudaStream_t stream);                  // quantize_lut.cu
+
 static float h_rh(float f) { return __half2float(__float2half_rn(f)); }
 
 static double h_max_norm(int ebit, int mbit)
@@ -634,7 +643,7 @@ static void launch_mx_fast(QArgs& a, dim3 grid, dim3 block, cudaStream_t stream)
 
 int quantize_launch(const void* x, int dtype, int64_t rows, int64_t K, const hbq_format* f,
                     void* deq, int deq_dtype, const hbq_packed_out* out, const float* tensor_amax,
-                    cudaStream_t stream)
+                    cudaStream_t stream, const KvWriteOpts* kv)
 {
     if (!f || rows < 0 || K < 0) return HBQ_ERR_ARG;
     if (dtype != HBQ_DTYPE_F16 && dtype != HBQ_DTYPE_BF16) return HBQ_ERR_UNSUPPORTED;
@@ -665,6 +674,15 @@ int quantize_launch(const void* x, int dtype, int64_t rows, int64_t K, const hbq
     while ((1 << a.log2G) < a.G) ++a.log2G;
     a.f = *f;
     a.f.per_tensor_scale = pts;
+    if (kv) {
+        if (K % B != 0 || !is_pow2((int)K) || K < 16 || K > 256 || pts || (kv->v_axis && f->kind != HBQ_KIND_HBQ)) return HBQ_ERR_UNSUPPORTED;
+        if (kv->cos && (dtype != HBQ_DTYPE_F16 || !kv->sin || kv->rope_rows <= 0)) return HBQ_ERR_UNSUPPORTED;
+        if (!deq) return HBQ_ERR_ARG;
+        a.rope_cos = (const uint16_t*)kv->cos; a.rope_sin = (const uint16_t*)kv->sin; a.rope_rows = kv->rope_rows;
+        a.perm_T = kv->T; a.perm_H = kv->H;
+        if ((kv->cos && ((reinterpret_cast<uintptr_t>(kv->cos) | reinterpret_cast<uintptr_t>(kv->sin)) & 15)) || !a.aligned)
+            return HBQ_ERR_ALIGN;
+    }
     a.scale_fast_e5m3 = (f->sc_ebit == 5 && f->sc_mbit == 3 && !f->use_ceil && !f->scale_allow_subnormal);
     a.exact_div = f->sc_mbit > 4;
     if (f->sc_mbit > 0) {
@@ -753,6 +771,8 @@ int quantize_launch(const void* x, int dtype, int64_t rows, int64_t K, const hbq
         const int tb = (B / L) * f->l2_sc_bit;
         if (tb != 8 && tb != 16 && tb != 32) return HBQ_ERR_UNSUPPORTED;
     }
+    if (kv && kv->v_axis)
+        return hbq_lut_v_launch(a, fast_mb, x, deq, a.in_bf16, a.out_bf16, kv->B, kv->T, kv->H, kv->D, stream);
     {
         bool launched = false;
         const int rc = hbq_lut_try_launch(a, fast_mb, stream, &launched);

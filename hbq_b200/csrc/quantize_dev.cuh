@@ -100,6 +100,12 @@ struct QArgs {
     uint16_t rm[8];         // fp16(1 / m) for the E5M3 mantissas m = 1 + i/8
     float inv_elem_max;     // 1 / elem_max (fp32), for the E5M3 scale
     uint32_t int_lim_pos, int_lim_neg;   // MXINT clip limits 2^(n-1)-1 and 2^(n-1) as packed fp16 pairs
+    // fused K/Q-cache write: rows are (b, t, h) of a projection output, RoPE is applied on load and
+    // the fake-quantised row is stored at (b, h, t)
+    const uint16_t* rope_cos;   // fp16 [rope_rows, K] or NULL (no RoPE)
+    const uint16_t* rope_sin;
+    int64_t rope_rows;          // B*T (per-batch tables) or T (one table for every batch)
+    int64_t perm_T, perm_H;     // > 0: permute output rows (b,t,h) -> (b,h,t)
     int code_bits;          // bits per stored element code (4, 5 or 8)
     int sign_bit;           // position of the sign in a byte code: ebit + mbit
 };
@@ -274,4 +280,34 @@ __device__ __forceinline__ __half2 div2_h(float x0, float x1, float s, float rs,
 }
 
 
+
+// Output row of input row r = (b*T + t)*H + h when the K/Q-cache permutation is on: (b*H + h)*T + t.
+__device__ __forceinline__ int64_t out_row(const QArgs& a, int64_t r)
+{
+    if (a.perm_T <= 0) return r;
+    const int64_t bt = r / a.perm_H, h = r - bt * a.perm_H;
+    const int64_t b = bt / a.perm_T, t = bt - b * a.perm_T;
+    return (b * a.perm_H + h) * a.perm_T + t;
+}
+
+// RoPE on a chunk (apply_rotary_pos_emb of transformers' Llama: x*cos + rotate_half(x)*sin with
+// rotate_half(x) = cat(-x[D/2:], x[:D/2]); every product and the sum are rounded to fp16 as the
+// reference's fp16 tensor ops round them).  A row is one head (K = D, a power of two <= 256), so its D/8
+// chunks sit in consecutive lanes of one warp and the partner elements d +- D/2 live D/16 lanes away.
+__device__ __forceinline__ void rope_chunk(const QArgs& a, Chunk& x, int64_t row, int64_t k0)
+{
+    const int64_t bt = a.perm_H > 0 ? row / a.perm_H : row;
+    const int64_t crow = bt % a.rope_rows;
+    const uint4 cv = __ldg(reinterpret_cast<const uint4*>(a.rope_cos + crow * a.K + k0));
+    const uint4 sv = __ldg(reinterpret_cast<const uint4*>(a.rope_sin + crow * a.K + k0));
+    const uint32_t c[4] = {cv.x, cv.y, cv.z, cv.w}, s[4] = {sv.x, sv.y, sv.z, sv.w};
+    const uint32_t neg = (2 * k0 < a.K) ? 0x80008000u : 0u;         // first half of D takes -x[d + D/2]
+    #pragma unroll
+    for (int p = 0; p < 4; ++p) {
+        const uint32_t partner = __shfl_xor_sync(0xFFFFFFFFu, h2_bits(x.h[p]), (int)(a.cpr >> 1));
+        const __half2 t1 = __hmul2(x.h[p], bits_h2(c[p]));
+        const __half2 t2 = __hmul2(bits_h2(partner ^ neg), bits_h2(s[p]));
+        x.h[p] = __hadd2(t1, t2);
+    }
+}
 }  // namespace hbq

@@ -146,11 +146,136 @@ __device__ __forceinline__ void add2_f32_f16(float& acc_lo, float& acc_hi, uint3
         : "+f"(acc_lo), "+f"(acc_hi) : "r"(e));
 }
 
+// One 8-element chunk of a block through the table: block scale, all candidates' errors, the
+// winner's values (dq), its signs (sgo) and, with CODES, its code magnitudes (mag).  The G lanes of
+// the block call this together (the maximum and the micro-block error sums are warp shuffles).
+template <int MB, bool CODES>
+__device__ __forceinline__ void lut_chunk(const LutArgs& a, const uint2* lut, const Chunk& x, uint32_t base2, uint32_t hi2,
+                                          __half2* dq, uint32_t* mag, uint32_t* sgo, int& best, uint32_t& l1b)
+{
+    uint32_t sg[4], ax[4];
+    #pragma unroll
+    for (int p = 0; p < 4; ++p) { sg[p] = h2_bits(x.h[p]) & 0x80008000u; ax[p] = h2_bits(x.h[p]) & 0x7FFF7FFFu; }
+
+    // -- block maximum and the E5M3 shared scale (round-half-up of the 3-bit mantissa) --
+    uint32_t mx = h2_bits(__hmax2(__hmax2(bits_h2(ax[0]), bits_h2(ax[1])), __hmax2(bits_h2(ax[2]), bits_h2(ax[3]))));
+    for (int off = a.q.G >> 1; off >= 1; off >>= 1)
+        mx = h2_bits(__hmax2(bits_h2(mx), bits_h2(__shfl_xor_sync(0xFFFFFFFFu, mx, off))));
+    const uint32_t am16 = max(mx & 0xFFFFu, mx >> 16);
+    // amax / ele_max as a multiplication by the rounded reciprocal: exact after the fp16 rounding
+    // because ele_max has a short significand (same argument as div2_h)
+    const float sf = __half2float(bits_h((uint16_t)am16)) * a.inv_ele_max;
+    uint32_t sb = (uint32_t)h_bits(__float2half_rn(sf));
+    sb = min(max(sb, 0x0400u), 0x7B80u);
+    l1b = (sb + 0x40u) & 0xFF80u;
+
+    // -- a = fp16(|x| / l1): l1 = m * 2^e; |x| is pre-scaled so that the residual of the
+    //    division by m stays exact, then the quotient is scaled back (exact unless a < 2^-14) --
+    const int e5 = (int)(l1b >> 10) - 15;
+    const int s1 = min(15, 8 - e5);
+    const uint32_t pre2 = ((uint32_t)(s1 + 15) << 10) * 0x00010001u;
+    const uint32_t post2 = ((uint32_t)(15 - (s1 + e5)) << 10) * 0x00010001u;
+    const uint32_t nm2 = (0xBC00u | (l1b & 0x03FFu)) * 0x00010001u;          // -m
+    const uint32_t rm2 = (uint32_t)a.rm[(l1b >> 7) & 7u] * 0x00010001u;
+    const __half2 l1_2 = bits_h2(l1b * 0x00010001u), nl1_2 = bits_h2((l1b | 0x8000u) * 0x00010001u);
+    const bool big = l1b >= a.big_l1;
+
+    __half2 aa[4];
+    uint32_t w[4];
+    #pragma unroll
+    for (int p = 0; p < 4; ++p) {
+        const __half2 axs = __hmul2(bits_h2(ax[p]), bits_h2(pre2));
+        const __half2 q0 = __hmul2(axs, bits_h2(rm2));
+        const __half2 r = __hfma2(q0, bits_h2(nm2), axs);
+        const __half2 q1 = __hfma2(r, bits_h2(rm2), q0);
+        aa[p] = __hmul2(q1, bits_h2(post2));
+        // byte offset of the table entry (8 B each; at most 12288 entries, so it fits 16 bits)
+        w[p] = (h2_bits(__hmin2(__hmax2(aa[p], bits_h2(base2)), bits_h2(hi2))) - base2) << 3;
+    }
+
+    // -- every candidate's squared error, two candidates per half2 --
+    uint32_t ct01[8], ct23[8];
+    float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
+    if (!big) {
+        #pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int p = j >> 1;
+            const uint32_t off = (j & 1) ? (w[p] >> 16) : (w[p] & 0xFFFFu);
+            const uint2 ent = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(lut) + off);
+            ct01[j] = ent.x; ct23[j] = ent.y;
+            const __half2 axb = (j & 1) ? __high2half2(bits_h2(ax[p])) : __low2half2(bits_h2(ax[p]));
+            const __half2 r01 = __hfma2(bits_h2(ent.x), nl1_2, axb), r23 = __hfma2(bits_h2(ent.y), nl1_2, axb);
+            add2_f32_f16(acc0, acc1, h2_bits(__hmul2(r01, r01)));
+            add2_f32_f16(acc2, acc3, h2_bits(__hmul2(r23, r23)));
+        }
+    } else {
+        // value * l1 may overflow to infinity here: keep the product's own rounding
+        #pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int p = j >> 1;
+            const uint32_t off = (j & 1) ? (w[p] >> 16) : (w[p] & 0xFFFFu);
+            const uint2 ent = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(lut) + off);
+            ct01[j] = ent.x; ct23[j] = ent.y;
+            const __half2 axb = (j & 1) ? __high2half2(bits_h2(ax[p])) : __low2half2(bits_h2(ax[p]));
+            const __half2 r01 = __hsub2(axb, __hmul2(bits_h2(ent.x), l1_2));
+            const __half2 r23 = __hsub2(axb, __hmul2(bits_h2(ent.y), l1_2));
+            add2_f32_f16(acc0, acc1, h2_bits(__hmul2(r01, r01)));
+            add2_f32_f16(acc2, acc3, h2_bits(__hmul2(r23, r23)));
+        }
+    }
+    for (int off = a.lpm >> 1; off >= 1; off >>= 1) {
+        acc0 += __shfl_xor_sync(0xFFFFFFFFu, acc0, off); acc1 += __shfl_xor_sync(0xFFFFFFFFu, acc1, off);
+        acc2 += __shfl_xor_sync(0xFFFFFFFFu, acc2, off); acc3 += __shfl_xor_sync(0xFFFFFFFFu, acc3, off);
+    }
+    // first minimum of the fp16-rounded sums (non-negative fp16 patterns order like integers)
+    const uint32_t E01 = h2_bits(__floats2half2_rn(acc0, acc1)), E23 = h2_bits(__floats2half2_rn(acc2, acc3));
+    uint32_t bv = E01 & 0xFFFFu;
+    best = 0;
+    if ((E01 >> 16) < bv) { bv = E01 >> 16; best = 1; }
+    if ((E23 & 0xFFFFu) < bv) { bv = E23 & 0xFFFFu; best = 2; }
+    if ((E23 >> 16) < bv) { bv = E23 >> 16; best = 3; }
+
+    // -- the winner's values, signs and (optionally) codes --
+    const uint32_t psel = (best & 1) ? 0x7632u : 0x5410u;
+    uint32_t tiny[4];
+    #pragma unroll
+    for (int p = 0; p < 4; ++p) {
+        const uint32_t ra = best < 2 ? ct01[2 * p] : ct23[2 * p], rb = best < 2 ? ct01[2 * p + 1] : ct23[2 * p + 1];
+        const __half2 ctw = bits_h2(__byte_perm(ra, rb, psel));
+        const __half2 d = __hmul2(ctw, l1_2);
+        // negative inputs whose quotient a is tiny: candidates for the reference's "+0" rule below
+        tiny[p] = __hle2_mask(aa[p], bits_h2(0x00200020u)) & ((sg[p] >> 15) * 0xFFFFu);
+        const uint32_t s = sg[p];
+        dq[p] = bits_h2(h2_bits(d) | s);
+        sgo[p] = s;
+        if (CODES) mag[p] = code2_e2<MB>(__hmul2(ctw, bits_h2((uint32_t)a.rt[best] * 0x00010001u)));
+    }
+
+    // The reference returns +0 (not -0) when fp16(a / t) is exactly zero.  Deciding that needs
+    // the exact a for tiny quotients, where the scaled division above may be off: rare, so branch.
+    if (tiny[0] | tiny[1] | tiny[2] | tiny[3]) {
+        const float l1f = __half2float(bits_h((uint16_t)l1b)), t = a.q.tab[0][best < a.q.nc ? best : a.q.nc - 1];
+        #pragma unroll
+        for (int p = 0; p < 4; ++p)
+            #pragma unroll
+            for (int h = 0; h < 2; ++h)
+                if ((tiny[p] >> (16 * h)) & 1u) {
+                    const float xf = __half2float(bits_h((uint16_t)(ax[p] >> (16 * h))));
+                    if (rh(__fdiv_rn(rh(__fdiv_rn(xf, l1f)), t)) == 0.f) {
+                        const uint32_t clr = ~(0x8000u << (16 * h));
+                        dq[p] = bits_h2(h2_bits(dq[p]) & clr);
+                        sgo[p] &= clr;
+                    }
+                }
+    }
+
+}
+
 // ---- the kernel -----------------------------------------------------------------------------------
 template <int MB, bool CODES>
 __global__ void __launch_bounds__(LUT_THREADS, 2) hbq_lut_kernel(const LutArgs a)
 {
-    extern __shared__ uint2 lut[];
+    extern __shared__ __align__(16) uint2 lut[];
     const QArgs& q = a.q;
     const int tid = threadIdx.x;
 
@@ -203,123 +328,12 @@ __global__ void __launch_bounds__(LUT_THREADS, 2) hbq_lut_kernel(const LutArgs a
         Chunk x;
         if (valid) x = load_chunk(q, row, k0);
         else { for (int p = 0; p < 4; ++p) x.h[p] = bits_h2(0u); }
+        if (q.rope_cos) rope_chunk(q, x, valid ? row : 0, k0);
 
-        uint32_t sg[4], ax[4];
-        #pragma unroll
-        for (int p = 0; p < 4; ++p) { sg[p] = h2_bits(x.h[p]) & 0x80008000u; ax[p] = h2_bits(x.h[p]) & 0x7FFF7FFFu; }
-
-        // -- block maximum and the E5M3 shared scale (round-half-up of the 3-bit mantissa) --
-        uint32_t mx = h2_bits(__hmax2(__hmax2(bits_h2(ax[0]), bits_h2(ax[1])), __hmax2(bits_h2(ax[2]), bits_h2(ax[3]))));
-        for (int off = q.G >> 1; off >= 1; off >>= 1)
-            mx = h2_bits(__hmax2(bits_h2(mx), bits_h2(__shfl_xor_sync(0xFFFFFFFFu, mx, off))));
-        const uint32_t am16 = max(mx & 0xFFFFu, mx >> 16);
-        // amax / ele_max as a multiplication by the rounded reciprocal: exact after the fp16 rounding
-        // because ele_max has a short significand (same argument as div2_h)
-        const float sf = __half2float(bits_h((uint16_t)am16)) * a.inv_ele_max;
-        uint32_t sb = (uint32_t)h_bits(__float2half_rn(sf));
-        sb = min(max(sb, 0x0400u), 0x7B80u);
-        const uint32_t l1b = (sb + 0x40u) & 0xFF80u;
-
-        // -- a = fp16(|x| / l1): l1 = m * 2^e; |x| is pre-scaled so that the residual of the
-        //    division by m stays exact, then the quotient is scaled back (exact unless a < 2^-14) --
-        const int e5 = (int)(l1b >> 10) - 15;
-        const int s1 = min(15, 8 - e5);
-        const uint32_t pre2 = ((uint32_t)(s1 + 15) << 10) * 0x00010001u;
-        const uint32_t post2 = ((uint32_t)(15 - (s1 + e5)) << 10) * 0x00010001u;
-        const uint32_t nm2 = (0xBC00u | (l1b & 0x03FFu)) * 0x00010001u;          // -m
-        const uint32_t rm2 = (uint32_t)a.rm[(l1b >> 7) & 7u] * 0x00010001u;
-        const __half2 l1_2 = bits_h2(l1b * 0x00010001u), nl1_2 = bits_h2((l1b | 0x8000u) * 0x00010001u);
-        const bool big = l1b >= a.big_l1;
-
-        __half2 aa[4];
-        uint32_t w[4];
-        #pragma unroll
-        for (int p = 0; p < 4; ++p) {
-            const __half2 axs = __hmul2(bits_h2(ax[p]), bits_h2(pre2));
-            const __half2 q0 = __hmul2(axs, bits_h2(rm2));
-            const __half2 r = __hfma2(q0, bits_h2(nm2), axs);
-            const __half2 q1 = __hfma2(r, bits_h2(rm2), q0);
-            aa[p] = __hmul2(q1, bits_h2(post2));
-            // byte offset of the table entry (8 B each; at most 12288 entries, so it fits 16 bits)
-            w[p] = (h2_bits(__hmin2(__hmax2(aa[p], bits_h2(base2)), bits_h2(hi2))) - base2) << 3;
-        }
-
-        // -- every candidate's squared error, two candidates per half2 --
-        uint32_t ct01[8], ct23[8];
-        float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
-        if (!big) {
-            #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const int p = j >> 1;
-                const uint32_t off = (j & 1) ? (w[p] >> 16) : (w[p] & 0xFFFFu);
-                const uint2 ent = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(lut) + off);
-                ct01[j] = ent.x; ct23[j] = ent.y;
-                const __half2 axb = (j & 1) ? __high2half2(bits_h2(ax[p])) : __low2half2(bits_h2(ax[p]));
-                const __half2 r01 = __hfma2(bits_h2(ent.x), nl1_2, axb), r23 = __hfma2(bits_h2(ent.y), nl1_2, axb);
-                add2_f32_f16(acc0, acc1, h2_bits(__hmul2(r01, r01)));
-                add2_f32_f16(acc2, acc3, h2_bits(__hmul2(r23, r23)));
-            }
-        } else {
-            // value * l1 may overflow to infinity here: keep the product's own rounding
-            #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const int p = j >> 1;
-                const uint32_t off = (j & 1) ? (w[p] >> 16) : (w[p] & 0xFFFFu);
-                const uint2 ent = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(lut) + off);
-                ct01[j] = ent.x; ct23[j] = ent.y;
-                const __half2 axb = (j & 1) ? __high2half2(bits_h2(ax[p])) : __low2half2(bits_h2(ax[p]));
-                const __half2 r01 = __hsub2(axb, __hmul2(bits_h2(ent.x), l1_2));
-                const __half2 r23 = __hsub2(axb, __hmul2(bits_h2(ent.y), l1_2));
-                add2_f32_f16(acc0, acc1, h2_bits(__hmul2(r01, r01)));
-                add2_f32_f16(acc2, acc3, h2_bits(__hmul2(r23, r23)));
-            }
-        }
-        for (int off = a.lpm >> 1; off >= 1; off >>= 1) {
-            acc0 += __shfl_xor_sync(0xFFFFFFFFu, acc0, off); acc1 += __shfl_xor_sync(0xFFFFFFFFu, acc1, off);
-            acc2 += __shfl_xor_sync(0xFFFFFFFFu, acc2, off); acc3 += __shfl_xor_sync(0xFFFFFFFFu, acc3, off);
-        }
-        // first minimum of the fp16-rounded sums (non-negative fp16 patterns order like integers)
-        const uint32_t E01 = h2_bits(__floats2half2_rn(acc0, acc1)), E23 = h2_bits(__floats2half2_rn(acc2, acc3));
-        uint32_t bv = E01 & 0xFFFFu;
-        int best = 0;
-        if ((E01 >> 16) < bv) { bv = E01 >> 16; best = 1; }
-        if ((E23 & 0xFFFFu) < bv) { bv = E23 & 0xFFFFu; best = 2; }
-        if ((E23 >> 16) < bv) { bv = E23 >> 16; best = 3; }
-
-        // -- the winner's values, signs and (optionally) codes --
-        const uint32_t psel = (best & 1) ? 0x7632u : 0x5410u;
         __half2 dq[4];
-        uint32_t mag[4], sgo[4], tiny[4];
-        #pragma unroll
-        for (int p = 0; p < 4; ++p) {
-            const uint32_t ra = best < 2 ? ct01[2 * p] : ct23[2 * p], rb = best < 2 ? ct01[2 * p + 1] : ct23[2 * p + 1];
-            const __half2 ctw = bits_h2(__byte_perm(ra, rb, psel));
-            const __half2 d = __hmul2(ctw, l1_2);
-            // negative inputs whose quotient a is tiny: candidates for the reference's "+0" rule below
-            tiny[p] = __hle2_mask(aa[p], bits_h2(0x00200020u)) & ((sg[p] >> 15) * 0xFFFFu);
-            const uint32_t s = sg[p];
-            dq[p] = bits_h2(h2_bits(d) | s);
-            sgo[p] = s;
-            if (CODES) mag[p] = code2_e2<MB>(__hmul2(ctw, bits_h2((uint32_t)a.rt[best] * 0x00010001u)));
-        }
-
-        // The reference returns +0 (not -0) when fp16(a / t) is exactly zero.  Deciding that needs
-        // the exact a for tiny quotients, where the scaled division above may be off: rare, so branch.
-        if (tiny[0] | tiny[1] | tiny[2] | tiny[3]) {
-            const float l1f = __half2float(bits_h((uint16_t)l1b)), t = q.tab[0][best < q.nc ? best : q.nc - 1];
-            #pragma unroll
-            for (int p = 0; p < 4; ++p)
-                #pragma unroll
-                for (int h = 0; h < 2; ++h)
-                    if ((tiny[p] >> (16 * h)) & 1u) {
-                        const float xf = __half2float(bits_h((uint16_t)(ax[p] >> (16 * h))));
-                        if (rh(__fdiv_rn(rh(__fdiv_rn(xf, l1f)), t)) == 0.f) {
-                            const uint32_t clr = ~(0x8000u << (16 * h));
-                            dq[p] = bits_h2(h2_bits(dq[p]) & clr);
-                            sgo[p] &= clr;
-                        }
-                    }
-        }
+        uint32_t mag[4], sgo[4], l1b;
+        int best;
+        lut_chunk<MB, CODES>(a, lut, x, base2, hi2, dq, mag, sgo, best, l1b);
 
         uint32_t l2word = 0;
         const bool mb_leader = (lig & (a.lpm - 1)) == 0;         // first lane of its micro-block
@@ -329,20 +343,144 @@ __global__ void __launch_bounds__(LUT_THREADS, 2) hbq_lut_kernel(const LutArgs a
 
         if (!valid) continue;
         const int64_t kb = c >> q.log2G;
-        store_deq(q, row, k0, dq);
-        if (CODES) store_codes<false>(q, row, k0, mag, sgo);
-        if (q.out.l2_idx && mb_leader) q.out.l2_idx[(row * q.nblk + kb) * nl2 + mb_index] = (uint8_t)best;
+        const int64_t orow = out_row(q, row);
+        store_deq(q, orow, k0, dq);
+        if (CODES) store_codes<false>(q, orow, k0, mag, sgo);
+        if (q.out.l2_idx && mb_leader) q.out.l2_idx[(orow * q.nblk + kb) * nl2 + mb_index] = (uint8_t)best;
         if (lig == 0) {
-            store_scale(q, row, kb, __half2float(bits_h((uint16_t)l1b)));
-            if (q.out.scheme) q.out.scheme[row * q.nblk + kb] = 0;
+            store_scale(q, orow, kb, __half2float(bits_h((uint16_t)l1b)));
+            if (q.out.scheme) q.out.scheme[orow * q.nblk + kb] = 0;
             if (q.out.l2_packed) {
                 const int nbytes = (nl2 * q.f.l2_sc_bit) >> 3;
-                uint8_t* lp = q.out.l2_packed + (row * q.nblk + kb) * nbytes;
+                uint8_t* lp = q.out.l2_packed + (orow * q.nblk + kb) * nbytes;
                 if (nbytes == 4) *reinterpret_cast<uint32_t*>(lp) = l2word;
                 else if (nbytes == 2) *reinterpret_cast<uint16_t*>(lp) = (uint16_t)l2word;
                 else *lp = (uint8_t)l2word;
             }
         }
+    }
+}
+
+// ---- V-cache write: quantisation along the token axis ------------------------------------------------
+// QLlamaAttention.forward quantises V in blocks of kv_block_size consecutive TOKENS per (batch, head,
+// channel) by transposing, quantising and transposing back (src/module.py:163-168).  Here a CTA takes a
+// tile of 128 tokens x 64 channels of the projection output [B, T, H, D], transposes it through shared
+// memory (so that a thread owns 8 consecutive tokens of one channel, the chunk shape of lut_chunk),
+// quantises in place and writes the tile to the cache layout [B, H, T, D].  Tokens beyond T are the
+// reference's zero padding.
+struct VArgs {
+    const uint16_t* in;
+    uint16_t* out;
+    int64_t B, T, H, D;
+    int in_bf16, out_bf16;
+    int64_t tiles;            // B * H * ceil(T/128) * (D/64)
+    int tblocks, dslabs;
+};
+constexpr int VT = 128, VD = 64, VLD = VT + 8;
+
+template <int MB>
+__global__ void __launch_bounds__(LUT_THREADS, 2) hbq_lut_v_kernel(const LutArgs a, const VArgs v)
+{
+    extern __shared__ __align__(16) uint2 lut[];
+    const int tid = threadIdx.x;
+    const int n = a.plan.hi - a.plan.base + 1;
+    uint16_t* tile = reinterpret_cast<uint16_t*>(lut + ((n + 1) & ~1));   // [VD][VLD] fp16, 16-byte aligned
+
+    __shared__ uint16_t s_thr[LUT_MAX_CAND][LUT_MAX_LEVELS + 1], s_val[LUT_MAX_CAND][LUT_MAX_LEVELS];
+    for (int i = tid; i < LUT_MAX_CAND * LUT_MAX_LEVELS; i += LUT_THREADS) {
+        const int c = i / LUT_MAX_LEVELS, k = i % LUT_MAX_LEVELS;
+        s_thr[c][k] = (k >= 1 && k < a.plan.nlev) ? a.plan.thr[c][k] : (uint16_t)0xFFFF;
+        s_val[c][k] = a.plan.val[c][k];
+        if (k == 0) s_thr[c][LUT_MAX_LEVELS] = 0xFFFF;
+    }
+    __syncthreads();
+    {
+        int lvl[LUT_MAX_CAND] = {0, 0, 0, 0};
+        for (int e = tid; e < n; e += LUT_THREADS) {
+            const uint32_t u = (uint32_t)(a.plan.base + e);
+            uint32_t val[LUT_MAX_CAND];
+            #pragma unroll
+            for (int i = 0; i < LUT_MAX_CAND; ++i) {
+                while (u >= s_thr[i][lvl[i] + 1]) ++lvl[i];
+                val[i] = s_val[i][lvl[i]];
+                if (MB == 1)
+                    for (int h = 0; h < a.plan.nhole[i]; ++h)
+                        if (u == a.plan.hole[i][h]) val[i] = 0;
+            }
+            lut[e] = make_uint2(val[0] | (val[1] << 16), val[2] | (val[3] << 16));
+        }
+    }
+    __syncthreads();
+
+    const uint32_t base2 = (uint32_t)a.plan.base * 0x00010001u, hi2 = (uint32_t)a.plan.hi * 0x00010001u;
+    for (int64_t tl = blockIdx.x; tl < v.tiles; tl += gridDim.x) {
+        const int ds = (int)(tl % v.dslabs);
+        const int tb = (int)((tl / v.dslabs) % v.tblocks);
+        const int64_t bh = tl / ((int64_t)v.dslabs * v.tblocks);
+        const int64_t b = bh / v.H, h = bh - b * v.H;
+        const int64_t t0 = (int64_t)tb * VT, d0 = (int64_t)ds * VD;
+
+        // -- load [128 tokens][64 channels], store transposed as tile[channel][token] --
+        #pragma unroll
+        for (int r = 0; r < (VT * VD / 8) / LUT_THREADS; ++r) {
+            const int idx = tid + r * LUT_THREADS;
+            const int tk = idx >> 3, seg = idx & 7;               // token in tile, 8-channel segment
+            uint32_t w[4] = {0u, 0u, 0u, 0u};
+            if (t0 + tk < v.T) {
+                const uint4 g = __ldg(reinterpret_cast<const uint4*>(v.in + (((b * v.T + t0 + tk) * v.H + h) * v.D + d0 + seg * 8)));
+                w[0] = g.x; w[1] = g.y; w[2] = g.z; w[3] = g.w;
+            }
+            #pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                uint32_t lo = w[i] & 0xFFFFu, hi = w[i] >> 16;
+                if (v.in_bf16) {
+                    const __half2 hh = __floats2half2_rn(__uint_as_float(lo << 16), __uint_as_float(hi << 16));
+                    lo = h2_bits(hh) & 0xFFFFu; hi = h2_bits(hh) >> 16;
+                }
+                tile[(seg * 8 + 2 * i) * VLD + tk] = (uint16_t)lo;
+                tile[(seg * 8 + 2 * i + 1) * VLD + tk] = (uint16_t)hi;
+            }
+        }
+        __syncthreads();
+
+        // -- quantise in place: a thread owns 8 consecutive tokens of one channel --
+        #pragma unroll
+        for (int pass = 0; pass < VD / (LUT_THREADS / 16); ++pass) {
+            const int d = pass * (LUT_THREADS / 16) + (tid >> 4);
+            const int lig16 = tid & 15;
+            uint4* cell = reinterpret_cast<uint4*>(tile + d * VLD + lig16 * 8);
+            const uint4 cv = *cell;
+            Chunk x;
+            x.h[0] = bits_h2(cv.x); x.h[1] = bits_h2(cv.y); x.h[2] = bits_h2(cv.z); x.h[3] = bits_h2(cv.w);
+            __half2 dq[4];
+            uint32_t mag[4], sgo[4], l1b;
+            int best;
+            lut_chunk<MB, false>(a, lut, x, base2, hi2, dq, mag, sgo, best, l1b);
+            *cell = make_uint4(h2_bits(dq[0]), h2_bits(dq[1]), h2_bits(dq[2]), h2_bits(dq[3]));
+        }
+        __syncthreads();
+
+        // -- write out[b][h][t][d0 .. d0+64) --
+        #pragma unroll
+        for (int r = 0; r < (VT * VD / 8) / LUT_THREADS; ++r) {
+            const int idx = tid + r * LUT_THREADS;
+            const int tk = idx >> 3, seg = idx & 7;
+            if (t0 + tk < v.T) {
+                uint32_t w[4];
+                #pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    uint32_t lo = tile[(seg * 8 + 2 * i) * VLD + tk], hi = tile[(seg * 8 + 2 * i + 1) * VLD + tk];
+                    if (v.out_bf16) {
+                        const float2 f = __half22float2(bits_h2(lo | (hi << 16)));
+                        __nv_bfloat162 bb = __floats2bfloat162_rn(f.x, f.y);
+                        w[i] = *reinterpret_cast<uint32_t*>(&bb);
+                    } else w[i] = lo | (hi << 16);
+                }
+                *reinterpret_cast<uint4*>(v.out + (((b * v.H + h) * v.T + t0 + tk) * v.D + d0 + seg * 8)) =
+                    make_uint4(w[0], w[1], w[2], w[3]);
+            }
+        }
+        __syncthreads();
     }
 }
 
@@ -437,6 +575,59 @@ int hbq_lut_try_launch(const QArgs& qa, int mb, cudaStream_t stream, bool* launc
     }
     if (rc == HBQ_OK) *launched = true;
     return rc;
+}
+
+
+// Launch the V-cache write.  qa carries the validated HBQ format (QArgs as quantize_launch builds it
+// for a [rows, block] problem); returns HBQ_ERR_UNSUPPORTED when the format does not fit the table
+// kernel (the caller then transposes and uses hbq_quantize like the reference).
+int hbq_lut_v_launch(const QArgs& qa, int mb, const void* in, void* out, int in_bf16, int out_bf16,
+                     int64_t B, int64_t T, int64_t H, int64_t D, cudaStream_t stream)
+{
+    const int L = qa.f.l2_block_size;
+    if (qa.nscheme != 1 || qa.nc > LUT_MAX_CAND || !qa.scale_fast_e5m3 || L < 8 || mb < 1 || mb > 3) return HBQ_ERR_UNSUPPORTED;
+    if (qa.f.block_size > VT || (VT % qa.f.block_size) != 0 || (D % VD) != 0) return HBQ_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15) return HBQ_ERR_ALIGN;
+    LutArgs a;
+    memset(&a, 0, sizeof(a));
+    if (!get_plan(mb, qa.tab[0], qa.nc, &a.plan)) return HBQ_ERR_UNSUPPORTED;
+    a.q = qa;
+    a.lpm = L / 8;
+    while ((1 << a.log2lpm) < a.lpm) ++a.log2lpm;
+    for (int i = 0; i < 8; ++i) a.rm[i] = d2h(1.0 / (1.0 + i / 8.0));
+    double vmax = 0;
+    for (int i = 0; i < LUT_MAX_CAND; ++i) {
+        a.rt[i] = d2h(1.0 / (double)qa.tab[0][i < qa.nc ? i : qa.nc - 1]);
+        const double val = h2d(a.plan.val[i][a.plan.nlev - 1]);
+        if (val > vmax) vmax = val;
+    }
+    a.inv_ele_max = 1.f / qa.ele_max[0];
+    a.big_l1 = 0x7C00;
+    for (int pat = 0x0400; pat <= 0x7B80; pat += 0x80)
+        if (h2d((uint16_t)pat) * vmax > 65504.0) { a.big_l1 = (uint16_t)pat; break; }
+
+    VArgs v;
+    v.in = (const uint16_t*)in; v.out = (uint16_t*)out;
+    v.B = B; v.T = T; v.H = H; v.D = D; v.in_bf16 = in_bf16; v.out_bf16 = out_bf16;
+    v.tblocks = (int)((T + VT - 1) / VT); v.dslabs = (int)(D / VD);
+    v.tiles = B * H * v.tblocks * v.dslabs;
+    if (v.tiles == 0) return HBQ_OK;
+    int dev = 0, sms = 0;
+    HBQ_CUDA_TRY(cudaGetDevice(&dev));
+    HBQ_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    const int grid = (int)(v.tiles < 2 * sms ? v.tiles : 2 * sms);
+    const size_t smem = (size_t)((a.plan.hi - a.plan.base + 2) & ~1) * sizeof(uint2) + (size_t)VD * VLD * 2;
+    #define HBQ_LAUNCH_V(MBV)                                                                                            \
+        HBQ_CUDA_TRY(cudaFuncSetAttribute(hbq_lut_v_kernel<MBV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        hbq_lut_v_kernel<MBV><<<grid, LUT_THREADS, smem, stream>>>(a, v);
+    switch (mb) {
+        case 1: HBQ_LAUNCH_V(1) break;
+        case 2: HBQ_LAUNCH_V(2) break;
+        default: HBQ_LAUNCH_V(3) break;
+    }
+    #undef HBQ_LAUNCH_V
+    HBQ_LAUNCH_CHECK("hbq_lut_v_kernel");
+    return HBQ_OK;
 }
 
 }  // namespace hbq

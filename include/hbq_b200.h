@@ -104,6 +104,28 @@ int hbq_dequantize(const hbq_packed_out* in, int64_t rows, int64_t K, const hbq_
 int hbq_fp_quant(const void* x, int64_t n, int ebit, int mbit, int allow_subnormal,
                  int use_ceil, int elem_variant, void* out, void* stream);
 
+/* ---- fused KV-cache writes --------------------------------------------------------------- */
+
+/* K-cache (or post-RoPE query) write of QLlamaAttention.forward (src/module.py:147-162) in one
+ * pass: k is the k_proj output viewed [B,T,H,D]; the kernel applies the rotary embedding
+ * x*cos + rotate_half(x)*sin in fp16 (each product and the sum rounded, as the fp16 tensor ops of
+ * apply_rotary_pos_emb round them), quantises along D with `fmt` (D a power of two in [16, 256] and a multiple of block_size) and
+ * stores the fake-quantised values in the cache layout [B,H,T,D] -- what the reference does as
+ * view + transpose + apply_rotary_pos_emb + kv_quantizer.q.  cos/sin are fp16 [rope_rows, D]
+ * tables with rope_rows = B*T, or T when one table serves every batch; both NULL skips the
+ * rotation (then k may be bf16).  Returns HBQ_ERR_UNSUPPORTED for formats outside the fused
+ * kernels (callers then run the three steps separately). */
+int hbq_kv_write_k(const void* k, int dtype, int64_t B, int64_t T, int64_t H, int64_t D,
+                   const void* cos, const void* sin, int64_t rope_rows, const hbq_format* fmt,
+                   void* out, int out_dtype, void* stream);
+
+/* V-cache write (src/module.py:163-168): v is the v_proj output viewed [B,T,H,D]; blocks of
+ * fmt->block_size consecutive TOKENS per (batch, head, channel) are quantised (the tail block
+ * zero padded) and the result is stored as [B,H,T,D] -- the reference's transpose, quantise,
+ * transpose back.  HBQ formats with one table, D a multiple of 64, block_size <= 128. */
+int hbq_kv_write_v(const void* v, int dtype, int64_t B, int64_t T, int64_t H, int64_t D,
+                   const hbq_format* fmt, void* out, int out_dtype, void* stream);
+
 /* ---- GEMM with modelled accumulation --------------------------------------------------- */
 
 enum { HBQ_ACC_FP32 = 0,       /* gemm_fp32_accum         blockquant_ext.cpp:21-29, gemm.cu:96-303 */
