@@ -305,9 +305,10 @@ __device__ __forceinline__ void rope_chunk(const QArgs& a, Chunk& x, int64_t row
     #pragma unroll
     for (int p = 0; p < 4; ++p) {
         const uint32_t partner = __shfl_xor_sync(0xFFFFFFFFu, h2_bits(x.h[p]), (int)(a.cpr >> 1));
-        const __half2 t1 = __hmul2(x.h[p], bits_h2(c[p]));
-        const __half2 t2 = __hmul2(bits_h2(partner ^ neg), bits_h2(s[p]));
-        x.h[p] = __hadd2(t1, t2);
+        // the _rn forms keep ptxas from contracting the products into the sum
+        const __half2 t1 = __hmul2_rn(x.h[p], bits_h2(c[p]));
+        const __half2 t2 = __hmul2_rn(bits_h2(partner ^ neg), bits_h2(s[p]));
+        x.h[p] = __hadd2_rn(t1, t2);
     }
 }
 }  // namespace hbq
