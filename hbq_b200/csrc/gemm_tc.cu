@@ -10,10 +10,14 @@
 // alternate, so the epilogue warps drain chunk c (tcgen05.ld -> round / quantise -> fp16 add
 // in registers) while the tensor core computes chunk c+1.
 //
-// One persistent CTA per SM, 320 threads (576 with 16 epilogue warps):
+// One persistent CTA per SM, 384 threads in three warpgroups:
 //   warp 0      TMA producer: 4-stage ring of {A 128x64, W 256x64} fp16 tiles, 128B swizzle
-//   warp 1      TMEM allocation and MMA issue (one lane)
-//   warps 2-9   epilogue: warp w owns TMEM lanes 32*(w%4).. and the 128 columns (w-2)/4
+//   warps 1-2   MMA issue (one lane each, alternate chunks); warp 1 also owns the TMEM allocation
+//   warp 3      idle (fills the control warpgroup, which gives its registers away)
+//   warps 4-11  epilogue: warp w owns TMEM lanes 32*(w%4).. and the 128 columns (w-4)/4; it takes
+//               232 registers (setmaxnreg) so that a whole chunk slice (4 TMEM loads, 128 values per
+//               thread) is in flight at once and the accumulator goes back to the MMA warps as soon
+//               as the loads land, before any arithmetic
 // The epilogue is the instruction-issue bottleneck (32768 fp32 values per 128-deep chunk against
 // 1024 tensor-pipe cycles), so its arithmetic is packed: fma.rn.f32x2 for the INT8 rounding,
 // cvt.rn.f16x2 and half2 min/max/add for the clamp and the fp16 accumulation.
@@ -28,8 +32,8 @@ namespace hbq {
 
 constexpr int BM = 128, BN = 256, BK = 64, NSTAGE = 4;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
-// Epilogue warps per CTA (template parameter EPW): 8 = two per TMEM lane quarter, 128 columns
-// each, TMEM loads double-buffered in registers; 16 = four per quarter, 64 columns each.
+constexpr int EPW = 8;                         // epilogue warps
+constexpr int NTHREADS = 128 + EPW * 32;
 constexpr uint32_t SMEM_BYTES = NSTAGE * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
 
 __device__ int g_tc_status;   // 0 = ok; otherwise the code of the wait that expired
@@ -92,6 +96,30 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     return false;
 }
 
+// The same wait executed by a whole warp with a warp-uniform result, so the code around it stays
+// warp-uniform (loop counters, barrier addresses and descriptors can then live in uniform registers).
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code)
+{
+    #pragma unroll 1
+    for (uint32_t it = 0; it < (1u << 23); ++it) {
+        if (__all_sync(0xFFFFFFFFu, mbar_test(bar, parity))) return true;
+        if ((it & 127u) == 127u && __any_sync(0xFFFFFFFFu, *abort_flag != 0)) return false;
+    }
+    if ((threadIdx.x & 31) == 0) {
+        *abort_flag = 1;
+        atomicCAS(&g_tc_status, 0, code);
+    }
+    __syncwarp();
+    return false;
+}
+// One lane of the (converged) warp.
+__device__ __forceinline__ bool elect_one()
+{
+    uint32_t p;
+    asm volatile("{\n .reg .pred P;\n elect.sync _|P, 0xFFFFFFFF;\n selp.u32 %0, 1, 0, P;\n}\n" : "=r"(p));
+    return p != 0;
+}
+
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar)
 {
     asm volatile(
@@ -141,6 +169,15 @@ __device__ __forceinline__ void tc_ld32_issue(uint32_t taddr, uint32_t* r)
 __device__ __forceinline__ void tc_ld_wait(uint32_t* r)
 {
     asm volatile("tcgen05.wait::ld.sync.aligned;"
+        : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+        :: "memory");
+}
+
+// Compiler-only companion of tc_ld_wait for further loads that the same wait covered: ties their
+// registers to this point so that no consumer is scheduled above the wait.  Emits nothing.
+__device__ __forceinline__ void tc_ld_landed(uint32_t* r)
+{
+    asm volatile(""
         : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
         :: "memory");
 }
@@ -252,11 +289,26 @@ struct TcArgs {
     int tiles_m, tiles_n;
     int k_stages;        // ceil(K / 64)
     int chunk_k16;       // MMAs (K = 16 each) per accumulation chunk
+    int issuers;         // MMA-issuing warps to use (1 or 2)
 };
 
+// Developer timeline trace, compiled in only with -DHBQ_TC_TRACE: CTA 0 records clock64() at the
+// hand-off points of every chunk into a caller-provided buffer of 16 slots per chunk.
+#ifdef HBQ_TC_TRACE
+__device__ long long* g_tc_trace = nullptr;
+__device__ int g_tc_trace_chunks = 0;
+#define TC_TRACE(chunk, slot)                                                                     \
+    do {                                                                                          \
+        if (blockIdx.x == 0 && g_tc_trace && (int)(chunk) < g_tc_trace_chunks)                    \
+            g_tc_trace[(int)(chunk) * 16 + (slot)] = clock64();                                    \
+    } while (0)
+#else
+#define TC_TRACE(chunk, slot) do { } while (0)
+#endif
+
 // ---- the kernel ------------------------------------------------------------------------------
-template <int MODE, int GN, int EPW>
-__global__ void __launch_bounds__(64 + EPW * 32, 1)
+template <int MODE, int GN>
+__global__ void __launch_bounds__(NTHREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                const TcArgs args)
 {
@@ -293,6 +345,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     const int total_tiles = args.tiles_m * args.tiles_n;
     const int total_k16 = args.k_stages * (BK / 16);
 
+    // Register re-balancing between the warpgroups: the control warpgroup (warps 0-3) gives registers
+    // away, the epilogue warpgroups take them (each setmaxnreg is executed by whole warpgroups).
+    if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
     if (warp == 0) {
         // ================= TMA producer =================
         if (lane == 0) {
@@ -302,6 +358,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                 const int m0 = (t % args.tiles_m) * BM, n0 = (t / args.tiles_m) * BN;
                 for (int ks = 0; ks < args.k_stages; ++ks) {
                     if (!(ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, 1))) break;
+#ifdef HBQ_TC_TRACE
+                    if ((ks & 1) == 0) TC_TRACE(((t - blockIdx.x) / gridDim.x) * (args.k_stages / 2) + ks / 2, 9);
+#endif
                     const uint32_t sa = tiles + stage * STAGE_BYTES, sb = sa + A_BYTES;
                     mbar_expect_tx(bar_full + 8 * stage, STAGE_BYTES);
                     tma_load_2d(sa, &mapA, ks * BK, m0, bar_full + 8 * stage);
@@ -310,84 +369,108 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                 }
             }
         }
-    } else if (warp == 1) {
+    } else if (warp == 1 || warp == 2) {
         // ================= MMA issue =================
-        // One thread feeds the tensor pipe; its serial latency per chunk (barrier polls ~160 cycles,
-        // commits ~130, MMA issues ~50 each) has to stay below the chunk's 1024 MMA cycles, so the
-        // polls of the next stage's / next chunk's barriers are issued before the MMAs and only
-        // consumed afterwards.
-        if (lane == 0) {
-            uint32_t stage = 0, phase = 0;
-            uint32_t chunk = 0;              // running chunk counter: buffer = chunk & 1
-            bool ok = true;
-            if ((args.chunk_k16 % (BK / 16)) == 0) {
-                // chunks are whole stages (group_k a multiple of 64, or the fp32 mode)
-                const int spc = args.chunk_k16 / (BK / 16);
-                bool full_pre = mbar_test(bar_full, 0);
-                bool tempty_pre = true;                       // first use of buffer 0 needs no wait
-                for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-                    int sic = 0;                              // stage within the chunk
-                    for (int ks = 0; ks < args.k_stages; ++ks) {
-                        const uint32_t buf = chunk & 1u;
-                        if (sic == 0 && !tempty_pre &&
-                            !(ok = mbar_wait(bar_tempty + 8 * buf, ((chunk >> 1) & 1u) ^ 1u, abort_flag, 3))) break;
-                        if (!full_pre && !(ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, 2))) break;
+        // Two warps issue MMAs, taking alternate chunks: chunk c belongs to warp 1 + (c & 1), which
+        // is also the accumulator it fills.  A chunk costs its issuing lane a serial chain of barrier
+        // polls, MMA issues and commits that is longer than the chunk's 1024 tensor-pipe cycles; with
+        // two warps each chain may take two chunk times.  All 32 lanes run the loop and wait on the
+        // barriers together, so that it is warp-uniform code (counters, barrier addresses and matrix
+        // descriptors in uniform registers); one fixed lane issues the MMAs and the commits that
+        // track them.  MMAs of different chunks go to different accumulators, so their interleaving
+        // in the tensor pipe is free; the shared-memory stages are consumed in the producer's order
+        // because both warps count every stage.
+        const uint32_t mw = (uint32_t)warp - 1u;
+        const bool leader = elect_one();
+        uint32_t chunk = 0;                  // running chunk counter: buffer = chunk & 1
+        uint32_t gks = 0;                    // running k-stage counter: stage = gks % NSTAGE
+        bool ok = true;
+        if ((args.chunk_k16 % (BK / 16)) == 0) {
+            // chunks are whole stages (group_k a multiple of 64, or the fp32 mode)
+            const int spc = args.chunk_k16 / (BK / 16);
+            // Two issuers only when every stage of the ring always meets the same warp: a warp may wait
+            // for a barrier phase only after it has seen the phase before it, or the parity wait
+            // aliases.  That holds when chunks are whole, equal and 2 * spc divides the ring; otherwise
+            // warp 1 issues everything.
+            const bool two = args.issuers == 2 && (NSTAGE % (2 * spc)) == 0 && (args.k_stages % spc) == 0;
+            if (!two && mw != 0) ok = false;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                for (int ks0 = 0; ks0 < args.k_stages && ok; ks0 += spc, ++chunk) {
+                    const int nst = min(spc, args.k_stages - ks0);
+                    if (two && (chunk & 1u) != mw) { gks += nst; continue; }
+                    const uint32_t buf = chunk & 1u;
+                    TC_TRACE(chunk, 0);
+                    uint32_t stage = gks % NSTAGE, phase = (gks / NSTAGE) & 1u;
+                    // poll the first stage while waiting for the accumulator
+                    bool full_pre = __all_sync(0xFFFFFFFFu, mbar_test(bar_full + 8 * stage, phase));
+                    // the epilogue must have drained this accumulator's previous chunk (a fresh
+                    // barrier passes the wait for the phase before its first)
+                    if (!(ok = mbar_wait_warp(bar_tempty + 8 * buf, ((chunk >> 1) & 1u) ^ 1u, abort_flag, 3))) break;
+                    TC_TRACE(chunk, 1);
+                    const uint32_t d_tmem = tmem_base + buf * BN;
+                    for (int s = 0; s < nst; ++s) {
+                        if (!full_pre && !(ok = mbar_wait_warp(bar_full + 8 * stage, phase, abort_flag, 2))) break;
+                        TC_TRACE(chunk, s == 0 ? 2 : 5);
                         tc_fence_after();
-                        // polls for what comes next: in flight while the MMAs below are issued
                         const uint32_t nstage = (stage + 1 == NSTAGE) ? 0u : stage + 1, nphase = (stage + 1 == NSTAGE) ? phase ^ 1u : phase;
-                        full_pre = mbar_test(bar_full + 8 * nstage, nphase);
-                        if (sic == 0) tempty_pre = mbar_test(bar_tempty + 8 * (buf ^ 1u), (((chunk + 1) >> 1) & 1u) ^ 1u);
+                        // poll for the next stage: in flight while the MMAs below are issued
+                        if (s + 1 < nst) full_pre = __all_sync(0xFFFFFFFFu, mbar_test(bar_full + 8 * nstage, nphase));
                         const uint32_t sa = tiles + stage * STAGE_BYTES, sb = sa + A_BYTES;
-                        const uint32_t d_tmem = tmem_base + buf * BN;
-                        #pragma unroll
-                        for (int kk = 0; kk < BK / 16; ++kk)
-                            tc_mma_f16(d_tmem, umma_desc(sa + kk * 32), umma_desc(sb + kk * 32), IDESC,
-                                       (sic != 0 || kk != 0) ? 1u : 0u);
-                        tc_commit(bar_empty + 8 * stage);   // smem slot free once these MMAs retire
-                        if (++sic == spc || ks + 1 == args.k_stages) {
-                            tc_commit(bar_tfull + 8 * buf);
-                            sic = 0;
-                            ++chunk;
+                        if (leader) {
+                            #pragma unroll
+                            for (int kk = 0; kk < BK / 16; ++kk)
+                                tc_mma_f16(d_tmem, umma_desc(sa + kk * 32), umma_desc(sb + kk * 32), IDESC,
+                                           (s != 0 || kk != 0) ? 1u : 0u);
+                            TC_TRACE(chunk, s == 0 ? 3 : 6);
+                            tc_commit(bar_empty + 8 * stage);   // smem slot free once these MMAs retire
+                            if (s + 1 == nst) tc_commit(bar_tfull + 8 * buf);
+                            TC_TRACE(chunk, s == 0 ? 4 : 7);
                         }
+                        __syncwarp();
                         stage = nstage; phase = nphase;
                     }
+                    gks += nst;
                 }
-            } else {
-                // chunks smaller than a stage (group_k 16 / 32): general bookkeeping per MMA
-                for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-                    int in_chunk = 0;
-                    for (int ks = 0; ks < args.k_stages && ok; ++ks) {
-                        if (!(ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, 2))) break;
-                        tc_fence_after();
-                        const uint32_t sa = tiles + stage * STAGE_BYTES, sb = sa + A_BYTES;
-                        #pragma unroll
-                        for (int kk = 0; kk < BK / 16; ++kk) {
-                            const uint32_t buf = chunk & 1u;
-                            if (in_chunk == 0) {
-                                // the epilogue must have drained this accumulator's previous chunk
-                                if (!(ok = mbar_wait(bar_tempty + 8 * buf, ((chunk >> 1) & 1u) ^ 1u, abort_flag, 3))) break;
-                                tc_fence_after();
-                            }
+            }
+        } else if (mw == 0) {
+            // chunks smaller than a stage (group_k 16 / 32): one warp, general bookkeeping per MMA
+            uint32_t stage = 0, phase = 0;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                int in_chunk = 0;
+                for (int ks = 0; ks < args.k_stages && ok; ++ks) {
+                    if (!(ok = mbar_wait_warp(bar_full + 8 * stage, phase, abort_flag, 2))) break;
+                    tc_fence_after();
+                    const uint32_t sa = tiles + stage * STAGE_BYTES, sb = sa + A_BYTES;
+                    #pragma unroll
+                    for (int kk = 0; kk < BK / 16; ++kk) {
+                        const uint32_t buf = chunk & 1u;
+                        if (in_chunk == 0) {
+                            // the epilogue must have drained this accumulator's previous chunk
+                            if (!(ok = mbar_wait_warp(bar_tempty + 8 * buf, ((chunk >> 1) & 1u) ^ 1u, abort_flag, 3))) break;
+                            tc_fence_after();
+                        }
+                        const int k16 = ks * (BK / 16) + kk;
+                        const bool last = (in_chunk + 1 == args.chunk_k16) || (k16 + 1 == total_k16);
+                        if (leader) {
                             tc_mma_f16(tmem_base + buf * BN, umma_desc(sa + kk * 32), umma_desc(sb + kk * 32),
                                        IDESC, in_chunk != 0);
-                            ++in_chunk;
-                            const int k16 = ks * (BK / 16) + kk;
-                            if (in_chunk == args.chunk_k16 || k16 + 1 == total_k16) {
-                                tc_commit(bar_tfull + 8 * buf);
-                                in_chunk = 0;
-                                ++chunk;
-                            }
+                            if (last) tc_commit(bar_tfull + 8 * buf);
                         }
-                        if (!ok) break;
-                        tc_commit(bar_empty + 8 * stage);
-                        if (++stage == NSTAGE) { stage = 0; phase ^= 1u; }
+                        __syncwarp();
+                        if (last) { in_chunk = 0; ++chunk; } else ++in_chunk;
                     }
+                    if (!ok) break;
+                    if (leader) tc_commit(bar_empty + 8 * stage);
+                    __syncwarp();
+                    if (++stage == NSTAGE) { stage = 0; phase ^= 1u; }
                 }
             }
         }
+    }
     } else {
         // ================= epilogue =================
-        const int ew = warp - 2;
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+        const int ew = warp - 4;
         const int quarter = warp & 3;            // TMEM lanes this warp may touch
         const int cgrp = ew >> 2;                // which EPI_COLS columns of the 256-wide tile
         const int chunks_per_tile = (total_k16 + args.chunk_k16 - 1) / args.chunk_k16;
@@ -400,44 +483,39 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
             for (int i = 0; i < EPI_COLS / 2; ++i) acc[i] = __float2half2_rn(0.f);
             for (int c = 0; c < chunks_per_tile; ++c, ++chunk) {
                 const uint32_t buf = chunk & 1u;
+                if (threadIdx.x == 128) TC_TRACE(chunk, 10);
+#ifdef HBQ_TC_TRACE
+                if (threadIdx.x == 128 && blockIdx.x == 0 && g_tc_trace && (int)chunk < g_tc_trace_chunks)
+                    g_tc_trace[(int)chunk * 16 + 15] = (long long)gtime_ns();
+#endif
                 ok = mbar_wait(bar_tfull + 8 * buf, (chunk >> 1) & 1u, abort_flag, 4);
                 ok = __all_sync(0xFFFFFFFFu, ok);
                 if (!ok) break;
                 tc_fence_after();
+                if (threadIdx.x == 128) TC_TRACE(chunk, 11);
                 const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN + cgrp * EPI_COLS;
-                if (EPW == 8) {
-                    // 4 loads of 32 columns, two register buffers: load h+1 flies while h is folded
-                    uint32_t ra[32], rb[32];
-                    tc_ld32_issue(taddr, ra);
+                {
+                    // the warp's whole slice of the chunk: 4 loads of 32 columns in flight together
+                    uint32_t r[4][32];
+                    #pragma unroll
+                    for (int h = 0; h < 4; ++h) tc_ld32_issue(taddr + h * 32, r[h]);
+                    tc_ld_wait(r[0]);                    // waits for all four
+                    #pragma unroll
+                    for (int h = 1; h < 4; ++h) tc_ld_landed(r[h]);
+                    // this warp's reads of the accumulator are complete: hand it back to the MMA warps
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
+                    if (threadIdx.x == 128) TC_TRACE(chunk, 12);
                     #pragma unroll
                     for (int h = 0; h < 4; ++h) {
-                        uint32_t* cur = (h & 1) ? rb : ra;
-                        uint32_t* nxt = (h & 1) ? ra : rb;
-                        tc_ld_wait(cur);
-                        if (h < 3) tc_ld32_issue(taddr + (h + 1) * 32, nxt);
-                        else {
-                            // this warp's reads of the accumulator are complete: hand it back to the MMA warp
-                            tc_fence_before();
-                            __syncwarp();
-                            if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
-                        }
                         float v[32];
                         #pragma unroll
-                        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(cur[i]);
+                        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[h][i]);
                         fold_chunk<MODE, GN>(v, acc + h * 16);
                     }
-                } else {
-                    #pragma unroll
-                    for (int h = 0; h < EPI_COLS / 32; ++h) {
-                        float v[32];
-                        tc_ld32(taddr + h * 32, v);
-                        if (h == EPI_COLS / 32 - 1) {
-                            tc_fence_before();
-                            __syncwarp();
-                            if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
-                        }
-                        fold_chunk<MODE, GN>(v, acc + h * 16);
-                    }
+                    if (threadIdx.x == 128) TC_TRACE(chunk, 13);
+                    if (threadIdx.x == 128 + 7 * 32) TC_TRACE(chunk, 14);
                 }
             }
             if (!ok) break;
@@ -477,6 +555,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
     }
 }
+
+#ifdef HBQ_TC_TRACE
+extern "C" int hbq_tc_trace_buffer(long long* buf, int chunks)
+{
+    cudaError_t e = cudaMemcpyToSymbol(g_tc_trace, &buf, sizeof(buf));
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_tc_trace_chunks, &chunks, sizeof(chunks));
+    return e == cudaSuccess ? 0 : -3;
+}
+#endif
 
 // ---- transpose [K,N] -> [N,K] ------------------------------------------------------------------
 __global__ void __launch_bounds__(256) transpose_kernel(const __half* __restrict__ in, __half* __restrict__ out,
@@ -540,28 +627,12 @@ bool gemm_tc_eligible(int64_t M, int64_t N, int64_t K, int mode, int group_k, in
     return true;
 }
 
-// HBQ_TC_EPILOGUE_WARPS=8|16 selects the epilogue shape (tuning knob; default 8).
-static int epilogue_warps()
-{
-    static int v = 0;
-    if (!v) {
-        const char* e = getenv("HBQ_TC_EPILOGUE_WARPS");
-        v = (e && atoi(e) == 16) ? 16 : 8;
-    }
-    return v;
-}
-
 template <int MODE, int GN>
 static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcArgs& args, int grid, cudaStream_t stream)
 {
     // per device, and cheap: set on every launch rather than caching per process
-    if (epilogue_warps() == 16) {
-        HBQ_CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel<MODE, GN, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-        gemm_tc_kernel<MODE, GN, 16><<<grid, 64 + 16 * 32, SMEM_BYTES, stream>>>(ma, mb, args);
-    } else {
-        HBQ_CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel<MODE, GN, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-        gemm_tc_kernel<MODE, GN, 8><<<grid, 64 + 8 * 32, SMEM_BYTES, stream>>>(ma, mb, args);
-    }
+    HBQ_CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel<MODE, GN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    gemm_tc_kernel<MODE, GN><<<grid, NTHREADS, SMEM_BYTES, stream>>>(ma, mb, args);
     HBQ_LAUNCH_CHECK("gemm_tc_kernel");
     return HBQ_OK;
 }
@@ -594,6 +665,11 @@ int gemm_tc_launch(const void* A, const void* W, void* C, int64_t M, int64_t N, 
     args.tiles_m = (int)((M + BM - 1) / BM); args.tiles_n = (int)((N + BN - 1) / BN);
     args.k_stages = (int)((K + BK - 1) / BK);
     args.chunk_k16 = (mode == HBQ_ACC_FP32) ? args.k_stages * (BK / 16) : group_k / 16;
+    {
+        // HBQ_TC_ISSUERS=1|2: tuning knob, number of MMA-issuing warps (default 2)
+        static const int issuers = [] { const char* e = getenv("HBQ_TC_ISSUERS"); return (e && atoi(e) == 1) ? 1 : 2; }();
+        args.issuers = issuers;
+    }
 
     int dev = 0, sms = 0;
     HBQ_CUDA_TRY(cudaGetDevice(&dev));
