@@ -413,8 +413,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                         TC_TRACE(chunk, s == 0 ? 2 : 5);
                         tc_fence_after();
                         const uint32_t nstage = (stage + 1 == NSTAGE) ? 0u : stage + 1, nphase = (stage + 1 == NSTAGE) ? phase ^ 1u : phase;
-                        // poll for the next stage: in flight while the MMAs below are issued
-                        if (s + 1 < nst) full_pre = __all_sync(0xFFFFFFFFu, mbar_test(bar_full + 8 * nstage, nphase));
+                        // poll for the next stage: in flight while the MMAs below are issued, consumed after
+                        const bool next_full = (s + 1 < nst) ? mbar_test(bar_full + 8 * nstage, nphase) : false;
                         const uint32_t sa = tiles + stage * STAGE_BYTES, sb = sa + A_BYTES;
                         if (leader) {
                             #pragma unroll
@@ -426,7 +426,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                             if (s + 1 == nst) tc_commit(bar_tfull + 8 * buf);
                             TC_TRACE(chunk, s == 0 ? 4 : 7);
                         }
-                        __syncwarp();
+                        full_pre = __all_sync(0xFFFFFFFFu, next_full);
                         stage = nstage; phase = nphase;
                     }
                     gks += nst;
