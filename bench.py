@@ -41,7 +41,7 @@ WGT = dict(block_size=128, ebit=2, mbit=1, sc_ebit=5, sc_mbit=3, l2_block_size=3
 # algorithmic HBM bytes per element of the activation quantize: 2 in + 2 fake-quantised out
 QUANT_BYTES_PER_ELEM = 4.0
 # DRAM bytes of one GEMM launch at this shape, from the ncu capture summarised under profiles/
-GEMM_DRAM_TRAFFIC_BYTES = 261090816
+GEMM_DRAM_TRAFFIC_BYTES = 257617920
 
 
 def make_inputs(rank: int):
