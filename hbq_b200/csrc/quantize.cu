@@ -217,7 +217,26 @@ __global__ void __launch_bounds__(256) mx_quantize_kernel(const QArgs a)
 //       every quotient >= 2^-14; smaller ones quantise to zero anyway).
 // CODES: also emit element codes (needs the extra extraction arithmetic).
 // ------------------------------------------------------------------------------------------
-template <int KIND, int MB, bool CODES>
+// LEAN: the tensor is contiguous, 16-byte aligned, K a multiple of the block, and only the
+//        fake-quantised output is wanted: chunk ci is elements [8 ci, 8 ci + 8) of both tensors, so
+//        the row / column bookkeeping, RoPE / permutation and side outputs drop out.
+__device__ __forceinline__ Chunk lean_load(const QArgs& a, int64_t ci)
+{
+    const uint4 v = __ldg(reinterpret_cast<const uint4*>(a.x) + ci);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    Chunk c;
+    if (!a.in_bf16) {
+        #pragma unroll
+        for (int p = 0; p < 4; ++p) c.h[p] = bits_h2(w[p]);
+    } else {
+        #pragma unroll
+        for (int p = 0; p < 4; ++p)
+            c.h[p] = __floats2half2_rn(__uint_as_float(w[p] << 16), __uint_as_float(w[p] & 0xFFFF0000u));
+    }
+    return c;
+}
+
+template <int KIND, int MB, bool CODES, bool LEAN>
 __global__ void __launch_bounds__(256) mx_fast_kernel(const QArgs a)
 {
     // Grid-stride loop with the next chunk's load issued before the current one is processed, so
@@ -226,22 +245,24 @@ __global__ void __launch_bounds__(256) mx_fast_kernel(const QArgs a)
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     int64_t ci = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     int64_t row = 0, c = 0;
-    split_chunk(a, ci < a.total_chunks ? ci : 0, row, c);
+    if (!LEAN) split_chunk(a, ci < a.total_chunks ? ci : 0, row, c);
     Chunk x;
-    if (ci < a.total_chunks) x = load_chunk(a, row, c * 8);
+    if (ci < a.total_chunks) x = LEAN ? lean_load(a, ci) : load_chunk(a, row, c * 8);
     else { for (int p = 0; p < 4; ++p) x.h[p] = bits_h2(0u); }
     for (; ci - lane < a.total_chunks; ci += stride) {
     const bool valid = ci < a.total_chunks;
     const int64_t k0 = c * 8;
     const int64_t row_cur = row, c_cur = c;
     // advance (row, chunk-in-row) by one grid stride and prefetch
-    row += a.step_rows; c += a.step_chunks;
-    if (c >= a.cpr) { c -= a.cpr; ++row; }
+    if (!LEAN) {
+        row += a.step_rows; c += a.step_chunks;
+        if (c >= a.cpr) { c -= a.cpr; ++row; }
+    }
     Chunk xn;
-    if (ci + stride < a.total_chunks) xn = load_chunk(a, row, c * 8);
+    if (ci + stride < a.total_chunks) xn = LEAN ? lean_load(a, ci + stride) : load_chunk(a, row, c * 8);
     else { for (int p = 0; p < 4; ++p) xn.h[p] = bits_h2(0u); }
 
-    if (a.rope_cos) rope_chunk(a, x, valid ? row_cur : 0, k0);
+    if (!LEAN && a.rope_cos) rope_chunk(a, x, valid ? row_cur : 0, k0);
     uint32_t ax[4];
     #pragma unroll
     for (int p = 0; p < 4; ++p) ax[p] = h2_bits(x.h[p]) & 0x7FFF7FFFu;
@@ -321,7 +342,23 @@ __global__ void __launch_bounds__(256) mx_fast_kernel(const QArgs a)
         }
         d[p] = __hmul2(q, s2);
     }
-    if (valid) {
+    if (LEAN) {
+        if (valid) {
+            uint32_t w[4];
+            if (!a.out_bf16) {
+                #pragma unroll
+                for (int p = 0; p < 4; ++p) w[p] = h2_bits(d[p]);
+            } else {
+                #pragma unroll
+                for (int p = 0; p < 4; ++p) {
+                    const float2 f = __half22float2(d[p]);
+                    __nv_bfloat162 b = __floats2bfloat162_rn(f.x, f.y);
+                    w[p] = *reinterpret_cast<uint32_t*>(&b);
+                }
+            }
+            reinterpret_cast<uint4*>(a.deq)[ci] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+    } else if (valid) {
         const int64_t orow = out_row(a, row_cur);
         store_deq(a, orow, k0, d);
         if (CODES) store_codes<KIND == HBQ_KIND_MXINT>(a, orow, k0, mag, sg);
@@ -637,8 +674,12 @@ static void launch_mx_fast(QArgs& a, dim3 grid, dim3 block, cudaStream_t stream)
     const int64_t stride = (int64_t)grid.x * block.x;
     a.step_rows = stride / a.cpr;
     a.step_chunks = stride % a.cpr;
-    if (a.out.codes) mx_fast_kernel<KIND, MB, true><<<grid, block, 0, stream>>>(a);
-    else mx_fast_kernel<KIND, MB, false><<<grid, block, 0, stream>>>(a);
+    const bool side_out = a.out.codes || a.out.sign || a.out.scale_u8 || a.out.scale_h || a.out.l2_packed ||
+                          a.out.l2_idx || a.out.scheme;
+    if (a.deq && !side_out && a.aligned && a.K == a.Kp && !a.rope_cos && a.perm_T <= 0)
+        mx_fast_kernel<KIND, MB, false, true><<<grid, block, 0, stream>>>(a);
+    else if (a.out.codes) mx_fast_kernel<KIND, MB, true, false><<<grid, block, 0, stream>>>(a);
+    else mx_fast_kernel<KIND, MB, false, false><<<grid, block, 0, stream>>>(a);
 }
 
 int quantize_launch(const void* x, int dtype, int64_t rows, int64_t K, const hbq_format* f,

@@ -361,6 +361,213 @@ __global__ void __launch_bounds__(LUT_THREADS, 2) hbq_lut_kernel(const LutArgs a
     }
 }
 
+// ---- the lean kernel: contiguous, aligned tensors, fake-quantised output only ---------------------
+// The shape every per-step activation quantize has: K a multiple of the block (no padding), 16-byte
+// aligned pointers, no packed or side outputs, no RoPE / permutation.  Chunk ci is then elements
+// [8 ci, 8 ci + 8) of both tensors and a thread's lane-in-block never changes, so the row / column
+// bookkeeping, the output selection and the dtype branches of the general kernel disappear; the
+// per-block division constants come from a second small shared table indexed by the E5M3 scale.
+// One CTA of 1024 threads per SM (the candidate table is built once per SM).
+constexpr int LEAN_THREADS = 1024;
+
+template <int MB>
+__device__ __forceinline__ void lut_build(const LutArgs& a, uint2* lut, int tid, int nthreads)
+{
+    __shared__ uint16_t s_thr[LUT_MAX_CAND][LUT_MAX_LEVELS + 1], s_val[LUT_MAX_CAND][LUT_MAX_LEVELS];
+    for (int i = tid; i < LUT_MAX_CAND * LUT_MAX_LEVELS; i += nthreads) {
+        const int c = i / LUT_MAX_LEVELS, k = i % LUT_MAX_LEVELS;
+        s_thr[c][k] = (k >= 1 && k < a.plan.nlev) ? a.plan.thr[c][k] : (uint16_t)0xFFFF;
+        s_val[c][k] = a.plan.val[c][k];
+        if (k == 0) s_thr[c][LUT_MAX_LEVELS] = 0xFFFF;
+    }
+    __syncthreads();
+    const int n = a.plan.hi - a.plan.base + 1;
+    int lvl[LUT_MAX_CAND] = {0, 0, 0, 0};
+    for (int e = tid; e < n; e += nthreads) {                 // increasing e: every level only moves up
+        const uint32_t u = (uint32_t)(a.plan.base + e);
+        uint32_t v[LUT_MAX_CAND];
+        #pragma unroll
+        for (int i = 0; i < LUT_MAX_CAND; ++i) {
+            while (u >= s_thr[i][lvl[i] + 1]) ++lvl[i];
+            uint32_t val = s_val[i][lvl[i]];
+            if (MB == 1)
+                for (int h = 0; h < a.plan.nhole[i]; ++h)
+                    if (u == a.plan.hole[i][h]) val = 0;
+            v[i] = val;
+        }
+        lut[e] = make_uint2(v[0] | (v[1] << 16), v[2] | (v[3] << 16));
+    }
+}
+
+template <int MB, bool IN_BF16, bool OUT_BF16>
+__global__ void __launch_bounds__(LEAN_THREADS, 1) hbq_lut_lean_kernel(const LutArgs a)
+{
+    extern __shared__ __align__(16) uint2 lut[];
+    __shared__ uint4 s_l1c[256];             // per E5M3 scale (pattern >> 7): {pre2, post2, -m2, 1/m 2}
+    const int tid = threadIdx.x;
+    lut_build<MB>(a, lut, tid, LEAN_THREADS);
+    if (tid < 256) {
+        const uint32_t l1b = (uint32_t)tid << 7;
+        const int e5 = (int)(l1b >> 10) - 15;
+        const int s1 = min(15, 8 - e5);
+        uint4 c;
+        c.x = ((uint32_t)(s1 + 15) << 10) * 0x00010001u;
+        c.y = ((uint32_t)(15 - (s1 + e5)) << 10) * 0x00010001u;
+        c.z = (0xBC00u | (l1b & 0x03FFu)) * 0x00010001u;
+        c.w = (uint32_t)a.rm[(l1b >> 7) & 7u] * 0x00010001u;
+        s_l1c[tid] = c;
+    }
+    __syncthreads();
+
+    const uint32_t base2 = (uint32_t)a.plan.base * 0x00010001u, hi2 = (uint32_t)a.plan.hi * 0x00010001u;
+    const uint4* __restrict__ in = reinterpret_cast<const uint4*>(a.q.x);
+    uint4* __restrict__ out = reinterpret_cast<uint4*>(a.q.deq);
+    const int64_t total = a.q.total_chunks, stride = (int64_t)gridDim.x * LEAN_THREADS;
+    const int lane = tid & 31;
+    const int G = a.q.G;
+    const uint8_t* lutb = reinterpret_cast<const uint8_t*>(lut);
+
+    int64_t ci = (int64_t)blockIdx.x * LEAN_THREADS + tid;
+    uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+    if (ci < total) raw = __ldg(in + ci);
+    for (; ci - lane < total; ci += stride) {
+        const bool valid = ci < total;
+        uint4 nraw = make_uint4(0u, 0u, 0u, 0u);
+        if (ci + stride < total) nraw = __ldg(in + ci + stride);       // next chunk in flight during this one
+
+        uint32_t xb[4] = {raw.x, raw.y, raw.z, raw.w};
+        if (IN_BF16) {
+            #pragma unroll
+            for (int p = 0; p < 4; ++p)
+                xb[p] = h2_bits(__floats2half2_rn(__uint_as_float(xb[p] << 16), __uint_as_float(xb[p] & 0xFFFF0000u)));
+        }
+        uint32_t ax[4];
+        #pragma unroll
+        for (int p = 0; p < 4; ++p) ax[p] = xb[p] & 0x7FFF7FFFu;
+
+        // -- block maximum and the E5M3 shared scale (round-half-up of the 3-bit mantissa) --
+        uint32_t mx = h2_bits(__hmax2(__hmax2(bits_h2(ax[0]), bits_h2(ax[1])), __hmax2(bits_h2(ax[2]), bits_h2(ax[3]))));
+        for (int off = G >> 1; off >= 1; off >>= 1)
+            mx = h2_bits(__hmax2(bits_h2(mx), bits_h2(__shfl_xor_sync(0xFFFFFFFFu, mx, off))));
+        const uint32_t am16 = max(mx & 0xFFFFu, mx >> 16);
+        const float sf = __half2float(bits_h((uint16_t)am16)) * a.inv_ele_max;
+        uint32_t sb = (uint32_t)h_bits(__float2half_rn(sf));
+        sb = min(max(sb, 0x0400u), 0x7B80u);
+        const uint32_t l1b = (sb + 0x40u) & 0xFF80u;
+        const uint4 cst = s_l1c[l1b >> 7];
+        const __half2 pre2 = bits_h2(cst.x), post2 = bits_h2(cst.y), nm2 = bits_h2(cst.z), rm2 = bits_h2(cst.w);
+        const uint32_t l1u = l1b * 0x00010001u;
+        const __half2 l1_2 = bits_h2(l1u), nl1_2 = bits_h2(l1u ^ 0x80008000u);
+
+        // -- a = fp16(|x| / l1) by the pre-scaled Markstein division, and the table offsets --
+        __half2 aa[4];
+        uint32_t w[4];
+        #pragma unroll
+        for (int p = 0; p < 4; ++p) {
+            const __half2 axs = __hmul2(bits_h2(ax[p]), pre2);
+            const __half2 q0 = __hmul2(axs, rm2);
+            const __half2 r = __hfma2(q0, nm2, axs);
+            const __half2 q1 = __hfma2(r, rm2, q0);
+            aa[p] = __hmul2(q1, post2);
+            w[p] = (h2_bits(__hmin2(__hmax2(aa[p], bits_h2(base2)), bits_h2(hi2))) - base2) << 3;
+        }
+
+        // -- every candidate's squared error, two candidates per half2 --
+        uint32_t ct01[8], ct23[8];
+        float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
+        if (l1b < a.big_l1) {
+            #pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int p = j >> 1;
+                const uint32_t off = (j & 1) ? (w[p] >> 16) : (w[p] & 0xFFFFu);
+                const uint2 ent = *reinterpret_cast<const uint2*>(lutb + off);
+                ct01[j] = ent.x; ct23[j] = ent.y;
+                const __half2 axb = (j & 1) ? __high2half2(bits_h2(ax[p])) : __low2half2(bits_h2(ax[p]));
+                const __half2 r01 = __hfma2(bits_h2(ent.x), nl1_2, axb), r23 = __hfma2(bits_h2(ent.y), nl1_2, axb);
+                add2_f32_f16(acc0, acc1, h2_bits(__hmul2(r01, r01)));
+                add2_f32_f16(acc2, acc3, h2_bits(__hmul2(r23, r23)));
+            }
+        } else {
+            // value * l1 may overflow to infinity here: keep the product's own rounding
+            #pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int p = j >> 1;
+                const uint32_t off = (j & 1) ? (w[p] >> 16) : (w[p] & 0xFFFFu);
+                const uint2 ent = *reinterpret_cast<const uint2*>(lutb + off);
+                ct01[j] = ent.x; ct23[j] = ent.y;
+                const __half2 axb = (j & 1) ? __high2half2(bits_h2(ax[p])) : __low2half2(bits_h2(ax[p]));
+                const __half2 r01 = __hsub2(axb, __hmul2(bits_h2(ent.x), l1_2));
+                const __half2 r23 = __hsub2(axb, __hmul2(bits_h2(ent.y), l1_2));
+                add2_f32_f16(acc0, acc1, h2_bits(__hmul2(r01, r01)));
+                add2_f32_f16(acc2, acc3, h2_bits(__hmul2(r23, r23)));
+            }
+        }
+        for (int off = a.lpm >> 1; off >= 1; off >>= 1) {
+            acc0 += __shfl_xor_sync(0xFFFFFFFFu, acc0, off); acc1 += __shfl_xor_sync(0xFFFFFFFFu, acc1, off);
+            acc2 += __shfl_xor_sync(0xFFFFFFFFu, acc2, off); acc3 += __shfl_xor_sync(0xFFFFFFFFu, acc3, off);
+        }
+        // first minimum of the fp16-rounded sums (non-negative fp16 patterns order like integers)
+        const uint32_t E01 = h2_bits(__floats2half2_rn(acc0, acc1)), E23 = h2_bits(__floats2half2_rn(acc2, acc3));
+        uint32_t bv = E01 & 0xFFFFu;
+        int best = 0;
+        if ((E01 >> 16) < bv) { bv = E01 >> 16; best = 1; }
+        if ((E23 & 0xFFFFu) < bv) { bv = E23 & 0xFFFFu; best = 2; }
+        if ((E23 >> 16) < bv) { bv = E23 >> 16; best = 3; }
+
+        // -- the winner's values with the inputs' signs --
+        const uint32_t psel = (best & 1) ? 0x7632u : 0x5410u;
+        uint32_t dq[4];
+        #pragma unroll
+        for (int p = 0; p < 4; ++p) {
+            const uint32_t ra = best < 2 ? ct01[2 * p] : ct23[2 * p], rb = best < 2 ? ct01[2 * p + 1] : ct23[2 * p + 1];
+            const __half2 d = __hmul2(bits_h2(__byte_perm(ra, rb, psel)), l1_2);
+            dq[p] = h2_bits(d) | (xb[p] & 0x80008000u);
+        }
+        // The reference returns +0 (not -0) when fp16(a / t) is exactly zero.  Only quotients a below
+        // 2^-19 can do that; deciding it needs the exact a, where the scaled division may be off: rare.
+        const __half2 amin = __hmin2(__hmin2(aa[0], aa[1]), __hmin2(aa[2], aa[3]));
+        if (__hle2_mask(amin, bits_h2(0x00200020u)) != 0u) {
+            const float l1f = __half2float(bits_h((uint16_t)l1b)), t = a.q.tab[0][best < a.q.nc ? best : a.q.nc - 1];
+            #pragma unroll
+            for (int p = 0; p < 4; ++p)
+                #pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const uint32_t abits = (h2_bits(aa[p]) >> (16 * h)) & 0xFFFFu;
+                    if (abits <= 0x0020u && ((xb[p] >> (16 * h)) & 0x8000u)) {
+                        const float xf = __half2float(bits_h((uint16_t)(ax[p] >> (16 * h))));
+                        if (rh(__fdiv_rn(rh(__fdiv_rn(xf, l1f)), t)) == 0.f) dq[p] &= ~(0x8000u << (16 * h));
+                    }
+                }
+        }
+
+        if (valid) {
+            if (OUT_BF16) {
+                #pragma unroll
+                for (int p = 0; p < 4; ++p) {
+                    const float2 f = __half22float2(bits_h2(dq[p]));
+                    __nv_bfloat162 bb = __floats2bfloat162_rn(f.x, f.y);
+                    dq[p] = *reinterpret_cast<uint32_t*>(&bb);
+                }
+            }
+            out[ci] = make_uint4(dq[0], dq[1], dq[2], dq[3]);
+        }
+        raw = nraw;
+    }
+}
+
+template <int MB>
+static int launch_lean(const LutArgs& a, int grid, size_t smem, cudaStream_t stream)
+{
+    #define HBQ_LAUNCH_LEAN(IB, OB)                                                                                              \
+        HBQ_CUDA_TRY(cudaFuncSetAttribute(hbq_lut_lean_kernel<MB, IB, OB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        hbq_lut_lean_kernel<MB, IB, OB><<<grid, LEAN_THREADS, smem, stream>>>(a);
+    if (a.q.in_bf16) { if (a.q.out_bf16) { HBQ_LAUNCH_LEAN(true, true) } else { HBQ_LAUNCH_LEAN(true, false) } }
+    else { if (a.q.out_bf16) { HBQ_LAUNCH_LEAN(false, true) } else { HBQ_LAUNCH_LEAN(false, false) } }
+    #undef HBQ_LAUNCH_LEAN
+    HBQ_LAUNCH_CHECK("hbq_lut_lean_kernel");
+    return HBQ_OK;
+}
+
 // ---- V-cache write: quantisation along the token axis ------------------------------------------------
 // QLlamaAttention.forward quantises V in blocks of kv_block_size consecutive TOKENS per (batch, head,
 // channel) by transposing, quantising and transposing back (src/module.py:163-168).  Here a CTA takes a
@@ -560,6 +767,22 @@ int hbq_lut_try_launch(const QArgs& qa, int mb, cudaStream_t stream, bool* launc
     int dev = 0, sms = 0;
     HBQ_CUDA_TRY(cudaGetDevice(&dev));
     HBQ_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    const QArgs& q = qa;
+    const bool side_out = q.out.codes || q.out.sign || q.out.scale_u8 || q.out.scale_h || q.out.l2_packed ||
+                          q.out.l2_idx || q.out.scheme;
+    if (q.deq && !side_out && q.aligned && q.K == q.Kp && !q.rope_cos && q.perm_T <= 0) {
+        const int64_t need = (qa.total_chunks + LEAN_THREADS - 1) / LEAN_THREADS;
+        const int grid = (int)(need < sms ? need : sms);
+        const size_t smem = (size_t)(a.plan.hi - a.plan.base + 1) * sizeof(uint2);
+        int rc;
+        switch (mb) {
+            case 1: rc = launch_lean<1>(a, grid, smem, stream); break;
+            case 2: rc = launch_lean<2>(a, grid, smem, stream); break;
+            default: rc = launch_lean<3>(a, grid, smem, stream); break;
+        }
+        if (rc == HBQ_OK) *launched = true;
+        return rc;
+    }
     const int64_t need = (qa.total_chunks + LUT_THREADS - 1) / LUT_THREADS;
     const int grid = (int)(need < 2 * sms ? need : 2 * sms);
     a.iters = (int)((need + grid - 1) / grid);
