@@ -289,7 +289,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                          "peak_burst": peaks["tf_burst"], "frac_of_burst": g_tf / peaks["tf_burst"],
                          "peak_source": peaks["source"], "ms_per_launch": g_ms, "traffic": GEMM_DRAM_TRAFFIC_BYTES,
                          "traffic_source": "ncu dram__bytes_read+write of one full-size launch, profiles/gemm_tc_kernel_int8psum_M4096_K4096_N14336.md"},
-            "quantize": {"kernel": "hbq_lut_kernel<2> (HBQ-E act, bf16 in, fp16 fake-quant out)", "bound": "hbm",
+            "quantize": {"kernel": "hbq_lut_lean_kernel<2> (HBQ-E act, bf16 in, fp16 fake-quant out)", "bound": "hbm",
                          "achieved": q_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": q_gbs / peaks["hbm_gbs"],
                          "ms_per_launch": q_ms, "bytes_per_elem": QUANT_BYTES_PER_ELEM},
         }
