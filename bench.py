@@ -248,9 +248,11 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     y_pin = torch.empty((M, N), dtype=torch.float16).pin_memory()
     x_dev = torch.empty_like(x)
 
+    last = [None]
+
     def e2e_step():
-        x_dev.copy_(x_pin, non_blocking=True)
-        y_pin.copy_(lin(x_dev), non_blocking=True)
+        # the host-buffer entry of the layer: pinned X in, pinned Y out, copies and kernels pipelined
+        _, last[0] = lin.forward_host(x_pin, y_pin, row_chunks=2, wait=False)
 
     for _ in range(3):
         e2e_step()
@@ -259,6 +261,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     e0.record()
     for _ in range(args.steps):
         e2e_step()
+    torch.cuda.current_stream().wait_event(last[0])      # the last step's result has reached the host
     e1.record()
     barrier()
     e2e_ms = e0.elapsed_time(e1)

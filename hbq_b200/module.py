@@ -24,6 +24,7 @@ class QLinear(nn.Linear):
         self.yq = _QBase()
         self.ops = ops
         self.check_finite = check_finite
+        self._host_pipe = None
 
     def forward(self, x: torch.Tensor):
         wq = self.weight
@@ -43,3 +44,66 @@ class QLinear(nn.Linear):
                 f"  weight quantizer:     {type(self.wq).__name__}\n"
                 f"  matmul:               {ops_name}")
         return self.yq(y)
+
+    # ---- host-buffer entry -------------------------------------------------------------------
+    def forward_host(self, x_host: torch.Tensor, out_host: torch.Tensor = None, row_chunks: int = 2,
+                     wait: bool = True):
+        """The same layer for callers whose activations live in (pinned) host memory.
+
+        Rows are cut into ``row_chunks`` pieces that travel through three streams: host-to-device
+        copy, quantize + GEMM, device-to-host copy of the result, with two staging buffers, so the
+        two PCIe directions and the kernels overlap within a call and across consecutive calls.
+        Returns ``out_host`` (pinned fp16 ``[rows, out_features]``).  With ``wait=False`` the
+        calling stream is not made to wait for the last copy; ``(out_host, event)`` is returned and
+        the caller synchronises on the event before reading, which lets the next call's uploads
+        start under this call's downloads."""
+        dev = self.weight.device
+        if x_host.is_cuda or x_host.dim() != 2 or x_host.shape[1] != self.in_features:
+            raise ValueError("forward_host expects a host tensor of shape [rows, in_features]")
+        rows = x_host.shape[0]
+        if out_host is None:
+            out_host = torch.empty((rows, self.out_features), dtype=self.weight.dtype, pin_memory=True)
+        if self._host_pipe is None or self._host_pipe["dev"] != dev:
+            self._host_pipe = {"dev": dev, "h2d": torch.cuda.Stream(dev), "comp": torch.cuda.Stream(dev),
+                               "d2h": torch.cuda.Stream(dev), "xbuf": [None, None], "x_free": [None, None], "n": 0}
+        P = self._host_pipe
+        h2d, comp, d2h = P["h2d"], P["comp"], P["d2h"]
+        cur = torch.cuda.current_stream(dev)
+        start = torch.cuda.Event()
+        start.record(cur)
+        h2d.wait_event(start)                      # inputs prepared on the calling stream are visible
+        step = -(-rows // max(1, row_chunks))
+        step = -(-step // 128) * 128               # whole GEMM row tiles per piece
+        done = None
+        for r0 in range(0, rows, step):
+            r1 = min(rows, r0 + step)
+            slot = P["n"] & 1
+            P["n"] += 1
+            with torch.cuda.stream(h2d):
+                if P["x_free"][slot] is not None:
+                    h2d.wait_event(P["x_free"][slot])          # the kernels that read this buffer are done
+                xb = P["xbuf"][slot]
+                if xb is None or xb.shape[0] < r1 - r0 or xb.dtype != x_host.dtype:
+                    xb = P["xbuf"][slot] = torch.empty((step, self.in_features), dtype=x_host.dtype, device=dev)
+                xv = xb[: r1 - r0]
+                xv.copy_(x_host[r0:r1], non_blocking=True)
+                up = torch.cuda.Event()
+                up.record(h2d)
+            with torch.cuda.stream(comp):
+                comp.wait_event(up)
+                y = self.forward(xv)
+                ev = torch.cuda.Event()
+                ev.record(comp)
+                P["x_free"][slot] = ev
+            with torch.cuda.stream(d2h):
+                d2h.wait_event(ev)
+                out_host[r0:r1].copy_(y, non_blocking=True)
+                y.record_stream(d2h)
+                done = torch.cuda.Event()
+                done.record(d2h)
+        if done is None:
+            return out_host if wait else (out_host, start)
+        if wait:
+            cur.wait_event(done)
+            return out_host
+        return out_host, done

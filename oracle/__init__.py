@@ -21,7 +21,7 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB_PATH = os.path.join(_HERE, "libhbq_oracle.so")
 
-KIND_MXFP, KIND_MXINT, KIND_HBQ = 0, 1, 2
+KIND_MXFP, KIND_MXINT, KIND_HBQ, KIND_MXEX, KIND_VSQ = 0, 1, 2, 3, 4
 L2_SCHEMES = ["PoT", "INT", "SIG-1", "FP-1", "FP1", "FP-10", "FP-100", "Mix"]
 ACC_FP32, ACC_FP16, ACC_GROUPED, ACC_PSUM_INT8, ACC_PSUM_E3M4 = range(5)
 
@@ -107,7 +107,8 @@ def quantize(x, fmt: Format, want_codes: bool = True) -> dict:
     """Block quantize-dequantize ``x`` [rows, K] (fp16) along K.
 
     Returns numpy arrays: ``deq`` float16 [rows, K]; ``scale`` float16 [rows, nblk];
-    ``l2`` uint8 [rows, nblk, block/l2_block] and ``scheme`` uint8 [rows, nblk] (HBQ);
+    ``l2`` uint8 [rows, nblk, block/l2_block] and ``scheme`` uint8 [rows, nblk] (HBQ; MXEx: ``l2`` is 1
+    where the step-2 grid won; VSQ: ``l2`` [rows, nblk, 1] second-level scales, ``scale`` the row's first);
     ``codes`` uint8 [rows, nblk, block] (one element code per byte)."""
     xu = _u16(x)
     rows, K = xu.shape
@@ -116,9 +117,13 @@ def quantize(x, fmt: Format, want_codes: bool = True) -> dict:
     deq = np.empty((rows, K), np.uint16)
     scale = np.empty((rows, nblk), np.uint16)
     hbq = fmt.kind == KIND_HBQ
-    l2 = np.zeros((rows, nblk, B // fmt.l2_block_size), np.uint8) if hbq else None
+    l2 = None
+    if hbq or fmt.kind == KIND_MXEX:
+        l2 = np.zeros((rows, nblk, B // fmt.l2_block_size), np.uint8)
+    elif fmt.kind == KIND_VSQ:
+        l2 = np.zeros((rows, nblk, 1), np.uint8)
     scheme = np.zeros((rows, nblk), np.uint8) if hbq else None
-    codes = np.zeros((rows, nblk, B), np.uint8) if want_codes else None
+    codes = np.zeros((rows, nblk, B), np.uint8) if want_codes and fmt.kind <= KIND_HBQ else None
     c = fmt.c()
     rc = lib().orc_quantize(_p(xu), ctypes.c_int64(rows), ctypes.c_int64(K), ctypes.byref(c),
                             _p(deq), _p(scale), _p(l2), _p(scheme), _p(codes))

@@ -268,9 +268,103 @@ static void hbq_block(const float* x, int B, const orc_format* f, const float* t
     if (scheme_out) *scheme_out = (uint8_t)best_s;
 }
 
+/* sign(v) * floor(|v| + 0.5) on an fp16 tensor, then clip (quantizer.py:421-422, 603-604, 691-692). */
+static inline float round_half_away_clip(float v, float lo, float hi)
+{
+    return clampf(rh(sgnf(v) * floorf(rh(fabsf(v) + 0.5f))), lo, hi);
+}
+
+/* One block of MXExQuantizer.q (quantizer.py:576-628): power-of-two shared scale, and per
+ * micro-block of l2_block_size elements the better (smaller squared error, ties: unshifted) of an
+ * integer grid with step 1 and one with step 2.  Format fields: mbit = element bits, sc_ebit =
+ * sc_bit (scale exponent width), l2_sc_bit, l2_block_size.  l2idx: 1 where the step-2 grid won. */
+static void mxex_block(const float* x, int B, const orc_format* f, float* deq, float* scale_out, uint8_t* l2idx)
+{
+    float amax = 0.f;
+    for (int j = 0; j < B; ++j) amax = fmaxf(amax, fabsf(x[j]));
+    const float emax = ldexpf(1.f, f->sc_ebit - 1) - 1.f;
+    float e = rh(rh(pot_exp(amax, 0) - (float)(f->mbit - 2)) - (float)f->l2_sc_bit);       /* :588-593 */
+    e = clampf(e, -emax, emax);
+    const float s = rh(exp2f(e));                                                            /* :594 */
+    const float qmin = -ldexpf(1.f, f->mbit - 1), qmax = ldexpf(1.f, f->mbit - 1) - 1.f;
+    const int L = f->l2_block_size;
+    for (int u = 0; u < B / L; ++u) {
+        float y[64], q2[64], q1[64], e2 = 0.f, e1 = 0.f;
+        for (int j = 0; j < L; ++j) {
+            y[j] = rh(x[u * L + j] / s);                                                     /* :601 */
+            q2[j] = rh(round_half_away_clip(rh(y[j] / 2.f), qmin, qmax) * 2.f);              /* :605-608 */
+            const float d2 = fabsf(rh(q2[j] - y[j]));
+            e2 += rh(d2 * d2);                                                               /* :609 */
+            q1[j] = round_half_away_clip(y[j], qmin, qmax);                                  /* :612-614 */
+            const float d1 = fabsf(rh(q1[j] - y[j]));
+            e1 += rh(d1 * d1);                                                               /* :615 */
+        }
+        const int shift = rh(e2) < rh(e1);                                                   /* :617 */
+        for (int j = 0; j < L; ++j) deq[u * L + j] = rh((shift ? q2[j] : q1[j]) * s);        /* :618-621 */
+        if (l2idx) l2idx[u] = (uint8_t)shift;
+    }
+    *scale_out = s;
+}
+
+/* One row of VSQQuantizer.q (quantizer.py:668-701): per-vector scale max/qmax, quantised to
+ * sc_mbit unsigned bits against a per-row first-level scale; the elements are quantised with the
+ * unquantised vector scale and dequantised with l1 * l2.  Format fields: mbit = nbit, sc_mbit.
+ * xr: the row zero padded to nblk * B values. */
+static void vsq_row(const float* xr, int64_t nblk, int B, const orc_format* f, float* dr, float* l1_out,
+                    uint8_t* l2_out)
+{
+    const float qmaxe = ldexpf(1.f, f->mbit - 1) - 1.f, qmine = -ldexpf(1.f, f->mbit - 1);
+    const float smax_u = ldexpf(1.f, f->sc_mbit) - 1.f;
+    float max_scale = 0.f;
+    for (int64_t kb = 0; kb < nblk; ++kb) {
+        float amax = 0.f;
+        for (int j = 0; j < B; ++j) amax = fmaxf(amax, fabsf(xr[kb * B + j]));
+        max_scale = fmaxf(max_scale, rh(amax / qmaxe));                                      /* :673-674 */
+    }
+    const float l1 = rh(max_scale / smax_u);                                                 /* :675 */
+    const float safe_l1 = l1 == 0.f ? 1.f : l1;
+    for (int64_t kb = 0; kb < nblk; ++kb) {
+        float amax = 0.f;
+        for (int j = 0; j < B; ++j) amax = fmaxf(amax, fabsf(xr[kb * B + j]));
+        const float sh = rh(amax / qmaxe);
+        const float l2 = round_half_away_clip(rh(sh / safe_l1), 0.f, smax_u);                /* :677-679 */
+        const float safe_sh = sh == 0.f ? 1.f : sh;
+        for (int j = 0; j < B; ++j) {
+            const float q = round_half_away_clip(rh(xr[kb * B + j] / safe_sh), qmine, qmaxe); /* :682-685 */
+            dr[kb * B + j] = rh(rh(q * l1) * l2);                                            /* :688 */
+        }
+        if (l2_out) l2_out[kb] = (uint8_t)l2;
+    }
+    *l1_out = l1;
+}
+
 int orc_quantize(const uint16_t* x, int64_t rows, int64_t K, const orc_format* f,
                  uint16_t* deq, uint16_t* scale, uint8_t* l2idx, uint8_t* scheme, uint8_t* codes)
 {
+    if (f->kind == ORC_KIND_VSQ) {
+        /* scale: the per-row first-level scale in every block slot; l2idx: one l2 value per block */
+        const int Bv = f->block_size;
+        if (Bv <= 0 || Bv > 1024 || f->mbit < 2 || f->mbit > 8 || f->sc_mbit < 1 || f->sc_mbit > 8) return -1;
+        const int64_t nb = (K + Bv - 1) / Bv;
+        #pragma omp parallel for schedule(static)
+        for (int64_t r = 0; r < rows; ++r) {
+            float* xr = (float*)malloc(sizeof(float) * (size_t)(nb * Bv) * 2);
+            float* dr = xr + nb * Bv;
+            uint8_t* l2r = (uint8_t*)malloc((size_t)nb);
+            for (int64_t k = 0; k < nb * Bv; ++k) xr[k] = k < K ? h2f(x[r * K + k]) : 0.f;
+            float l1;
+            vsq_row(xr, nb, Bv, f, dr, &l1, l2r);
+            for (int64_t k = 0; k < K; ++k) deq[r * K + k] = f2h(dr[k]);
+            for (int64_t kb = 0; kb < nb; ++kb) {
+                if (scale) scale[r * nb + kb] = f2h(l1);
+                if (l2idx) l2idx[r * nb + kb] = l2r[kb];
+            }
+            free(xr); free(l2r);
+        }
+        return 0;
+    }
+    if (f->kind == ORC_KIND_MXEX && (f->l2_block_size <= 0 || f->l2_block_size > 64 || f->block_size / f->l2_block_size > 128 || f->block_size % f->l2_block_size != 0 ||
+                                     f->mbit < 2 || f->mbit > 8)) return -1;
     const int B = f->block_size;
     if (B <= 0 || B > 1024) return -1;
     if (f->kind == ORC_KIND_HBQ && (B % f->l2_block_size != 0 || B / f->l2_block_size > 128 ||
@@ -289,6 +383,7 @@ int orc_quantize(const uint16_t* x, int64_t rows, int64_t K, const orc_format* f
     float tab[32]; int nscheme = 1;
     int nl2 = 0;
     if (f->kind == ORC_KIND_HBQ) { l2_table(f->l2_scheme, f->l2_sc_bit, tab, &nscheme); nl2 = B / f->l2_block_size; }
+    if (f->kind == ORC_KIND_MXEX) nl2 = B / f->l2_block_size;
 
     #pragma omp parallel for schedule(static)
     for (int64_t r = 0; r < rows; ++r) {
@@ -301,11 +396,13 @@ int orc_quantize(const uint16_t* x, int64_t rows, int64_t K, const orc_format* f
             float s; uint8_t sch = 0;
             if (f->kind == ORC_KIND_MXFP) mxfp_block(xb, B, f, db, &s, cb);
             else if (f->kind == ORC_KIND_MXINT) mxint_block(xb, B, f, db, &s, cb);
+            else if (f->kind == ORC_KIND_MXEX) mxex_block(xb, B, f, db, &s, ib);
             else hbq_block(xb, B, f, tab, nscheme, db, &s, ib, &sch, cb);
             if (pts) for (int j = 0; j < B; ++j) db[j] = rh(db[j] * tsf);
             for (int j = 0; j < valid; ++j) deq[r * K + k0 + j] = f2h(db[j]);
             if (scale) scale[r * nblk + kb] = f2h(s);
-            if (codes) memcpy(codes + (r * nblk + kb) * B, cb, (size_t)B);
+            if (codes && f->kind != ORC_KIND_MXEX) memcpy(codes + (r * nblk + kb) * B, cb, (size_t)B);
+            if (f->kind == ORC_KIND_MXEX && l2idx) memcpy(l2idx + (r * nblk + kb) * nl2, ib, (size_t)nl2);
             if (f->kind == ORC_KIND_HBQ) {
                 if (l2idx) memcpy(l2idx + (r * nblk + kb) * nl2, ib, (size_t)nl2);
                 if (scheme) scheme[r * nblk + kb] = sch;

@@ -19,7 +19,9 @@
 extern "C" {
 #endif
 
-enum { ORC_KIND_MXFP = 0, ORC_KIND_MXINT = 1, ORC_KIND_HBQ = 2 };
+enum { ORC_KIND_MXFP = 0, ORC_KIND_MXINT = 1, ORC_KIND_HBQ = 2,
+       ORC_KIND_MXEX = 3,   /* MXExQuantizer: mbit = element bits, sc_ebit = sc_bit, l2_sc_bit, l2_block_size */
+       ORC_KIND_VSQ = 4 };  /* VSQQuantizer: mbit = nbit, sc_mbit */
 /* Index into HBQQuantizer.L2_SCHEME (quantizer.py:708). */
 enum { ORC_L2_POT = 0, ORC_L2_INT = 1, ORC_L2_SIG1 = 2, ORC_L2_FPM1 = 3,
        ORC_L2_FP1 = 4, ORC_L2_FPM10 = 5, ORC_L2_FPM100 = 6, ORC_L2_MIX = 7 };
@@ -42,8 +44,9 @@ typedef struct {
 /* Quantize-dequantize rows x K fp16 values along K in blocks (zero padded to a
  * multiple of block_size, quantizer.py:67-130).  nblk = ceil(K/block_size).
  *   deq     [rows*K]            dequantised fp16 (required)
- *   scale   [rows*nblk]         shared (L1) scale as fp16, or NULL
- *   l2idx   [rows*nblk*nl2]     HBQ chosen candidate index per micro-block, or NULL
+ *   scale   [rows*nblk]         shared (L1) scale as fp16 (VSQ: the row's first-level scale), or NULL
+ *   l2idx   [rows*nblk*nl2]     HBQ chosen candidate index per micro-block (MXEx: 1 where the
+ *                               step-2 grid won; VSQ: the block's second-level scale, nl2 = 1), or NULL
  *   scheme  [rows*nblk]         HBQ "Mix" chosen scheme, or NULL
  *   codes   [rows*nblk*block]   one element code per byte, or NULL:
  *                               FP: {sign, exp field, mantissa} as make_fp_quant's

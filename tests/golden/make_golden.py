@@ -13,7 +13,7 @@ stores, as compressed ``.npz`` files of fp16 bit patterns:
   quantizer ``fp_quant`` over all 65 536 fp16 inputs, and ``floor(log2(x))``
   as evaluated on fp16 tensors;
 * ``quantizers.npz`` -- seeded tensors pushed through ``MXFPQuantizer``,
-  ``MXINTQuantizer`` and ``HBQQuantizer`` for every format the shipped YAML
+  ``MXINTQuantizer``, ``HBQQuantizer``, ``MXExQuantizer`` and ``VSQQuantizer`` for every format the shipped YAML
   configs use (plus a few corner formats), with the HBQ side outputs
   (``shared_scale``, ``l2_scale``, ``blk_l2_scheme``).
 
@@ -28,8 +28,8 @@ import torch
 
 REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
 sys.path.insert(0, REF)
-from src.quantizer import (HBQQuantizer, MXFPQuantizer, MXINTQuantizer,  # noqa: E402
-                           fp_quant, make_fp_quant)
+from src.quantizer import (HBQQuantizer, MXExQuantizer, MXFPQuantizer, MXINTQuantizer,  # noqa: E402
+                           VSQQuantizer, fp_quant, make_fp_quant)
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 warnings.filterwarnings("ignore")
@@ -60,6 +60,11 @@ FORMATS = {
     "mxint8": ("mxint", dict(nbit=8, sc_ebit=8, sc_mbit=0, block_size=32)),
     "mxint4": ("mxint", dict(nbit=4, sc_ebit=8, sc_mbit=0, block_size=32)),
     "mxint8_fpscale": ("mxint", dict(nbit=8, sc_ebit=5, sc_mbit=3, block_size=16)),
+    # the two remaining quantizer classes of src/quantizer.py (no shipped YAML selects them)
+    "mxex_m3": ("mxex", dict(block_size=16, l2_block_size=2, sc_bit=8, l2_sc_bit=1, mbit=3)),
+    "mxex_m5_l4": ("mxex", dict(block_size=32, l2_block_size=4, sc_bit=8, l2_sc_bit=1, mbit=5)),
+    "vsq4": ("vsq", dict(nbit=4, block_size=16, sc_mbit=4)),
+    "vsq8_b32": ("vsq", dict(nbit=8, block_size=32, sc_mbit=6)),
 }
 
 
@@ -68,6 +73,10 @@ def make_quantizer(kind, kw):
         return HBQQuantizer(keep_l2_scale=True, use_quant_kernel=False, **kw)
     if kind == "mxfp":
         return MXFPQuantizer(activate_dynamo=False, **kw)
+    if kind == "mxex":
+        return MXExQuantizer(**kw)
+    if kind == "vsq":
+        return VSQQuantizer(**kw)
     return MXINTQuantizer(**kw)
 
 

@@ -191,6 +191,36 @@ def test_qlinear_layer(oracle):
     assert rel < 1e-3, rel
 
 
+def test_qlinear_forward_host_matches_forward():
+    """The pipelined host-buffer entry (chunked copies and kernels on three streams) returns exactly
+    what forward() returns for the same rows, for ragged row counts, repeated calls and wait=False."""
+    import hbq_b200 as H
+    M, K, N = 1000, 512, 384
+    x = torch.from_numpy(seeded_inputs("act", M, K, 31)).to(torch.bfloat16)
+    w = seeded_inputs("wgt", N, K, 32)
+    aq = H.HBQQuantizer(128, 2, 2, 5, 3, l2_block_size=32, l2_sc_bit=2, l2_scheme="FP-1")
+    aq.out_dtype = torch.float16
+    lin = H.QLinear(K, N, bias=True, device="cuda", dtype=torch.float16, check_finite=False)
+    lin.weight.data = dev(w)
+    lin.bias.data = torch.linspace(-1, 1, N, device="cuda", dtype=torch.float16)
+    lin.aq = aq
+    lin.ops = H.FP16AccumMatMul(group_size=128, quant_block_size=32)
+    with torch.no_grad():
+        want = lin(x.cuda()).cpu()
+        xp = x.pin_memory()
+        for chunks in (1, 2, 3, 8):
+            got = lin.forward_host(xp, row_chunks=chunks)
+            torch.cuda.synchronize()
+            assert torch.equal(got, want), chunks
+        out = torch.empty((M, N), dtype=torch.float16).pin_memory()
+        ev = None
+        for _ in range(3):
+            _, ev = lin.forward_host(xp, out, row_chunks=2, wait=False)
+        ev.synchronize()
+        assert torch.equal(out, want)
+        assert lin.forward_host(xp[:0]).shape == (0, N)
+
+
 def _load_reference_ext():
     """The reference's own extension compiled by oracle/build_ref.py, if it has been built."""
     import importlib.util

@@ -27,6 +27,11 @@ def oracle_format(O, spec):
         return O.Format(O.KIND_MXFP, spec["ebit"], spec["mbit"], spec["sc_ebit"], spec["sc_mbit"], spec["block_size"],
                         use_round=spec.get("use_round", False), use_ceil=spec.get("use_ceil", False),
                         per_tensor_scale=spec.get("per_tensor_scale", False))
+    if kind == "mxex":
+        return O.Format(O.KIND_MXEX, 0, spec["mbit"], spec["sc_bit"], 0, spec["block_size"],
+                        l2_block_size=spec["l2_block_size"], l2_sc_bit=spec["l2_sc_bit"])
+    if kind == "vsq":
+        return O.Format(O.KIND_VSQ, 0, spec["nbit"], 0, spec["sc_mbit"], spec["block_size"])
     return O.Format(O.KIND_MXINT, 0, spec["nbit"], spec["sc_ebit"], spec["sc_mbit"], spec["block_size"])
 
 
