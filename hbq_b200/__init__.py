@@ -11,10 +11,11 @@ from .kvcache import write_k_cache, write_v_cache  # noqa: F401
 from .module import QLinear  # noqa: F401
 from .ops import FP16AccumMatMul  # noqa: F401
 from .ptq import PTQConfig, load_quant_config  # noqa: F401
-from .quantizer import (HBQQuantizer, MXFPQuantizer, MXINTQuantizer, PackedTensor, _QBase,  # noqa: F401
+from .quantizer import (HBQQuantizer, MXExQuantizer, MXFPQuantizer, MXINTQuantizer, PackedTensor,  # noqa: F401
+                        VSQQuantizer, _QBase,
                         dequantize_packed, get_max_norm, get_min_norm, get_min_subnorm)
 
-__all__ = ["HBQQuantizer", "MXFPQuantizer", "MXINTQuantizer", "_QBase", "FP16AccumMatMul", "QLinear",
+__all__ = ["HBQQuantizer", "MXFPQuantizer", "MXINTQuantizer", "MXExQuantizer", "VSQQuantizer", "_QBase", "FP16AccumMatMul", "QLinear",
            "PTQConfig", "load_quant_config", "blockquant_ext", "gemm", "gemm_status", "PackedTensor",
            "dequantize_packed", "HbqError", "launch_count", "get_max_norm", "get_min_norm", "get_min_subnorm",
            "write_k_cache", "write_v_cache"]

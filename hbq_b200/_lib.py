@@ -10,7 +10,7 @@ import os
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "lib", "libhbq_b200.so")
 
-KIND_MXFP, KIND_MXINT, KIND_HBQ = 0, 1, 2
+KIND_MXFP, KIND_MXINT, KIND_HBQ, KIND_MXEX, KIND_VSQ = 0, 1, 2, 3, 4
 ERR_UNSUPPORTED = -2          # HBQ_ERR_UNSUPPORTED
 DTYPE_F16, DTYPE_BF16 = 0, 1
 L2_SCHEMES = ["PoT", "INT", "SIG-1", "FP-1", "FP1", "FP-10", "FP-100", "Mix"]

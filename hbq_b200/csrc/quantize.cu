@@ -598,6 +598,7 @@ absmax_final_kernel(const float* partial, int nparts, int in_bf16, float* amax)
 // ------------------------------------------------------------------------------------------
 int hbq_lut_try_launch(const QArgs& qa, int mb, cudaStream_t stream, bool* launched);   // quantize_lut.cu
 
+int quantize_extra_launch(const QArgs& qa, cudaStream_t stream);                                       // quantize_extra.cu
 int hbq_lut_v_launch(const QArgs& qa, int mb, const void* in, void* out, int in_bf16, int out_bf16,
                      int64_t B, int64_t T, int64_t H, int64_t D, cudaStream_t stream);                  // quantize_lut.cu
 
@@ -723,6 +724,10 @@ int quantize_launch(const void* x, int dtype, int64_t rows, int64_t K, const hbq
         a.perm_T = kv->T; a.perm_H = kv->H;
         if ((kv->cos && ((reinterpret_cast<uintptr_t>(kv->cos) | reinterpret_cast<uintptr_t>(kv->sin)) & 15)) || !a.aligned)
             return HBQ_ERR_ALIGN;
+    }
+    if (f->kind == HBQ_KIND_MXEX || f->kind == HBQ_KIND_VSQ) {
+        if (kv) return HBQ_ERR_UNSUPPORTED;
+        return quantize_extra_launch(a, stream);
     }
     a.scale_fast_e5m3 = (f->sc_ebit == 5 && f->sc_mbit == 3 && !f->use_ceil && !f->scale_allow_subnormal);
     a.exact_div = f->sc_mbit > 4;

@@ -73,7 +73,7 @@ class QLinear(nn.Linear):
         start.record(cur)
         h2d.wait_event(start)                      # inputs prepared on the calling stream are visible
         step = -(-rows // max(1, row_chunks))
-        step = -(-step // 128) * 128               # whole GEMM row tiles per piece
+        step = max(128, -(-step // 128) * 128)     # whole GEMM row tiles per piece
         done = None
         for r0 in range(0, rows, step):
             r1 = min(rows, r0 + step)

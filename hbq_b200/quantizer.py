@@ -300,3 +300,42 @@ class HBQQuantizer(MXFPQuantizer):
         tab = self.l2_table(dev)
         self.real_l2_scale = tab[self.blk_l2_scheme[..., None].expand_as(self.l2_scale), self.l2_scale]
         return deq.view(x.shape)
+
+
+class MXExQuantizer(_CudaBlockQuantizer):
+    """MicroExponent quantization (src/quantizer.py:541-628): a power-of-two shared scale per block
+    and, per micro-block of ``l2_block_size`` elements, the better of an integer grid with step 1
+    and one with step 2.  ``l2_block_size`` up to 8."""
+
+    def __init__(self, block_size: int = 16, l2_block_size: int = 2, sc_bit: int = 8, l2_sc_bit: int = 1,
+                 mbit: int = 3):
+        super().__init__()
+        self.sc_bit = sc_bit
+        self.l2_sc_bit = l2_sc_bit
+        self.mbit = mbit
+        self.block_size = block_size
+        self.l2_block_size = l2_block_size
+
+    def _format(self):
+        return _lib.Format(_lib.KIND_MXEX, 0, self.mbit, self.sc_bit, 0, self.block_size, 0, 0, 0,
+                           self.l2_block_size, self.l2_sc_bit, 0, 0, 0)
+
+    def quantize_packed(self, x, with_deq: bool = False):
+        raise NotImplementedError("MXExQuantizer has no packed storage form")
+
+
+class VSQQuantizer(_CudaBlockQuantizer):
+    """VSQ two-level integer quantization (src/quantizer.py:630-702): a per-vector scale quantised to
+    ``sc_mbit`` unsigned bits against a per-row first-level scale."""
+
+    def __init__(self, nbit: int, block_size: int = 16, sc_mbit: int = 4):
+        super().__init__()
+        self.nbit = nbit
+        self.block_size = block_size
+        self.sc_mbit = sc_mbit
+
+    def _format(self):
+        return _lib.Format(_lib.KIND_VSQ, 0, self.nbit, 0, self.sc_mbit, self.block_size, 0, 0, 0, 0, 0, 0, 0, 0)
+
+    def quantize_packed(self, x, with_deq: bool = False):
+        raise NotImplementedError("VSQQuantizer has no packed storage form")

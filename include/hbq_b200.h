@@ -24,7 +24,10 @@ extern "C" {
 
 /* ---- formats --------------------------------------------------------------------------- */
 
-enum { HBQ_KIND_MXFP = 0, HBQ_KIND_MXINT = 1, HBQ_KIND_HBQ = 2 };
+enum { HBQ_KIND_MXFP = 0, HBQ_KIND_MXINT = 1, HBQ_KIND_HBQ = 2,
+       HBQ_KIND_MXEX = 3,   /* MXExQuantizer (src/quantizer.py:541-628): mbit = element bits, sc_ebit = sc_bit,
+                               l2_sc_bit, l2_block_size (<= 8); fake-quantised output only */
+       HBQ_KIND_VSQ = 4 };  /* VSQQuantizer (src/quantizer.py:630-702): mbit = nbit, sc_mbit; fake-quantised output only */
 /* Index into HBQQuantizer.L2_SCHEME, src/quantizer.py:708 */
 enum { HBQ_L2_POT = 0, HBQ_L2_INT = 1, HBQ_L2_SIG1 = 2, HBQ_L2_FPM1 = 3,
        HBQ_L2_FP1 = 4, HBQ_L2_FPM10 = 5, HBQ_L2_FPM100 = 6, HBQ_L2_MIX = 7 };

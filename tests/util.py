@@ -40,6 +40,10 @@ def make_quantizer(spec, **extra):
     import hbq_b200 as H
     kw = {k: v for k, v in spec.items() if k != "kind"}
     kw.update(extra)
+    if spec["kind"] == "mxex":
+        return H.MXExQuantizer(**kw)
+    if spec["kind"] == "vsq":
+        return H.VSQQuantizer(**kw)
     if spec["kind"] == "hbq":
         return H.HBQQuantizer(**kw)
     if spec["kind"] == "mxfp":
