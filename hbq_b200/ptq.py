@@ -141,14 +141,27 @@ class PTQConfig:
                                    quant_block_size=self.accumulation_quant_block_size)
         raise ValueError(f"Invalid accumulation type: {self.accumulation_type}")
 
+    # which YAML switch gives a projection an output quantizer ``yq`` (src/ptq.py:287-324)
+    _YQ_SWITCH = {"o_proj": "quant_before_rms_norm", "down_proj": "quant_before_rms_norm", "w2": "quant_before_rms_norm",
+                  "up_proj": "quant_before_hadamard", "w3": "quant_before_hadamard",
+                  "gate_proj": "quant_before_silu", "w1": "quant_before_silu"}
+
     @torch.no_grad()
-    def apply_to_linear(self, linear: QLinear, qk_proj: bool = False) -> QLinear:
+    def apply_to_linear(self, linear: QLinear, qk_proj: bool = False, role: Optional[str] = None) -> QLinear:
         """Inject quantizers, fake-quantise the weight once and set the GEMM operator: what
         inject_quantizers / static_quant_wgt / replace_accum_kernel do to one layer
-        (src/ptq.py:259-290, 337-404).  ``qk_proj`` selects the q/k-projection rounding rule."""
+        (src/ptq.py:259-324, 337-404).  ``qk_proj`` selects the q/k-projection rounding rule;
+        ``role`` (the projection's name in the reference's blocks: ``o_proj``, ``up_proj``,
+        ``gate_proj``, ``down_proj``, ``w1``/``w2``/``w3``) adds the output quantizer ``yq`` when the
+        matching ``quant_before_*`` switch is on."""
         use_round = self.qk_mx_round if qk_proj else False
         linear.wq = self.map_wgt_quantizer(use_round=use_round)
         linear.aq = self.map_act_quantizer(use_round=use_round)
+        switch = self._YQ_SWITCH.get(role) if role is not None else None
+        if role is not None and switch is None and role not in ("q_proj", "k_proj", "v_proj"):
+            raise ValueError(f"unknown projection role: {role}")
+        if switch is not None and getattr(self, switch):
+            linear.yq = self.map_act_quantizer()
         linear.weight.data = linear.wq(linear.weight.data)
         linear.ops = self.make_accum_op()
         return linear

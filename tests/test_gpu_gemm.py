@@ -191,6 +191,30 @@ def test_qlinear_layer(oracle):
     assert rel < 1e-3, rel
 
 
+def test_output_quantizer_roles():
+    """quant_before_* switches give the named projections an output quantizer (src/ptq.py:287-324)."""
+    import hbq_b200 as H
+    cfg = H.PTQConfig({"quantization": {"xqtype": "mxfp", "wqtype": "mxfp", "quant_before_rms_norm": True},
+                       "block_quant": {"act_ebit": 2, "act_mbit": 1, "act_sc_ebit": 5, "act_sc_mbit": 0, "act_block_size": 32,
+                                       "wgt_ebit": 2, "wgt_mbit": 1, "wgt_sc_ebit": 5, "wgt_sc_mbit": 0, "wgt_block_size": 32,
+                                       "scale_allow_subnormal": False},
+                       "accumulation": {"type": "fp32"}})
+    K, N = 256, 128
+    x = dev(seeded_inputs("act", 64, K, 41))
+
+    def layer(role):
+        lin = H.QLinear(K, N, bias=False, device="cuda", dtype=torch.float16)
+        lin.weight.data = dev(seeded_inputs("wgt", N, K, 42))
+        return cfg.apply_to_linear(lin, role=role)
+
+    down, gate = layer("down_proj"), layer("gate_proj")
+    assert isinstance(down.yq, H.MXFPQuantizer) and not isinstance(gate.yq, H.MXFPQuantizer)
+    with torch.no_grad():
+        assert torch.equal(down(x), down.yq.q(gate(x)))
+    with pytest.raises(ValueError):
+        layer("nonsense")
+
+
 def test_qlinear_forward_host_matches_forward():
     """The pipelined host-buffer entry (chunked copies and kernels on three streams) returns exactly
     what forward() returns for the same rows, for ragged row counts, repeated calls and wait=False."""
