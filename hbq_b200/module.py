@@ -7,7 +7,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from .quantizer import _QBase
+from .quantizer import PackedTensor, _QBase, dequantize_packed
 
 
 class QLinear(nn.Linear):
@@ -25,6 +25,7 @@ class QLinear(nn.Linear):
         self.ops = ops
         self.check_finite = check_finite
         self._host_pipe = None
+        self.packed_weight = None
 
     def forward(self, x: torch.Tensor):
         wq = self.weight
@@ -44,6 +45,27 @@ class QLinear(nn.Linear):
                 f"  weight quantizer:     {type(self.wq).__name__}\n"
                 f"  matmul:               {ops_name}")
         return self.yq(y)
+
+    # ---- packed weight storage -----------------------------------------------------------------
+    def pack_weight(self, wq=None):
+        """Quantise the weight with ``wq`` (default ``self.wq``) into packed codes and scales
+        (``PackedTensor``, 0.52-0.54 B per element for the HBQ weight formats), keep that as
+        ``self.packed_weight`` and install its dequantised form as the fp16 weight the GEMM reads.
+        The reference keeps only the fp16 fake-quantised weight (src/ptq.py:349) and re-runs the
+        quantizer (12 s per 4096x4096 matrix on CPU) whenever a model is loaded."""
+        wq = self.wq if wq is None else wq
+        self.packed_weight = wq.quantize_packed(self.weight.data)
+        self.weight.data = dequantize_packed(self.packed_weight).to(self.weight.dtype)
+        return self.packed_weight
+
+    def load_packed_weight(self, packed):
+        """Install a weight from its packed form (``PackedTensor`` or its ``state_dict()``)."""
+        if isinstance(packed, dict):
+            packed = PackedTensor.from_state_dict(packed, device=self.weight.device)
+        if tuple(packed.shape) != tuple(self.weight.shape):
+            raise ValueError(f"packed weight has shape {tuple(packed.shape)}, layer expects {tuple(self.weight.shape)}")
+        self.packed_weight = packed
+        self.weight.data = dequantize_packed(packed).to(self.weight.dtype)
 
     # ---- host-buffer entry -------------------------------------------------------------------
     def forward_host(self, x_host: torch.Tensor, out_host: torch.Tensor = None, row_chunks: int = 2,

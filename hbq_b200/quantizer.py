@@ -67,6 +67,26 @@ class PackedTensor:
         return sum(t.numel() * t.element_size() for t in
                    (self.codes, self.sign, self.scale_u8, self.l2_packed, self.scheme) if t is not None)
 
+    _PLANES = ("codes", "sign", "scale_u8", "l2_packed", "scheme")
+
+    def state_dict(self) -> dict:
+        """Plain dict (tensors, ints, strings) for ``torch.save``: the packed planes plus the format
+        fields, so a quantised weight is stored at its real size and restored without re-quantising."""
+        d = {"shape": tuple(self.shape), "dtype": str(self.dtype).replace("torch.", ""),
+             "format": {n: int(getattr(self.fmt, n)) for n, _ in _lib.Format._fields_}}
+        for n in self._PLANES:
+            t = getattr(self, n)
+            if t is not None:
+                d[n] = t
+        return d
+
+    @classmethod
+    def from_state_dict(cls, d: dict, device=None) -> "PackedTensor":
+        fmt = _lib.Format(*[int(d["format"][n]) for n, _ in _lib.Format._fields_])
+        planes = {n: (d[n].to(device) if device is not None else d[n]) if n in d else None for n in cls._PLANES}
+        return cls(torch.Size(d["shape"]), getattr(torch, d["dtype"]), fmt, planes["codes"], planes["sign"],
+                   planes["scale_u8"], planes["l2_packed"], planes["scheme"])
+
 
 def _stream_ptr(device) -> int:
     return torch.cuda.current_stream(device).cuda_stream

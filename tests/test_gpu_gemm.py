@@ -215,6 +215,27 @@ def test_output_quantizer_roles():
         layer("nonsense")
 
 
+def test_packed_weight_storage(tmp_path):
+    """A layer's weight survives pack -> torch.save -> load -> unpack bit for bit, at its packed size."""
+    import hbq_b200 as H
+    K, N = 512, 256
+    w = dev(seeded_inputs("wgt", N, K, 51))
+    wq = H.HBQQuantizer(128, 2, 1, 5, 3, l2_block_size=8, l2_sc_bit=2, l2_scheme="Mix")
+    lin = H.QLinear(K, N, bias=False, device="cuda", dtype=torch.float16)
+    lin.weight.data = w.clone()
+    lin.wq = wq
+    p = lin.pack_weight()
+    assert torch.equal(lin.weight.data, wq.q(w))
+    assert p.nbytes() < 0.56 * w.numel()
+    path = tmp_path / "w.pt"
+    torch.save(p.state_dict(), path)
+    lin2 = H.QLinear(K, N, bias=False, device="cuda", dtype=torch.float16)
+    lin2.load_packed_weight(torch.load(path))
+    assert torch.equal(lin2.weight.data, lin.weight.data)
+    with pytest.raises(ValueError):
+        H.QLinear(K, N + 8, bias=False, device="cuda", dtype=torch.float16).load_packed_weight(p)
+
+
 def test_qlinear_forward_host_matches_forward():
     """The pipelined host-buffer entry (chunked copies and kernels on three streams) returns exactly
     what forward() returns for the same rows, for ragged row counts, repeated calls and wait=False."""
