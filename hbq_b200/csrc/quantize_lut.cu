@@ -132,6 +132,7 @@ struct LutArgs {
     float inv_ele_max;        // 1 / (element max * largest candidate), rounded to fp32
     uint16_t big_l1;          // smallest l1 pattern with l1 * max value > 65504 (fp16 overflow of deq)
     int lpm, log2lpm;         // lanes per micro-block (l2_block_size / 8) and its log2
+    int log2cpr;              // log2(chunks per row) when that is a power of two (KV-cache write), else -1
     int iters;                // chunks per thread
     int64_t step_rows, step_chunks;   // one grid stride of chunks = step_rows rows + step_chunks chunks
 };
@@ -144,6 +145,38 @@ __device__ __forceinline__ void add2_f32_f16(float& acc_lo, float& acc_hi, uint3
     asm("{ .reg .b16 lo, hi;\n mov.b32 {lo, hi}, %2;\n"
         " add.rn.f32.f16 %0, lo, %0;\n add.rn.f32.f16 %1, hi, %1; }"
         : "+f"(acc_lo), "+f"(acc_hi) : "r"(e));
+}
+
+// Build the candidate table: entry e covers |a| pattern base + e and holds the 4 candidates' values.
+// Each thread walks its entries in increasing order, so every candidate's level only moves up.  Ends
+// without a barrier: callers synchronise before the first lookup.
+template <int MB>
+__device__ __forceinline__ void lut_build(const LutArgs& a, uint2* lut, int tid, int nthreads)
+{
+    __shared__ uint16_t s_thr[LUT_MAX_CAND][LUT_MAX_LEVELS + 1], s_val[LUT_MAX_CAND][LUT_MAX_LEVELS];
+    for (int i = tid; i < LUT_MAX_CAND * LUT_MAX_LEVELS; i += nthreads) {
+        const int c = i / LUT_MAX_LEVELS, k = i % LUT_MAX_LEVELS;
+        s_thr[c][k] = (k >= 1 && k < a.plan.nlev) ? a.plan.thr[c][k] : (uint16_t)0xFFFF;
+        s_val[c][k] = a.plan.val[c][k];
+        if (k == 0) s_thr[c][LUT_MAX_LEVELS] = 0xFFFF;
+    }
+    __syncthreads();
+    const int n = a.plan.hi - a.plan.base + 1;
+    int lvl[LUT_MAX_CAND] = {0, 0, 0, 0};
+    for (int e = tid; e < n; e += nthreads) {                 // increasing e: every level only moves up
+        const uint32_t u = (uint32_t)(a.plan.base + e);
+        uint32_t v[LUT_MAX_CAND];
+        #pragma unroll
+        for (int i = 0; i < LUT_MAX_CAND; ++i) {
+            while (u >= s_thr[i][lvl[i] + 1]) ++lvl[i];
+            uint32_t val = s_val[i][lvl[i]];
+            if (MB == 1)
+                for (int h = 0; h < a.plan.nhole[i]; ++h)
+                    if (u == a.plan.hole[i][h]) val = 0;
+            v[i] = val;
+        }
+        lut[e] = make_uint2(v[0] | (v[1] << 16), v[2] | (v[3] << 16));
+    }
 }
 
 // One 8-element chunk of a block through the table: block scale, all candidates' errors, the
@@ -281,32 +314,7 @@ __global__ void __launch_bounds__(LUT_THREADS, 2) hbq_lut_kernel(const LutArgs a
 
     // -- build the table: entry e covers |a| pattern base + e and holds the 4 candidates' values.
     //    Each thread walks its entries in increasing order, so every candidate's level only moves up.
-    __shared__ uint16_t s_thr[LUT_MAX_CAND][LUT_MAX_LEVELS + 1], s_val[LUT_MAX_CAND][LUT_MAX_LEVELS];
-    for (int i = tid; i < LUT_MAX_CAND * LUT_MAX_LEVELS; i += LUT_THREADS) {
-        const int c = i / LUT_MAX_LEVELS, k = i % LUT_MAX_LEVELS;
-        s_thr[c][k] = (k >= 1 && k < a.plan.nlev) ? a.plan.thr[c][k] : (uint16_t)0xFFFF;
-        s_val[c][k] = a.plan.val[c][k];
-        if (k == 0) s_thr[c][LUT_MAX_LEVELS] = 0xFFFF;
-    }
-    __syncthreads();
-    {
-        const int n = a.plan.hi - a.plan.base + 1;
-        int lvl[LUT_MAX_CAND] = {0, 0, 0, 0};
-        for (int e = tid; e < n; e += LUT_THREADS) {
-            const uint32_t u = (uint32_t)(a.plan.base + e);
-            uint32_t v[LUT_MAX_CAND];
-            #pragma unroll
-            for (int i = 0; i < LUT_MAX_CAND; ++i) {
-                while (u >= s_thr[i][lvl[i] + 1]) ++lvl[i];
-                uint32_t val = s_val[i][lvl[i]];
-                if (MB == 1)
-                    for (int h = 0; h < a.plan.nhole[i]; ++h)
-                        if (u == a.plan.hole[i][h]) val = 0;
-                v[i] = val;
-            }
-            lut[e] = make_uint2(v[0] | (v[1] << 16), v[2] | (v[3] << 16));
-        }
-    }
+    lut_build<MB>(a, lut, tid, LUT_THREADS);
     __syncthreads();
 
     const int lane = tid & 31;
@@ -370,42 +378,115 @@ __global__ void __launch_bounds__(LUT_THREADS, 2) hbq_lut_kernel(const LutArgs a
 // One CTA of 1024 threads per SM (the candidate table is built once per SM).
 constexpr int LEAN_THREADS = 1024;
 
+// One 8-element chunk through the tables: xb = the chunk as packed fp16 pairs, dq = its fake-quantised
+// values (fp16 pairs, input signs).  The G lanes of a block call this together.
 template <int MB>
-__device__ __forceinline__ void lut_build(const LutArgs& a, uint2* lut, int tid, int nthreads)
+__device__ __forceinline__ void lean_chunk(const LutArgs& a, const uint8_t* lutb, const uint4* s_l1c, uint32_t base2,
+                                           uint32_t hi2, int G, const uint32_t* xb, uint32_t* dq)
 {
-    __shared__ uint16_t s_thr[LUT_MAX_CAND][LUT_MAX_LEVELS + 1], s_val[LUT_MAX_CAND][LUT_MAX_LEVELS];
-    for (int i = tid; i < LUT_MAX_CAND * LUT_MAX_LEVELS; i += nthreads) {
-        const int c = i / LUT_MAX_LEVELS, k = i % LUT_MAX_LEVELS;
-        s_thr[c][k] = (k >= 1 && k < a.plan.nlev) ? a.plan.thr[c][k] : (uint16_t)0xFFFF;
-        s_val[c][k] = a.plan.val[c][k];
-        if (k == 0) s_thr[c][LUT_MAX_LEVELS] = 0xFFFF;
+    uint32_t ax[4];
+    #pragma unroll
+    for (int p = 0; p < 4; ++p) ax[p] = xb[p] & 0x7FFF7FFFu;
+
+    // -- block maximum and the E5M3 shared scale (round-half-up of the 3-bit mantissa) --
+    uint32_t mx = h2_bits(__hmax2(__hmax2(bits_h2(ax[0]), bits_h2(ax[1])), __hmax2(bits_h2(ax[2]), bits_h2(ax[3]))));
+    for (int off = G >> 1; off >= 1; off >>= 1)
+        mx = h2_bits(__hmax2(bits_h2(mx), bits_h2(__shfl_xor_sync(0xFFFFFFFFu, mx, off))));
+    const uint32_t am16 = max(mx & 0xFFFFu, mx >> 16);
+    const float sf = __half2float(bits_h((uint16_t)am16)) * a.inv_ele_max;
+    uint32_t sb = (uint32_t)h_bits(__float2half_rn(sf));
+    sb = min(max(sb, 0x0400u), 0x7B80u);
+    const uint32_t l1b = (sb + 0x40u) & 0xFF80u;
+    const uint4 cst = s_l1c[l1b >> 7];
+    const __half2 pre2 = bits_h2(cst.x), post2 = bits_h2(cst.y), nm2 = bits_h2(cst.z), rm2 = bits_h2(cst.w);
+    const uint32_t l1u = l1b * 0x00010001u;
+    const __half2 l1_2 = bits_h2(l1u), nl1_2 = bits_h2(l1u ^ 0x80008000u);
+
+    // -- a = fp16(|x| / l1) by the pre-scaled Markstein division, and the table offsets --
+    __half2 aa[4];
+    uint32_t w[4];
+    #pragma unroll
+    for (int p = 0; p < 4; ++p) {
+        const __half2 axs = __hmul2(bits_h2(ax[p]), pre2);
+        const __half2 q0 = __hmul2(axs, rm2);
+        const __half2 r = __hfma2(q0, nm2, axs);
+        const __half2 q1 = __hfma2(r, rm2, q0);
+        aa[p] = __hmul2(q1, post2);
+        w[p] = (h2_bits(__hmin2(__hmax2(aa[p], bits_h2(base2)), bits_h2(hi2))) - base2) << 3;
     }
-    __syncthreads();
-    const int n = a.plan.hi - a.plan.base + 1;
-    int lvl[LUT_MAX_CAND] = {0, 0, 0, 0};
-    for (int e = tid; e < n; e += nthreads) {                 // increasing e: every level only moves up
-        const uint32_t u = (uint32_t)(a.plan.base + e);
-        uint32_t v[LUT_MAX_CAND];
+
+    // -- every candidate's squared error, two candidates per half2 --
+    uint32_t ct01[8], ct23[8];
+    float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
+    if (l1b < a.big_l1) {
         #pragma unroll
-        for (int i = 0; i < LUT_MAX_CAND; ++i) {
-            while (u >= s_thr[i][lvl[i] + 1]) ++lvl[i];
-            uint32_t val = s_val[i][lvl[i]];
-            if (MB == 1)
-                for (int h = 0; h < a.plan.nhole[i]; ++h)
-                    if (u == a.plan.hole[i][h]) val = 0;
-            v[i] = val;
+        for (int j = 0; j < 8; ++j) {
+            const int p = j >> 1;
+            const uint32_t off = (j & 1) ? (w[p] >> 16) : (w[p] & 0xFFFFu);
+            const uint2 ent = *reinterpret_cast<const uint2*>(lutb + off);
+            ct01[j] = ent.x; ct23[j] = ent.y;
+            const __half2 axb = (j & 1) ? __high2half2(bits_h2(ax[p])) : __low2half2(bits_h2(ax[p]));
+            const __half2 r01 = __hfma2(bits_h2(ent.x), nl1_2, axb), r23 = __hfma2(bits_h2(ent.y), nl1_2, axb);
+            add2_f32_f16(acc0, acc1, h2_bits(__hmul2(r01, r01)));
+            add2_f32_f16(acc2, acc3, h2_bits(__hmul2(r23, r23)));
         }
-        lut[e] = make_uint2(v[0] | (v[1] << 16), v[2] | (v[3] << 16));
+    } else {
+        // value * l1 may overflow to infinity here: keep the product's own rounding
+        #pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int p = j >> 1;
+            const uint32_t off = (j & 1) ? (w[p] >> 16) : (w[p] & 0xFFFFu);
+            const uint2 ent = *reinterpret_cast<const uint2*>(lutb + off);
+            ct01[j] = ent.x; ct23[j] = ent.y;
+            const __half2 axb = (j & 1) ? __high2half2(bits_h2(ax[p])) : __low2half2(bits_h2(ax[p]));
+            const __half2 r01 = __hsub2(axb, __hmul2(bits_h2(ent.x), l1_2));
+            const __half2 r23 = __hsub2(axb, __hmul2(bits_h2(ent.y), l1_2));
+            add2_f32_f16(acc0, acc1, h2_bits(__hmul2(r01, r01)));
+            add2_f32_f16(acc2, acc3, h2_bits(__hmul2(r23, r23)));
+        }
     }
+    for (int off = a.lpm >> 1; off >= 1; off >>= 1) {
+        acc0 += __shfl_xor_sync(0xFFFFFFFFu, acc0, off); acc1 += __shfl_xor_sync(0xFFFFFFFFu, acc1, off);
+        acc2 += __shfl_xor_sync(0xFFFFFFFFu, acc2, off); acc3 += __shfl_xor_sync(0xFFFFFFFFu, acc3, off);
+    }
+    // first minimum of the fp16-rounded sums (non-negative fp16 patterns order like integers)
+    const uint32_t E01 = h2_bits(__floats2half2_rn(acc0, acc1)), E23 = h2_bits(__floats2half2_rn(acc2, acc3));
+    uint32_t bv = E01 & 0xFFFFu;
+    int best = 0;
+    if ((E01 >> 16) < bv) { bv = E01 >> 16; best = 1; }
+    if ((E23 & 0xFFFFu) < bv) { bv = E23 & 0xFFFFu; best = 2; }
+    if ((E23 >> 16) < bv) { bv = E23 >> 16; best = 3; }
+
+    // -- the winner's values with the inputs' signs --
+    const uint32_t psel = (best & 1) ? 0x7632u : 0x5410u;
+    #pragma unroll
+    for (int p = 0; p < 4; ++p) {
+        const uint32_t ra = best < 2 ? ct01[2 * p] : ct23[2 * p], rb = best < 2 ? ct01[2 * p + 1] : ct23[2 * p + 1];
+        const __half2 d = __hmul2(bits_h2(__byte_perm(ra, rb, psel)), l1_2);
+        dq[p] = h2_bits(d) | (xb[p] & 0x80008000u);
+    }
+    // The reference returns +0 (not -0) when fp16(a / t) is exactly zero.  Only quotients a below
+    // 2^-19 can do that; deciding it needs the exact a, where the scaled division may be off: rare.
+    const __half2 amin = __hmin2(__hmin2(aa[0], aa[1]), __hmin2(aa[2], aa[3]));
+    if (__hle2_mask(amin, bits_h2(0x00200020u)) != 0u) {
+        const float l1f = __half2float(bits_h((uint16_t)l1b)), t = a.q.tab[0][best < a.q.nc ? best : a.q.nc - 1];
+        #pragma unroll
+        for (int p = 0; p < 4; ++p)
+            #pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const uint32_t abits = (h2_bits(aa[p]) >> (16 * h)) & 0xFFFFu;
+                if (abits <= 0x0020u && ((xb[p] >> (16 * h)) & 0x8000u)) {
+                    const float xf = __half2float(bits_h((uint16_t)(ax[p] >> (16 * h))));
+                    if (rh(__fdiv_rn(rh(__fdiv_rn(xf, l1f)), t)) == 0.f) dq[p] &= ~(0x8000u << (16 * h));
+                }
+            }
+    }
+
 }
 
-template <int MB, bool IN_BF16, bool OUT_BF16>
-__global__ void __launch_bounds__(LEAN_THREADS, 1) hbq_lut_lean_kernel(const LutArgs a)
+// Per E5M3 scale (fp16 pattern >> 7): the division constants {2^s1, 2^-(s1+e), -m, fp16(1/m)} as fp16 pairs.
+__device__ __forceinline__ void l1_table_build(const LutArgs& a, uint4* s_l1c, int tid)
 {
-    extern __shared__ __align__(16) uint2 lut[];
-    __shared__ uint4 s_l1c[256];             // per E5M3 scale (pattern >> 7): {pre2, post2, -m2, 1/m 2}
-    const int tid = threadIdx.x;
-    lut_build<MB>(a, lut, tid, LEAN_THREADS);
     if (tid < 256) {
         const uint32_t l1b = (uint32_t)tid << 7;
         const int e5 = (int)(l1b >> 10) - 15;
@@ -417,6 +498,19 @@ __global__ void __launch_bounds__(LEAN_THREADS, 1) hbq_lut_lean_kernel(const Lut
         c.w = (uint32_t)a.rm[(l1b >> 7) & 7u] * 0x00010001u;
         s_l1c[tid] = c;
     }
+}
+
+// KV: the K / post-RoPE Q cache write on the same fast path -- a row is one (token, head) vector of
+// D = K elements (D a power of two <= 256, fp16), RoPE is applied on load and the row is stored at its
+// (batch, head, token) position.
+template <int MB, bool IN_BF16, bool OUT_BF16, bool KV>
+__global__ void __launch_bounds__(LEAN_THREADS, 1) hbq_lut_lean_kernel(const LutArgs a)
+{
+    extern __shared__ __align__(16) uint2 lut[];
+    __shared__ uint4 s_l1c[256];             // per E5M3 scale (pattern >> 7): {pre2, post2, -m2, 1/m 2}
+    const int tid = threadIdx.x;
+    lut_build<MB>(a, lut, tid, LEAN_THREADS);
+    l1_table_build(a, s_l1c, tid);
     __syncthreads();
 
     const uint32_t base2 = (uint32_t)a.plan.base * 0x00010001u, hi2 = (uint32_t)a.plan.hi * 0x00010001u;
@@ -436,110 +530,24 @@ __global__ void __launch_bounds__(LEAN_THREADS, 1) hbq_lut_lean_kernel(const Lut
         if (ci + stride < total) nraw = __ldg(in + ci + stride);       // next chunk in flight during this one
 
         uint32_t xb[4] = {raw.x, raw.y, raw.z, raw.w};
+        int64_t oci = ci;                                  // chunk index of the output
+        if (KV) {
+            const int64_t row = valid ? ci >> a.log2cpr : 0, c = ci & (a.q.cpr - 1);
+            Chunk xr;
+            #pragma unroll
+            for (int p = 0; p < 4; ++p) xr.h[p] = bits_h2(xb[p]);
+            if (a.q.rope_cos) rope_chunk(a.q, xr, row, c * 8);
+            #pragma unroll
+            for (int p = 0; p < 4; ++p) xb[p] = h2_bits(xr.h[p]);
+            oci = (out_row(a.q, row) << a.log2cpr) + c;
+        }
         if (IN_BF16) {
             #pragma unroll
             for (int p = 0; p < 4; ++p)
                 xb[p] = h2_bits(__floats2half2_rn(__uint_as_float(xb[p] << 16), __uint_as_float(xb[p] & 0xFFFF0000u)));
         }
-        uint32_t ax[4];
-        #pragma unroll
-        for (int p = 0; p < 4; ++p) ax[p] = xb[p] & 0x7FFF7FFFu;
-
-        // -- block maximum and the E5M3 shared scale (round-half-up of the 3-bit mantissa) --
-        uint32_t mx = h2_bits(__hmax2(__hmax2(bits_h2(ax[0]), bits_h2(ax[1])), __hmax2(bits_h2(ax[2]), bits_h2(ax[3]))));
-        for (int off = G >> 1; off >= 1; off >>= 1)
-            mx = h2_bits(__hmax2(bits_h2(mx), bits_h2(__shfl_xor_sync(0xFFFFFFFFu, mx, off))));
-        const uint32_t am16 = max(mx & 0xFFFFu, mx >> 16);
-        const float sf = __half2float(bits_h((uint16_t)am16)) * a.inv_ele_max;
-        uint32_t sb = (uint32_t)h_bits(__float2half_rn(sf));
-        sb = min(max(sb, 0x0400u), 0x7B80u);
-        const uint32_t l1b = (sb + 0x40u) & 0xFF80u;
-        const uint4 cst = s_l1c[l1b >> 7];
-        const __half2 pre2 = bits_h2(cst.x), post2 = bits_h2(cst.y), nm2 = bits_h2(cst.z), rm2 = bits_h2(cst.w);
-        const uint32_t l1u = l1b * 0x00010001u;
-        const __half2 l1_2 = bits_h2(l1u), nl1_2 = bits_h2(l1u ^ 0x80008000u);
-
-        // -- a = fp16(|x| / l1) by the pre-scaled Markstein division, and the table offsets --
-        __half2 aa[4];
-        uint32_t w[4];
-        #pragma unroll
-        for (int p = 0; p < 4; ++p) {
-            const __half2 axs = __hmul2(bits_h2(ax[p]), pre2);
-            const __half2 q0 = __hmul2(axs, rm2);
-            const __half2 r = __hfma2(q0, nm2, axs);
-            const __half2 q1 = __hfma2(r, rm2, q0);
-            aa[p] = __hmul2(q1, post2);
-            w[p] = (h2_bits(__hmin2(__hmax2(aa[p], bits_h2(base2)), bits_h2(hi2))) - base2) << 3;
-        }
-
-        // -- every candidate's squared error, two candidates per half2 --
-        uint32_t ct01[8], ct23[8];
-        float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
-        if (l1b < a.big_l1) {
-            #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const int p = j >> 1;
-                const uint32_t off = (j & 1) ? (w[p] >> 16) : (w[p] & 0xFFFFu);
-                const uint2 ent = *reinterpret_cast<const uint2*>(lutb + off);
-                ct01[j] = ent.x; ct23[j] = ent.y;
-                const __half2 axb = (j & 1) ? __high2half2(bits_h2(ax[p])) : __low2half2(bits_h2(ax[p]));
-                const __half2 r01 = __hfma2(bits_h2(ent.x), nl1_2, axb), r23 = __hfma2(bits_h2(ent.y), nl1_2, axb);
-                add2_f32_f16(acc0, acc1, h2_bits(__hmul2(r01, r01)));
-                add2_f32_f16(acc2, acc3, h2_bits(__hmul2(r23, r23)));
-            }
-        } else {
-            // value * l1 may overflow to infinity here: keep the product's own rounding
-            #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const int p = j >> 1;
-                const uint32_t off = (j & 1) ? (w[p] >> 16) : (w[p] & 0xFFFFu);
-                const uint2 ent = *reinterpret_cast<const uint2*>(lutb + off);
-                ct01[j] = ent.x; ct23[j] = ent.y;
-                const __half2 axb = (j & 1) ? __high2half2(bits_h2(ax[p])) : __low2half2(bits_h2(ax[p]));
-                const __half2 r01 = __hsub2(axb, __hmul2(bits_h2(ent.x), l1_2));
-                const __half2 r23 = __hsub2(axb, __hmul2(bits_h2(ent.y), l1_2));
-                add2_f32_f16(acc0, acc1, h2_bits(__hmul2(r01, r01)));
-                add2_f32_f16(acc2, acc3, h2_bits(__hmul2(r23, r23)));
-            }
-        }
-        for (int off = a.lpm >> 1; off >= 1; off >>= 1) {
-            acc0 += __shfl_xor_sync(0xFFFFFFFFu, acc0, off); acc1 += __shfl_xor_sync(0xFFFFFFFFu, acc1, off);
-            acc2 += __shfl_xor_sync(0xFFFFFFFFu, acc2, off); acc3 += __shfl_xor_sync(0xFFFFFFFFu, acc3, off);
-        }
-        // first minimum of the fp16-rounded sums (non-negative fp16 patterns order like integers)
-        const uint32_t E01 = h2_bits(__floats2half2_rn(acc0, acc1)), E23 = h2_bits(__floats2half2_rn(acc2, acc3));
-        uint32_t bv = E01 & 0xFFFFu;
-        int best = 0;
-        if ((E01 >> 16) < bv) { bv = E01 >> 16; best = 1; }
-        if ((E23 & 0xFFFFu) < bv) { bv = E23 & 0xFFFFu; best = 2; }
-        if ((E23 >> 16) < bv) { bv = E23 >> 16; best = 3; }
-
-        // -- the winner's values with the inputs' signs --
-        const uint32_t psel = (best & 1) ? 0x7632u : 0x5410u;
         uint32_t dq[4];
-        #pragma unroll
-        for (int p = 0; p < 4; ++p) {
-            const uint32_t ra = best < 2 ? ct01[2 * p] : ct23[2 * p], rb = best < 2 ? ct01[2 * p + 1] : ct23[2 * p + 1];
-            const __half2 d = __hmul2(bits_h2(__byte_perm(ra, rb, psel)), l1_2);
-            dq[p] = h2_bits(d) | (xb[p] & 0x80008000u);
-        }
-        // The reference returns +0 (not -0) when fp16(a / t) is exactly zero.  Only quotients a below
-        // 2^-19 can do that; deciding it needs the exact a, where the scaled division may be off: rare.
-        const __half2 amin = __hmin2(__hmin2(aa[0], aa[1]), __hmin2(aa[2], aa[3]));
-        if (__hle2_mask(amin, bits_h2(0x00200020u)) != 0u) {
-            const float l1f = __half2float(bits_h((uint16_t)l1b)), t = a.q.tab[0][best < a.q.nc ? best : a.q.nc - 1];
-            #pragma unroll
-            for (int p = 0; p < 4; ++p)
-                #pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const uint32_t abits = (h2_bits(aa[p]) >> (16 * h)) & 0xFFFFu;
-                    if (abits <= 0x0020u && ((xb[p] >> (16 * h)) & 0x8000u)) {
-                        const float xf = __half2float(bits_h((uint16_t)(ax[p] >> (16 * h))));
-                        if (rh(__fdiv_rn(rh(__fdiv_rn(xf, l1f)), t)) == 0.f) dq[p] &= ~(0x8000u << (16 * h));
-                    }
-                }
-        }
-
+        lean_chunk<MB>(a, lutb, s_l1c, base2, hi2, G, xb, dq);
         if (valid) {
             if (OUT_BF16) {
                 #pragma unroll
@@ -549,7 +557,7 @@ __global__ void __launch_bounds__(LEAN_THREADS, 1) hbq_lut_lean_kernel(const Lut
                     dq[p] = *reinterpret_cast<uint32_t*>(&bb);
                 }
             }
-            out[ci] = make_uint4(dq[0], dq[1], dq[2], dq[3]);
+            out[oci] = make_uint4(dq[0], dq[1], dq[2], dq[3]);
         }
         raw = nraw;
     }
@@ -558,11 +566,13 @@ __global__ void __launch_bounds__(LEAN_THREADS, 1) hbq_lut_lean_kernel(const Lut
 template <int MB>
 static int launch_lean(const LutArgs& a, int grid, size_t smem, cudaStream_t stream)
 {
-    #define HBQ_LAUNCH_LEAN(IB, OB)                                                                                              \
-        HBQ_CUDA_TRY(cudaFuncSetAttribute(hbq_lut_lean_kernel<MB, IB, OB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-        hbq_lut_lean_kernel<MB, IB, OB><<<grid, LEAN_THREADS, smem, stream>>>(a);
-    if (a.q.in_bf16) { if (a.q.out_bf16) { HBQ_LAUNCH_LEAN(true, true) } else { HBQ_LAUNCH_LEAN(true, false) } }
-    else { if (a.q.out_bf16) { HBQ_LAUNCH_LEAN(false, true) } else { HBQ_LAUNCH_LEAN(false, false) } }
+    #define HBQ_LAUNCH_LEAN(IB, OB, KVW)                                                                                              \
+        HBQ_CUDA_TRY(cudaFuncSetAttribute(hbq_lut_lean_kernel<MB, IB, OB, KVW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        hbq_lut_lean_kernel<MB, IB, OB, KVW><<<grid, LEAN_THREADS, smem, stream>>>(a);
+    const bool kvw = a.q.rope_cos || a.q.perm_T > 0;
+    if (kvw) { if (a.q.out_bf16) { HBQ_LAUNCH_LEAN(false, true, true) } else { HBQ_LAUNCH_LEAN(false, false, true) } }
+    else if (a.q.in_bf16) { if (a.q.out_bf16) { HBQ_LAUNCH_LEAN(true, true, false) } else { HBQ_LAUNCH_LEAN(true, false, false) } }
+    else { if (a.q.out_bf16) { HBQ_LAUNCH_LEAN(false, true, false) } else { HBQ_LAUNCH_LEAN(false, false, false) } }
     #undef HBQ_LAUNCH_LEAN
     HBQ_LAUNCH_CHECK("hbq_lut_lean_kernel");
     return HBQ_OK;
@@ -593,33 +603,13 @@ __global__ void __launch_bounds__(LUT_THREADS, 2) hbq_lut_v_kernel(const LutArgs
     const int n = a.plan.hi - a.plan.base + 1;
     uint16_t* tile = reinterpret_cast<uint16_t*>(lut + ((n + 1) & ~1));   // [VD][VLD] fp16, 16-byte aligned
 
-    __shared__ uint16_t s_thr[LUT_MAX_CAND][LUT_MAX_LEVELS + 1], s_val[LUT_MAX_CAND][LUT_MAX_LEVELS];
-    for (int i = tid; i < LUT_MAX_CAND * LUT_MAX_LEVELS; i += LUT_THREADS) {
-        const int c = i / LUT_MAX_LEVELS, k = i % LUT_MAX_LEVELS;
-        s_thr[c][k] = (k >= 1 && k < a.plan.nlev) ? a.plan.thr[c][k] : (uint16_t)0xFFFF;
-        s_val[c][k] = a.plan.val[c][k];
-        if (k == 0) s_thr[c][LUT_MAX_LEVELS] = 0xFFFF;
-    }
-    __syncthreads();
-    {
-        int lvl[LUT_MAX_CAND] = {0, 0, 0, 0};
-        for (int e = tid; e < n; e += LUT_THREADS) {
-            const uint32_t u = (uint32_t)(a.plan.base + e);
-            uint32_t val[LUT_MAX_CAND];
-            #pragma unroll
-            for (int i = 0; i < LUT_MAX_CAND; ++i) {
-                while (u >= s_thr[i][lvl[i] + 1]) ++lvl[i];
-                val[i] = s_val[i][lvl[i]];
-                if (MB == 1)
-                    for (int h = 0; h < a.plan.nhole[i]; ++h)
-                        if (u == a.plan.hole[i][h]) val[i] = 0;
-            }
-            lut[e] = make_uint2(val[0] | (val[1] << 16), val[2] | (val[3] << 16));
-        }
-    }
+    __shared__ uint4 s_l1c[256];
+    lut_build<MB>(a, lut, tid, LUT_THREADS);
+    l1_table_build(a, s_l1c, tid);
     __syncthreads();
 
     const uint32_t base2 = (uint32_t)a.plan.base * 0x00010001u, hi2 = (uint32_t)a.plan.hi * 0x00010001u;
+    const uint8_t* lutb = reinterpret_cast<const uint8_t*>(lut);
     for (int64_t tl = blockIdx.x; tl < v.tiles; tl += gridDim.x) {
         const int ds = (int)(tl % v.dslabs);
         const int tb = (int)((tl / v.dslabs) % v.tblocks);
@@ -657,13 +647,10 @@ __global__ void __launch_bounds__(LUT_THREADS, 2) hbq_lut_v_kernel(const LutArgs
             const int lig16 = tid & 15;
             uint4* cell = reinterpret_cast<uint4*>(tile + d * VLD + lig16 * 8);
             const uint4 cv = *cell;
-            Chunk x;
-            x.h[0] = bits_h2(cv.x); x.h[1] = bits_h2(cv.y); x.h[2] = bits_h2(cv.z); x.h[3] = bits_h2(cv.w);
-            __half2 dq[4];
-            uint32_t mag[4], sgo[4], l1b;
-            int best;
-            lut_chunk<MB, false>(a, lut, x, base2, hi2, dq, mag, sgo, best, l1b);
-            *cell = make_uint4(h2_bits(dq[0]), h2_bits(dq[1]), h2_bits(dq[2]), h2_bits(dq[3]));
+            const uint32_t xb[4] = {cv.x, cv.y, cv.z, cv.w};
+            uint32_t dq[4];
+            lean_chunk<MB>(a, lutb, s_l1c, base2, hi2, a.q.G, xb, dq);
+            *cell = make_uint4(dq[0], dq[1], dq[2], dq[3]);
         }
         __syncthreads();
 
@@ -741,16 +728,14 @@ static int launch_lut(const LutArgs& a, bool codes, int grid, size_t smem, cudaS
 
 // Runs the table kernel if the (already validated) HBQ arguments fit it.  *launched tells the
 // caller whether it did; when it did not, the arithmetic kernel must be used.
-int hbq_lut_try_launch(const QArgs& qa, int mb, cudaStream_t stream, bool* launched)
+// Kernel arguments of the table kernels for a validated HBQ format; false when no table plan fits it.
+static bool fill_lut_args(const QArgs& qa, int mb, LutArgs* out)
 {
-    *launched = false;
-    const int L = qa.f.l2_block_size;
-    if (qa.nscheme != 1 || qa.nc > LUT_MAX_CAND || !qa.scale_fast_e5m3 || L < 8 || mb < 1 || mb > 3) return HBQ_OK;
-    LutArgs a;
+    LutArgs& a = *out;
     memset(&a, 0, sizeof(a));
-    if (!get_plan(mb, qa.tab[0], qa.nc, &a.plan)) return HBQ_OK;
+    if (!get_plan(mb, qa.tab[0], qa.nc, &a.plan)) return false;
     a.q = qa;
-    a.lpm = L / 8;
+    a.lpm = qa.f.l2_block_size / 8;
     while ((1 << a.log2lpm) < a.lpm) ++a.log2lpm;
     for (int i = 0; i < 8; ++i) a.rm[i] = d2h(1.0 / (1.0 + i / 8.0));
     double vmax = 0;
@@ -760,9 +745,19 @@ int hbq_lut_try_launch(const QArgs& qa, int mb, cudaStream_t stream, bool* launc
         if (v > vmax) vmax = v;
     }
     a.inv_ele_max = 1.f / qa.ele_max[0];
-    a.big_l1 = 0x7C00;
+    a.big_l1 = 0x7C00;                         // smallest scale whose product with the largest value overflows fp16
     for (int pat = 0x0400; pat <= 0x7B80; pat += 0x80)
         if (h2d((uint16_t)pat) * vmax > 65504.0) { a.big_l1 = (uint16_t)pat; break; }
+    return true;
+}
+
+int hbq_lut_try_launch(const QArgs& qa, int mb, cudaStream_t stream, bool* launched)
+{
+    *launched = false;
+    const int L = qa.f.l2_block_size;
+    if (qa.nscheme != 1 || qa.nc > LUT_MAX_CAND || !qa.scale_fast_e5m3 || L < 8 || mb < 1 || mb > 3) return HBQ_OK;
+    LutArgs a;
+    if (!fill_lut_args(qa, mb, &a)) return HBQ_OK;
 
     int dev = 0, sms = 0;
     HBQ_CUDA_TRY(cudaGetDevice(&dev));
@@ -770,7 +765,11 @@ int hbq_lut_try_launch(const QArgs& qa, int mb, cudaStream_t stream, bool* launc
     const QArgs& q = qa;
     const bool side_out = q.out.codes || q.out.sign || q.out.scale_u8 || q.out.scale_h || q.out.l2_packed ||
                           q.out.l2_idx || q.out.scheme;
-    if (q.deq && !side_out && q.aligned && q.K == q.Kp && !q.rope_cos && q.perm_T <= 0) {
+    const bool kvw = q.rope_cos || q.perm_T > 0;
+    a.log2cpr = -1;
+    if ((q.cpr & (q.cpr - 1)) == 0) { a.log2cpr = 0; while ((1ll << a.log2cpr) < q.cpr) ++a.log2cpr; }
+    // the K-cache write takes the fast path for fp16 rows of a power-of-two length
+    if (q.deq && !side_out && q.aligned && q.K == q.Kp && (!kvw || (!q.in_bf16 && a.log2cpr >= 0))) {
         const int64_t need = (qa.total_chunks + LEAN_THREADS - 1) / LEAN_THREADS;
         const int grid = (int)(need < sms ? need : sms);
         const size_t smem = (size_t)(a.plan.hi - a.plan.base + 1) * sizeof(uint2);
@@ -812,22 +811,7 @@ int hbq_lut_v_launch(const QArgs& qa, int mb, const void* in, void* out, int in_
     if (qa.f.block_size > VT || (VT % qa.f.block_size) != 0 || (D % VD) != 0) return HBQ_ERR_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15) return HBQ_ERR_ALIGN;
     LutArgs a;
-    memset(&a, 0, sizeof(a));
-    if (!get_plan(mb, qa.tab[0], qa.nc, &a.plan)) return HBQ_ERR_UNSUPPORTED;
-    a.q = qa;
-    a.lpm = L / 8;
-    while ((1 << a.log2lpm) < a.lpm) ++a.log2lpm;
-    for (int i = 0; i < 8; ++i) a.rm[i] = d2h(1.0 / (1.0 + i / 8.0));
-    double vmax = 0;
-    for (int i = 0; i < LUT_MAX_CAND; ++i) {
-        a.rt[i] = d2h(1.0 / (double)qa.tab[0][i < qa.nc ? i : qa.nc - 1]);
-        const double val = h2d(a.plan.val[i][a.plan.nlev - 1]);
-        if (val > vmax) vmax = val;
-    }
-    a.inv_ele_max = 1.f / qa.ele_max[0];
-    a.big_l1 = 0x7C00;
-    for (int pat = 0x0400; pat <= 0x7B80; pat += 0x80)
-        if (h2d((uint16_t)pat) * vmax > 65504.0) { a.big_l1 = (uint16_t)pat; break; }
+    if (!fill_lut_args(qa, mb, &a)) return HBQ_ERR_UNSUPPORTED;
 
     VArgs v;
     v.in = (const uint16_t*)in; v.out = (uint16_t*)out;
