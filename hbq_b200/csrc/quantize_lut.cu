@@ -593,15 +593,20 @@ struct VArgs {
     int64_t tiles;            // B * H * ceil(T/128) * (D/64)
     int tblocks, dslabs;
 };
-constexpr int VT = 128, VD = 64, VLD = VT + 8;
+constexpr int VT = 128, VD = 64;
+// Shared tile of 32-bit words: row = channel pair (d, d+1), column = token, value = the two channels'
+// fp16 values of that token.  The 8-token granules of a row are XOR-swizzled with the row's segment
+// so that the token-major writes of the load phase spread over the banks, while a thread's 8
+// consecutive tokens stay one aligned 32-byte run for the channel-major compute phase.
+__device__ __forceinline__ int v_word(int dp, int tk) { return dp * VT + ((((tk >> 3) ^ ((dp >> 2) & 3)) << 3) | (tk & 7)); }
 
 template <int MB>
 __global__ void __launch_bounds__(LUT_THREADS, 2) hbq_lut_v_kernel(const LutArgs a, const VArgs v)
 {
     extern __shared__ __align__(16) uint2 lut[];
-    const int tid = threadIdx.x;
+    const int tid = threadIdx.x, lane = tid & 31;
     const int n = a.plan.hi - a.plan.base + 1;
-    uint16_t* tile = reinterpret_cast<uint16_t*>(lut + ((n + 1) & ~1));   // [VD][VLD] fp16, 16-byte aligned
+    uint32_t* tile = reinterpret_cast<uint32_t*>(lut + ((n + 1) & ~1));   // [VD/2][VT] words, 16-byte aligned
 
     __shared__ uint4 s_l1c[256];
     lut_build<MB>(a, lut, tid, LUT_THREADS);
@@ -617,7 +622,7 @@ __global__ void __launch_bounds__(LUT_THREADS, 2) hbq_lut_v_kernel(const LutArgs
         const int64_t b = bh / v.H, h = bh - b * v.H;
         const int64_t t0 = (int64_t)tb * VT, d0 = (int64_t)ds * VD;
 
-        // -- load [128 tokens][64 channels], store transposed as tile[channel][token] --
+        // -- load [128 tokens][64 channels]: a thread brings 8 channels of one token = 4 words --
         #pragma unroll
         for (int r = 0; r < (VT * VD / 8) / LUT_THREADS; ++r) {
             const int idx = tid + r * LUT_THREADS;
@@ -629,28 +634,39 @@ __global__ void __launch_bounds__(LUT_THREADS, 2) hbq_lut_v_kernel(const LutArgs
             }
             #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                uint32_t lo = w[i] & 0xFFFFu, hi = w[i] >> 16;
-                if (v.in_bf16) {
-                    const __half2 hh = __floats2half2_rn(__uint_as_float(lo << 16), __uint_as_float(hi << 16));
-                    lo = h2_bits(hh) & 0xFFFFu; hi = h2_bits(hh) >> 16;
-                }
-                tile[(seg * 8 + 2 * i) * VLD + tk] = (uint16_t)lo;
-                tile[(seg * 8 + 2 * i + 1) * VLD + tk] = (uint16_t)hi;
+                if (v.in_bf16)
+                    w[i] = h2_bits(__floats2half2_rn(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xFFFF0000u)));
+                tile[v_word(seg * 4 + i, tk)] = w[i];
             }
         }
         __syncthreads();
 
-        // -- quantise in place: a thread owns 8 consecutive tokens of one channel --
+        // -- quantise in place: a thread owns 8 consecutive tokens of one channel; lanes 0-15 of a warp
+        //    hold an even channel, lanes 16-31 the odd channel of the same words --
         #pragma unroll
         for (int pass = 0; pass < VD / (LUT_THREADS / 16); ++pass) {
             const int d = pass * (LUT_THREADS / 16) + (tid >> 4);
             const int lig16 = tid & 15;
-            uint4* cell = reinterpret_cast<uint4*>(tile + d * VLD + lig16 * 8);
-            const uint4 cv = *cell;
-            const uint32_t xb[4] = {cv.x, cv.y, cv.z, cv.w};
-            uint32_t dq[4];
+            uint32_t* cell = tile + v_word(d >> 1, lig16 * 8);
+            const uint4 c0 = *reinterpret_cast<const uint4*>(cell), c1 = *reinterpret_cast<const uint4*>(cell + 4);
+            const uint32_t wt[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};      // tokens 0..7, both channels
+            const uint32_t pick = (d & 1) ? 0x7632u : 0x5410u;
+            uint32_t xb[4], dq[4];
+            #pragma unroll
+            for (int p = 0; p < 4; ++p) xb[p] = __byte_perm(wt[2 * p], wt[2 * p + 1], pick);   // this channel, tokens 2p, 2p+1
             lean_chunk<MB>(a, lutb, s_l1c, base2, hi2, a.q.G, xb, dq);
-            *cell = make_uint4(dq[0], dq[1], dq[2], dq[3]);
+            // rebuild the words with the partner channel's results: the even lane writes tokens 0-3, the odd lane 4-7
+            uint32_t ow[4];
+            #pragma unroll
+            for (int p = 0; p < 2; ++p) {
+                const int mine = (d & 1) ? 2 + p : p, theirs = (d & 1) ? p : 2 + p;      // pair index this lane keeps / gives away
+                const uint32_t got = __shfl_xor_sync(0xFFFFFFFFu, dq[theirs], 16);      // partner's values for the pair I keep
+                const uint32_t ev = (d & 1) ? got : dq[mine], od = (d & 1) ? dq[mine] : got;
+                ow[2 * p] = __byte_perm(ev, od, 0x5410u);
+                ow[2 * p + 1] = __byte_perm(ev, od, 0x7632u);
+            }
+            __syncwarp();
+            *reinterpret_cast<uint4*>(cell + ((d & 1) ? 4 : 0)) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
         }
         __syncthreads();
 
@@ -663,12 +679,12 @@ __global__ void __launch_bounds__(LUT_THREADS, 2) hbq_lut_v_kernel(const LutArgs
                 uint32_t w[4];
                 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    uint32_t lo = tile[(seg * 8 + 2 * i) * VLD + tk], hi = tile[(seg * 8 + 2 * i + 1) * VLD + tk];
+                    w[i] = tile[v_word(seg * 4 + i, tk)];
                     if (v.out_bf16) {
-                        const float2 f = __half22float2(bits_h2(lo | (hi << 16)));
+                        const float2 f = __half22float2(bits_h2(w[i]));
                         __nv_bfloat162 bb = __floats2bfloat162_rn(f.x, f.y);
                         w[i] = *reinterpret_cast<uint32_t*>(&bb);
-                    } else w[i] = lo | (hi << 16);
+                    }
                 }
                 *reinterpret_cast<uint4*>(v.out + (((b * v.H + h) * v.T + t0 + tk) * v.D + d0 + seg * 8)) =
                     make_uint4(w[0], w[1], w[2], w[3]);
@@ -676,6 +692,7 @@ __global__ void __launch_bounds__(LUT_THREADS, 2) hbq_lut_v_kernel(const LutArgs
         }
         __syncthreads();
     }
+    (void)lane;
 }
 
 // ---- host side ------------------------------------------------------------------------------------
@@ -823,7 +840,7 @@ int hbq_lut_v_launch(const QArgs& qa, int mb, const void* in, void* out, int in_
     HBQ_CUDA_TRY(cudaGetDevice(&dev));
     HBQ_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     const int grid = (int)(v.tiles < 2 * sms ? v.tiles : 2 * sms);
-    const size_t smem = (size_t)((a.plan.hi - a.plan.base + 2) & ~1) * sizeof(uint2) + (size_t)VD * VLD * 2;
+    const size_t smem = (size_t)((a.plan.hi - a.plan.base + 2) & ~1) * sizeof(uint2) + (size_t)(VD / 2) * VT * 4;
     #define HBQ_LAUNCH_V(MBV)                                                                                            \
         HBQ_CUDA_TRY(cudaFuncSetAttribute(hbq_lut_v_kernel<MBV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
         hbq_lut_v_kernel<MBV><<<grid, LUT_THREADS, smem, stream>>>(a, v);
