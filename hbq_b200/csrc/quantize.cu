@@ -10,6 +10,7 @@
 // the G = block_size/8 lanes that own one quantisation block reduce with warp shuffles, so a
 // tensor is read once from HBM and every output is written once.
 #include "quantize_dev.cuh"
+#include "vcache_dev.cuh"
 #include <math.h>
 #include <mutex>
 
@@ -217,52 +218,12 @@ __global__ void __launch_bounds__(256) mx_quantize_kernel(const QArgs a)
 //       every quotient >= 2^-14; smaller ones quantise to zero anyway).
 // CODES: also emit element codes (needs the extra extraction arithmetic).
 // ------------------------------------------------------------------------------------------
-// LEAN: the tensor is contiguous, 16-byte aligned, K a multiple of the block, and only the
-//        fake-quantised output is wanted: chunk ci is elements [8 ci, 8 ci + 8) of both tensors, so
-//        the row / column bookkeeping, RoPE / permutation and side outputs drop out.
-__device__ __forceinline__ Chunk lean_load(const QArgs& a, int64_t ci)
+// The arithmetic of one 8-element chunk on the fast path: block maximum (G lanes), shared scale `sb`
+// (fp16 pattern), fake-quantised values d and, with CODES, code magnitudes and signs.
+template <int KIND, int MB, bool CODES>
+__device__ __forceinline__ void mx_fast_chunk(const QArgs& a, const Chunk& x, __half2* d, uint32_t* mag, uint32_t* sg,
+                                              uint32_t& sb)
 {
-    const uint4 v = __ldg(reinterpret_cast<const uint4*>(a.x) + ci);
-    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-    Chunk c;
-    if (!a.in_bf16) {
-        #pragma unroll
-        for (int p = 0; p < 4; ++p) c.h[p] = bits_h2(w[p]);
-    } else {
-        #pragma unroll
-        for (int p = 0; p < 4; ++p)
-            c.h[p] = __floats2half2_rn(__uint_as_float(w[p] << 16), __uint_as_float(w[p] & 0xFFFF0000u));
-    }
-    return c;
-}
-
-template <int KIND, int MB, bool CODES, bool LEAN>
-__global__ void __launch_bounds__(256) mx_fast_kernel(const QArgs a)
-{
-    // Grid-stride loop with the next chunk's load issued before the current one is processed, so
-    // every thread keeps a 16-byte load in flight while it computes.
-    const int lane = threadIdx.x & 31;
-    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-    int64_t ci = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    int64_t row = 0, c = 0;
-    if (!LEAN) split_chunk(a, ci < a.total_chunks ? ci : 0, row, c);
-    Chunk x;
-    if (ci < a.total_chunks) x = LEAN ? lean_load(a, ci) : load_chunk(a, row, c * 8);
-    else { for (int p = 0; p < 4; ++p) x.h[p] = bits_h2(0u); }
-    for (; ci - lane < a.total_chunks; ci += stride) {
-    const bool valid = ci < a.total_chunks;
-    const int64_t k0 = c * 8;
-    const int64_t row_cur = row, c_cur = c;
-    // advance (row, chunk-in-row) by one grid stride and prefetch
-    if (!LEAN) {
-        row += a.step_rows; c += a.step_chunks;
-        if (c >= a.cpr) { c -= a.cpr; ++row; }
-    }
-    Chunk xn;
-    if (ci + stride < a.total_chunks) xn = LEAN ? lean_load(a, ci + stride) : load_chunk(a, row, c * 8);
-    else { for (int p = 0; p < 4; ++p) xn.h[p] = bits_h2(0u); }
-
-    if (!LEAN && a.rope_cos) rope_chunk(a, x, valid ? row_cur : 0, k0);
     uint32_t ax[4];
     #pragma unroll
     for (int p = 0; p < 4; ++p) ax[p] = h2_bits(x.h[p]) & 0x7FFF7FFFu;
@@ -271,7 +232,6 @@ __global__ void __launch_bounds__(256) mx_fast_kernel(const QArgs a)
         mx = h2_bits(__hmax2(bits_h2(mx), bits_h2(__shfl_xor_sync(0xFFFFFFFFu, mx, off))));
     const uint32_t am16 = max(mx & 0xFFFFu, mx >> 16);
 
-    uint32_t sb;                       // fp16 pattern of the shared scale
     __half2 y[4];
     if (a.f.sc_mbit == 0) {
         int g;                         // floor|round(log2(absmax)) as the reference's fp16 tensor op gives it
@@ -319,8 +279,6 @@ __global__ void __launch_bounds__(256) mx_fast_kernel(const QArgs a)
     }
     const __half2 s2 = bits_h2(sb * 0x00010001u);
 
-    __half2 d[4];
-    uint32_t mag[4], sg[4];
     #pragma unroll
     for (int p = 0; p < 4; ++p) {
         __half2 q;
@@ -342,6 +300,57 @@ __global__ void __launch_bounds__(256) mx_fast_kernel(const QArgs a)
         }
         d[p] = __hmul2(q, s2);
     }
+}
+
+// LEAN: the tensor is contiguous, 16-byte aligned, K a multiple of the block, and only the
+//        fake-quantised output is wanted: chunk ci is elements [8 ci, 8 ci + 8) of both tensors, so
+//        the row / column bookkeeping, RoPE / permutation and side outputs drop out.
+__device__ __forceinline__ Chunk lean_load(const QArgs& a, int64_t ci)
+{
+    const uint4 v = __ldg(reinterpret_cast<const uint4*>(a.x) + ci);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    Chunk c;
+    if (!a.in_bf16) {
+        #pragma unroll
+        for (int p = 0; p < 4; ++p) c.h[p] = bits_h2(w[p]);
+    } else {
+        #pragma unroll
+        for (int p = 0; p < 4; ++p)
+            c.h[p] = __floats2half2_rn(__uint_as_float(w[p] << 16), __uint_as_float(w[p] & 0xFFFF0000u));
+    }
+    return c;
+}
+
+template <int KIND, int MB, bool CODES, bool LEAN>
+__global__ void __launch_bounds__(256) mx_fast_kernel(const QArgs a)
+{
+    // Grid-stride loop with the next chunk's load issued before the current one is processed, so
+    // every thread keeps a 16-byte load in flight while it computes.
+    const int lane = threadIdx.x & 31;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    int64_t ci = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    int64_t row = 0, c = 0;
+    if (!LEAN) split_chunk(a, ci < a.total_chunks ? ci : 0, row, c);
+    Chunk x;
+    if (ci < a.total_chunks) x = LEAN ? lean_load(a, ci) : load_chunk(a, row, c * 8);
+    else { for (int p = 0; p < 4; ++p) x.h[p] = bits_h2(0u); }
+    for (; ci - lane < a.total_chunks; ci += stride) {
+    const bool valid = ci < a.total_chunks;
+    const int64_t k0 = c * 8;
+    const int64_t row_cur = row, c_cur = c;
+    // advance (row, chunk-in-row) by one grid stride and prefetch
+    if (!LEAN) {
+        row += a.step_rows; c += a.step_chunks;
+        if (c >= a.cpr) { c -= a.cpr; ++row; }
+    }
+    Chunk xn;
+    if (ci + stride < a.total_chunks) xn = LEAN ? lean_load(a, ci + stride) : load_chunk(a, row, c * 8);
+    else { for (int p = 0; p < 4; ++p) xn.h[p] = bits_h2(0u); }
+
+    if (!LEAN && a.rope_cos) rope_chunk(a, x, valid ? row_cur : 0, k0);
+    __half2 d[4];
+    uint32_t mag[4], sg[4], sb;
+    mx_fast_chunk<KIND, MB, CODES>(a, x, d, mag, sg, sb);
     if (LEAN) {
         if (valid) {
             uint32_t w[4];
@@ -370,6 +379,47 @@ __global__ void __launch_bounds__(256) mx_fast_kernel(const QArgs a)
     }
     x = xn;
     }   // grid-stride loop
+}
+
+// V-cache write for the MX / NV fast-path formats: blocks of block_size consecutive tokens per channel,
+// through the shared-memory tile of vcache_dev.cuh.
+template <int KIND, int MB>
+struct MxChunkFn {
+    const QArgs& a;
+    __device__ __forceinline__ void operator()(const uint32_t* xb, uint32_t* dq) const
+    {
+        Chunk x;
+        #pragma unroll
+        for (int p = 0; p < 4; ++p) x.h[p] = bits_h2(xb[p]);
+        __half2 d[4];
+        uint32_t mag[4], sg[4], sb;
+        mx_fast_chunk<KIND, MB, false>(a, x, d, mag, sg, sb);
+        #pragma unroll
+        for (int p = 0; p < 4; ++p) dq[p] = h2_bits(d[p]);
+    }
+};
+
+template <int KIND, int MB>
+__global__ void __launch_bounds__(V_THREADS, 2) mx_v_kernel(const QArgs a, const VArgs v)
+{
+    extern __shared__ __align__(16) uint32_t v_tile[];
+    const MxChunkFn<KIND, MB> fn = {a};
+    v_cache_tiles(v, v_tile, fn);
+}
+
+template <int KIND, int MB>
+static int launch_mx_v(const QArgs& a, const KvWriteOpts* kv, cudaStream_t stream)
+{
+    VArgs v;
+    if (!v_args_fill(&v, a.x, a.deq, a.in_bf16, a.out_bf16, kv->B, kv->T, kv->H, kv->D, a.f.block_size)) return HBQ_ERR_UNSUPPORTED;
+    if (v.tiles == 0) return HBQ_OK;
+    int dev = 0, sms = 0;
+    HBQ_CUDA_TRY(cudaGetDevice(&dev));
+    HBQ_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    const int grid = (int)(v.tiles < 2 * sms ? v.tiles : 2 * sms);
+    mx_v_kernel<KIND, MB><<<grid, V_THREADS, V_TILE_BYTES, stream>>>(a, v);
+    HBQ_LAUNCH_CHECK("mx_v_kernel");
+    return HBQ_OK;
 }
 
 // ------------------------------------------------------------------------------------------
@@ -717,7 +767,7 @@ int quantize_launch(const void* x, int dtype, int64_t rows, int64_t K, const hbq
     a.f = *f;
     a.f.per_tensor_scale = pts;
     if (kv) {
-        if (K % B != 0 || !is_pow2((int)K) || K < 16 || K > 256 || pts || (kv->v_axis && f->kind != HBQ_KIND_HBQ)) return HBQ_ERR_UNSUPPORTED;
+        if (K % B != 0 || !is_pow2((int)K) || K < 16 || K > 256 || pts) return HBQ_ERR_UNSUPPORTED;
         if (kv->cos && (dtype != HBQ_DTYPE_F16 || !kv->sin || kv->rope_rows <= 0)) return HBQ_ERR_UNSUPPORTED;
         if (!deq) return HBQ_ERR_ARG;
         a.rope_cos = (const uint16_t*)kv->cos; a.rope_sin = (const uint16_t*)kv->sin; a.rope_rows = kv->rope_rows;
@@ -748,10 +798,12 @@ int quantize_launch(const void* x, int dtype, int64_t rows, int64_t K, const hbq
             const float qmax = (float)((1 << (f->mbit - 1)) - 1);
             a.int_lim_pos = (uint32_t)__half_as_ushort(__float2half_rn(qmax)) * 0x00010001u;
             a.int_lim_neg = (uint32_t)__half_as_ushort(__float2half_rn(qmax + 1.f)) * 0x00010001u;
+            if (kv && kv->v_axis) return launch_mx_v<HBQ_KIND_MXINT, 0>(a, kv, stream);
             launch_mx_fast<HBQ_KIND_MXINT, 0>(a, grid, block, stream);
             HBQ_LAUNCH_CHECK("mx_fast_kernel<mxint>");
             return HBQ_OK;
         }
+        if (kv && kv->v_axis) return HBQ_ERR_UNSUPPORTED;      // token-axis write: fast-path formats only
         mx_quantize_kernel<HBQ_KIND_MXINT, 0><<<grid, block, 0, stream>>>(a);
         HBQ_LAUNCH_CHECK("mx_quantize_kernel<mxint>");
         return HBQ_OK;
@@ -777,6 +829,14 @@ int quantize_launch(const void* x, int dtype, int64_t rows, int64_t K, const hbq
             if (f->sc_mbit == 0) build_pot_table(f->use_round != 0, a.pot_thr);
             for (int i = 0; i < 8; ++i) a.rm[i] = __half_as_ushort(__float2half_rn(1.f / (1.f + i / 8.f)));
             a.inv_elem_max = 1.f / a.elem_max;
+            if (kv && kv->v_axis) {
+                switch (fast_mb) {
+                    case 1: return launch_mx_v<HBQ_KIND_MXFP, 1>(a, kv, stream);
+                    case 2: return launch_mx_v<HBQ_KIND_MXFP, 2>(a, kv, stream);
+                    case 3: return launch_mx_v<HBQ_KIND_MXFP, 3>(a, kv, stream);
+                    default: return launch_mx_v<HBQ_KIND_MXFP, 5>(a, kv, stream);
+                }
+            }
             switch (fast_mb) {
                 case 1: launch_mx_fast<HBQ_KIND_MXFP, 1>(a, grid, block, stream); break;
                 case 2: launch_mx_fast<HBQ_KIND_MXFP, 2>(a, grid, block, stream); break;
@@ -786,6 +846,7 @@ int quantize_launch(const void* x, int dtype, int64_t rows, int64_t K, const hbq
             HBQ_LAUNCH_CHECK("mx_fast_kernel<mxfp>");
             return HBQ_OK;
         }
+        if (kv && kv->v_axis) return HBQ_ERR_UNSUPPORTED;
         switch (fast_mb) {
             case 1: mx_quantize_kernel<HBQ_KIND_MXFP, 1><<<grid, block, 0, stream>>>(a); break;
             case 2: mx_quantize_kernel<HBQ_KIND_MXFP, 2><<<grid, block, 0, stream>>>(a); break;

@@ -42,6 +42,7 @@ def quantizers():
         "hbq_b64": lambda: Hq.HBQQuantizer(64, 2, 3, 5, 3, l2_block_size=8, l2_sc_bit=2, l2_scheme="INT"),
         "hbq_sig1_b32": lambda: Hq.HBQQuantizer(32, 2, 2, 5, 3, l2_block_size=8, l2_sc_bit=2, l2_scheme="SIG-1"),
         "mxfp4_b32": lambda: Hq.MXFPQuantizer(32, 2, 1, 8, 0),
+        "mxfp4_e5_b32": lambda: Hq.MXFPQuantizer(32, 2, 1, 5, 0),        # config/mxfp4.yaml
         "nvfp4_b16": lambda: Hq.MXFPQuantizer(16, 2, 1, 5, 3),
         "mxfp8ish_b32": lambda: Hq.MXFPQuantizer(32, 2, 5, 5, 0),
         "mxint8_b32": lambda: Hq.MXINTQuantizer(8, 5, 0, 32),
@@ -108,7 +109,8 @@ def test_k_write_no_rope_bf16_and_empty():
     assert e.shape == (B, H, 0, D)
 
 
-@pytest.mark.parametrize("name", ["hbq_a_sig1_l8", "hbq_e_fp1_l32", "hbq_sig1_b32", "hbq_b64", "mxfp4_b32"])
+@pytest.mark.parametrize("name", ["hbq_a_sig1_l8", "hbq_e_fp1_l32", "hbq_sig1_b32", "hbq_b64", "mxfp4_b32",
+                                  "mxfp4_e5_b32", "nvfp4_b16", "mxfp8ish_b32", "mxint8_b32"])
 @pytest.mark.parametrize("T", [1, 128, 300])
 def test_v_write_matches_unfused(name, T):
     from hbq_b200 import kvcache
@@ -116,8 +118,9 @@ def test_v_write_matches_unfused(name, T):
     q = quantizers()[name]()
     v = torch.from_numpy(seeded_inputs("act", B * T, H * D, seed=T).astype(np.float16)).cuda().view(B, T, H * D)
     got = kvcache.write_v_cache(v, H, q)
-    # the token-axis kernel serves the table-driven HBQ formats; the others run the three steps
-    assert kvcache.fused_last == (name in ("hbq_a_sig1_l8", "hbq_e_fp1_l32", "hbq_sig1_b32"))
+    # the token-axis kernels serve the table-driven HBQ formats and the MX / NV fast-path formats;
+    # the others (8-bit scale exponent, E2M3 with an INT table) run the three steps
+    assert kvcache.fused_last == (name not in ("hbq_b64", "mxfp4_b32"))
     x = v.view(B, T, H, D).transpose(1, 2)                                  # [B,H,T,D]
     want = q.q(x.transpose(-1, -2).contiguous()).transpose(-1, -2).contiguous()      # src/module.py:163-168
     assert got.shape == (B, H, T, D)
