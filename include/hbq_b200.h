@@ -125,7 +125,8 @@ int hbq_kv_write_k(const void* k, int dtype, int64_t B, int64_t T, int64_t H, in
 /* V-cache write (src/module.py:163-168): v is the v_proj output viewed [B,T,H,D]; blocks of
  * fmt->block_size consecutive TOKENS per (batch, head, channel) are quantised (the tail block
  * zero padded) and the result is stored as [B,H,T,D] -- the reference's transpose, quantise,
- * transpose back.  HBQ formats with one table, D a multiple of 64, block_size <= 128. */
+ * transpose back.  Served formats: HBQ with one candidate table, MXFP / NVFP E2Mx and MXINT with a
+ * scale inside fp16's range; D a multiple of 64, block_size 16..128.  HBQ_ERR_UNSUPPORTED otherwise. */
 int hbq_kv_write_v(const void* v, int dtype, int64_t B, int64_t T, int64_t H, int64_t D,
                    const hbq_format* fmt, void* out, int out_dtype, void* stream);
 
