@@ -10,6 +10,9 @@ import torch.nn.functional as F
 from .quantizer import PackedTensor, _QBase, dequantize_packed
 
 
+_HOST_PIPES = {}      # device -> streams and staging buffers of forward_host
+
+
 class QLinear(nn.Linear):
     """y = yq(ops(aq(x), W, b)); W is expected to be fake-quantised already (static weight
     quantisation, src/ptq.py:337-382).  ``ops=None`` uses ``F.linear`` like the reference
@@ -24,7 +27,6 @@ class QLinear(nn.Linear):
         self.yq = _QBase()
         self.ops = ops
         self.check_finite = check_finite
-        self._host_pipe = None
         self.packed_weight = None
 
     def forward(self, x: torch.Tensor):
@@ -85,10 +87,11 @@ class QLinear(nn.Linear):
         rows = x_host.shape[0]
         if out_host is None:
             out_host = torch.empty((rows, self.out_features), dtype=self.weight.dtype, pin_memory=True)
-        if self._host_pipe is None or self._host_pipe["dev"] != dev:
-            self._host_pipe = {"dev": dev, "h2d": torch.cuda.Stream(dev), "comp": torch.cuda.Stream(dev),
-                               "d2h": torch.cuda.Stream(dev), "xbuf": [None, None], "x_free": [None, None], "n": 0}
-        P = self._host_pipe
+        P = _HOST_PIPES.get(dev)
+        if P is None:
+            # one set of streams and staging buffers per device, shared by every layer
+            P = _HOST_PIPES[dev] = {"h2d": torch.cuda.Stream(dev), "comp": torch.cuda.Stream(dev),
+                                    "d2h": torch.cuda.Stream(dev), "xbuf": [None, None], "x_free": [None, None], "n": 0}
         h2d, comp, d2h = P["h2d"], P["comp"], P["d2h"]
         cur = torch.cuda.current_stream(dev)
         start = torch.cuda.Event()
@@ -105,9 +108,10 @@ class QLinear(nn.Linear):
                 if P["x_free"][slot] is not None:
                     h2d.wait_event(P["x_free"][slot])          # the kernels that read this buffer are done
                 xb = P["xbuf"][slot]
-                if xb is None or xb.shape[0] < r1 - r0 or xb.dtype != x_host.dtype:
-                    xb = P["xbuf"][slot] = torch.empty((step, self.in_features), dtype=x_host.dtype, device=dev)
-                xv = xb[: r1 - r0]
+                need = (r1 - r0) * self.in_features
+                if xb is None or xb.numel() < need or xb.dtype != x_host.dtype:
+                    xb = P["xbuf"][slot] = torch.empty(step * self.in_features, dtype=x_host.dtype, device=dev)
+                xv = xb[:need].view(r1 - r0, self.in_features)
                 xv.copy_(x_host[r0:r1], non_blocking=True)
                 up = torch.cuda.Event()
                 up.record(h2d)
