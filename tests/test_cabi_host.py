@@ -41,6 +41,29 @@ def test_no_cpu_fallback():
         H.HBQQuantizer().q(torch.zeros(2, 128, dtype=torch.float16))
     with pytest.raises(RuntimeError):
         H.blockquant_ext.gemm_fp32_accum(torch.zeros(2, 8, dtype=torch.float16), torch.zeros(8, 4, dtype=torch.float16))
+    for q in (H.MXExQuantizer(), H.VSQQuantizer(4), H.MXFPQuantizer(), H.MXINTQuantizer(8)):
+        with pytest.raises(H.HbqError):
+            q.q(torch.zeros(2, 64, dtype=torch.float16))
+    with pytest.raises(H.HbqError):
+        H.write_k_cache(torch.zeros(1, 4, 256, dtype=torch.float16), 2, H.HBQQuantizer())
+    with pytest.raises(H.HbqError):
+        H.write_v_cache(torch.zeros(1, 4, 256, dtype=torch.float16), 2, H.HBQQuantizer())
+
+
+def test_kvcache_argument_checks():
+    torch = pytest.importorskip("torch")
+    from hbq_b200 import kvcache
+    x = torch.arange(8, dtype=torch.float16).view(1, 1, 1, 8)
+    assert kvcache.rotate_half(x).flatten().tolist() == [-4, -5, -6, -7, 0, 1, 2, 3]
+    with pytest.raises(ValueError):
+        kvcache._head_dim(torch.zeros(1, 4, 250), 4)                 # H does not divide the last axis
+    assert kvcache._head_dim(torch.zeros(2, 4, 8, 16), 8) == 16 and kvcache._head_dim(torch.zeros(2, 4, 128), 8) == 16
+    cos = torch.zeros(1, 4, 16)
+    with pytest.raises(ValueError):
+        kvcache._tables(cos, torch.zeros(1, 4, 8), 2, 4, 16)         # cos / sin shapes differ
+    with pytest.raises(ValueError):
+        kvcache._tables(torch.zeros(3, 4, 16), torch.zeros(3, 4, 16), 2, 4, 16)   # batch neither 1 nor B
+    assert kvcache._tables(cos, cos, 2, 4, 16)[2] == 4 and kvcache._tables(cos.expand(2, 4, 16), cos.expand(2, 4, 16), 2, 4, 16)[2] == 8
 
 
 HBQ_E_PSUM_YAML = """
