@@ -81,6 +81,27 @@ def lib() -> ctypes.CDLL:
     return L
 
 
+class _NoGuard:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_GUARD = _NoGuard()
+
+
+def device_guard(device):
+    """``torch.cuda.device(device)`` when ``device`` is not the current one, else nothing: the context
+    manager costs several microseconds, which is most of a decode-sized kernel."""
+    import torch
+    idx = device.index
+    if idx is None or idx == torch.cuda.current_device():
+        return _NO_GUARD
+    return torch.cuda.device(device)
+
+
 def check(rc: int, what: str) -> None:
     if rc != 0:
         L = lib()

@@ -1,6 +1,7 @@
 // C ABI of the library (declared in include/hbq_b200.h) and the packed-code dequantizer.
 #include "common.cuh"
 #include <atomic>
+#include <mutex>
 #include <cstring>
 #include <cstdio>
 #include <math.h>
@@ -16,6 +17,27 @@ int set_cuda_error(cudaError_t e, const char* where)
 {
     snprintf(g_last_cuda_error, sizeof(g_last_cuda_error), "%s: %s", where, cudaGetErrorString(e));
     return HBQ_ERR_CUDA;
+}
+
+// (kernel, device) -> largest dynamic shared-memory size already granted
+struct SmemGrant { const void* kernel; int dev; size_t bytes; };
+static SmemGrant g_grants[256];
+static int g_ngrants = 0;
+static std::mutex g_grant_mutex;
+
+int ensure_dynamic_smem_impl(const void* kernel, size_t bytes)
+{
+    int dev = 0;
+    HBQ_CUDA_TRY(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(g_grant_mutex);
+    SmemGrant* slot = nullptr;
+    for (int i = 0; i < g_ngrants; ++i)
+        if (g_grants[i].kernel == kernel && g_grants[i].dev == dev) { slot = &g_grants[i]; break; }
+    if (slot && slot->bytes >= bytes) return HBQ_OK;
+    HBQ_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+    if (!slot && g_ngrants < 256) slot = &g_grants[g_ngrants++];
+    if (slot) *slot = {kernel, dev, bytes};
+    return HBQ_OK;
 }
 
 // implemented in quantize.cu / gemm_simt.cu / gemm_tc.cu

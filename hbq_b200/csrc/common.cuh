@@ -4,6 +4,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <atomic>
 #include "../../include/hbq_b200.h"
 
 namespace hbq {
@@ -35,6 +36,35 @@ struct KvWriteOpts {
         if (_e != cudaSuccess) return ::hbq::set_cuda_error(_e, what);         \
         ::hbq::note_launch();                                                  \
     } while (0)
+
+// Host-side per-device caches: the launch paths run tens of thousands of times per second for
+// decode-sized tensors, so nothing that can be looked up once is asked of the runtime per call.
+constexpr int kMaxDevices = 64;
+
+// Current device and its SM count.
+inline int device_sms(int* sms)
+{
+    static std::atomic<int> cached[kMaxDevices];
+    int dev = 0;
+    HBQ_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return HBQ_ERR_DEVICE;
+    int v = cached[dev].load(std::memory_order_relaxed);
+    if (v == 0) {
+        HBQ_CUDA_TRY(cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev));
+        cached[dev].store(v, std::memory_order_relaxed);
+    }
+    *sms = v;
+    return HBQ_OK;
+}
+
+// Raise a kernel's dynamic shared-memory limit to `bytes` on the current device, once per kernel,
+// device and size (api.cu keeps the table, keyed by the kernel's address).
+int ensure_dynamic_smem_impl(const void* kernel, size_t bytes);
+template <class Kernel>
+inline int ensure_dynamic_smem(Kernel kernel, size_t bytes)
+{
+    return ensure_dynamic_smem_impl(reinterpret_cast<const void*>(kernel), bytes);
+}
 
 __device__ __forceinline__ uint32_t h2_bits(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
 __device__ __forceinline__ __half2 bits_h2(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }

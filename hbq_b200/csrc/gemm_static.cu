@@ -23,7 +23,6 @@ int transpose_launch(const void*, void*, int64_t, int64_t, cudaStream_t);
 // address obtained from it is what the kernels receive.
 static __device__ __align__(256) __half g_bt_scratch[HBQ_GEMM_NOALLOC_MAX_ELEMS];
 
-constexpr int kMaxDevices = 64;
 static void* g_scratch_ptr[kMaxDevices];
 static std::mutex g_scratch_mutex;
 

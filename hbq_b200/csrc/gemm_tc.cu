@@ -27,6 +27,7 @@
 #include <cuda.h>
 #include <math.h>
 #include <stdlib.h>
+#include <mutex>
 
 namespace hbq {
 
@@ -602,8 +603,24 @@ static EncodeTiledFn encode_fn()
 }
 
 // fp16 row-major [rows, K] matrix, boxes of box_rows x 64 elements, 128-byte swizzle, zero fill
+// Tensor maps depend on (pointer, rows, K, box) only and a serving loop presents the same few operands
+// (the weights above all) again and again: a small cache saves the driver call.
+struct MapKey { const void* ptr; int64_t rows, K; int box_rows; };
+struct MapSlot { MapKey key; CUtensorMap map; bool used; };
+static MapSlot g_map_cache[64];
+static std::mutex g_map_mutex;
+
 static int make_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t K, int box_rows)
 {
+    const size_t h = ((reinterpret_cast<uintptr_t>(ptr) >> 8) * 0x9E3779B97F4A7C15ull ^ (size_t)rows * 31u ^ (size_t)K ^ (size_t)box_rows) >> 58;
+    {
+        std::lock_guard<std::mutex> lock(g_map_mutex);
+        const MapSlot& s = g_map_cache[h & 63];
+        if (s.used && s.key.ptr == ptr && s.key.rows == rows && s.key.K == K && s.key.box_rows == box_rows) {
+            *map = s.map;
+            return HBQ_OK;
+        }
+    }
     EncodeTiledFn fn = encode_fn();
     if (!fn) return HBQ_ERR_CUDA;
     const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
@@ -613,7 +630,13 @@ static int make_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t K, 
     const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? HBQ_OK : HBQ_ERR_CUDA;
+    if (r != CUDA_SUCCESS) return HBQ_ERR_CUDA;
+    std::lock_guard<std::mutex> lock(g_map_mutex);
+    MapSlot& s = g_map_cache[h & 63];
+    s.key = {ptr, rows, K, box_rows};
+    s.map = *map;
+    s.used = true;
+    return HBQ_OK;
 }
 
 bool gemm_tc_eligible(int64_t M, int64_t N, int64_t K, int mode, int group_k, int group_n)
@@ -630,8 +653,7 @@ bool gemm_tc_eligible(int64_t M, int64_t N, int64_t K, int mode, int group_k, in
 template <int MODE, int GN>
 static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcArgs& args, int grid, cudaStream_t stream)
 {
-    // per device, and cheap: set on every launch rather than caching per process
-    HBQ_CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel<MODE, GN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    { const int rc = ensure_dynamic_smem(gemm_tc_kernel<MODE, GN>, SMEM_BYTES); if (rc) return rc; }
     gemm_tc_kernel<MODE, GN><<<grid, NTHREADS, SMEM_BYTES, stream>>>(ma, mb, args);
     HBQ_LAUNCH_CHECK("gemm_tc_kernel");
     return HBQ_OK;
@@ -671,9 +693,8 @@ int gemm_tc_launch(const void* A, const void* W, void* C, int64_t M, int64_t N, 
         args.issuers = issuers;
     }
 
-    int dev = 0, sms = 0;
-    HBQ_CUDA_TRY(cudaGetDevice(&dev));
-    HBQ_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    int sms = 0;
+    { const int rc2 = device_sms(&sms); if (rc2) return rc2; }
     const int64_t total = (int64_t)args.tiles_m * args.tiles_n;
     const int grid = (int)(total < sms ? total : sms);
 

@@ -413,10 +413,10 @@ static int launch_mx_v(const QArgs& a, const KvWriteOpts* kv, cudaStream_t strea
     VArgs v;
     if (!v_args_fill(&v, a.x, a.deq, a.in_bf16, a.out_bf16, kv->B, kv->T, kv->H, kv->D, a.f.block_size)) return HBQ_ERR_UNSUPPORTED;
     if (v.tiles == 0) return HBQ_OK;
-    int dev = 0, sms = 0;
-    HBQ_CUDA_TRY(cudaGetDevice(&dev));
-    HBQ_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    int sms = 0;
+    { const int rc = device_sms(&sms); if (rc) return rc; }
     const int grid = (int)(v.tiles < 2 * sms ? v.tiles : 2 * sms);
+    { const int rc = ensure_dynamic_smem(mx_v_kernel<KIND, MB>, V_TILE_BYTES); if (rc) return rc; }
     mx_v_kernel<KIND, MB><<<grid, V_THREADS, V_TILE_BYTES, stream>>>(a, v);
     HBQ_LAUNCH_CHECK("mx_v_kernel");
     return HBQ_OK;
@@ -719,8 +719,8 @@ template <int KIND, int MB>
 static void launch_mx_fast(QArgs& a, dim3 grid, dim3 block, cudaStream_t stream)
 {
     // at most 8 CTAs of 256 threads per SM (a full complement of warps), each looping over chunks
-    int dev = 0, sms = 148;
-    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    int sms = 148;
+    device_sms(&sms);
     if ((int64_t)grid.x > (int64_t)sms * 8) grid.x = (unsigned)(sms * 8);
     const int64_t stride = (int64_t)grid.x * block.x;
     a.step_rows = stride / a.cpr;

@@ -22,6 +22,7 @@ namespace hbq {
 
 constexpr int LUT_MAX_CAND = 4;
 constexpr int LUT_MAX_LEVELS = 32;
+constexpr int LUT_MAX_SEG = 192;
 
 struct LutPlan {
     int nlev;                                   // 2^(mbit+2) magnitudes of E2M<mbit>
@@ -31,6 +32,10 @@ struct LutPlan {
     uint16_t zmax[LUT_MAX_CAND];                // largest |a| pattern with fp16(a / t_i) == 0
     uint16_t hole[LUT_MAX_CAND][4];             // E2M1: |a| patterns with fp16(a / t_i) == 0x39FF (value 0)
     int nhole[LUT_MAX_CAND];
+    // the table is piecewise constant: sorted first patterns of its runs (every threshold of every
+    // candidate, and both edges of every hole), so a CTA fills it run by run
+    int nseg;
+    uint16_t seg_start[LUT_MAX_SEG];
 };
 
 // ---- exact host-side scalar arithmetic on fp16 patterns ------------------------------------------
@@ -120,7 +125,28 @@ bool lut_plan_build(int mb, const float* tab, int nc, LutPlan* p)
     }
     p->base = lo - 1;
     p->hi = hi;
-    return p->base >= 1 && (p->hi - p->base + 1) <= 8191;   // byte offsets of the entries must fit 16 bits
+    if (!(p->base >= 1 && (p->hi - p->base + 1) <= 8191)) return false;   // byte offsets of the entries must fit 16 bits
+    // run starts inside [base, hi], sorted and unique
+    int cand[LUT_MAX_CAND * (LUT_MAX_LEVELS + 8) + 1], nb = 0;
+    cand[nb++] = p->base;
+    for (int i = 0; i < LUT_MAX_CAND; ++i) {
+        for (int k = 1; k < p->nlev; ++k) cand[nb++] = p->thr[i][k];
+        for (int h = 0; h < p->nhole[i]; ++h) { cand[nb++] = p->hole[i][h]; cand[nb++] = p->hole[i][h] + 1; }
+    }
+    for (int i = 1; i < nb; ++i) {                      // insertion sort, a few hundred values at most
+        const int v = cand[i];
+        int j = i - 1;
+        while (j >= 0 && cand[j] > v) { cand[j + 1] = cand[j]; --j; }
+        cand[j + 1] = v;
+    }
+    p->nseg = 0;
+    for (int i = 0; i < nb; ++i) {
+        if (cand[i] < p->base || cand[i] > p->hi) continue;
+        if (p->nseg > 0 && p->seg_start[p->nseg - 1] == (uint16_t)cand[i]) continue;
+        if (p->nseg == LUT_MAX_SEG) return false;
+        p->seg_start[p->nseg++] = (uint16_t)cand[i];
+    }
+    return true;
 }
 
 
@@ -139,6 +165,7 @@ struct LutArgs {
 };
 
 constexpr int LUT_THREADS = 512;
+static_assert(sizeof(LutArgs) <= 4000, "kernel parameters are limited to 4 KB");
 
 // acc_lo += lo(e), acc_hi += hi(e): fp32 accumulation of two fp16 values (one rounding each)
 __device__ __forceinline__ void add2_f32_f16(float& acc_lo, float& acc_hi, uint32_t e)
@@ -149,34 +176,48 @@ __device__ __forceinline__ void add2_f32_f16(float& acc_lo, float& acc_hi, uint3
 }
 
 // Build the candidate table: entry e covers |a| pattern base + e and holds the 4 candidates' values.
-// Each thread walks its entries in increasing order, so every candidate's level only moves up.  Ends
-// without a barrier: callers synchronise before the first lookup.
+// The table is piecewise constant (a run per threshold of any candidate), so the runs' values are found
+// first and then copied out.  Ends without a barrier: callers synchronise before the first lookup.
 template <int MB>
 __device__ __forceinline__ void lut_build(const LutArgs& a, uint2* lut, int tid, int nthreads)
 {
-    __shared__ uint16_t s_thr[LUT_MAX_CAND][LUT_MAX_LEVELS + 1], s_val[LUT_MAX_CAND][LUT_MAX_LEVELS];
-    for (int i = tid; i < LUT_MAX_CAND * LUT_MAX_LEVELS; i += nthreads) {
-        const int c = i / LUT_MAX_LEVELS, k = i % LUT_MAX_LEVELS;
-        s_thr[c][k] = (k >= 1 && k < a.plan.nlev) ? a.plan.thr[c][k] : (uint16_t)0xFFFF;
-        s_val[c][k] = a.plan.val[c][k];
-        if (k == 0) s_thr[c][LUT_MAX_LEVELS] = 0xFFFF;
-    }
-    __syncthreads();
-    const int n = a.plan.hi - a.plan.base + 1;
-    int lvl[LUT_MAX_CAND] = {0, 0, 0, 0};
-    for (int e = tid; e < n; e += nthreads) {                 // increasing e: every level only moves up
-        const uint32_t u = (uint32_t)(a.plan.base + e);
+    __shared__ uint16_t s_seg[LUT_MAX_SEG + 1];
+    __shared__ uint2 s_segval[LUT_MAX_SEG];
+    // the value of every run: one thread per run finds each candidate's level at the run's first pattern
+    for (int sidx = tid; sidx < a.plan.nseg; sidx += nthreads) {
+        const uint32_t u = a.plan.seg_start[sidx];
         uint32_t v[LUT_MAX_CAND];
         #pragma unroll
         for (int i = 0; i < LUT_MAX_CAND; ++i) {
-            while (u >= s_thr[i][lvl[i] + 1]) ++lvl[i];
-            uint32_t val = s_val[i][lvl[i]];
+            int lvl = 0;
+            for (int k = 1; k < a.plan.nlev; ++k) lvl += (u >= a.plan.thr[i][k]) ? 1 : 0;     // thresholds are sorted
+            uint32_t val = a.plan.val[i][lvl];
             if (MB == 1)
                 for (int h = 0; h < a.plan.nhole[i]; ++h)
                     if (u == a.plan.hole[i][h]) val = 0;
             v[i] = val;
         }
-        lut[e] = make_uint2(v[0] | (v[1] << 16), v[2] | (v[3] << 16));
+        s_seg[sidx] = (uint16_t)u;
+        s_segval[sidx] = make_uint2(v[0] | (v[1] << 16), v[2] | (v[3] << 16));
+    }
+    if (tid == 0) s_seg[a.plan.nseg] = 0xFFFF;
+    __syncthreads();
+    // fill: a thread takes consecutive entries, finds the run of its first one and walks on from there
+    const int n = a.plan.hi - a.plan.base + 1;
+    const int per = (n + nthreads - 1) / nthreads;
+    const int e0 = tid * per, e1 = min(n, e0 + per);
+    if (e0 < e1) {
+        const uint32_t u0 = (uint32_t)(a.plan.base + e0);
+        int lo = 0, hi = a.plan.nseg - 1;                     // largest run start <= u0 (run 0 starts at base)
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (s_seg[mid] <= u0) lo = mid; else hi = mid - 1;
+        }
+        int sidx = lo;
+        for (int e = e0; e < e1; ++e) {
+            while ((uint32_t)(a.plan.base + e) >= s_seg[sidx + 1]) ++sidx;
+            lut[e] = s_segval[sidx];
+        }
     }
 }
 
@@ -313,8 +354,6 @@ __global__ void __launch_bounds__(LUT_THREADS, 2) hbq_lut_kernel(const LutArgs a
     const QArgs& q = a.q;
     const int tid = threadIdx.x;
 
-    // -- build the table: entry e covers |a| pattern base + e and holds the 4 candidates' values.
-    //    Each thread walks its entries in increasing order, so every candidate's level only moves up.
     lut_build<MB>(a, lut, tid, LUT_THREADS);
     __syncthreads();
 
@@ -568,7 +607,7 @@ template <int MB>
 static int launch_lean(const LutArgs& a, int grid, size_t smem, cudaStream_t stream)
 {
     #define HBQ_LAUNCH_LEAN(IB, OB, KVW)                                                                                              \
-        HBQ_CUDA_TRY(cudaFuncSetAttribute(hbq_lut_lean_kernel<MB, IB, OB, KVW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        { const int rc_ = ensure_dynamic_smem(hbq_lut_lean_kernel<MB, IB, OB, KVW>, smem); if (rc_) return rc_; }                    \
         hbq_lut_lean_kernel<MB, IB, OB, KVW><<<grid, LEAN_THREADS, smem, stream>>>(a);
     const bool kvw = a.q.rope_cos || a.q.perm_T > 0;
     if (kvw) { if (a.q.out_bf16) { HBQ_LAUNCH_LEAN(false, true, true) } else { HBQ_LAUNCH_LEAN(false, false, true) } }
@@ -619,17 +658,26 @@ struct CachedPlan {
     float tab[LUT_MAX_CAND];
     bool ok;
     LutPlan plan;
+    uint16_t rm[8], rt[LUT_MAX_CAND], big_l1;       // derived kernel arguments (see LutArgs)
 };
 static std::mutex g_plan_mutex;
 static std::vector<CachedPlan> g_plans;
 
 // Plans depend on the format only; building one costs ~2000 scalar quantizer evaluations.
-static bool get_plan(int mb, const float* tab, int nc, LutPlan* out)
+static void plan_to_args(const CachedPlan& c, LutArgs* a)
+{
+    a->plan = c.plan;
+    memcpy(a->rm, c.rm, sizeof(c.rm));
+    memcpy(a->rt, c.rt, sizeof(c.rt));
+    a->big_l1 = c.big_l1;
+}
+
+static bool get_plan(int mb, const float* tab, int nc, LutArgs* out)
 {
     std::lock_guard<std::mutex> lock(g_plan_mutex);
     for (const CachedPlan& c : g_plans)
         if (c.mb == mb && c.nc == nc && memcmp(c.tab, tab, sizeof(float) * nc) == 0) {
-            if (c.ok) *out = c.plan;
+            if (c.ok) plan_to_args(c, out);
             return c.ok;
         }
     CachedPlan c;
@@ -637,8 +685,20 @@ static bool get_plan(int mb, const float* tab, int nc, LutPlan* out)
     c.mb = mb; c.nc = nc;
     memcpy(c.tab, tab, sizeof(float) * nc);
     c.ok = lut_plan_build(mb, tab, nc, &c.plan);
+    if (c.ok) {
+        for (int i = 0; i < 8; ++i) c.rm[i] = d2h(1.0 / (1.0 + i / 8.0));
+        double vmax = 0;
+        for (int i = 0; i < LUT_MAX_CAND; ++i) {
+            c.rt[i] = d2h(1.0 / (double)tab[i < nc ? i : nc - 1]);
+            const double v = h2d(c.plan.val[i][c.plan.nlev - 1]);
+            if (v > vmax) vmax = v;
+        }
+        c.big_l1 = 0x7C00;                     // smallest scale whose product with the largest value overflows fp16
+        for (int pat = 0x0400; pat <= 0x7B80; pat += 0x80)
+            if (h2d((uint16_t)pat) * vmax > 65504.0) { c.big_l1 = (uint16_t)pat; break; }
+    }
     if (g_plans.size() < 64) g_plans.push_back(c);
-    if (c.ok) *out = c.plan;
+    if (c.ok) plan_to_args(c, out);
     return c.ok;
 }
 
@@ -646,10 +706,10 @@ template <int MB>
 static int launch_lut(const LutArgs& a, bool codes, int grid, size_t smem, cudaStream_t stream)
 {
     if (codes) {
-        HBQ_CUDA_TRY(cudaFuncSetAttribute(hbq_lut_kernel<MB, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        { const int rc_ = ensure_dynamic_smem(hbq_lut_kernel<MB, true>, smem); if (rc_) return rc_; }
         hbq_lut_kernel<MB, true><<<grid, LUT_THREADS, smem, stream>>>(a);
     } else {
-        HBQ_CUDA_TRY(cudaFuncSetAttribute(hbq_lut_kernel<MB, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        { const int rc_ = ensure_dynamic_smem(hbq_lut_kernel<MB, false>, smem); if (rc_) return rc_; }
         hbq_lut_kernel<MB, false><<<grid, LUT_THREADS, smem, stream>>>(a);
     }
     HBQ_LAUNCH_CHECK("hbq_lut_kernel");
@@ -663,21 +723,11 @@ static bool fill_lut_args(const QArgs& qa, int mb, LutArgs* out)
 {
     LutArgs& a = *out;
     memset(&a, 0, sizeof(a));
-    if (!get_plan(mb, qa.tab[0], qa.nc, &a.plan)) return false;
+    if (!get_plan(mb, qa.tab[0], qa.nc, &a)) return false;
     a.q = qa;
     a.lpm = qa.f.l2_block_size / 8;
     while ((1 << a.log2lpm) < a.lpm) ++a.log2lpm;
-    for (int i = 0; i < 8; ++i) a.rm[i] = d2h(1.0 / (1.0 + i / 8.0));
-    double vmax = 0;
-    for (int i = 0; i < LUT_MAX_CAND; ++i) {
-        a.rt[i] = d2h(1.0 / (double)qa.tab[0][i < qa.nc ? i : qa.nc - 1]);
-        const double v = h2d(a.plan.val[i][a.plan.nlev - 1]);
-        if (v > vmax) vmax = v;
-    }
     a.inv_ele_max = 1.f / qa.ele_max[0];
-    a.big_l1 = 0x7C00;                         // smallest scale whose product with the largest value overflows fp16
-    for (int pat = 0x0400; pat <= 0x7B80; pat += 0x80)
-        if (h2d((uint16_t)pat) * vmax > 65504.0) { a.big_l1 = (uint16_t)pat; break; }
     return true;
 }
 
@@ -689,9 +739,8 @@ int hbq_lut_try_launch(const QArgs& qa, int mb, cudaStream_t stream, bool* launc
     LutArgs a;
     if (!fill_lut_args(qa, mb, &a)) return HBQ_OK;
 
-    int dev = 0, sms = 0;
-    HBQ_CUDA_TRY(cudaGetDevice(&dev));
-    HBQ_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    int sms = 0;
+    { const int rc_ = device_sms(&sms); if (rc_) return rc_; }
     const QArgs& q = qa;
     const bool side_out = q.out.codes || q.out.sign || q.out.scale_u8 || q.out.scale_h || q.out.l2_packed ||
                           q.out.l2_idx || q.out.scheme;
@@ -745,13 +794,12 @@ int hbq_lut_v_launch(const QArgs& qa, int mb, const void* in, void* out, int in_
     VArgs v;
     if (!v_args_fill(&v, in, out, in_bf16, out_bf16, B, T, H, D, qa.f.block_size)) return HBQ_ERR_UNSUPPORTED;
     if (v.tiles == 0) return HBQ_OK;
-    int dev = 0, sms = 0;
-    HBQ_CUDA_TRY(cudaGetDevice(&dev));
-    HBQ_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    int sms = 0;
+    { const int rc_ = device_sms(&sms); if (rc_) return rc_; }
     const int grid = (int)(v.tiles < 2 * sms ? v.tiles : 2 * sms);
     const size_t smem = (size_t)((a.plan.hi - a.plan.base + 2) & ~1) * sizeof(uint2) + (size_t)V_TILE_BYTES;
     #define HBQ_LAUNCH_V(MBV)                                                                                            \
-        HBQ_CUDA_TRY(cudaFuncSetAttribute(hbq_lut_v_kernel<MBV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        { const int rc_ = ensure_dynamic_smem(hbq_lut_v_kernel<MBV>, smem); if (rc_) return rc_; }                    \
         hbq_lut_v_kernel<MBV><<<grid, V_THREADS, smem, stream>>>(a, v);
     switch (mb) {
         case 1: HBQ_LAUNCH_V(1) break;

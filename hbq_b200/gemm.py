@@ -32,13 +32,14 @@ def gemm(a: torch.Tensor, b: torch.Tensor, mode: int, group_k: int = 0, group_n:
         bias = bias.to(device=a.device, dtype=torch.float16).contiguous()
     c = torch.empty((M, N), dtype=torch.float16, device=a.device)
     L = _lib.lib()
-    with torch.cuda.device(a.device):
+    with _lib.device_guard(a.device):
         stream = _stream_ptr(a.device)
         if force_simt:
             rc = L.hbq_gemm_simt(_ptr(a), _ptr(b), _ptr(c), M, N, K, int(b_is_nk), mode, group_k, group_n,
                                  _ptr(bias), stream)
         else:
-            ws_bytes = int(L.hbq_gemm_workspace_bytes(M, N, K, int(b_is_nk), mode, group_k, group_n))
+            # only the [K,N] layout needs scratch (for the transposed operand)
+            ws_bytes = 0 if b_is_nk else int(L.hbq_gemm_workspace_bytes(M, N, K, 0, mode, group_k, group_n))
             ws = torch.empty(ws_bytes, dtype=torch.uint8, device=a.device) if ws_bytes else None
             rc = L.hbq_gemm(_ptr(a), _ptr(b), _ptr(c), M, N, K, int(b_is_nk), mode, group_k, group_n,
                             _ptr(bias), _ptr(ws), ws_bytes, stream)

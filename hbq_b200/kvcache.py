@@ -71,7 +71,7 @@ def write_k_cache(k: torch.Tensor, num_heads: int, quantizer: _CudaBlockQuantize
     fusable = (cos is None or (kc.dtype == torch.float16 and cos.dtype == torch.float16 and sin.dtype == torch.float16))
     rc = _lib.ERR_UNSUPPORTED
     if fusable:
-        with torch.cuda.device(kc.device):
+        with _lib.device_guard(kc.device):
             rc = _lib.lib().hbq_kv_write_k(_ptr(kc), _dtype_code(kc), B, T, num_heads, D, _ptr(cos), _ptr(sin),
                                            rope_rows, ctypes.byref(fmt), _ptr(out), _dtype_code(out),
                                            _stream_ptr(kc.device))
@@ -99,7 +99,7 @@ def write_v_cache(v: torch.Tensor, num_heads: int, quantizer: _CudaBlockQuantize
     fmt = quantizer._format()
     odt = quantizer.out_dtype or vc.dtype
     out = torch.empty((B, num_heads, T, D), dtype=odt, device=vc.device)
-    with torch.cuda.device(vc.device):
+    with _lib.device_guard(vc.device):
         rc = _lib.lib().hbq_kv_write_v(_ptr(vc), _dtype_code(vc), B, T, num_heads, D, ctypes.byref(fmt), _ptr(out),
                                        _dtype_code(out), _stream_ptr(vc.device))
     if rc == _lib.ERR_UNSUPPORTED:

@@ -113,7 +113,7 @@ def dequantize_packed(p: PackedTensor) -> torch.Tensor:
                         p.scale_u8.data_ptr(), None,
                         p.l2_packed.data_ptr() if p.l2_packed is not None else None, None,
                         p.scheme.data_ptr() if p.scheme is not None else None)
-    with torch.cuda.device(out.device):
+    with _lib.device_guard(out.device):
         rc = _lib.lib().hbq_dequantize(ctypes.byref(po), rows, K, ctypes.byref(p.fmt), _ptr(out),
                                        _dtype_code(out), _stream_ptr(out.device))
     _lib.check(rc, "hbq_dequantize")
@@ -162,7 +162,7 @@ class _CudaBlockQuantizer(_QBase):
         odt = self.out_dtype or xc.dtype
         deq = torch.empty(xc.shape, dtype=odt, device=xc.device) if want_deq else None
         amax = None
-        with torch.cuda.device(xc.device):
+        with _lib.device_guard(xc.device):
             stream = _stream_ptr(xc.device)
             L = _lib.lib()
             if fmt.kind == _lib.KIND_MXFP and fmt.per_tensor_scale and xc.numel():
@@ -178,7 +178,7 @@ class _CudaBlockQuantizer(_QBase):
         return deq
 
     def q(self, x: torch.Tensor) -> torch.Tensor:
-        return self._launch(x, True, None).view(x.shape)
+        return self._launch(x, True, None)          # allocated with x's shape
 
     def quantize_packed(self, x: torch.Tensor, with_deq: bool = False):
         """Quantise ``x`` along its last axis into packed codes and scales.

@@ -215,6 +215,36 @@ def test_output_quantizer_roles():
         layer("nonsense")
 
 
+def test_cuda_graph_capture_of_the_layer():
+    """Quantize + GEMM make no allocation or synchronisation of their own, so a layer step can be
+    captured in a CUDA graph and replayed on new input."""
+    import hbq_b200 as H
+    M, K, N = 256, 512, 512
+    aq = H.HBQQuantizer(128, 2, 2, 5, 3, l2_block_size=8, l2_sc_bit=2, l2_scheme="SIG-1")
+    lin = H.QLinear(K, N, bias=False, device="cuda", dtype=torch.float16, check_finite=False)
+    lin.weight.data = dev(seeded_inputs("wgt", N, K, 61))
+    lin.aq = aq
+    lin.ops = H.FP16AccumMatMul(group_size=128, quant_block_size=32)
+    x_static = dev(seeded_inputs("act", M, K, 62))
+    with torch.no_grad():
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                lin(x_static)                         # warm-up: table plans, kernel attributes, allocator pools
+        torch.cuda.current_stream().wait_stream(side)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            y_static = lin(x_static)
+        for seed in (63, 64):
+            x_new = dev(seeded_inputs("act", M, K, seed))
+            x_static.copy_(x_new)
+            g.replay()
+            torch.cuda.synchronize()
+            assert torch.equal(y_static, lin(x_new))
+    assert H.gemm_status() == 0
+
+
 def test_packed_weight_storage(tmp_path):
     """A layer's weight survives pack -> torch.save -> load -> unpack bit for bit, at its packed size."""
     import hbq_b200 as H
