@@ -67,8 +67,8 @@ def lib() -> ctypes.CDLL:
     L.hbq_gemm.argtypes = [vp, vp, vp, i64, i64, i64, ci, ci, ci, ci, vp, vp, i64, vp]
     L.hbq_gemm_simt.argtypes = [vp, vp, vp, i64, i64, i64, ci, ci, ci, ci, vp, vp]
     L.hbq_gemm_kn_noalloc.argtypes = [vp, vp, vp, i64, i64, i64, ci, ci, ci, vp, vp]
-    L.hbq_kv_write_k.argtypes = [vp, ci, i64, i64, i64, i64, vp, vp, i64, ctypes.POINTER(Format), vp, ci, vp]
-    L.hbq_kv_write_v.argtypes = [vp, ci, i64, i64, i64, i64, ctypes.POINTER(Format), vp, ci, vp]
+    L.hbq_kv_write_k.argtypes = [vp, ci, i64, i64, i64, i64, vp, vp, i64, vp, ctypes.POINTER(Format), vp, ci, vp]
+    L.hbq_kv_write_v.argtypes = [vp, ci, i64, i64, i64, i64, ctypes.POINTER(Format), vp, ci, ci, vp]
     L.hbq_gemm_workspace_bytes.argtypes = [i64, i64, i64, ci, ci, ci, ci]
     L.hbq_gemm_workspace_bytes.restype = i64
     L.hbq_gemm_uses_tensor_cores.argtypes = [i64, i64, i64, ci, ci, ci, ci]

@@ -193,23 +193,24 @@ int hbq_quantize(const void* x, int dtype, int64_t rows, int64_t K, const hbq_fo
 }
 
 int hbq_kv_write_k(const void* k, int dtype, int64_t B, int64_t T, int64_t H, int64_t D, const void* cos,
-                   const void* sin, int64_t rope_rows, const hbq_format* fmt, void* out, int out_dtype, void* stream)
+                   const void* sin, int64_t rope_rows, const void* center, const hbq_format* fmt, void* out,
+                   int out_dtype, void* stream)
 {
     if (!fmt || B < 0 || T < 0 || H < 0 || D <= 0 || (cos != nullptr) != (sin != nullptr)) return HBQ_ERR_ARG;
     if (B * T * H == 0) return HBQ_OK;
     if (!out) return HBQ_ERR_ARG;
     if (fmt->kind == HBQ_KIND_MXFP && fmt->per_tensor_scale) return HBQ_ERR_UNSUPPORTED;   // needs max|x| of the rotated tensor first
-    KvWriteOpts kv = {cos, sin, rope_rows, B, T, H, D, 0};
+    KvWriteOpts kv = {cos, sin, rope_rows, B, T, H, D, 0, center, 0};
     return quantize_launch(k, dtype, B * T * H, D, fmt, out, out_dtype, nullptr, nullptr, (cudaStream_t)stream, &kv);
 }
 
 int hbq_kv_write_v(const void* v, int dtype, int64_t B, int64_t T, int64_t H, int64_t D, const hbq_format* fmt,
-                   void* out, int out_dtype, void* stream)
+                   void* out, int out_dtype, int out_token_major, void* stream)
 {
     if (!fmt || B < 0 || T < 0 || H < 0 || D <= 0) return HBQ_ERR_ARG;
     if (B * T * H == 0) return HBQ_OK;
     if (!out) return HBQ_ERR_ARG;
-    KvWriteOpts kv = {nullptr, nullptr, 0, B, T, H, D, 1};
+    KvWriteOpts kv = {nullptr, nullptr, 0, B, T, H, D, 1, nullptr, out_token_major};
     // rows / K only size the format checks here; the token-axis kernel takes its shape from kv
     return quantize_launch(v, dtype, B * H * D, fmt->block_size, fmt, out, out_dtype, nullptr, nullptr,
                            (cudaStream_t)stream, &kv);

@@ -22,6 +22,8 @@ struct KvWriteOpts {
     int64_t rope_rows;        // rows of the cos/sin tables: B*T, or T when one table serves every batch
     int64_t B, T, H, D;
     int v_axis;
+    const void* center;       // fp16 [B, H, D] subtracted after the rotation (K only), or NULL
+    int v_out_token_major;    // V only: write [B,T,H,D] instead of [B,H,T,D]
 };
 
 #define HBQ_CUDA_TRY(expr)                                                     \

@@ -124,6 +124,7 @@ __global__ void __launch_bounds__(256) mx_quantize_kernel(const QArgs a)
     if (valid) x = load_chunk(a, row, k0);
     else { for (int p = 0; p < 4; ++p) x.h[p] = bits_h2(0u); }
     if (a.rope_cos) rope_chunk(a, x, row, k0);
+    if (a.k_center) center_chunk(a, x, row, k0);
 
     // per-tensor scale (src/quantizer.py:516-524): the reference divides the fp16 tensor by a
     // Python double, which torch evaluates as an fp32 division by float(scale) rounded to fp16
@@ -348,6 +349,7 @@ __global__ void __launch_bounds__(256) mx_fast_kernel(const QArgs a)
     else { for (int p = 0; p < 4; ++p) xn.h[p] = bits_h2(0u); }
 
     if (!LEAN && a.rope_cos) rope_chunk(a, x, valid ? row_cur : 0, k0);
+    if (!LEAN && a.k_center) center_chunk(a, x, valid ? row_cur : 0, k0);
     __half2 d[4];
     uint32_t mag[4], sg[4], sb;
     mx_fast_chunk<KIND, MB, CODES>(a, x, d, mag, sg, sb);
@@ -411,7 +413,7 @@ template <int KIND, int MB>
 static int launch_mx_v(const QArgs& a, const KvWriteOpts* kv, cudaStream_t stream)
 {
     VArgs v;
-    if (!v_args_fill(&v, a.x, a.deq, a.in_bf16, a.out_bf16, kv->B, kv->T, kv->H, kv->D, a.f.block_size)) return HBQ_ERR_UNSUPPORTED;
+    if (!v_args_fill(&v, a.x, a.deq, a.in_bf16, a.out_bf16, kv->B, kv->T, kv->H, kv->D, a.f.block_size, kv->v_out_token_major)) return HBQ_ERR_UNSUPPORTED;
     if (v.tiles == 0) return HBQ_OK;
     int sms = 0;
     { const int rc = device_sms(&sms); if (rc) return rc; }
@@ -457,6 +459,7 @@ __global__ void __launch_bounds__(256) hbq_quantize_kernel(const QArgs a)
     if (valid) x = load_chunk(a, row, k0);
     else { for (int p = 0; p < 4; ++p) x.h[p] = bits_h2(0u); }
     if (a.rope_cos) rope_chunk(a, x, row, k0);
+    if (a.k_center) center_chunk(a, x, row, k0);
 
     const int L = a.f.l2_block_size;
     const int lpm = L >> 3;                  // lanes per micro-block (0 => two micro-blocks per lane)
@@ -650,7 +653,7 @@ int hbq_lut_try_launch(const QArgs& qa, int mb, cudaStream_t stream, bool* launc
 
 int quantize_extra_launch(const QArgs& qa, cudaStream_t stream);                                       // quantize_extra.cu
 int hbq_lut_v_launch(const QArgs& qa, int mb, const void* in, void* out, int in_bf16, int out_bf16,
-                     int64_t B, int64_t T, int64_t H, int64_t D, cudaStream_t stream);                  // quantize_lut.cu
+                     int64_t B, int64_t T, int64_t H, int64_t D, int out_token_major, cudaStream_t stream);                  // quantize_lut.cu
 
 static float h_rh(float f) { return __half2float(__float2half_rn(f)); }
 
@@ -727,7 +730,7 @@ static void launch_mx_fast(QArgs& a, dim3 grid, dim3 block, cudaStream_t stream)
     a.step_chunks = stride % a.cpr;
     const bool side_out = a.out.codes || a.out.sign || a.out.scale_u8 || a.out.scale_h || a.out.l2_packed ||
                           a.out.l2_idx || a.out.scheme;
-    if (a.deq && !side_out && a.aligned && a.K == a.Kp && !a.rope_cos && a.perm_T <= 0)
+    if (a.deq && !side_out && a.aligned && a.K == a.Kp && !a.rope_cos && a.perm_T <= 0 && !a.k_center)
         mx_fast_kernel<KIND, MB, false, true><<<grid, block, 0, stream>>>(a);
     else if (a.out.codes) mx_fast_kernel<KIND, MB, true, false><<<grid, block, 0, stream>>>(a);
     else mx_fast_kernel<KIND, MB, false, false><<<grid, block, 0, stream>>>(a);
@@ -772,6 +775,8 @@ int quantize_launch(const void* x, int dtype, int64_t rows, int64_t K, const hbq
         if (!deq) return HBQ_ERR_ARG;
         a.rope_cos = (const uint16_t*)kv->cos; a.rope_sin = (const uint16_t*)kv->sin; a.rope_rows = kv->rope_rows;
         a.perm_T = kv->T; a.perm_H = kv->H;
+        a.k_center = (const uint16_t*)kv->center;
+        if (kv->center && ((reinterpret_cast<uintptr_t>(kv->center) & 15) || dtype != HBQ_DTYPE_F16 || kv->v_axis)) return HBQ_ERR_UNSUPPORTED;
         if ((kv->cos && ((reinterpret_cast<uintptr_t>(kv->cos) | reinterpret_cast<uintptr_t>(kv->sin)) & 15)) || !a.aligned)
             return HBQ_ERR_ALIGN;
     }
@@ -879,7 +884,7 @@ int quantize_launch(const void* x, int dtype, int64_t rows, int64_t K, const hbq
         if (tb != 8 && tb != 16 && tb != 32) return HBQ_ERR_UNSUPPORTED;
     }
     if (kv && kv->v_axis)
-        return hbq_lut_v_launch(a, fast_mb, x, deq, a.in_bf16, a.out_bf16, kv->B, kv->T, kv->H, kv->D, stream);
+        return hbq_lut_v_launch(a, fast_mb, x, deq, a.in_bf16, a.out_bf16, kv->B, kv->T, kv->H, kv->D, kv->v_out_token_major, stream);
     {
         bool launched = false;
         const int rc = hbq_lut_try_launch(a, fast_mb, stream, &launched);

@@ -106,6 +106,7 @@ struct QArgs {
     const uint16_t* rope_sin;
     int64_t rope_rows;          // B*T (per-batch tables) or T (one table for every batch)
     int64_t perm_T, perm_H;     // > 0: permute output rows (b,t,h) -> (b,h,t)
+    const uint16_t* k_center;   // fp16 [B, H, K] or NULL: subtracted after RoPE (K-cache centring, src/module.py:221-244)
     int code_bits;          // bits per stored element code (4, 5 or 8)
     int sign_bit;           // position of the sign in a byte code: ebit + mbit
 };
@@ -310,5 +311,15 @@ __device__ __forceinline__ void rope_chunk(const QArgs& a, Chunk& x, int64_t row
         const __half2 t2 = __hmul2_rn(bits_h2(partner ^ neg), bits_h2(s[p]));
         x.h[p] = __hadd2_rn(t1, t2);
     }
+}
+// K-cache centring (src/module.py:229-244): key_states - center with center [B, H, 1, D], one fp16
+// subtraction after the rotation.  Rows are (b, t, h) of the projection output.
+__device__ __forceinline__ void center_chunk(const QArgs& a, Chunk& x, int64_t row, int64_t k0)
+{
+    const int64_t bt = row / a.perm_H, h = row - bt * a.perm_H, b = bt / a.perm_T;
+    const uint4 cv = __ldg(reinterpret_cast<const uint4*>(a.k_center + ((b * a.perm_H + h) * a.K + k0)));
+    const uint32_t c[4] = {cv.x, cv.y, cv.z, cv.w};
+    #pragma unroll
+    for (int p = 0; p < 4; ++p) x.h[p] = __hsub2_rn(x.h[p], bits_h2(c[p]));
 }
 }  // namespace hbq

@@ -136,7 +136,7 @@ int quantize_extra_launch(const QArgs& qa, cudaStream_t stream)
     if (!qa.deq) return HBQ_ERR_ARG;
     const bool side_out = qa.out.codes || qa.out.sign || qa.out.scale_u8 || qa.out.scale_h || qa.out.l2_packed ||
                           qa.out.l2_idx || qa.out.scheme;
-    if (side_out || qa.rope_cos || qa.perm_T > 0) return HBQ_ERR_UNSUPPORTED;
+    if (side_out || qa.rope_cos || qa.perm_T > 0 || qa.k_center) return HBQ_ERR_UNSUPPORTED;
     if (f.kind == HBQ_KIND_MXEX) {
         const int L = f.l2_block_size;
         if (f.mbit < 2 || f.mbit > 8 || f.sc_ebit < 2 || f.sc_ebit > 8 || f.l2_sc_bit < 0 || f.l2_sc_bit > 4) return HBQ_ERR_UNSUPPORTED;

@@ -377,6 +377,7 @@ __global__ void __launch_bounds__(LUT_THREADS, 2) hbq_lut_kernel(const LutArgs a
         if (valid) x = load_chunk(q, row, k0);
         else { for (int p = 0; p < 4; ++p) x.h[p] = bits_h2(0u); }
         if (q.rope_cos) rope_chunk(q, x, valid ? row : 0, k0);
+        if (q.k_center) center_chunk(q, x, valid ? row : 0, k0);
 
         __half2 dq[4];
         uint32_t mag[4], sgo[4], l1b;
@@ -577,6 +578,7 @@ __global__ void __launch_bounds__(LEAN_THREADS, 1) hbq_lut_lean_kernel(const Lut
             #pragma unroll
             for (int p = 0; p < 4; ++p) xr.h[p] = bits_h2(xb[p]);
             if (a.q.rope_cos) rope_chunk(a.q, xr, row, c * 8);
+            if (a.q.k_center) center_chunk(a.q, xr, row, c * 8);
             #pragma unroll
             for (int p = 0; p < 4; ++p) xb[p] = h2_bits(xr.h[p]);
             oci = (out_row(a.q, row) << a.log2cpr) + c;
@@ -609,7 +611,7 @@ static int launch_lean(const LutArgs& a, int grid, size_t smem, cudaStream_t str
     #define HBQ_LAUNCH_LEAN(IB, OB, KVW)                                                                                              \
         { const int rc_ = ensure_dynamic_smem(hbq_lut_lean_kernel<MB, IB, OB, KVW>, smem); if (rc_) return rc_; }                    \
         hbq_lut_lean_kernel<MB, IB, OB, KVW><<<grid, LEAN_THREADS, smem, stream>>>(a);
-    const bool kvw = a.q.rope_cos || a.q.perm_T > 0;
+    const bool kvw = a.q.rope_cos || a.q.perm_T > 0 || a.q.k_center;
     if (kvw) { if (a.q.out_bf16) { HBQ_LAUNCH_LEAN(false, true, true) } else { HBQ_LAUNCH_LEAN(false, false, true) } }
     else if (a.q.in_bf16) { if (a.q.out_bf16) { HBQ_LAUNCH_LEAN(true, true, false) } else { HBQ_LAUNCH_LEAN(true, false, false) } }
     else { if (a.q.out_bf16) { HBQ_LAUNCH_LEAN(false, true, false) } else { HBQ_LAUNCH_LEAN(false, false, false) } }
@@ -744,7 +746,7 @@ int hbq_lut_try_launch(const QArgs& qa, int mb, cudaStream_t stream, bool* launc
     const QArgs& q = qa;
     const bool side_out = q.out.codes || q.out.sign || q.out.scale_u8 || q.out.scale_h || q.out.l2_packed ||
                           q.out.l2_idx || q.out.scheme;
-    const bool kvw = q.rope_cos || q.perm_T > 0;
+    const bool kvw = q.rope_cos || q.perm_T > 0 || q.k_center;
     a.log2cpr = -1;
     if ((q.cpr & (q.cpr - 1)) == 0) { a.log2cpr = 0; while ((1ll << a.log2cpr) < q.cpr) ++a.log2cpr; }
     // the K-cache write takes the fast path for fp16 rows of a power-of-two length
@@ -783,7 +785,7 @@ int hbq_lut_try_launch(const QArgs& qa, int mb, cudaStream_t stream, bool* launc
 // for a [rows, block] problem); returns HBQ_ERR_UNSUPPORTED when the format does not fit the table
 // kernel (the caller then transposes and uses hbq_quantize like the reference).
 int hbq_lut_v_launch(const QArgs& qa, int mb, const void* in, void* out, int in_bf16, int out_bf16,
-                     int64_t B, int64_t T, int64_t H, int64_t D, cudaStream_t stream)
+                     int64_t B, int64_t T, int64_t H, int64_t D, int out_token_major, cudaStream_t stream)
 {
     const int L = qa.f.l2_block_size;
     if (qa.nscheme != 1 || qa.nc > LUT_MAX_CAND || !qa.scale_fast_e5m3 || L < 8 || mb < 1 || mb > 3) return HBQ_ERR_UNSUPPORTED;
@@ -792,7 +794,7 @@ int hbq_lut_v_launch(const QArgs& qa, int mb, const void* in, void* out, int in_
     if (!fill_lut_args(qa, mb, &a)) return HBQ_ERR_UNSUPPORTED;
 
     VArgs v;
-    if (!v_args_fill(&v, in, out, in_bf16, out_bf16, B, T, H, D, qa.f.block_size)) return HBQ_ERR_UNSUPPORTED;
+    if (!v_args_fill(&v, in, out, in_bf16, out_bf16, B, T, H, D, qa.f.block_size, out_token_major)) return HBQ_ERR_UNSUPPORTED;
     if (v.tiles == 0) return HBQ_OK;
     int sms = 0;
     { const int rc_ = device_sms(&sms); if (rc_) return rc_; }

@@ -17,6 +17,7 @@ struct VArgs {
     uint16_t* out;
     int64_t B, T, H, D;
     int in_bf16, out_bf16;
+    int out_token_major;      // 0: out is [B,H,T,D] (the cache layout); 1: out keeps the input's [B,T,H,D]
     int64_t tiles;            // B * H * ceil(T/128) * (D/64)
     int tblocks, dslabs;
 };
@@ -107,8 +108,8 @@ __device__ __forceinline__ void v_cache_tiles(const VArgs& v, uint32_t* tile, co
                         w[i] = *reinterpret_cast<uint32_t*>(&bb);
                     }
                 }
-                *reinterpret_cast<uint4*>(v.out + (((b * v.H + h) * v.T + t0 + tk) * v.D + d0 + seg * 8)) =
-                    make_uint4(w[0], w[1], w[2], w[3]);
+                const int64_t orow = v.out_token_major ? (b * v.T + t0 + tk) * v.H + h : (b * v.H + h) * v.T + t0 + tk;
+                *reinterpret_cast<uint4*>(v.out + (orow * v.D + d0 + seg * 8)) = make_uint4(w[0], w[1], w[2], w[3]);
             }
         }
         __syncthreads();
@@ -117,8 +118,9 @@ __device__ __forceinline__ void v_cache_tiles(const VArgs& v, uint32_t* tile, co
 
 // Tile count and geometry of a [B,T,H,D] V write; false when the shape does not fit the tile kernel.
 inline bool v_args_fill(VArgs* v, const void* in, void* out, int in_bf16, int out_bf16, int64_t B, int64_t T, int64_t H,
-                        int64_t D, int block_size)
+                        int64_t D, int block_size, int out_token_major)
 {
+    v->out_token_major = out_token_major;
     if (block_size > VT || block_size < 8 || (VT % block_size) != 0 || (D % VD) != 0) return false;
     v->in = (const uint16_t*)in; v->out = (uint16_t*)out;
     v->B = B; v->T = T; v->H = H; v->D = D; v->in_bf16 = in_bf16; v->out_bf16 = out_bf16;

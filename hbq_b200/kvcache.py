@@ -51,11 +51,15 @@ def _tables(cos: torch.Tensor, sin: torch.Tensor, B: int, T: int, D: int):
 
 
 def write_k_cache(k: torch.Tensor, num_heads: int, quantizer: _CudaBlockQuantizer,
-                  cos: Optional[torch.Tensor] = None, sin: Optional[torch.Tensor] = None) -> torch.Tensor:
+                  cos: Optional[torch.Tensor] = None, sin: Optional[torch.Tensor] = None,
+                  center: Optional[torch.Tensor] = None) -> torch.Tensor:
     """RoPE + quantise along head_dim + ``[B,T,H,D] -> [B,H,T,D]`` for the k_proj (or q_proj) output.
 
     ``k`` is ``[B, T, H*D]`` (or ``[B, T, H, D]``); returns what the reference computes as
-    ``quantizer.q(apply_rotary_pos_emb(k.view(B,T,H,D).transpose(1,2)))`` (src/module.py:147-162)."""
+    ``quantizer.q(apply_rotary_pos_emb(k.view(B,T,H,D).transpose(1,2)))`` (src/module.py:147-162).
+    ``center`` (``[B, H, 1, D]`` or ``[B, H, D]``, fp16) is subtracted after the rotation: the
+    K-cache centring of the Qwen2 block (``kv_quantizer.q(key_states - center)``,
+    src/module.py:221-244), with the centre computed by the caller at prefill."""
     global fused_last
     if not k.is_cuda:
         raise _lib.HbqError("write_k_cache needs a CUDA tensor (there is no CPU fallback)")
@@ -68,28 +72,39 @@ def write_k_cache(k: torch.Tensor, num_heads: int, quantizer: _CudaBlockQuantize
     rope_rows = 0
     if cos is not None:
         cos, sin, rope_rows = _tables(cos, sin, B, T, D)
+    if center is not None:
+        if center.numel() != B * num_heads * D:
+            raise ValueError(f"center must hold B*H*D = {B * num_heads * D} values; got {tuple(center.shape)}")
+        center = center.reshape(B, num_heads, D).contiguous()
     fusable = (cos is None or (kc.dtype == torch.float16 and cos.dtype == torch.float16 and sin.dtype == torch.float16))
+    fusable = fusable and (center is None or (kc.dtype == torch.float16 and center.dtype == torch.float16))
     rc = _lib.ERR_UNSUPPORTED
     if fusable:
         with _lib.device_guard(kc.device):
             rc = _lib.lib().hbq_kv_write_k(_ptr(kc), _dtype_code(kc), B, T, num_heads, D, _ptr(cos), _ptr(sin),
-                                           rope_rows, ctypes.byref(fmt), _ptr(out), _dtype_code(out),
+                                           rope_rows, _ptr(center), ctypes.byref(fmt), _ptr(out), _dtype_code(out),
                                            _stream_ptr(kc.device))
     if rc == _lib.ERR_UNSUPPORTED:
         fused_last = False
         x = kc.view(B, T, num_heads, D).transpose(1, 2)
         if cos is not None:
             x = apply_rope(x, cos.view(-1, T, D), sin.view(-1, T, D))
+        if center is not None:
+            x = x - center.view(B, num_heads, 1, D).to(x.dtype)
         return quantizer.q(x.contiguous())
     _lib.check(rc, "hbq_kv_write_k")
     fused_last = True
     return out
 
 
-def write_v_cache(v: torch.Tensor, num_heads: int, quantizer: _CudaBlockQuantizer) -> torch.Tensor:
+def write_v_cache(v: torch.Tensor, num_heads: int, quantizer: _CudaBlockQuantizer,
+                  token_major: bool = False) -> torch.Tensor:
     """Quantise the v_proj output along the TOKEN axis and store it as ``[B,H,T,D]``.
 
-    Equals the reference's transpose / ``kv_quantizer.q`` / transpose (src/module.py:163-168)."""
+    Equals the reference's transpose / ``kv_quantizer.q`` / transpose (src/module.py:163-168).
+    ``token_major=True`` returns ``[B,T,H,D]`` instead (the input's layout), which is what a serving
+    engine with a flattened-token cache wants (vllm/src/hbq_vllm_quant.py:322-345: one call per
+    sequence span with B = 1)."""
     global fused_last
     if not v.is_cuda:
         raise _lib.HbqError("write_v_cache needs a CUDA tensor (there is no CPU fallback)")
@@ -98,14 +113,15 @@ def write_v_cache(v: torch.Tensor, num_heads: int, quantizer: _CudaBlockQuantize
     vc = v.contiguous()
     fmt = quantizer._format()
     odt = quantizer.out_dtype or vc.dtype
-    out = torch.empty((B, num_heads, T, D), dtype=odt, device=vc.device)
+    out = torch.empty((B, T, num_heads, D) if token_major else (B, num_heads, T, D), dtype=odt, device=vc.device)
     with _lib.device_guard(vc.device):
         rc = _lib.lib().hbq_kv_write_v(_ptr(vc), _dtype_code(vc), B, T, num_heads, D, ctypes.byref(fmt), _ptr(out),
-                                       _dtype_code(out), _stream_ptr(vc.device))
+                                       _dtype_code(out), int(token_major), _stream_ptr(vc.device))
     if rc == _lib.ERR_UNSUPPORTED:
         fused_last = False
         x = vc.view(B, T, num_heads, D).permute(0, 2, 3, 1).contiguous()          # [B,H,D,T]
-        return quantizer.q(x).transpose(-1, -2).contiguous()
+        y = quantizer.q(x)
+        return y.permute(0, 3, 1, 2).contiguous() if token_major else y.transpose(-1, -2).contiguous()
     _lib.check(rc, "hbq_kv_write_v")
     fused_last = True
     return out

@@ -116,19 +116,21 @@ int hbq_fp_quant(const void* x, int64_t n, int ebit, int mbit, int allow_subnorm
  * stores the fake-quantised values in the cache layout [B,H,T,D] -- what the reference does as
  * view + transpose + apply_rotary_pos_emb + kv_quantizer.q.  cos/sin are fp16 [rope_rows, D]
  * tables with rope_rows = B*T, or T when one table serves every batch; both NULL skips the
- * rotation (then k may be bf16).  Returns HBQ_ERR_UNSUPPORTED for formats outside the fused
+ * rotation (then k may be bf16).  `center` (fp16 [B,H,D] or NULL) is subtracted after the rotation:
+ * the K-cache centring of the Qwen2 attention block (src/module.py:221-244).  Returns HBQ_ERR_UNSUPPORTED for formats outside the fused
  * kernels (callers then run the three steps separately). */
 int hbq_kv_write_k(const void* k, int dtype, int64_t B, int64_t T, int64_t H, int64_t D,
-                   const void* cos, const void* sin, int64_t rope_rows, const hbq_format* fmt,
-                   void* out, int out_dtype, void* stream);
+                   const void* cos, const void* sin, int64_t rope_rows, const void* center,
+                   const hbq_format* fmt, void* out, int out_dtype, void* stream);
 
 /* V-cache write (src/module.py:163-168): v is the v_proj output viewed [B,T,H,D]; blocks of
  * fmt->block_size consecutive TOKENS per (batch, head, channel) are quantised (the tail block
  * zero padded) and the result is stored as [B,H,T,D] -- the reference's transpose, quantise,
- * transpose back.  Served formats: HBQ with one candidate table, MXFP / NVFP E2Mx and MXINT with a
+ * transpose back.  With out_token_major != 0 the result keeps the input's [B,T,H,D] layout (serving
+ * engines with flattened-token caches, vllm/src/hbq_vllm_quant.py:322-345).  Served formats: HBQ with one candidate table, MXFP / NVFP E2Mx and MXINT with a
  * scale inside fp16's range; D a multiple of 64, block_size 16..128.  HBQ_ERR_UNSUPPORTED otherwise. */
 int hbq_kv_write_v(const void* v, int dtype, int64_t B, int64_t T, int64_t H, int64_t D,
-                   const hbq_format* fmt, void* out, int out_dtype, void* stream);
+                   const hbq_format* fmt, void* out, int out_dtype, int out_token_major, void* stream);
 
 /* ---- GEMM with modelled accumulation --------------------------------------------------- */
 

@@ -139,3 +139,37 @@ def test_v_write_bf16_d64():
     want = q.q(v.view(B, T, H, D).permute(0, 2, 3, 1).contiguous()).transpose(-1, -2).contiguous()
     assert torch.equal(got, want)
     assert kvcache.write_v_cache(v[:, :0], H, q).shape == (B, H, 0, D)
+
+
+@pytest.mark.parametrize("name", ["hbq_a_sig1_l8", "nvfp4_b16", "hbq_mix_l4", "mxfp_e4m3_b32"])
+def test_k_write_with_centre(name):
+    """K-cache centring of the Qwen2 block (src/module.py:221-244): quantise key_states - center."""
+    from hbq_b200 import kvcache
+    B, T, H, D = 2, 50, 4, 128
+    q = quantizers()[name]()
+    k = torch.from_numpy(seeded_inputs("act", B * T, H * D, seed=11).astype(np.float16)).cuda().view(B, T, H * D) + 3.0
+    cos, sin = rope_tables(B, T, D, False)
+    rot = kvcache.apply_rope(k.view(B, T, H, D).transpose(1, 2), cos, sin)
+    center = rot.mean(dim=-2, keepdim=True)                       # [B,H,1,D], as the reference computes it at prefill
+    got = kvcache.write_k_cache(k, H, q, cos, sin, center=center)
+    assert kvcache.fused_last
+    want = q.q((rot - center).contiguous())
+    bad = hbits(got) != hbits(want)
+    assert not bad.any(), f"{name}: {bad.sum()} of {bad.size} differ"
+    # without rotation
+    got = kvcache.write_k_cache(k, H, q, center=center)
+    want = q.q((k.view(B, T, H, D).transpose(1, 2) - center).contiguous())
+    assert np.array_equal(hbits(got), hbits(want))
+
+
+@pytest.mark.parametrize("name", ["hbq_a_sig1_l8", "nvfp4_b16", "mxfp4_b32"])
+def test_v_write_token_major(name):
+    """Flattened-token layout of a serving engine: the result stays [B,T,H,D]."""
+    from hbq_b200 import kvcache
+    B, T, H, D = 1, 173, 8, 128
+    q = quantizers()[name]()
+    v = torch.from_numpy(seeded_inputs("act", B * T, H * D, seed=13).astype(np.float16)).cuda().view(B, T, H * D)
+    got = kvcache.write_v_cache(v, H, q, token_major=True)
+    assert got.shape == (B, T, H, D)
+    want = kvcache.write_v_cache(v, H, q)                      # [B,H,T,D], checked against the unfused chain above
+    assert torch.equal(got, want.permute(0, 2, 1, 3).contiguous())
