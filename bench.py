@@ -2,6 +2,7 @@
 """Benchmark of the HBQ hot path on B200: one quantised linear layer.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py --sweep [CASE]      # configs[2] quantize sweep and KV-cache writes, one line per case
 
 Workload (the reference's HBQ-E quant-GEMM configuration with partial-sum-quantised
 accumulation, config/hbq_e_psum_quant.yaml): X bf16 [4096, 4096] ~ N(0,1) with 0.5 % outlier
@@ -303,6 +304,67 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         dist.destroy_process_group()
 
 
+# ---- quantize sweep (configs[2]: [8192, 8192] over the six shipped activation formats) and the fused
+#      KV-cache writes; not part of the default run --------------------------------------------------
+SWEEP_FORMATS = {
+    "mxfp4": ("mxfp", dict(block_size=32, ebit=2, mbit=1, sc_ebit=5, sc_mbit=0)),
+    "nvfp4": ("mxfp", dict(block_size=16, ebit=2, mbit=1, sc_ebit=5, sc_mbit=3)),
+    "mxint8": ("mxint", dict(nbit=8, sc_ebit=8, sc_mbit=0, block_size=32)),
+    "mxfp_a8": ("mxfp", dict(block_size=32, ebit=2, mbit=5, sc_ebit=5, sc_mbit=0)),
+    "hbq_a": ("hbq", dict(block_size=128, ebit=2, mbit=2, sc_ebit=5, sc_mbit=3, l2_block_size=8, l2_sc_bit=2, l2_scheme="SIG-1")),
+    "hbq_e": ("hbq", ACT),
+}
+
+
+def run_sweep(args):
+    """One JSON line per case: `--sweep` runs all, `--sweep NAME` one (a format name, `k_write` or `v_write`)."""
+    import torch
+    import hbq_b200 as H
+    from hbq_b200 import kvcache
+    torch.cuda.set_device(0)
+    peaks = measured_peaks()
+    torch.manual_seed(2)
+    cls = {"mxfp": H.MXFPQuantizer, "mxint": H.MXINTQuantizer, "hbq": H.HBQQuantizer}
+
+    def timed(fn, numel, label, extra):
+        for _ in range(max(args.warmup, 3)):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / args.steps
+        gbs = numel * QUANT_BYTES_PER_ELEM / ms / 1e6
+        print(json.dumps({"case": label, "ms": ms, "GB/s": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"],
+                          "bytes_per_elem": QUANT_BYTES_PER_ELEM, **extra}))
+
+    want = None if args.sweep == "all" else args.sweep
+    x = None
+    for name, (kind, kw) in SWEEP_FORMATS.items():
+        if want not in (None, name):
+            continue
+        if x is None:      # configs[2]: 0.5 * Student-t(3), [8192, 8192], inputs larger than L2
+            x = (0.5 * torch.distributions.StudentT(3.0).sample((8192, 8192))).to(torch.float16).cuda()
+        q = cls[kind](**kw)
+        timed(lambda: q.q(x), x.numel(), f"quantize {name}", {"shape": [8192, 8192], "dtype": "f16"})
+    if want in (None, "k_write", "v_write"):
+        B, T, Hh, D = 8, 4096, 32, 128
+        k = torch.randn(B, T, Hh * D, device="cuda", dtype=torch.float16)
+        inv = 1.0 / (10000.0 ** (torch.arange(0, D, 2).float() / D))
+        ang = torch.arange(T).float()[:, None] * inv[None]
+        emb = torch.cat((ang, ang), -1)[None]
+        cos, sin = emb.cos().half().cuda(), emb.sin().half().cuda()
+        q = cls["hbq"](**SWEEP_FORMATS["hbq_a"][1])
+        shape = {"shape": [B, T, Hh, D], "dtype": "f16", "format": "hbq_a"}
+        if want in (None, "k_write"):
+            timed(lambda: kvcache.write_k_cache(k, Hh, q, cos, sin), k.numel(), "k_write (RoPE + quantize + layout)", shape)
+        if want in (None, "v_write"):
+            timed(lambda: kvcache.write_v_cache(k, Hh, q), k.numel(), "v_write (token-axis quantize + layout)", shape)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -310,7 +372,13 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--sweep", nargs="?", const="all", default=None,
+                    help="instead of the benchmark line: quantize sweep of configs[2] and the KV-cache writes "
+                         "(all cases, or one: " + ", ".join(SWEEP_FORMATS) + ", k_write, v_write)")
     args = ap.parse_args()
+    if args.sweep is not None:
+        run_sweep(args)
+        return
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
