@@ -191,6 +191,26 @@ def test_qlinear_layer(oracle):
     assert rel < 1e-3, rel
 
 
+@pytest.mark.parametrize("K", [384, 320, 256])
+@pytest.mark.parametrize("mode", [("grouped", 2, 128, 0), ("int8", 3, 128, 32), ("grouped64", 2, 64, 0), ("fp32", 0, 0, 0)],
+                         ids=lambda m: m[0])
+def test_tensor_core_several_tiles_per_cta(oracle, K, mode):
+    """156 output tiles on 148 SMs: some CTAs run two tiles back to back, with an odd number of
+    chunks per tile (K = 384: the two MMA-issuing warps swap accumulators from tile to tile), a
+    ragged last chunk (K = 320: one issuing warp) and an even count (K = 256)."""
+    import hbq_b200 as H
+    M, N = 128 * 13, 256 * 12
+    _, m, gk, gn = mode
+    rng = np.random.default_rng(K)
+    A = rng.standard_normal((M, K)).astype(np.float16)
+    W = (0.05 * rng.standard_normal((N, K))).astype(np.float16)
+    ref = oracle.gemm(A, np.ascontiguousarray(W.T), m, gk, gn)
+    got = H.gemm(dev(A), dev(W), m, gk, gn, b_is_nk=True)
+    torch.cuda.synchronize()
+    assert H.gemm_status() == 0, "a bounded wait expired inside the tensor-core kernel"
+    compare(got.cpu().numpy(), ref, f"tc {mode[0]} K={K}")
+
+
 def test_output_quantizer_roles():
     """quant_before_* switches give the named projections an output quantizer (src/ptq.py:287-324)."""
     import hbq_b200 as H
