@@ -1,7 +1,7 @@
 """Generate the golden vectors under tests/golden/ from the reference's own code.
 
-Run where the reference checkout is available (its path is the first argument,
-default ``/root/reference``)::
+Run where the reference checkout is available (its path is the first argument, or the
+environment variable ``HBQ_REFERENCE_DIR``)::
 
     python tests/golden/make_golden.py [/path/to/HBQ]
 
@@ -26,7 +26,7 @@ import warnings
 import numpy as np
 import torch
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("HBQ_REFERENCE_DIR", "/root/reference")
 sys.path.insert(0, REF)
 from src.quantizer import (HBQQuantizer, MXExQuantizer, MXFPQuantizer, MXINTQuantizer,  # noqa: E402
                            VSQQuantizer, fp_quant, make_fp_quant)
