@@ -12,6 +12,7 @@
 //
 // One persistent CTA per SM, 384 threads in three warpgroups:
 //   warp 0      TMA producer: 4-stage ring of {A 128x64, W 256x64} fp16 tiles, 128B swizzle
+//               (decode-sized M: 6 stages of {A 128x64, W 128x64}, twice the CTAs)
 //   warps 1-2   MMA issue (one lane each, alternate chunks); warp 1 also owns the TMEM allocation
 //   warp 3      idle (fills the control warpgroup, which gives its registers away)
 //   warps 4-11  epilogue: warp w owns TMEM lanes 32*(w%4).. and the 128 columns (w-4)/4; it takes
@@ -31,11 +32,17 @@
 
 namespace hbq {
 
-constexpr int BM = 128, BN = 256, BK = 64, NSTAGE = 4;
-constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int BM = 128, BK = 64;
+constexpr int TMEM_BUF_COLS = 256;                 // column stride of the two accumulators
+constexpr int A_BYTES = BM * BK * 2;
+// Two tile shapes (template parameters BN, NSTAGE of the kernel):
+//   256 columns, 4 stages of 48 KB: the shape for every problem that fills the SMs;
+//   128 columns, 6 stages of 32 KB: decode-sized M, where 256-column tiles would leave most SMs without
+//   work and the time is the streaming of W -- twice the CTAs, the same bytes in flight per CTA.
+constexpr int stage_bytes(int bn) { return A_BYTES + bn * BK * 2; }
+constexpr uint32_t smem_bytes(int bn, int nstage) { return nstage * stage_bytes(bn) + 1024 /* alignment slack */ + 256 /* barriers */; }
 constexpr int EPW = 8;                         // epilogue warps
 constexpr int NTHREADS = 128 + EPW * 32;
-constexpr uint32_t SMEM_BYTES = NSTAGE * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
 
 __device__ int g_tc_status;   // 0 = ok; otherwise the code of the wait that expired
 
@@ -200,8 +207,6 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr)
     const uint32_t lo = ((saddr & 0x3FFFFu) >> 4) | (1u << 16);      // start address, LBO
     return ((uint64_t)kHi << 32) | lo;
 }
-// kind::f16: D fp32, A/B fp16, both K-major, M = 128, N = 256
-constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 
 // ---- epilogue arithmetic ---------------------------------------------------------------------
 // INT8 partial-sum fake quantisation of `n` consecutive columns (gemm.cu:1145-1152, 1198-1249):
@@ -291,6 +296,7 @@ struct TcArgs {
     int k_stages;        // ceil(K / 64)
     int chunk_k16;       // MMAs (K = 16 each) per accumulation chunk
     int issuers;         // MMA-issuing warps to use (1 or 2)
+    int bn;              // tile width chosen by the host: 256, or 128 for decode-sized M
 };
 
 // Developer timeline trace, compiled in only with -DHBQ_TC_TRACE: CTA 0 records clock64() at the
@@ -308,11 +314,14 @@ __device__ int g_tc_trace_chunks = 0;
 #endif
 
 // ---- the kernel ------------------------------------------------------------------------------
-template <int MODE, int GN>
+template <int MODE, int GN, int BN, int NSTAGE>
 __global__ void __launch_bounds__(NTHREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                const TcArgs args)
 {
+    constexpr int STAGE_BYTES = A_BYTES + BN * BK * 2;
+    // kind::f16: D fp32, A/B fp16, both K-major, M = 128, N = BN
+    constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t tiles = (raw + 1023u) & ~1023u;                  // 1024-byte aligned tile ring
@@ -325,6 +334,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     volatile int* abort_flag = reinterpret_cast<volatile int*>(ctrl + 16 * NSTAGE + 40);
 
     constexpr int EPI_COLS = BN / (EPW / 4);
+    constexpr int EPI_GROUPS = EPI_COLS / 32;        // TMEM loads (32 columns each) per warp and chunk
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
@@ -408,7 +418,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                     // barrier passes the wait for the phase before its first)
                     if (!(ok = mbar_wait_warp(bar_tempty + 8 * buf, ((chunk >> 1) & 1u) ^ 1u, abort_flag, 3))) break;
                     TC_TRACE(chunk, 1);
-                    const uint32_t d_tmem = tmem_base + buf * BN;
+                    const uint32_t d_tmem = tmem_base + buf * TMEM_BUF_COLS;
                     for (int s = 0; s < nst; ++s) {
                         if (!full_pre && !(ok = mbar_wait_warp(bar_full + 8 * stage, phase, abort_flag, 2))) break;
                         TC_TRACE(chunk, s == 0 ? 2 : 5);
@@ -453,7 +463,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                         const int k16 = ks * (BK / 16) + kk;
                         const bool last = (in_chunk + 1 == args.chunk_k16) || (k16 + 1 == total_k16);
                         if (leader) {
-                            tc_mma_f16(tmem_base + buf * BN, umma_desc(sa + kk * 32), umma_desc(sb + kk * 32),
+                            tc_mma_f16(tmem_base + buf * TMEM_BUF_COLS, umma_desc(sa + kk * 32), umma_desc(sb + kk * 32),
                                        IDESC, in_chunk != 0);
                             if (last) tc_commit(bar_tfull + 8 * buf);
                         }
@@ -494,22 +504,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                 if (!ok) break;
                 tc_fence_after();
                 if (threadIdx.x == 128) TC_TRACE(chunk, 11);
-                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN + cgrp * EPI_COLS;
+                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * TMEM_BUF_COLS + cgrp * EPI_COLS;
                 {
-                    // the warp's whole slice of the chunk: 4 loads of 32 columns in flight together
-                    uint32_t r[4][32];
+                    // the warp's whole slice of the chunk: all its 32-column loads in flight together
+                    uint32_t r[EPI_GROUPS][32];
                     #pragma unroll
-                    for (int h = 0; h < 4; ++h) tc_ld32_issue(taddr + h * 32, r[h]);
-                    tc_ld_wait(r[0]);                    // waits for all four
+                    for (int h = 0; h < EPI_GROUPS; ++h) tc_ld32_issue(taddr + h * 32, r[h]);
+                    tc_ld_wait(r[0]);                    // waits for all of them
                     #pragma unroll
-                    for (int h = 1; h < 4; ++h) tc_ld_landed(r[h]);
+                    for (int h = 1; h < EPI_GROUPS; ++h) tc_ld_landed(r[h]);
                     // this warp's reads of the accumulator are complete: hand it back to the MMA warps
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
                     if (threadIdx.x == 128) TC_TRACE(chunk, 12);
                     #pragma unroll
-                    for (int h = 0; h < 4; ++h) {
+                    for (int h = 0; h < EPI_GROUPS; ++h) {
                         float v[32];
                         #pragma unroll
                         for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[h][i]);
@@ -653,8 +663,13 @@ bool gemm_tc_eligible(int64_t M, int64_t N, int64_t K, int mode, int group_k, in
 template <int MODE, int GN>
 static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcArgs& args, int grid, cudaStream_t stream)
 {
-    { const int rc = ensure_dynamic_smem(gemm_tc_kernel<MODE, GN>, SMEM_BYTES); if (rc) return rc; }
-    gemm_tc_kernel<MODE, GN><<<grid, NTHREADS, SMEM_BYTES, stream>>>(ma, mb, args);
+    if (args.bn == 128) {
+        { const int rc = ensure_dynamic_smem(gemm_tc_kernel<MODE, GN, 128, 6>, smem_bytes(128, 6)); if (rc) return rc; }
+        gemm_tc_kernel<MODE, GN, 128, 6><<<grid, NTHREADS, smem_bytes(128, 6), stream>>>(ma, mb, args);
+    } else {
+        { const int rc = ensure_dynamic_smem(gemm_tc_kernel<MODE, GN, 256, 4>, smem_bytes(256, 4)); if (rc) return rc; }
+        gemm_tc_kernel<MODE, GN, 256, 4><<<grid, NTHREADS, smem_bytes(256, 4), stream>>>(ma, mb, args);
+    }
     HBQ_LAUNCH_CHECK("gemm_tc_kernel");
     return HBQ_OK;
 }
@@ -678,13 +693,18 @@ int gemm_tc_launch(const void* A, const void* W, void* C, int64_t M, int64_t N, 
     CUtensorMap ma, mb;
     int rc = make_map(&ma, A, M, K, BM);
     if (rc) return rc;
-    rc = make_map(&mb, W, N, K, BN);
-    if (rc) return rc;
 
     TcArgs args;
     args.C = (__half*)C; args.bias = (const __half*)bias;
     args.M = (int)M; args.N = (int)N; args.K = (int)K;
-    args.tiles_m = (int)((M + BM - 1) / BM); args.tiles_n = (int)((N + BN - 1) / BN);
+    int sms = 0;
+    { const int rc2 = device_sms(&sms); if (rc2) return rc2; }
+    args.tiles_m = (int)((M + BM - 1) / BM);
+    // 128-column tiles when 256-column ones would leave more than half of the SMs without work
+    args.bn = ((int64_t)args.tiles_m * ((N + 255) / 256) * 2 <= sms) ? 128 : 256;
+    args.tiles_n = (int)((N + args.bn - 1) / args.bn);
+    rc = make_map(&mb, W, N, K, args.bn);
+    if (rc) return rc;
     args.k_stages = (int)((K + BK - 1) / BK);
     args.chunk_k16 = (mode == HBQ_ACC_FP32) ? args.k_stages * (BK / 16) : group_k / 16;
     {
@@ -693,8 +713,6 @@ int gemm_tc_launch(const void* A, const void* W, void* C, int64_t M, int64_t N, 
         args.issuers = issuers;
     }
 
-    int sms = 0;
-    { const int rc2 = device_sms(&sms); if (rc2) return rc2; }
     const int64_t total = (int64_t)args.tiles_m * args.tiles_n;
     const int grid = (int)(total < sms ? total : sms);
 
