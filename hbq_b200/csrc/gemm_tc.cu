@@ -238,35 +238,31 @@ __device__ __forceinline__ void psum_int8_accumulate(const float* v, __half2* ac
     }
 }
 
-__device__ float tc_e3m4(float x, float scale)
-{
-    const float sg = copysignf(1.f, x), a = fabsf(x);
-    if (a == 0.f) return copysignf(0.f, x);
-    const float y = __fdiv_rn(a, scale);
-    if (y < 0.5f * 0.015625f) return 0.f;
-    if (y >= 0.25f) {
-        int e = max(-2, min(3, ilogbf(y)));
-        float p = ldexpf(1.f, e);
-        float m = nearbyintf((__fdiv_rn(y, p) - 1.f) * 16.f);
-        if (m >= 16.f) { m = 0.f; ++e; if (e > 3) { e = 3; m = 15.f; } p = ldexpf(1.f, e); }
-        return sg * fminf((1.f + m * 0.0625f) * p, 15.5f) * scale;
-    }
-    const float m = nearbyintf(y * 64.f);
-    if (m <= 0.f) return 0.f;
-    if (m >= 16.f) return sg * 0.25f * scale;
-    return sg * (m * 0.0625f) * 0.25f * scale;
-}
-
+// E3M4 partial-sum fake quantisation (gemm.cu:677-745, 810-887): scale = 2^(floor(log2 max|v|) - 3), so
+// y = |v| / scale lies in [0, 16); y is rounded (ties to even) to 4 mantissa bits with the exponent
+// clamped at -2 -- a quantum of 2^(e_y - 4), never below 1/64 -- and capped at 15.5.  In fp32 that is one
+// magic-number rounding per value with the quantum's exponent taken from the value's own exponent field.
 template <int GN>
 __device__ __forceinline__ void psum_e3m4_accumulate(const float* v, __half2* acc)
 {
     float mx = 0.f;
     #pragma unroll
-    for (int i = 0; i < GN; ++i) mx = fmaxf(mx, fabsf(v[i]));
-    const float scale = mx > 0.f ? ldexpf(1.f, ilogbf(mx) - 3) : 1.f;
+    for (int i = 0; i < GN; i += 2) mx = fmaxf(fmaxf(mx, fabsf(v[i])), fabsf(v[i + 1]));
+    const int se = mx > 0.f ? (int)((__float_as_uint(mx) >> 23) & 0xFFu) - 3 : 127;      // exponent field of the scale
+    const float cap = 15.5f * __uint_as_float((uint32_t)se << 23);
+    const int qmin = se - 6;                                                               // quantum floor: scale / 64
+    float o[GN];
     #pragma unroll
-    for (int i = 0; i < GN; i += 2)
-        acc[i >> 1] = __hadd2(acc[i >> 1], __floats2half2_rn(tc_e3m4(v[i], scale), tc_e3m4(v[i + 1], scale)));
+    for (int i = 0; i < GN; ++i) {
+        const uint32_t b = __float_as_uint(v[i]);
+        const uint32_t ab = b & 0x7FFFFFFFu;
+        const int q = max((int)(ab >> 23) - 4, qmin);                                      // exponent field of the quantum
+        const float magic = __uint_as_float(((uint32_t)(q + 23) << 23) | 0x00400000u);     // 1.5 * 2^23 quanta
+        const float r = fminf((__uint_as_float(ab) + magic) - magic, cap);
+        o[i] = __uint_as_float(__float_as_uint(r) | (b & 0x80000000u));
+    }
+    #pragma unroll
+    for (int i = 0; i < GN; i += 2) acc[i >> 1] = __hadd2(acc[i >> 1], __floats2half2_rn(o[i], o[i + 1]));
 }
 
 // Fold 32 fp32 partial sums (one TMEM load) of this thread's row into its fp16 running sums.
