@@ -160,6 +160,10 @@ struct LutArgs {
     uint16_t big_l1;          // smallest l1 pattern with l1 * max value > 65504 (fp16 overflow of deq)
     int lpm, log2lpm;         // lanes per micro-block (l2_block_size / 8) and its log2
     int log2cpr;              // log2(chunks per row) when that is a power of two (KV-cache write), else -1
+    // second candidate table of the two-table ("Mix") weight formats
+    LutPlan plan2;
+    float inv_ele_max2;
+    uint16_t big_l12;
     int iters;                // chunks per thread
     int64_t step_rows, step_chunks;   // one grid stride of chunks = step_rows rows + step_chunks chunks
 };
@@ -179,43 +183,43 @@ __device__ __forceinline__ void add2_f32_f16(float& acc_lo, float& acc_hi, uint3
 // The table is piecewise constant (a run per threshold of any candidate), so the runs' values are found
 // first and then copied out.  Ends without a barrier: callers synchronise before the first lookup.
 template <int MB>
-__device__ __forceinline__ void lut_build(const LutArgs& a, uint2* lut, int tid, int nthreads)
+__device__ __forceinline__ void lut_build(const LutPlan& plan, uint2* lut, int tid, int nthreads)
 {
     __shared__ uint16_t s_seg[LUT_MAX_SEG + 1];
     __shared__ uint2 s_segval[LUT_MAX_SEG];
     // the value of every run: one thread per run finds each candidate's level at the run's first pattern
-    for (int sidx = tid; sidx < a.plan.nseg; sidx += nthreads) {
-        const uint32_t u = a.plan.seg_start[sidx];
+    for (int sidx = tid; sidx < plan.nseg; sidx += nthreads) {
+        const uint32_t u = plan.seg_start[sidx];
         uint32_t v[LUT_MAX_CAND];
         #pragma unroll
         for (int i = 0; i < LUT_MAX_CAND; ++i) {
             int lvl = 0;
-            for (int k = 1; k < a.plan.nlev; ++k) lvl += (u >= a.plan.thr[i][k]) ? 1 : 0;     // thresholds are sorted
-            uint32_t val = a.plan.val[i][lvl];
+            for (int k = 1; k < plan.nlev; ++k) lvl += (u >= plan.thr[i][k]) ? 1 : 0;     // thresholds are sorted
+            uint32_t val = plan.val[i][lvl];
             if (MB == 1)
-                for (int h = 0; h < a.plan.nhole[i]; ++h)
-                    if (u == a.plan.hole[i][h]) val = 0;
+                for (int h = 0; h < plan.nhole[i]; ++h)
+                    if (u == plan.hole[i][h]) val = 0;
             v[i] = val;
         }
         s_seg[sidx] = (uint16_t)u;
         s_segval[sidx] = make_uint2(v[0] | (v[1] << 16), v[2] | (v[3] << 16));
     }
-    if (tid == 0) s_seg[a.plan.nseg] = 0xFFFF;
+    if (tid == 0) s_seg[plan.nseg] = 0xFFFF;
     __syncthreads();
     // fill: a thread takes consecutive entries, finds the run of its first one and walks on from there
-    const int n = a.plan.hi - a.plan.base + 1;
+    const int n = plan.hi - plan.base + 1;
     const int per = (n + nthreads - 1) / nthreads;
     const int e0 = tid * per, e1 = min(n, e0 + per);
     if (e0 < e1) {
-        const uint32_t u0 = (uint32_t)(a.plan.base + e0);
-        int lo = 0, hi = a.plan.nseg - 1;                     // largest run start <= u0 (run 0 starts at base)
+        const uint32_t u0 = (uint32_t)(plan.base + e0);
+        int lo = 0, hi = plan.nseg - 1;                     // largest run start <= u0 (run 0 starts at base)
         while (lo < hi) {
             const int mid = (lo + hi + 1) >> 1;
             if (s_seg[mid] <= u0) lo = mid; else hi = mid - 1;
         }
         int sidx = lo;
         for (int e = e0; e < e1; ++e) {
-            while ((uint32_t)(a.plan.base + e) >= s_seg[sidx + 1]) ++sidx;
+            while ((uint32_t)(plan.base + e) >= s_seg[sidx + 1]) ++sidx;
             lut[e] = s_segval[sidx];
         }
     }
@@ -354,7 +358,7 @@ __global__ void __launch_bounds__(LUT_THREADS, 2) hbq_lut_kernel(const LutArgs a
     const QArgs& q = a.q;
     const int tid = threadIdx.x;
 
-    lut_build<MB>(a, lut, tid, LUT_THREADS);
+    lut_build<MB>(a.plan, lut, tid, LUT_THREADS);
     __syncthreads();
 
     const int lane = tid & 31;
@@ -419,11 +423,23 @@ __global__ void __launch_bounds__(LUT_THREADS, 2) hbq_lut_kernel(const LutArgs a
 // One CTA of 1024 threads per SM (the candidate table is built once per SM).
 constexpr int LEAN_THREADS = 1024;
 
+// One candidate table as the chunk arithmetic sees it.
+struct LutView {
+    const uint8_t* lutb;          // the table in shared memory
+    uint32_t base2, hi2;          // first / last covered |a| pattern, in both halves
+    float inv_ele_max;
+    uint32_t big_l1;
+    const float* tab;             // the candidates (for the rare exact sign-of-zero check)
+    int nc;
+};
+
 // One 8-element chunk through the tables: xb = the chunk as packed fp16 pairs, dq = its fake-quantised
-// values (fp16 pairs, input signs).  The G lanes of a block call this together.
-template <int MB>
-__device__ __forceinline__ void lean_chunk(const LutArgs& a, const uint8_t* lutb, const uint4* s_l1c, uint32_t base2,
-                                           uint32_t hi2, int G, const uint32_t* xb, uint32_t* dq)
+// values (fp16 pairs, input signs).  The G lanes of a block call this together.  WANT_ERR: also return
+// this thread's fp32 sum of the chosen candidates' squared errors (the block total decides between
+// the two tables of a "Mix" format).
+template <int MB, bool WANT_ERR>
+__device__ __forceinline__ void lean_chunk(const LutView& t, const uint4* s_l1c, int lpm, int G, const uint32_t* xb,
+                                           uint32_t* dq, float* err)
 {
     uint32_t ax[4];
     #pragma unroll
@@ -434,7 +450,7 @@ __device__ __forceinline__ void lean_chunk(const LutArgs& a, const uint8_t* lutb
     for (int off = G >> 1; off >= 1; off >>= 1)
         mx = h2_bits(__hmax2(bits_h2(mx), bits_h2(__shfl_xor_sync(0xFFFFFFFFu, mx, off))));
     const uint32_t am16 = max(mx & 0xFFFFu, mx >> 16);
-    const float sf = __half2float(bits_h((uint16_t)am16)) * a.inv_ele_max;
+    const float sf = __half2float(bits_h((uint16_t)am16)) * t.inv_ele_max;
     uint32_t sb = (uint32_t)h_bits(__float2half_rn(sf));
     sb = min(max(sb, 0x0400u), 0x7B80u);
     const uint32_t l1b = (sb + 0x40u) & 0xFF80u;
@@ -453,18 +469,19 @@ __device__ __forceinline__ void lean_chunk(const LutArgs& a, const uint8_t* lutb
         const __half2 r = __hfma2(q0, nm2, axs);
         const __half2 q1 = __hfma2(r, rm2, q0);
         aa[p] = __hmul2(q1, post2);
-        w[p] = (h2_bits(__hmin2(__hmax2(aa[p], bits_h2(base2)), bits_h2(hi2))) - base2) << 3;
+        w[p] = (h2_bits(__hmin2(__hmax2(aa[p], bits_h2(t.base2)), bits_h2(t.hi2))) - t.base2) << 3;
     }
 
     // -- every candidate's squared error, two candidates per half2 --
     uint32_t ct01[8], ct23[8];
     float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
-    if (l1b < a.big_l1) {
+    const bool small = l1b < t.big_l1;
+    if (small) {
         #pragma unroll
         for (int j = 0; j < 8; ++j) {
             const int p = j >> 1;
             const uint32_t off = (j & 1) ? (w[p] >> 16) : (w[p] & 0xFFFFu);
-            const uint2 ent = *reinterpret_cast<const uint2*>(lutb + off);
+            const uint2 ent = *reinterpret_cast<const uint2*>(t.lutb + off);
             ct01[j] = ent.x; ct23[j] = ent.y;
             const __half2 axb = (j & 1) ? __high2half2(bits_h2(ax[p])) : __low2half2(bits_h2(ax[p]));
             const __half2 r01 = __hfma2(bits_h2(ent.x), nl1_2, axb), r23 = __hfma2(bits_h2(ent.y), nl1_2, axb);
@@ -477,7 +494,7 @@ __device__ __forceinline__ void lean_chunk(const LutArgs& a, const uint8_t* lutb
         for (int j = 0; j < 8; ++j) {
             const int p = j >> 1;
             const uint32_t off = (j & 1) ? (w[p] >> 16) : (w[p] & 0xFFFFu);
-            const uint2 ent = *reinterpret_cast<const uint2*>(lutb + off);
+            const uint2 ent = *reinterpret_cast<const uint2*>(t.lutb + off);
             ct01[j] = ent.x; ct23[j] = ent.y;
             const __half2 axb = (j & 1) ? __high2half2(bits_h2(ax[p])) : __low2half2(bits_h2(ax[p]));
             const __half2 r01 = __hsub2(axb, __hmul2(bits_h2(ent.x), l1_2));
@@ -486,7 +503,7 @@ __device__ __forceinline__ void lean_chunk(const LutArgs& a, const uint8_t* lutb
             add2_f32_f16(acc2, acc3, h2_bits(__hmul2(r23, r23)));
         }
     }
-    for (int off = a.lpm >> 1; off >= 1; off >>= 1) {
+    for (int off = lpm >> 1; off >= 1; off >>= 1) {
         acc0 += __shfl_xor_sync(0xFFFFFFFFu, acc0, off); acc1 += __shfl_xor_sync(0xFFFFFFFFu, acc1, off);
         acc2 += __shfl_xor_sync(0xFFFFFFFFu, acc2, off); acc3 += __shfl_xor_sync(0xFFFFFFFFu, acc3, off);
     }
@@ -503,14 +520,21 @@ __device__ __forceinline__ void lean_chunk(const LutArgs& a, const uint8_t* lutb
     #pragma unroll
     for (int p = 0; p < 4; ++p) {
         const uint32_t ra = best < 2 ? ct01[2 * p] : ct23[2 * p], rb = best < 2 ? ct01[2 * p + 1] : ct23[2 * p + 1];
-        const __half2 d = __hmul2(bits_h2(__byte_perm(ra, rb, psel)), l1_2);
+        const __half2 ctw = bits_h2(__byte_perm(ra, rb, psel));
+        const __half2 d = __hmul2(ctw, l1_2);
         dq[p] = h2_bits(d) | (xb[p] & 0x80008000u);
+        if (WANT_ERR) {
+            const __half2 r = small ? __hfma2(ctw, nl1_2, bits_h2(ax[p])) : __hsub2(bits_h2(ax[p]), d);
+            float e0 = 0.f, e1 = 0.f;
+            add2_f32_f16(e0, e1, h2_bits(__hmul2(r, r)));
+            *err += e0; *err += e1;
+        }
     }
     // The reference returns +0 (not -0) when fp16(a / t) is exactly zero.  Only quotients a below
     // 2^-19 can do that; deciding it needs the exact a, where the scaled division may be off: rare.
     const __half2 amin = __hmin2(__hmin2(aa[0], aa[1]), __hmin2(aa[2], aa[3]));
     if (__hle2_mask(amin, bits_h2(0x00200020u)) != 0u) {
-        const float l1f = __half2float(bits_h((uint16_t)l1b)), t = a.q.tab[0][best < a.q.nc ? best : a.q.nc - 1];
+        const float l1f = __half2float(bits_h((uint16_t)l1b)), tc = t.tab[best < t.nc ? best : t.nc - 1];
         #pragma unroll
         for (int p = 0; p < 4; ++p)
             #pragma unroll
@@ -518,7 +542,7 @@ __device__ __forceinline__ void lean_chunk(const LutArgs& a, const uint8_t* lutb
                 const uint32_t abits = (h2_bits(aa[p]) >> (16 * h)) & 0xFFFFu;
                 if (abits <= 0x0020u && ((xb[p] >> (16 * h)) & 0x8000u)) {
                     const float xf = __half2float(bits_h((uint16_t)(ax[p] >> (16 * h))));
-                    if (rh(__fdiv_rn(rh(__fdiv_rn(xf, l1f)), t)) == 0.f) dq[p] &= ~(0x8000u << (16 * h));
+                    if (rh(__fdiv_rn(rh(__fdiv_rn(xf, l1f)), tc)) == 0.f) dq[p] &= ~(0x8000u << (16 * h));
                 }
             }
     }
@@ -544,23 +568,33 @@ __device__ __forceinline__ void l1_table_build(const LutArgs& a, uint4* s_l1c, i
 // KV: the K / post-RoPE Q cache write on the same fast path -- a row is one (token, head) vector of
 // D = K elements (D a power of two <= 256, fp16), RoPE is applied on load and the row is stored at its
 // (batch, head, token) position.
-template <int MB, bool IN_BF16, bool OUT_BF16, bool KV>
+// MIX: the two-table weight formats -- both tables are evaluated (each with its own block scale) and
+// the one with the smaller fp16 total of the chosen candidates' squared errors over the block wins,
+// the first on ties (src/quantizer.py:806-840).
+template <int MB, bool IN_BF16, bool OUT_BF16, bool KV, bool MIX>
 __global__ void __launch_bounds__(LEAN_THREADS, 1) hbq_lut_lean_kernel(const LutArgs a)
 {
     extern __shared__ __align__(16) uint2 lut[];
     __shared__ uint4 s_l1c[256];             // per E5M3 scale (pattern >> 7): {pre2, post2, -m2, 1/m 2}
     const int tid = threadIdx.x;
-    lut_build<MB>(a, lut, tid, LEAN_THREADS);
+    lut_build<MB>(a.plan, lut, tid, LEAN_THREADS);
     l1_table_build(a, s_l1c, tid);
+    const int n0 = a.plan.hi - a.plan.base + 1;
+    if (MIX) {
+        __syncthreads();                     // the builder's staging arrays are reused
+        lut_build<MB>(a.plan2, lut + n0, tid, LEAN_THREADS);
+    }
     __syncthreads();
 
-    const uint32_t base2 = (uint32_t)a.plan.base * 0x00010001u, hi2 = (uint32_t)a.plan.hi * 0x00010001u;
+    const LutView view0 = {reinterpret_cast<const uint8_t*>(lut), (uint32_t)a.plan.base * 0x00010001u,
+                           (uint32_t)a.plan.hi * 0x00010001u, a.inv_ele_max, a.big_l1, a.q.tab[0], a.q.nc};
+    const LutView view1 = {reinterpret_cast<const uint8_t*>(lut + n0), (uint32_t)a.plan2.base * 0x00010001u,
+                           (uint32_t)a.plan2.hi * 0x00010001u, a.inv_ele_max2, a.big_l12, a.q.tab[1], a.q.nc};
     const uint4* __restrict__ in = reinterpret_cast<const uint4*>(a.q.x);
     uint4* __restrict__ out = reinterpret_cast<uint4*>(a.q.deq);
     const int64_t total = a.q.total_chunks, stride = (int64_t)gridDim.x * LEAN_THREADS;
     const int lane = tid & 31;
     const int G = a.q.G;
-    const uint8_t* lutb = reinterpret_cast<const uint8_t*>(lut);
 
     int64_t ci = (int64_t)blockIdx.x * LEAN_THREADS + tid;
     uint4 raw = make_uint4(0u, 0u, 0u, 0u);
@@ -589,7 +623,22 @@ __global__ void __launch_bounds__(LEAN_THREADS, 1) hbq_lut_lean_kernel(const Lut
                 xb[p] = h2_bits(__floats2half2_rn(__uint_as_float(xb[p] << 16), __uint_as_float(xb[p] & 0xFFFF0000u)));
         }
         uint32_t dq[4];
-        lean_chunk<MB>(a, lutb, s_l1c, base2, hi2, G, xb, dq);
+        if (!MIX) {
+            lean_chunk<MB, false>(view0, s_l1c, a.lpm, G, xb, dq, nullptr);
+        } else {
+            uint32_t dq1[4];
+            float e0 = 0.f, e1 = 0.f;
+            lean_chunk<MB, true>(view0, s_l1c, a.lpm, G, xb, dq, &e0);
+            lean_chunk<MB, true>(view1, s_l1c, a.lpm, G, xb, dq1, &e1);
+            for (int off = G >> 1; off >= 1; off >>= 1) {
+                e0 += __shfl_xor_sync(0xFFFFFFFFu, e0, off);
+                e1 += __shfl_xor_sync(0xFFFFFFFFu, e1, off);
+            }
+            if (rh(e1) < rh(e0)) {
+                #pragma unroll
+                for (int p = 0; p < 4; ++p) dq[p] = dq1[p];
+            }
+        }
         if (valid) {
             if (OUT_BF16) {
                 #pragma unroll
@@ -609,13 +658,20 @@ template <int MB>
 static int launch_lean(const LutArgs& a, int grid, size_t smem, cudaStream_t stream)
 {
     #define HBQ_LAUNCH_LEAN(IB, OB, KVW)                                                                                              \
-        { const int rc_ = ensure_dynamic_smem(hbq_lut_lean_kernel<MB, IB, OB, KVW>, smem); if (rc_) return rc_; }                    \
-        hbq_lut_lean_kernel<MB, IB, OB, KVW><<<grid, LEAN_THREADS, smem, stream>>>(a);
+        { const int rc_ = ensure_dynamic_smem(hbq_lut_lean_kernel<MB, IB, OB, KVW, false>, smem); if (rc_) return rc_; }             \
+        hbq_lut_lean_kernel<MB, IB, OB, KVW, false><<<grid, LEAN_THREADS, smem, stream>>>(a);
+    #define HBQ_LAUNCH_LEAN_MIX(IB, OB)                                                                                               \
+        { const int rc_ = ensure_dynamic_smem(hbq_lut_lean_kernel<MB, IB, OB, false, true>, smem); if (rc_) return rc_; }            \
+        hbq_lut_lean_kernel<MB, IB, OB, false, true><<<grid, LEAN_THREADS, smem, stream>>>(a);
     const bool kvw = a.q.rope_cos || a.q.perm_T > 0 || a.q.k_center;
-    if (kvw) { if (a.q.out_bf16) { HBQ_LAUNCH_LEAN(false, true, true) } else { HBQ_LAUNCH_LEAN(false, false, true) } }
+    if (a.q.nscheme == 2) {
+        if (a.q.in_bf16) { if (a.q.out_bf16) { HBQ_LAUNCH_LEAN_MIX(true, true) } else { HBQ_LAUNCH_LEAN_MIX(true, false) } }
+        else { if (a.q.out_bf16) { HBQ_LAUNCH_LEAN_MIX(false, true) } else { HBQ_LAUNCH_LEAN_MIX(false, false) } }
+    } else if (kvw) { if (a.q.out_bf16) { HBQ_LAUNCH_LEAN(false, true, true) } else { HBQ_LAUNCH_LEAN(false, false, true) } }
     else if (a.q.in_bf16) { if (a.q.out_bf16) { HBQ_LAUNCH_LEAN(true, true, false) } else { HBQ_LAUNCH_LEAN(true, false, false) } }
     else { if (a.q.out_bf16) { HBQ_LAUNCH_LEAN(false, true, false) } else { HBQ_LAUNCH_LEAN(false, false, false) } }
     #undef HBQ_LAUNCH_LEAN
+    #undef HBQ_LAUNCH_LEAN_MIX
     HBQ_LAUNCH_CHECK("hbq_lut_lean_kernel");
     return HBQ_OK;
 }
@@ -623,13 +679,12 @@ static int launch_lean(const LutArgs& a, int grid, size_t smem, cudaStream_t str
 // ---- V-cache write: quantisation along the token axis (tile machinery in vcache_dev.cuh) ----------
 template <int MB>
 struct LutChunkFn {
-    const LutArgs& a;
-    const uint8_t* lutb;
+    LutView view;
     const uint4* s_l1c;
-    uint32_t base2, hi2;
+    int lpm, G;
     __device__ __forceinline__ void operator()(const uint32_t* xb, uint32_t* dq) const
     {
-        lean_chunk<MB>(a, lutb, s_l1c, base2, hi2, a.q.G, xb, dq);
+        lean_chunk<MB, false>(view, s_l1c, lpm, G, xb, dq, nullptr);
     }
 };
 
@@ -641,11 +696,12 @@ __global__ void __launch_bounds__(V_THREADS, 2) hbq_lut_v_kernel(const LutArgs a
     const int n = a.plan.hi - a.plan.base + 1;
     uint32_t* tile = reinterpret_cast<uint32_t*>(lut + ((n + 1) & ~1));   // 16-byte aligned, after the candidate table
     __shared__ uint4 s_l1c[256];
-    lut_build<MB>(a, lut, tid, V_THREADS);
+    lut_build<MB>(a.plan, lut, tid, V_THREADS);
     l1_table_build(a, s_l1c, tid);
     __syncthreads();
-    const LutChunkFn<MB> fn = {a, reinterpret_cast<const uint8_t*>(lut), s_l1c,
-                               (uint32_t)a.plan.base * 0x00010001u, (uint32_t)a.plan.hi * 0x00010001u};
+    const LutChunkFn<MB> fn = {{reinterpret_cast<const uint8_t*>(lut), (uint32_t)a.plan.base * 0x00010001u,
+                                (uint32_t)a.plan.hi * 0x00010001u, a.inv_ele_max, a.big_l1, a.q.tab[0], a.q.nc},
+                               s_l1c, a.lpm, a.q.G};
     v_cache_tiles(v, tile, fn);
 }
 
@@ -726,6 +782,14 @@ static bool fill_lut_args(const QArgs& qa, int mb, LutArgs* out)
     LutArgs& a = *out;
     memset(&a, 0, sizeof(a));
     if (!get_plan(mb, qa.tab[0], qa.nc, &a)) return false;
+    if (qa.nscheme == 2) {                     // second table: through a scratch copy, then into the plan2 fields
+        LutArgs b;
+        memset(&b, 0, sizeof(b));
+        if (!get_plan(mb, qa.tab[1], qa.nc, &b)) return false;
+        a.plan2 = b.plan;
+        a.big_l12 = b.big_l1;
+        a.inv_ele_max2 = 1.f / qa.ele_max[1];
+    }
     a.q = qa;
     a.lpm = qa.f.l2_block_size / 8;
     while ((1 << a.log2lpm) < a.lpm) ++a.log2lpm;
@@ -737,7 +801,7 @@ int hbq_lut_try_launch(const QArgs& qa, int mb, cudaStream_t stream, bool* launc
 {
     *launched = false;
     const int L = qa.f.l2_block_size;
-    if (qa.nscheme != 1 || qa.nc > LUT_MAX_CAND || !qa.scale_fast_e5m3 || L < 8 || mb < 1 || mb > 3) return HBQ_OK;
+    if (qa.nscheme > 2 || qa.nc > LUT_MAX_CAND || !qa.scale_fast_e5m3 || L < 8 || mb < 1 || mb > 3) return HBQ_OK;
     LutArgs a;
     if (!fill_lut_args(qa, mb, &a)) return HBQ_OK;
 
@@ -750,10 +814,11 @@ int hbq_lut_try_launch(const QArgs& qa, int mb, cudaStream_t stream, bool* launc
     a.log2cpr = -1;
     if ((q.cpr & (q.cpr - 1)) == 0) { a.log2cpr = 0; while ((1ll << a.log2cpr) < q.cpr) ++a.log2cpr; }
     // the K-cache write takes the fast path for fp16 rows of a power-of-two length
-    if (q.deq && !side_out && q.aligned && q.K == q.Kp && (!kvw || (!q.in_bf16 && a.log2cpr >= 0))) {
+    const bool mix = q.nscheme == 2;
+    if (q.deq && !side_out && q.aligned && q.K == q.Kp && (!kvw || (!mix && !q.in_bf16 && a.log2cpr >= 0))) {
         const int64_t need = (qa.total_chunks + LEAN_THREADS - 1) / LEAN_THREADS;
         const int grid = (int)(need < sms ? need : sms);
-        const size_t smem = (size_t)(a.plan.hi - a.plan.base + 1) * sizeof(uint2);
+        const size_t smem = (size_t)((a.plan.hi - a.plan.base + 1) + (mix ? a.plan2.hi - a.plan2.base + 1 : 0)) * sizeof(uint2);
         int rc;
         switch (mb) {
             case 1: rc = launch_lean<1>(a, grid, smem, stream); break;
@@ -763,6 +828,7 @@ int hbq_lut_try_launch(const QArgs& qa, int mb, cudaStream_t stream, bool* launc
         if (rc == HBQ_OK) *launched = true;
         return rc;
     }
+    if (mix) return HBQ_OK;                    // two tables: only the lean kernel; the arithmetic kernel serves the rest
     const int64_t need = (qa.total_chunks + LUT_THREADS - 1) / LUT_THREADS;
     const int grid = (int)(need < 2 * sms ? need : 2 * sms);
     a.iters = (int)((need + grid - 1) / grid);

@@ -86,8 +86,11 @@ def test_quantizers_match_reference_golden(name):
     g = load_npz("quantizers.npz")
     extra = {"keep_l2_scale": True} if spec["kind"] == "hbq" else {}
     q = make_quantizer(spec, **extra)
+    q_plain = make_quantizer(spec)            # no side outputs: the kernels specialised for that case
     for k in sorted(f[3:] for f in g.files if f.startswith("in/")):
         x = dev(g[f"in/{k}"])
+        n = int((hbits(q_plain.q(x)) != g[f"out/{name}/{k}/deq"]).sum())
+        assert n == 0, f"{name}/{k}: {n} deq mismatches without side outputs"
         y = q.q(x)
         assert y.shape == x.shape and y.dtype == x.dtype
         n = int((hbits(y) != g[f"out/{name}/{k}/deq"]).sum())
