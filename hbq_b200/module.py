@@ -77,10 +77,10 @@ class QLinear(nn.Linear):
         Rows are cut into ``row_chunks`` pieces that travel through three streams: host-to-device
         copy, quantize + GEMM, device-to-host copy of the result, with two staging buffers, so the
         two PCIe directions and the kernels overlap within a call and across consecutive calls.
-        Returns ``out_host`` (pinned fp16 ``[rows, out_features]``).  With ``wait=False`` the
-        calling stream is not made to wait for the last copy; ``(out_host, event)`` is returned and
-        the caller synchronises on the event before reading, which lets the next call's uploads
-        start under this call's downloads."""
+        Returns ``out_host`` (pinned fp16 ``[rows, out_features]``) after the host has waited for
+        the last download, so the caller may read it at once.  With ``wait=False`` nothing waits;
+        ``(out_host, event)`` is returned and the caller synchronises on the event before reading,
+        which lets the next call's uploads start under this call's downloads."""
         dev = self.weight.device
         if x_host.is_cuda or x_host.dim() != 2 or x_host.shape[1] != self.in_features:
             raise ValueError("forward_host expects a host tensor of shape [rows, in_features]")
@@ -130,6 +130,6 @@ class QLinear(nn.Linear):
         if done is None:
             return out_host if wait else (out_host, start)
         if wait:
-            cur.wait_event(done)
+            done.synchronize()
             return out_host
         return out_host, done
