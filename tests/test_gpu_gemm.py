@@ -77,6 +77,36 @@ def test_tensor_core_vs_oracle_small(oracle, shape, mode):
     assert torch.equal(got_kn.view(torch.int16), got.view(torch.int16))
 
 
+@pytest.mark.parametrize("mode", [m for m in MODES if m[1] != 1], ids=lambda m: f"{m[0]}-{m[2]}-{m[3]}")
+def test_tensor_core_exact_on_integer_operands(oracle, mode):
+    """Small-integer operands make every chunk sum exact in fp32 whatever the summation order, so the
+    tensor-core kernel must equal the oracle bit for bit: this pins the epilogue arithmetic itself
+    (scales, ties-to-even rounding, the +-127 clamp of the INT8 partial sums, the E3M4 grid)."""
+    import hbq_b200 as H
+    _, m, gk, gn = mode
+    M, N, K = 256, 512, 512
+    rng = np.random.default_rng(99)
+    Ai = rng.integers(-8, 9, size=(M, K))
+    Wi = rng.integers(-8, 9, size=(N, K))
+    if m == 3:
+        # the case the clamp exists for: a partial sum that rounds to 128 steps of its group's scale
+        g = gk
+        hits = 0
+        for c in range(K // g):
+            ps = Ai[:, c * g:(c + 1) * g] @ Wi[:, c * g:(c + 1) * g].T
+            mx = np.abs(ps).reshape(M, N // gn, gn).max(axis=2)
+            scale = 2.0 ** (np.floor(np.log2(np.maximum(mx, 1))) - 6)
+            hits += int((np.rint(mx / scale) == 128).sum())
+        assert hits > 0, "inputs do not exercise the clamp"
+    A = Ai.astype(np.float16)
+    W = Wi.astype(np.float16)
+    ref = oracle.gemm(A, np.ascontiguousarray(W.T), m, gk, gn)
+    got = H.gemm(dev(A), dev(W), m, gk, gn, b_is_nk=True)
+    torch.cuda.synchronize()
+    assert H.gemm_status() == 0
+    assert np.array_equal(bits(got.cpu().numpy()), bits(ref)), mode
+
+
 def _hbq_operands(M, N, K, seed):
     """HBQ-E fake-quantised activation and weight (the operands of the benchmark GEMM)."""
     f = load_formats()
