@@ -38,3 +38,53 @@ def k_range(k: int, rank: int, world: int, block: int = 128) -> Tuple[int, int]:
         raise ValueError(f"K={k} is not a multiple of {block}")
     b, e = row_range(k // block, rank, world)
     return b * block, e * block
+
+
+def bind_host_to_device(device_index: int) -> dict:
+    """Keep this process's threads and its future host allocations (pinned staging buffers above
+    all) on the NUMA node that the GPU's PCIe slot hangs off, so that host<->device copies do not
+    cross the socket interconnect.  One process per GPU calls it once, before it allocates pinned
+    memory.  Best effort and process-local: CPU affinity is narrowed to the node's CPUs that the
+    process may already use, and the memory policy becomes "prefer that node"; whatever the
+    platform refuses is skipped.  Returns what was done, for the caller's log."""
+    import ctypes
+    import os
+    import platform
+
+    import torch
+
+    info = {"numa_node": None, "cpus_bound": 0, "mempolicy": False}
+    try:
+        p = torch.cuda.get_device_properties(device_index)
+        bdf = f"{p.pci_domain_id:04x}:{p.pci_bus_id:02x}:{p.pci_device_id:02x}.0"
+        with open(f"/sys/bus/pci/devices/{bdf}/numa_node") as f:
+            node = int(f.read().strip())
+    except (OSError, ValueError, AttributeError, RuntimeError):
+        return info
+    if node < 0:
+        return info
+    info["numa_node"] = node
+    try:
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+            cpus = set()
+            for part in f.read().strip().split(","):
+                if part:
+                    lo, _, hi = part.partition("-")
+                    cpus.update(range(int(lo), int(hi or lo) + 1))
+        mine = os.sched_getaffinity(0) & cpus
+        if mine:
+            os.sched_setaffinity(0, mine)
+            info["cpus_bound"] = len(mine)
+    except (OSError, ValueError, AttributeError):
+        pass
+    try:
+        nr = {"x86_64": 238, "aarch64": 237}.get(platform.machine())
+        if nr is not None and node < 64:
+            libc = ctypes.CDLL(None, use_errno=True)
+            mask = ctypes.c_ulong(1 << node)
+            MPOL_PREFERRED = 1
+            rc = libc.syscall(ctypes.c_long(nr), ctypes.c_int(MPOL_PREFERRED), ctypes.byref(mask), ctypes.c_ulong(65))
+            info["mempolicy"] = rc == 0
+    except (OSError, AttributeError):
+        pass
+    return info
