@@ -209,3 +209,32 @@ def test_full_size_properties():
     bound = x.float().abs().view(8192, -1, 128).amax(-1, keepdim=True) * (0.5 / 7) * 2.5 * 1.07 + 1e-7
     assert bool((err <= bound).all())
     assert packed.nbytes() == x.numel() * 5 // 8 + x.numel() // 128 + x.numel() // 8 * 2 // 8
+
+
+@pytest.mark.parametrize("name", ["hbq_e_act", "hbq_a_wgt", "mxfp4", "nvfp4"])
+def test_more_than_2_31_elements(name):
+    """A tensor of 2^31 + 2^20 elements (4.3 GB of fp16): element offsets pass 2^31.  Blocks are
+    independent, so slices quantised on their own must give the same bits as the same slices of the
+    whole; the packed path (codes, scales, side outputs) is checked by its round trip on the tail."""
+    import hbq_b200 as H
+    q = make_quantizer(load_formats()[name])
+    K = 8192
+    rows = (2 ** 31 + 2 ** 20) // K
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x = torch.empty((rows, K), dtype=torch.float16, device="cuda")
+    for r0 in range(0, rows, 32768):                     # filled in pieces: no fp32 copy of the whole
+        n = min(32768, rows - r0)
+        x[r0:r0 + n] = torch.randn((n, K), device="cuda", generator=g).to(torch.float16)
+    y = q.q(x)
+    assert y.shape == x.shape
+    for r0 in (0, rows // 2 - 64, 2 ** 31 // K - 64, rows - 128):       # head, middle, across 2^31, tail
+        part = q.q(x[r0:r0 + 128].contiguous())
+        assert torch.equal(part.view(torch.int16), y[r0:r0 + 128].view(torch.int16)), (name, r0)
+    del y
+    packed, yd = q.quantize_packed(x, with_deq=True)
+    tail = q.q(x[rows - 128:].contiguous())
+    assert torch.equal(yd[rows - 128:].view(torch.int16), tail.view(torch.int16))
+    back = H.dequantize_packed(packed)
+    assert torch.equal(back[rows - 128:].view(torch.int16), tail.view(torch.int16))
+    assert torch.equal(back[2 ** 31 // K - 64:2 ** 31 // K + 64].view(torch.int16),
+                       yd[2 ** 31 // K - 64:2 ** 31 // K + 64].view(torch.int16))
