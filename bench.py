@@ -373,6 +373,79 @@ def run_sweep(args):
             timed(lambda: kvcache.write_v_cache(k, Hh, q), k.numel(), "v_write (token-axis quantize + layout)", shape)
 
 
+def run_tp_mlp(args, rank: int, world: int, local_rank: int):
+    """`--tp-mlp`: the MLP block of configs[3] (Llama-3-8B shapes: hidden 4096, intermediate 14336; 8 x 2048
+    tokens) with HBQ-A activation quantizers and fp32 accumulation, tensor-parallel over the ranks: gate / up
+    column-parallel, down row-parallel with its all-reduce.  Strong scaling: the token batch is fixed.  One
+    JSON line from rank 0 (device time, max over ranks)."""
+    import torch
+    import torch.distributed as dist
+    import hbq_b200 as H
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    hidden, inter, tokens = 4096, 14336, 8 * 2048
+    act = dict(block_size=128, ebit=2, mbit=2, sc_ebit=5, sc_mbit=3, l2_block_size=8, l2_sc_bit=2, l2_scheme="SIG-1")
+    wgt = dict(block_size=128, ebit=2, mbit=1, sc_ebit=5, sc_mbit=3, l2_block_size=8, l2_sc_bit=2, l2_scheme="Mix")
+    g = torch.Generator(device=dev).manual_seed(11)       # the same full tensors on every rank, sliced locally
+
+    def mk(cls, i, o, **kw):
+        lin = cls(i, o, bias=False, device=dev, dtype=torch.float16, **kw)
+        w = (0.02 * torch.randn((o, i), device=dev, generator=g)).half()
+        lin.load_full(H.HBQQuantizer(**wgt).q(w))
+        lin.aq = H.HBQQuantizer(**act)
+        return lin
+
+    gate = mk(H.ColumnParallelQLinear, hidden, inter, multiple=128)
+    up = mk(H.ColumnParallelQLinear, hidden, inter, multiple=128)
+    down = mk(H.RowParallelQLinear, inter, hidden, row_chunks=4)
+    x = torch.randn((tokens, hidden), device=dev, generator=g).half()
+
+    def step():
+        with torch.no_grad():
+            xq = gate.aq(x)                                   # one quantize feeds both projections
+            a = H.blockquant_ext.gemm_fp32_accum(xq, gate.weight, b_is_nk=True)
+            b = H.blockquant_ext.gemm_fp32_accum(xq, up.weight, b_is_nk=True)
+            return down(torch.nn.functional.silu(a) * b)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        y = step()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms /= args.steps
+    flops = 3 * 2.0 * tokens * hidden * inter
+    if H.gemm_status() != 0:
+        raise RuntimeError("tensor-core GEMM reported an expired wait")
+    if rank == 0:
+        print(json.dumps({"metric": "tp_mlp_tflops", "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": world,
+                          "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+                          "scaling": "strong", "dtype": "f16", "data": "synthetic",
+                          "config": {"workload": "configs[3] MLP block: 16384 tokens, hidden 4096, intermediate 14336, HBQ-A "
+                                                 "activations and weights, fp32 accumulation",
+                                     "parallelism": f"tp{world}: gate/up column-parallel, down row-parallel, all-reduce of "
+                                                    f"[16384,4096] fp16 in {down.row_chunks} pieces under the GEMM"},
+                          "finite": bool(torch.isfinite(y).all().item())}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -383,6 +456,8 @@ def main():
     ap.add_argument("--sweep", nargs="?", const="all", default=None,
                     help="instead of the benchmark line: quantize sweep of configs[2] and the KV-cache writes "
                          "(all cases, or one: " + ", ".join(SWEEP_FORMATS) + ", k_write, v_write)")
+    ap.add_argument("--tp-mlp", action="store_true",
+                    help="instead of the benchmark line: the tensor-parallel MLP block of configs[3] over the launched ranks")
     args = ap.parse_args()
     if args.sweep is not None:
         run_sweep(args)
@@ -390,6 +465,9 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.tp_mlp:
+        run_tp_mlp(args, rank, world, local_rank)
+        return
     if args.impl == "reference":
         run_reference(args, rank, world)
     else:

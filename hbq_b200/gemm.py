@@ -12,8 +12,10 @@ from .quantizer import _ptr, _stream_ptr
 
 
 def gemm(a: torch.Tensor, b: torch.Tensor, mode: int, group_k: int = 0, group_n: int = 0,
-         bias: Optional[torch.Tensor] = None, b_is_nk: bool = False, force_simt: bool = False) -> torch.Tensor:
-    """``hbq_gemm``: a [M, K] fp16, b [K, N] (or [N, K] when ``b_is_nk``) fp16 -> [M, N] fp16."""
+         bias: Optional[torch.Tensor] = None, b_is_nk: bool = False, force_simt: bool = False,
+         out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``hbq_gemm``: a [M, K] fp16, b [K, N] (or [N, K] when ``b_is_nk``) fp16 -> [M, N] fp16.
+    ``out``: write into this contiguous fp16 [M, N] tensor instead of a new one."""
     if a.dtype != torch.float16 or b.dtype != torch.float16:
         raise RuntimeError("A must be fp16" if a.dtype != torch.float16 else "B must be fp16")
     if a.dim() != 2 or b.dim() != 2:
@@ -30,7 +32,13 @@ def gemm(a: torch.Tensor, b: torch.Tensor, mode: int, group_k: int = 0, group_n:
     b = b.contiguous()
     if bias is not None:
         bias = bias.to(device=a.device, dtype=torch.float16).contiguous()
-    c = torch.empty((M, N), dtype=torch.float16, device=a.device)
+    if out is None:
+        c = torch.empty((M, N), dtype=torch.float16, device=a.device)
+    else:
+        if (out.dtype != torch.float16 or tuple(out.shape) != (M, N) or out.device != a.device
+                or not out.is_contiguous()):
+            raise RuntimeError("out must be a contiguous fp16 [M, N] tensor on A's device")
+        c = out
     L = _lib.lib()
     with _lib.device_guard(a.device):
         stream = _stream_ptr(a.device)

@@ -23,7 +23,7 @@ class FP16AccumMatMul(nn.Module):
         self.group_size = group_size
         self.quant_block_size = quant_block_size
 
-    def forward(self, x, w, bias=None) -> torch.Tensor:
+    def forward(self, x, w, bias=None, out=None) -> torch.Tensor:
         orig_shape = x.shape
         x2d = x.reshape(-1, x.shape[-1])
         if x2d.dtype != torch.float16:
@@ -36,13 +36,13 @@ class FP16AccumMatMul(nn.Module):
                 raise ValueError(f"Invalid group size: {self.group_size}")
             if self.quant_block_size not in [4, 8, 16, 32]:
                 raise ValueError(f"Invalid quant block size: {self.quant_block_size}")
-            out2d = ext.gemm_blockquant_mxint8(x2d, wh, self.group_size, self.quant_block_size, b_is_nk=True)
+            out2d = ext.gemm_blockquant_mxint8(x2d, wh, self.group_size, self.quant_block_size, b_is_nk=True, out=out)
         elif self.group_size is not None:
             if self.group_size not in [4, 8, 16, 32, 64, 128]:
                 raise ValueError(f"Invalid group size: {self.group_size}")
-            out2d = ext.gemm_fp16_grouped_accum(x2d, wh, self.group_size, b_is_nk=True)
+            out2d = ext.gemm_fp16_grouped_accum(x2d, wh, self.group_size, b_is_nk=True, out=out)
         else:
-            out2d = ext.gemm_fp16_accum(x2d, wh, b_is_nk=True)
+            out2d = ext.gemm_fp16_accum(x2d, wh, b_is_nk=True, out=out)
 
         if bias is not None:
             out2d = out2d + bias
