@@ -400,7 +400,7 @@ def run_tp_mlp(args, rank: int, world: int, local_rank: int):
 
     gate = mk(H.ColumnParallelQLinear, hidden, inter, multiple=128)
     up = mk(H.ColumnParallelQLinear, hidden, inter, multiple=128)
-    down = mk(H.RowParallelQLinear, inter, hidden, row_chunks=4)
+    down = mk(H.RowParallelQLinear, inter, hidden, row_chunks=args.tp_row_chunks, reserve_sms=args.tp_reserve_sms)
     x = torch.randn((tokens, hidden), device=dev, generator=g).half()
 
     def step():
@@ -440,7 +440,7 @@ def run_tp_mlp(args, rank: int, world: int, local_rank: int):
                           "config": {"workload": "configs[3] MLP block: 16384 tokens, hidden 4096, intermediate 14336, HBQ-A "
                                                  "activations and weights, fp32 accumulation",
                                      "parallelism": f"tp{world}: gate/up column-parallel, down row-parallel, all-reduce of "
-                                                    f"[16384,4096] fp16 in {down.row_chunks} pieces under the GEMM"},
+                                                    f"[16384,4096] fp16 in {down._pieces(tokens)} piece(s)"},
                           "finite": bool(torch.isfinite(y).all().item())}))
     if world > 1:
         dist.destroy_process_group()
@@ -458,6 +458,11 @@ def main():
                          "(all cases, or one: " + ", ".join(SWEEP_FORMATS) + ", k_write, v_write)")
     ap.add_argument("--tp-mlp", action="store_true",
                     help="instead of the benchmark line: the tensor-parallel MLP block of configs[3] over the launched ranks")
+    ap.add_argument("--tp-row-chunks", type=int, default=None,
+                    help="--tp-mlp: pieces the row-parallel layer cuts its rows into (1 = all-reduce after the whole GEMM; "
+                         "default: chosen from the per-rank GEMM size)")
+    ap.add_argument("--tp-reserve-sms", type=int, default=0,
+                    help="--tp-mlp: SMs the row-parallel GEMM leaves free for the all-reduce running beside it")
     args = ap.parse_args()
     if args.sweep is not None:
         run_sweep(args)

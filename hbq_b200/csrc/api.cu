@@ -54,6 +54,7 @@ int gemm_tc_launch(const void*, const void*, void*, int64_t, int64_t, int64_t, i
 int transpose_launch(const void*, void*, int64_t, int64_t, cudaStream_t);
 int gemm_tc_status(int*);
 int gemm_tc_status_reset();
+int gemm_tc_reserve_sms(int n);
 
 // ------------------------------------------------------------------------------------------
 // Packed codes -> fake-quantised fp16/bf16 tensor.
@@ -292,6 +293,7 @@ int hbq_gemm_status(int* status_host)
     return gemm_tc_status(status_host);
 }
 int hbq_gemm_status_reset(void) { return gemm_tc_status_reset(); }
+int hbq_gemm_reserve_sms(int n) { return gemm_tc_reserve_sms(n); }
 
 const char* hbq_error_string(int code)
 {

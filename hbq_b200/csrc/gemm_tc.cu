@@ -28,6 +28,7 @@
 #include <cuda.h>
 #include <math.h>
 #include <stdlib.h>
+#include <atomic>
 #include <mutex>
 
 namespace hbq {
@@ -678,6 +679,9 @@ int transpose_launch(const void* in, void* out, int64_t R, int64_t Ccols, cudaSt
     return HBQ_OK;
 }
 
+// SMs that launches leave free for a kernel of another stream (hbq_gemm_reserve_sms)
+static std::atomic<int> g_reserved_sms{0};
+
 // A [M,K], W [N,K], both fp16 row-major and 16-byte aligned.
 int gemm_tc_launch(const void* A, const void* W, void* C, int64_t M, int64_t N, int64_t K, int mode,
                    int group_k, int group_n, const void* bias, cudaStream_t stream)
@@ -710,7 +714,8 @@ int gemm_tc_launch(const void* A, const void* W, void* C, int64_t M, int64_t N, 
     }
 
     const int64_t total = (int64_t)args.tiles_m * args.tiles_n;
-    const int grid = (int)(total < sms ? total : sms);
+    const int usable = sms - g_reserved_sms.load() > 0 ? sms - g_reserved_sms.load() : 1;
+    const int grid = (int)(total < usable ? total : usable);
 
     switch (mode) {
         case HBQ_ACC_FP32: return launch_tc<HBQ_ACC_FP32, 32>(ma, mb, args, grid, stream);
@@ -731,6 +736,11 @@ int gemm_tc_launch(const void* A, const void* W, void* C, int64_t M, int64_t N, 
             }
     }
     return HBQ_ERR_ARG;
+}
+
+int gemm_tc_reserve_sms(int n)
+{
+    return g_reserved_sms.exchange(n < 0 ? 0 : n);
 }
 
 int gemm_tc_status(int* host_out)

@@ -60,3 +60,9 @@ def gemm_status() -> int:
     v = ctypes.c_int(0)
     _lib.check(_lib.lib().hbq_gemm_status(ctypes.byref(v)), "hbq_gemm_status")
     return v.value
+
+
+def gemm_reserve_sms(n: int) -> int:
+    """``hbq_gemm_reserve_sms``: later tensor-core GEMM launches leave ``n`` SMs free for a kernel of
+    another stream (a collective running under the GEMM); returns the previous value."""
+    return int(_lib.lib().hbq_gemm_reserve_sms(int(n)))

@@ -25,6 +25,7 @@ import torch
 import torch.distributed as dist
 
 from . import blockquant_ext as ext
+from .gemm import gemm_reserve_sms
 from .module import QLinear
 from .ops import FP16AccumMatMul
 from .shard import column_range, k_range
@@ -75,14 +76,19 @@ _SIDE_STREAMS = {}      # device -> the stream the all-reduces of RowParallelQLi
 class RowParallelQLinear(QLinear):
     """Input features ``[k0, k1)`` of a ``[N, K]`` linear layer: ``y = sum over ranks of
     ops(aq(x[:, k0:k1]), W[:, k0:k1])`` + bias.  ``x`` is this rank's slice ``[..., k1 - k0]``.
-    ``row_chunks`` pieces of rows are reduced while the next piece is computed."""
+    ``row_chunks`` pieces of rows are reduced while the next piece is computed; ``None`` chooses the
+    count from the work: a piece must keep the GEMM busy for about the time its all-reduce takes
+    (measured on 2 and 8 B200s: cutting pays with two ranks, where this rank's GEMM is long, and
+    costs 12 % with eight, where the all-reduce outlasts the GEMM and every extra call adds latency)."""
 
     def __init__(self, in_features: int, out_features: int, bias: bool = True, ops=None, group=None,
-                 block: int = 128, row_chunks: int = 4, check_finite: bool = False, device=None, dtype=None):
+                 block: int = 128, row_chunks: Optional[int] = None, reserve_sms: int = 0, check_finite: bool = False,
+                 device=None, dtype=None):
         self.group = group
         self.k0, self.k1 = k_range(in_features, _rank(group), _world(group), block)
         self.full_in_features = in_features
-        self.row_chunks = max(1, int(row_chunks))
+        self.row_chunks = None if row_chunks is None else max(1, int(row_chunks))
+        self.reserve_sms = max(0, int(reserve_sms))     # SMs the GEMM leaves to the all-reduce running beside it
         super().__init__(self.k1 - self.k0, out_features, bias, ops=ops, check_finite=check_finite,
                          device=device, dtype=dtype)
 
@@ -109,6 +115,12 @@ class RowParallelQLinear(QLinear):
             return out
         return y
 
+    def _pieces(self, rows: int) -> int:
+        if self.row_chunks is not None:
+            return self.row_chunks
+        flops = 2.0 * rows * self.out_features * self.in_features          # this rank's GEMM
+        return int(max(1, min(4, flops // 2.5e11)))                         # about 0.2 ms of GEMM per piece
+
     def forward(self, x: torch.Tensor):
         world = _world(self.group)
         lead = x.shape[:-1]
@@ -126,12 +138,18 @@ class RowParallelQLinear(QLinear):
             if side is None:
                 side = _SIDE_STREAMS[dev] = torch.cuda.Stream(dev)
             cur = torch.cuda.current_stream(dev)
-            step = -(-rows // self.row_chunks)
+            step = -(-rows // self._pieces(rows))
             step = max(128, -(-step // 128) * 128)          # whole GEMM row tiles per piece
             for r0 in range(0, rows, step):
                 r1 = min(rows, r0 + step)
                 piece = y[r0:r1]
-                self._partial(x2d[r0:r1], out=piece)
+                # from the second piece on an all-reduce is in flight beside the GEMM
+                prev = gemm_reserve_sms(self.reserve_sms) if (self.reserve_sms and r0 > 0) else None
+                try:
+                    self._partial(x2d[r0:r1], out=piece)
+                finally:
+                    if prev is not None:
+                        gemm_reserve_sms(prev)
                 ev = torch.cuda.Event()
                 ev.record(cur)
                 side.wait_event(ev)

@@ -189,6 +189,14 @@ int hbq_gemm_kn_noalloc(const void* A, const void* B, void* C, int64_t M, int64_
 int hbq_gemm_status(int* status_host);
 int hbq_gemm_status_reset(void);
 
+/* The tensor-core kernel is persistent: one CTA per SM, each holding most of an SM's shared
+ * memory, with a fixed round-robin share of the tiles.  A kernel of another stream that already
+ * sits on some SMs (a collective running under the GEMM) keeps those CTAs from starting until it
+ * ends, and they still owe their whole share.  hbq_gemm_reserve_sms(n) makes every later launch
+ * of this process leave n SMs free for such a neighbour (0 = use all, the default); it returns
+ * the previous value.  Host-side setting read at launch time; no reference counterpart. */
+int hbq_gemm_reserve_sms(int n);
+
 /* ---- misc ------------------------------------------------------------------------------ */
 
 const char* hbq_error_string(int code);
