@@ -446,6 +446,78 @@ def run_tp_mlp(args, rank: int, world: int, local_rank: int):
         dist.destroy_process_group()
 
 
+def run_ep_moe(args, rank: int, world: int, local_rank: int):
+    """`--ep-moe`: the sparse MoE block of configs[4] (Mixtral-8x7B shapes: hidden 4096, intermediate 14336,
+    8 experts, top-2; 4 x 4096 tokens) with HBQ-E quantizers and fp16 / partial-sum-quantised accumulation,
+    experts spread over the ranks, each rank routing its share of the tokens.  Strong scaling: the token batch
+    is fixed.  One JSON line from rank 0 (device time, max over ranks)."""
+    import torch
+    import torch.distributed as dist
+    import hbq_b200 as H
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    hidden, inter, experts, top_k, tokens = 4096, 14336, 8, 2, 4 * 4096
+    wq = H.HBQQuantizer(**WGT)
+    moe = H.ExpertParallelMoE(hidden, inter, experts, top_k=top_k, packed_dispatch=args.ep_packed_dispatch, device=dev,
+                              dtype=torch.float16, ops_factory=lambda: H.FP16AccumMatMul(group_size=128, quant_block_size=32))
+    moe.aq = H.HBQQuantizer(**ACT)
+    g = torch.Generator(device=dev).manual_seed(21)
+    with torch.no_grad():
+        moe.gate.weight.copy_(torch.randn((experts, hidden), device=dev, generator=g).half())
+        for e in range(experts):                    # every rank draws all experts' weights, keeps its own
+            ws = [(0.02 * torch.randn(shape, device=dev, generator=g)).half()
+                  for shape in ((inter, hidden), (inter, hidden), (hidden, inter))]
+            if moe.e0 <= e < moe.e0 + moe.per_rank:
+                ex = moe.experts[e - moe.e0]
+                for lin, w in zip((ex.w1, ex.w3, ex.w2), ws):
+                    lin.weight.copy_(wq.q(w))
+                ex.w2.aq = H.HBQQuantizer(**ACT)
+    mine = tokens // world
+    x = torch.randn((mine, hidden), device=dev, generator=torch.Generator(device=dev).manual_seed(100 + rank)).half()
+
+    def step():
+        with torch.no_grad():
+            return moe(x)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        y = step()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms /= args.steps
+    flops = top_k * 3 * 2.0 * tokens * hidden * inter
+    if H.gemm_status() != 0:
+        raise RuntimeError("tensor-core GEMM reported an expired wait")
+    if rank == 0:
+        print(json.dumps({"metric": "ep_moe_tflops", "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": world,
+                          "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+                          "scaling": "strong", "dtype": "f16", "data": "synthetic",
+                          "config": {"workload": "configs[4] MoE block: 16384 tokens, 8 experts, top-2, hidden 4096, intermediate "
+                                                 "14336, HBQ-E activations and weights, accumulation fp16_quant(group 128, block 32)",
+                                     "parallelism": f"ep{world}: {moe.per_rank} expert(s) per rank, all-to-all dispatch "
+                                                    f"({'packed codes and scales' if moe.packed_dispatch else 'fp16'}) and combine (fp16)"},
+                          "finite": bool(torch.isfinite(y).all().item())}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -458,6 +530,10 @@ def main():
                          "(all cases, or one: " + ", ".join(SWEEP_FORMATS) + ", k_write, v_write)")
     ap.add_argument("--tp-mlp", action="store_true",
                     help="instead of the benchmark line: the tensor-parallel MLP block of configs[3] over the launched ranks")
+    ap.add_argument("--ep-moe", action="store_true",
+                    help="instead of the benchmark line: the expert-parallel MoE block of configs[4] over the launched ranks")
+    ap.add_argument("--ep-packed-dispatch", action="store_true",
+                    help="--ep-moe: dispatch packed codes and scales instead of fp16 rows")
     ap.add_argument("--tp-row-chunks", type=int, default=None,
                     help="--tp-mlp: pieces the row-parallel layer cuts its rows into (1 = all-reduce after the whole GEMM; "
                          "default: chosen from the per-rank GEMM size)")
@@ -472,6 +548,9 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.tp_mlp:
         run_tp_mlp(args, rank, world, local_rank)
+        return
+    if args.ep_moe:
+        run_ep_moe(args, rank, world, local_rank)
         return
     if args.impl == "reference":
         run_reference(args, rank, world)

@@ -11,6 +11,7 @@ from .kvcache import write_k_cache, write_v_cache  # noqa: F401
 from .module import QLinear  # noqa: F401
 from .ops import FP16AccumMatMul  # noqa: F401
 from .ptq import PTQConfig, load_quant_config  # noqa: F401
+from .ep_moe import ExpertParallelMoE, QuantExpert  # noqa: F401
 from .tp_linear import ColumnParallelQLinear, RowParallelQLinear  # noqa: F401
 from .quantizer import (HBQQuantizer, MXExQuantizer, MXFPQuantizer, MXINTQuantizer, PackedTensor,  # noqa: F401
                         VSQQuantizer, _QBase,
@@ -19,4 +20,4 @@ from .quantizer import (HBQQuantizer, MXExQuantizer, MXFPQuantizer, MXINTQuantiz
 __all__ = ["HBQQuantizer", "MXFPQuantizer", "MXINTQuantizer", "MXExQuantizer", "VSQQuantizer", "_QBase", "FP16AccumMatMul", "QLinear",
            "PTQConfig", "load_quant_config", "blockquant_ext", "gemm", "gemm_status", "PackedTensor",
            "dequantize_packed", "HbqError", "launch_count", "get_max_norm", "get_min_norm", "get_min_subnorm",
-           "write_k_cache", "write_v_cache", "ColumnParallelQLinear", "RowParallelQLinear"]
+           "write_k_cache", "write_v_cache", "ColumnParallelQLinear", "RowParallelQLinear", "ExpertParallelMoE", "QuantExpert"]
