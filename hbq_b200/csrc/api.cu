@@ -40,6 +40,29 @@ int ensure_dynamic_smem_impl(const void* kernel, size_t bytes)
     return HBQ_OK;
 }
 
+// (kernel, device, threads, smem) -> resident CTAs per SM
+struct Occupancy { const void* kernel; int dev, threads; size_t smem; int ctas; };
+static Occupancy g_occ[256];
+static int g_nocc = 0;
+
+int resident_ctas_impl(const void* kernel, int threads, size_t smem, int* ctas)
+{
+    int dev = 0;
+    HBQ_CUDA_TRY(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(g_grant_mutex);
+    for (int i = 0; i < g_nocc; ++i)
+        if (g_occ[i].kernel == kernel && g_occ[i].dev == dev && g_occ[i].threads == threads && g_occ[i].smem == smem) {
+            *ctas = g_occ[i].ctas;
+            return HBQ_OK;
+        }
+    int n = 0;
+    HBQ_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, threads, smem));
+    if (n < 1) n = 1;
+    if (g_nocc < 256) g_occ[g_nocc++] = {kernel, dev, threads, smem, n};
+    *ctas = n;
+    return HBQ_OK;
+}
+
 // implemented in quantize.cu / gemm_simt.cu / gemm_tc.cu
 int quantize_launch(const void*, int, int64_t, int64_t, const hbq_format*, void*, int, const hbq_packed_out*,
                     const float*, cudaStream_t, const KvWriteOpts*);

@@ -68,6 +68,16 @@ inline int ensure_dynamic_smem(Kernel kernel, size_t bytes)
     return ensure_dynamic_smem_impl(reinterpret_cast<const void*>(kernel), bytes);
 }
 
+// CTAs of `threads` threads and `smem` dynamic bytes that one SM holds at once (the occupancy
+// calculator's answer, cached per kernel address and device in api.cu).  A grid-stride kernel sized to
+// more CTAs than are resident runs the excess as a thinly occupied second wave.
+int resident_ctas_impl(const void* kernel, int threads, size_t smem, int* ctas);
+template <class Kernel>
+inline int resident_ctas(Kernel kernel, int threads, size_t smem, int* ctas)
+{
+    return resident_ctas_impl(reinterpret_cast<const void*>(kernel), threads, smem, ctas);
+}
+
 __device__ __forceinline__ uint32_t h2_bits(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
 __device__ __forceinline__ __half2 bits_h2(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
 __device__ __forceinline__ uint16_t h_bits(__half h) { return __half_as_ushort(h); }

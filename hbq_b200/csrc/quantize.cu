@@ -718,22 +718,31 @@ static void build_pot_table(bool use_round, uint16_t thr[32])
     memcpy(thr, cache[w], sizeof(cache[w]));
 }
 
-template <int KIND, int MB>
-static void launch_mx_fast(QArgs& a, dim3 grid, dim3 block, cudaStream_t stream)
+template <int KIND, int MB, bool CODES, bool LEAN>
+static int launch_mx_fast_as(QArgs& a, dim3 grid, dim3 block, cudaStream_t stream)
 {
-    // at most 8 CTAs of 256 threads per SM (a full complement of warps), each looping over chunks
-    int sms = 148;
-    device_sms(&sms);
-    if ((int64_t)grid.x > (int64_t)sms * 8) grid.x = (unsigned)(sms * 8);
+    // as many CTAs as are resident at once (registers allow 6 of 256 threads per SM, not the 8 that
+    // the warp slots would), each looping over chunks: no thinly occupied second wave
+    int sms = 0, per_sm = 0;
+    { const int rc = device_sms(&sms); if (rc) return rc; }
+    { const int rc = resident_ctas(mx_fast_kernel<KIND, MB, CODES, LEAN>, (int)block.x, 0, &per_sm); if (rc) return rc; }
+    if ((int64_t)grid.x > (int64_t)sms * per_sm) grid.x = (unsigned)(sms * per_sm);
     const int64_t stride = (int64_t)grid.x * block.x;
     a.step_rows = stride / a.cpr;
     a.step_chunks = stride % a.cpr;
+    mx_fast_kernel<KIND, MB, CODES, LEAN><<<grid, block, 0, stream>>>(a);
+    return HBQ_OK;
+}
+
+template <int KIND, int MB>
+static int launch_mx_fast(QArgs& a, dim3 grid, dim3 block, cudaStream_t stream)
+{
     const bool side_out = a.out.codes || a.out.sign || a.out.scale_u8 || a.out.scale_h || a.out.l2_packed ||
                           a.out.l2_idx || a.out.scheme;
     if (a.deq && !side_out && a.aligned && a.K == a.Kp && !a.rope_cos && a.perm_T <= 0 && !a.k_center)
-        mx_fast_kernel<KIND, MB, false, true><<<grid, block, 0, stream>>>(a);
-    else if (a.out.codes) mx_fast_kernel<KIND, MB, true, false><<<grid, block, 0, stream>>>(a);
-    else mx_fast_kernel<KIND, MB, false, false><<<grid, block, 0, stream>>>(a);
+        return launch_mx_fast_as<KIND, MB, false, true>(a, grid, block, stream);
+    if (a.out.codes) return launch_mx_fast_as<KIND, MB, true, false>(a, grid, block, stream);
+    return launch_mx_fast_as<KIND, MB, false, false>(a, grid, block, stream);
 }
 
 int quantize_launch(const void* x, int dtype, int64_t rows, int64_t K, const hbq_format* f,
@@ -804,7 +813,7 @@ int quantize_launch(const void* x, int dtype, int64_t rows, int64_t K, const hbq
             a.int_lim_pos = (uint32_t)__half_as_ushort(__float2half_rn(qmax)) * 0x00010001u;
             a.int_lim_neg = (uint32_t)__half_as_ushort(__float2half_rn(qmax + 1.f)) * 0x00010001u;
             if (kv && kv->v_axis) return launch_mx_v<HBQ_KIND_MXINT, 0>(a, kv, stream);
-            launch_mx_fast<HBQ_KIND_MXINT, 0>(a, grid, block, stream);
+            { const int rc = launch_mx_fast<HBQ_KIND_MXINT, 0>(a, grid, block, stream); if (rc) return rc; }
             HBQ_LAUNCH_CHECK("mx_fast_kernel<mxint>");
             return HBQ_OK;
         }
@@ -842,12 +851,14 @@ int quantize_launch(const void* x, int dtype, int64_t rows, int64_t K, const hbq
                     default: return launch_mx_v<HBQ_KIND_MXFP, 5>(a, kv, stream);
                 }
             }
+            int rc = HBQ_OK;
             switch (fast_mb) {
-                case 1: launch_mx_fast<HBQ_KIND_MXFP, 1>(a, grid, block, stream); break;
-                case 2: launch_mx_fast<HBQ_KIND_MXFP, 2>(a, grid, block, stream); break;
-                case 3: launch_mx_fast<HBQ_KIND_MXFP, 3>(a, grid, block, stream); break;
-                default: launch_mx_fast<HBQ_KIND_MXFP, 5>(a, grid, block, stream); break;
+                case 1: rc = launch_mx_fast<HBQ_KIND_MXFP, 1>(a, grid, block, stream); break;
+                case 2: rc = launch_mx_fast<HBQ_KIND_MXFP, 2>(a, grid, block, stream); break;
+                case 3: rc = launch_mx_fast<HBQ_KIND_MXFP, 3>(a, grid, block, stream); break;
+                default: rc = launch_mx_fast<HBQ_KIND_MXFP, 5>(a, grid, block, stream); break;
             }
+            if (rc) return rc;
             HBQ_LAUNCH_CHECK("mx_fast_kernel<mxfp>");
             return HBQ_OK;
         }

@@ -18,7 +18,7 @@ With one rank (or no process group) every expert is local and no collective runs
 """
 from __future__ import annotations
 
-from typing import List, Optional
+from typing import List
 
 import torch
 import torch.distributed as dist
@@ -92,11 +92,14 @@ class ExpertParallelMoE(nn.Module):
                                group=self.group)
         return out
 
-    def _dispatch(self, copies: torch.Tensor, send_counts, recv_counts) -> torch.Tensor:
-        """Quantise the sorted token copies and bring every rank the rows of its experts (fake-quantised)."""
+    def _dispatch(self, x2d: torch.Tensor, src_rows: torch.Tensor, send_counts, recv_counts) -> torch.Tensor:
+        """Quantise and bring every rank the rows of its experts (fake-quantised).  ``src_rows[c]`` is the
+        token of copy c, copies sorted by expert."""
         if not self.packed_dispatch:
-            xq = self.aq(copies)
+            # rows are quantised independently: quantise each token once, then copy it top_k times
+            xq = self.aq(x2d).index_select(0, src_rows)
             return xq if self.world == 1 else self._exchange_rows(xq, send_counts, recv_counts)
+        copies = x2d.index_select(0, src_rows)
         packed = self.aq.quantize_packed(copies)
         if self.world == 1:
             return dequantize_packed(packed)
@@ -119,12 +122,12 @@ class ExpertParallelMoE(nn.Module):
         w, idx = self.route(x2d)
         flat_e = idx.reshape(-1)                                       # expert of copy c = (token c // k, choice c % k)
         order = torch.sort(flat_e, stable=True).indices               # copies grouped by expert, hence by rank
-        copies = x2d.index_select(0, torch.div(order, self.top_k, rounding_mode="floor"))
+        src_rows = torch.div(order, self.top_k, rounding_mode="floor")
         per_expert = torch.bincount(flat_e, minlength=self.num_experts)
 
         if self.world == 1:
             recv_per_expert = per_expert.tolist()
-            xq = self._dispatch(copies, None, None)
+            xq = self._dispatch(x2d, src_rows, None, None)
             send_counts = recv_counts = None
         else:
             # row counts: what every rank sends me for each of my experts (one small all-to-all, then the host reads it)
@@ -133,7 +136,7 @@ class ExpertParallelMoE(nn.Module):
             send_counts = per_expert.view(self.world, self.per_rank).sum(dim=1).tolist()
             got = counts_out.view(self.world, self.per_rank)
             recv_counts = got.sum(dim=1).tolist()
-            xq_by_src = self._dispatch(copies, send_counts, recv_counts)
+            xq_by_src = self._dispatch(x2d, src_rows, send_counts, recv_counts)
             # arrived rows are grouped by source rank, then by expert: regroup by expert
             got_l = got.tolist()
             pieces = torch.split(xq_by_src, [c for src in got_l for c in src])
@@ -159,5 +162,5 @@ class ExpertParallelMoE(nn.Module):
         # y_rows is in `order`: weight each copy and add it to its token
         wc = w.reshape(-1).index_select(0, order).unsqueeze(1)
         y = torch.zeros((T, self.hidden), dtype=x2d.dtype, device=x2d.device)
-        y.index_add_(0, torch.div(order, self.top_k, rounding_mode="floor"), y_rows * wc)
+        y.index_add_(0, src_rows, y_rows * wc)
         return y.reshape(*lead, self.hidden)
