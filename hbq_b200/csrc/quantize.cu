@@ -10,6 +10,7 @@
 // the G = block_size/8 lanes that own one quantisation block reduce with warp shuffles, so a
 // tensor is read once from HBM and every output is written once.
 #include "quantize_dev.cuh"
+#include <stdlib.h>
 #include "vcache_dev.cuh"
 #include <math.h>
 #include <mutex>
@@ -721,12 +722,15 @@ static void build_pot_table(bool use_round, uint16_t thr[32])
 template <int KIND, int MB, bool CODES, bool LEAN>
 static int launch_mx_fast_as(QArgs& a, dim3 grid, dim3 block, cudaStream_t stream)
 {
-    // as many CTAs as are resident at once (registers allow 6 of 256 threads per SM, not the 8 that
-    // the warp slots would), each looping over chunks: no thinly occupied second wave
+    // a multiple of the CTAs that are resident at once (registers allow 6 of 256 threads per SM, not
+    // the 8 that the warp slots would), each looping over chunks: no thinly occupied last wave
     int sms = 0, per_sm = 0;
     { const int rc = device_sms(&sms); if (rc) return rc; }
     { const int rc = resident_ctas(mx_fast_kernel<KIND, MB, CODES, LEAN>, (int)block.x, 0, &per_sm); if (rc) return rc; }
-    if ((int64_t)grid.x > (int64_t)sms * per_sm) grid.x = (unsigned)(sms * per_sm);
+    // ... times 4: the warps of an SM do not finish together, and with four generations of CTAs the
+    // hardware scheduler refills the gaps (measured: 1 wave 3949, 2: 4026, 4 or 8: 4125, 16: 3996 GB/s)
+    constexpr int kWaves = 4;
+    if ((int64_t)grid.x > (int64_t)sms * per_sm * kWaves) grid.x = (unsigned)(sms * per_sm * kWaves);
     const int64_t stride = (int64_t)grid.x * block.x;
     a.step_rows = stride / a.cpr;
     a.step_chunks = stride % a.cpr;
