@@ -408,7 +408,7 @@ def run_tp_mlp(args, rank: int, world: int, local_rank: int):
             xq = gate.aq(x)                                   # one quantize feeds both projections
             a = H.blockquant_ext.gemm_fp32_accum(xq, gate.weight, b_is_nk=True)
             b = H.blockquant_ext.gemm_fp32_accum(xq, up.weight, b_is_nk=True)
-            return down(torch.nn.functional.silu(a) * b)
+            return down(H.swiglu_quantize(a, b, down.aq), input_quantized=True)
 
     def barrier():
         if world > 1:
@@ -534,6 +534,8 @@ def main():
                     help="instead of the benchmark line: the expert-parallel MoE block of configs[4] over the launched ranks")
     ap.add_argument("--ep-packed-dispatch", action="store_true",
                     help="--ep-moe: dispatch packed codes and scales instead of fp16 rows")
+    ap.add_argument("--no-fused-act", action="store_true",
+                    help="--tp-mlp / --ep-moe: run silu, product and quantizer as separate ops (A/B of the fused kernel)")
     ap.add_argument("--tp-row-chunks", type=int, default=None,
                     help="--tp-mlp: pieces the row-parallel layer cuts its rows into (1 = all-reduce after the whole GEMM; "
                          "default: chosen from the per-rank GEMM size)")
@@ -546,6 +548,9 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.no_fused_act:
+        from hbq_b200 import kvcache
+        kvcache.FUSE_SWIGLU = False
     if args.tp_mlp:
         run_tp_mlp(args, rank, world, local_rank)
         return

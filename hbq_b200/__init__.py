@@ -7,7 +7,7 @@ Importing the package does not need a GPU; the CUDA library (``lib/libhbq_b200.s
 from . import blockquant_ext  # noqa: F401
 from ._lib import HbqError, launch_count  # noqa: F401
 from .gemm import gemm, gemm_status  # noqa: F401
-from .kvcache import write_k_cache, write_v_cache  # noqa: F401
+from .kvcache import swiglu_quantize, write_k_cache, write_v_cache  # noqa: F401
 from .module import QLinear  # noqa: F401
 from .ops import FP16AccumMatMul  # noqa: F401
 from .ptq import PTQConfig, load_quant_config  # noqa: F401
@@ -20,4 +20,4 @@ from .quantizer import (HBQQuantizer, MXExQuantizer, MXFPQuantizer, MXINTQuantiz
 __all__ = ["HBQQuantizer", "MXFPQuantizer", "MXINTQuantizer", "MXExQuantizer", "VSQQuantizer", "_QBase", "FP16AccumMatMul", "QLinear",
            "PTQConfig", "load_quant_config", "blockquant_ext", "gemm", "gemm_status", "PackedTensor",
            "dequantize_packed", "HbqError", "launch_count", "get_max_norm", "get_min_norm", "get_min_subnorm",
-           "write_k_cache", "write_v_cache", "ColumnParallelQLinear", "RowParallelQLinear", "ExpertParallelMoE", "QuantExpert"]
+           "write_k_cache", "write_v_cache", "swiglu_quantize", "ColumnParallelQLinear", "RowParallelQLinear", "ExpertParallelMoE", "QuantExpert"]

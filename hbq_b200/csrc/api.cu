@@ -224,7 +224,7 @@ int hbq_kv_write_k(const void* k, int dtype, int64_t B, int64_t T, int64_t H, in
     if (B * T * H == 0) return HBQ_OK;
     if (!out) return HBQ_ERR_ARG;
     if (fmt->kind == HBQ_KIND_MXFP && fmt->per_tensor_scale) return HBQ_ERR_UNSUPPORTED;   // needs max|x| of the rotated tensor first
-    KvWriteOpts kv = {cos, sin, rope_rows, B, T, H, D, 0, center, 0};
+    KvWriteOpts kv = {cos, sin, rope_rows, B, T, H, D, 0, center, 0, nullptr};
     return quantize_launch(k, dtype, B * T * H, D, fmt, out, out_dtype, nullptr, nullptr, (cudaStream_t)stream, &kv);
 }
 
@@ -234,10 +234,20 @@ int hbq_kv_write_v(const void* v, int dtype, int64_t B, int64_t T, int64_t H, in
     if (!fmt || B < 0 || T < 0 || H < 0 || D <= 0) return HBQ_ERR_ARG;
     if (B * T * H == 0) return HBQ_OK;
     if (!out) return HBQ_ERR_ARG;
-    KvWriteOpts kv = {nullptr, nullptr, 0, B, T, H, D, 1, nullptr, out_token_major};
+    KvWriteOpts kv = {nullptr, nullptr, 0, B, T, H, D, 1, nullptr, out_token_major, nullptr};
     // rows / K only size the format checks here; the token-axis kernel takes its shape from kv
     return quantize_launch(v, dtype, B * H * D, fmt->block_size, fmt, out, out_dtype, nullptr, nullptr,
                            (cudaStream_t)stream, &kv);
+}
+
+int hbq_swiglu_quantize(const void* gate, const void* up, int64_t rows, int64_t K, const hbq_format* fmt, void* out,
+                        void* stream)
+{
+    if (!fmt || rows < 0 || K <= 0) return HBQ_ERR_ARG;
+    if (rows == 0) return HBQ_OK;
+    if (!gate || !up || !out) return HBQ_ERR_ARG;
+    KvWriteOpts o = {nullptr, nullptr, 0, 0, 0, 0, 0, 0, nullptr, 0, gate};
+    return quantize_launch(up, HBQ_DTYPE_F16, rows, K, fmt, out, HBQ_DTYPE_F16, nullptr, nullptr, (cudaStream_t)stream, &o);
 }
 
 int hbq_absmax(const void* x, int dtype, int64_t n, float* amax, void* scratch, void* stream)

@@ -24,6 +24,8 @@ struct KvWriteOpts {
     int v_axis;
     const void* center;       // fp16 [B, H, D] subtracted after the rotation (K only), or NULL
     int v_out_token_major;    // V only: write [B,T,H,D] instead of [B,H,T,D]
+    const void* glu_gate;     // not a cache write: quantise silu(glu_gate) * x (fp16, same shape as x); the
+                              // other fields are then unused
 };
 
 #define HBQ_CUDA_TRY(expr)                                                     \

@@ -782,6 +782,17 @@ int quantize_launch(const void* x, int dtype, int64_t rows, int64_t K, const hbq
     while ((1 << a.log2G) < a.G) ++a.log2G;
     a.f = *f;
     a.f.per_tensor_scale = pts;
+    if (kv && kv->glu_gate) {
+        // fused silu(gate) * x: only the contiguous fp16 -> fp16 table path of the HBQ formats has it
+        const bool side = out && (out->codes || out->sign || out->scale_u8 || out->scale_h || out->l2_packed ||
+                                  out->l2_idx || out->scheme);
+        if (!deq) return HBQ_ERR_ARG;
+        if (f->kind != HBQ_KIND_HBQ || dtype != HBQ_DTYPE_F16 || deq_dtype != HBQ_DTYPE_F16 || side || pts || K % B != 0)
+            return HBQ_ERR_UNSUPPORTED;
+        if (!a.aligned || (reinterpret_cast<uintptr_t>(kv->glu_gate) & 15)) return HBQ_ERR_ALIGN;
+        a.glu_gate = kv->glu_gate;
+        kv = nullptr;
+    }
     if (kv) {
         if (K % B != 0 || !is_pow2((int)K) || K < 16 || K > 256 || pts) return HBQ_ERR_UNSUPPORTED;
         if (kv->cos && (dtype != HBQ_DTYPE_F16 || !kv->sin || kv->rope_rows <= 0)) return HBQ_ERR_UNSUPPORTED;
@@ -905,6 +916,7 @@ int quantize_launch(const void* x, int dtype, int64_t rows, int64_t K, const hbq
         const int rc = hbq_lut_try_launch(a, fast_mb, stream, &launched);
         if (rc != HBQ_OK || launched) return rc;
     }
+    if (a.glu_gate) return HBQ_ERR_UNSUPPORTED;
     switch (fast_mb) {
         case 1: hbq_quantize_kernel<1><<<grid, block, 0, stream>>>(a); break;
         case 2: hbq_quantize_kernel<2><<<grid, block, 0, stream>>>(a); break;

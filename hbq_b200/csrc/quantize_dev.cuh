@@ -107,6 +107,7 @@ struct QArgs {
     int64_t rope_rows;          // B*T (per-batch tables) or T (one table for every batch)
     int64_t perm_T, perm_H;     // > 0: permute output rows (b,t,h) -> (b,h,t)
     const uint16_t* k_center;   // fp16 [B, H, K] or NULL: subtracted after RoPE (K-cache centring, src/module.py:221-244)
+    const void* glu_gate;   // fp16, same shape as x, or NULL: the quantised tensor is silu(glu_gate) * x
     int code_bits;          // bits per stored element code (4, 5 or 8)
     int sign_bit;           // position of the sign in a byte code: ebit + mbit
 };

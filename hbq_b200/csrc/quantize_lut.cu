@@ -571,7 +571,10 @@ __device__ __forceinline__ void l1_table_build(const LutArgs& a, uint4* s_l1c, i
 // MIX: the two-table weight formats -- both tables are evaluated (each with its own block scale) and
 // the one with the smaller fp16 total of the chosen candidates' squared errors over the block wins,
 // the first on ties (src/quantizer.py:806-840).
-template <int MB, bool IN_BF16, bool OUT_BF16, bool KV, bool MIX>
+// GLU: the tensor to quantise is silu(gate) * x, computed on the fly from two fp16 tensors with the
+// roundings of the two separate elementwise ops it replaces (silu in fp32 from the fp16 input, rounded
+// to fp16; the product of the two fp16 values rounded to fp16).
+template <int MB, bool IN_BF16, bool OUT_BF16, bool KV, bool MIX, bool GLU = false>
 __global__ void __launch_bounds__(LEAN_THREADS, 1) hbq_lut_lean_kernel(const LutArgs a)
 {
     extern __shared__ __align__(16) uint2 lut[];
@@ -591,20 +594,33 @@ __global__ void __launch_bounds__(LEAN_THREADS, 1) hbq_lut_lean_kernel(const Lut
     const LutView view1 = {reinterpret_cast<const uint8_t*>(lut + n0), (uint32_t)a.plan2.base * 0x00010001u,
                            (uint32_t)a.plan2.hi * 0x00010001u, a.inv_ele_max2, a.big_l12, a.q.tab[1], a.q.nc};
     const uint4* __restrict__ in = reinterpret_cast<const uint4*>(a.q.x);
+    const uint4* __restrict__ gate = reinterpret_cast<const uint4*>(a.q.glu_gate);
     uint4* __restrict__ out = reinterpret_cast<uint4*>(a.q.deq);
     const int64_t total = a.q.total_chunks, stride = (int64_t)gridDim.x * LEAN_THREADS;
     const int lane = tid & 31;
     const int G = a.q.G;
 
     int64_t ci = (int64_t)blockIdx.x * LEAN_THREADS + tid;
-    uint4 raw = make_uint4(0u, 0u, 0u, 0u);
-    if (ci < total) raw = __ldg(in + ci);
+    uint4 raw = make_uint4(0u, 0u, 0u, 0u), graw = make_uint4(0u, 0u, 0u, 0u);
+    if (ci < total) { raw = __ldg(in + ci); if (GLU) graw = __ldg(gate + ci); }
     for (; ci - lane < total; ci += stride) {
         const bool valid = ci < total;
-        uint4 nraw = make_uint4(0u, 0u, 0u, 0u);
-        if (ci + stride < total) nraw = __ldg(in + ci + stride);       // next chunk in flight during this one
+        uint4 nraw = make_uint4(0u, 0u, 0u, 0u), ngraw = make_uint4(0u, 0u, 0u, 0u);
+        if (ci + stride < total) {                                     // next chunk in flight during this one
+            nraw = __ldg(in + ci + stride);
+            if (GLU) ngraw = __ldg(gate + ci + stride);
+        }
 
         uint32_t xb[4] = {raw.x, raw.y, raw.z, raw.w};
+        if (GLU) {
+            const uint32_t gb[4] = {graw.x, graw.y, graw.z, graw.w};
+            #pragma unroll
+            for (int p = 0; p < 4; ++p) {
+                const float2 g = __half22float2(bits_h2(gb[p])), u = __half22float2(bits_h2(xb[p]));
+                const float s0 = rh(__fdiv_rn(g.x, 1.f + expf(-g.x))), s1 = rh(__fdiv_rn(g.y, 1.f + expf(-g.y)));
+                xb[p] = h2_bits(__floats2half2_rn(s0 * u.x, s1 * u.y));      // fp16 x fp16 is exact in fp32
+            }
+        }
         int64_t oci = ci;                                  // chunk index of the output
         if (KV) {
             const int64_t row = valid ? ci >> a.log2cpr : 0, c = ci & (a.q.cpr - 1);
@@ -651,6 +667,7 @@ __global__ void __launch_bounds__(LEAN_THREADS, 1) hbq_lut_lean_kernel(const Lut
             out[oci] = make_uint4(dq[0], dq[1], dq[2], dq[3]);
         }
         raw = nraw;
+        if (GLU) graw = ngraw;
     }
 }
 
@@ -664,7 +681,11 @@ static int launch_lean(const LutArgs& a, int grid, size_t smem, cudaStream_t str
         { const int rc_ = ensure_dynamic_smem(hbq_lut_lean_kernel<MB, IB, OB, false, true>, smem); if (rc_) return rc_; }            \
         hbq_lut_lean_kernel<MB, IB, OB, false, true><<<grid, LEAN_THREADS, smem, stream>>>(a);
     const bool kvw = a.q.rope_cos || a.q.perm_T > 0 || a.q.k_center;
-    if (a.q.nscheme == 2) {
+    if (a.q.glu_gate) {
+        if (a.q.nscheme == 2 || kvw || a.q.in_bf16 || a.q.out_bf16) return HBQ_ERR_UNSUPPORTED;
+        { const int rc_ = ensure_dynamic_smem(hbq_lut_lean_kernel<MB, false, false, false, false, true>, smem); if (rc_) return rc_; }
+        hbq_lut_lean_kernel<MB, false, false, false, false, true><<<grid, LEAN_THREADS, smem, stream>>>(a);
+    } else if (a.q.nscheme == 2) {
         if (a.q.in_bf16) { if (a.q.out_bf16) { HBQ_LAUNCH_LEAN_MIX(true, true) } else { HBQ_LAUNCH_LEAN_MIX(true, false) } }
         else { if (a.q.out_bf16) { HBQ_LAUNCH_LEAN_MIX(false, true) } else { HBQ_LAUNCH_LEAN_MIX(false, false) } }
     } else if (kvw) { if (a.q.out_bf16) { HBQ_LAUNCH_LEAN(false, true, true) } else { HBQ_LAUNCH_LEAN(false, false, true) } }
@@ -828,6 +849,7 @@ int hbq_lut_try_launch(const QArgs& qa, int mb, cudaStream_t stream, bool* launc
         if (rc == HBQ_OK) *launched = true;
         return rc;
     }
+    if (q.glu_gate) return HBQ_ERR_UNSUPPORTED;   // the fused silu(gate) * x exists in the lean kernel only
     if (mix) return HBQ_OK;                    // two tables: only the lean kernel; the arithmetic kernel serves the rest
     const int64_t need = (qa.total_chunks + LUT_THREADS - 1) / LUT_THREADS;
     const int grid = (int)(need < 2 * sms ? need : 2 * sms);

@@ -25,6 +25,7 @@ import torch.distributed as dist
 import torch.nn as nn
 import torch.nn.functional as F
 
+from .kvcache import swiglu_quantize
 from .module import QLinear
 from .quantizer import PackedTensor, _QBase, dequantize_packed
 
@@ -48,7 +49,11 @@ class QuantExpert(nn.Module):
         self.w2 = QLinear(inter, hidden, **kw)
 
     def forward(self, xq: torch.Tensor) -> torch.Tensor:
-        return self.w2(F.silu(self.w1(xq)) * self.w3(xq))
+        a, b = self.w1(xq), self.w3(xq)
+        if a.is_cuda:
+            # activation, product and w2's input quantizer in one pass where the format has the fused kernel
+            return self.w2(swiglu_quantize(a, b, self.w2.aq), input_quantized=True)
+        return self.w2(F.silu(a) * b)
 
 
 class ExpertParallelMoE(nn.Module):

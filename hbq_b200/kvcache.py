@@ -125,3 +125,34 @@ def write_v_cache(v: torch.Tensor, num_heads: int, quantizer: _CudaBlockQuantize
     _lib.check(rc, "hbq_kv_write_v")
     fused_last = True
     return out
+
+
+FUSE_SWIGLU = True      # False: always run the separate ops (for A/B timing)
+
+
+def swiglu_quantize(gate: torch.Tensor, up: torch.Tensor, quantizer) -> torch.Tensor:
+    """``quantizer.q(silu(gate) * up)`` in one pass over the two projection outputs: the input of the
+    down projection of a gated MLP (``down_proj(act_fn(gate_proj(x)) * up_proj(x))`` in the patched
+    transformers blocks, with ``down_proj.aq`` as the quantizer, src/module.py:45).  Same bits as the
+    three separate ops; formats outside the fused kernel (and non-fp16 inputs) run those ops."""
+    global fused_last
+    if not (gate.is_cuda and up.is_cuda):
+        raise _lib.HbqError("swiglu_quantize needs CUDA tensors (there is no CPU fallback)")
+    if gate.shape != up.shape or gate.dtype != up.dtype:
+        raise ValueError("gate and up must have the same shape and dtype")
+    fusable = (FUSE_SWIGLU and isinstance(quantizer, _CudaBlockQuantizer) and gate.dtype == torch.float16
+               and quantizer.out_dtype in (None, torch.float16) and not getattr(quantizer, "keep_l2_scale", False))
+    if fusable:
+        g, u = gate.contiguous(), up.contiguous()
+        K = g.shape[-1]
+        rows = g.numel() // K if K else 0
+        out = torch.empty_like(u)
+        fmt = quantizer._format()
+        with _lib.device_guard(g.device):
+            rc = _lib.lib().hbq_swiglu_quantize(_ptr(g), _ptr(u), rows, K, ctypes.byref(fmt), _ptr(out), _stream_ptr(g.device))
+        if rc != _lib.ERR_UNSUPPORTED:
+            _lib.check(rc, "hbq_swiglu_quantize")
+            fused_last = True
+            return out
+    fused_last = False
+    return quantizer(torch.nn.functional.silu(gate) * up)

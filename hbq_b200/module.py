@@ -29,9 +29,11 @@ class QLinear(nn.Linear):
         self.check_finite = check_finite
         self.packed_weight = None
 
-    def forward(self, x: torch.Tensor):
+    def forward(self, x: torch.Tensor, input_quantized: bool = False):
+        """``input_quantized``: ``x`` has been through ``self.aq`` already (a producer that fuses the
+        quantizer, e.g. ``swiglu_quantize``)."""
         wq = self.weight
-        xq = self.aq(x)
+        xq = x if input_quantized else self.aq(x)
         if self.ops is None:
             y = F.linear(xq, wq, self.bias)
         else:

@@ -98,9 +98,9 @@ class RowParallelQLinear(QLinear):
         if bias is not None and self.bias is not None:
             self.bias.data.copy_(bias)
 
-    def _partial(self, x2d: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def _partial(self, x2d: torch.Tensor, out: Optional[torch.Tensor] = None, input_quantized: bool = False) -> torch.Tensor:
         """This rank's partial product, written into ``out`` when the operator can do that."""
-        xq = self.aq(x2d)
+        xq = x2d if input_quantized else self.aq(x2d)
         if self.ops is None:
             if xq.is_cuda and xq.dtype == torch.float16 and self.weight.dtype == torch.float16:
                 # fp32 accumulation (what F.linear models in the reference) on the tensor-core kernel
@@ -121,15 +121,15 @@ class RowParallelQLinear(QLinear):
         flops = 2.0 * rows * self.out_features * self.in_features          # this rank's GEMM
         return int(max(1, min(4, flops // 2.5e11)))                         # about 0.2 ms of GEMM per piece
 
-    def forward(self, x: torch.Tensor):
+    def forward(self, x: torch.Tensor, input_quantized: bool = False):
         world = _world(self.group)
         lead = x.shape[:-1]
         x2d = x.reshape(-1, x.shape[-1])
         rows = x2d.shape[0]
         if world == 1:
-            y = self._partial(x2d)
+            y = self._partial(x2d, input_quantized=input_quantized)
         elif not x2d.is_cuda:
-            y = self._partial(x2d)
+            y = self._partial(x2d, input_quantized=input_quantized)
             dist.all_reduce(y, group=self.group)
         else:
             y = torch.empty((rows, self.out_features), dtype=self.weight.dtype, device=x2d.device)
@@ -146,7 +146,7 @@ class RowParallelQLinear(QLinear):
                 # from the second piece on an all-reduce is in flight beside the GEMM
                 prev = gemm_reserve_sms(self.reserve_sms) if (self.reserve_sms and r0 > 0) else None
                 try:
-                    self._partial(x2d[r0:r1], out=piece)
+                    self._partial(x2d[r0:r1], out=piece, input_quantized=input_quantized)
                 finally:
                     if prev is not None:
                         gemm_reserve_sms(prev)

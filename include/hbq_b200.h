@@ -132,6 +132,17 @@ int hbq_kv_write_k(const void* k, int dtype, int64_t B, int64_t T, int64_t H, in
 int hbq_kv_write_v(const void* v, int dtype, int64_t B, int64_t T, int64_t H, int64_t D,
                    const hbq_format* fmt, void* out, int out_dtype, int out_token_major, void* stream);
 
+/* Gated-MLP activation fused into the quantizer of the down projection's input: what the reference
+ * runs as three tensor ops, act_fn(gate_proj(x)) * up_proj(x) (the MLP forward of the patched
+ * transformers blocks) followed by down_proj.aq.q(...) (src/module.py:45), in one pass over the two
+ * projection outputs.  gate, up and out are fp16 [rows, K], contiguous and 16-byte aligned; act_fn is
+ * SiLU.  Roundings are those of the separate ops: silu evaluated in fp32 and rounded to fp16, the
+ * product rounded to fp16, then the HBQ quantizer.  Served formats: HBQ with one candidate table,
+ * K a multiple of block_size; HBQ_ERR_UNSUPPORTED otherwise (callers then run the steps separately). */
+int hbq_swiglu_quantize(const void* gate, const void* up, int64_t rows, int64_t K,
+                        const hbq_format* fmt, void* out, void* stream);
+
+
 /* ---- GEMM with modelled accumulation --------------------------------------------------- */
 
 enum { HBQ_ACC_FP32 = 0,       /* gemm_fp32_accum         blockquant_ext.cpp:21-29, gemm.cu:96-303 */

@@ -173,3 +173,31 @@ def test_v_write_token_major(name):
     assert got.shape == (B, T, H, D)
     want = kvcache.write_v_cache(v, H, q)                      # [B,H,T,D], checked against the unfused chain above
     assert torch.equal(got, want.permute(0, 2, 1, 3).contiguous())
+
+
+@pytest.mark.parametrize("name", ["hbq_a_sig1_l8", "hbq_e_fp1_l32", "hbq_sig1_b32", "mxfp4_b32", "hbq_mix_l4"])
+def test_swiglu_quantize_matches_the_three_ops(name):
+    """silu(gate) * up followed by the quantizer, fused (HBQ table formats) or not (the rest): the
+    same bits as torch's silu, multiplication and the quantizer run one after the other."""
+    import torch.nn.functional as F
+    import hbq_b200 as Hq
+    from hbq_b200 import kvcache
+    q = quantizers()[name]()
+    g = torch.Generator(device="cuda").manual_seed(17)
+    gate = (3.0 * torch.randn((2, 777, 1024), device="cuda", generator=g)).half()
+    up = torch.randn((2, 777, 1024), device="cuda", generator=g).half()
+    gate[0, 0, :8] = torch.tensor([0.0, -0.0, 65504.0, -65504.0, 1e-7, -1e-7, 20.0, -20.0], device="cuda").half()
+    want = q.q(F.silu(gate) * up)
+    got = Hq.swiglu_quantize(gate, up, q)
+    assert kvcache.fused_last == (name.startswith("hbq_") and name != "hbq_mix_l4")
+    assert got.shape == want.shape and got.dtype == want.dtype
+    assert np.array_equal(hbits(got), hbits(want)), name
+    # every fp16 value as the gate (silu itself, against torch's)
+    allg = torch.arange(65536, dtype=torch.int32, device="cuda").to(torch.int16).view(torch.float16)
+    allg = allg[torch.isfinite(allg)]
+    n = (allg.numel() // 128) * 128
+    allg = allg[:n].view(-1, 128).contiguous()
+    ones = torch.full_like(allg, 1.0)
+    want = q.q(F.silu(allg) * ones)
+    got = Hq.swiglu_quantize(allg, ones, q)
+    assert np.array_equal(hbits(got), hbits(want)), name + " (all gate values)"
