@@ -390,3 +390,33 @@ def test_against_reference_extension():
             torch.cuda.synchronize()
             assert H.gemm_status() == 0
             compare(tc.cpu().numpy(), ref.cpu().numpy(), f"tensor-core vs reference gemm.cu, {name}")
+
+
+def test_out_argument_and_reserved_sms():
+    """`out=` writes into the caller's tensor; leaving SMs free for a neighbouring kernel changes the
+    persistent grid, not the result."""
+    import hbq_b200 as H
+    from hbq_b200.gemm import gemm_reserve_sms
+    M, N, K = 1500, 2048, 512
+    a = torch.randn((M, K), device="cuda").half()
+    w = (0.05 * torch.randn((N, K), device="cuda")).half()
+    y0 = H.gemm(a, w, 3, 128, 32, b_is_nk=True)
+    out = torch.full((M, N), float("nan"), dtype=torch.float16, device="cuda")
+    y1 = H.gemm(a, w, 3, 128, 32, b_is_nk=True, out=out)
+    assert y1.data_ptr() == out.data_ptr() and torch.equal(out.view(torch.int16), y0.view(torch.int16))
+    prev = gemm_reserve_sms(40)
+    try:
+        y2 = H.gemm(a, w, 3, 128, 32, b_is_nk=True)
+        assert gemm_reserve_sms(10 ** 6) == 40                 # more than the device has: one CTA does everything
+        y3 = H.gemm(a[:256].contiguous(), w, 0, b_is_nk=True)
+    finally:
+        gemm_reserve_sms(prev)
+    torch.cuda.synchronize()
+    assert H.gemm_status() == 0
+    assert torch.equal(y2.view(torch.int16), y0.view(torch.int16))
+    assert torch.equal(y3.view(torch.int16), H.gemm(a[:256].contiguous(), w, 0, b_is_nk=True).view(torch.int16))
+    with pytest.raises(RuntimeError):
+        H.gemm(a, w, 3, 128, 32, b_is_nk=True, out=out[:, :100])
+    op = H.FP16AccumMatMul(group_size=128, quant_block_size=32)
+    buf = torch.empty((M, N), dtype=torch.float16, device="cuda")
+    assert torch.equal(op(a, w, None, out=buf).view(torch.int16), y0.view(torch.int16))
