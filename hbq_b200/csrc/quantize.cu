@@ -323,8 +323,11 @@ __device__ __forceinline__ Chunk lean_load(const QArgs& a, int64_t ci)
     return c;
 }
 
+// The lean form is held to 32 registers so that 8 CTAs (all 64 warp slots) fit an SM: it needs 34
+// without the cap and loses nothing to it (no spills), and the issue-bound loop gains 4-7 % from the
+// extra warps.  The general form spills under that cap and is left alone.
 template <int KIND, int MB, bool CODES, bool LEAN>
-__global__ void __launch_bounds__(256) mx_fast_kernel(const QArgs a)
+__global__ void __launch_bounds__(256, LEAN ? 8 : 1) mx_fast_kernel(const QArgs a)
 {
     // Grid-stride loop with the next chunk's load issued before the current one is processed, so
     // every thread keeps a 16-byte load in flight while it computes.
@@ -722,13 +725,14 @@ static void build_pot_table(bool use_round, uint16_t thr[32])
 template <int KIND, int MB, bool CODES, bool LEAN>
 static int launch_mx_fast_as(QArgs& a, dim3 grid, dim3 block, cudaStream_t stream)
 {
-    // a multiple of the CTAs that are resident at once (registers allow 6 of 256 threads per SM, not
-    // the 8 that the warp slots would), each looping over chunks: no thinly occupied last wave
+    // a multiple of the CTAs that are resident at once (asked of the occupancy calculator: registers
+    // decide, 8 for the lean form, fewer for the general one), each looping over chunks: no thinly
+    // occupied last wave
     int sms = 0, per_sm = 0;
     { const int rc = device_sms(&sms); if (rc) return rc; }
     { const int rc = resident_ctas(mx_fast_kernel<KIND, MB, CODES, LEAN>, (int)block.x, 0, &per_sm); if (rc) return rc; }
     // ... times 4: the warps of an SM do not finish together, and with four generations of CTAs the
-    // hardware scheduler refills the gaps (measured: 1 wave 3949, 2: 4026, 4 or 8: 4125, 16: 3996 GB/s)
+    // hardware scheduler refills the gaps (measured at 6 CTAs per SM: 1 wave 3949, 2: 4026, 4 or 8: 4125, 16: 3996 GB/s)
     constexpr int kWaves = 4;
     if ((int64_t)grid.x > (int64_t)sms * per_sm * kWaves) grid.x = (unsigned)(sms * per_sm * kWaves);
     const int64_t stride = (int64_t)grid.x * block.x;
