@@ -66,6 +66,7 @@ int resident_ctas_impl(const void* kernel, int threads, size_t smem, int* ctas)
 // implemented in quantize.cu / gemm_simt.cu / gemm_tc.cu
 int quantize_launch(const void*, int, int64_t, int64_t, const hbq_format*, void*, int, const hbq_packed_out*,
                     const float*, cudaStream_t, const KvWriteOpts*);
+int packed_form_supported(const hbq_format*);
 int fp_quant_launch(const void*, int64_t, int, int, int, int, int, void*, cudaStream_t);
 int64_t absmax_scratch_bytes();
 int absmax_launch(const void*, int, int64_t, float*, void*, cudaStream_t);
@@ -74,6 +75,8 @@ int gemm_simt_launch(const void*, const void*, void*, int64_t, int64_t, int64_t,
 bool gemm_tc_eligible(int64_t, int64_t, int64_t, int, int, int);
 int gemm_tc_launch(const void*, const void*, void*, int64_t, int64_t, int64_t, int, int, int, const void*,
                    cudaStream_t);
+int gemm_tc_launch_ex(const void*, const void*, void*, int64_t, int64_t, int64_t, int, int, int, const void*,
+                      cudaStream_t, uint32_t, int);
 int transpose_launch(const void*, void*, int64_t, int64_t, cudaStream_t);
 int gemm_tc_status(int*);
 int gemm_tc_status_reset();
@@ -158,6 +161,7 @@ static int dequantize_launch(const hbq_packed_out* in, int64_t rows, int64_t K, 
                              void* deq, int dtype, cudaStream_t stream)
 {
     if (!in || !f || !deq || !in->codes || !in->scale_u8) return HBQ_ERR_ARG;
+    { const int rc = packed_form_supported(f); if (rc) return rc; }
     if (rows == 0 || K == 0) return HBQ_OK;
     const int B = f->block_size;
     DqArgs a;
@@ -268,10 +272,14 @@ int hbq_fp_quant(const void* x, int64_t n, int ebit, int mbit, int allow_subnorm
     return fp_quant_launch(x, n, ebit, mbit, allow_subnormal, use_ceil, elem_variant, out, (cudaStream_t)stream);
 }
 
+constexpr int64_t kMaxGemmDim = 0x7FFFFFFF;
+
 static int check_gemm_args(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int mode,
                            int group_k, int group_n)
 {
     if (!A || !B || !C || M < 0 || N < 0 || K < 0) return HBQ_ERR_ARG;
+    // every kernel indexes with 32-bit dimensions; this also keeps M*N, N*K and their byte counts inside int64
+    if (M > kMaxGemmDim || N > kMaxGemmDim || K > kMaxGemmDim) return HBQ_ERR_UNSUPPORTED;
     if (mode < HBQ_ACC_FP32 || mode > HBQ_ACC_PSUM_E3M4) return HBQ_ERR_ARG;
     if (mode >= HBQ_ACC_GROUPED && group_k <= 0) return HBQ_ERR_ARG;
     if (mode >= HBQ_ACC_PSUM_INT8 && (group_n <= 0 || 64 % group_n != 0)) return HBQ_ERR_ARG;
@@ -287,7 +295,7 @@ int hbq_gemm_uses_tensor_cores(int64_t M, int64_t N, int64_t K, int b_is_nk, int
 int64_t hbq_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int b_is_nk, int mode, int group_k, int group_n)
 {
     if (b_is_nk || !gemm_tc_eligible(M, N, K, mode, group_k, group_n)) return 0;
-    return N * K * 2;
+    return N * K * 2;      // eligible operands have N, K <= 2^30: the product fits
 }
 
 int hbq_gemm(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int b_is_nk, int mode,
@@ -318,6 +326,18 @@ int hbq_gemm_simt(const void* A, const void* B, void* C, int64_t M, int64_t N, i
     if (rc) return rc;
     if (M == 0 || N == 0) return HBQ_OK;
     return gemm_simt_launch(A, B, C, M, N, K, b_is_nk, mode, group_k, group_n, bias, (cudaStream_t)stream);
+}
+
+int hbq_gemm_wait_selftest(const void* A, const void* W, void* C, int64_t M, int64_t N, int64_t K, int mode, int group_k,
+                           int group_n, uint32_t poll_limit, void* stream)
+{
+    int rc = check_gemm_args(A, W, C, M, N, K, mode, group_k, group_n);
+    if (rc) return rc;
+    if (poll_limit == 0 || poll_limit > (1u << 23)) return HBQ_ERR_ARG;
+    if (M == 0 || N == 0 || K == 0) return HBQ_ERR_ARG;
+    if ((((uintptr_t)A | (uintptr_t)W | (uintptr_t)C) & 15) || !gemm_tc_eligible(M, N, K, mode, group_k, group_n))
+        return HBQ_ERR_UNSUPPORTED;
+    return gemm_tc_launch_ex(A, W, C, M, N, K, mode, group_k, group_n, nullptr, (cudaStream_t)stream, poll_limit, 1);
 }
 
 int hbq_gemm_status(int* status_host)

@@ -53,7 +53,10 @@ extern "C" int hbq_gemm_kn_noalloc(const void* A, const void* B, void* C, int64_
     if (mode < HBQ_ACC_FP32 || mode > HBQ_ACC_PSUM_E3M4) return HBQ_ERR_ARG;
     if (mode >= HBQ_ACC_GROUPED && group_k <= 0) return HBQ_ERR_ARG;
     if (mode >= HBQ_ACC_PSUM_INT8 && (group_n <= 0 || 64 % group_n != 0)) return HBQ_ERR_ARG;
-    if (N * K > (int64_t)HBQ_GEMM_NOALLOC_MAX_ELEMS) return HBQ_ERR_TOO_LARGE;
+    // each factor first: N * K itself could wrap for absurd sizes
+    if (N > (int64_t)HBQ_GEMM_NOALLOC_MAX_ELEMS || K > (int64_t)HBQ_GEMM_NOALLOC_MAX_ELEMS ||
+        N * K > (int64_t)HBQ_GEMM_NOALLOC_MAX_ELEMS)
+        return HBQ_ERR_TOO_LARGE;
     if (M == 0 || N == 0) return HBQ_OK;
     cudaStream_t st = (cudaStream_t)stream;
     const bool aligned = (((uintptr_t)A | (uintptr_t)B | (uintptr_t)C | (uintptr_t)bias) & 15) == 0;

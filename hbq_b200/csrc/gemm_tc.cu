@@ -27,7 +27,6 @@
 #include "common.cuh"
 #include <cuda.h>
 #include <math.h>
-#include <stdlib.h>
 #include <atomic>
 #include <mutex>
 
@@ -91,12 +90,12 @@ __device__ __forceinline__ unsigned long long gtime_ns()
 // Bounded wait.  Returns false when the limit expired or another role already gave up.  The
 // polls are non-suspending and the loop body is minimal: a poll of a completed barrier costs
 // ~160 cycles of the waiting thread, which matters for the single MMA-issuing thread.  The
-// iteration cap (2^23 polls, a fraction of a second at any clock) is the bound; the caller's
-// `code` tells hbq_gemm_status which wait gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code)
+// iteration cap (`limit` polls; 2^23 by default, a fraction of a second at any clock) is the bound;
+// the caller's `code` tells hbq_gemm_status which wait gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code, uint32_t limit)
 {
     #pragma unroll 1
-    for (uint32_t it = 0; it < (1u << 23); ++it) {
+    for (uint32_t it = 0; it < limit; ++it) {
         if (mbar_test(bar, parity)) return true;
         if ((it & 127u) == 127u && *abort_flag) return false;
     }
@@ -107,10 +106,10 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 
 // The same wait executed by a whole warp with a warp-uniform result, so the code around it stays
 // warp-uniform (loop counters, barrier addresses and descriptors can then live in uniform registers).
-__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code)
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code, uint32_t limit)
 {
     #pragma unroll 1
-    for (uint32_t it = 0; it < (1u << 23); ++it) {
+    for (uint32_t it = 0; it < limit; ++it) {
         if (__all_sync(0xFFFFFFFFu, mbar_test(bar, parity))) return true;
         if ((it & 127u) == 127u && __any_sync(0xFFFFFFFFu, *abort_flag != 0)) return false;
     }
@@ -212,8 +211,10 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr)
 // ---- epilogue arithmetic ---------------------------------------------------------------------
 // INT8 partial-sum fake quantisation of `n` consecutive columns (gemm.cu:1145-1152, 1198-1249):
 // scale = 2^(floor(log2 max|v|) - 6) (1 for an all-zero run), q = clamp(rint(v / scale), +-127).
-// v / scale is exact, so rint is one FMA against 1.5 * 2^23.  Non-finite partial sums are not
-// given the reference's special treatment.
+// v / scale is exact, so rint is one FMA against 1.5 * 2^23.  Non-finite partial sums behave as in the
+// reference: a NaN does not count towards the maximum and stays NaN (the clamp is NaN-propagating); an
+// infinite maximum makes the reference's scale infinite and with it every value of the run NaN
+// (gemm.cu:1145-1152, 1236-1249), which the NaN scale below reproduces.
 template <int GN>
 __device__ __forceinline__ void psum_int8_accumulate(const float* v, __half2* acc)
 {
@@ -221,7 +222,8 @@ __device__ __forceinline__ void psum_int8_accumulate(const float* v, __half2* ac
     #pragma unroll
     for (int i = 0; i < GN; i += 2) mx = fmaxf(fmaxf(mx, fabsf(v[i])), fabsf(v[i + 1]));
     const uint32_t e = (__float_as_uint(mx) >> 23) & 0xFFu;
-    const float scale = mx > 0.f ? __uint_as_float((e - 6u) << 23) : 1.f;
+    float scale = mx > 0.f ? __uint_as_float((e - 6u) << 23) : 1.f;
+    if (e == 255u) scale = __uint_as_float(0x7FC00000u);
     const float inv = mx > 0.f ? __uint_as_float((260u - e) << 23) : 1.f;
     constexpr float kMagic = 12582912.f;                 // 1.5 * 2^23: v*inv + kMagic rounds to an integer (RNE)
     const float unmagic = -kMagic * scale;               // exact
@@ -234,7 +236,7 @@ __device__ __forceinline__ void psum_int8_accumulate(const float* v, __half2* ac
         float t0, t1, o0, o1;
         fma2(t0, t1, v[i], v[i + 1], inv, kMagic);
         fma2(o0, o1, t0, t1, scale, unmagic);            // (t - kMagic) * scale, exact
-        const __half2 h = __hmin2(__hmax2(__floats2half2_rn(o0, o1), nlim), lim);
+        const __half2 h = __hmin2_nan(__hmax2_nan(__floats2half2_rn(o0, o1), nlim), lim);
         acc[i >> 1] = __hadd2(acc[i >> 1], h);
     }
 }
@@ -294,21 +296,11 @@ struct TcArgs {
     int chunk_k16;       // MMAs (K = 16 each) per accumulation chunk
     int issuers;         // MMA-issuing warps to use (1 or 2)
     int bn;              // tile width chosen by the host: 256, or 128 for decode-sized M
+    uint32_t poll_limit; // polls after which a wait on an mbarrier gives up (kDefaultPollLimit)
+    int withhold_loads;  // self-test of the give-up path: the producer issues no load at all, so every
+                         // consumer wait runs out with nothing in flight
 };
-
-// Developer timeline trace, compiled in only with -DHBQ_TC_TRACE: CTA 0 records clock64() at the
-// hand-off points of every chunk into a caller-provided buffer of 16 slots per chunk.
-#ifdef HBQ_TC_TRACE
-__device__ long long* g_tc_trace = nullptr;
-__device__ int g_tc_trace_chunks = 0;
-#define TC_TRACE(chunk, slot)                                                                     \
-    do {                                                                                          \
-        if (blockIdx.x == 0 && g_tc_trace && (int)(chunk) < g_tc_trace_chunks)                    \
-            g_tc_trace[(int)(chunk) * 16 + (slot)] = clock64();                                    \
-    } while (0)
-#else
-#define TC_TRACE(chunk, slot) do { } while (0)
-#endif
+constexpr uint32_t kDefaultPollLimit = 1u << 23;
 
 // ---- the kernel ------------------------------------------------------------------------------
 template <int MODE, int GN, int BN, int NSTAGE>
@@ -362,13 +354,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+            for (int t = blockIdx.x; t < total_tiles && ok && !args.withhold_loads; t += gridDim.x) {
                 const int m0 = (t % args.tiles_m) * BM, n0 = (t / args.tiles_m) * BN;
                 for (int ks = 0; ks < args.k_stages; ++ks) {
-                    if (!(ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, 1))) break;
-#ifdef HBQ_TC_TRACE
-                    if ((ks & 1) == 0) TC_TRACE(((t - blockIdx.x) / gridDim.x) * (args.k_stages / 2) + ks / 2, 9);
-#endif
+                    if (!(ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, 1, args.poll_limit))) break;
                     const uint32_t sa = tiles + stage * STAGE_BYTES, sb = sa + A_BYTES;
                     mbar_expect_tx(bar_full + 8 * stage, STAGE_BYTES);
                     tma_load_2d(sa, &mapA, ks * BK, m0, bar_full + 8 * stage);
@@ -407,18 +396,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                     const int nst = min(spc, args.k_stages - ks0);
                     if (two && (chunk & 1u) != mw) { gks += nst; continue; }
                     const uint32_t buf = chunk & 1u;
-                    TC_TRACE(chunk, 0);
                     uint32_t stage = gks % NSTAGE, phase = (gks / NSTAGE) & 1u;
                     // poll the first stage while waiting for the accumulator
                     bool full_pre = __all_sync(0xFFFFFFFFu, mbar_test(bar_full + 8 * stage, phase));
                     // the epilogue must have drained this accumulator's previous chunk (a fresh
                     // barrier passes the wait for the phase before its first)
-                    if (!(ok = mbar_wait_warp(bar_tempty + 8 * buf, ((chunk >> 1) & 1u) ^ 1u, abort_flag, 3))) break;
-                    TC_TRACE(chunk, 1);
+                    if (!(ok = mbar_wait_warp(bar_tempty + 8 * buf, ((chunk >> 1) & 1u) ^ 1u, abort_flag, 3, args.poll_limit))) break;
                     const uint32_t d_tmem = tmem_base + buf * TMEM_BUF_COLS;
                     for (int s = 0; s < nst; ++s) {
-                        if (!full_pre && !(ok = mbar_wait_warp(bar_full + 8 * stage, phase, abort_flag, 2))) break;
-                        TC_TRACE(chunk, s == 0 ? 2 : 5);
+                        if (!full_pre && !(ok = mbar_wait_warp(bar_full + 8 * stage, phase, abort_flag, 2, args.poll_limit))) break;
                         tc_fence_after();
                         const uint32_t nstage = (stage + 1 == NSTAGE) ? 0u : stage + 1, nphase = (stage + 1 == NSTAGE) ? phase ^ 1u : phase;
                         // poll for the next stage: in flight while the MMAs below are issued, consumed after
@@ -429,10 +415,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                             for (int kk = 0; kk < BK / 16; ++kk)
                                 tc_mma_f16(d_tmem, umma_desc(sa + kk * 32), umma_desc(sb + kk * 32), IDESC,
                                            (s != 0 || kk != 0) ? 1u : 0u);
-                            TC_TRACE(chunk, s == 0 ? 3 : 6);
                             tc_commit(bar_empty + 8 * stage);   // smem slot free once these MMAs retire
                             if (s + 1 == nst) tc_commit(bar_tfull + 8 * buf);
-                            TC_TRACE(chunk, s == 0 ? 4 : 7);
                         }
                         full_pre = __all_sync(0xFFFFFFFFu, next_full);
                         stage = nstage; phase = nphase;
@@ -446,7 +430,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
                 int in_chunk = 0;
                 for (int ks = 0; ks < args.k_stages && ok; ++ks) {
-                    if (!(ok = mbar_wait_warp(bar_full + 8 * stage, phase, abort_flag, 2))) break;
+                    if (!(ok = mbar_wait_warp(bar_full + 8 * stage, phase, abort_flag, 2, args.poll_limit))) break;
                     tc_fence_after();
                     const uint32_t sa = tiles + stage * STAGE_BYTES, sb = sa + A_BYTES;
                     #pragma unroll
@@ -454,7 +438,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                         const uint32_t buf = chunk & 1u;
                         if (in_chunk == 0) {
                             // the epilogue must have drained this accumulator's previous chunk
-                            if (!(ok = mbar_wait_warp(bar_tempty + 8 * buf, ((chunk >> 1) & 1u) ^ 1u, abort_flag, 3))) break;
+                            if (!(ok = mbar_wait_warp(bar_tempty + 8 * buf, ((chunk >> 1) & 1u) ^ 1u, abort_flag, 3, args.poll_limit))) break;
                             tc_fence_after();
                         }
                         const int k16 = ks * (BK / 16) + kk;
@@ -491,16 +475,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
             for (int i = 0; i < EPI_COLS / 2; ++i) acc[i] = __float2half2_rn(0.f);
             for (int c = 0; c < chunks_per_tile; ++c, ++chunk) {
                 const uint32_t buf = chunk & 1u;
-                if (threadIdx.x == 128) TC_TRACE(chunk, 10);
-#ifdef HBQ_TC_TRACE
-                if (threadIdx.x == 128 && blockIdx.x == 0 && g_tc_trace && (int)chunk < g_tc_trace_chunks)
-                    g_tc_trace[(int)chunk * 16 + 15] = (long long)gtime_ns();
-#endif
-                ok = mbar_wait(bar_tfull + 8 * buf, (chunk >> 1) & 1u, abort_flag, 4);
+                ok = mbar_wait(bar_tfull + 8 * buf, (chunk >> 1) & 1u, abort_flag, 4, args.poll_limit);
                 ok = __all_sync(0xFFFFFFFFu, ok);
                 if (!ok) break;
                 tc_fence_after();
-                if (threadIdx.x == 128) TC_TRACE(chunk, 11);
                 const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * TMEM_BUF_COLS + cgrp * EPI_COLS;
                 {
                     // the warp's whole slice of the chunk: all its 32-column loads in flight together
@@ -514,7 +492,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
-                    if (threadIdx.x == 128) TC_TRACE(chunk, 12);
                     #pragma unroll
                     for (int h = 0; h < EPI_GROUPS; ++h) {
                         float v[32];
@@ -522,8 +499,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                         for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[h][i]);
                         fold_chunk<MODE, GN>(v, acc + h * 16);
                     }
-                    if (threadIdx.x == 128) TC_TRACE(chunk, 13);
-                    if (threadIdx.x == 128 + 7 * 32) TC_TRACE(chunk, 14);
                 }
             }
             if (!ok) break;
@@ -564,14 +539,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     }
 }
 
-#ifdef HBQ_TC_TRACE
-extern "C" int hbq_tc_trace_buffer(long long* buf, int chunks)
-{
-    cudaError_t e = cudaMemcpyToSymbol(g_tc_trace, &buf, sizeof(buf));
-    if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_tc_trace_chunks, &chunks, sizeof(chunks));
-    return e == cudaSuccess ? 0 : -3;
-}
-#endif
 
 // ---- transpose [K,N] -> [N,K] ------------------------------------------------------------------
 __global__ void __launch_bounds__(256) transpose_kernel(const __half* __restrict__ in, __half* __restrict__ out,
@@ -683,8 +650,10 @@ int transpose_launch(const void* in, void* out, int64_t R, int64_t Ccols, cudaSt
 static std::atomic<int> g_reserved_sms{0};
 
 // A [M,K], W [N,K], both fp16 row-major and 16-byte aligned.
-int gemm_tc_launch(const void* A, const void* W, void* C, int64_t M, int64_t N, int64_t K, int mode,
-                   int group_k, int group_n, const void* bias, cudaStream_t stream)
+// poll_limit = 0: the default bound; withhold_loads: see TcArgs (the self-test of hbq_gemm_wait_selftest).
+int gemm_tc_launch_ex(const void* A, const void* W, void* C, int64_t M, int64_t N, int64_t K, int mode,
+                      int group_k, int group_n, const void* bias, cudaStream_t stream, uint32_t poll_limit,
+                      int withhold_loads)
 {
     if (!gemm_tc_eligible(M, N, K, mode, group_k, group_n)) return HBQ_ERR_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(C) |
@@ -707,11 +676,9 @@ int gemm_tc_launch(const void* A, const void* W, void* C, int64_t M, int64_t N, 
     if (rc) return rc;
     args.k_stages = (int)((K + BK - 1) / BK);
     args.chunk_k16 = (mode == HBQ_ACC_FP32) ? args.k_stages * (BK / 16) : group_k / 16;
-    {
-        // HBQ_TC_ISSUERS=1|2: tuning knob, number of MMA-issuing warps (default 2)
-        static const int issuers = [] { const char* e = getenv("HBQ_TC_ISSUERS"); return (e && atoi(e) == 1) ? 1 : 2; }();
-        args.issuers = issuers;
-    }
+    args.issuers = 2;
+    args.poll_limit = poll_limit ? poll_limit : kDefaultPollLimit;
+    args.withhold_loads = withhold_loads;
 
     const int64_t total = (int64_t)args.tiles_m * args.tiles_n;
     const int usable = sms - g_reserved_sms.load() > 0 ? sms - g_reserved_sms.load() : 1;
@@ -736,6 +703,12 @@ int gemm_tc_launch(const void* A, const void* W, void* C, int64_t M, int64_t N, 
             }
     }
     return HBQ_ERR_ARG;
+}
+
+int gemm_tc_launch(const void* A, const void* W, void* C, int64_t M, int64_t N, int64_t K, int mode,
+                   int group_k, int group_n, const void* bias, cudaStream_t stream)
+{
+    return gemm_tc_launch_ex(A, W, C, M, N, K, mode, group_k, group_n, bias, stream, 0, 0);
 }
 
 int gemm_tc_reserve_sms(int n)

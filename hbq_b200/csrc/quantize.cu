@@ -753,6 +753,21 @@ static int launch_mx_fast(QArgs& a, dim3 grid, dim3 block, cudaStream_t stream)
     return launch_mx_fast_as<KIND, MB, false, false>(a, grid, block, stream);
 }
 
+// The packed form stores a block's scale as one byte (bits 14..7 of its fp16 pattern) and nothing per tensor.
+// Formats whose scale does not fit that byte would dequantise to other values than their fake-quantised
+// tensor, so they have no packed form: a per-tensor scale (the tensor maximum is not stored), a scale
+// mantissa wider than 3 bits (truncated by the byte), a power-of-two scale outside fp16's exponent range.
+int packed_form_supported(const hbq_format* f)
+{
+    if (f->kind == HBQ_KIND_MXFP && f->per_tensor_scale) return HBQ_ERR_UNSUPPORTED;
+    if (f->kind == HBQ_KIND_MXFP || f->kind == HBQ_KIND_MXINT || f->kind == HBQ_KIND_HBQ) {
+        if (f->sc_mbit > 3) return HBQ_ERR_UNSUPPORTED;
+        if (f->sc_mbit > 0 && f->sc_ebit > 5) return HBQ_ERR_UNSUPPORTED;
+        if (f->kind == HBQ_KIND_MXFP && f->sc_mbit == 0 && f->sc_ebit > 5) return HBQ_ERR_UNSUPPORTED;
+    }
+    return HBQ_OK;
+}
+
 int quantize_launch(const void* x, int dtype, int64_t rows, int64_t K, const hbq_format* f,
                     void* deq, int deq_dtype, const hbq_packed_out* out, const float* tensor_amax,
                     cudaStream_t stream, const KvWriteOpts* kv)
@@ -766,6 +781,10 @@ int quantize_launch(const void* x, int dtype, int64_t rows, int64_t K, const hbq
     if (!is_pow2(B) || B < 8 || B > 256) return HBQ_ERR_UNSUPPORTED;
     const bool pts = f->kind == HBQ_KIND_MXFP && f->per_tensor_scale;    // the other kinds ignore it
     if (pts && !tensor_amax) return HBQ_ERR_ARG;
+    if (out && (out->codes || out->scale_u8)) {
+        const int rc = packed_form_supported(f);
+        if (rc) return rc;
+    }
 
     QArgs a;
     memset(&a, 0, sizeof(a));

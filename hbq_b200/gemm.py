@@ -62,6 +62,26 @@ def gemm_status() -> int:
     return v.value
 
 
+def gemm_status_reset() -> None:
+    """Clear the status word (``hbq_gemm_status_reset``)."""
+    _lib.check(_lib.lib().hbq_gemm_status_reset(), "hbq_gemm_status_reset")
+
+
+def gemm_wait_selftest(a: torch.Tensor, w: torch.Tensor, mode: int, group_k: int = 0, group_n: int = 0,
+                       poll_limit: int = 4096) -> torch.Tensor:
+    """``hbq_gemm_wait_selftest``: run the tensor-core kernel on ``a`` [M, K] and ``w`` [N, K] with its loader
+    switched off and every wait bounded by ``poll_limit`` polls.  The kernel returns with nothing computed
+    and ``gemm_status()`` becomes non-zero until ``gemm_status_reset()``.  Returns the (undefined) output."""
+    M, K = a.shape
+    N = w.shape[0]
+    c = torch.empty((M, N), dtype=torch.float16, device=a.device)
+    with _lib.device_guard(a.device):
+        rc = _lib.lib().hbq_gemm_wait_selftest(_ptr(a), _ptr(w), _ptr(c), M, N, K, mode, group_k, group_n,
+                                               int(poll_limit), _stream_ptr(a.device))
+    _lib.check(rc, "hbq_gemm_wait_selftest")
+    return c
+
+
 def gemm_reserve_sms(n: int) -> int:
     """``hbq_gemm_reserve_sms``: later tensor-core GEMM launches leave ``n`` SMs free for a kernel of
     another stream (a collective running under the GEMM); returns the previous value."""

@@ -7,6 +7,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from .ops import FP16AccumMatMul
 from .quantizer import PackedTensor, _QBase, dequantize_packed
 
 
@@ -38,6 +39,14 @@ class QLinear(nn.Linear):
             y = F.linear(xq, wq, self.bias)
         else:
             y = self.ops(xq, wq, self.bias)
+        if self.check_finite and isinstance(self.ops, FP16AccumMatMul) and y.is_cuda:
+            # the host synchronises for the non-finite guard below anyway: also ask whether a bounded wait
+            # of the tensor-core kernel ran out (its output would be undefined)
+            from .gemm import gemm_status
+            st = gemm_status()
+            if st != 0:
+                raise RuntimeError(f"tensor-core GEMM gave up on a wait (status {st}); the output is undefined. "
+                                   "Clear with hbq_gemm_status_reset after finding the cause.")
         if self.check_finite and not torch.isfinite(y).all():
             ops_name = type(self.ops).__name__ if self.ops is not None else "F.linear"
             raise RuntimeError(

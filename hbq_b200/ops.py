@@ -3,6 +3,7 @@
 Same constructor, ``forward(x, w, bias=None)`` and validation errors as the reference.  The
 reference transposes ``w`` ([N, K]) into a fresh [K, N] tensor on every call before handing it
 to the extension; here ``w`` is consumed as it is stored (K-major) by the tensor-core kernel.
+``forward`` additionally takes ``out=`` (a contiguous fp16 ``[rows, N]`` tensor to write into).
 """
 from __future__ import annotations
 
@@ -36,14 +37,14 @@ class FP16AccumMatMul(nn.Module):
                 raise ValueError(f"Invalid group size: {self.group_size}")
             if self.quant_block_size not in [4, 8, 16, 32]:
                 raise ValueError(f"Invalid quant block size: {self.quant_block_size}")
-            out2d = ext.gemm_blockquant_mxint8(x2d, wh, self.group_size, self.quant_block_size, b_is_nk=True, out=out)
+            out2d = ext.gemm_blockquant_mxint8(x2d, wh, self.group_size, self.quant_block_size, b_is_nk=True, out=out,
+                                               bias=bias)
         elif self.group_size is not None:
             if self.group_size not in [4, 8, 16, 32, 64, 128]:
                 raise ValueError(f"Invalid group size: {self.group_size}")
-            out2d = ext.gemm_fp16_grouped_accum(x2d, wh, self.group_size, b_is_nk=True, out=out)
+            out2d = ext.gemm_fp16_grouped_accum(x2d, wh, self.group_size, b_is_nk=True, out=out, bias=bias)
         else:
-            out2d = ext.gemm_fp16_accum(x2d, wh, b_is_nk=True, out=out)
-
-        if bias is not None:
-            out2d = out2d + bias
+            out2d = ext.gemm_fp16_accum(x2d, wh, b_is_nk=True, out=out, bias=bias)
+        # the bias was added by the kernel's store (one fp16 add per output, as the reference's `out2d + bias`,
+        # src/ops.py:59-60), so with `out=` the result, bias included, is in `out`
         return out2d.view(*orig_shape[:-1], -1)

@@ -11,7 +11,7 @@ import torch
 
 from .module import QLinear
 from .ops import FP16AccumMatMul
-from .quantizer import HBQQuantizer, MXFPQuantizer, MXINTQuantizer, _QBase
+from .quantizer import HBQQuantizer, MXExQuantizer, MXFPQuantizer, MXINTQuantizer, VSQQuantizer, _QBase
 
 
 def load_quant_config(path: str) -> Dict[str, Any]:
@@ -44,6 +44,9 @@ class PTQConfig:
         self.w_block_size = b.get("wgt_block_size", 32)
         self.w_per_tensor_scale = b.get("wgt_per_tensor_scale", False)
         self.scale_allow_subnormal = b.get("scale_allow_subnormal", True)
+        # MicroExponent quantization (src/ptq.py:60-61)
+        self.a_sc_bit = b.get("act_sc_bit", 8)
+        self.w_sc_bit = b.get("wgt_sc_bit", 8)
         self.qk_mx_round = b.get("qk_mx_round", False)
         self.act_scale_use_ceil = b.get("act_scale_use_ceil", False)
         self.wgt_scale_use_ceil = b.get("wgt_scale_use_ceil", False)
@@ -63,6 +66,8 @@ class PTQConfig:
         self.quant_4b_kv = q.get("quant_4b_kv", False)
         self.quant_k_cache = q.get("quant_k_cache", False)
         self.quant_v_cache = q.get("quant_v_cache", False)
+        self.quant_post_rope_qk = q.get("quant_post_rope_qk", False)        # read and unused, as in the reference
+        self.quant_attn_wgt_use_quant_kernel = q.get("quant_attn_wgt_use_quant_kernel", True)
         self.accumulation_type = acc.get("type", "fp32")
         self.accumulation_group_size = acc.get("group_size", 128)
         self.accumulation_quant_block_size = acc.get("quant_block_size", 16)
@@ -77,6 +82,11 @@ class PTQConfig:
         if self.wqtype == "mxint":
             return MXINTQuantizer(nbit=self.w_mbit, sc_ebit=self.w_sc_ebit, sc_mbit=self.w_sc_mbit,
                                   block_size=self.w_block_size, scale_allow_subnormal=self.scale_allow_subnormal)
+        if self.wqtype == "mxex":
+            return MXExQuantizer(sc_bit=self.w_sc_bit, l2_sc_bit=self.wgt_l2_sc_bit, mbit=self.w_mbit,
+                                 block_size=self.w_block_size, l2_block_size=self.wgt_l2_block_size)
+        if self.wqtype == "vsq":
+            return VSQQuantizer(nbit=self.w_mbit, block_size=self.w_block_size, sc_mbit=self.w_sc_mbit)
         if self.wqtype == "hbq":
             return HBQQuantizer(ebit=self.w_ebit, mbit=self.w_mbit, sc_ebit=self.w_sc_ebit, sc_mbit=self.w_sc_mbit,
                                 block_size=self.w_block_size, scale_allow_subnormal=self.scale_allow_subnormal,
@@ -87,7 +97,9 @@ class PTQConfig:
         raise AssertionError(f"Invalid weight quantizer type: {self.wqtype}")
 
     # ---- src/ptq.py:159-212 ----
-    def map_act_quantizer(self, use_round: bool = False):
+    def map_act_quantizer(self, use_round: bool = False, use_quant_kernel: bool = True):
+        """``use_quant_kernel`` is accepted as in the reference and has no effect: there is one
+        implementation, the CUDA kernel."""
         if self.xqtype == "mxfp":
             return MXFPQuantizer(ebit=self.a_ebit, mbit=self.a_mbit, sc_ebit=self.a_sc_ebit, sc_mbit=self.a_sc_mbit,
                                  block_size=self.a_block_size, per_tensor_scale=self.a_per_tensor_scale,
@@ -96,6 +108,11 @@ class PTQConfig:
         if self.xqtype == "mxint":
             return MXINTQuantizer(nbit=self.a_mbit, sc_ebit=self.a_sc_ebit, sc_mbit=self.a_sc_mbit,
                                   block_size=self.a_block_size, scale_allow_subnormal=self.scale_allow_subnormal)
+        if self.xqtype == "mxex":
+            return MXExQuantizer(sc_bit=self.a_sc_bit, l2_sc_bit=self.act_l2_sc_bit, mbit=self.a_mbit,
+                                 block_size=self.a_block_size, l2_block_size=self.act_l2_block_size)
+        if self.xqtype == "vsq":
+            return VSQQuantizer(nbit=self.a_mbit, block_size=self.a_block_size, sc_mbit=self.a_sc_mbit)
         if self.xqtype == "hbq":
             return HBQQuantizer(ebit=self.a_ebit, mbit=self.a_mbit, sc_ebit=self.a_sc_ebit, sc_mbit=self.a_sc_mbit,
                                 block_size=self.a_block_size, scale_allow_subnormal=self.scale_allow_subnormal,
@@ -129,6 +146,56 @@ class PTQConfig:
         if self.quant_4b_kv:
             return self.map_4b_kv_quantizer(use_round=self.qk_mx_round)
         return self.map_act_quantizer(use_round=self.qk_mx_round)
+
+    # ---- src/ptq.py:259-290: quantizers of one attention block ----
+    def q_attn(self, module):
+        """``module`` has ``q_proj / k_proj / v_proj / o_proj`` (``QLinear``-like: fields ``wq``, ``aq``,
+        ``yq``) and receives the switches and quantizers the reference's attention forwards read:
+        ``quant_attn_wgt``, ``quant_post_rope_q``, ``quant_k_cache``, ``quant_v_cache``,
+        ``kv_quantizer``, ``attn_wgt_quantizer``."""
+        module.quant_attn_wgt = self.quant_attn_wgt
+        module.quant_post_rope_q = self.quant_post_rope_q
+        module.quant_k_cache = self.quant_k_cache
+        module.quant_v_cache = self.quant_v_cache
+        module.kv_quantizer = self.map_kv_quantizer()
+        module.attn_wgt_quantizer = (self.map_act_quantizer(use_round=self.qk_mx_round,
+                                                            use_quant_kernel=self.quant_attn_wgt_use_quant_kernel)
+                                     if self.quant_attn_wgt else None)
+        for proj in (module.q_proj, module.k_proj):
+            proj.wq = self.map_wgt_quantizer(use_round=self.qk_mx_round)
+            proj.aq = self.map_act_quantizer(use_round=self.qk_mx_round)
+        module.v_proj.wq = self.map_wgt_quantizer()
+        module.v_proj.aq = self.map_act_quantizer()
+        module.o_proj.wq = self.map_wgt_quantizer()
+        module.o_proj.aq = self.map_act_quantizer()
+        if self.quant_before_rms_norm:
+            module.o_proj.yq = self.map_act_quantizer()
+
+    # ---- src/ptq.py:292-324: quantizers of one gated MLP (names of the Llama / Qwen2 block, or of a Mixtral expert) ----
+    def _q_gated(self, module, gate: str, up: str, down: str):
+        u, g, d = getattr(module, up), getattr(module, gate), getattr(module, down)
+        u.wq, u.aq = self.map_wgt_quantizer(), self.map_act_quantizer()
+        if self.quant_before_hadamard:
+            u.yq = self.map_act_quantizer()
+            module.quantizer_after_act_fn = self.map_act_quantizer(None)
+        g.wq, g.aq = self.map_wgt_quantizer(), self.map_act_quantizer()
+        if self.quant_before_silu:
+            g.yq = self.map_act_quantizer()
+        d.wq, d.aq = self.map_wgt_quantizer(), self.map_act_quantizer()
+        if self.quant_before_rms_norm:
+            d.yq = self.map_act_quantizer()
+
+    def q_mlp(self, module):
+        self._q_gated(module, "gate_proj", "up_proj", "down_proj")
+
+    def q_mixtral_expert(self, module):
+        self._q_gated(module, "w1", "w3", "w2")
+
+    @torch.no_grad()
+    def static_quant_linear_weight(self, linear):
+        """``weight.data = linear.wq(weight)`` (src/ptq.py:337-358; the reference's row chunking only bounds
+        the memory of its eager quantizer, which expands tensors 4-8x, and is not needed here)."""
+        linear.weight.data = linear.wq(linear.weight.data)
 
     # ---- src/ptq.py:384-404 ----
     def make_accum_op(self) -> Optional[FP16AccumMatMul]:

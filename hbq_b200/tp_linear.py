@@ -13,9 +13,12 @@ ways a transformer block needs:
   step of the path.  The rows are cut into pieces; piece i is all-reduced on a side stream while
   the kernels of piece i+1 run, so that the transfer hides under the GEMM.
 
-The cross-rank sum is not the reference's single sequential chain, so a K split keeps bit parity
-only for world size 1; for the fp32 accumulation model the difference is one extra fp16 rounding
-per rank and partial product.
+The cross-rank sum is not the reference's single sequential chain, so a K split changes the bits:
+for the fp32 accumulation model the difference is one extra fp16 rounding per rank and partial
+product.  At world size 1 the layer equals ``QLinear`` with the same operator bit for bit when an
+``FP16AccumMatMul`` is set; with ``ops=None`` it runs the tensor-core fp32-accumulation kernel where
+``QLinear`` calls ``F.linear`` (cuBLAS), two fp32-accumulating GEMMs whose outputs agree to the
+fp16 output rounding, not bit for bit.
 """
 from __future__ import annotations
 
@@ -51,6 +54,9 @@ class ColumnParallelQLinear(QLinear):
         self.n0, self.n1 = column_range(out_features, _rank(group), _world(group), multiple)
         self.full_out_features = out_features
         self.gather_output = gather_output
+        if gather_output and (out_features // multiple) % _world(group) != 0:
+            raise ValueError(f"gather_output needs equal shards: {out_features // multiple} blocks of {multiple} output "
+                             f"features do not divide over {_world(group)} ranks")
         super().__init__(in_features, self.n1 - self.n0, bias, ops=ops, check_finite=check_finite,
                          device=device, dtype=dtype)
 
@@ -92,6 +98,12 @@ class RowParallelQLinear(QLinear):
         super().__init__(self.k1 - self.k0, out_features, bias, ops=ops, check_finite=check_finite,
                          device=device, dtype=dtype)
 
+    def _check_quantizer(self):
+        # a per-tensor scale is the maximum over the WHOLE input; this layer sees one K slice of some rows
+        # at a time, so the result would depend on the sharding and the row pieces
+        if getattr(self.aq, "per_tensor_scale", False) and type(self.aq).__name__ == "MXFPQuantizer":
+            raise ValueError("RowParallelQLinear does not take an activation quantizer with per_tensor_scale")
+
     @torch.no_grad()
     def load_full(self, weight: torch.Tensor, bias: Optional[torch.Tensor] = None):
         self.weight.data.copy_(weight[:, self.k0:self.k1])
@@ -123,6 +135,8 @@ class RowParallelQLinear(QLinear):
 
     def forward(self, x: torch.Tensor, input_quantized: bool = False):
         world = _world(self.group)
+        if not input_quantized:
+            self._check_quantizer()
         lead = x.shape[:-1]
         x2d = x.reshape(-1, x.shape[-1])
         rows = x2d.shape[0]

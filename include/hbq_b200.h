@@ -199,6 +199,15 @@ int hbq_gemm_kn_noalloc(const void* A, const void* B, void* C, int64_t M, int64_
  * No reference counterpart (the reference kernels do not wait on anything). */
 int hbq_gemm_status(int* status_host);
 int hbq_gemm_status_reset(void);
+/* Self-test of that give-up path, for a test suite: launches the tensor-core kernel on the given
+ * problem (A [M,K], W [N,K], C [M,N] as for hbq_gemm with b_is_nk = 1; the shape must be one
+ * hbq_gemm_uses_tensor_cores accepts) with its loader switched off and the wait bound lowered to
+ * `poll_limit` polls (1 .. 2^23).  Nothing is ever in flight, so every wait inside the kernel runs
+ * out, every role leaves its loop, tensor memory is freed and the kernel returns normally; afterwards
+ * hbq_gemm_status reports a non-zero code (2 = operand wait, 4 = accumulator wait) until
+ * hbq_gemm_status_reset.  C is left undefined.  No reference counterpart. */
+int hbq_gemm_wait_selftest(const void* A, const void* W, void* C, int64_t M, int64_t N, int64_t K,
+                           int mode, int group_k, int group_n, uint32_t poll_limit, void* stream);
 
 /* The tensor-core kernel is persistent: one CTA per SM, each holding most of an SM's shared
  * memory, with a fixed round-robin share of the tiles.  A kernel of another stream that already

@@ -2,7 +2,7 @@
 for sm_100a, from the sources where they lie in the reference checkout, into
 ``oracle/_ref/blockquant_ext.so`` -- TEST INFRASTRUCTURE: the on-device oracle of the GEMM tests.
 
-    python oracle/build_ref.py [/path/to/HBQ]
+    python oracle/build_ref.py /path/to/HBQ        (or: HBQ_REFERENCE_DIR=/path/to/HBQ python oracle/build_ref.py)
 
 Nothing is copied into this repository; only the built module lands in ``oracle/_ref/`` (which
 is git-ignored).  The flags are those of the reference's setup.py (-O3 --use_fast_math
@@ -18,7 +18,9 @@ OUT = os.path.join(HERE, "_ref")
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("HBQ_REFERENCE_DIR")
+    if not ref or not os.path.isdir(os.path.join(ref, "blockquant_ext_src")):
+        raise SystemExit("usage: build_ref.py REFERENCE_DIR (a checkout of SeoLabCornell/HBQ), or set HBQ_REFERENCE_DIR")
     src = os.path.join(ref, "blockquant_ext_src")
     cu, cpp = os.path.join(src, "gemm.cu"), os.path.join(src, "blockquant_ext.cpp")
     so = os.path.join(OUT, "blockquant_ext.so")

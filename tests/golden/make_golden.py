@@ -26,7 +26,9 @@ import warnings
 import numpy as np
 import torch
 
-REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("HBQ_REFERENCE_DIR", "/root/reference")
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("HBQ_REFERENCE_DIR")
+if not REF or not os.path.isdir(os.path.join(REF, "src")):
+    raise SystemExit("usage: make_golden.py REFERENCE_DIR (a checkout of SeoLabCornell/HBQ), or set HBQ_REFERENCE_DIR")
 sys.path.insert(0, REF)
 from src.quantizer import (HBQQuantizer, MXExQuantizer, MXFPQuantizer, MXINTQuantizer,  # noqa: E402
                            VSQQuantizer, fp_quant, make_fp_quant)

@@ -238,3 +238,38 @@ def test_more_than_2_31_elements(name):
     assert torch.equal(back[rows - 128:].view(torch.int16), tail.view(torch.int16))
     assert torch.equal(back[2 ** 31 // K - 64:2 ** 31 // K + 64].view(torch.int16),
                        yd[2 ** 31 // K - 64:2 ** 31 // K + 64].view(torch.int16))
+
+
+def test_packed_form_round_trips_or_is_refused():
+    """Every format with a packed form: dequantize(pack(x)) == q(x) bit for bit.  Formats whose scale does not
+    fit the packed layout (a per-tensor scale, a scale mantissa wider than 3 bits, a power-of-two scale beyond
+    fp16's exponent range) are refused by both directions instead of dequantising to other values."""
+    import hbq_b200 as H
+    x = dev(seeded_inputs("act", 64, 1024, seed=77))
+    f = load_formats()
+    for name, spec in sorted(f.items()):
+        if spec["kind"] in ("mxex", "vsq"):
+            continue
+        q = make_quantizer(spec)
+        fmt = q._format()
+        refused = (spec.get("per_tensor_scale", False) or fmt.sc_mbit > 3 or
+                   (spec["kind"] == "mxfp" and fmt.sc_mbit == 0 and fmt.sc_ebit > 5))
+        if refused:
+            with pytest.raises(H.HbqError):
+                q.quantize_packed(x)
+            continue
+        packed, y = q.quantize_packed(x, with_deq=True)
+        back = H.dequantize_packed(packed)
+        a, b = hbits(back), hbits(y).copy()
+        if spec["kind"] == "mxint":
+            b[b == 0x8000] = 0            # two's-complement codes cannot carry the reference's -0.0
+        assert np.array_equal(a, b), name
+    for q in (H.MXFPQuantizer(16, 2, 1, 4, 3, per_tensor_scale=True), H.MXFPQuantizer(32, 2, 1, 8, 0),
+              H.MXINTQuantizer(8, 5, 6, 32)):
+        q.q(x)                                          # the fake-quantised tensor itself is served
+        with pytest.raises(H.HbqError):
+            q.quantize_packed(x)
+        lin = H.QLinear(1024, 64, bias=False, device="cuda", dtype=torch.float16)
+        lin.weight.data = x.clone()
+        with pytest.raises(H.HbqError):
+            lin.pack_weight(q)

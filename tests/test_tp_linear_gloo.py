@@ -46,6 +46,21 @@ def _worker(rank, world, port, out_dir):
         full_up = gathered(x)
     ok = ok and y.shape == ref.shape and torch.allclose(y, ref, rtol=1e-5, atol=1e-5)
     ok = ok and torch.equal(full_up, torch.nn.functional.linear(x, w_up, b_up))
+    # shards of unequal width cannot be all-gathered into equal buffers: refused at construction
+    try:
+        H.ColumnParallelQLinear(Hd, 96, bias=False, gather_output=True, multiple=32)      # 3 blocks over 2 ranks
+        ok = False
+    except ValueError:
+        pass
+    uneven = H.ColumnParallelQLinear(Hd, 96, bias=False, multiple=32)                    # fine while it stays sharded
+    ok = ok and (uneven.n1 - uneven.n0) == (64 if rank == 0 else 32)
+    # a per-tensor-scaled activation quantizer would make the result depend on the sharding: refused
+    down.aq = H.MXFPQuantizer(16, 2, 1, 4, 3, per_tensor_scale=True)
+    try:
+        down(h)
+        ok = False
+    except ValueError:
+        pass
     # every rank holds the same reduced result
     ys = [torch.empty_like(y) for _ in range(world)]
     dist.all_gather(ys, y)
