@@ -12,6 +12,7 @@
 #include "quantize_dev.cuh"
 #include <stdlib.h>
 #include "vcache_dev.cuh"
+#include "quantize_tab.cuh"
 #include <math.h>
 #include <mutex>
 
@@ -936,7 +937,9 @@ int quantize_launch(const void* x, int dtype, int64_t rows, int64_t K, const hbq
         return hbq_lut_v_launch(a, fast_mb, x, deq, a.in_bf16, a.out_bf16, kv->B, kv->T, kv->H, kv->D, kv->v_out_token_major, stream);
     {
         bool launched = false;
-        const int rc = hbq_lut_try_launch(a, fast_mb, stream, &launched);
+        int rc = hbq_tab_try_launch(a, fast_mb, stream, &launched);          // byte-table kernels (quantize_tab.cu)
+        if (rc != HBQ_OK || launched) return rc;
+        rc = hbq_lut_try_launch(a, fast_mb, stream, &launched);
         if (rc != HBQ_OK || launched) return rc;
     }
     if (a.glu_gate) return HBQ_ERR_UNSUPPORTED;

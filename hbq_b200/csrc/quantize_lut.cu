@@ -15,7 +15,9 @@
 // reference's (src/quantizer.py:741-859).
 #include "quantize_dev.cuh"
 #include "vcache_dev.cuh"
+#include "quantize_tab.cuh"
 #include <math.h>
+#include <stdlib.h>
 #include <string.h>
 
 namespace hbq {
@@ -738,9 +740,36 @@ struct CachedPlan {
     bool ok;
     LutPlan plan;
     uint16_t rm[8], rt[LUT_MAX_CAND], big_l1;       // derived kernel arguments (see LutArgs)
+    uint32_t* bytes;                                // byte form of the table (hbq_tab_table), or NULL
+    int nbytes_entries;
 };
 static std::mutex g_plan_mutex;
 static std::vector<CachedPlan> g_plans;
+
+// Byte form of a plan's candidate table, for E2M1 / E2M2 elements: entry e (the |a| pattern base + e) holds,
+// for each of the four candidates, the TOP BYTE of the fp16 pattern of the element value Q(fp16(a / t_i)) --
+// every E2M1 / E2M2 value has at most two mantissa bits, so that byte followed by a zero byte IS the value.
+// Padded with copies of the last entry to a multiple of 4 entries (16 bytes, the bulk-copy granule).
+static void byte_table_build(CachedPlan& c)
+{
+    const LutPlan& p = c.plan;
+    const int n = p.hi - p.base + 1, npad = (n + 3) & ~3;
+    c.bytes = (uint32_t*)malloc(sizeof(uint32_t) * npad);           // kept for the life of the process
+    c.nbytes_entries = npad;
+    for (int e = 0; e < npad; ++e) {
+        const uint32_t u = (uint32_t)(p.base + (e < n ? e : n - 1));
+        uint32_t w = 0;
+        for (int i = 0; i < LUT_MAX_CAND; ++i) {
+            int lvl = 0;
+            for (int k = 1; k < p.nlev; ++k) lvl += (u >= p.thr[i][k]) ? 1 : 0;
+            uint32_t hb = d2h(e2_value(c.mb, lvl));
+            for (int h = 0; h < p.nhole[i]; ++h)
+                if (u == p.hole[i][h]) hb = 0;
+            w |= (hb >> 8) << (8 * i);
+        }
+        c.bytes[e] = w;
+    }
+}
 
 // Plans depend on the format only; building one costs ~2000 scalar quantizer evaluations.
 static void plan_to_args(const CachedPlan& c, LutArgs* a)
@@ -779,6 +808,33 @@ static bool get_plan(int mb, const float* tab, int nc, LutArgs* out)
     if (g_plans.size() < 64) g_plans.push_back(c);
     if (c.ok) plan_to_args(c, out);
     return c.ok;
+}
+
+// The byte table of a format for the kernels of quantize_tab.cu; false when the format has none (elements
+// wider than E2M2, no table plan, or the cache of plans is full).  `slot` identifies the format among the
+// cached ones (stable for the life of the process).
+bool hbq_tab_table(int mb, const float* tab, int nc, TabTable* out)
+{
+    if (mb < 1 || mb > 2) return false;
+    LutArgs scratch;
+    memset(&scratch, 0, sizeof(scratch));
+    if (!get_plan(mb, tab, nc, &scratch)) return false;
+    std::lock_guard<std::mutex> lock(g_plan_mutex);
+    for (size_t i = 0; i < g_plans.size(); ++i) {
+        CachedPlan& c = g_plans[i];
+        if (c.ok && c.mb == mb && c.nc == nc && memcmp(c.tab, tab, sizeof(float) * nc) == 0) {
+            if (!c.bytes) byte_table_build(c);
+            out->slot = (int)i;
+            out->host = c.bytes;
+            out->entries = c.nbytes_entries;
+            out->base = c.plan.base;
+            out->hi = c.plan.hi;
+            out->big_l1 = c.big_l1;
+            memcpy(out->rm, c.rm, sizeof(c.rm));
+            return true;
+        }
+    }
+    return false;
 }
 
 template <int MB>

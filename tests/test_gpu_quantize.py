@@ -254,6 +254,8 @@ def test_packed_form_round_trips_or_is_refused():
         fmt = q._format()
         refused = (spec.get("per_tensor_scale", False) or fmt.sc_mbit > 3 or
                    (spec["kind"] == "mxfp" and fmt.sc_mbit == 0 and fmt.sc_ebit > 5))
+        if spec["kind"] == "hbq":           # packed micro-scale indices: whole bytes per block, up to one 32-bit word
+            refused = refused or (spec["block_size"] // spec["l2_block_size"]) * spec["l2_sc_bit"] not in (8, 16, 32)
         if refused:
             with pytest.raises(H.HbqError):
                 q.quantize_packed(x)
