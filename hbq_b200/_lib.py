@@ -12,6 +12,7 @@ LIB_PATH = os.path.join(HERE, "lib", "libhbq_b200.so")
 
 KIND_MXFP, KIND_MXINT, KIND_HBQ, KIND_MXEX, KIND_VSQ = 0, 1, 2, 3, 4
 ERR_UNSUPPORTED = -2          # HBQ_ERR_UNSUPPORTED
+ERR_ALIGN = -4                # HBQ_ERR_ALIGN
 DTYPE_F16, DTYPE_BF16 = 0, 1
 L2_SCHEMES = ["PoT", "INT", "SIG-1", "FP-1", "FP1", "FP-10", "FP-100", "Mix"]
 ACC_FP32, ACC_FP16, ACC_GROUPED, ACC_PSUM_INT8, ACC_PSUM_E3M4 = range(5)
@@ -21,7 +22,7 @@ GEMM_NOALLOC_MAX_ELEMS = 4 * 1024 * 1024      # HBQ_GEMM_NOALLOC_MAX_ELEMS
 EXPORTS = [
     "hbq_quantize", "hbq_absmax", "hbq_absmax_scratch_bytes", "hbq_dequantize", "hbq_fp_quant",
     "hbq_gemm", "hbq_gemm_workspace_bytes", "hbq_gemm_uses_tensor_cores", "hbq_gemm_simt",
-    "hbq_gemm_kn_noalloc", "hbq_kv_write_k", "hbq_kv_write_v", "hbq_swiglu_quantize",
+    "hbq_gemm_kn_noalloc", "hbq_kv_write_k", "hbq_kv_write_v", "hbq_swiglu_quantize", "hbq_rmsnorm_quantize", "hbq_softmax_quantize",
     "hbq_gemm_status", "hbq_gemm_status_reset", "hbq_gemm_wait_selftest", "hbq_gemm_reserve_sms", "hbq_error_string", "hbq_last_cuda_error",
     "hbq_version", "hbq_launch_count",
 ]
@@ -70,6 +71,8 @@ def lib() -> ctypes.CDLL:
     L.hbq_kv_write_k.argtypes = [vp, ci, i64, i64, i64, i64, vp, vp, i64, vp, ctypes.POINTER(Format), vp, ci, vp]
     L.hbq_kv_write_v.argtypes = [vp, ci, i64, i64, i64, i64, ctypes.POINTER(Format), vp, ci, ci, vp]
     L.hbq_swiglu_quantize.argtypes = [vp, vp, i64, i64, ctypes.POINTER(Format), vp, vp]
+    L.hbq_rmsnorm_quantize.argtypes = [vp, vp, vp, ctypes.c_float, i64, i64, ctypes.POINTER(Format), vp, vp, vp]
+    L.hbq_softmax_quantize.argtypes = [vp, i64, i64, i64, i64, ctypes.c_float, ci, vp, i64, ctypes.POINTER(Format), vp, vp]
     L.hbq_gemm_workspace_bytes.argtypes = [i64, i64, i64, ci, ci, ci, ci]
     L.hbq_gemm_workspace_bytes.restype = i64
     L.hbq_gemm_uses_tensor_cores.argtypes = [i64, i64, i64, ci, ci, ci, ci]

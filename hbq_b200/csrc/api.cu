@@ -67,6 +67,10 @@ int resident_ctas_impl(const void* kernel, int threads, size_t smem, int* ctas)
 int quantize_launch(const void*, int, int64_t, int64_t, const hbq_format*, void*, int, const hbq_packed_out*,
                     const float*, cudaStream_t, const KvWriteOpts*);
 int packed_form_supported(const hbq_format*);
+int rmsnorm_quantize_launch(const void*, const void*, const void*, float, int64_t, int64_t, const hbq_format*, void*, void*,
+                            cudaStream_t);
+int softmax_quantize_launch(const void*, int64_t, int64_t, int64_t, int64_t, float, int, const void*, int64_t,
+                            const hbq_format*, void*, cudaStream_t);
 int fp_quant_launch(const void*, int64_t, int, int, int, int, int, void*, cudaStream_t);
 int64_t absmax_scratch_bytes();
 int absmax_launch(const void*, int, int64_t, float*, void*, cudaStream_t);
@@ -252,6 +256,18 @@ int hbq_swiglu_quantize(const void* gate, const void* up, int64_t rows, int64_t 
     if (!gate || !up || !out) return HBQ_ERR_ARG;
     KvWriteOpts o = {nullptr, nullptr, 0, 0, 0, 0, 0, 0, nullptr, 0, gate};
     return quantize_launch(up, HBQ_DTYPE_F16, rows, K, fmt, out, HBQ_DTYPE_F16, nullptr, nullptr, (cudaStream_t)stream, &o);
+}
+
+int hbq_rmsnorm_quantize(const void* x, const void* residual, const void* weight, float eps, int64_t rows, int64_t K,
+                         const hbq_format* fmt, void* x_out, void* out, void* stream)
+{
+    return rmsnorm_quantize_launch(x, residual, weight, eps, rows, K, fmt, x_out, out, (cudaStream_t)stream);
+}
+
+int hbq_softmax_quantize(const void* scores, int64_t rows, int64_t S, int64_t L, int64_t heads, float scale, int causal,
+                         const void* mask, int64_t mask_batches, const hbq_format* fmt, void* out, void* stream)
+{
+    return softmax_quantize_launch(scores, rows, S, L, heads, scale, causal, mask, mask_batches, fmt, out, (cudaStream_t)stream);
 }
 
 int hbq_absmax(const void* x, int dtype, int64_t n, float* amax, void* scratch, void* stream)

@@ -769,6 +769,33 @@ int packed_form_supported(const hbq_format* f)
     return HBQ_OK;
 }
 
+// The format part of QArgs for an HBQ format (candidate tables, element maxima, scale rule), as
+// quantize_launch fills it; *mb = mantissa bits of the E2Mx element.  HBQ_ERR_UNSUPPORTED for anything else.
+int hbq_format_qargs(const hbq_format* f, QArgs* a, int* mb)
+{
+    if (!f || f->kind != HBQ_KIND_HBQ) return HBQ_ERR_UNSUPPORTED;
+    const int B = f->block_size, L = f->l2_block_size;
+    if (!is_pow2(B) || B < 8 || B > 256) return HBQ_ERR_UNSUPPORTED;
+    if (f->ebit != 2 || f->mbit < 1 || f->mbit > 3 || f->sc_mbit == 0) return HBQ_ERR_UNSUPPORTED;
+    if (!is_pow2(L) || L < 4 || L > B || f->l2_sc_bit < 0 || f->l2_sc_bit > 4) return HBQ_ERR_UNSUPPORTED;
+    memset(a, 0, sizeof(*a));
+    a->f = *f;
+    a->f.per_tensor_scale = 0;
+    a->G = B / 8;
+    a->scale_fast_e5m3 = (f->sc_ebit == 5 && f->sc_mbit == 3 && !f->use_ceil && !f->scale_allow_subnormal);
+    a->elem_max = (float)h_max_norm(f->ebit, f->mbit);
+    a->nc = 1 << f->l2_sc_bit;
+    a->nscheme = l2_tables(f->l2_scheme, f->l2_sc_bit, a->tab);
+    if (a->nscheme < 0) return HBQ_ERR_ARG;
+    for (int s = 0; s < a->nscheme; ++s) {
+        float tmax = a->tab[s][0];
+        for (int i = 0; i < a->nc; ++i) tmax = fmaxf(tmax, a->tab[s][i]);
+        a->ele_max[s] = h_rh(h_rh(a->elem_max) * tmax);
+    }
+    *mb = f->mbit;
+    return HBQ_OK;
+}
+
 int quantize_launch(const void* x, int dtype, int64_t rows, int64_t K, const hbq_format* f,
                     void* deq, int deq_dtype, const hbq_packed_out* out, const float* tensor_amax,
                     cudaStream_t stream, const KvWriteOpts* kv)

@@ -118,12 +118,15 @@ __device__ __forceinline__ int first_min4(const float* acc)
 
 // The C chunks of one thread-unit, after the block scale is known.  SMALL: see chunk_errors (warp-uniform).
 // On return xb[k] holds chunk k's fake-quantised values (fp16 pairs with the inputs' signs), `bests` the chosen
-// candidate of every chunk (2 bits each) and the return value is the packed minimum of all quotients a (the
-// caller's trigger for the exact sign-of-zero rule).
-template <int MB, int C, int ML, bool SMALL, bool SIDE>
+// candidate of every chunk (2 bits each) and the return value is the packed minimum of all quotients a.
+// The reference returns +0 (not -0) when fp16(a / t) is exactly zero; only quotients a below 2^-19 can do
+// that, and deciding it needs the exact a (the scaled division may be off down there), so it is a rare slow
+// path.  TINY = 0: the caller runs it (from the returned minimum, re-reading its inputs); 1: it runs here, per
+// chunk, before the inputs are overwritten; 2: the inputs are non-negative, the rule cannot apply.
+template <int MB, int C, int ML, bool SMALL, bool SIDE, int TINY>
 __device__ __forceinline__ uint32_t unit_chunks(const TabArgs& a, const uint32_t tab_addr, const uint32_t* s_nt2,
-                                                 uint32_t (*xb)[4], uint32_t l1b, const uint4 cst, int m_lanes,
-                                                 uint32_t& bests, uint32_t (*cwout)[4])
+                                                 const float* s_tabf, uint32_t (*xb)[4], uint32_t l1b, const uint4 cst,
+                                                 int m_lanes, uint32_t& bests, uint32_t (*cwout)[4])
 {
     const __half2 pre2 = bits_h2(cst.x), post2 = bits_h2(cst.y), nm2 = bits_h2(cst.z), rm2 = bits_h2(cst.w);
     const uint32_t l1u = l1b * 0x00010001u;
@@ -136,7 +139,7 @@ __device__ __forceinline__ uint32_t unit_chunks(const TabArgs& a, const uint32_t
     const uint32_t addr0 = tab_addr - 4u * (a.base2 & 0xFFFFu);
     #pragma unroll
     for (int k = 0; k < C; ++k) {
-        uint32_t ent[8];
+        uint32_t ent[8], av[TINY == 1 ? 4 : 1];
         #pragma unroll
         for (int p = 0; p < 4; ++p) {
             // a = fp16(|x| / l1) by the pre-scaled Markstein division (exact for every quotient >= 2^-14)
@@ -145,7 +148,8 @@ __device__ __forceinline__ uint32_t unit_chunks(const TabArgs& a, const uint32_t
             const __half2 r = __hfma2(q0, nm2, axs);
             const __half2 q1 = __hfma2(r, rm2, q0);
             const __half2 aa = __hmul2(q1, post2);
-            amin = h2_bits(__hmin2(bits_h2(amin), aa));
+            if (TINY == 0) amin = h2_bits(__hmin2(bits_h2(amin), aa));
+            if (TINY == 1) av[p] = h2_bits(aa);
             const uint32_t w = h2_bits(__hmin2(__hmax2(aa, bits_h2(a.base2)), bits_h2(a.hi2)));
             uint32_t e0, e1;
             // entry address = pattern * 4 + addr0; the 4 is a kernel argument so that the scaling stays one
@@ -174,32 +178,47 @@ __device__ __forceinline__ uint32_t unit_chunks(const TabArgs& a, const uint32_t
         const uint32_t wsel = 0x4C08u + (uint32_t)best * 0x1111u;
         const uint32_t ntb = s_nt2[best];
         const __half2 tlb = __hmul2(bits_h2(l1u), bits_h2(ntb));
+        uint32_t dq[4];
         #pragma unroll
         for (int p = 0; p < 4; ++p) {
             const uint32_t cw = prmt(ent[2 * p], ent[2 * p + 1], wsel);
             if (SIDE) cwout[k][p] = cw;
             const __half2 dneg = SMALL ? __hmul2(bits_h2(cw), tlb)
                                        : __hmul2(__hmul2(bits_h2(cw), bits_h2(ntb)), bits_h2(l1u));
-            xb[k][p] = (h2_bits(dneg) & 0x7FFF7FFFu) | (xb[k][p] & 0x80008000u);
+            dq[p] = (h2_bits(dneg) & 0x7FFF7FFFu) | (xb[k][p] & 0x80008000u);
         }
+        if (TINY == 1) {
+            const __half2 am = __hmin2(__hmin2(bits_h2(av[0]), bits_h2(av[1])), __hmin2(bits_h2(av[2]), bits_h2(av[3])));
+            if (__hle2_mask(am, bits_h2(0x00200020u)) != 0u) {
+                const float l1f = __half2float(bits_h((uint16_t)l1b)), tc = s_tabf[best];
+                #pragma unroll
+                for (int p = 0; p < 4; ++p)
+                    #pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const uint32_t xbits = (xb[k][p] >> (16 * h)) & 0xFFFFu;
+                        if ((xbits & 0x8000u) && ((av[p] >> (16 * h)) & 0xFFFFu) <= 0x0020u) {
+                            const float xf = __half2float(bits_h((uint16_t)(xbits & 0x7FFFu)));
+                            if (rh(__fdiv_rn(rh(__fdiv_rn(xf, l1f)), tc)) == 0.f) dq[p] &= ~(0x8000u << (16 * h));
+                        }
+                    }
+            }
+        }
+        #pragma unroll
+        for (int p = 0; p < 4; ++p) xb[k][p] = dq[p];
     }
     return amin;
 }
 
-// GT / ML: lanes per block / per micro-block as compile-time constants (0: read from the arguments).
-template <int MB, int C, int GT, int ML, bool SIDE, bool GLU>
-__global__ void __launch_bounds__(TAB_THREADS, 2) hbq_tab_kernel(const TabArgs a)
+// Stage a format's tables into shared memory; every thread of the CTA calls it.  The candidate table comes
+// by ONE bulk async copy whose completion is counted on an mbarrier, with a bounded wait: if the copy has not
+// landed by then, every thread loads the table with plain loads (the same values, so a late completion of the
+// copy is harmless).  Returns the shared-memory address of the table.
+__device__ __forceinline__ uint32_t stage_table(const TabArgs& a, uint32_t* s_tab, uint4* s_l1c, unsigned long long* s_bar,
+                                                 uint32_t* s_nt2, float* s_tabf, int nthreads)
 {
-    extern __shared__ __align__(128) uint32_t s_tab[];
-    __shared__ uint4 s_l1c[256];             // per E5M3 scale (pattern >> 7): {2^s1, 2^-(s1+e), -m, fp16(1/m)} as fp16 pairs
-    __shared__ __align__(8) unsigned long long s_bar;
-    __shared__ uint32_t s_nt2[4];            // the candidates, where a run-time index can reach them
-    __shared__ float s_tabf[4];
-    const int tid = threadIdx.x, lane = tid & 31;
+    const int tid = threadIdx.x;
     if (tid < 4) { s_nt2[tid] = a.nt2[tid]; s_tabf[tid] = a.tabf[tid]; }
-
-    // ---- stage the candidate table: one bulk async copy, completion on an mbarrier ----
-    const uint32_t bar = smem_addr(&s_bar), dst = smem_addr(s_tab);
+    const uint32_t bar = smem_addr(s_bar), dst = smem_addr(s_tab);
     const uint32_t bytes = (uint32_t)a.entries * 4u;
     if (tid == 0) {
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar));
@@ -222,8 +241,6 @@ __global__ void __launch_bounds__(TAB_THREADS, 2) hbq_tab_kernel(const TabArgs a
         c.w = (uint32_t)a.rm[(l1b >> 7) & 7u] * 0x00010001u;
         s_l1c[tid] = c;
     }
-    // bounded wait; if the copy has not landed by then, every thread loads the table with plain loads
-    // (the same values, so a late completion of the copy is harmless)
     bool landed = false;
     #pragma unroll 1
     for (int it = 0; it < (1 << 20) && !landed; ++it) {
@@ -235,9 +252,42 @@ __global__ void __launch_bounds__(TAB_THREADS, 2) hbq_tab_kernel(const TabArgs a
     if (!__syncthreads_and(landed ? 1 : 0)) {
         const uint4* src = reinterpret_cast<const uint4*>(a.table);
         uint4* d4 = reinterpret_cast<uint4*>(s_tab);
-        for (int i = tid; i < a.entries / 4; i += TAB_THREADS) d4[i] = __ldg(src + i);
+        for (int i = tid; i < a.entries / 4; i += nthreads) d4[i] = __ldg(src + i);
         __syncthreads();
     }
+    return dst;
+}
+
+// The block scale of a thread-unit whose C chunks are in xb: the maximum over the block's GT lanes, then the
+// E5M3 scale (round-half-up of the 3-bit mantissa).  Returns the scale's fp16 pattern.
+template <int C>
+__device__ __forceinline__ uint32_t unit_scale(const uint32_t (*xb)[4], int Gt, float inv_ele_max)
+{
+    uint32_t mx = 0u;
+    #pragma unroll
+    for (int k = 0; k < C; ++k)
+        #pragma unroll
+        for (int p = 0; p < 4; ++p) mx = h2_bits(__hmax2(bits_h2(mx), __habs2(bits_h2(xb[k][p]))));
+    for (int off = Gt >> 1; off >= 1; off >>= 1)
+        mx = h2_bits(__hmax2(bits_h2(mx), bits_h2(__shfl_xor_sync(0xFFFFFFFFu, mx, off))));
+    const uint32_t am16 = max(mx & 0xFFFFu, mx >> 16);
+    const float sf = __half2float(bits_h((uint16_t)am16)) * inv_ele_max;
+    uint32_t sb = (uint32_t)h_bits(__float2half_rn(sf));
+    sb = min(max(sb, 0x0400u), 0x7B80u);
+    return (sb + 0x40u) & 0xFF80u;
+}
+
+// GT / ML: lanes per block / per micro-block as compile-time constants (0: read from the arguments).
+template <int MB, int C, int GT, int ML, bool SIDE, bool GLU>
+__global__ void __launch_bounds__(TAB_THREADS, 2) hbq_tab_kernel(const TabArgs a)
+{
+    extern __shared__ __align__(128) uint32_t s_tab[];
+    __shared__ uint4 s_l1c[256];             // per E5M3 scale (pattern >> 7): {2^s1, 2^-(s1+e), -m, fp16(1/m)} as fp16 pairs
+    __shared__ __align__(8) unsigned long long s_bar;
+    __shared__ uint32_t s_nt2[4];            // the candidates, where a run-time index can reach them
+    __shared__ float s_tabf[4];
+    const int tid = threadIdx.x, lane = tid & 31;
+    const uint32_t dst = stage_table(a, s_tab, s_l1c, &s_bar, s_nt2, s_tabf, TAB_THREADS);
 
     const int log2Gt = GT > 0 ? (GT == 1 ? 0 : GT == 2 ? 1 : GT == 4 ? 2 : GT == 8 ? 3 : GT == 16 ? 4 : 5) : a.log2Gt;
     const int Gt = 1 << log2Gt;
@@ -315,8 +365,8 @@ __global__ void __launch_bounds__(TAB_THREADS, 2) hbq_tab_kernel(const TabArgs a
         uint32_t cw[SIDE ? C : 1][4];
         // value * t * l1 overflows fp16 only for blocks whose maximum is within 1 % of fp16's own: one
         // warp-uniform branch between the fused form and the form that keeps each product's rounding
-        if (__all_sync(0xFFFFFFFFu, l1b < a.big_l1)) amin = unit_chunks<MB, C, ML, true, SIDE>(a, dst, s_nt2, xb, l1b, cst, a.m_lanes, bests, cw);
-        else amin = unit_chunks<MB, C, ML, false, SIDE>(a, dst, s_nt2, xb, l1b, cst, a.m_lanes, bests, cw);
+        if (__all_sync(0xFFFFFFFFu, l1b < a.big_l1)) amin = unit_chunks<MB, C, ML, true, SIDE, 0>(a, dst, s_nt2, s_tabf, xb, l1b, cst, a.m_lanes, bests, cw);
+        else amin = unit_chunks<MB, C, ML, false, SIDE, 0>(a, dst, s_nt2, s_tabf, xb, l1b, cst, a.m_lanes, bests, cw);
 
         // The reference returns +0 (not -0) when fp16(a / t) is exactly zero.  Only quotients a below 2^-19
         // can do that; deciding it needs the exact a, where the scaled division may be off: rare, so the
@@ -412,6 +462,233 @@ __global__ void __launch_bounds__(TAB_THREADS, 2) hbq_tab_kernel(const TabArgs a
     }
 }
 
+
+// ---- row kernels: a per-row prologue fused in front of the quantizer --------------------------------
+// Two activation quantizers of the attention / MLP blocks consume a tensor that only exists to be quantised
+// and whose producer needs a whole-row reduction first:
+//   RMSNORM  the input of q/k/v_proj and gate/up_proj: aq(weight * rmsnorm(x [+ residual])) (the decoder
+//            layer's input_layernorm / post_attention_layernorm followed by _QBaseLinear.forward's
+//            self.aq(x), src/module.py:45); the sum x + residual is also written (the new residual stream);
+//   SOFTMAX  the attention probabilities: attn_wgt_quantizer.q(softmax(q k^T * scale + bias)) along the key
+//            axis (manual_sdpa, src/module.py:108-115).
+// One warp owns a row.  It sweeps the row for the reduction (sum of squares; maximum, then sum of exponentials),
+// then sweeps it again (from L1 / L2) to form the fp16 values with the reference's per-op roundings and hands
+// each 128-element block straight to the table quantizer above -- the normalised tensor / the probabilities
+// never go to HBM unquantised.  Geometry: blocks of 128, four lanes per block, four chunks per lane.
+enum { ROW_RMSNORM = 0, ROW_SOFTMAX = 1 };
+constexpr int ROW_THREADS = 512;
+constexpr int ROW_WARPS = ROW_THREADS / 32;
+
+struct RowArgs {
+    TabArgs t;                // the quantizer's format (table, candidates); t.x / t.deq unused
+    const uint4* in;          // [rows, K] fp16: x (RMSNORM) or the raw scores q k^T (SOFTMAX)
+    uint4* out;               // [rows, K] fp16
+    int64_t rows;
+    int K, nblk;              // row length, 128-element blocks per row
+    // RMSNORM
+    const uint4* res;         // residual to add first, or NULL
+    uint4* x_out;             // where x + residual goes (required with res)
+    const uint4* w;           // weight [K] fp16
+    float eps;
+    // SOFTMAX
+    float scale;              // the score scale (a Python float in the reference: applied in fp32)
+    int causal;               // key j of query row r is masked when j > (r % L) + key_offset
+    int64_t L, HL, key_offset;
+    const uint4* mask;        // additive fp16 mask [mask_batches, L, K] or NULL (row r uses batch r / HL, query r % L)
+    int64_t mask_batches;
+};
+static_assert(sizeof(RowArgs) <= 4000, "kernel parameters are limited to 4 KB");
+
+__device__ __forceinline__ float warp_sum(float v)
+{
+    #pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v)
+{
+    #pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, off));
+    return v;
+}
+
+// The pre-softmax score chunk as the reference's fp16 ops leave it: fp16(fp16(s * scale) + bias), bias = the
+// additive mask and / or -inf beyond the causal limit.  cir: chunk index in the row.
+__device__ __forceinline__ void score_chunk(const RowArgs& a, const uint4* rin, const uint4* rmask, int cir, int64_t limit,
+                                            uint32_t* sv)
+{
+    const uint4 raw = __ldg(rin + cir);
+    const uint32_t r[4] = {raw.x, raw.y, raw.z, raw.w};
+    uint32_t m[4] = {0u, 0u, 0u, 0u};
+    if (rmask) { const uint4 mv = __ldg(rmask + cir); m[0] = mv.x; m[1] = mv.y; m[2] = mv.z; m[3] = mv.w; }
+    #pragma unroll
+    for (int p = 0; p < 4; ++p) {
+        // tensor * Python scalar: torch multiplies in fp32 with the scalar as fp32 and rounds the product to fp16
+        const float2 sf = __half22float2(bits_h2(r[p]));
+        __half2 v = __floats2half2_rn(sf.x * a.scale, sf.y * a.scale);
+        if (rmask) v = __hadd2(v, bits_h2(m[p]));
+        uint32_t b = h2_bits(v);
+        const int64_t j0 = (int64_t)cir * 8 + 2 * p;
+        if (j0 > limit) b = (b & 0xFFFF0000u) | 0x0000FC00u;
+        if (j0 + 1 > limit) b = (b & 0x0000FFFFu) | 0xFC000000u;
+        sv[p] = b;
+    }
+}
+
+template <int MB, int ML, int PRO, bool QUANT>
+__global__ void __launch_bounds__(ROW_THREADS, 2) hbq_row_kernel(const RowArgs a)
+{
+    extern __shared__ __align__(128) uint32_t s_tab[];
+    __shared__ uint4 s_l1c[256];
+    __shared__ __align__(8) unsigned long long s_bar;
+    __shared__ uint32_t s_nt2[4];
+    __shared__ float s_tabf[4];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    uint32_t dst = 0u;
+    if (QUANT) dst = stage_table(a.t, s_tab, s_l1c, &s_bar, s_nt2, s_tabf, ROW_THREADS);
+    const int bl = lane >> 2, g = lane & 3;                  // block of the iteration, lane of the block
+    const int cpr = a.K >> 3;                                // chunks per row
+    const int iters_all = (a.nblk + 7) >> 3;                 // 8 blocks (1024 elements) per warp iteration
+
+    #pragma unroll 1
+    for (int64_t row = (int64_t)blockIdx.x * ROW_WARPS + warp; row < a.rows; row += (int64_t)gridDim.x * ROW_WARPS) {
+        const uint4* rin = a.in + row * cpr;
+        uint4* rout = a.out + row * cpr;
+        float stat0 = 0.f, stat1 = 0.f;                      // RMSNORM: rstd; SOFTMAX: max, sum
+        int iters = iters_all;
+        int64_t limit = (int64_t)a.K;                        // SOFTMAX: last unmasked key
+        const uint4* rmask = nullptr;
+        const uint4* rsrc = rin;                             // what the second sweep reads
+
+        if (PRO == ROW_RMSNORM) {
+            float ss = 0.f;
+            uint4* rx = a.x_out ? a.x_out + row * cpr : nullptr;
+            const uint4* rres = a.res ? a.res + row * cpr : nullptr;
+            if (rres) rsrc = rx;
+            for (int it = 0; it < iters; ++it) {
+                const int blk = it * 8 + bl;
+                if (blk < a.nblk) {
+                    #pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const int ci = blk * 16 + g + 4 * k;
+                        if (ci >= cpr) continue;                 // ragged last block (unquantised form only)
+                        uint4 v = __ldg(rin + ci);
+                        if (rres) {
+                            const uint4 rv = __ldg(rres + ci);
+                            v.x = h2_bits(__hadd2(bits_h2(v.x), bits_h2(rv.x))); v.y = h2_bits(__hadd2(bits_h2(v.y), bits_h2(rv.y)));
+                            v.z = h2_bits(__hadd2(bits_h2(v.z), bits_h2(rv.z))); v.w = h2_bits(__hadd2(bits_h2(v.w), bits_h2(rv.w)));
+                            rx[ci] = v;
+                        }
+                        const uint32_t q[4] = {v.x, v.y, v.z, v.w};
+                        #pragma unroll
+                        for (int p = 0; p < 4; ++p) {
+                            const float2 f = __half22float2(bits_h2(q[p]));
+                            ss = fmaf(f.x, f.x, ss); ss = fmaf(f.y, f.y, ss);
+                        }
+                    }
+                }
+            }
+            ss = warp_sum(ss);
+            stat0 = rsqrtf(ss / (float)a.K + a.eps);
+        } else {
+            const int64_t qpos = row % a.L;
+            if (a.causal) limit = qpos + a.key_offset;
+            if (limit > (int64_t)a.K - 1) limit = (int64_t)a.K - 1;
+            if (a.mask) rmask = a.mask + ((a.mask_batches > 1 ? row / a.HL : 0) * a.L + qpos) * cpr;
+            // whole iterations beyond the causal limit hold only masked keys: probabilities 0 (warp-uniform skip)
+            iters = min(iters_all, (int)(limit / 1024) + 1);
+            float mx = -INFINITY;
+            for (int it = 0; it < iters; ++it) {
+                const int blk = it * 8 + bl;
+                if (blk < a.nblk) {
+                    #pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        uint32_t sv[4];
+                        if (blk * 16 + g + 4 * k >= cpr) continue;
+                        score_chunk(a, rin, rmask, blk * 16 + g + 4 * k, limit, sv);
+                        const __half2 m2 = __hmax2(__hmax2(bits_h2(sv[0]), bits_h2(sv[1])), __hmax2(bits_h2(sv[2]), bits_h2(sv[3])));
+                        mx = fmaxf(mx, fmaxf(__low2float(m2), __high2float(m2)));
+                    }
+                }
+            }
+            mx = warp_max(mx);
+            float sum = 0.f;
+            for (int it = 0; it < iters; ++it) {
+                const int blk = it * 8 + bl;
+                if (blk < a.nblk) {
+                    #pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        uint32_t sv[4];
+                        if (blk * 16 + g + 4 * k >= cpr) continue;
+                        score_chunk(a, rin, rmask, blk * 16 + g + 4 * k, limit, sv);
+                        #pragma unroll
+                        for (int p = 0; p < 4; ++p) {
+                            const float2 f = __half22float2(bits_h2(sv[p]));
+                            sum += expf(f.x - mx); sum += expf(f.y - mx);
+                        }
+                    }
+                }
+            }
+            stat0 = mx;
+            stat1 = warp_sum(sum);
+        }
+
+        // ---- second sweep: the fp16 values, block by block into the quantizer ----
+        for (int it = 0; it < iters_all; ++it) {
+            const int blk = it * 8 + bl;
+            const bool valid = blk < a.nblk;
+            if (PRO == ROW_SOFTMAX && it >= iters) {         // only masked keys: zeros (warp-uniform branch)
+                if (valid) {
+                    #pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        if (blk * 16 + g + 4 * k < cpr) rout[blk * 16 + g + 4 * k] = make_uint4(0u, 0u, 0u, 0u);
+                }
+                continue;
+            }
+            uint32_t xb[4][4];
+            #pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int ci = blk * 16 + g + 4 * k;
+                #pragma unroll
+                for (int p = 0; p < 4; ++p) xb[k][p] = 0u;
+                if (!valid || ci >= cpr) continue;
+                if (PRO == ROW_RMSNORM) {
+                    // weight * fp16(x_f32 * rstd): the rounding points of transformers' LlamaRMSNorm on an fp16 tensor
+                    const uint4 v = a.res ? rsrc[ci] : __ldg(rsrc + ci), wv = __ldg(a.w + ci);
+                    const uint32_t q[4] = {v.x, v.y, v.z, v.w}, ww[4] = {wv.x, wv.y, wv.z, wv.w};
+                    #pragma unroll
+                    for (int p = 0; p < 4; ++p) {
+                        const float2 f = __half22float2(bits_h2(q[p]));
+                        xb[k][p] = h2_bits(__hmul2(bits_h2(ww[p]), __floats2half2_rn(f.x * stat0, f.y * stat0)));
+                    }
+                } else {
+                    uint32_t sv[4];
+                    score_chunk(a, rin, rmask, ci, limit, sv);
+                    #pragma unroll
+                    for (int p = 0; p < 4; ++p) {
+                        const float2 f = __half22float2(bits_h2(sv[p]));
+                        xb[k][p] = h2_bits(__floats2half2_rn(__fdiv_rn(expf(f.x - stat0), stat1), __fdiv_rn(expf(f.y - stat0), stat1)));
+                    }
+                }
+            }
+            if (QUANT) {
+                const uint32_t l1b = unit_scale<4>(xb, 4, a.t.inv_ele_max);
+                const uint4 cst = s_l1c[l1b >> 7];
+                uint32_t bests;
+                uint32_t cw[1][4];
+                constexpr int TINY = PRO == ROW_SOFTMAX ? 2 : 1;
+                if (__all_sync(0xFFFFFFFFu, l1b < a.t.big_l1)) unit_chunks<MB, 4, ML, true, false, TINY>(a.t, dst, s_nt2, s_tabf, xb, l1b, cst, ML, bests, cw);
+                else unit_chunks<MB, 4, ML, false, false, TINY>(a.t, dst, s_nt2, s_tabf, xb, l1b, cst, ML, bests, cw);
+            }
+            if (valid) {
+                #pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    if (blk * 16 + g + 4 * k < cpr) rout[blk * 16 + g + 4 * k] = make_uint4(xb[k][0], xb[k][1], xb[k][2], xb[k][3]);
+            }
+        }
+    }
+}
+
 // ---- host side ------------------------------------------------------------------------------------
 static std::mutex g_tab_mutex;
 static uint32_t* g_tab_dev[kMaxDevices];                 // device address of g_tab_slots, per device
@@ -477,6 +754,120 @@ static int launch_tab_geometry(const TabArgs& a, int C, int Gt, int m, bool side
     if (C == 4 && Gt == 4 && m == 4) return launch_tab_variant<MB, 4, 4, 4>(a, side, glu, smem, stream);
     if (C == 4) return launch_tab_variant<MB, 4, 0, 0>(a, side, glu, smem, stream);
     return launch_tab_variant<MB, 2, 0, 0>(a, side, glu, smem, stream);
+}
+
+// Fill the format part of the arguments shared by every kernel of this file (table on the device, candidates,
+// scale constants).  *ok = false when the format has no byte table or its table cannot be uploaded now.
+static int fill_format(const QArgs& q, int mb, cudaStream_t stream, TabArgs* a, bool* ok)
+{
+    *ok = false;
+    TabTable t;
+    if (!hbq_tab_table(mb, q.tab[0], q.nc, &t) || t.slot >= TAB_SLOTS || t.entries > TAB_MAX_ENTRIES) return HBQ_OK;
+    memset(a, 0, sizeof(*a));
+    { const int rc = table_on_device(t, stream, &a->table); if (rc) return rc; }
+    if (!a->table) return HBQ_OK;
+    a->entries = t.entries;
+    a->entry_bytes = 4u;
+    a->base2 = (uint32_t)t.base * 0x00010001u;
+    a->hi2 = (uint32_t)t.hi * 0x00010001u;
+    a->big_l1 = t.big_l1;
+    a->inv_ele_max = 1.f / q.ele_max[0];
+    for (int i = 0; i < 4; ++i) {
+        const float tv = q.tab[0][i < q.nc ? i : q.nc - 1];     // unused slots repeat the last candidate: they never win a tie
+        a->tabf[i] = tv;
+        a->nt2[i] = (uint32_t)__half_as_ushort(__float2half_rn(-tv)) * 0x00010001u;
+    }
+    memcpy(a->rm, t.rm, sizeof(a->rm));
+    *ok = true;
+    return HBQ_OK;
+}
+
+template <int MB, int ML, int PRO>
+static int launch_row(const RowArgs& a, bool quant, cudaStream_t stream)
+{
+    int sms = 0;
+    { const int rc = device_sms(&sms); if (rc) return rc; }
+    const size_t smem = quant ? (size_t)a.t.entries * 4 : 0;
+    const int64_t need = (a.rows + ROW_WARPS - 1) / ROW_WARPS;
+    const int grid = (int)(need < 2ll * sms ? need : 2ll * sms);
+    if (quant) {
+        { const int rc = ensure_dynamic_smem(hbq_row_kernel<MB, ML, PRO, true>, smem); if (rc) return rc; }
+        hbq_row_kernel<MB, ML, PRO, true><<<grid, ROW_THREADS, smem, stream>>>(a);
+    } else {
+        hbq_row_kernel<MB, ML, PRO, false><<<grid, ROW_THREADS, 0, stream>>>(a);
+    }
+    HBQ_LAUNCH_CHECK("hbq_row_kernel");
+    return HBQ_OK;
+}
+
+// q: the validated HBQ format (QArgs as quantize_launch builds it), or NULL for the prologue alone.  Returns
+// HBQ_ERR_UNSUPPORTED when the format does not fit the fused kernel (the caller then runs the prologue alone
+// and the plain quantizer).
+int hbq_row_launch(int pro, const QArgs* q, int mb, RowArgs& a, cudaStream_t stream)
+{
+    if (a.rows == 0 || a.K == 0) return HBQ_OK;
+    if ((a.K % 8) != 0) return HBQ_ERR_UNSUPPORTED;
+    a.nblk = (a.K + 127) / 128;
+    bool quant = false;
+    int ml = 1;
+    if (q) {
+        const int L = q->f.l2_block_size;
+        if (mb < 1 || mb > 2 || q->nscheme != 1 || q->nc > 4 || !q->scale_fast_e5m3 || q->f.block_size != 128 ||
+            (L != 8 && L != 32) || (a.K % 128) != 0)
+            return HBQ_ERR_UNSUPPORTED;
+        bool ok = false;
+        { const int rc = fill_format(*q, mb, stream, &a.t, &ok); if (rc) return rc; }
+        if (!ok) return HBQ_ERR_UNSUPPORTED;
+        quant = true;
+        ml = L / 8;
+    }
+    #define HBQ_ROW(MBV, MLV)                                                                              \
+        return pro == ROW_RMSNORM ? launch_row<MBV, MLV, ROW_RMSNORM>(a, quant, stream)                   \
+                                  : launch_row<MBV, MLV, ROW_SOFTMAX>(a, quant, stream);
+    if (mb == 1) { if (ml == 4) { HBQ_ROW(1, 4) } else { HBQ_ROW(1, 1) } }
+    if (ml == 4) { HBQ_ROW(2, 4) } else { HBQ_ROW(2, 1) }
+    #undef HBQ_ROW
+}
+
+int hbq_format_qargs(const hbq_format* f, QArgs* a, int* mb);      // quantize.cu
+
+int rmsnorm_quantize_launch(const void* x, const void* residual, const void* weight, float eps, int64_t rows, int64_t K,
+                            const hbq_format* fmt, void* x_out, void* out, cudaStream_t stream)
+{
+    if (rows < 0 || K < 0) return HBQ_ERR_ARG;
+    if (rows == 0 || K == 0) return HBQ_OK;
+    if (!x || !weight || !out || (residual && !x_out) || K > (1 << 24)) return HBQ_ERR_ARG;
+    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(residual) | reinterpret_cast<uintptr_t>(weight) |
+         reinterpret_cast<uintptr_t>(x_out) | reinterpret_cast<uintptr_t>(out)) & 15)
+        return HBQ_ERR_ALIGN;
+    RowArgs a;
+    memset(&a, 0, sizeof(a));
+    a.in = (const uint4*)x; a.out = (uint4*)out; a.rows = rows; a.K = (int)K;
+    a.res = (const uint4*)residual; a.x_out = residual ? (uint4*)x_out : nullptr; a.w = (const uint4*)weight; a.eps = eps;
+    QArgs q;
+    int mb = 0;
+    if (fmt) { const int rc = hbq_format_qargs(fmt, &q, &mb); if (rc) return rc; }
+    return hbq_row_launch(ROW_RMSNORM, fmt ? &q : nullptr, mb ? mb : 2, a, stream);
+}
+
+int softmax_quantize_launch(const void* scores, int64_t rows, int64_t S, int64_t L, int64_t heads, float scale, int causal,
+                            const void* mask, int64_t mask_batches, const hbq_format* fmt, void* out, cudaStream_t stream)
+{
+    if (rows < 0 || S < 0 || L <= 0 || heads <= 0) return HBQ_ERR_ARG;
+    if (rows == 0 || S == 0) return HBQ_OK;
+    if (!scores || !out || S > (1 << 24) || (mask && mask_batches < 1)) return HBQ_ERR_ARG;
+    if ((reinterpret_cast<uintptr_t>(scores) | reinterpret_cast<uintptr_t>(mask) | reinterpret_cast<uintptr_t>(out)) & 15)
+        return HBQ_ERR_ALIGN;
+    RowArgs a;
+    memset(&a, 0, sizeof(a));
+    a.in = (const uint4*)scores; a.out = (uint4*)out; a.rows = rows; a.K = (int)S;
+    a.scale = scale;
+    a.causal = causal; a.L = L; a.HL = heads * L; a.key_offset = S - L;
+    a.mask = (const uint4*)mask; a.mask_batches = mask_batches;
+    QArgs q;
+    int mb = 0;
+    if (fmt) { const int rc = hbq_format_qargs(fmt, &q, &mb); if (rc) return rc; }
+    return hbq_row_launch(ROW_SOFTMAX, fmt ? &q : nullptr, mb ? mb : 2, a, stream);
 }
 
 int hbq_tab_try_launch(const QArgs& q, int mb, cudaStream_t stream, bool* launched)

@@ -142,6 +142,31 @@ int hbq_kv_write_v(const void* v, int dtype, int64_t B, int64_t T, int64_t H, in
 int hbq_swiglu_quantize(const void* gate, const void* up, int64_t rows, int64_t K,
                         const hbq_format* fmt, void* out, void* stream);
 
+/* Normalisation fused into the quantizer of the q/k/v and gate/up projections' input: what the patched decoder
+ * layer runs as hidden = hidden + residual_branch, LlamaRMSNorm(hidden) (transformers; weight * fp16(x_f32 *
+ * rsqrt(mean(x_f32^2) + eps))) and then _QBaseLinear.forward's self.aq(x) (src/module.py:45), in one kernel: a
+ * warp owns a row, sweeps it once for the sum of squares (writing x + residual to x_out when `residual` is
+ * given; x_out may be x itself) and once more to normalise and hand each 128-element block to the table
+ * quantizer -- the normalised tensor never goes to memory unquantised.  x, residual, x_out, out: fp16 [rows, K],
+ * weight fp16 [K], all 16-byte aligned, K a multiple of 8.  fmt = NULL writes the normalised tensor itself (the
+ * model's final norm).  Served formats: HBQ with one candidate table, E2M1 / E2M2, block 128, micro-block 8 or
+ * 32, K a multiple of 128; HBQ_ERR_UNSUPPORTED otherwise (callers then pass NULL and run hbq_quantize). */
+int hbq_rmsnorm_quantize(const void* x, const void* residual, const void* weight, float eps, int64_t rows,
+                         int64_t K, const hbq_format* fmt, void* x_out, void* out, void* stream);
+
+/* Attention probabilities with their quantizer: manual_sdpa's attn_weight = softmax(q k^T * scale + bias) and
+ * attn_wgt_quantizer.q(attn_weight) (src/module.py:108-115) from the raw scores q k^T (fp16 [rows, S], rows =
+ * batch * heads * L query rows) in one kernel.  Rounding points are the reference's: fp16(score * scale) with the product taken in fp32 (a tensor times a Python float),
+ * fp16(+ bias), softmax evaluated in fp32 (maximum, exp(x - max), sum, division) and rounded to fp16, then the
+ * quantizer along the key axis.  causal != 0 masks key j of query row r when j > (r % L) + (S - L) (is_causal of
+ * manual_sdpa; with a key/value cache the new queries are the last L positions); `mask` is an optional additive
+ * fp16 mask [mask_batches, L, S] (mask_batches = 1 or batch; `heads` = query rows per batch / L).  Runs of 1024
+ * keys that are masked for a row are written as zeros without being evaluated.  out may be scores itself.
+ * fmt = NULL writes the probabilities unquantised.  Served formats as hbq_rmsnorm_quantize, S a multiple of 128. */
+int hbq_softmax_quantize(const void* scores, int64_t rows, int64_t S, int64_t L, int64_t heads, float scale,
+                         int causal, const void* mask, int64_t mask_batches, const hbq_format* fmt, void* out,
+                         void* stream);
+
 
 /* ---- GEMM with modelled accumulation --------------------------------------------------- */
 
