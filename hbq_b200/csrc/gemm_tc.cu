@@ -670,7 +670,8 @@ int gemm_tc_launch_ex(const void* A, const void* W, void* C, int64_t M, int64_t 
     { const int rc2 = device_sms(&sms); if (rc2) return rc2; }
     args.tiles_m = (int)((M + BM - 1) / BM);
     // 128-column tiles when 256-column ones would leave more than half of the SMs without work
-    args.bn = ((int64_t)args.tiles_m * ((N + 255) / 256) * 2 <= sms) ? 128 : 256;
+    // ... or when the whole problem is at most 128 columns wide (a 256-column tile would be half empty)
+    args.bn = (N <= 128 || (int64_t)args.tiles_m * ((N + 255) / 256) * 2 <= sms) ? 128 : 256;
     args.tiles_n = (int)((N + args.bn - 1) / args.bn);
     rc = make_map(&mb, W, N, K, args.bn);
     if (rc) return rc;
