@@ -35,14 +35,14 @@ sys.path.insert(0, ROOT)
 
 M, K, N = 4096, 4096, 14336
 GROUP_K, GROUP_N = 128, 32
+WARM_SECONDS = 0.8         # continuous load before the timed interval
+TIMED_SECONDS = 1.5        # least duration of the timed interval (blocks of --steps steps, back to back)
 WORKLOAD = ("configs[1]: HBQ-E linear, X[4096,4096] (0.5% outlier channels x30) * W[14336,4096]^T, "
             "act E2M2 / wgt E2M1, block 128, micro-block 32, accumulation fp16_quant(group 128, block 32)")
 ACT = dict(block_size=128, ebit=2, mbit=2, sc_ebit=5, sc_mbit=3, l2_block_size=32, l2_sc_bit=2, l2_scheme="SIG-1")
 WGT = dict(block_size=128, ebit=2, mbit=1, sc_ebit=5, sc_mbit=3, l2_block_size=32, l2_sc_bit=2, l2_scheme="Mix")
 # algorithmic HBM bytes per element of the activation quantize: 2 in + 2 fake-quantised out
 QUANT_BYTES_PER_ELEM = 4.0
-# DRAM bytes of one GEMM launch at this shape, from the ncu capture summarised under profiles/
-GEMM_DRAM_TRAFFIC_BYTES = 257617920
 
 
 def make_inputs(rank: int):
@@ -85,16 +85,13 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
 
-    def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.25)
-        self.proc.terminate()
+    @staticmethod
+    def _stats(rows):
         sm, smax, power, reasons = [], [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
+        for _, r in rows:
             try:
                 sm.append(float(r[0])); smax.append(float(r[1]))
             except (ValueError, IndexError):
@@ -108,6 +105,20 @@ class ClockSampler:
                     reasons.add(n)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
                 "samples": len(sm), "power_w_max": max(power) if power else None, "reasons": sorted(reasons)}
+
+    def window(self, t0: float, t1: float):
+        """Statistics of the samples taken inside [t0, t1] (host wall clock)."""
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        return self._stats([r for r in list(self.rows) if t0 <= r[0] <= t1])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        return self._stats(list(self.rows))
 
 
 def cpu_baseline_sample(x_bf16, wq_f16, seconds_target: float = 15.0):
@@ -200,53 +211,75 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     lin.aq = aq
     lin.ops = H.FP16AccumMatMul(group_size=GROUP_K, quant_block_size=GROUP_N)
     x = x_host.to(dev)
+    wq_host = lin.weight.data.cpu() if (rank == 0 and world == 1 and not args.no_cpu_baseline) else None
     torch.cuda.synchronize()
 
     def step():
         return lin(x)
 
+    # clocks are sampled from the warm-up on: the timed interval below lasts >= TIMED_SECONDS
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    t_warm = time.perf_counter()
     for _ in range(max(args.warmup, 3)):
         y = step()
+    torch.cuda.synchronize()
+    while time.perf_counter() - t_warm < WARM_SECONDS:       # bring clocks and power to their sustained state
+        for _ in range(args.steps):
+            y = step()
+        torch.cuda.synchronize()
     barrier()
     if H.gemm_status() != 0:
         raise RuntimeError("tensor-core GEMM reported an expired wait")
 
-    # ---- timed region: K steps, device time, max over ranks ----
-    # (clocks are sampled from here to the end of the end-to-end loop: the timed region alone is ~10 ms)
-    sampler = ClockSampler(local_rank)
-    sampler.start()
-    time.sleep(0.3)
-    l0 = H.launch_count()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    ev0.record()
+    # ---- timed region: blocks of exactly K steps, back to back for >= TIMED_SECONDS; the reported step time is
+    #      the MEDIAN block (device time between events, max over ranks per block) ----
+    one = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    one[0].record()
     for _ in range(args.steps):
         y = step()
-    ev1.record()
-    barrier()
-    total_ms = ev0.elapsed_time(ev1)
-    launches = H.launch_count() - l0
+    one[1].record()
+    torch.cuda.synchronize()
+    est_ms = max(one[0].elapsed_time(one[1]), 1e-3)
+    nblocks = int(min(2000, max(5, TIMED_SECONDS * 1e3 / est_ms)))
     if world > 1:
-        t = torch.tensor([total_ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        total_ms = float(t.item())
+        nb = torch.tensor([nblocks], device=dev)
+        dist.all_reduce(nb, op=dist.ReduceOp.MAX)
+        nblocks = int(nb.item())
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(nblocks + 1)]
+    l0 = H.launch_count()
+    barrier()
+    t_timed0 = time.time()
+    evs[0].record()
+    for b in range(nblocks):
+        for _ in range(args.steps):
+            y = step()
+        evs[b + 1].record()
+    barrier()
+    t_timed1 = time.time()
+    launches = (H.launch_count() - l0) // nblocks
+    block_ms = torch.tensor([evs[b].elapsed_time(evs[b + 1]) for b in range(nblocks)], device=dev)
+    if world > 1:
+        dist.all_reduce(block_ms, op=dist.ReduceOp.MAX)
+    total_ms = float(block_ms.median().item())
     ms_step = total_ms / args.steps
     flops_step = 2.0 * M * N * K
     value = flops_step * world / (ms_step * 1e-3) / 1e12
+    clocks_timed = sampler.window(t_timed0, t_timed1)
 
-    # ---- per-kernel device times (events on the launching stream, same steady state) ----
-    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
-           for _ in range(args.steps)]
+    # ---- per-kernel device times (events on the launching stream, same sustained state) ----
+    kev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+           for _ in range(max(args.steps, 50))]
     barrier()
-    for a, b, c in evs:
+    for a, b, c in kev:
         a.record()
         xq_i = aq.q(x)
         b.record()
         lin.ops(xq_i, lin.weight)
         c.record()
     torch.cuda.synchronize()
-    q_ms = statistics.mean(a.elapsed_time(b) for a, b, c in evs)
-    g_ms = statistics.mean(b.elapsed_time(c) for a, b, c in evs)
+    q_ms = statistics.median(a.elapsed_time(b) for a, b, c in kev)
+    g_ms = statistics.median(b.elapsed_time(c) for a, b, c in kev)
     peaks = measured_peaks()
     g_tf = flops_step / (g_ms * 1e-3) / 1e12
     q_gbs = M * K * QUANT_BYTES_PER_ELEM / (q_ms * 1e-3) / 1e9
@@ -282,34 +315,142 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     if H.gemm_status() != 0:
         raise RuntimeError("tensor-core GEMM reported an expired wait")
 
+    # ---- the metric's second leg: HBQ-A activation quantize of configs[2]'s tensor (rank 0) ----
+    act_quant = act_quant_record(dev, peaks) if rank == 0 else None
+    # ---- the reference's own CUDA-core kernel on the same GPU and shape (rank 0, outside every timed region) ----
+    ref_gpu = reference_gemm_record(lin.aq.q(x), lin.weight.data) if (rank == 0 and world == 1) else None
+    torch.cuda.empty_cache()
+
+    # ---- whole-model and collective sub-records ----
+    sub = {}
+    if not args.no_model:
+        one = llama_prefill_record(rank, world, dev, 2, 1, 1, layers=args.llama_layers, parallel=False)
+        sub["llama_prefill"] = {"one_gpu": one}
+        if world > 1:
+            tp = llama_prefill_record(rank, world, dev, 2, 1, args.llama_pieces, layers=args.llama_layers)
+            sub["llama_prefill"]["tensor_parallel"] = tp
+            sub["llama_prefill"]["speedup_over_one_gpu"] = one["ms_per_forward"] / tp["ms_per_forward"]
+            sa = argparse.Namespace(**vars(args))
+            sa.steps, sa.warmup = 5, 3
+            sub["tp_mlp"] = run_tp_mlp(sa, rank, world, local_rank, standalone=False)
+            sub["ep_moe"] = run_ep_moe(sa, rank, world, local_rank, standalone=False)
+
     if rank == 0:
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
-            cpu = cpu_baseline_sample(x_host, lin.weight.data.cpu())
+            cpu = cpu_baseline_sample(x_host, wq_host)
+        traffic, traffic_src = profile_traffic("gemm_tc_kernel_int8psum_M4096_K4096_N14336.md")
         line = {
             "metric": "quant_gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {"workload": WORKLOAD, "global_rows": M * world, "parallelism": f"row-sharded x{world}, no collective",
                        "l2": "no flush: per-step working set 266 MB (X 32 + Xq 32 + W 117 + Y 117) exceeds the 126 MB L2",
+                       "timed_interval": f"{nblocks} blocks of {args.steps} steps back to back after {WARM_SECONDS} s of the same "
+                                         f"load; ms_per_step = median block / {args.steps}",
                        "host_binding": binding},
-            "clocks": clocks,
+            "clocks": clocks_timed, "clocks_whole_run": clocks,
+            "mhz_ms_per_step": (clocks_timed["sm_mhz"] or 0) * ms_step,
             "e2e": {"value": e2e_val, "unit": "TFLOP/s", "h2d_bytes_per_step": M * K * 2, "d2h_bytes_per_step": M * N * 2},
-            "gpu_launches": int(launches),
+            "gpu_launches": int(launches) * nblocks, "gpu_launches_per_block": int(launches), "blocks": nblocks,
+            # the kernel is timed inside a seconds-long load: its denominator is the SUSTAINED measured peak
             "roofline": {"bound": "tensor", "kernel": "gemm_tc_kernel<PSUM_INT8,32>", "achieved": g_tf,
                          "peak": peaks["tf_sustained"], "unit": "TFLOP/s", "frac": g_tf / peaks["tf_sustained"],
+                         "peak_kind": "sustained (kernel timed inside a >= 2 s load)",
                          "peak_burst": peaks["tf_burst"], "frac_of_burst": g_tf / peaks["tf_burst"],
-                         "peak_source": peaks["source"], "ms_per_launch": g_ms, "traffic": GEMM_DRAM_TRAFFIC_BYTES,
-                         "traffic_source": "ncu dram__bytes_read+write of one full-size launch, profiles/gemm_tc_kernel_int8psum_M4096_K4096_N14336.md"},
-            "quantize": {"kernel": "hbq_lut_lean_kernel<2> (HBQ-E act, bf16 in, fp16 fake-quant out)", "bound": "hbm",
+                         "peak_source": peaks["source"], "ms_per_launch": g_ms, "traffic": traffic, "traffic_source": traffic_src},
+            "quantize": {"kernel": "hbq_tab_kernel (HBQ-E act, bf16 in, fp16 fake-quant out)", "bound": "hbm",
                          "achieved": q_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": q_gbs / peaks["hbm_gbs"],
                          "ms_per_launch": q_ms, "bytes_per_elem": QUANT_BYTES_PER_ELEM},
+            "act_quant": act_quant,
         }
+        if ref_gpu is not None:
+            line["ref_gpu"] = ref_gpu
+        line.update(sub)
         if cpu is not None:
             line["cpu_baseline"] = cpu
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def profile_traffic(name: str):
+    """DRAM bytes per launch from the committed ncu summary `profiles/<name>` (its line
+    `traffic_bytes_per_launch = N`), so the number always belongs to the capture that is on file."""
+    import re
+    path = os.path.join(ROOT, "profiles", name)
+    try:
+        with open(path) as fh:
+            m = re.search(r"traffic_bytes_per_launch\s*=\s*(\d+)", fh.read())
+        if m:
+            return int(m.group(1)), f"ncu dram__bytes_read.sum + dram__bytes_write.sum of one full-size launch, profiles/{name}"
+    except OSError:
+        pass
+    return None, "no capture on file"
+
+
+def act_quant_record(dev, peaks, steps: int = 30):
+    """HBQ-A activation quantize of configs[2]'s tensor, [8192, 8192] bf16 ~ 0.5 * Student-t(3) (268 MB in + out: larger
+    than L2).  `as_stated`: bf16 in, packed codes + scales AND the bf16 dequantised tensor out (the configuration's
+    own wording); `fake_quant_only`: fp16 in, fp16 fake-quantised tensor out (what a linear layer's step runs).
+    Algorithmic bytes per element: 2 in + 2 dequantised out (+ 0.6641 codes and scales)."""
+    import torch
+    import hbq_b200 as H
+    torch.manual_seed(2)
+    t = (0.5 * torch.distributions.StudentT(3.0).sample((8192, 8192))).to(dev)
+    q = H.HBQQuantizer(block_size=128, ebit=2, mbit=2, sc_ebit=5, sc_mbit=3, l2_block_size=8, l2_sc_bit=2, l2_scheme="SIG-1")
+    rec = {"workload": "configs[2] hbq_a: activation quantizer of config/hbq_a.yaml on [8192, 8192]", "peak": peaks["hbm_gbs"],
+           "unit": "GB/s", "peak_source": peaks["source"]}
+    for name, x, fn, bpe in (("as_stated", t.to(torch.bfloat16), lambda v: q.quantize_packed(v, with_deq=True), 4.6641),
+                             ("fake_quant_only", t.to(torch.float16), lambda v: q.q(v), 4.0)):
+        for _ in range(5):
+            fn(x)
+        torch.cuda.synchronize()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+        ev[0].record()
+        for i in range(steps):
+            fn(x)
+            ev[i + 1].record()
+        torch.cuda.synchronize()
+        ms = statistics.median(ev[i].elapsed_time(ev[i + 1]) for i in range(steps))
+        gbs = x.numel() * bpe / ms / 1e6
+        rec[name] = {"ms": ms, "achieved": gbs, "frac": gbs / peaks["hbm_gbs"], "bytes_per_elem": bpe}
+    # the headline fraction is the configuration as stated
+    rec["achieved"], rec["frac"] = rec["as_stated"]["achieved"], rec["as_stated"]["frac"]
+    return rec
+
+
+def reference_gemm_record(xq, wq, launches: int = 3):
+    """The reference's own `gemm_blockquant_mxint8` (blockquant_ext_src/gemm.cu compiled for sm_100a into oracle/_ref/,
+    CUDA cores only) on the benchmark's operands, on this GPU: the kernel the tensor-core kernel replaces.  The
+    reference's caller also transposes the weight on every call (src/ops.py:41); that copy is timed separately."""
+    import importlib.util
+    import torch
+    so = os.path.join(ROOT, "oracle", "_ref", "blockquant_ext.so")
+    if not os.path.exists(so):
+        return {"unavailable": "oracle/_ref/blockquant_ext.so has not been built (python oracle/build_ref.py REFERENCE_DIR)"}
+    spec = importlib.util.spec_from_file_location("blockquant_ext", so)
+    ref = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ref)
+    torch.cuda.synchronize()
+    e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    legacy = torch.cuda.default_stream()
+    with torch.cuda.stream(legacy):                  # the reference launches on the legacy default stream
+        wt = wq.t().contiguous()
+        ref.gemm_blockquant_mxint8(xq, wt, GROUP_K, GROUP_N)          # warm-up
+        torch.cuda.synchronize()
+        e[0].record(legacy)
+        for _ in range(launches):
+            wt = wq.t().contiguous()
+        e[1].record(legacy)
+        for _ in range(launches):
+            ref.gemm_blockquant_mxint8(xq, wt, GROUP_K, GROUP_N)
+        e[2].record(legacy)
+    torch.cuda.synchronize()
+    g_ms, t_ms = e[1].elapsed_time(e[2]) / launches, e[0].elapsed_time(e[1]) / launches
+    return {"kernel": "gemm_blockquant_mxint8_core_kernel<128,32> (reference gemm.cu, sm_100a build)", "ms_per_launch": g_ms,
+            "achieved": 2.0 * M * N * K / (g_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "weight_transpose_ms_per_call": t_ms,
+            "launches": launches}
 
 
 # ---- quantize sweep (configs[2]: [8192, 8192] over the six shipped activation formats) and the fused
@@ -373,7 +514,91 @@ def run_sweep(args):
             timed(lambda: kvcache.write_v_cache(k, Hh, q), k.numel(), "v_write (token-axis quantize + layout)", shape)
 
 
-def run_tp_mlp(args, rank: int, world: int, local_rank: int):
+# config/hbq_a_kv.yaml of the reference as PTQ reads it: HBQ-A W4A5 on every linear, 4-bit K/V, post-RoPE Q and
+# attention-probability quantisation, fp32 accumulation
+HBQ_A_KV = {
+    "quantization": {"xqtype": "hbq", "wqtype": "hbq", "quant_attn_wgt": True, "quant_post_rope_q": True, "quant_4b_kv": True,
+                     "quant_k_cache": True, "quant_v_cache": True, "quant_attn_wgt_use_quant_kernel": False},
+    "block_quant": {"act_ebit": 2, "act_mbit": 2, "act_block_size": 128, "act_sc_ebit": 5, "act_sc_mbit": 3,
+                    "act_l2_sc_bit": 2, "act_l2_block_size": 8, "act_l2_scheme": "SIG-1",
+                    "wgt_ebit": 2, "wgt_mbit": 1, "wgt_block_size": 128, "wgt_sc_ebit": 5, "wgt_sc_mbit": 3,
+                    "wgt_l2_sc_bit": 2, "wgt_l2_block_size": 8, "wgt_l2_scheme": "Mix",
+                    "scale_allow_subnormal": False, "qk_mx_round": False},
+    "accumulation": {"type": "fp32"},
+}
+
+
+def llama_prefill_record(rank: int, world: int, dev, steps: int, warmup: int, pieces: int, layers: int = 32,
+                         batch: int = 8, seq: int = 2048, parallel: bool = True):
+    """configs[3]: Llama-3-8B-architecture random-init model, HBQ-A W4A5 + KV quantisation (hbq_a_kv.yaml), prefill of
+    `batch` x `seq` tokens, tensor/sequence-parallel over `world` ranks (strong scaling: the batch is fixed).  Returns
+    the record for the benchmark line (device time per forward, max over ranks)."""
+    import torch
+    import torch.distributed as dist
+    import hbq_b200 as H
+    arch = H.LlamaArch(layers=layers)
+    model = H.QLlamaModel(arch, device=dev, pieces=pieces, parallel=parallel)
+    tp = world if parallel else 1
+    model.init_weights(seed=0)
+    model.apply_ptq(H.PTQConfig(HBQ_A_KV))
+    ids = torch.randint(0, arch.vocab, (batch, seq), generator=torch.Generator().manual_seed(3)).to(dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(1, warmup)):
+        out = model(ids)
+    barrier()
+    l0 = H.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        out = model(ids)
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms /= steps
+    tokens = batch * seq
+    flops = model.flops_per_token() * tokens + model.attention_flops(batch, seq)
+    finite = bool(torch.isfinite(out[:256]).all().item())
+    if H.gemm_status() != 0:
+        raise RuntimeError("tensor-core GEMM reported an expired wait")
+    rec = {"workload": f"configs[3]: Llama-3-8B architecture, {layers} layers, hbq_a_kv.yaml, prefill {batch}x{seq}",
+           "parallelism": f"tp{tp} heads / MLP features over ranks, residual stream by tokens: reduce-scatter + all-gather "
+                          f"per half-layer, batch in {model.pieces} piece(s)" if tp > 1 else "1 GPU (whole model on every rank)",
+           "ms_per_forward": ms, "tokens_per_s": tokens / (ms * 1e-3), "tflops": flops / (ms * 1e-3) / 1e12,
+           "flops_counted": "2*MAC of all linear layers + lm_head + uncausal attention matmuls",
+           "kernel_launches_per_forward": (H.launch_count() - l0) // steps, "finite": finite,
+           "logit_columns_per_rank": arch.vocab // tp}
+    del model, out
+    torch.cuda.empty_cache()
+    return rec
+
+
+def run_llama(args, rank: int, world: int, local_rank: int):
+    """`--llama`: the whole-model prefill of configs[3] over the launched ranks, one JSON line from rank 0."""
+    import torch
+    import torch.distributed as dist
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    rec = llama_prefill_record(rank, world, dev, args.steps, args.warmup, args.llama_pieces, layers=args.llama_layers)
+    if rank == 0:
+        print(json.dumps({"metric": "llama_prefill_tokens_per_s", "value": rec["tokens_per_s"], "unit": "tokens/s", "n_gpus": world,
+                          "steps": args.steps, "warmup": args.warmup, "ms_per_step": rec["ms_per_forward"],
+                          "higher_is_better": True, "scaling": "strong", "dtype": "f16", "data": "synthetic", "config": rec}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_tp_mlp(args, rank: int, world: int, local_rank: int, standalone: bool = True):
     """`--tp-mlp`: the MLP block of configs[3] (Llama-3-8B shapes: hidden 4096, intermediate 14336; 8 x 2048
     tokens) with HBQ-A activation quantizers and fp32 accumulation, tensor-parallel over the ranks: gate / up
     column-parallel, down row-parallel with its all-reduce.  Strong scaling: the token batch is fixed.  One
@@ -384,7 +609,7 @@ def run_tp_mlp(args, rank: int, world: int, local_rank: int):
 
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-    if world > 1:
+    if world > 1 and standalone:
         dist.init_process_group("nccl", device_id=dev)
     hidden, inter, tokens = 4096, 14336, 8 * 2048
     act = dict(block_size=128, ebit=2, mbit=2, sc_ebit=5, sc_mbit=3, l2_block_size=8, l2_sc_bit=2, l2_scheme="SIG-1")
@@ -433,20 +658,25 @@ def run_tp_mlp(args, rank: int, world: int, local_rank: int):
     flops = 3 * 2.0 * tokens * hidden * inter
     if H.gemm_status() != 0:
         raise RuntimeError("tensor-core GEMM reported an expired wait")
+    line = None
     if rank == 0:
-        print(json.dumps({"metric": "tp_mlp_tflops", "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": world,
+        line = ({"metric": "tp_mlp_tflops", "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": world,
                           "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
                           "scaling": "strong", "dtype": "f16", "data": "synthetic",
                           "config": {"workload": "configs[3] MLP block: 16384 tokens, hidden 4096, intermediate 14336, HBQ-A "
                                                  "activations and weights, fp32 accumulation",
                                      "parallelism": f"tp{world}: gate/up column-parallel, down row-parallel, all-reduce of "
                                                     f"[16384,4096] fp16 in {down._pieces(tokens)} piece(s)"},
-                          "finite": bool(torch.isfinite(y).all().item())}))
+                          "finite": bool(torch.isfinite(y).all().item())})
+    if not standalone:
+        return line                  # a sub-record of the benchmark line (rank 0; None elsewhere)
+    if rank == 0:
+        print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
 
 
-def run_ep_moe(args, rank: int, world: int, local_rank: int):
+def run_ep_moe(args, rank: int, world: int, local_rank: int, standalone: bool = True):
     """`--ep-moe`: the sparse MoE block of configs[4] (Mixtral-8x7B shapes: hidden 4096, intermediate 14336,
     8 experts, top-2; 4 x 4096 tokens) with HBQ-E quantizers and fp16 / partial-sum-quantised accumulation,
     experts spread over the ranks, each rank routing its share of the tokens.  Strong scaling: the token batch
@@ -457,7 +687,7 @@ def run_ep_moe(args, rank: int, world: int, local_rank: int):
 
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-    if world > 1:
+    if world > 1 and standalone:
         dist.init_process_group("nccl", device_id=dev)
     hidden, inter, experts, top_k, tokens = 4096, 14336, 8, 2, 4 * 4096
     wq = H.HBQQuantizer(**WGT)
@@ -505,15 +735,20 @@ def run_ep_moe(args, rank: int, world: int, local_rank: int):
     flops = top_k * 3 * 2.0 * tokens * hidden * inter
     if H.gemm_status() != 0:
         raise RuntimeError("tensor-core GEMM reported an expired wait")
+    line = None
     if rank == 0:
-        print(json.dumps({"metric": "ep_moe_tflops", "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": world,
+        line = ({"metric": "ep_moe_tflops", "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": world,
                           "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
                           "scaling": "strong", "dtype": "f16", "data": "synthetic",
                           "config": {"workload": "configs[4] MoE block: 16384 tokens, 8 experts, top-2, hidden 4096, intermediate "
                                                  "14336, HBQ-E activations and weights, accumulation fp16_quant(group 128, block 32)",
                                      "parallelism": f"ep{world}: {moe.per_rank} expert(s) per rank, all-to-all dispatch "
                                                     f"({'packed codes and scales' if moe.packed_dispatch else 'fp16'}) and combine (fp16)"},
-                          "finite": bool(torch.isfinite(y).all().item())}))
+                          "finite": bool(torch.isfinite(y).all().item())})
+    if not standalone:
+        return line                  # a sub-record of the benchmark line (rank 0; None elsewhere)
+    if rank == 0:
+        print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
 
@@ -525,11 +760,19 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-model", action="store_true",
+                    help="leave out the whole-model and collective sub-records (configs[3] prefill; tensor-parallel MLP and "
+                         "expert-parallel MoE blocks at N > 1)")
     ap.add_argument("--sweep", nargs="?", const="all", default=None,
                     help="instead of the benchmark line: quantize sweep of configs[2] and the KV-cache writes "
                          "(all cases, or one: " + ", ".join(SWEEP_FORMATS) + ", k_write, v_write)")
     ap.add_argument("--tp-mlp", action="store_true",
                     help="instead of the benchmark line: the tensor-parallel MLP block of configs[3] over the launched ranks")
+    ap.add_argument("--llama", action="store_true",
+                    help="instead of the benchmark line: the Llama-3-8B-architecture prefill of configs[3] over the launched ranks")
+    ap.add_argument("--llama-layers", type=int, default=32)
+    ap.add_argument("--llama-pieces", type=int, default=2,
+                    help="--llama: pieces of whole sequences the batch is cut into (collectives of one run under the GEMMs of the next)")
     ap.add_argument("--ep-moe", action="store_true",
                     help="instead of the benchmark line: the expert-parallel MoE block of configs[4] over the launched ranks")
     ap.add_argument("--ep-packed-dispatch", action="store_true",
@@ -551,6 +794,9 @@ def main():
     if args.no_fused_act:
         from hbq_b200 import kvcache
         kvcache.FUSE_SWIGLU = False
+    if args.llama:
+        run_llama(args, rank, world, local_rank)
+        return
     if args.tp_mlp:
         run_tp_mlp(args, rank, world, local_rank)
         return

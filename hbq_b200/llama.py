@@ -207,11 +207,13 @@ class QLlamaModel(nn.Module):
     them, for small models).  Weights are drawn N(0, 0.02) per tensor from a seed derived from the tensor's name, in
     full on every rank and then sliced, so every world size holds the same model."""
 
-    def __init__(self, arch: LlamaArch, group=None, device=None, pieces: int = 1):
+    def __init__(self, arch: LlamaArch, group=None, device=None, pieces: int = 1, parallel: bool = True):
+        """``parallel=False`` builds the whole model on this rank even when a process group exists (the one-GPU
+        baseline of a scaling measurement)."""
         super().__init__()
         self.arch = arch
         self.group = group
-        on = dist.is_available() and dist.is_initialized()
+        on = parallel and dist.is_available() and dist.is_initialized()
         self.world = dist.get_world_size(group) if on else 1
         self.rank = dist.get_rank(group) if on else 0
         self.pieces = max(1, int(pieces))
