@@ -6,7 +6,8 @@ experts on one device.  Here the experts are spread over the ranks of a process 
 router is replicated.  Per call:
 
 1. router: softmax over the expert logits in fp32, top-k, weights renormalised to sum to one;
-2. every (token, choice) copy is quantised with the experts' input quantizer *before* it travels --
+2. the ranks learn each other's row counts from one small all-gather (the call's only host read);
+   every (token, choice) copy is quantised with the experts' input quantizer *before* it travels --
    block quantisation is per row, so this gives the same values as quantising at the expert -- and
    sent to the rank that owns its expert (all-to-all with per-rank row counts).  With
    ``packed_dispatch`` the copies travel as packed codes and scales (0.52-0.66 B per element instead
@@ -64,9 +65,10 @@ class ExpertParallelMoE(nn.Module):
     quantizer with a packed form (MXFP / MXINT / HBQ)."""
 
     def __init__(self, hidden: int, inter: int, num_experts: int, top_k: int = 2, group=None, ops_factory=None,
-                 packed_dispatch: bool = False, device=None, dtype=None):
+                 packed_dispatch: bool = False, device=None, dtype=None, local_only: bool = False):
+        """``local_only``: every expert on this rank whatever process group exists."""
         super().__init__()
-        world, rank = _world(group), _rank(group)
+        world, rank = (1, 0) if local_only else (_world(group), _rank(group))
         if num_experts % world:
             raise ValueError(f"{num_experts} experts do not divide over {world} ranks")
         self.group, self.world, self.rank = group, world, rank
@@ -131,22 +133,26 @@ class ExpertParallelMoE(nn.Module):
         per_expert = torch.bincount(flat_e, minlength=self.num_experts)
 
         if self.world == 1:
-            recv_per_expert = per_expert.tolist()
+            recv_per_expert = per_expert.tolist()                      # the call's one host read
             xq = self._dispatch(x2d, src_rows, None, None)
             send_counts = recv_counts = None
         else:
-            # row counts: what every rank sends me for each of my experts (one small all-to-all, then the host reads it)
-            counts_out = torch.empty_like(per_expert)
-            dist.all_to_all_single(counts_out, per_expert, group=self.group)
-            send_counts = per_expert.view(self.world, self.per_rank).sum(dim=1).tolist()
-            got = counts_out.view(self.world, self.per_rank)
-            recv_counts = got.sum(dim=1).tolist()
+            # every rank's copies per expert, in one small all-gather and ONE host read: row r is what rank r sends,
+            # so my row gives the split sizes of what I send and my experts' columns those of what I receive
+            rows = [torch.empty_like(per_expert) for _ in range(self.world)]
+            dist.all_gather(rows, per_expert.contiguous(), group=self.group)
+            tl = torch.stack(rows).tolist()
+            send_counts = [sum(tl[self.rank][d * self.per_rank:(d + 1) * self.per_rank]) for d in range(self.world)]
+            got_l = [tl[s][self.e0:self.e0 + self.per_rank] for s in range(self.world)]
+            recv_counts = [sum(g) for g in got_l]
             xq_by_src = self._dispatch(x2d, src_rows, send_counts, recv_counts)
             # arrived rows are grouped by source rank, then by expert: regroup by expert
-            got_l = got.tolist()
-            pieces = torch.split(xq_by_src, [c for src in got_l for c in src])
-            by_expert = [[pieces[s * self.per_rank + e] for s in range(self.world)] for e in range(self.per_rank)]
-            xq = torch.cat([p for e in by_expert for p in e]) if xq_by_src.shape[0] else xq_by_src
+            if self.per_rank == 1:
+                xq = xq_by_src                                          # one expert here: already in order
+            else:
+                pieces = torch.split(xq_by_src, [c for src in got_l for c in src])
+                by_expert = [[pieces[s * self.per_rank + e] for s in range(self.world)] for e in range(self.per_rank)]
+                xq = torch.cat([p for e in by_expert for p in e]) if xq_by_src.shape[0] else xq_by_src
             recv_per_expert = [sum(got_l[s][e] for s in range(self.world)) for e in range(self.per_rank)]
 
         # local experts on their row segments
@@ -160,9 +166,11 @@ class ExpertParallelMoE(nn.Module):
 
         if self.world > 1:
             # back to (source rank, expert) order, then home
-            segs = torch.split(y_rows, [got_l[s][e] for e in range(self.per_rank) for s in range(self.world)])
-            back = [segs[e * self.world + s] for s in range(self.world) for e in range(self.per_rank)]
-            y_rows = self._exchange_rows(torch.cat(back) if y_rows.shape[0] else y_rows, recv_counts, send_counts)
+            if self.per_rank > 1:
+                segs = torch.split(y_rows, [got_l[s][e] for e in range(self.per_rank) for s in range(self.world)])
+                back = [segs[e * self.world + s] for s in range(self.world) for e in range(self.per_rank)]
+                y_rows = torch.cat(back) if y_rows.shape[0] else y_rows
+            y_rows = self._exchange_rows(y_rows, recv_counts, send_counts)
 
         # y_rows is in `order`: weight each copy and add it to its token
         wc = w.reshape(-1).index_select(0, order).unsqueeze(1)

@@ -35,8 +35,9 @@ import torch.nn as nn
 from . import blockquant_ext as ext
 from . import kvcache
 from .fused import rmsnorm_quantize, softmax_quantize
+from .ep_moe import ExpertParallelMoE
 from .module import QLinear
-from .ops import FP16AccumMatMul
+from .ops import FP16AccumMatMul, FP32AccumMatMul
 from .quantizer import _CudaBlockQuantizer, _QBase
 
 
@@ -52,6 +53,14 @@ class LlamaArch:
     vocab: int = 128256
     eps: float = 1e-5
     theta: float = 500000.0
+    num_experts: int = 0          # > 0: a sparse mixture-of-experts MLP (Mixtral), experts spread over the ranks
+    top_k: int = 2
+
+
+def mixtral_8x7b() -> "LlamaArch":
+    """Mixtral-8x7B's constants."""
+    return LlamaArch(hidden=4096, layers=32, heads=32, kv_heads=8, head_dim=128, ffn=14336, vocab=32000, eps=1e-5,
+                     theta=1000000.0, num_experts=8, top_k=2)
 
 
 def rope_tables(T: int, head_dim: int, theta: float, device, offset: int = 0):
@@ -182,10 +191,20 @@ class QLlamaMLP(nn.Module):
 
 
 class QLlamaDecoderLayer(nn.Module):
-    def __init__(self, arch: LlamaArch, rank: int = 0, world: int = 1, device=None):
+    """Attention + gated MLP, or (``arch.num_experts > 0``, the Mixtral layer) attention + sparse MoE block whose
+    experts are ``QMixtralBlockSparseTop2MLP``s (src/module.py:597-622) spread over the ranks."""
+
+    def __init__(self, arch: LlamaArch, rank: int = 0, world: int = 1, device=None, group=None):
         super().__init__()
         self.self_attn = QLlamaAttention(arch, rank, world, device)
-        self.mlp = QLlamaMLP(arch, rank, world, device)
+        if arch.num_experts > 0:
+            self.mlp = None
+            self.block_sparse_moe = ExpertParallelMoE(arch.hidden, arch.ffn, arch.num_experts, arch.top_k,
+                                                      group=group if world > 1 else None, device=device, dtype=torch.float16,
+                                                      local_only=world == 1)
+        else:
+            self.mlp = QLlamaMLP(arch, rank, world, device)
+            self.block_sparse_moe = None
         self.input_layernorm = nn.Parameter(torch.ones(arch.hidden, dtype=torch.float16, device=device))
         self.post_attention_layernorm = nn.Parameter(torch.ones(arch.hidden, dtype=torch.float16, device=device))
 
@@ -220,7 +239,7 @@ class QLlamaModel(nn.Module):
         if arch.vocab % self.world:
             raise ValueError(f"vocabulary {arch.vocab} does not divide over {self.world} ranks")
         self.embed_tokens = nn.Embedding(arch.vocab, arch.hidden, device=device, dtype=torch.float16)
-        self.layers = nn.ModuleList([QLlamaDecoderLayer(arch, self.rank, self.world, device) for _ in range(arch.layers)])
+        self.layers = nn.ModuleList([QLlamaDecoderLayer(arch, self.rank, self.world, device, group) for _ in range(arch.layers)])
         self.norm = nn.Parameter(torch.ones(arch.hidden, dtype=torch.float16, device=device))
         self.lm_head = nn.Linear(arch.hidden, arch.vocab // self.world, bias=False, device=device, dtype=torch.float16)
         self._comm = None
@@ -244,6 +263,15 @@ class QLlamaModel(nn.Module):
             for nm, lin in (("k_proj", at.k_proj), ("v_proj", at.v_proj)):
                 lin.weight.copy_(self._draw(f"{i}.{nm}", (a.kv_heads * D, a.hidden), seed, dev)[at.kv0 * D:(at.kv0 + at.num_key_value_heads) * D])
             at.o_proj.weight.copy_(self._draw(f"{i}.o_proj", (a.hidden, a.heads * D), seed, dev)[:, at.h0 * D:(at.h0 + at.num_heads) * D])
+            if ml is None:
+                moe = layer.block_sparse_moe
+                moe.gate.weight.copy_(self._draw(f"{i}.gate", (a.num_experts, a.hidden), seed, dev))
+                for j, ex in enumerate(moe.experts):
+                    e = moe.e0 + j
+                    ex.w1.weight.copy_(self._draw(f"{i}.experts.{e}.w1", (a.ffn, a.hidden), seed, dev))
+                    ex.w3.weight.copy_(self._draw(f"{i}.experts.{e}.w3", (a.ffn, a.hidden), seed, dev))
+                    ex.w2.weight.copy_(self._draw(f"{i}.experts.{e}.w2", (a.hidden, a.ffn), seed, dev))
+                continue
             for nm, lin in (("gate_proj", ml.gate_proj), ("up_proj", ml.up_proj)):
                 lin.weight.copy_(self._draw(f"{i}.{nm}", (a.ffn, a.hidden), seed, dev)[ml.f0:ml.f0 + ml.f])
             ml.down_proj.weight.copy_(self._draw(f"{i}.down_proj", (a.hidden, a.ffn), seed, dev)[:, ml.f0:ml.f0 + ml.f])
@@ -254,11 +282,31 @@ class QLlamaModel(nn.Module):
         set the accumulation operator on every projection of the decoder layers (lm_head stays as it is)."""
         for layer in self.layers:
             cfg.q_attn(layer.self_attn)
-            cfg.q_mlp(layer.mlp)
-            for lin in (layer.self_attn.q_proj, layer.self_attn.k_proj, layer.self_attn.v_proj, layer.self_attn.o_proj,
-                        layer.mlp.gate_proj, layer.mlp.up_proj, layer.mlp.down_proj):
+            lins = [layer.self_attn.q_proj, layer.self_attn.k_proj, layer.self_attn.v_proj, layer.self_attn.o_proj]
+            if layer.mlp is not None:
+                cfg.q_mlp(layer.mlp)
+                lins += [layer.mlp.gate_proj, layer.mlp.up_proj, layer.mlp.down_proj]
+            for lin in lins:
                 cfg.static_quant_linear_weight(lin)
                 lin.ops = cfg.make_accum_op()
+            if layer.block_sparse_moe is not None:
+                # q_mixtral_expert (src/ptq.py:292-307) gives w1 and w3 the same input quantizer; block quantisation
+                # is per row, so it is applied once per token before the copies travel (the block's `aq`) and the
+                # experts' own w1 / w3 input quantizers stay the identity
+                moe = layer.block_sparse_moe
+                moe.aq = cfg.map_act_quantizer()
+                for ex in moe.experts:
+                    for lin in (ex.w1, ex.w3, ex.w2):
+                        lin.wq = cfg.map_wgt_quantizer()
+                        cfg.static_quant_linear_weight(lin)
+                        lin.ops = cfg.make_accum_op() or FP32AccumMatMul()
+                    ex.w2.aq = cfg.map_act_quantizer()
+                    if cfg.quant_before_hadamard:
+                        ex.w3.yq = cfg.map_act_quantizer()
+                    if cfg.quant_before_silu:
+                        ex.w1.yq = cfg.map_act_quantizer()
+                    if cfg.quant_before_rms_norm:
+                        ex.w2.yq = cfg.map_act_quantizer()
         return self
 
     # ---- collectives on the side stream -----------------------------------------------------------
@@ -339,7 +387,7 @@ class QLlamaModel(nn.Module):
 
         for layer in self.layers:
             at, ml = layer.self_attn, layer.mlp
-            aq_attn, aq_mlp = at.input_quantizer(), ml.input_quantizer()
+            aq_attn, aq_mlp = at.input_quantizer(), (ml.input_quantizer() if ml is not None else None)
             # residual add of the previous branch + input norm + the q/k/v input quantizer, on the token shard
             for p in pieces:
                 self._await(p)
@@ -353,6 +401,14 @@ class QLlamaModel(nn.Module):
                 self._done(p, p.part)
             for p in pieces:
                 p.branch = self._scatter_rows(p, p.part)
+            if layer.block_sparse_moe is not None:
+                # sparse MoE on this rank's own tokens: router on the normalised rows, copies to the experts' ranks
+                # and back by all-to-all (inside the block); no gather / scatter of rows in this half
+                for p in pieces:
+                    self._await(p)
+                    h, p.x = rmsnorm_quantize(p.x, layer.post_attention_layernorm, a.eps, None, residual=p.branch)
+                    p.branch = layer.block_sparse_moe(h)
+                continue
             for p in pieces:
                 self._await(p)
                 p.act, p.x = rmsnorm_quantize(p.x, layer.post_attention_layernorm, a.eps, aq_mlp, residual=p.branch)
@@ -388,7 +444,8 @@ class QLlamaModel(nn.Module):
         grow with the sequence, are counted by ``attention_flops``)."""
         a = self.arch
         D = a.head_dim
-        per_layer = a.hidden * (a.heads * D + 2 * a.kv_heads * D) + a.heads * D * a.hidden + 3 * a.hidden * a.ffn
+        mlp = 3 * a.hidden * a.ffn * (a.top_k if a.num_experts > 0 else 1) + a.hidden * a.num_experts
+        per_layer = a.hidden * (a.heads * D + 2 * a.kv_heads * D) + a.heads * D * a.hidden + mlp
         return 2.0 * (a.layers * per_layer + a.hidden * a.vocab)
 
     def attention_flops(self, B: int, T: int) -> float:

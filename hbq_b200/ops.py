@@ -48,3 +48,15 @@ class FP16AccumMatMul(nn.Module):
         # the bias was added by the kernel's store (one fp16 add per output, as the reference's `out2d + bias`,
         # src/ops.py:59-60), so with `out=` the result, bias included, is in `out`
         return out2d.view(*orig_shape[:-1], -1)
+
+
+class FP32AccumMatMul(nn.Module):
+    """``F.linear`` with fp32 accumulation (what ``_QBaseLinear.forward`` runs when no accumulation operator is set,
+    src/module.py:47-48) on the library's tensor-core kernel instead of cuBLAS, as an ``ops`` object."""
+
+    def forward(self, x, w, bias=None, out=None) -> torch.Tensor:
+        x2d = x.reshape(-1, x.shape[-1])
+        if x2d.dtype != torch.float16:
+            x2d = x2d.half()
+        y = ext.gemm_fp32_accum(x2d, w if w.dtype == torch.float16 else w.half(), b_is_nk=True, out=out, bias=bias)
+        return y.view(*x.shape[:-1], -1)

@@ -183,3 +183,86 @@ def test_hbq_a_kv_logits_against_the_oracle_forward(oracle):
         layer.self_attn.quant_attn_wgt = True
     m.pieces = 2
     assert torch.equal(m(ids).float().cpu(), got)
+
+
+def _moe_arch():
+    import hbq_b200 as H
+    return H.LlamaArch(hidden=256, layers=2, heads=4, kv_heads=2, head_dim=128, ffn=512, vocab=512, eps=1e-5, theta=1e6,
+                       num_experts=4, top_k=2)
+
+
+def test_mixtral_layer_unquantised_agrees_with_transformers():
+    """The sparse-MoE decoder (router, top-2, experts, combine) against transformers' MixtralForCausalLM with the same
+    weights.  The reference's own Mixtral attention evaluates its matmuls and softmax in fp32 (src/module.py:438-496);
+    here they are fp16 tensor-core matmuls with an fp32 softmax, which is inside the bound below."""
+    tf = pytest.importorskip("transformers")
+    import hbq_b200 as H
+    a = _moe_arch()
+    m = H.QLlamaModel(a, device="cuda")
+    m.init_weights(4)
+    ids = torch.randint(0, a.vocab, (2, 256), generator=torch.Generator().manual_seed(0)).cuda()
+    got = m(ids).float()
+    try:
+        hcfg = tf.MixtralConfig(vocab_size=a.vocab, hidden_size=a.hidden, intermediate_size=a.ffn, num_hidden_layers=a.layers,
+                                num_attention_heads=a.heads, num_key_value_heads=a.kv_heads, head_dim=a.head_dim,
+                                rms_norm_eps=a.eps, rope_theta=a.theta, max_position_embeddings=4096, sliding_window=None,
+                                num_local_experts=a.num_experts, num_experts_per_tok=a.top_k, tie_word_embeddings=False)
+        hcfg._attn_implementation = "eager"
+        hf = tf.MixtralForCausalLM(hcfg).to(device="cuda", dtype=torch.float32).eval()
+        sd = hf.state_dict()
+        mine = {k: v.float() for k, v in m.state_dict().items()}
+        new = {"model.embed_tokens.weight": mine["embed_tokens.weight"], "model.norm.weight": mine["norm"],
+               "lm_head.weight": mine["lm_head.weight"]}
+        for i in range(a.layers):
+            for n in ("q_proj", "k_proj", "v_proj", "o_proj"):
+                new[f"model.layers.{i}.self_attn.{n}.weight"] = mine[f"layers.{i}.self_attn.{n}.weight"]
+            new[f"model.layers.{i}.input_layernorm.weight"] = mine[f"layers.{i}.input_layernorm"]
+            new[f"model.layers.{i}.post_attention_layernorm.weight"] = mine[f"layers.{i}.post_attention_layernorm"]
+            pre = f"model.layers.{i}.block_sparse_moe."
+            alt = f"model.layers.{i}.mlp."
+            gate_key = pre + "gate.weight" if pre + "gate.weight" in sd else alt + "gate.weight"
+            new[gate_key] = mine[f"layers.{i}.block_sparse_moe.gate.weight"]
+            if pre + "experts.0.w1.weight" in sd:
+                for e in range(a.num_experts):
+                    for n in ("w1", "w2", "w3"):
+                        new[pre + f"experts.{e}.{n}.weight"] = mine[f"layers.{i}.block_sparse_moe.experts.{e}.{n}.weight"]
+            elif alt + "experts.gate_up_proj" in sd:        # fused expert tensors of newer releases
+                w1 = torch.stack([mine[f"layers.{i}.block_sparse_moe.experts.{e}.w1.weight"] for e in range(a.num_experts)])
+                w3 = torch.stack([mine[f"layers.{i}.block_sparse_moe.experts.{e}.w3.weight"] for e in range(a.num_experts)])
+                w2 = torch.stack([mine[f"layers.{i}.block_sparse_moe.experts.{e}.w2.weight"] for e in range(a.num_experts)])
+                gu = torch.cat([w1, w3], dim=1)
+                new[alt + "experts.gate_up_proj"] = gu if sd[alt + "experts.gate_up_proj"].shape == gu.shape else gu.transpose(1, 2).contiguous()
+                new[alt + "experts.down_proj"] = w2 if sd[alt + "experts.down_proj"].shape == w2.shape else w2.transpose(1, 2).contiguous()
+            else:
+                pytest.skip("unknown expert parameter layout in this transformers release")
+        missing = hf.load_state_dict(new, strict=False)
+        left = [k for k in missing.missing_keys if "rotary" not in k]
+        if left or missing.unexpected_keys:
+            pytest.skip(f"state dict layout of this transformers release: missing {left[:3]}, unexpected {missing.unexpected_keys[:3]}")
+        with torch.no_grad():
+            want = hf(ids).logits.reshape(-1, a.vocab)
+    except (TypeError, AttributeError, KeyError) as e:
+        pytest.skip(f"transformers API: {e}")
+    rel = _rel(got, want)
+    print(f"unquantised Mixtral-style model vs transformers MixtralForCausalLM (fp32): rel_fro {rel:.3e}")
+    assert rel <= 5e-3, rel
+
+
+def test_mixtral_layer_hbq_e():
+    """config/hbq_e.yaml on the sparse-MoE decoder: the same logits whether the batch runs whole or in pieces, finite,
+    and the experts' GEMMs are the library's (no cuBLAS linear in the MoE block)."""
+    import hbq_b200 as H
+    with open(os.path.join(HERE, "golden", "ptq_configs.json")) as fh:
+        cfgd = json.load(fh)["hbq_e.yaml"]["config"]
+    a = _moe_arch()
+    m = H.QLlamaModel(a, device="cuda")
+    m.init_weights(4)
+    m.apply_ptq(H.PTQConfig(cfgd))
+    ex = m.layers[0].block_sparse_moe.experts[0]
+    assert isinstance(ex.w1.ops, H.FP32AccumMatMul) and isinstance(ex.w2.aq, H.HBQQuantizer) and type(ex.w1.aq).__name__ == "_QBase"
+    assert isinstance(m.layers[0].block_sparse_moe.aq, H.HBQQuantizer)
+    ids = torch.randint(0, a.vocab, (4, 128), generator=torch.Generator().manual_seed(2)).cuda()
+    y = m(ids)
+    assert torch.isfinite(y).all() and H.gemm_status() == 0
+    m.pieces = 2
+    assert torch.equal(m(ids), y)

@@ -70,6 +70,21 @@ def _worker(rank, world, port, out_dir):
         ok = ok and torch.allclose(cols, want[:, 32 * rank:32 * rank + 32], rtol=2e-2, atol=2e-3)
         full = tp(ids, gather_logits=True).float()
         ok = ok and full.shape == want.shape and torch.allclose(full, want, rtol=2e-2, atol=2e-3)
+    # the Mixtral layer: attention as above, experts spread over the ranks, tokens routed by all-to-all
+    moe_arch = H.LlamaArch(hidden=128, layers=2, heads=4, kv_heads=2, head_dim=32, ffn=256, vocab=64, num_experts=4, top_k=2)
+    whole = H.QLlamaModel(moe_arch, parallel=False)
+    whole.init_weights(6)
+    want = whole(ids).float()
+    ep = H.QLlamaModel(moe_arch, pieces=2)
+    ep.init_weights(6)
+    moe = ep.layers[0].block_sparse_moe
+    ok = ok and (moe.world, moe.per_rank, moe.e0, len(whole.layers[0].block_sparse_moe.experts)) == (2, 2, 2 * rank, 4)
+    ok = ok and torch.equal(moe.experts[1].w2.weight, whole.layers[0].block_sparse_moe.experts[2 * rank + 1].w2.weight)
+    full = ep(ids, gather_logits=True).float()
+    # a token whose two best router scores nearly tie may take another expert when the hidden state differs in its
+    # last fp16 bit: rows are compared one by one and a few may differ
+    good = ((full - want).abs() <= 2e-3 + 2e-2 * want.abs()).all(dim=1)
+    ok = ok and full.shape == want.shape and float(good.float().mean()) >= 0.95
     try:
         H.QLlamaModel(H.LlamaArch(hidden=128, layers=1, heads=3, kv_heads=3, head_dim=32, ffn=256, vocab=64))
         ok = False                                               # 3 heads do not divide over 2 ranks
