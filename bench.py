@@ -330,6 +330,11 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             tp = llama_prefill_record(rank, world, dev, 2, 1, args.llama_pieces, layers=args.llama_layers)
             sub["llama_prefill"]["tensor_parallel"] = tp
             sub["llama_prefill"]["speedup_over_one_gpu"] = one["ms_per_forward"] / tp["ms_per_forward"]
+            m1 = llama_prefill_record(rank, world, dev, 2, 1, 1, layers=args.llama_layers, batch=4, seq=4096, parallel=False,
+                                      mixtral=True)
+            mp_ = llama_prefill_record(rank, world, dev, 2, 1, 1, layers=args.llama_layers, batch=4, seq=4096, mixtral=True)
+            sub["mixtral_prefill"] = {"one_gpu": m1, "expert_parallel": mp_,
+                                      "speedup_over_one_gpu": m1["ms_per_forward"] / mp_["ms_per_forward"]}
             sa = argparse.Namespace(**vars(args))
             sa.steps, sa.warmup = 5, 3
             sub["tp_mlp"] = run_tp_mlp(sa, rank, world, local_rank, standalone=False)
@@ -528,19 +533,32 @@ HBQ_A_KV = {
 }
 
 
+# config/hbq_e.yaml of the reference as PTQ reads it: HBQ-E W4A5 (micro-block 32) on every linear, fp32 accumulation
+HBQ_E = {
+    "quantization": {"xqtype": "hbq", "wqtype": "hbq"},
+    "block_quant": {"act_ebit": 2, "act_mbit": 2, "act_block_size": 128, "act_sc_ebit": 5, "act_sc_mbit": 3,
+                    "act_l2_sc_bit": 2, "act_l2_block_size": 32, "act_l2_scheme": "SIG-1",
+                    "wgt_ebit": 2, "wgt_mbit": 1, "wgt_block_size": 128, "wgt_sc_ebit": 5, "wgt_sc_mbit": 3,
+                    "wgt_l2_sc_bit": 2, "wgt_l2_block_size": 32, "wgt_l2_scheme": "Mix",
+                    "scale_allow_subnormal": False, "qk_mx_round": False},
+    "accumulation": {"type": "fp32"},
+}
+
+
 def llama_prefill_record(rank: int, world: int, dev, steps: int, warmup: int, pieces: int, layers: int = 32,
-                         batch: int = 8, seq: int = 2048, parallel: bool = True):
+                         batch: int = 8, seq: int = 2048, parallel: bool = True, mixtral: bool = False):
     """configs[3]: Llama-3-8B-architecture random-init model, HBQ-A W4A5 + KV quantisation (hbq_a_kv.yaml), prefill of
     `batch` x `seq` tokens, tensor/sequence-parallel over `world` ranks (strong scaling: the batch is fixed).  Returns
     the record for the benchmark line (device time per forward, max over ranks)."""
     import torch
     import torch.distributed as dist
     import hbq_b200 as H
-    arch = H.LlamaArch(layers=layers)
+    arch = H.mixtral_8x7b() if mixtral else H.LlamaArch()
+    arch.layers = layers
     model = H.QLlamaModel(arch, device=dev, pieces=pieces, parallel=parallel)
     tp = world if parallel else 1
     model.init_weights(seed=0)
-    model.apply_ptq(H.PTQConfig(HBQ_A_KV))
+    model.apply_ptq(H.PTQConfig(HBQ_E if mixtral else HBQ_A_KV))
     ids = torch.randint(0, arch.vocab, (batch, seq), generator=torch.Generator().manual_seed(3)).to(dev)
 
     def barrier():
@@ -569,9 +587,14 @@ def llama_prefill_record(rank: int, world: int, dev, steps: int, warmup: int, pi
     finite = bool(torch.isfinite(out[:256]).all().item())
     if H.gemm_status() != 0:
         raise RuntimeError("tensor-core GEMM reported an expired wait")
-    rec = {"workload": f"configs[3]: Llama-3-8B architecture, {layers} layers, hbq_a_kv.yaml, prefill {batch}x{seq}",
-           "parallelism": f"tp{tp} heads / MLP features over ranks, residual stream by tokens: reduce-scatter + all-gather "
-                          f"per half-layer, batch in {model.pieces} piece(s)" if tp > 1 else "1 GPU (whole model on every rank)",
+    what = (f"configs[4]: Mixtral-8x7B architecture, {layers} layers, 8 experts top-2, hbq_e.yaml" if mixtral
+            else f"configs[3]: Llama-3-8B architecture, {layers} layers, hbq_a_kv.yaml")
+    how = (f"tp{tp} attention heads over ranks (reduce-scatter + all-gather of token shards), ep{tp} experts over ranks "
+           f"(all-to-all dispatch / combine of each rank's tokens), batch in {model.pieces} piece(s)" if mixtral else
+           f"tp{tp} heads / MLP features over ranks, residual stream by tokens: reduce-scatter + all-gather per half-layer, "
+           f"batch in {model.pieces} piece(s)")
+    rec = {"workload": f"{what}, prefill {batch}x{seq}",
+           "parallelism": how if tp > 1 else "1 GPU (whole model on every rank)",
            "ms_per_forward": ms, "tokens_per_s": tokens / (ms * 1e-3), "tflops": flops / (ms * 1e-3) / 1e12,
            "flops_counted": "2*MAC of all linear layers + lm_head + uncausal attention matmuls",
            "kernel_launches_per_forward": (H.launch_count() - l0) // steps, "finite": finite,
@@ -589,9 +612,13 @@ def run_llama(args, rank: int, world: int, local_rank: int):
     dev = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    rec = llama_prefill_record(rank, world, dev, args.steps, args.warmup, args.llama_pieces, layers=args.llama_layers)
+    if args.mixtral:
+        rec = llama_prefill_record(rank, world, dev, args.steps, args.warmup, args.llama_pieces, layers=args.llama_layers,
+                                   batch=4, seq=4096, mixtral=True)
+    else:
+        rec = llama_prefill_record(rank, world, dev, args.steps, args.warmup, args.llama_pieces, layers=args.llama_layers)
     if rank == 0:
-        print(json.dumps({"metric": "llama_prefill_tokens_per_s", "value": rec["tokens_per_s"], "unit": "tokens/s", "n_gpus": world,
+        print(json.dumps({"metric": "mixtral_prefill_tokens_per_s" if args.mixtral else "llama_prefill_tokens_per_s", "value": rec["tokens_per_s"], "unit": "tokens/s", "n_gpus": world,
                           "steps": args.steps, "warmup": args.warmup, "ms_per_step": rec["ms_per_forward"],
                           "higher_is_better": True, "scaling": "strong", "dtype": "f16", "data": "synthetic", "config": rec}))
     if world > 1:
@@ -770,6 +797,8 @@ def main():
                     help="instead of the benchmark line: the tensor-parallel MLP block of configs[3] over the launched ranks")
     ap.add_argument("--llama", action="store_true",
                     help="instead of the benchmark line: the Llama-3-8B-architecture prefill of configs[3] over the launched ranks")
+    ap.add_argument("--mixtral", action="store_true",
+                    help="instead of the benchmark line: the Mixtral-8x7B-architecture prefill of configs[4] over the launched ranks")
     ap.add_argument("--llama-layers", type=int, default=32)
     ap.add_argument("--llama-pieces", type=int, default=2,
                     help="--llama: pieces of whole sequences the batch is cut into (collectives of one run under the GEMMs of the next)")
@@ -794,7 +823,7 @@ def main():
     if args.no_fused_act:
         from hbq_b200 import kvcache
         kvcache.FUSE_SWIGLU = False
-    if args.llama:
+    if args.llama or args.mixtral:
         run_llama(args, rank, world, local_rank)
         return
     if args.tp_mlp:
