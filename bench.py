@@ -1,23 +1,27 @@
 #!/usr/bin/env python
-"""Benchmark of the HBQ hot path on B200: one quantised linear layer.
+"""Benchmark of the HBQ hot path on B200: one quantised linear layer, with the whole-model prefills beside it.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-model] [--no-cpu-baseline]
     python bench.py --sweep [CASE]      # configs[2] quantize sweep and KV-cache writes, one line per case
+    python bench.py --llama | --mixtral # configs[3] / configs[4] prefill alone over the launched ranks
+    python bench.py --tp-mlp | --ep-moe # the tensor-parallel MLP / expert-parallel MoE block alone
 
-Workload (the reference's HBQ-E quant-GEMM configuration with partial-sum-quantised
-accumulation, config/hbq_e_psum_quant.yaml): X bf16 [4096, 4096] ~ N(0,1) with 0.5 % outlier
-channels x30, W bf16 [14336, 4096] ~ N(0, 0.02) (the Llama-3-8B MLP up-projection shape),
-synthetic and seeded.  The weight is fake-quantised once (static weight quantisation, not
-timed).  One step = HBQ-E activation quantize of X followed by the GEMM whose fp32 partial sums
-are INT8-quantised per (128 k, 32 n) block and accumulated in fp16.  The metric counts 2*M*N*K
-flops per step and nothing else.
+Workload of the line's `value` (the reference's HBQ-E quant-GEMM configuration with partial-sum-quantised
+accumulation, config/hbq_e_psum_quant.yaml): X bf16 [4096, 4096] ~ N(0,1) with 0.5 % outlier channels x30,
+W bf16 [14336, 4096] ~ N(0, 0.02) (the Llama-3-8B MLP up-projection shape), synthetic and seeded.  The weight is
+fake-quantised once (static weight quantisation, not timed).  One step = HBQ-E activation quantize of X followed by
+the GEMM whose fp32 partial sums are INT8-quantised per (128 k, 32 n) block and accumulated in fp16.  The metric
+counts 2*M*N*K flops per step and nothing else.  After 0.8 s of the same load, blocks of exactly K steps run back to
+back for at least 1.5 s; the reported step time is the median block (device time, max over ranks) / K.
 
-With N > 1 (torchrun, one rank per GPU) every rank runs its own batch X against the same W: the
-path shards over rows without any exchange, so the scaling is weak and no collective is on the
-data path; ranks only meet in the barriers around the timed region.
+With N > 1 (torchrun, one rank per GPU) every rank runs its own batch X against the same W: the layer shards over
+rows without any exchange, so `value` scales weakly with no collective on its data path.  The collectives of the
+path are in the sub-records of the same line: `llama_prefill` (configs[3], tensor/sequence-parallel: reduce-scatter +
+all-gather), `mixtral_prefill` (configs[4], expert-parallel all-to-all), `tp_mlp`, `ep_moe`, each with the one-GPU
+time measured in the same call.
 
-`--impl reference` times the CPU restatement of the reference's path (oracle/, all host
-threads) on a bounded sample of the same workload.
+`--impl reference` times the CPU restatement of the reference's path (oracle/, all host threads) on a bounded sample
+of the same workload.
 """
 from __future__ import annotations
 

@@ -1,0 +1,119 @@
+"""The hot path as a serving engine calls it: flattened token batches, decode-sized shapes.
+
+The reference's second caller is its vLLM plugin (vllm/src/hbq_vllm_quant.py): a linear method that fake-quantises
+the loaded weights once and the activations on every call (``HBQNVFP4LinearMethod``, :493-554), and an attention
+forward patched to quantise post-RoPE Q, K and V of a flattened ``[tokens, heads * head_dim]`` batch
+(:288-345, :398-454), V per sequence span along the token axis.  The functions below are those hooks on this
+library's kernels, with the reference functions' names and argument meaning; they do not import the engine, so the
+plugin's registration code (``register_quantization_config``, the attention-class patching) stays where it is and
+only its calls into ``src.quantizer`` change.  Quantizers are passed in (the plugin builds them from its YAML with
+``PTQConfig.map_act_quantizer`` / ``map_kv_quantizer``).
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from . import blockquant_ext as ext
+from .kvcache import write_v_cache
+from .quantizer import _CudaBlockQuantizer
+
+
+def quantize_post_rope_q(q: torch.Tensor, num_heads: int, head_dim: int, quantizer) -> torch.Tensor:
+    """``_quantize_post_rope_q`` (:288-294): the activation quantizer along head_dim of ``[tokens, H * D]``."""
+    return quantizer.q(q.reshape(-1, num_heads, head_dim)).reshape(q.shape).to(q.dtype)
+
+
+def quantize_k_cache(k: torch.Tensor, num_kv_heads: int, head_dim: int, quantizer) -> torch.Tensor:
+    """``_quantize_k_cache`` (:297-304): the KV quantizer along head_dim of ``[tokens, Hkv * D]``, after RoPE."""
+    return quantizer.q(k.reshape(-1, num_kv_heads, head_dim)).reshape(k.shape).to(k.dtype)
+
+
+def sequence_spans_from_positions(positions: Optional[torch.Tensor], n_tokens: int) -> List[Tuple[int, int]]:
+    """``_sequence_spans_from_positions`` (:307-318): ``[left, right)`` runs of consecutive positions -- a new run
+    starts wherever a position is not its predecessor + 1.  One device-to-host read instead of one per token."""
+    if positions is None or positions.numel() != n_tokens or n_tokens == 0:
+        return [(0, n_tokens)]
+    pos = positions.detach().flatten().to(torch.long)
+    breaks = (torch.nonzero(pos[1:] != pos[:-1] + 1).flatten() + 1).tolist()
+    starts = [0] + breaks + [n_tokens]
+    return list(zip(starts, starts[1:]))
+
+
+def quantize_v_cache(v: torch.Tensor, num_kv_heads: int, head_dim: int, quantizer,
+                     positions: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``_quantize_v_cache`` (:321-345): V quantised along the TOKEN axis, each sequence span on its own (blocks and
+    scales never straddle two requests).  Per span the reference permutes to ``[Hkv, D, tokens]``, quantises and
+    permutes back; here each span is one launch of the token-axis kernel that keeps the flattened layout."""
+    vv = v.reshape(-1, num_kv_heads, head_dim)
+    out = torch.empty_like(vv)
+    for left, right in sequence_spans_from_positions(positions, vv.shape[0]):
+        if right <= left:
+            continue
+        seq = vv[left:right]
+        if isinstance(quantizer, _CudaBlockQuantizer):
+            out[left:right] = write_v_cache(seq.unsqueeze(0), num_kv_heads, quantizer, token_major=True)[0]
+        else:
+            out[left:right] = quantizer.q(seq.permute(1, 2, 0).contiguous()).permute(2, 0, 1)
+    return out.reshape(v.shape).to(v.dtype)
+
+
+class KCenterTracker:
+    """``_center_qwen_k_cache`` (:348-395): K of a Qwen2 block is centred over the prefill tokens of a sequence and
+    the same centre serves that sequence's later decode tokens.  The engine hands over flattened batches without
+    sequence ids, so centres are queued by the next position that will consume them, as in the reference."""
+
+    def __init__(self):
+        self.center_by_pos: Dict[int, List[torch.Tensor]] = {}
+
+    def __call__(self, k: torch.Tensor, positions: torch.Tensor, num_kv_heads: int, head_dim: int) -> torch.Tensor:
+        if positions.numel() != k.shape[0]:
+            return k
+        kv = k.reshape(-1, num_kv_heads, head_dim)
+        pos = positions.detach().flatten().to(torch.long).tolist()
+        centered = None
+        for left, right in sequence_spans_from_positions(positions, kv.shape[0]):
+            if right - left > 1:                                  # a prefill span: its own mean, queued for the next position
+                center = kv[left:right].mean(dim=0, keepdim=True).detach()
+                nxt = pos[right - 1] + 1
+            else:                                                 # a decode token: the centre queued for its position
+                queue = self.center_by_pos.get(pos[left])
+                if not queue:
+                    continue
+                center = queue.pop(0).to(device=kv.device, dtype=kv.dtype)
+                if not queue:
+                    self.center_by_pos.pop(pos[left], None)
+                nxt = pos[left] + 1
+            if centered is None:
+                centered = kv.clone()
+            centered[left:right] = kv[left:right] - center
+            self.center_by_pos.setdefault(nxt, []).append(center)
+        return k if centered is None else centered.reshape_as(k).to(k.dtype)
+
+
+class HBQLinearMethod:
+    """``HBQNVFP4LinearMethod`` (:493-554) without the engine's base class: ``process_weights_after_loading``
+    fake-quantises ``layer.weight`` once (idempotent through the ``hbq_weight_quantized`` mark, as the reference;
+    no row chunking -- the reference chunks only to bound its eager quantizer's temporaries), ``apply`` quantises the
+    activations and multiplies.  The product is the reference's ``F.linear`` (fp32 accumulation) on the tensor-core
+    kernel, whose 128-column tile serves decode-sized batches."""
+
+    def __init__(self, act_quantizer, wgt_quantizer):
+        self.act_quantizer = act_quantizer
+        self.wgt_quantizer = wgt_quantizer
+
+    @torch.inference_mode()
+    def process_weights_after_loading(self, layer: torch.nn.Module) -> None:
+        if getattr(layer, "hbq_weight_quantized", False) or getattr(layer, "weight", None) is None:
+            return
+        layer.weight.data = self.wgt_quantizer.q(layer.weight.data).to(layer.weight.dtype)
+        setattr(layer, "hbq_weight_quantized", True)
+
+    def apply(self, layer: torch.nn.Module, x: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+        xq = self.act_quantizer.q(x)
+        w = layer.weight
+        if xq.is_cuda and xq.dtype == torch.float16 and w.dtype == torch.float16:
+            y = ext.gemm_fp32_accum(xq.reshape(-1, xq.shape[-1]), w, b_is_nk=True, bias=bias)
+            return y.view(*x.shape[:-1], w.shape[0])
+        return torch.nn.functional.linear(xq, w, bias)
