@@ -508,6 +508,45 @@ def run_sweep(args):
             x = (0.5 * torch.distributions.StudentT(3.0).sample((8192, 8192))).to(torch.float16).cuda()
         q = cls[kind](**kw)
         timed(lambda: q.q(x), x.numel(), f"quantize {name}", {"shape": [8192, 8192], "dtype": "f16"})
+    if want in (None, "hbq_a_packed"):       # configs[2] as stated: bf16 in, packed codes + scales + bf16 dequantised out
+        xb = (0.5 * torch.distributions.StudentT(3.0).sample((8192, 8192))).to(torch.bfloat16).cuda()
+        q = cls["hbq"](**SWEEP_FORMATS["hbq_a"][1])
+        timed(lambda: q.quantize_packed(xb, with_deq=True), xb.numel() * 4.6641 / QUANT_BYTES_PER_ELEM,
+              "quantize hbq_a (packed + dequantised)", {"shape": [8192, 8192], "dtype": "bf16", "bytes_per_elem_counted": 4.6641})
+        del xb
+    if want in (None, "gemm"):               # the benchmark step's GEMM alone (INT8 partial sums, group 128, block 32)
+        xq = cls["hbq"](**ACT).q(torch.randn(M, K, device="cuda", dtype=torch.float16))
+        wt = cls["hbq"](**WGT).q((0.02 * torch.randn(N, K, device="cuda")).half())
+        ops = H.FP16AccumMatMul(group_size=GROUP_K, quant_block_size=GROUP_N)
+        for _ in range(max(args.warmup, 3)):
+            ops(xq, wt)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            ops(xq, wt)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / args.steps
+        print(json.dumps({"case": "gemm int8-psum", "ms": ms, "TFLOP/s": 2.0 * M * N * K / ms / 1e9, "shape": [M, K, N],
+                          "status": H.gemm_status()}))
+        del xq, wt
+    if want in (None, "softmax", "rmsnorm"):  # the fused row kernels at configs[3]'s shapes (one batch row of the prefill)
+        from hbq_b200 import fused
+        q = cls["hbq"](**SWEEP_FORMATS["hbq_a"][1])
+        if want in (None, "softmax"):
+            Hh, T = 32, 2048
+            sc = torch.randn(4, Hh, T, T, device="cuda", dtype=torch.float16)
+            timed(lambda: fused.softmax_quantize(sc, 128 ** -0.5, q, causal=True, q_len=T, heads=Hh, inplace=False),
+                  sc.numel(), "softmax + quantize (causal)",
+                  {"shape": [4, Hh, T, T], "dtype": "f16", "format": "hbq_a"})
+            del sc
+        if want in (None, "rmsnorm"):
+            xr = torch.randn(16384, 4096, device="cuda", dtype=torch.float16)
+            wr = torch.ones(4096, device="cuda", dtype=torch.float16)
+            timed(lambda: fused.rmsnorm_quantize(xr, wr, 1e-5, q, inplace=False), xr.numel(), "rmsnorm + quantize",
+                  {"shape": [16384, 4096], "dtype": "f16", "format": "hbq_a"})
+            del xr
     if want in (None, "k_write", "v_write"):
         B, T, Hh, D = 8, 4096, 32, 128
         k = torch.randn(B, T, Hh * D, device="cuda", dtype=torch.float16)
@@ -796,7 +835,7 @@ def main():
                          "expert-parallel MoE blocks at N > 1)")
     ap.add_argument("--sweep", nargs="?", const="all", default=None,
                     help="instead of the benchmark line: quantize sweep of configs[2] and the KV-cache writes "
-                         "(all cases, or one: " + ", ".join(SWEEP_FORMATS) + ", k_write, v_write)")
+                         "(all cases, or one: " + ", ".join(SWEEP_FORMATS) + ", hbq_a_packed, gemm, softmax, rmsnorm, k_write, v_write)")
     ap.add_argument("--tp-mlp", action="store_true",
                     help="instead of the benchmark line: the tensor-parallel MLP block of configs[3] over the launched ranks")
     ap.add_argument("--llama", action="store_true",

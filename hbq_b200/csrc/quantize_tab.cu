@@ -499,17 +499,28 @@ struct RowArgs {
 };
 static_assert(sizeof(RowArgs) <= 4000, "kernel parameters are limited to 4 KB");
 
-__device__ __forceinline__ float warp_sum(float v)
+// Reductions over the W lanes that share a row (a whole warp, or one of its halves).
+template <int W>
+__device__ __forceinline__ float lanes_sum(float v)
 {
     #pragma unroll
-    for (int off = 16; off >= 1; off >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off);
+    for (int off = W / 2; off >= 1; off >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off);
     return v;
 }
-__device__ __forceinline__ float warp_max(float v)
+template <int W>
+__device__ __forceinline__ float lanes_max(float v)
 {
     #pragma unroll
-    for (int off = 16; off >= 1; off >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, off));
+    for (int off = W / 2; off >= 1; off >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, off));
     return v;
+}
+
+// -inf into the halves of a packed pair whose key index (j0, j0 + 1) lies beyond the causal limit.
+__device__ __forceinline__ uint32_t mask_beyond(uint32_t b, int64_t j0, int64_t limit)
+{
+    if (j0 > limit) b = (b & 0xFFFF0000u) | 0x0000FC00u;
+    if (j0 + 1 > limit) b = (b & 0x0000FFFFu) | 0xFC000000u;
+    return b;
 }
 
 // The pre-softmax score chunk as the reference's fp16 ops leave it: fp16(fp16(s * scale) + bias), bias = the
@@ -527,12 +538,21 @@ __device__ __forceinline__ void score_chunk(const RowArgs& a, const uint4* rin, 
         const float2 sf = __half22float2(bits_h2(r[p]));
         __half2 v = __floats2half2_rn(sf.x * a.scale, sf.y * a.scale);
         if (rmask) v = __hadd2(v, bits_h2(m[p]));
-        uint32_t b = h2_bits(v);
-        const int64_t j0 = (int64_t)cir * 8 + 2 * p;
-        if (j0 > limit) b = (b & 0xFFFF0000u) | 0x0000FC00u;
-        if (j0 + 1 > limit) b = (b & 0x0000FFFFu) | 0xFC000000u;
-        sv[p] = b;
+        sv[p] = h2_bits(v);
     }
+    if ((int64_t)cir * 8 + 7 > limit) {                      // the chunk that holds the causal limit (or lies beyond it)
+        #pragma unroll
+        for (int p = 0; p < 4; ++p) sv[p] = mask_beyond(sv[p], (int64_t)cir * 8 + 2 * p, limit);
+    }
+}
+
+// fp32 quotient a / b, correctly rounded, from r = RN(1 / b): first guess, its exact residual, one correction
+// (Markstein's sequence).  b is a softmax row sum (>= 1 when finite); NaN and Inf operands end in NaN like a / b.
+__device__ __forceinline__ float div_by_sum(float a, float b, float r)
+{
+    const float q0 = a * r;
+    const float rem = fmaf(-q0, b, a);
+    return fmaf(rem, r, q0);
 }
 
 template <int MB, int ML, int PRO, bool QUANT>
@@ -546,12 +566,22 @@ __global__ void __launch_bounds__(ROW_THREADS, 2) hbq_row_kernel(const RowArgs a
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     uint32_t dst = 0u;
     if (QUANT) dst = stage_table(a.t, s_tab, s_l1c, &s_bar, s_nt2, s_tabf, ROW_THREADS);
-    const int bl = lane >> 2, g = lane & 3;                  // block of the iteration, lane of the block
+    // RMSNorm: one row per warp, 8 blocks (1024 elements) per iteration.  Softmax: one row per half-warp, 4 blocks
+    // per iteration -- a causal row ends anywhere, and the masked blocks of its last iteration are lanes without
+    // work (1.5 blocks on average instead of 3.5).
+    constexpr int RPW = PRO == ROW_SOFTMAX ? 2 : 1;          // rows per warp
+    constexpr int BPI = 8 / RPW;                             // blocks of a row per iteration
+    constexpr int RL = 32 / RPW;                             // lanes of a row
+    const int sub = lane / RL;
+    const int bl = (lane >> 2) & (BPI - 1), g = lane & 3;    // block of the iteration, lane of the block
     const int cpr = a.K >> 3;                                // chunks per row
-    const int iters_all = (a.nblk + 7) >> 3;                 // 8 blocks (1024 elements) per warp iteration
+    const int iters_all = (a.nblk + BPI - 1) / BPI;
 
     #pragma unroll 1
-    for (int64_t row = (int64_t)blockIdx.x * ROW_WARPS + warp; row < a.rows; row += (int64_t)gridDim.x * ROW_WARPS) {
+    for (int64_t rb = ((int64_t)blockIdx.x * ROW_WARPS + warp) * RPW; rb < a.rows; rb += (int64_t)gridDim.x * ROW_WARPS * RPW) {
+        int64_t row = rb + sub;
+        const bool live = row < a.rows;                      // odd row count: the idle half repeats the last row, stores nothing
+        if (!live) row = a.rows - 1;
         const uint4* rin = a.in + row * cpr;
         uint4* rout = a.out + row * cpr;
         float stat0 = 0.f, stat1 = 0.f;                      // RMSNORM: rstd; SOFTMAX: max, sum
@@ -566,7 +596,7 @@ __global__ void __launch_bounds__(ROW_THREADS, 2) hbq_row_kernel(const RowArgs a
             const uint4* rres = a.res ? a.res + row * cpr : nullptr;
             if (rres) rsrc = rx;
             for (int it = 0; it < iters; ++it) {
-                const int blk = it * 8 + bl;
+                const int blk = it * BPI + bl;
                 if (blk < a.nblk) {
                     #pragma unroll
                     for (int k = 0; k < 4; ++k) {
@@ -588,56 +618,84 @@ __global__ void __launch_bounds__(ROW_THREADS, 2) hbq_row_kernel(const RowArgs a
                     }
                 }
             }
-            ss = warp_sum(ss);
+            ss = lanes_sum<32>(ss);
             stat0 = rsqrtf(ss / (float)a.K + a.eps);
         } else {
             const int64_t qpos = row % a.L;
             if (a.causal) limit = qpos + a.key_offset;
             if (limit > (int64_t)a.K - 1) limit = (int64_t)a.K - 1;
             if (a.mask) rmask = a.mask + ((a.mask_batches > 1 ? row / a.HL : 0) * a.L + qpos) * cpr;
-            // whole iterations beyond the causal limit hold only masked keys: probabilities 0 (warp-uniform skip)
-            iters = min(iters_all, (int)(limit / 1024) + 1);
+            // whole iterations beyond the causal limit hold only masked keys: probabilities 0
+            iters = min(iters_all, (int)(limit / (128 * BPI)) + 1);
             float mx = -INFINITY;
-            for (int it = 0; it < iters; ++it) {
-                const int blk = it * 8 + bl;
-                if (blk < a.nblk) {
+            if (!rmask && a.scale > 0.f) {
+                // rounding is monotonic, so the largest scaled score is the scaled largest score: one max per pair
+                __half2 m2 = bits_h2(0xFC00FC00u);
+                for (int it = 0; it < iters; ++it) {
+                    const int blk = it * BPI + bl;
+                    #pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const int ci = blk * 16 + g + 4 * k;
+                        const int64_t j0 = (int64_t)ci * 8;
+                        if (ci >= cpr || j0 > limit) continue;
+                        const uint4 raw = __ldg(rin + ci);
+                        uint32_t r[4] = {raw.x, raw.y, raw.z, raw.w};
+                        if (j0 + 7 > limit) {
+                            #pragma unroll
+                            for (int p = 0; p < 4; ++p) r[p] = mask_beyond(r[p], j0 + 2 * p, limit);
+                        }
+                        m2 = __hmax2(m2, __hmax2(__hmax2(bits_h2(r[0]), bits_h2(r[1])), __hmax2(bits_h2(r[2]), bits_h2(r[3]))));
+                    }
+                }
+                mx = lanes_max<RL>(fmaxf(__low2float(m2), __high2float(m2)));
+                mx = __half2float(__float2half_rn(mx * a.scale));
+            } else {
+                for (int it = 0; it < iters; ++it) {
+                    const int blk = it * BPI + bl;
                     #pragma unroll
                     for (int k = 0; k < 4; ++k) {
                         uint32_t sv[4];
-                        if (blk * 16 + g + 4 * k >= cpr) continue;
-                        score_chunk(a, rin, rmask, blk * 16 + g + 4 * k, limit, sv);
+                        const int ci = blk * 16 + g + 4 * k;
+                        if (ci >= cpr) continue;
+                        score_chunk(a, rin, rmask, ci, limit, sv);
                         const __half2 m2 = __hmax2(__hmax2(bits_h2(sv[0]), bits_h2(sv[1])), __hmax2(bits_h2(sv[2]), bits_h2(sv[3])));
                         mx = fmaxf(mx, fmaxf(__low2float(m2), __high2float(m2)));
                     }
                 }
+                mx = lanes_max<RL>(mx);
             }
-            mx = warp_max(mx);
             float sum = 0.f;
             for (int it = 0; it < iters; ++it) {
-                const int blk = it * 8 + bl;
-                if (blk < a.nblk) {
+                const int blk = it * BPI + bl;
+                #pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    uint32_t sv[4];
+                    const int ci = blk * 16 + g + 4 * k;
+                    if (ci >= cpr || (int64_t)ci * 8 > limit) continue;      // masked keys add exp(-inf) = 0
+                    score_chunk(a, rin, rmask, ci, limit, sv);
                     #pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        uint32_t sv[4];
-                        if (blk * 16 + g + 4 * k >= cpr) continue;
-                        score_chunk(a, rin, rmask, blk * 16 + g + 4 * k, limit, sv);
-                        #pragma unroll
-                        for (int p = 0; p < 4; ++p) {
-                            const float2 f = __half22float2(bits_h2(sv[p]));
-                            sum += expf(f.x - mx); sum += expf(f.y - mx);
-                        }
+                    for (int p = 0; p < 4; ++p) {
+                        const float2 f = __half22float2(bits_h2(sv[p]));
+                        sum += expf(f.x - mx); sum += expf(f.y - mx);
                     }
                 }
             }
+            __syncwarp();
             stat0 = mx;
-            stat1 = warp_sum(sum);
+            stat1 = lanes_sum<RL>(sum);
         }
 
         // ---- second sweep: the fp16 values, block by block into the quantizer ----
+        int iters_w = iters;                                 // the quantizer's shuffles need the whole warp in every iteration
+        float rsum = 0.f;
+        if (PRO == ROW_SOFTMAX) {
+            iters_w = max(iters, __shfl_xor_sync(0xFFFFFFFFu, iters, 16));
+            rsum = __frcp_rn(stat1);
+        }
         for (int it = 0; it < iters_all; ++it) {
-            const int blk = it * 8 + bl;
-            const bool valid = blk < a.nblk;
-            if (PRO == ROW_SOFTMAX && it >= iters) {         // only masked keys: zeros (warp-uniform branch)
+            const int blk = it * BPI + bl;
+            const bool valid = blk < a.nblk && live;
+            if (PRO == ROW_SOFTMAX && it >= iters_w) {       // only masked keys: zeros (warp-uniform branch)
                 if (valid) {
                     #pragma unroll
                     for (int k = 0; k < 4; ++k)
@@ -651,7 +709,7 @@ __global__ void __launch_bounds__(ROW_THREADS, 2) hbq_row_kernel(const RowArgs a
                 const int ci = blk * 16 + g + 4 * k;
                 #pragma unroll
                 for (int p = 0; p < 4; ++p) xb[k][p] = 0u;
-                if (!valid || ci >= cpr) continue;
+                if (blk >= a.nblk || ci >= cpr) continue;
                 if (PRO == ROW_RMSNORM) {
                     // weight * fp16(x_f32 * rstd): the rounding points of transformers' LlamaRMSNorm on an fp16 tensor
                     const uint4 v = a.res ? rsrc[ci] : __ldg(rsrc + ci), wv = __ldg(a.w + ci);
@@ -662,12 +720,14 @@ __global__ void __launch_bounds__(ROW_THREADS, 2) hbq_row_kernel(const RowArgs a
                         xb[k][p] = h2_bits(__hmul2(bits_h2(ww[p]), __floats2half2_rn(f.x * stat0, f.y * stat0)));
                     }
                 } else {
+                    if ((int64_t)ci * 8 > limit) continue;   // masked keys: exp(-inf) / sum = 0
                     uint32_t sv[4];
                     score_chunk(a, rin, rmask, ci, limit, sv);
                     #pragma unroll
                     for (int p = 0; p < 4; ++p) {
                         const float2 f = __half22float2(bits_h2(sv[p]));
-                        xb[k][p] = h2_bits(__floats2half2_rn(__fdiv_rn(expf(f.x - stat0), stat1), __fdiv_rn(expf(f.y - stat0), stat1)));
+                        xb[k][p] = h2_bits(__floats2half2_rn(div_by_sum(expf(f.x - stat0), stat1, rsum),
+                                                             div_by_sum(expf(f.y - stat0), stat1, rsum)));
                     }
                 }
             }
@@ -788,7 +848,8 @@ static int launch_row(const RowArgs& a, bool quant, cudaStream_t stream)
     int sms = 0;
     { const int rc = device_sms(&sms); if (rc) return rc; }
     const size_t smem = quant ? (size_t)a.t.entries * 4 : 0;
-    const int64_t need = (a.rows + ROW_WARPS - 1) / ROW_WARPS;
+    const int64_t rows_per_cta = ROW_WARPS * (PRO == ROW_SOFTMAX ? 2 : 1);
+    const int64_t need = (a.rows + rows_per_cta - 1) / rows_per_cta;
     const int grid = (int)(need < 2ll * sms ? need : 2ll * sms);
     if (quant) {
         { const int rc = ensure_dynamic_smem(hbq_row_kernel<MB, ML, PRO, true>, smem); if (rc) return rc; }

@@ -266,3 +266,31 @@ def test_mixtral_layer_hbq_e():
     assert torch.isfinite(y).all() and H.gemm_status() == 0
     m.pieces = 2
     assert torch.equal(m(ids), y)
+
+
+def test_causal_prefill_in_query_runs_is_the_same_attention():
+    """Runs of 128 queries against the keys up to the run's end: the left-out keys are masked for every query of the
+    run, so the probabilities and their quantisation blocks are those of the whole-square evaluation; only the
+    library matmul's accumulation order over the keys may differ (fp32 accumulation, fp16 output)."""
+    m, _ = _build(_hbq_a_kv())
+    a = _arch()
+    ids = torch.randint(0, a.vocab, (2, 512), generator=torch.Generator().manual_seed(5)).cuda()
+    for layer in m.layers:
+        layer.self_attn.query_chunk = 1 << 30                  # whole square
+    whole = m(ids).float().cpu()
+    for layer in m.layers:
+        layer.self_attn.query_chunk = 128
+    runs = m(ids).float().cpu()
+    rel = _rel(runs, whole)
+    print(f"query runs of 128 vs whole square: rel_fro {rel:.3e}")
+    assert rel <= 2e-3, rel
+    # the attention block alone, before later quantizers amplify a last-bit difference: within fp16 rounding
+    at = m.layers[0].self_attn
+    x = torch.randn(2 * 512, a.hidden, device="cuda").half()
+    from hbq_b200.llama import rope_tables
+    cos, sin = rope_tables(512, a.head_dim, a.theta, x.device)
+    at.query_chunk = 1 << 30
+    y0 = at(x, 2, 512, cos, sin).float()
+    at.query_chunk = 128
+    y1 = at(x, 2, 512, cos, sin).float()
+    assert float((y1 - y0).norm() / y0.norm()) <= 2.0 ** -9
