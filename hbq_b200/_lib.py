@@ -22,7 +22,8 @@ GEMM_NOALLOC_MAX_ELEMS = 4 * 1024 * 1024      # HBQ_GEMM_NOALLOC_MAX_ELEMS
 EXPORTS = [
     "hbq_quantize", "hbq_absmax", "hbq_absmax_scratch_bytes", "hbq_dequantize", "hbq_fp_quant",
     "hbq_gemm", "hbq_gemm_workspace_bytes", "hbq_gemm_uses_tensor_cores", "hbq_gemm_simt",
-    "hbq_gemm_kn_noalloc", "hbq_kv_write_k", "hbq_kv_write_v", "hbq_swiglu_quantize", "hbq_rmsnorm_quantize", "hbq_softmax_quantize",
+    "hbq_gemm_kn_noalloc", "hbq_gemm_w4", "hbq_gemm_w4_prepack", "hbq_gemm_w4_prepacked_bytes",
+    "hbq_gemm_w4_workspace_bytes", "hbq_kv_write_k", "hbq_kv_write_v", "hbq_swiglu_quantize", "hbq_rmsnorm_quantize", "hbq_softmax_quantize",
     "hbq_gemm_status", "hbq_gemm_status_reset", "hbq_gemm_wait_selftest", "hbq_gemm_reserve_sms", "hbq_error_string", "hbq_last_cuda_error",
     "hbq_version", "hbq_launch_count",
 ]
@@ -76,6 +77,12 @@ def lib() -> ctypes.CDLL:
     L.hbq_gemm_workspace_bytes.argtypes = [i64, i64, i64, ci, ci, ci, ci]
     L.hbq_gemm_workspace_bytes.restype = i64
     L.hbq_gemm_uses_tensor_cores.argtypes = [i64, i64, i64, ci, ci, ci, ci]
+    L.hbq_gemm_w4_prepacked_bytes.argtypes = [i64, i64]
+    L.hbq_gemm_w4_prepacked_bytes.restype = i64
+    L.hbq_gemm_w4_prepack.argtypes = [ctypes.POINTER(PackedOut), i64, i64, ctypes.POINTER(Format), vp, vp]
+    L.hbq_gemm_w4_workspace_bytes.argtypes = [i64, i64, i64]
+    L.hbq_gemm_w4_workspace_bytes.restype = i64
+    L.hbq_gemm_w4.argtypes = [vp, vp, vp, i64, i64, i64, ctypes.POINTER(Format), vp, vp, i64, vp]
     L.hbq_gemm_status.argtypes = [ctypes.POINTER(ci)]
     L.hbq_gemm_wait_selftest.argtypes = [vp, vp, vp, i64, i64, i64, ci, ci, ci, ctypes.c_uint32, vp]
     L.hbq_gemm_reserve_sms.argtypes = [ci]

@@ -16,8 +16,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libhbq_b200.so")
-SOURCES = ["api.cu", "quantize.cu", "quantize_lut.cu", "quantize_tab.cu", "quantize_extra.cu", "gemm_simt.cu", "gemm_tc.cu", "gemm_static.cu"]
-HEADERS = [os.path.join(CSRC, "common.cuh"), os.path.join(CSRC, "quantize_dev.cuh"), os.path.join(CSRC, "vcache_dev.cuh"), os.path.join(CSRC, "quantize_tab.cuh"), os.path.join(HERE, "..", "include", "hbq_b200.h")]
+SOURCES = ["api.cu", "quantize.cu", "quantize_lut.cu", "quantize_tab.cu", "quantize_extra.cu", "gemm_simt.cu", "gemm_tc.cu", "gemm_packed.cu", "gemm_static.cu"]
+HEADERS = [os.path.join(CSRC, "common.cuh"), os.path.join(CSRC, "quantize_dev.cuh"), os.path.join(CSRC, "vcache_dev.cuh"), os.path.join(CSRC, "quantize_tab.cuh"), os.path.join(CSRC, "tc_dev.cuh"), os.path.join(HERE, "..", "include", "hbq_b200.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-shared", "--threads", "4"]
 

@@ -1,0 +1,444 @@
+// Decode-shape GEMM that reads the HBQ weight as packed 4-bit codes and scales (0.5625 B per weight instead of
+// the 2 B of the fp16 fake-quantised tensor) and expands them to fp16 in shared memory in front of the tensor core.
+//
+//   C[M,N] = X[M,K] * deq(Wp)[N,K]^T     M <= 128 tokens, fp32 accumulation, fp16 output
+//
+// For M this small the time of the fp16-operand kernel is the streaming of W from HBM.  The reference keeps W as an
+// fp16 tensor (src/ptq.py:349) and multiplies with F.linear (src/module.py:64); the values here are the same fp16
+// values, rebuilt per tile:  w = fp16(level(code) * t * s)  with level the E2M1 element value, t the micro-scale
+// candidate chosen for the element's micro-block and s the E5M3 block scale.  t * s is exact in fp16 (4 + 4
+// significant bits), level * t is exact as well, so one multiply by the per-micro-block product t*s rounds exactly
+// like the quantizer's fp16(fp16(level * t) * s).
+//
+// Operands are swapped with respect to gemm_tc.cu: the 128 weight rows of a tile are the M side of the MMA
+// (A operand, expanded here), the tokens its N side (B operand, X through TMA, zero filled beyond M), so the MMA's
+// cost follows the token count.  The accumulator D^T[n, m] sits in tensor memory, lane = weight row.
+//
+// Prepacked weight (hbq_gemm_w4_prepack): one 9216-byte record per (tile of 128 rows, block of 128 k) -- what one
+// pipeline stage consumes, fetched with ONE bulk async copy:
+//   [4 pieces][128 rows][16 B]   codes: piece q holds the 32 elements k = 32q..32q+31 of every row, element j of a
+//                                32-bit word in nibble j as {sign, e1, e0, m}; rows are contiguous so that a warp's
+//                                16-byte reads (one row per lane) hit every bank once
+//   [128 rows][8 B]              micro-scale indices (2 bits each, 32 bits), the block scale as fp16, the table bit
+//
+// One CTA per work unit (tile x K slice), 384 threads:
+//   warp 0      producer: bulk copy of the packed record + two TMA loads of X (128 k) per stage
+//   warp 1      MMA issue (one lane), owner of the tensor-memory allocation
+//   warps 4-11  expansion: thread (row r, half h) turns 64 codes into 8 swizzled 16-byte chunks of the K-major
+//               fp16 tile; afterwards warps 4-7 drain the accumulator
+// K slices of one tile meet in an fp32 workspace; the CTA that arrives last adds the slices in slice order
+// (deterministic) and writes C.  Every mbarrier wait is bounded as in gemm_tc.cu.
+#include "tc_dev.cuh"
+#include <math.h>
+#include <mutex>
+
+namespace hbq {
+
+int gemm_make_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t K, int box_rows);   // gemm_tc.cu
+
+constexpr int PK_ROWS = 128;                                  // weight rows per tile
+constexpr int PK_KB = 128;                                    // k per stage: one quantisation block
+constexpr int PK_CODE_BYTES = PK_ROWS * PK_KB / 2;            // 8192
+constexpr int PK_SIDE_BYTES = PK_ROWS * 8;                    // 1024
+constexpr int PK_REC_BYTES = PK_CODE_BYTES + PK_SIDE_BYTES;   // 9216
+constexpr int PK_EXP_BYTES = 2 * PK_ROWS * 128;               // two K-major 128 x 64 fp16 tiles
+constexpr int PK_NE = 3;                                      // expanded stages
+constexpr int PK_NL_MAX = 6;                                  // load stages (fewer when X tiles are large)
+constexpr int PK_EXP_WARPS = 8;
+constexpr int PK_THREADS = 128 + PK_EXP_WARPS * 32;
+constexpr int PK_CTRL_BYTES = 256;
+
+struct PkArgs {
+    const uint8_t* wp;          // prepacked weight [tiles][nblk][PK_REC_BYTES]
+    __half* C;
+    const __half* bias;
+    float* ws;                  // [slices][m_pad][N] partial sums (slices > 1)
+    int* counters;              // [tiles], zero between calls
+    int M, N, K;
+    int m_pad;                  // tokens rounded up to 16: the MMA's N
+    int nblk, tiles, slices, nl;
+    int micro_shift;            // log2(chunks of 8 per micro-block): 0 or 2
+    uint32_t base2[2], step2[2];// micro-scale t = base + idx * step as packed fp16 pairs, per table
+    uint32_t tmem_cols;
+    uint32_t poll_limit;
+};
+
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel)
+{
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+
+// Eight E2M1 codes (nibbles {sign, e1, e0, m} of w) times the packed scale ts2 -> four fp16 pairs.
+// Top bytes of the element values 0, .5, 1, 1.5, 2, 3, 4, 6 come from a byte lookup (their low bytes are zero), the
+// signs from the nibbles' top bits replicated into byte masks.
+__device__ __forceinline__ void expand8(uint32_t w, uint32_t ts2, bool two_step, uint32_t t2, uint32_t s2, uint32_t* o)
+{
+    constexpr uint32_t LUT0 = 0x3E3C3800u, LUT1 = 0x46444240u;
+    const uint32_t w7 = w & 0x77777777u, wl = w << 4;
+    uint32_t plo = prmt(LUT0, LUT1, w7), phi = prmt(LUT0, LUT1, w7 >> 16);
+    const uint32_t mlo = prmt(w, wl, 0x9D8Cu), mhi = prmt(w, wl, 0xBFAEu);
+    plo |= mlo & 0x80808080u;
+    phi |= mhi & 0x80808080u;
+    const uint32_t v[4] = {prmt(plo, 0u, 0x1404u), prmt(plo, 0u, 0x3424u), prmt(phi, 0u, 0x1404u), prmt(phi, 0u, 0x3424u)};
+    #pragma unroll
+    for (int p = 0; p < 4; ++p)
+        o[p] = two_step ? h2_bits(__hmul2(__hmul2(bits_h2(v[p]), bits_h2(t2)), bits_h2(s2)))
+                        : h2_bits(__hmul2(bits_h2(v[p]), bits_h2(ts2)));
+}
+
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+__global__ void __launch_bounds__(PK_THREADS, 1)
+gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const PkArgs a)
+{
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t exp0 = (raw + 1023u) & ~1023u;                    // expanded tiles (1024-byte aligned for the swizzle)
+    const uint32_t LS = PK_REC_BYTES + (uint32_t)a.m_pad * 256u;     // load stage: packed record + two X tiles
+    const uint32_t ld0 = exp0 + PK_NE * PK_EXP_BYTES;
+    const uint32_t ctrl_u = ld0 + (uint32_t)a.nl * LS;
+    uint8_t* ctrl = smem_raw + (ctrl_u - raw);
+    // control block: ld_full[6] ld_empty[6] ex_full[3] ex_empty[3] acc_full (8 B each), tensor-memory base,
+    // abort flag, "this CTA adds the slices" flag
+    const uint32_t bar_lfull = ctrl_u, bar_lempty = ctrl_u + 8 * PK_NL_MAX;
+    const uint32_t bar_efull = ctrl_u + 16 * PK_NL_MAX, bar_eempty = bar_efull + 8 * PK_NE;
+    const uint32_t bar_acc = bar_eempty + 8 * PK_NE;
+    uint32_t* tmem_base_smem = reinterpret_cast<uint32_t*>(ctrl + 16 * PK_NL_MAX + 16 * PK_NE + 16);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(ctrl + 16 * PK_NL_MAX + 16 * PK_NE + 24);
+    volatile int* last_flag = reinterpret_cast<volatile int*>(ctrl + 16 * PK_NL_MAX + 16 * PK_NE + 28);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile = blockIdx.x / a.slices, slice = blockIdx.x % a.slices;
+    const int kb0 = (int)(((int64_t)a.nblk * slice) / a.slices), kb1 = (int)(((int64_t)a.nblk * (slice + 1)) / a.slices);
+    const int nst = kb1 - kb0;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < PK_NL_MAX; ++s) { mbar_init(bar_lfull + 8 * s, 1); mbar_init(bar_lempty + 8 * s, 1 + PK_EXP_WARPS); }
+        for (int s = 0; s < PK_NE; ++s) { mbar_init(bar_efull + 8 * s, PK_EXP_WARPS); mbar_init(bar_eempty + 8 * s, 1); }
+        mbar_init(bar_acc, 1);
+        *abort_flag = 0;
+        *last_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_base_smem)), "r"(a.tmem_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_base_smem;
+
+    if (warp == 0) {
+        // ================= producer =================
+        if (lane == 0) {
+            const uint8_t* src = a.wp + ((int64_t)tile * a.nblk + kb0) * PK_REC_BYTES;
+            uint32_t stage = 0, phase = 0;
+            for (int i = 0; i < nst; ++i) {
+                if (!mbar_wait(bar_lempty + 8 * stage, phase ^ 1u, abort_flag, 1, a.poll_limit)) break;
+                const uint32_t dst = ld0 + stage * LS, bar = bar_lfull + 8 * stage;
+                mbar_expect_tx(bar, LS);
+                bulk_load(dst, src + (int64_t)i * PK_REC_BYTES, PK_REC_BYTES, bar);
+                tma_load_2d(dst + PK_REC_BYTES, &mapX, (kb0 + i) * PK_KB, 0, bar);
+                tma_load_2d(dst + PK_REC_BYTES + (uint32_t)a.m_pad * 128u, &mapX, (kb0 + i) * PK_KB + 64, 0, bar);
+                if (++stage == (uint32_t)a.nl) { stage = 0; phase ^= 1u; }
+            }
+        }
+    } else if (warp == 1) {
+        // ================= MMA issue =================
+        // kind::f16: D fp32, A/B fp16, both K-major, M = 128 weight rows, N = m_pad tokens
+        const uint32_t idesc = (1u << 4) | ((uint32_t)(a.m_pad >> 3) << 17) | ((uint32_t)(PK_ROWS >> 4) << 24);
+        const bool leader = elect_one();
+        uint32_t ls = 0, lph = 0, es = 0, eph = 0;
+        for (int i = 0; i < nst; ++i) {
+            if (!mbar_wait_warp(bar_lfull + 8 * ls, lph, abort_flag, 2, a.poll_limit)) break;       // X tiles landed
+            if (!mbar_wait_warp(bar_efull + 8 * es, eph, abort_flag, 3, a.poll_limit)) break;       // weights expanded
+            tc_fence_after();
+            if (leader) {
+                const uint32_t wa = exp0 + es * PK_EXP_BYTES, xa = ld0 + ls * LS + PK_REC_BYTES;
+                #pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    #pragma unroll
+                    for (int kk = 0; kk < 4; ++kk)
+                        tc_mma_f16(tmem_base, umma_desc(wa + h * (PK_ROWS * 128) + kk * 32),
+                                   umma_desc(xa + h * ((uint32_t)a.m_pad * 128u) + kk * 32), idesc, (i | h | kk) != 0 ? 1u : 0u);
+                }
+                tc_commit(bar_eempty + 8 * es);
+                tc_commit(bar_lempty + 8 * ls);
+                if (i + 1 == nst) tc_commit(bar_acc);
+            }
+            __syncwarp();
+            if (++ls == (uint32_t)a.nl) { ls = 0; lph ^= 1u; }
+            if (++es == PK_NE) { es = 0; eph ^= 1u; }
+        }
+    } else if (warp >= 4) {
+        // ================= expansion =================
+        const int te = threadIdx.x - 128;
+        const int r = te & (PK_ROWS - 1), h = te >> 7;
+        const uint32_t swz = (uint32_t)(r & 7);
+        uint32_t ls = 0, lph = 0, es = 0, eph = 0;
+        bool ok = true;
+        for (int i = 0; i < nst; ++i) {
+            if (!(ok = mbar_wait_warp(bar_lfull + 8 * ls, lph, abort_flag, 4, a.poll_limit))) break;
+            if (!(ok = mbar_wait_warp(bar_eempty + 8 * es, eph ^ 1u, abort_flag, 5, a.poll_limit))) break;
+            const uint32_t rec = ld0 + ls * LS;
+            uint32_t l2w, meta;
+            asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(l2w), "=r"(meta) : "r"(rec + PK_CODE_BYTES + r * 8));
+            uint32_t cw[8];
+            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(cw[0]), "=r"(cw[1]), "=r"(cw[2]), "=r"(cw[3]) : "r"(rec + ((2 * h) * PK_ROWS + r) * 16));
+            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(cw[4]), "=r"(cw[5]), "=r"(cw[6]), "=r"(cw[7]) : "r"(rec + ((2 * h + 1) * PK_ROWS + r) * 16));
+            const uint32_t sc = meta & 0xFFFFu, s2 = sc * 0x10001u, tb = (meta >> 16) & 1u;
+            const uint32_t base2 = tb ? a.base2[1] : a.base2[0], step2 = tb ? a.step2[1] : a.step2[0];
+            // a scale in fp16's top binade could overflow t*s where (level*t)*s stays finite: multiply in two steps there
+            const bool two_step = sc >= 0x7800u;
+            const uint32_t out = exp0 + es * PK_EXP_BYTES + h * (PK_ROWS * 128) + r * 128;
+            #pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                const uint32_t idx = (l2w >> (2 * ((8 * h + c) >> a.micro_shift))) & 3u;
+                const uint32_t t2 = base2 + idx * step2;
+                const uint32_t ts2 = h2_bits(__hmul2(bits_h2(t2), bits_h2(s2)));
+                uint32_t o[4];
+                expand8(cw[c], ts2, two_step, t2, s2, o);
+                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};"
+                             ::"r"(out + (((uint32_t)c ^ swz) << 4)), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
+            }
+            // the tensor core reads shared memory through the async proxy: order these generic-proxy stores before it
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) { mbar_arrive(bar_efull + 8 * es); mbar_arrive(bar_lempty + 8 * ls); }
+            if (++ls == (uint32_t)a.nl) { ls = 0; lph ^= 1u; }
+            if (++es == PK_NE) { es = 0; eph ^= 1u; }
+        }
+        // ================= epilogue (warps 4-7: one per quarter of the tensor-memory lanes) =================
+        if (warp < 8) {
+            ok = ok && mbar_wait(bar_acc, 0u, abort_flag, 6, a.poll_limit);
+            ok = __all_sync(0xFFFFFFFFu, ok);
+            const int quarter = warp & 3;
+            const int gn = tile * PK_ROWS + quarter * 32 + lane;             // this thread's output column
+            if (ok) {
+                tc_fence_after();
+                for (int c0 = 0; c0 < a.m_pad; c0 += 32) {
+                    float v[32];
+                    tc_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + c0, v);
+                    #pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int m = c0 + j;
+                        if (m >= a.M) break;
+                        if (a.slices == 1) {
+                            __half o = __float2half_rn(v[j]);
+                            if (a.bias) o = __hadd(o, a.bias[gn]);
+                            a.C[(int64_t)m * a.N + gn] = o;
+                        } else {
+                            a.ws[((int64_t)slice * a.m_pad + m) * a.N + gn] = v[j];
+                        }
+                    }
+                }
+            }
+            if (a.slices > 1) {
+                __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (te == 0) *last_flag = ok && (atomicAdd(a.counters + tile, 1) == a.slices - 1);
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (*last_flag) {
+                    __threadfence();
+                    for (int m = 0; m < a.M; ++m) {
+                        float acc = 0.f;
+                        for (int s = 0; s < a.slices; ++s) acc += __ldcg(a.ws + ((int64_t)s * a.m_pad + m) * a.N + gn);
+                        __half o = __float2half_rn(acc);
+                        if (a.bias) o = __hadd(o, a.bias[gn]);
+                        a.C[(int64_t)m * a.N + gn] = o;
+                    }
+                    if (te == 0) a.counters[tile] = 0;
+                }
+            }
+        }
+    }
+
+    // ---- teardown: every role arrives here, also after an expired wait ----
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        const unsigned long long t0 = gtime_ns();
+        while (gtime_ns() - t0 < 200000ull) { }          // copies that may still be in flight land before smem is released
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(a.tmem_cols) : "memory");
+    }
+}
+
+// ---- prepack: the planes of hbq_quantize -> the per-(tile, block) records above --------------------------
+struct PrepackArgs {
+    const uint8_t* codes;       // [N, K/2]
+    const uint8_t* scale_u8;    // [N, nblk]
+    const uint8_t* l2;          // [N, nblk, l2_bytes]
+    const uint8_t* scheme;      // [N, nblk] or NULL
+    uint4* out;
+    int64_t total;              // 16-byte slots of the output
+    int K, nblk, l2_bytes;
+};
+
+__global__ void __launch_bounds__(256) gemm_w4_prepack_kernel(const PrepackArgs a)
+{
+    constexpr int SLOTS = PK_REC_BYTES / 16;                  // 576 per record: 512 of codes, 64 of side records
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= a.total) return;
+    const int slot = (int)(i % SLOTS);
+    const int64_t rec = i / SLOTS;
+    const int kb = (int)(rec % a.nblk);
+    const int64_t tile = rec / a.nblk;
+    if (slot < 512) {
+        const int q = slot >> 7, r = slot & 127;
+        a.out[i] = *reinterpret_cast<const uint4*>(a.codes + (tile * PK_ROWS + r) * (int64_t)(a.K / 2) + kb * 64 + q * 16);
+    } else {
+        uint32_t w[4];
+        #pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const int64_t blk = (tile * PK_ROWS + (slot - 512) * 2 + j) * a.nblk + kb;
+            uint32_t l2w = 0;
+            for (int b = 0; b < a.l2_bytes; ++b) l2w |= (uint32_t)a.l2[blk * a.l2_bytes + b] << (8 * b);
+            w[2 * j] = l2w;
+            w[2 * j + 1] = ((uint32_t)a.scale_u8[blk] << 7) | ((a.scheme ? (uint32_t)(a.scheme[blk] & 1u) : 0u) << 16);
+        }
+        a.out[i] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+}
+
+// ---- host side ---------------------------------------------------------------------------------------
+// Formats the kernel expands: HBQ weights with E2M1 elements, an E5M3 scale per 128 and 2-bit micro-scales per 8 or 32
+// whose candidates are base + idx * step in fp16 (the "Mix" pair and its members; not SIG-1 / INT / POT).
+static bool w4_format(const hbq_format* f, PkArgs* a)
+{
+    if (!f || f->kind != HBQ_KIND_HBQ || f->ebit != 2 || f->mbit != 1 || f->block_size != 128 || f->sc_ebit != 5 ||
+        f->sc_mbit != 3 || f->l2_sc_bit != 2 || (f->l2_block_size != 8 && f->l2_block_size != 32))
+        return false;
+    uint32_t base[2] = {0x3C00u, 0x3C00u}, step[2] = {0x0100u, 0x0100u};
+    switch (f->l2_scheme) {
+        case HBQ_L2_FPM1: break;
+        case HBQ_L2_FP1: base[0] = 0x3D00u; break;
+        case HBQ_L2_FPM10: step[0] = 0x0080u; break;
+        case HBQ_L2_FPM100: step[0] = 0x0040u; break;
+        case HBQ_L2_MIX: step[1] = 0x0080u; break;
+        default: return false;
+    }
+    if (a) {
+        for (int i = 0; i < 2; ++i) { a->base2[i] = base[i] * 0x10001u; a->step2[i] = step[i] * 0x10001u; }
+        a->micro_shift = f->l2_block_size == 8 ? 0 : 2;
+    }
+    return true;
+}
+
+static bool w4_shape(int64_t M, int64_t N, int64_t K)
+{
+    return M >= 1 && M <= 128 && N >= PK_ROWS && (N % PK_ROWS) == 0 && K >= PK_KB && (K % PK_KB) == 0 &&
+           N <= (1ll << 24) && K <= (1ll << 24);
+}
+
+// K slices per tile: the count that leaves the fewest SM-rounds per unit of work, with a small charge per slice
+// for its share of the partial-sum traffic and the launch of more CTAs.
+static int w4_slices(int64_t tiles, int64_t nblk, int sms)
+{
+    int best = 1;
+    double best_cost = 1e30;
+    for (int s = 1; s <= 16 && s <= nblk; ++s) {
+        const double rounds = (double)((tiles * s + sms - 1) / sms);
+        const double cost = rounds / s + 0.02 * s;
+        if (cost < best_cost - 1e-9) { best_cost = cost; best = s; }
+    }
+    return best;
+}
+
+int64_t gemm_w4_prepacked_bytes(int64_t N, int64_t K)
+{
+    if (N <= 0 || K <= 0 || (N % PK_ROWS) || (K % PK_KB)) return -1;
+    return (N / PK_ROWS) * (K / PK_KB) * (int64_t)PK_REC_BYTES;
+}
+
+int gemm_w4_prepack(const hbq_packed_out* in, int64_t N, int64_t K, const hbq_format* f, void* out, cudaStream_t stream)
+{
+    if (!in || !out || !in->codes || !in->scale_u8 || !in->l2_packed) return HBQ_ERR_ARG;
+    if (!w4_format(f, nullptr) || !w4_shape(1, N, K)) return HBQ_ERR_UNSUPPORTED;
+    if (f->l2_scheme == HBQ_L2_MIX && !in->scheme) return HBQ_ERR_ARG;
+    if ((reinterpret_cast<uintptr_t>(in->codes) | reinterpret_cast<uintptr_t>(out)) & 15) return HBQ_ERR_ALIGN;
+    PrepackArgs a;
+    a.codes = in->codes; a.scale_u8 = in->scale_u8; a.l2 = in->l2_packed;
+    a.scheme = f->l2_scheme == HBQ_L2_MIX ? in->scheme : nullptr;
+    a.out = (uint4*)out;
+    a.K = (int)K; a.nblk = (int)(K / PK_KB); a.l2_bytes = (128 / f->l2_block_size) * 2 / 8;
+    a.total = gemm_w4_prepacked_bytes(N, K) / 16;
+    gemm_w4_prepack_kernel<<<(unsigned)((a.total + 255) / 256), 256, 0, stream>>>(a);
+    HBQ_LAUNCH_CHECK("gemm_w4_prepack_kernel");
+    return HBQ_OK;
+}
+
+int64_t gemm_w4_workspace_bytes(int64_t M, int64_t N, int64_t K)
+{
+    if (!w4_shape(M, N, K)) return -1;
+    int sms = 0;
+    if (device_sms(&sms) != HBQ_OK) return -1;
+    const int64_t tiles = N / PK_ROWS, m_pad = (M + 15) / 16 * 16;
+    const int s = w4_slices(tiles, K / PK_KB, sms);
+    return (s > 1 ? (int64_t)s * m_pad * N * 4 : 0) + tiles * 4;
+}
+
+// workspace: gemm_w4_workspace_bytes() bytes, 16-byte aligned, zeroed once by the caller (the kernel leaves the tile
+// counters at zero again); one call at a time per workspace.
+int gemm_w4_launch(const void* X, const void* Wp, void* C, int64_t M, int64_t N, int64_t K, const hbq_format* f,
+                   const void* bias, void* workspace, cudaStream_t stream, uint32_t poll_limit)
+{
+    PkArgs a;
+    memset(&a, 0, sizeof(a));
+    if (!X || !Wp || !C || !workspace) return HBQ_ERR_ARG;
+    if (!w4_format(f, &a) || !w4_shape(M, N, K)) return HBQ_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(Wp) | reinterpret_cast<uintptr_t>(workspace)) & 15)
+        return HBQ_ERR_ALIGN;
+    if ((reinterpret_cast<uintptr_t>(C) | reinterpret_cast<uintptr_t>(bias)) & 1) return HBQ_ERR_ALIGN;
+    int sms = 0;
+    { const int rc = device_sms(&sms); if (rc) return rc; }
+    a.wp = (const uint8_t*)Wp; a.C = (__half*)C; a.bias = (const __half*)bias;
+    a.M = (int)M; a.N = (int)N; a.K = (int)K;
+    a.m_pad = (int)((M + 15) / 16 * 16);
+    a.nblk = (int)(K / PK_KB); a.tiles = (int)(N / PK_ROWS);
+    a.slices = w4_slices(a.tiles, a.nblk, sms);
+    const int64_t part = a.slices > 1 ? (int64_t)a.slices * a.m_pad * N * 4 : 0;
+    a.ws = (float*)workspace;
+    a.counters = (int*)((uint8_t*)workspace + part);
+    const uint32_t LS = PK_REC_BYTES + (uint32_t)a.m_pad * 256u;
+    const uint32_t avail = 227u * 1024u - 1024u - PK_NE * PK_EXP_BYTES - PK_CTRL_BYTES;
+    a.nl = (int)(avail / LS);
+    if (a.nl > PK_NL_MAX) a.nl = PK_NL_MAX;
+    if (a.nl < 2) return HBQ_ERR_UNSUPPORTED;
+    a.tmem_cols = a.m_pad <= 32 ? 32u : (a.m_pad <= 64 ? 64u : 128u);
+    a.poll_limit = poll_limit ? poll_limit : (1u << 23);
+    CUtensorMap mx;
+    { const int rc = gemm_make_map(&mx, X, M, K, a.m_pad); if (rc) return rc; }
+    const size_t smem = 1024 + PK_NE * PK_EXP_BYTES + (size_t)a.nl * LS + PK_CTRL_BYTES;
+    { const int rc = ensure_dynamic_smem(gemm_packed_kernel, smem); if (rc) return rc; }
+    gemm_packed_kernel<<<a.tiles * a.slices, PK_THREADS, smem, stream>>>(mx, a);
+    HBQ_LAUNCH_CHECK("gemm_packed_kernel");
+    return HBQ_OK;
+}
+
+int gemm_w4_status(int* host_out)
+{
+    HBQ_CUDA_TRY(cudaMemcpyFromSymbol(host_out, g_tc_status, sizeof(int)));
+    return HBQ_OK;
+}
+int gemm_w4_status_reset()
+{
+    const int z = 0;
+    HBQ_CUDA_TRY(cudaMemcpyToSymbol(g_tc_status, &z, sizeof(int)));
+    return HBQ_OK;
+}
+
+}  // namespace hbq

@@ -234,6 +234,36 @@ int hbq_gemm_status_reset(void);
 int hbq_gemm_wait_selftest(const void* A, const void* W, void* C, int64_t M, int64_t N, int64_t K,
                            int mode, int group_k, int group_n, uint32_t poll_limit, void* stream);
 
+/* ---- GEMM on the packed weight (decode shapes) ---------------------------------------------- */
+
+/* C[M,N] = X[M,K] * deq(W)[N,K]^T for M <= 128 tokens, reading W as packed 4-bit codes, block scales and
+ * micro-scale indices (0.5625 B per weight) and expanding it to the fp16 fake-quantised values in shared memory
+ * in front of the tensor core; fp32 accumulation, fp16 output, bias as in hbq_gemm.  Replaces, for a statically
+ * quantised HBQ weight (src/ptq.py:349, the fp16 tensor the reference keeps) under fp32 accumulation, the
+ * F.linear of _QBaseLinear.forward (src/module.py:64) at decode-sized batches, where the time is the streaming
+ * of W: the products are those of the fp16 tensor (each expanded value equals hbq_dequantize's bit for bit).
+ *
+ * Served: HBQ weights with E2M1 elements, block 128 with an E5M3 scale, 2-bit micro-scales per 8 or 32 with the
+ * FPM1 / FP1 / FPM10 / FPM100 / Mix tables (every shipped HBQ weight format); N and K multiples of 128;
+ * 1 <= M <= 128.  HBQ_ERR_UNSUPPORTED otherwise (callers then use hbq_gemm on the fp16 tensor).
+ *
+ * hbq_gemm_w4_prepack turns the planes of hbq_quantize (codes, scale_u8, l2_packed, scheme; W is [N, K]) into the
+ * kernel's operand, hbq_gemm_w4_prepacked_bytes(N, K) bytes, 16-byte aligned: one 9216-byte record per (128 rows,
+ * 128 k) -- four 32-element pieces of every row's codes with the rows contiguous, then per row the 32 bits of
+ * micro-scale indices, the block scale as fp16 and the table bit.  Done once per weight.
+ *
+ * workspace: hbq_gemm_w4_workspace_bytes(M, N, K) bytes (-1: shape not served), 16-byte aligned, ZEROED ONCE by
+ * the caller before its first use; the kernel returns it zeroed where that matters, so it can be reused by later
+ * calls on the same stream.  It holds the fp32 partial sums of the K slices a tile is cut into when N alone does
+ * not fill the SMs (the slices are added in slice order: results do not vary from run to run) and one counter per
+ * tile.  After a call that hbq_gemm_status reports as failed, zero it again. */
+int64_t hbq_gemm_w4_prepacked_bytes(int64_t N, int64_t K);
+int hbq_gemm_w4_prepack(const hbq_packed_out* in, int64_t N, int64_t K, const hbq_format* fmt, void* out,
+                        void* stream);
+int64_t hbq_gemm_w4_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int hbq_gemm_w4(const void* X, const void* Wp, void* C, int64_t M, int64_t N, int64_t K,
+                const hbq_format* fmt, const void* bias, void* workspace, int64_t workspace_bytes, void* stream);
+
 /* The tensor-core kernel is persistent: one CTA per SM, each holding most of an SM's shared
  * memory, with a fixed round-robin share of the tiles.  A kernel of another stream that already
  * sits on some SMs (a collective running under the GEMM) keeps those CTAs from starting until it

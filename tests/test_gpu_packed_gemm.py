@@ -1,0 +1,110 @@
+"""GPU: the GEMM on the packed 4-bit weight (hbq_gemm_w4) against the same product on the fp16 fake-quantised tensor
+the reference keeps (src/ptq.py:349, F.linear in src/module.py:64).
+
+Two bars.  (1) The values the kernel expands in shared memory are the fake-quantised weights BIT FOR BIT: one-hot rows
+of X make every output a single product 1 * w, so C spells out the expanded tile.  (2) With real activations the
+result is the fp32-accumulated product rounded to fp16: relative Frobenius error <= 2^-9 against an fp64 product of
+the same fp16 operands and at most 1 % of the outputs further than 2 fp16 ulps from it (the bound of the fp16-operand
+tensor-core kernel); K slices are added in a fixed order, so two runs give the same bits."""
+import pytest
+
+from util import load_formats, make_quantizer
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+REL_TOL = 2.0 ** -9
+FAR_ULP_FRACTION = 0.01
+
+
+def _weight(name, N, K, seed):
+    import hbq_b200 as H
+    from hbq_b200.packed_gemm import W4Weight
+    q = make_quantizer(load_formats()[name])
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    w = (0.02 * torch.randn((N, K), device="cuda", generator=g)).half()
+    w[:, ::97] *= 8                                       # a few large columns: more than one scale binade per row
+    packed, deq = q.quantize_packed(w, with_deq=True)
+    assert W4Weight.supported(packed)
+    assert torch.equal(H.dequantize_packed(packed).view(torch.int16), deq.view(torch.int16))
+    return W4Weight.from_packed(packed), deq
+
+
+def _ulps(a, b):
+    ia, ib = a.view(torch.int16).to(torch.int32), b.view(torch.int16).to(torch.int32)
+    ia = torch.where(ia < 0, -(ia & 0x7FFF), ia)
+    ib = torch.where(ib < 0, -(ib & 0x7FFF), ib)
+    return (ia - ib).abs()
+
+
+@pytest.mark.parametrize("name", ["hbq_a_wgt", "hbq_e_wgt", "hbq_fp1", "hbq_fpm100"])
+@pytest.mark.parametrize("shape", [(256, 512), (1024, 4096)])
+def test_expanded_values_are_the_fake_quantised_weights(name, shape):
+    spec = load_formats()[name]
+    if spec["mbit"] != 1 or spec["block_size"] != 128 or spec["l2_block_size"] not in (8, 32) or spec["l2_sc_bit"] != 2:
+        pytest.skip("not a 4-bit block-128 weight format")
+    N, K = shape
+    w4, deq = _weight(name, N, K, seed=N + K)
+    assert w4.nbytes() == N * K * 9216 // (128 * 128)
+    for rows in (128, 16, 5):
+        for off in range(0, K, 128 if K <= 512 else 1024):
+            x = torch.zeros((rows, K), device="cuda", dtype=torch.float16)
+            cols = (off + torch.arange(rows, device="cuda") * 7) % K
+            x[torch.arange(rows, device="cuda"), cols] = 1.0
+            c = w4.matmul(x)
+            want = deq[:, cols].t().contiguous()
+            # -0 * 1 accumulated into +0 reads +0: compare values, then the bits of everything non-zero
+            nz = want != 0
+            assert torch.equal(c[nz].view(torch.int16), want[nz].view(torch.int16)), (name, rows, off)
+            assert bool((c[~nz] == 0).all())
+
+
+@pytest.mark.parametrize("name", ["hbq_a_wgt", "hbq_e_wgt"])
+@pytest.mark.parametrize("N,K", [(14336, 4096), (4096, 14336), (1024, 4096), (128, 128)])
+def test_against_the_fp16_operand_product(name, N, K):
+    import hbq_b200 as H
+    from hbq_b200 import blockquant_ext as ext
+    w4, deq = _weight(name, N, K, seed=1)
+    aq = make_quantizer(load_formats()["hbq_a_act" if name == "hbq_a_wgt" else "hbq_e_act"])
+    g = torch.Generator(device="cuda").manual_seed(N)
+    bias = torch.randn(N, device="cuda", generator=g).half()
+    for M in (1, 7, 16, 33, 64, 128):
+        x = aq.q(torch.randn((M, K), device="cuda", generator=g).half())
+        for b in (None, bias):
+            c = w4.matmul(x, bias=b)
+            assert H.gemm_status() == 0
+            ref = x.double() @ deq.double().t()
+            ref16 = ref.float().half()
+            if b is not None:
+                ref16 = ref16 + b
+                ref = ref16.double()
+            rel = float((c.double() - ref).norm() / ref.norm())
+            far = float((_ulps(c, ref16 if b is not None else ref.float().half()) > 2).float().mean())
+            assert rel <= REL_TOL and far <= FAR_ULP_FRACTION, (M, rel, far)
+            # the same call again: slices are added in a fixed order
+            assert torch.equal(w4.matmul(x, bias=b), c)
+        # and the tensor-core kernel on the fp16 tensor agrees to the same bound
+        c16 = ext.gemm_fp32_accum(x, deq, b_is_nk=True)
+        assert float((w4.matmul(x).double() - c16.double()).norm() / c16.double().norm()) <= REL_TOL
+
+
+def test_shapes_and_formats_outside_the_kernel_are_refused():
+    import hbq_b200 as H
+    from hbq_b200 import _lib
+    from hbq_b200.packed_gemm import W4Weight
+    w4, _ = _weight("hbq_a_wgt", 256, 256, seed=2)
+    with pytest.raises(_lib.HbqError):
+        w4.matmul(torch.zeros((129, 256), device="cuda", dtype=torch.float16))
+    with pytest.raises(RuntimeError):
+        w4.matmul(torch.zeros((4, 128), device="cuda", dtype=torch.float16))
+    fm = load_formats()
+    for name, shape in (("hbq_a_act", (256, 256)), ("hbq_a_wgt", (200, 256)), ("mxfp4", (256, 256))):
+        q = make_quantizer(fm[name])
+        packed = q.quantize_packed(torch.randn(shape, device="cuda").half())
+        assert not W4Weight.supported(packed), name
+    # a 4-bit HBQ weight whose micro-scale table is not base + idx * step (SIG-1): the library refuses it
+    spec = dict(fm["hbq_a_wgt"], l2_scheme="SIG-1")
+    packed = make_quantizer(spec).quantize_packed(torch.randn((256, 256), device="cuda").half())
+    with pytest.raises(_lib.HbqError):
+        W4Weight.from_packed(packed)
+    assert H.gemm_status() == 0
