@@ -21,13 +21,24 @@
 //                                16-byte reads (one row per lane) hit every bank once
 //   [128 rows][8 B]              micro-scale indices (2 bits each, 32 bits), the block scale as fp16, the table bit
 //
-// One CTA per work unit (tile x K slice), 384 threads:
-//   warp 0      producer: bulk copy of the packed record + two TMA loads of X (128 k) per stage
-//   warp 1      MMA issue (one lane), owner of the tensor-memory allocation
-//   warps 4-11  expansion: thread (row r, half h) turns 64 codes into 8 swizzled 16-byte chunks of the K-major
-//               fp16 tile; afterwards warps 4-7 drain the accumulator
-// K slices of one tile meet in an fp32 workspace; the CTA that arrives last adds the slices in slice order
-// (deterministic) and writes C.  Every mbarrier wait is bounded as in gemm_tc.cu.
+// Work split: the (tile, block) records form one sequence of tiles * K/128 stages; CTA c of G (one per SM) takes the
+// c-th of G equal runs of it, whatever tile boundaries fall inside ("stream-K"), so every SM streams the same number
+// of bytes.  A run is a sequence of segments (tile, blocks kb0..kb1); a segment that covers its tile's whole K goes
+// straight to C, the others leave fp32 partial sums in a workspace and the CTA that completes a tile adds its
+// segments in CTA order (deterministic) and writes C.
+//
+// 768 threads:
+//   warps 0-3   epilogue: one per quarter of the tensor-memory lanes; two accumulators alternate between segments
+//   warp 4      record producer: one bulk copy of a packed record per stage, six stages ahead
+//   warp 5      MMA issue (one lane), owner of the tensor-memory allocation
+//   warp 6      X producer: two TMA loads (128 k of every token) into the operand stage the expansion is filling
+//   warps 8-23  expansion, two groups of eight warps on alternate stages: thread (row r, half hh) turns 64 codes into
+//               the 8 swizzled 16-byte chunks of its row in one of the stage's two K-major 128 x 64 tiles
+// What bounds a stage (measured with per-role cycle stamps): the MMA thread's serial chain -- about 90 cycles per
+// issued MMA whatever its width, eight per stage -- and the expansion's ~25 half-rate instructions per 8 codes; so
+// the MMA thread waits on ONE barrier per stage (completed by the expansion warps' arrivals and the X tiles' bytes
+// together) and commits once, and the expansion warps issue the barrier tests of their next stage before the
+// arithmetic of the current one, because a test costs hundreds of cycles of latency even when it succeeds.
 #include "tc_dev.cuh"
 #include <math.h>
 #include <mutex>
@@ -44,22 +55,24 @@ constexpr int PK_REC_BYTES = PK_CODE_BYTES + PK_SIDE_BYTES;   // 9216
 constexpr int PK_EXP_BYTES = 2 * PK_ROWS * 128;               // two K-major 128 x 64 fp16 tiles
 constexpr int PK_NE = 3;                                      // expanded stages
 constexpr int PK_NL_MAX = 6;                                  // load stages (fewer when X tiles are large)
-constexpr int PK_EXP_WARPS = 8;
-constexpr int PK_THREADS = 128 + PK_EXP_WARPS * 32;
+constexpr int PK_EPI_WARPS = 4;
+constexpr int PK_EXP_WARPS = 16;
+constexpr int PK_EXP_WARP0 = PK_EPI_WARPS + 4;              // warps 4, 5, 6: record producer, MMA issue, X producer
+constexpr int PK_THREADS = (PK_EXP_WARP0 + PK_EXP_WARPS) * 32;
 constexpr int PK_CTRL_BYTES = 256;
 
 struct PkArgs {
     const uint8_t* wp;          // prepacked weight [tiles][nblk][PK_REC_BYTES]
     __half* C;
     const __half* bias;
-    float* ws;                  // [slices][m_pad][N] partial sums (slices > 1)
+    float* ws;                  // [grid][2][m_pad][128] partial sums of segments that do not cover their tile's K
     int* counters;              // [tiles], zero between calls
     int M, N, K;
     int m_pad;                  // tokens rounded up to 16: the MMA's N
-    int nblk, tiles, slices, nl;
-    int micro_shift;            // log2(chunks of 8 per micro-block): 0 or 2
+    int nblk, tiles, nl;
+    int64_t total;              // tiles * nblk stages
     uint32_t base2[2], step2[2];// micro-scale t = base + idx * step as packed fp16 pairs, per table
-    uint32_t tmem_cols;
+    uint32_t acc_cols;          // tensor-memory columns of one accumulator (32, 64 or 128); two are allocated
     uint32_t poll_limit;
 };
 
@@ -73,7 +86,8 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel)
 // Eight E2M1 codes (nibbles {sign, e1, e0, m} of w) times the packed scale ts2 -> four fp16 pairs.
 // Top bytes of the element values 0, .5, 1, 1.5, 2, 3, 4, 6 come from a byte lookup (their low bytes are zero), the
 // signs from the nibbles' top bits replicated into byte masks.
-__device__ __forceinline__ void expand8(uint32_t w, uint32_t ts2, bool two_step, uint32_t t2, uint32_t s2, uint32_t* o)
+template <bool TWO_STEP>
+__device__ __forceinline__ void expand8(uint32_t w, uint32_t ts2, uint32_t t2, uint32_t s2, uint32_t* o)
 {
     constexpr uint32_t LUT0 = 0x3E3C3800u, LUT1 = 0x46444240u;
     const uint32_t w7 = w & 0x77777777u, wl = w << 4;
@@ -84,7 +98,7 @@ __device__ __forceinline__ void expand8(uint32_t w, uint32_t ts2, bool two_step,
     const uint32_t v[4] = {prmt(plo, 0u, 0x1404u), prmt(plo, 0u, 0x3424u), prmt(phi, 0u, 0x1404u), prmt(phi, 0u, 0x3424u)};
     #pragma unroll
     for (int p = 0; p < 4; ++p)
-        o[p] = two_step ? h2_bits(__hmul2(__hmul2(bits_h2(v[p]), bits_h2(t2)), bits_h2(s2)))
+        o[p] = TWO_STEP ? h2_bits(__hmul2(__hmul2(bits_h2(v[p]), bits_h2(t2)), bits_h2(s2)))
                         : h2_bits(__hmul2(bits_h2(v[p]), bits_h2(ts2)));
 }
 
@@ -94,41 +108,78 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
 
+// Bounded waits for the roles that have nothing to do until the barrier completes: mbarrier.try_wait parks the
+// thread for a hardware-chosen while instead of spinning, so waiting warps leave the issue slots to the warps that
+// expand.  `limit` parked attempts (each ends by itself), then the wait gives up like mbar_wait.
+__device__ __forceinline__ bool mbar_wait_parked(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code, uint32_t limit)
+{
+    #pragma unroll 1
+    for (uint32_t it = 0; it < limit; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+    }
+    *abort_flag = 1;
+    atomicCAS(&g_tc_status, 0, code);
+    return false;
+}
+// The same for a whole warp: lane 0 waits, the others are held at the shuffle.
+__device__ __forceinline__ bool mbar_wait_parked_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code, uint32_t limit)
+{
+    int ok = 1;
+    if ((threadIdx.x & 31) == 0) ok = mbar_wait_parked(bar, parity, abort_flag, code, limit) ? 1 : 0;
+    return __shfl_sync(0xFFFFFFFFu, ok, 0) != 0;
+}
+
+
+// First stage of CTA c's run, and the CTA whose run holds stage g.
+__device__ __forceinline__ int64_t run_begin(int64_t total, int c, int G) { return total * c / G; }
+__device__ __forceinline__ int cta_of_stage(int64_t total, int64_t g, int G)
+{
+    int c = (int)(g * G / total);
+    while (c + 1 < G && run_begin(total, c + 1, G) <= g) ++c;
+    while (c > 0 && run_begin(total, c, G) > g) --c;
+    return c;
+}
+
+template <int MS>       // log2(chunks of 8 per micro-block): 0 (micro-block 8) or 2 (micro-block 32)
 __global__ void __launch_bounds__(PK_THREADS, 1)
 gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const PkArgs a)
 {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t exp0 = (raw + 1023u) & ~1023u;                    // expanded tiles (1024-byte aligned for the swizzle)
-    const uint32_t LS = PK_REC_BYTES + (uint32_t)a.m_pad * 256u;     // load stage: packed record + two X tiles
-    const uint32_t ld0 = exp0 + PK_NE * PK_EXP_BYTES;
+    const uint32_t ES = PK_EXP_BYTES + (uint32_t)a.m_pad * 256u;     // operand stage: expanded weight tiles + two X tiles
+    constexpr uint32_t LS = PK_REC_BYTES;                            // load stage: one packed record
+    const uint32_t ld0 = exp0 + PK_NE * ES;
     const uint32_t ctrl_u = ld0 + (uint32_t)a.nl * LS;
     uint8_t* ctrl = smem_raw + (ctrl_u - raw);
-    // control block: ld_full[6] ld_empty[6] ex_full[3] ex_empty[3] acc_full (8 B each), tensor-memory base,
-    // abort flag, "this CTA adds the slices" flag
+    // control block: ld_full[6] ld_empty[6] ex_full[3] ex_empty[3] acc_full[2] acc_empty[2] (8 B each), then the
+    // tensor-memory base, the abort flag and the "this CTA completes the tile" flag
     const uint32_t bar_lfull = ctrl_u, bar_lempty = ctrl_u + 8 * PK_NL_MAX;
     const uint32_t bar_efull = ctrl_u + 16 * PK_NL_MAX, bar_eempty = bar_efull + 8 * PK_NE;
-    const uint32_t bar_acc = bar_eempty + 8 * PK_NE;
-    uint32_t* tmem_base_smem = reinterpret_cast<uint32_t*>(ctrl + 16 * PK_NL_MAX + 16 * PK_NE + 16);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(ctrl + 16 * PK_NL_MAX + 16 * PK_NE + 24);
-    volatile int* last_flag = reinterpret_cast<volatile int*>(ctrl + 16 * PK_NL_MAX + 16 * PK_NE + 28);
+    const uint32_t bar_afull = bar_eempty + 8 * PK_NE, bar_aempty = bar_afull + 16;
+    constexpr int CTRL_WORDS = 16 * PK_NL_MAX + 16 * PK_NE + 32;
+    uint32_t* tmem_base_smem = reinterpret_cast<uint32_t*>(ctrl + CTRL_WORDS);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(ctrl + CTRL_WORDS + 8);
+    volatile int* last_flag = reinterpret_cast<volatile int*>(ctrl + CTRL_WORDS + 12);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tile = blockIdx.x / a.slices, slice = blockIdx.x % a.slices;
-    const int kb0 = (int)(((int64_t)a.nblk * slice) / a.slices), kb1 = (int)(((int64_t)a.nblk * (slice + 1)) / a.slices);
-    const int nst = kb1 - kb0;
+    const int G = gridDim.x, cta = blockIdx.x;
+    const int64_t g0 = run_begin(a.total, cta, G), g1 = run_begin(a.total, cta + 1, G);
+    const int nst = (int)(g1 - g0);
+    const uint32_t park_limit = (a.poll_limit >> 6) + 64u;          // parked attempts last far longer than a poll
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < PK_NL_MAX; ++s) { mbar_init(bar_lfull + 8 * s, 1); mbar_init(bar_lempty + 8 * s, 1 + PK_EXP_WARPS); }
-        for (int s = 0; s < PK_NE; ++s) { mbar_init(bar_efull + 8 * s, PK_EXP_WARPS); mbar_init(bar_eempty + 8 * s, 1); }
-        mbar_init(bar_acc, 1);
+        for (int s = 0; s < PK_NL_MAX; ++s) { mbar_init(bar_lfull + 8 * s, 1); mbar_init(bar_lempty + 8 * s, PK_EXP_WARPS / 2); }
+        for (int s = 0; s < PK_NE; ++s) { mbar_init(bar_efull + 8 * s, PK_EXP_WARPS / 2 + 1); mbar_init(bar_eempty + 8 * s, 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(bar_afull + 8 * b, 1); mbar_init(bar_aempty + 8 * b, PK_EPI_WARPS); }
         *abort_flag = 0;
         *last_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) {
+    if (warp == 5) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(smem_u32(tmem_base_smem)), "r"(a.tmem_cols) : "memory");
+                     ::"r"(smem_u32(tmem_base_smem)), "r"(2u * a.acc_cols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
@@ -136,128 +187,229 @@ gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const PkArgs a)
     tc_fence_after();
     const uint32_t tmem_base = *tmem_base_smem;
 
-    if (warp == 0) {
-        // ================= producer =================
+    if (warp == 4) {
+        // ================= record producer =================
         if (lane == 0) {
-            const uint8_t* src = a.wp + ((int64_t)tile * a.nblk + kb0) * PK_REC_BYTES;
+            const uint8_t* src = a.wp + g0 * PK_REC_BYTES;           // the run's records are consecutive in memory
             uint32_t stage = 0, phase = 0;
             for (int i = 0; i < nst; ++i) {
-                if (!mbar_wait(bar_lempty + 8 * stage, phase ^ 1u, abort_flag, 1, a.poll_limit)) break;
-                const uint32_t dst = ld0 + stage * LS, bar = bar_lfull + 8 * stage;
+                if (!mbar_wait_parked(bar_lempty + 8 * stage, phase ^ 1u, abort_flag, 1, park_limit)) break;
+                const uint32_t bar = bar_lfull + 8 * stage;
                 mbar_expect_tx(bar, LS);
-                bulk_load(dst, src + (int64_t)i * PK_REC_BYTES, PK_REC_BYTES, bar);
-                tma_load_2d(dst + PK_REC_BYTES, &mapX, (kb0 + i) * PK_KB, 0, bar);
-                tma_load_2d(dst + PK_REC_BYTES + (uint32_t)a.m_pad * 128u, &mapX, (kb0 + i) * PK_KB + 64, 0, bar);
+                bulk_load(ld0 + stage * LS, src + (int64_t)i * PK_REC_BYTES, PK_REC_BYTES, bar);
                 if (++stage == (uint32_t)a.nl) { stage = 0; phase ^= 1u; }
             }
         }
-    } else if (warp == 1) {
+    } else if (warp == 6) {
+        // ================= X producer: the tokens' tiles travel with the operand stage =================
+        // They complete the same barrier as the expansion's arrivals, so the MMA warp waits once per stage and one
+        // commit hands the whole stage back.
+        if (lane == 0) {
+            uint32_t es = 0, eph = 0;
+            for (int i = 0; i < nst; ++i) {
+                if (!mbar_wait_parked(bar_eempty + 8 * es, eph ^ 1u, abort_flag, 8, park_limit)) break;
+                const uint32_t dst = exp0 + es * ES + PK_EXP_BYTES, bar = bar_efull + 8 * es;
+                const int kb = (int)((g0 + i) % a.nblk);
+                mbar_expect_tx(bar, (uint32_t)a.m_pad * 256u);
+                tma_load_2d(dst, &mapX, kb * PK_KB, 0, bar);
+                tma_load_2d(dst + (uint32_t)a.m_pad * 128u, &mapX, kb * PK_KB + 64, 0, bar);
+                if (++es == PK_NE) { es = 0; eph ^= 1u; }
+            }
+        }
+    } else if (warp == 5) {
         // ================= MMA issue =================
         // kind::f16: D fp32, A/B fp16, both K-major, M = 128 weight rows, N = m_pad tokens
         const uint32_t idesc = (1u << 4) | ((uint32_t)(a.m_pad >> 3) << 17) | ((uint32_t)(PK_ROWS >> 4) << 24);
         const bool leader = elect_one();
-        uint32_t ls = 0, lph = 0, es = 0, eph = 0;
-        for (int i = 0; i < nst; ++i) {
-            if (!mbar_wait_warp(bar_lfull + 8 * ls, lph, abort_flag, 2, a.poll_limit)) break;       // X tiles landed
-            if (!mbar_wait_warp(bar_efull + 8 * es, eph, abort_flag, 3, a.poll_limit)) break;       // weights expanded
-            tc_fence_after();
-            if (leader) {
-                const uint32_t wa = exp0 + es * PK_EXP_BYTES, xa = ld0 + ls * LS + PK_REC_BYTES;
-                #pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    #pragma unroll
-                    for (int kk = 0; kk < 4; ++kk)
-                        tc_mma_f16(tmem_base, umma_desc(wa + h * (PK_ROWS * 128) + kk * 32),
-                                   umma_desc(xa + h * ((uint32_t)a.m_pad * 128u) + kk * 32), idesc, (i | h | kk) != 0 ? 1u : 0u);
-                }
-                tc_commit(bar_eempty + 8 * es);
-                tc_commit(bar_lempty + 8 * ls);
-                if (i + 1 == nst) tc_commit(bar_acc);
-            }
-            __syncwarp();
-            if (++ls == (uint32_t)a.nl) { ls = 0; lph ^= 1u; }
-            if (++es == PK_NE) { es = 0; eph ^= 1u; }
-        }
-    } else if (warp >= 4) {
-        // ================= expansion =================
-        const int te = threadIdx.x - 128;
-        const int r = te & (PK_ROWS - 1), h = te >> 7;
-        const uint32_t swz = (uint32_t)(r & 7);
-        uint32_t ls = 0, lph = 0, es = 0, eph = 0;
+        uint32_t es = 0, eph = 0;
         bool ok = true;
-        for (int i = 0; i < nst; ++i) {
-            if (!(ok = mbar_wait_warp(bar_lfull + 8 * ls, lph, abort_flag, 4, a.poll_limit))) break;
-            if (!(ok = mbar_wait_warp(bar_eempty + 8 * es, eph ^ 1u, abort_flag, 5, a.poll_limit))) break;
+        int j = 0;
+        for (int64_t g = g0; g < g1 && ok; ++j) {
+            const int kb = (int)(g % a.nblk);
+            const int len = (int)min((int64_t)(a.nblk - kb), g1 - g);
+            const uint32_t buf = (uint32_t)j & 1u;
+            // the epilogue must have drained this accumulator's previous segment
+            if (!(ok = mbar_wait_warp(bar_aempty + 8 * buf, (((uint32_t)j >> 1) & 1u) ^ 1u, abort_flag, 7, a.poll_limit))) break;
+            const uint32_t d_tmem = tmem_base + buf * a.acc_cols;
+            for (int i = 0; i < len; ++i) {
+                // weights expanded and X tiles landed
+                if (!(ok = mbar_wait_warp(bar_efull + 8 * es, eph, abort_flag, 3, a.poll_limit))) break;
+                tc_fence_after();
+                if (leader) {
+                    const uint32_t wa = exp0 + es * ES, xa = wa + PK_EXP_BYTES;
+                    #pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        #pragma unroll
+                        for (int kk = 0; kk < 4; ++kk)
+                            tc_mma_f16(d_tmem, umma_desc(wa + h * (PK_ROWS * 128) + kk * 32),
+                                       umma_desc(xa + h * ((uint32_t)a.m_pad * 128u) + kk * 32), idesc, (i | h | kk) != 0 ? 1u : 0u);
+                    }
+                    tc_commit(bar_eempty + 8 * es);
+                    if (i + 1 == len) tc_commit(bar_afull + 8 * buf);
+                }
+                __syncwarp();
+                if (++es == PK_NE) { es = 0; eph ^= 1u; }
+            }
+            g += len;
+        }
+    } else if (warp >= PK_EXP_WARP0) {
+        // ================= expansion =================
+        // Two groups of eight warps take alternate stages, so that one group's arithmetic runs under the other's
+        // stores, fence and barrier traffic; thread (row r, half hh) of a group turns 64 codes into the 8 chunks of its
+        // row in one of the stage's two 64-wide K tiles.
+        const int te = threadIdx.x - PK_EXP_WARP0 * 32;
+        const int grp = te >> 8, tg = te & 255;
+        const int r = tg & (PK_ROWS - 1), hh = tg >> 7;
+        const uint32_t swz = (uint32_t)(r & 7);
+        const uint32_t nl = (uint32_t)a.nl;
+        // A test of a barrier costs a few hundred cycles of latency even when it has completed, so the tests for the
+        // group's NEXT stage are issued before this stage's arithmetic and read after it; a wait loop runs only when
+        // one failed.
+        bool pre_l = grp < nst && mbar_test(bar_lfull + 8 * ((uint32_t)grp % nl), ((uint32_t)grp / nl) & 1u);
+        bool pre_e = grp < nst && mbar_test(bar_eempty + 8 * ((uint32_t)grp % PK_NE), (((uint32_t)grp / PK_NE) & 1u) ^ 1u);
+        for (int i = grp; i < nst; i += 2) {
+            const uint32_t ls = (uint32_t)i % nl, lph = ((uint32_t)i / nl) & 1u;
+            const uint32_t es = (uint32_t)i % PK_NE, eph = ((uint32_t)i / PK_NE) & 1u;
+            if (!__all_sync(0xFFFFFFFFu, pre_l) && !mbar_wait_warp(bar_lfull + 8 * ls, lph, abort_flag, 4, a.poll_limit)) break;
             const uint32_t rec = ld0 + ls * LS;
-            uint32_t l2w, meta;
+            uint32_t l2w, meta, cw[8];
             asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(l2w), "=r"(meta) : "r"(rec + PK_CODE_BYTES + r * 8));
-            uint32_t cw[8];
             asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
-                         : "=r"(cw[0]), "=r"(cw[1]), "=r"(cw[2]), "=r"(cw[3]) : "r"(rec + ((2 * h) * PK_ROWS + r) * 16));
+                         : "=r"(cw[0]), "=r"(cw[1]), "=r"(cw[2]), "=r"(cw[3]) : "r"(rec + ((2 * hh) * PK_ROWS + r) * 16));
             asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
-                         : "=r"(cw[4]), "=r"(cw[5]), "=r"(cw[6]), "=r"(cw[7]) : "r"(rec + ((2 * h + 1) * PK_ROWS + r) * 16));
+                         : "=r"(cw[4]), "=r"(cw[5]), "=r"(cw[6]), "=r"(cw[7]) : "r"(rec + ((2 * hh + 1) * PK_ROWS + r) * 16));
             const uint32_t sc = meta & 0xFFFFu, s2 = sc * 0x10001u, tb = (meta >> 16) & 1u;
             const uint32_t base2 = tb ? a.base2[1] : a.base2[0], step2 = tb ? a.step2[1] : a.step2[0];
             // a scale in fp16's top binade could overflow t*s where (level*t)*s stays finite: multiply in two steps there
             const bool two_step = sc >= 0x7800u;
-            const uint32_t out = exp0 + es * PK_EXP_BYTES + h * (PK_ROWS * 128) + r * 128;
-            #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                const uint32_t idx = (l2w >> (2 * ((8 * h + c) >> a.micro_shift))) & 3u;
-                const uint32_t t2 = base2 + idx * step2;
-                const uint32_t ts2 = h2_bits(__hmul2(bits_h2(t2), bits_h2(s2)));
-                uint32_t o[4];
-                expand8(cw[c], ts2, two_step, t2, s2, o);
-                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};"
-                             ::"r"(out + (((uint32_t)c ^ swz) << 4)), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
+            // this half's micro-scale indices: chunk 8hh + c of the block, one index per 2^MS chunks
+            const uint32_t l2q = l2w >> (2 * ((8 * hh) >> MS));
+            const uint32_t out = (exp0 + es * ES + hh * (PK_ROWS * 128) + r * 128) ^ (swz << 4);
+            // the operand stage must have been read by the MMAs of its previous use
+            if (!__all_sync(0xFFFFFFFFu, pre_e) && !mbar_wait_warp(bar_eempty + 8 * es, eph ^ 1u, abort_flag, 5, a.poll_limit)) break;
+            // Only now: the parity test tells "completed" from "not yet" for the phase this group waits for next, but
+            // not from a phase two behind, and the MMAs of stage i - 3 having finished (the wait above) is what
+            // guarantees that the barrier of stage i + 2's slot is at most one phase behind.
+            const bool more = i + 2 < nst;
+            const uint32_t ni = (uint32_t)i + 2u;
+            const bool nxt_l = more && mbar_test(bar_lfull + 8 * (ni % nl), (ni / nl) & 1u);
+            const bool nxt_e = more && mbar_test(bar_eempty + 8 * (ni % PK_NE), ((ni / PK_NE) & 1u) ^ 1u);
+            uint32_t t2 = 0u, ts2 = 0u;
+            if (!two_step) {
+                #pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    if (MS == 0 || (c & 3) == 0) {
+                        const uint32_t idx = (l2q >> (2 * (c >> MS))) & 3u;
+                        t2 = base2 + idx * step2;
+                        ts2 = h2_bits(__hmul2(bits_h2(t2), bits_h2(s2)));
+                    }
+                    uint32_t o[4];
+                    expand8<false>(cw[c], ts2, t2, s2, o);
+                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};"
+                                 ::"r"(out ^ ((uint32_t)c << 4)), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
+                }
+            } else {
+                #pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const uint32_t idx = (l2q >> (2 * (c >> MS))) & 3u;
+                    t2 = base2 + idx * step2;
+                    uint32_t o[4];
+                    expand8<true>(cw[c], 0u, t2, s2, o);
+                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};"
+                                 ::"r"(out ^ ((uint32_t)c << 4)), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
+                }
             }
             // the tensor core reads shared memory through the async proxy: order these generic-proxy stores before it
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (lane == 0) { mbar_arrive(bar_efull + 8 * es); mbar_arrive(bar_lempty + 8 * ls); }
-            if (++ls == (uint32_t)a.nl) { ls = 0; lph ^= 1u; }
-            if (++es == PK_NE) { es = 0; eph ^= 1u; }
+            pre_l = nxt_l; pre_e = nxt_e;
         }
-        // ================= epilogue (warps 4-7: one per quarter of the tensor-memory lanes) =================
-        if (warp < 8) {
-            ok = ok && mbar_wait(bar_acc, 0u, abort_flag, 6, a.poll_limit);
-            ok = __all_sync(0xFFFFFFFFu, ok);
-            const int quarter = warp & 3;
-            const int gn = tile * PK_ROWS + quarter * 32 + lane;             // this thread's output column
-            if (ok) {
-                tc_fence_after();
-                for (int c0 = 0; c0 < a.m_pad; c0 += 32) {
-                    float v[32];
-                    tc_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + c0, v);
-                    #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int m = c0 + j;
-                        if (m >= a.M) break;
-                        if (a.slices == 1) {
-                            __half o = __float2half_rn(v[j]);
-                            if (a.bias) o = __hadd(o, a.bias[gn]);
-                            a.C[(int64_t)m * a.N + gn] = o;
-                        } else {
-                            a.ws[((int64_t)slice * a.m_pad + m) * a.N + gn] = v[j];
-                        }
+    } else if (warp < PK_EPI_WARPS) {
+        // ================= epilogue (warps 0-3: one per quarter of the tensor-memory lanes) =================
+        const int quarter = warp, nloc = quarter * 32 + lane;          // this thread's weight row inside the tile
+        bool ok = true;
+        int j = 0;
+        for (int64_t g = g0; g < g1; ++j) {
+            const int tile = (int)(g / a.nblk), kb = (int)(g % a.nblk);
+            const int len = (int)min((int64_t)(a.nblk - kb), g1 - g);
+            g += len;
+            const uint32_t buf = (uint32_t)j & 1u;
+            ok = ok && mbar_wait_parked_warp(bar_afull + 8 * buf, ((uint32_t)j >> 1) & 1u, abort_flag, 6, park_limit);
+            if (!ok) break;
+            tc_fence_after();
+            const bool whole = len == a.nblk;
+            const int gn = tile * PK_ROWS + nloc;
+            float* part = a.ws + ((int64_t)cta * 2 + (tile == (int)(g0 / a.nblk) ? 0 : 1)) * a.m_pad * PK_ROWS + nloc;
+            const __half bv = a.bias ? a.bias[gn] : __float2half_rn(0.f);
+            for (int c0 = 0; c0 < a.m_pad; c0 += 32) {
+                float v[32];
+                tc_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * a.acc_cols + c0, v);
+                #pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const int m = c0 + i;
+                    if (m >= a.M) break;
+                    if (whole) {
+                        __half o = __float2half_rn(v[i]);
+                        if (a.bias) o = __hadd(o, bv);
+                        a.C[(int64_t)m * a.N + gn] = o;
+                    } else {
+                        part[(int64_t)m * PK_ROWS] = v[i];
                     }
                 }
             }
-            if (a.slices > 1) {
+            // the accumulator has been read: hand it back to the MMA warp
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_aempty + 8 * buf);
+            if (!whole) {
+                // the tile's segments sit in consecutive CTAs; the one that arrives last adds them in CTA order
+                const int c_first = cta_of_stage(a.total, (int64_t)tile * a.nblk, G);
+                const int c_last = cta_of_stage(a.total, (int64_t)tile * a.nblk + a.nblk - 1, G);
+                // every thread orders its own partial sums before the count (a fence by the counting thread alone, after
+                // the barrier, was seen to let a reader on another SM run ahead of a warp's stores)
                 __threadfence();
                 asm volatile("bar.sync 1, 128;" ::: "memory");
-                if (te == 0) *last_flag = ok && (atomicAdd(a.counters + tile, 1) == a.slices - 1);
+                if (threadIdx.x == 0) {
+                    int old;
+                    asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(old) : "l"(a.counters + tile) : "memory");
+                    *last_flag = old == c_last - c_first;
+                }
                 asm volatile("bar.sync 1, 128;" ::: "memory");
-                if (*last_flag) {
+                const bool last = *last_flag != 0;
+                asm volatile("bar.sync 1, 128;" ::: "memory");        // everyone has read the flag before its next use
+                if (last) {
                     __threadfence();
-                    for (int m = 0; m < a.M; ++m) {
-                        float acc = 0.f;
-                        for (int s = 0; s < a.slices; ++s) acc += __ldcg(a.ws + ((int64_t)s * a.m_pad + m) * a.N + gn);
-                        __half o = __float2half_rn(acc);
-                        if (a.bias) o = __hadd(o, a.bias[gn]);
-                        a.C[(int64_t)m * a.N + gn] = o;
+                    for (int m0 = 0; m0 < a.M; m0 += 16) {            // sixteen rows, two segments: 32 loads in flight
+                        float acc[16];
+                        #pragma unroll
+                        for (int i = 0; i < 16; ++i) acc[i] = 0.f;
+                        for (int cc = c_first; cc <= c_last; cc += 2) {
+                            float v[2][16];
+                            #pragma unroll
+                            for (int u = 0; u < 2; ++u) {
+                                const int cu = cc + u <= c_last ? cc + u : c_last;
+                                const int slot = tile == (int)(run_begin(a.total, cu, G) / a.nblk) ? 0 : 1;
+                                const float* p = a.ws + ((int64_t)cu * 2 + slot) * a.m_pad * PK_ROWS + nloc;
+                                #pragma unroll
+                                for (int i = 0; i < 16; ++i)
+                                    v[u][i] = (cc + u <= c_last && m0 + i < a.M) ? __ldcg(p + (int64_t)(m0 + i) * PK_ROWS) : 0.f;
+                            }
+                            #pragma unroll
+                            for (int u = 0; u < 2; ++u) {
+                                #pragma unroll
+                                for (int i = 0; i < 16; ++i) acc[i] += v[u][i];
+                            }
+                        }
+                        #pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            if (m0 + i >= a.M) break;
+                            __half o = __float2half_rn(acc[i]);
+                            if (a.bias) o = __hadd(o, bv);
+                            a.C[(int64_t)(m0 + i) * a.N + gn] = o;
+                        }
                     }
-                    if (te == 0) a.counters[tile] = 0;
+                    if (threadIdx.x == 0) a.counters[tile] = 0;
                 }
             }
         }
@@ -271,9 +423,9 @@ gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const PkArgs a)
         while (gtime_ns() - t0 < 200000ull) { }          // copies that may still be in flight land before smem is released
         __syncthreads();
     }
-    if (warp == 1) {
+    if (warp == 5) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(a.tmem_cols) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2u * a.acc_cols) : "memory");
     }
 }
 
@@ -317,7 +469,7 @@ __global__ void __launch_bounds__(256) gemm_w4_prepack_kernel(const PrepackArgs 
 // ---- host side ---------------------------------------------------------------------------------------
 // Formats the kernel expands: HBQ weights with E2M1 elements, an E5M3 scale per 128 and 2-bit micro-scales per 8 or 32
 // whose candidates are base + idx * step in fp16 (the "Mix" pair and its members; not SIG-1 / INT / POT).
-static bool w4_format(const hbq_format* f, PkArgs* a)
+static bool w4_format(const hbq_format* f, PkArgs* a, int* micro_shift)
 {
     if (!f || f->kind != HBQ_KIND_HBQ || f->ebit != 2 || f->mbit != 1 || f->block_size != 128 || f->sc_ebit != 5 ||
         f->sc_mbit != 3 || f->l2_sc_bit != 2 || (f->l2_block_size != 8 && f->l2_block_size != 32))
@@ -333,8 +485,8 @@ static bool w4_format(const hbq_format* f, PkArgs* a)
     }
     if (a) {
         for (int i = 0; i < 2; ++i) { a->base2[i] = base[i] * 0x10001u; a->step2[i] = step[i] * 0x10001u; }
-        a->micro_shift = f->l2_block_size == 8 ? 0 : 2;
     }
+    if (micro_shift) *micro_shift = f->l2_block_size == 8 ? 0 : 2;
     return true;
 }
 
@@ -342,20 +494,6 @@ static bool w4_shape(int64_t M, int64_t N, int64_t K)
 {
     return M >= 1 && M <= 128 && N >= PK_ROWS && (N % PK_ROWS) == 0 && K >= PK_KB && (K % PK_KB) == 0 &&
            N <= (1ll << 24) && K <= (1ll << 24);
-}
-
-// K slices per tile: the count that leaves the fewest SM-rounds per unit of work, with a small charge per slice
-// for its share of the partial-sum traffic and the launch of more CTAs.
-static int w4_slices(int64_t tiles, int64_t nblk, int sms)
-{
-    int best = 1;
-    double best_cost = 1e30;
-    for (int s = 1; s <= 16 && s <= nblk; ++s) {
-        const double rounds = (double)((tiles * s + sms - 1) / sms);
-        const double cost = rounds / s + 0.02 * s;
-        if (cost < best_cost - 1e-9) { best_cost = cost; best = s; }
-    }
-    return best;
 }
 
 int64_t gemm_w4_prepacked_bytes(int64_t N, int64_t K)
@@ -367,7 +505,7 @@ int64_t gemm_w4_prepacked_bytes(int64_t N, int64_t K)
 int gemm_w4_prepack(const hbq_packed_out* in, int64_t N, int64_t K, const hbq_format* f, void* out, cudaStream_t stream)
 {
     if (!in || !out || !in->codes || !in->scale_u8 || !in->l2_packed) return HBQ_ERR_ARG;
-    if (!w4_format(f, nullptr) || !w4_shape(1, N, K)) return HBQ_ERR_UNSUPPORTED;
+    if (!w4_format(f, nullptr, nullptr) || !w4_shape(1, N, K)) return HBQ_ERR_UNSUPPORTED;
     if (f->l2_scheme == HBQ_L2_MIX && !in->scheme) return HBQ_ERR_ARG;
     if ((reinterpret_cast<uintptr_t>(in->codes) | reinterpret_cast<uintptr_t>(out)) & 15) return HBQ_ERR_ALIGN;
     PrepackArgs a;
@@ -387,8 +525,7 @@ int64_t gemm_w4_workspace_bytes(int64_t M, int64_t N, int64_t K)
     int sms = 0;
     if (device_sms(&sms) != HBQ_OK) return -1;
     const int64_t tiles = N / PK_ROWS, m_pad = (M + 15) / 16 * 16;
-    const int s = w4_slices(tiles, K / PK_KB, sms);
-    return (s > 1 ? (int64_t)s * m_pad * N * 4 : 0) + tiles * 4;
+    return (int64_t)sms * 2 * m_pad * PK_ROWS * 4 + tiles * 4;        // two partial-sum slots per CTA, one counter per tile
 }
 
 // workspace: gemm_w4_workspace_bytes() bytes, 16-byte aligned, zeroed once by the caller (the kernel leaves the tile
@@ -398,8 +535,9 @@ int gemm_w4_launch(const void* X, const void* Wp, void* C, int64_t M, int64_t N,
 {
     PkArgs a;
     memset(&a, 0, sizeof(a));
+    int ms = 0;
     if (!X || !Wp || !C || !workspace) return HBQ_ERR_ARG;
-    if (!w4_format(f, &a) || !w4_shape(M, N, K)) return HBQ_ERR_UNSUPPORTED;
+    if (!w4_format(f, &a, &ms) || !w4_shape(M, N, K)) return HBQ_ERR_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(Wp) | reinterpret_cast<uintptr_t>(workspace)) & 15)
         return HBQ_ERR_ALIGN;
     if ((reinterpret_cast<uintptr_t>(C) | reinterpret_cast<uintptr_t>(bias)) & 1) return HBQ_ERR_ALIGN;
@@ -409,22 +547,32 @@ int gemm_w4_launch(const void* X, const void* Wp, void* C, int64_t M, int64_t N,
     a.M = (int)M; a.N = (int)N; a.K = (int)K;
     a.m_pad = (int)((M + 15) / 16 * 16);
     a.nblk = (int)(K / PK_KB); a.tiles = (int)(N / PK_ROWS);
-    a.slices = w4_slices(a.tiles, a.nblk, sms);
-    const int64_t part = a.slices > 1 ? (int64_t)a.slices * a.m_pad * N * 4 : 0;
+    a.total = (int64_t)a.tiles * a.nblk;
+    const int grid = (int)(a.total < sms ? a.total : sms);
     a.ws = (float*)workspace;
-    a.counters = (int*)((uint8_t*)workspace + part);
-    const uint32_t LS = PK_REC_BYTES + (uint32_t)a.m_pad * 256u;
-    const uint32_t avail = 227u * 1024u - 1024u - PK_NE * PK_EXP_BYTES - PK_CTRL_BYTES;
+    a.counters = (int*)((uint8_t*)workspace + (int64_t)sms * 2 * a.m_pad * PK_ROWS * 4);
+    const uint32_t LS = PK_REC_BYTES, ES = PK_EXP_BYTES + (uint32_t)a.m_pad * 256u;
+    const uint32_t avail = 227u * 1024u - 1024u - PK_NE * ES - PK_CTRL_BYTES;
     a.nl = (int)(avail / LS);
     if (a.nl > PK_NL_MAX) a.nl = PK_NL_MAX;
+    // An even count: the two expansion groups take alternate stages, so with an even ring a slot always serves the same
+    // group, and a group only ever waits for the fill that follows one it has consumed itself.  (A parity wait cannot
+    // tell "this fill has landed" from "the fill before it has not landed yet"; with an odd ring the fill before is the
+    // other group's and nothing orders it before the wait.)
+    a.nl &= ~1;
     if (a.nl < 2) return HBQ_ERR_UNSUPPORTED;
-    a.tmem_cols = a.m_pad <= 32 ? 32u : (a.m_pad <= 64 ? 64u : 128u);
+    a.acc_cols = a.m_pad <= 32 ? 32u : (a.m_pad <= 64 ? 64u : 128u);
     a.poll_limit = poll_limit ? poll_limit : (1u << 23);
     CUtensorMap mx;
     { const int rc = gemm_make_map(&mx, X, M, K, a.m_pad); if (rc) return rc; }
-    const size_t smem = 1024 + PK_NE * PK_EXP_BYTES + (size_t)a.nl * LS + PK_CTRL_BYTES;
-    { const int rc = ensure_dynamic_smem(gemm_packed_kernel, smem); if (rc) return rc; }
-    gemm_packed_kernel<<<a.tiles * a.slices, PK_THREADS, smem, stream>>>(mx, a);
+    const size_t smem = 1024 + (size_t)PK_NE * ES + (size_t)a.nl * LS + PK_CTRL_BYTES;
+    if (ms == 0) {
+        { const int rc = ensure_dynamic_smem(gemm_packed_kernel<0>, smem); if (rc) return rc; }
+        gemm_packed_kernel<0><<<grid, PK_THREADS, smem, stream>>>(mx, a);
+    } else {
+        { const int rc = ensure_dynamic_smem(gemm_packed_kernel<2>, smem); if (rc) return rc; }
+        gemm_packed_kernel<2><<<grid, PK_THREADS, smem, stream>>>(mx, a);
+    }
     HBQ_LAUNCH_CHECK("gemm_packed_kernel");
     return HBQ_OK;
 }

@@ -29,13 +29,31 @@ class QLinear(nn.Linear):
         self.ops = ops
         self.check_finite = check_finite
         self.packed_weight = None
+        self.w4_weight = None          # the packed weight in the decode GEMM's tile order (prepare_decode)
+        self.w4_max_rows = 0           # batches up to this many rows take it while the fp16 tensor is kept; 0: none --
+                                       # on B200 the packed kernel runs at about 0.8x the library fp16 GEMM for
+                                       # 1..16 rows (its limit is instruction issue, not bytes), so what it buys is
+                                       # the 3.6x smaller weight (prepare_decode(drop_fp16=True)), not time
 
     def forward(self, x: torch.Tensor, input_quantized: bool = False):
         """``input_quantized``: ``x`` has been through ``self.aq`` already (a producer that fuses the
         quantizer, e.g. ``swiglu_quantize``)."""
         wq = self.weight
         xq = x if input_quantized else self.aq(x)
-        if self.ops is None:
+        w4 = self.w4_weight
+        rows = xq.numel() // xq.shape[-1] if xq.shape[-1] else 0
+        if w4 is not None and self.ops is None and xq.is_cuda and xq.dtype == torch.float16 and \
+                (0 < rows <= self.w4_max_rows or wq.numel() == 0):
+            # the packed weight streams at 0.56 B per element instead of 2; 128 rows per launch
+            x2d = xq.reshape(-1, xq.shape[-1])
+            if rows <= 128:
+                y = w4.matmul(x2d, self.bias)
+            else:
+                y = torch.empty((rows, self.out_features), dtype=torch.float16, device=xq.device)
+                for r0 in range(0, rows, 128):
+                    w4.matmul(x2d[r0:r0 + 128], self.bias, out=y[r0:r0 + 128])
+            y = y.view(*xq.shape[:-1], self.out_features)
+        elif self.ops is None:
             y = F.linear(xq, wq, self.bias)
         else:
             y = self.ops(xq, wq, self.bias)
@@ -70,6 +88,38 @@ class QLinear(nn.Linear):
         self.packed_weight = wq.quantize_packed(self.weight.data)
         self.weight.data = dequantize_packed(self.packed_weight).to(self.weight.dtype)
         return self.packed_weight
+
+    def prepare_decode(self, wq=None, drop_fp16: bool = False) -> bool:
+        """Keep the packed weight also in the tile order of ``hbq_gemm_w4`` so that batches of up to
+        ``w4_max_rows`` rows multiply against 4-bit codes and scales expanded in shared memory (same products as
+        with the fp16 tensor: the expanded values are its values bit for bit).  ``drop_fp16`` frees the fp16 tensor:
+        the layer then holds 0.56 B per weight and EVERY batch goes through the packed kernel, 128 rows per launch
+        (a capacity mode: large batches are slower than on the fp16 tensor).  Returns False, and changes nothing, for
+        formats and shapes outside that kernel or when the layer has an accumulation operator (the kernel
+        accumulates in fp32 like ``F.linear``)."""
+        from .packed_gemm import W4Weight
+        if self.ops is not None or not self.weight.is_cuda or self.weight.dtype != torch.float16:
+            return False
+        if self.packed_weight is None:
+            wq = self.wq if wq is None else wq
+            if not hasattr(wq, "quantize_packed"):
+                return False
+            try:
+                self.pack_weight(wq)
+            except NotImplementedError:
+                return False
+        if not W4Weight.supported(self.packed_weight):
+            return False
+        from ._lib import HbqError
+        try:
+            self.w4_weight = W4Weight.from_packed(self.packed_weight)
+        except HbqError:               # a micro-scale table the kernel does not expand
+            self.w4_weight = None
+            return False
+        if drop_fp16:
+            self.weight.data = torch.empty(0, dtype=self.weight.dtype, device=self.weight.device)
+            self.packed_weight = None
+        return True
 
     def load_packed_weight(self, packed):
         """Install a weight from its packed form (``PackedTensor`` or its ``state_dict()``)."""

@@ -24,6 +24,9 @@ class PTQConfig:
     """Parsed quantization YAML (the second YAML of a reference run, config/README.md)."""
 
     def __init__(self, quant_config: Dict[str, Any]):
+        # not a YAML field: keep every statically quantised weight also as packed codes in the decode GEMM's tile
+        # order (QLinear.prepare_decode), so that decode-sized batches stream 0.56 B per weight
+        self.pack_for_decode = False
         self.quant_config = quant_config
         q = quant_config.get("quantization", {})
         b = quant_config.get("block_quant", {})
@@ -195,6 +198,15 @@ class PTQConfig:
     def static_quant_linear_weight(self, linear):
         """``weight.data = linear.wq(weight)`` (src/ptq.py:337-358; the reference's row chunking only bounds
         the memory of its eager quantizer, which expands tensors 4-8x, and is not needed here)."""
+        if self.pack_for_decode and self.accumulation_type == "fp32" and hasattr(linear, "prepare_decode") and \
+                linear.weight.is_cuda and hasattr(linear.wq, "quantize_packed"):
+            # one pass gives the packed codes and the fp16 tensor; the packed form also serves decode-sized batches
+            try:
+                linear.pack_weight(linear.wq)
+                linear.prepare_decode()
+                return
+            except NotImplementedError:
+                pass
         linear.weight.data = linear.wq(linear.weight.data)
 
     # ---- src/ptq.py:384-404 ----

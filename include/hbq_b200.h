@@ -253,10 +253,11 @@ int hbq_gemm_wait_selftest(const void* A, const void* W, void* C, int64_t M, int
  * micro-scale indices, the block scale as fp16 and the table bit.  Done once per weight.
  *
  * workspace: hbq_gemm_w4_workspace_bytes(M, N, K) bytes (-1: shape not served), 16-byte aligned, ZEROED ONCE by
- * the caller before its first use; the kernel returns it zeroed where that matters, so it can be reused by later
- * calls on the same stream.  It holds the fp32 partial sums of the K slices a tile is cut into when N alone does
- * not fill the SMs (the slices are added in slice order: results do not vary from run to run) and one counter per
- * tile.  After a call that hbq_gemm_status reports as failed, zero it again. */
+ * the caller before its first use; the kernel leaves it usable for the next call on the same stream.  The work is
+ * cut into equal runs of (128 rows, 128 k) records, one run per SM, whatever tile boundaries fall inside a run; the
+ * parts of a tile that different SMs computed meet here as fp32 partial sums (two slots per SM) and are added in a
+ * fixed order, so results do not vary from run to run; one counter per tile tells which SM finishes it.  After a
+ * call that hbq_gemm_status reports as failed, zero it again. */
 int64_t hbq_gemm_w4_prepacked_bytes(int64_t N, int64_t K);
 int hbq_gemm_w4_prepack(const hbq_packed_out* in, int64_t N, int64_t K, const hbq_format* fmt, void* out,
                         void* stream);

@@ -108,3 +108,41 @@ def test_shapes_and_formats_outside_the_kernel_are_refused():
     with pytest.raises(_lib.HbqError):
         W4Weight.from_packed(packed)
     assert H.gemm_status() == 0
+
+
+def test_linear_layer_on_the_packed_weight():
+    """QLinear.prepare_decode: decode-sized batches take the packed kernel, larger ones the fp16 tensor; with the fp16
+    tensor dropped every batch goes through the packed kernel and the layer holds 0.5625 B per weight."""
+    import hbq_b200 as H
+    fm = load_formats()
+    N, K = 1024, 2048
+    lin = H.QLinear(K, N, bias=True, device="cuda", dtype=torch.float16, check_finite=False)
+    g = torch.Generator(device="cuda").manual_seed(9)
+    lin.weight.data = (0.02 * torch.randn((N, K), device="cuda", generator=g)).half()
+    lin.bias.data = torch.randn(N, device="cuda", generator=g).half()
+    lin.wq = make_quantizer(fm["hbq_a_wgt"])
+    lin.aq = make_quantizer(fm["hbq_a_act"])
+    assert lin.prepare_decode() and lin.w4_max_rows == 0     # opt-in while the fp16 tensor is kept
+    lin.w4_max_rows = 32
+    wq = lin.weight.data.clone()
+    for rows in (1, 20, 32, 33, 300):
+        x = torch.randn((rows, K), device="cuda", generator=g).half()
+        l0 = H.launch_count()
+        y = lin(x)
+        ours = H.launch_count() - l0                          # quantize + packed GEMM; F.linear is not counted
+        ref = (lin.aq.q(x).double() @ wq.double().t()).float().half() + lin.bias.data
+        rel = float((y.double() - ref.double()).norm() / ref.double().norm())
+        assert y.shape == (rows, N) and rel <= REL_TOL, (rows, rel)
+        assert ours == (2 if rows <= lin.w4_max_rows else 1)
+    before = lin.weight.numel()
+    assert lin.prepare_decode(drop_fp16=True) and lin.weight.numel() == 0 and before == N * K
+    assert lin.w4_weight.nbytes() * 128 * 128 == N * K * 9216
+    x = torch.randn((300, K), device="cuda", generator=g).half()
+    y = lin(x)
+    ref = (lin.aq.q(x).double() @ wq.double().t()).float().half() + lin.bias.data
+    assert float((y.double() - ref.double()).norm() / ref.double().norm()) <= REL_TOL
+    assert H.gemm_status() == 0
+    # a layer with an accumulation operator keeps its own kernel
+    lin2 = H.QLinear(K, N, bias=False, device="cuda", dtype=torch.float16, ops=H.FP16AccumMatMul(group_size=128))
+    lin2.wq = make_quantizer(fm["hbq_a_wgt"])
+    assert not lin2.prepare_decode()
