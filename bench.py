@@ -323,6 +323,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     act_quant = act_quant_record(dev, peaks) if rank == 0 else None
     # ---- the reference's own CUDA-core kernel on the same GPU and shape (rank 0, outside every timed region) ----
     ref_gpu = reference_gemm_record(lin.aq.q(x), lin.weight.data) if (rank == 0 and world == 1) else None
+    # ---- decode-sized GEMMs: the packed-weight kernel beside the fp16-operand ones (rank 0) ----
+    decode = decode_gemm_record(dev) if (rank == 0 and world == 1) else None
     torch.cuda.empty_cache()
 
     # ---- whole-model and collective sub-records ----
@@ -375,6 +377,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         }
         if ref_gpu is not None:
             line["ref_gpu"] = ref_gpu
+        if decode is not None:
+            line["decode_gemm"] = decode
         line.update(sub)
         if cpu is not None:
             line["cpu_baseline"] = cpu
@@ -426,6 +430,55 @@ def act_quant_record(dev, peaks, steps: int = 30):
         rec[name] = {"ms": ms, "achieved": gbs, "frac": gbs / peaks["hbm_gbs"], "bytes_per_elem": bpe}
     # the headline fraction is the configuration as stated
     rec["achieved"], rec["frac"] = rec["as_stated"]["achieved"], rec["as_stated"]["frac"]
+    return rec
+
+
+def decode_gemm_record(dev, rows: int = 16, copies: int = 8, reps: int = 6):
+    """Decode-sized linear layers of configs[3] (Llama-3-8B MLP: 4096 -> 14336 and 14336 -> 4096, `rows` tokens, HBQ-A
+    weights): the GEMM on the packed 4-bit weight (hbq_gemm_w4, 0.5625 B per weight) beside the same product on the
+    fp16 fake-quantised tensor by this library's tensor-core kernel and by F.linear (the reference's path,
+    src/module.py:64).  Each variant walks `copies` separate weights back to back so that no call finds its weight in
+    L2; us per call from CUDA events around the whole walk (host launch gaps included: the calls are this short)."""
+    import torch
+    import hbq_b200 as H
+    from hbq_b200 import blockquant_ext as ext
+    from hbq_b200.packed_gemm import W4Weight
+    q = H.HBQQuantizer(**dict(WGT, l2_block_size=8))
+    rec = {"rows": rows, "weight_format": "HBQ-A weight (E2M1, E5M3 per 128, Mix micro-scales per 8)", "unit": "us per call",
+           "note": "w4 = packed-weight kernel; fp16_tc = gemm_tc_kernel on the fp16 tensor; fp16_library = F.linear", "shapes": {}}
+
+    def walk(fns):
+        for f in fns:
+            f()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        best = None
+        for _ in range(3):
+            e0.record()
+            for _ in range(reps):
+                for f in fns:
+                    f()
+            e1.record()
+            torch.cuda.synchronize()
+            t = e0.elapsed_time(e1) * 1e3 / (reps * len(fns))
+            best = t if best is None else min(best, t)
+        return best
+
+    for N, Kd in ((14336, 4096), (4096, 14336)):
+        w = (0.02 * torch.randn(N, Kd, device=dev)).half()
+        packed, deq = q.quantize_packed(w, with_deq=True)
+        w4s = [W4Weight.from_packed(packed) for _ in range(copies)]
+        deqs = [deq.clone() for _ in range(copies)]
+        x = torch.randn(rows, Kd, device=dev).half()
+        outs = [torch.empty(rows, N, device=dev, dtype=torch.float16) for _ in range(copies)]
+        t4 = walk([(lambda ww=ww, o=o: ww.matmul(x, out=o)) for ww, o in zip(w4s, outs)])
+        tt = walk([(lambda d=d, o=o: ext.gemm_fp32_accum(x, d, b_is_nk=True, out=o)) for d, o in zip(deqs, outs)])
+        tl = walk([(lambda d=d, o=o: torch.mm(x, d.t(), out=o)) for d, o in zip(deqs, outs)])
+        rec["shapes"][f"N{N}_K{Kd}"] = {"w4": t4, "fp16_tc": tt, "fp16_library": tl, "w4_bytes": w4s[0].nbytes(),
+                                        "fp16_bytes": N * Kd * 2, "w4_GBs": w4s[0].nbytes() / t4 / 1e3,
+                                        "fp16_library_GBs": N * Kd * 2 / tl / 1e3}
+        del w4s, deqs, outs
+    torch.cuda.empty_cache()
     return rec
 
 
@@ -531,6 +584,24 @@ def run_sweep(args):
         print(json.dumps({"case": "gemm int8-psum", "ms": ms, "TFLOP/s": 2.0 * M * N * K / ms / 1e9, "shape": [M, K, N],
                           "status": H.gemm_status()}))
         del xq, wt
+    if want in (None, "gemm_w4"):            # the decode GEMM on the packed weight: 16 tokens, Llama-3-8B up projection
+        from hbq_b200.packed_gemm import W4Weight
+        packed = cls["hbq"](**dict(WGT, l2_block_size=8)).quantize_packed((0.02 * torch.randn(N, K, device="cuda")).half())
+        w4 = W4Weight.from_packed(packed)
+        x16 = torch.randn(16, K, device="cuda", dtype=torch.float16)
+        for _ in range(max(args.warmup, 3)):
+            w4.matmul(x16)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            w4.matmul(x16)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / args.steps
+        print(json.dumps({"case": "gemm on the packed weight (weight L2-resident after the first call)", "ms": ms, "shape": [16, K, N],
+                          "packed_bytes": w4.nbytes(), "status": H.gemm_status()}))
+        del w4, packed
     if want in (None, "softmax", "rmsnorm"):  # the fused row kernels at configs[3]'s shapes (one batch row of the prefill)
         from hbq_b200 import fused
         q = cls["hbq"](**SWEEP_FORMATS["hbq_a"][1])
@@ -835,7 +906,7 @@ def main():
                          "expert-parallel MoE blocks at N > 1)")
     ap.add_argument("--sweep", nargs="?", const="all", default=None,
                     help="instead of the benchmark line: quantize sweep of configs[2] and the KV-cache writes "
-                         "(all cases, or one: " + ", ".join(SWEEP_FORMATS) + ", hbq_a_packed, gemm, softmax, rmsnorm, k_write, v_write)")
+                         "(all cases, or one: " + ", ".join(SWEEP_FORMATS) + ", hbq_a_packed, gemm, gemm_w4, softmax, rmsnorm, k_write, v_write)")
     ap.add_argument("--tp-mlp", action="store_true",
                     help="instead of the benchmark line: the tensor-parallel MLP block of configs[3] over the launched ranks")
     ap.add_argument("--llama", action="store_true",
