@@ -99,19 +99,45 @@ class HBQLinearMethod:
     activations and multiplies.  The product is the reference's ``F.linear`` (fp32 accumulation) on the tensor-core
     kernel, whose 128-column tile serves decode-sized batches."""
 
-    def __init__(self, act_quantizer, wgt_quantizer):
+    def __init__(self, act_quantizer, wgt_quantizer, packed_weights: bool = False):
+        """``packed_weights``: keep each weight ONLY as 4-bit codes and scales in the tile order of ``hbq_gemm_w4``
+        (0.56 B per weight; formats and shapes outside that kernel keep the fp16 tensor) -- the engine then holds a
+        3.6x smaller model and every batch multiplies against codes expanded in shared memory."""
         self.act_quantizer = act_quantizer
         self.wgt_quantizer = wgt_quantizer
+        self.packed_weights = packed_weights
 
     @torch.inference_mode()
     def process_weights_after_loading(self, layer: torch.nn.Module) -> None:
         if getattr(layer, "hbq_weight_quantized", False) or getattr(layer, "weight", None) is None:
             return
-        layer.weight.data = self.wgt_quantizer.q(layer.weight.data).to(layer.weight.dtype)
+        w4 = None
+        if self.packed_weights and layer.weight.is_cuda and layer.weight.dtype == torch.float16 and \
+                hasattr(self.wgt_quantizer, "quantize_packed"):
+            from ._lib import HbqError
+            from .packed_gemm import W4Weight
+            try:
+                packed = self.wgt_quantizer.quantize_packed(layer.weight.data)
+                if W4Weight.supported(packed):
+                    w4 = W4Weight.from_packed(packed)
+            except (NotImplementedError, HbqError):
+                w4 = None
+        if w4 is not None:
+            layer.hbq_w4_weight = w4
+            layer.weight.data = torch.empty(0, dtype=layer.weight.dtype, device=layer.weight.device)
+        else:
+            layer.weight.data = self.wgt_quantizer.q(layer.weight.data).to(layer.weight.dtype)
         setattr(layer, "hbq_weight_quantized", True)
 
     def apply(self, layer: torch.nn.Module, x: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
         xq = self.act_quantizer.q(x)
+        w4 = getattr(layer, "hbq_w4_weight", None)
+        if w4 is not None:
+            x2d = xq.reshape(-1, xq.shape[-1])
+            y = torch.empty((x2d.shape[0], w4.shape[0]), dtype=torch.float16, device=x2d.device)
+            for r0 in range(0, x2d.shape[0], 128):
+                w4.matmul(x2d[r0:r0 + 128], bias, out=y[r0:r0 + 128])
+            return y.view(*x.shape[:-1], w4.shape[0])
         w = layer.weight
         if xq.is_cuda and xq.dtype == torch.float16 and w.dtype == torch.float16:
             y = ext.gemm_fp32_accum(xq.reshape(-1, xq.shape[-1]), w, b_is_nk=True, bias=bias)

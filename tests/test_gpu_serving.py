@@ -85,3 +85,27 @@ def test_linear_method_at_decode_shapes(tokens):
     assert y.shape == (tokens, N) and rel <= 2.0 ** -9, rel
     y3 = method.apply(layer, x.view(1, tokens, K), layer.bias)
     assert y3.shape == (1, tokens, N) and torch.equal(y3[0], y)
+
+
+def test_linear_method_on_packed_weights():
+    """``packed_weights``: the layer keeps 0.5625 B per weight and no fp16 tensor; outputs agree with the fp16 path."""
+    from hbq_b200 import serving
+    fm = load_formats()
+    K, N = 2048, 1024
+    g = torch.Generator(device="cuda").manual_seed(11)
+    w0 = (0.02 * torch.randn((N, K), device="cuda", generator=g)).half()
+    outs = []
+    for packed in (False, True):
+        method = serving.HBQLinearMethod(make_quantizer(fm["hbq_e_act"]), make_quantizer(fm["hbq_e_wgt"]), packed_weights=packed)
+        layer = torch.nn.Linear(K, N, bias=True, device="cuda", dtype=torch.float16)
+        layer.weight.data = w0.clone()
+        layer.bias.data = torch.linspace(-1, 1, N, device="cuda").half()
+        method.process_weights_after_loading(layer)
+        assert (layer.weight.numel() == 0) == packed
+        if packed:
+            assert layer.hbq_w4_weight.nbytes() * 128 * 128 == N * K * 9216
+        x = torch.randn((3, 50, K), device="cuda", generator=torch.Generator(device="cuda").manual_seed(12)).half()
+        outs.append(method.apply(layer, x, layer.bias.data))
+        assert outs[-1].shape == (3, 50, N)
+    rel = float((outs[0].double() - outs[1].double()).norm() / outs[0].double().norm())
+    assert rel <= 2.0 ** -9, rel
