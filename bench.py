@@ -445,7 +445,7 @@ def decode_gemm_record(dev, rows: int = 16, copies: int = 8, reps: int = 6):
     from hbq_b200.packed_gemm import W4Weight
     q = H.HBQQuantizer(**dict(WGT, l2_block_size=8))
     rec = {"rows": rows, "weight_format": "HBQ-A weight (E2M1, E5M3 per 128, Mix micro-scales per 8)", "unit": "us per call",
-           "note": "w4 = packed-weight kernel; fp16_tc = gemm_tc_kernel on the fp16 tensor; fp16_library = F.linear", "shapes": {}}
+           "note": "w4 = packed-weight kernel, codes as nibbles (0.5625 B per weight); w4_in_8bit_containers = the same codes one per byte (1.0625 B); fp16_tc = gemm_tc_kernel on the fp16 tensor; fp16_library = F.linear", "shapes": {}}
 
     def walk(fns):
         for f in fns:
@@ -468,16 +468,18 @@ def decode_gemm_record(dev, rows: int = 16, copies: int = 8, reps: int = 6):
         w = (0.02 * torch.randn(N, Kd, device=dev)).half()
         packed, deq = q.quantize_packed(w, with_deq=True)
         w4s = [W4Weight.from_packed(packed) for _ in range(copies)]
+        w8s = [W4Weight.from_packed(packed, container_bits=8) for _ in range(copies)]
         deqs = [deq.clone() for _ in range(copies)]
         x = torch.randn(rows, Kd, device=dev).half()
         outs = [torch.empty(rows, N, device=dev, dtype=torch.float16) for _ in range(copies)]
         t4 = walk([(lambda ww=ww, o=o: ww.matmul(x, out=o)) for ww, o in zip(w4s, outs)])
+        t8 = walk([(lambda ww=ww, o=o: ww.matmul(x, out=o)) for ww, o in zip(w8s, outs)])
         tt = walk([(lambda d=d, o=o: ext.gemm_fp32_accum(x, d, b_is_nk=True, out=o)) for d, o in zip(deqs, outs)])
         tl = walk([(lambda d=d, o=o: torch.mm(x, d.t(), out=o)) for d, o in zip(deqs, outs)])
-        rec["shapes"][f"N{N}_K{Kd}"] = {"w4": t4, "fp16_tc": tt, "fp16_library": tl, "w4_bytes": w4s[0].nbytes(),
+        rec["shapes"][f"N{N}_K{Kd}"] = {"w4": t4, "w4_in_8bit_containers": t8, "w8_bytes": w8s[0].nbytes(), "fp16_tc": tt, "fp16_library": tl, "w4_bytes": w4s[0].nbytes(),
                                         "fp16_bytes": N * Kd * 2, "w4_GBs": w4s[0].nbytes() / t4 / 1e3,
                                         "fp16_library_GBs": N * Kd * 2 / tl / 1e3}
-        del w4s, deqs, outs
+        del w4s, w8s, deqs, outs
     torch.cuda.empty_cache()
     return rec
 

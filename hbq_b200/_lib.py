@@ -77,12 +77,12 @@ def lib() -> ctypes.CDLL:
     L.hbq_gemm_workspace_bytes.argtypes = [i64, i64, i64, ci, ci, ci, ci]
     L.hbq_gemm_workspace_bytes.restype = i64
     L.hbq_gemm_uses_tensor_cores.argtypes = [i64, i64, i64, ci, ci, ci, ci]
-    L.hbq_gemm_w4_prepacked_bytes.argtypes = [i64, i64]
+    L.hbq_gemm_w4_prepacked_bytes.argtypes = [i64, i64, ci]
     L.hbq_gemm_w4_prepacked_bytes.restype = i64
-    L.hbq_gemm_w4_prepack.argtypes = [ctypes.POINTER(PackedOut), i64, i64, ctypes.POINTER(Format), vp, vp]
+    L.hbq_gemm_w4_prepack.argtypes = [ctypes.POINTER(PackedOut), i64, i64, ctypes.POINTER(Format), ci, vp, vp]
     L.hbq_gemm_w4_workspace_bytes.argtypes = [i64, i64, i64]
     L.hbq_gemm_w4_workspace_bytes.restype = i64
-    L.hbq_gemm_w4.argtypes = [vp, vp, vp, i64, i64, i64, ctypes.POINTER(Format), vp, vp, i64, vp]
+    L.hbq_gemm_w4.argtypes = [vp, vp, vp, i64, i64, i64, ctypes.POINTER(Format), ci, vp, vp, i64, vp]
     L.hbq_gemm_status.argtypes = [ctypes.POINTER(ci)]
     L.hbq_gemm_wait_selftest.argtypes = [vp, vp, vp, i64, i64, i64, ci, ci, ci, ctypes.c_uint32, vp]
     L.hbq_gemm_reserve_sms.argtypes = [ci]

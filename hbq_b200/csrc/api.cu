@@ -85,10 +85,10 @@ int transpose_launch(const void*, void*, int64_t, int64_t, cudaStream_t);
 int gemm_tc_status(int*);
 int gemm_tc_status_reset();
 int gemm_tc_reserve_sms(int n);
-int64_t gemm_w4_prepacked_bytes(int64_t, int64_t);
-int gemm_w4_prepack(const hbq_packed_out*, int64_t, int64_t, const hbq_format*, void*, cudaStream_t);
+int64_t gemm_w4_prepacked_bytes(int64_t, int64_t, int);
+int gemm_w4_prepack(const hbq_packed_out*, int64_t, int64_t, const hbq_format*, int, void*, cudaStream_t);
 int64_t gemm_w4_workspace_bytes(int64_t, int64_t, int64_t);
-int gemm_w4_launch(const void*, const void*, void*, int64_t, int64_t, int64_t, const hbq_format*, const void*, void*,
+int gemm_w4_launch(const void*, const void*, void*, int64_t, int64_t, int64_t, const hbq_format*, int, const void*, void*,
                    cudaStream_t, uint32_t);
 
 // ------------------------------------------------------------------------------------------
@@ -361,25 +361,29 @@ int hbq_gemm_wait_selftest(const void* A, const void* W, void* C, int64_t M, int
     return gemm_tc_launch_ex(A, W, C, M, N, K, mode, group_k, group_n, nullptr, (cudaStream_t)stream, poll_limit, 1);
 }
 
-int64_t hbq_gemm_w4_prepacked_bytes(int64_t N, int64_t K) { return gemm_w4_prepacked_bytes(N, K); }
+int64_t hbq_gemm_w4_prepacked_bytes(int64_t N, int64_t K, int container_bits)
+{
+    return gemm_w4_prepacked_bytes(N, K, container_bits);
+}
 
-int hbq_gemm_w4_prepack(const hbq_packed_out* in, int64_t N, int64_t K, const hbq_format* fmt, void* out, void* stream)
+int hbq_gemm_w4_prepack(const hbq_packed_out* in, int64_t N, int64_t K, const hbq_format* fmt, int container_bits,
+                        void* out, void* stream)
 {
     if (N <= 0 || K <= 0) return HBQ_ERR_ARG;
-    return gemm_w4_prepack(in, N, K, fmt, out, (cudaStream_t)stream);
+    return gemm_w4_prepack(in, N, K, fmt, container_bits, out, (cudaStream_t)stream);
 }
 
 int64_t hbq_gemm_w4_workspace_bytes(int64_t M, int64_t N, int64_t K) { return gemm_w4_workspace_bytes(M, N, K); }
 
 int hbq_gemm_w4(const void* X, const void* Wp, void* C, int64_t M, int64_t N, int64_t K, const hbq_format* fmt,
-                const void* bias, void* workspace, int64_t workspace_bytes, void* stream)
+                int container_bits, const void* bias, void* workspace, int64_t workspace_bytes, void* stream)
 {
     if (M < 0 || N < 0 || K < 0) return HBQ_ERR_ARG;
     if (M == 0 || N == 0) return HBQ_OK;
     const int64_t need = gemm_w4_workspace_bytes(M, N, K);
     if (need < 0) return HBQ_ERR_UNSUPPORTED;
     if (!workspace || workspace_bytes < need) return HBQ_ERR_WORKSPACE;
-    return gemm_w4_launch(X, Wp, C, M, N, K, fmt, bias, workspace, (cudaStream_t)stream, 0);
+    return gemm_w4_launch(X, Wp, C, M, N, K, fmt, container_bits, bias, workspace, (cudaStream_t)stream, 0);
 }
 
 int hbq_gemm_status(int* status_host)

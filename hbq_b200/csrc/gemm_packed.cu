@@ -30,7 +30,8 @@
 // 768 threads:
 //   warps 0-3   epilogue: one per quarter of the tensor-memory lanes; two accumulators alternate between segments
 //   warp 4      record producer: one bulk copy of a packed record per stage, six stages ahead
-//   warp 5      MMA issue (one lane), owner of the tensor-memory allocation
+//   warps 5, 7  MMA issue (one lane each: first / second 64-wide K tile of every stage, an accumulator each);
+//               warp 5 owns the tensor-memory allocation
 //   warp 6      X producer: two TMA loads (128 k of every token) into the operand stage the expansion is filling
 //   warps 8-23  expansion, two groups of eight warps on alternate stages: thread (row r, half hh) turns 64 codes into
 //               the 8 swizzled 16-byte chunks of its row in one of the stage's two K-major 128 x 64 tiles
@@ -49,9 +50,12 @@ int gemm_make_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t K, in
 
 constexpr int PK_ROWS = 128;                                  // weight rows per tile
 constexpr int PK_KB = 128;                                    // k per stage: one quantisation block
-constexpr int PK_CODE_BYTES = PK_ROWS * PK_KB / 2;            // 8192
 constexpr int PK_SIDE_BYTES = PK_ROWS * 8;                    // 1024
-constexpr int PK_REC_BYTES = PK_CODE_BYTES + PK_SIDE_BYTES;   // 9216
+// Two containers for the element codes: 4 bits ({sign, e1, e0, m}: 9216-byte records, 0.5625 B per weight) or 8 bits
+// (the top byte of the element value's fp16 pattern, sign included -- its low byte is zero: 17408-byte records,
+// 1.0625 B per weight).  The 4-bit form costs about 25 instructions per 8 codes to expand, the 8-bit form about 12.
+__host__ __device__ constexpr int pk_code_bytes(int cb) { return PK_ROWS * PK_KB * cb / 8; }
+__host__ __device__ constexpr int pk_rec_bytes(int cb) { return pk_code_bytes(cb) + PK_SIDE_BYTES; }
 constexpr int PK_EXP_BYTES = 2 * PK_ROWS * 128;               // two K-major 128 x 64 fp16 tiles
 constexpr int PK_NE = 3;                                      // expanded stages
 constexpr int PK_NL_MAX = 6;                                  // load stages (fewer when X tiles are large)
@@ -62,7 +66,7 @@ constexpr int PK_THREADS = (PK_EXP_WARP0 + PK_EXP_WARPS) * 32;
 constexpr int PK_CTRL_BYTES = 256;
 
 struct PkArgs {
-    const uint8_t* wp;          // prepacked weight [tiles][nblk][PK_REC_BYTES]
+    const uint8_t* wp;          // prepacked weight [tiles][nblk][record]
     __half* C;
     const __half* bias;
     float* ws;                  // [grid][2][m_pad][128] partial sums of segments that do not cover their tile's K
@@ -70,9 +74,10 @@ struct PkArgs {
     int M, N, K;
     int m_pad;                  // tokens rounded up to 16: the MMA's N
     int nblk, tiles, nl;
+    int ne;                     // operand stages: 3, or 2 when the tokens' tiles are large
     int64_t total;              // tiles * nblk stages
     uint32_t base2[2], step2[2];// micro-scale t = base + idx * step as packed fp16 pairs, per table
-    uint32_t acc_cols;          // tensor-memory columns of one accumulator (32, 64 or 128); two are allocated
+    uint32_t acc_cols;          // tensor-memory columns of one accumulator (32, 64 or 128); four are allocated
     uint32_t poll_limit;
 };
 
@@ -141,7 +146,19 @@ __device__ __forceinline__ int cta_of_stage(int64_t total, int64_t g, int G)
     return c;
 }
 
-template <int MS>       // log2(chunks of 8 per micro-block): 0 (micro-block 8) or 2 (micro-block 32)
+// Eight element values given as the top bytes of their fp16 patterns (two words) times the packed scale.
+template <bool TWO_STEP>
+__device__ __forceinline__ void expand8_bytes(uint32_t w0, uint32_t w1, uint32_t ts2, uint32_t t2, uint32_t s2, uint32_t* o)
+{
+    const uint32_t v[4] = {prmt(w0, 0u, 0x1404u), prmt(w0, 0u, 0x3424u), prmt(w1, 0u, 0x1404u), prmt(w1, 0u, 0x3424u)};
+    #pragma unroll
+    for (int p = 0; p < 4; ++p)
+        o[p] = TWO_STEP ? h2_bits(__hmul2(__hmul2(bits_h2(v[p]), bits_h2(t2)), bits_h2(s2)))
+                        : h2_bits(__hmul2(bits_h2(v[p]), bits_h2(ts2)));
+}
+
+// MS: log2(chunks of 8 per micro-block): 0 (micro-block 8) or 2 (micro-block 32); CB: bits of the code container
+template <int MS, int CB>
 __global__ void __launch_bounds__(PK_THREADS, 1)
 gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const PkArgs a)
 {
@@ -149,8 +166,10 @@ gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const PkArgs a)
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t exp0 = (raw + 1023u) & ~1023u;                    // expanded tiles (1024-byte aligned for the swizzle)
     const uint32_t ES = PK_EXP_BYTES + (uint32_t)a.m_pad * 256u;     // operand stage: expanded weight tiles + two X tiles
-    constexpr uint32_t LS = PK_REC_BYTES;                            // load stage: one packed record
-    const uint32_t ld0 = exp0 + PK_NE * ES;
+    constexpr uint32_t LS = pk_rec_bytes(CB);                        // load stage: one packed record
+    constexpr uint32_t CODE_BYTES = pk_code_bytes(CB);
+    const uint32_t ne = (uint32_t)a.ne;
+    const uint32_t ld0 = exp0 + ne * ES;
     const uint32_t ctrl_u = ld0 + (uint32_t)a.nl * LS;
     uint8_t* ctrl = smem_raw + (ctrl_u - raw);
     // control block: ld_full[6] ld_empty[6] ex_full[3] ex_empty[3] acc_full[2] acc_empty[2] (8 B each), then the
@@ -171,15 +190,15 @@ gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const PkArgs a)
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < PK_NL_MAX; ++s) { mbar_init(bar_lfull + 8 * s, 1); mbar_init(bar_lempty + 8 * s, PK_EXP_WARPS / 2); }
-        for (int s = 0; s < PK_NE; ++s) { mbar_init(bar_efull + 8 * s, PK_EXP_WARPS / 2 + 1); mbar_init(bar_eempty + 8 * s, 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(bar_afull + 8 * b, 1); mbar_init(bar_aempty + 8 * b, PK_EPI_WARPS); }
+        for (int s = 0; s < PK_NE; ++s) { mbar_init(bar_efull + 8 * s, PK_EXP_WARPS / 2 + 1); mbar_init(bar_eempty + 8 * s, 2); }
+        for (int b = 0; b < 2; ++b) { mbar_init(bar_afull + 8 * b, 2); mbar_init(bar_aempty + 8 * b, PK_EPI_WARPS); }
         *abort_flag = 0;
         *last_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 5) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(smem_u32(tmem_base_smem)), "r"(2u * a.acc_cols) : "memory");
+                     ::"r"(smem_u32(tmem_base_smem)), "r"(4u * a.acc_cols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
@@ -190,13 +209,13 @@ gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const PkArgs a)
     if (warp == 4) {
         // ================= record producer =================
         if (lane == 0) {
-            const uint8_t* src = a.wp + g0 * PK_REC_BYTES;           // the run's records are consecutive in memory
+            const uint8_t* src = a.wp + g0 * (int64_t)LS;            // the run's records are consecutive in memory
             uint32_t stage = 0, phase = 0;
             for (int i = 0; i < nst; ++i) {
                 if (!mbar_wait_parked(bar_lempty + 8 * stage, phase ^ 1u, abort_flag, 1, park_limit)) break;
                 const uint32_t bar = bar_lfull + 8 * stage;
                 mbar_expect_tx(bar, LS);
-                bulk_load(ld0 + stage * LS, src + (int64_t)i * PK_REC_BYTES, PK_REC_BYTES, bar);
+                bulk_load(ld0 + stage * LS, src + (int64_t)i * LS, LS, bar);
                 if (++stage == (uint32_t)a.nl) { stage = 0; phase ^= 1u; }
             }
         }
@@ -213,13 +232,18 @@ gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const PkArgs a)
                 mbar_expect_tx(bar, (uint32_t)a.m_pad * 256u);
                 tma_load_2d(dst, &mapX, kb * PK_KB, 0, bar);
                 tma_load_2d(dst + (uint32_t)a.m_pad * 128u, &mapX, kb * PK_KB + 64, 0, bar);
-                if (++es == PK_NE) { es = 0; eph ^= 1u; }
+                if (++es == ne) { es = 0; eph ^= 1u; }
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == 5 || warp == 7) {
         // ================= MMA issue =================
+        // Two issuing threads: the serial cost of issuing an MMA (about 90 cycles whatever its width) is what bounds a
+        // stage, so warp 5 issues the four MMAs of a stage's first 64-wide K tile and warp 7 those of the second, each
+        // into an accumulator of its own (MMAs of different threads are not ordered with each other); the epilogue
+        // adds the two.  Each thread's commit tracks its own MMAs, so the stage and accumulator barriers count two.
         // kind::f16: D fp32, A/B fp16, both K-major, M = 128 weight rows, N = m_pad tokens
         const uint32_t idesc = (1u << 4) | ((uint32_t)(a.m_pad >> 3) << 17) | ((uint32_t)(PK_ROWS >> 4) << 24);
+        const uint32_t h = warp == 7 ? 1u : 0u;
         const bool leader = elect_one();
         uint32_t es = 0, eph = 0;
         bool ok = true;
@@ -228,27 +252,24 @@ gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const PkArgs a)
             const int kb = (int)(g % a.nblk);
             const int len = (int)min((int64_t)(a.nblk - kb), g1 - g);
             const uint32_t buf = (uint32_t)j & 1u;
-            // the epilogue must have drained this accumulator's previous segment
+            // the epilogue must have drained this accumulator pair's previous segment
             if (!(ok = mbar_wait_warp(bar_aempty + 8 * buf, (((uint32_t)j >> 1) & 1u) ^ 1u, abort_flag, 7, a.poll_limit))) break;
-            const uint32_t d_tmem = tmem_base + buf * a.acc_cols;
+            const uint32_t d_tmem = tmem_base + (2u * buf + h) * a.acc_cols;
             for (int i = 0; i < len; ++i) {
                 // weights expanded and X tiles landed
                 if (!(ok = mbar_wait_warp(bar_efull + 8 * es, eph, abort_flag, 3, a.poll_limit))) break;
                 tc_fence_after();
                 if (leader) {
-                    const uint32_t wa = exp0 + es * ES, xa = wa + PK_EXP_BYTES;
+                    const uint32_t wa = exp0 + es * ES + h * (PK_ROWS * 128);
+                    const uint32_t xa = exp0 + es * ES + PK_EXP_BYTES + h * ((uint32_t)a.m_pad * 128u);
                     #pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        #pragma unroll
-                        for (int kk = 0; kk < 4; ++kk)
-                            tc_mma_f16(d_tmem, umma_desc(wa + h * (PK_ROWS * 128) + kk * 32),
-                                       umma_desc(xa + h * ((uint32_t)a.m_pad * 128u) + kk * 32), idesc, (i | h | kk) != 0 ? 1u : 0u);
-                    }
+                    for (int kk = 0; kk < 4; ++kk)
+                        tc_mma_f16(d_tmem, umma_desc(wa + kk * 32), umma_desc(xa + kk * 32), idesc, (i | kk) != 0 ? 1u : 0u);
                     tc_commit(bar_eempty + 8 * es);
                     if (i + 1 == len) tc_commit(bar_afull + 8 * buf);
                 }
                 __syncwarp();
-                if (++es == PK_NE) { es = 0; eph ^= 1u; }
+                if (++es == ne) { es = 0; eph ^= 1u; }
             }
             g += len;
         }
@@ -266,18 +287,21 @@ gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const PkArgs a)
         // group's NEXT stage are issued before this stage's arithmetic and read after it; a wait loop runs only when
         // one failed.
         bool pre_l = grp < nst && mbar_test(bar_lfull + 8 * ((uint32_t)grp % nl), ((uint32_t)grp / nl) & 1u);
-        bool pre_e = grp < nst && mbar_test(bar_eempty + 8 * ((uint32_t)grp % PK_NE), (((uint32_t)grp / PK_NE) & 1u) ^ 1u);
+        bool pre_e = grp < nst && mbar_test(bar_eempty + 8 * ((uint32_t)grp % ne), (((uint32_t)grp / ne) & 1u) ^ 1u);
         for (int i = grp; i < nst; i += 2) {
             const uint32_t ls = (uint32_t)i % nl, lph = ((uint32_t)i / nl) & 1u;
-            const uint32_t es = (uint32_t)i % PK_NE, eph = ((uint32_t)i / PK_NE) & 1u;
+            const uint32_t es = (uint32_t)i % ne, eph = ((uint32_t)i / ne) & 1u;
             if (!__all_sync(0xFFFFFFFFu, pre_l) && !mbar_wait_warp(bar_lfull + 8 * ls, lph, abort_flag, 4, a.poll_limit)) break;
             const uint32_t rec = ld0 + ls * LS;
-            uint32_t l2w, meta, cw[8];
-            asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(l2w), "=r"(meta) : "r"(rec + PK_CODE_BYTES + r * 8));
-            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
-                         : "=r"(cw[0]), "=r"(cw[1]), "=r"(cw[2]), "=r"(cw[3]) : "r"(rec + ((2 * hh) * PK_ROWS + r) * 16));
-            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
-                         : "=r"(cw[4]), "=r"(cw[5]), "=r"(cw[6]), "=r"(cw[7]) : "r"(rec + ((2 * hh + 1) * PK_ROWS + r) * 16));
+            // this thread's 64 codes: 16-byte pieces, rows contiguous inside a piece (2 pieces of 32 codes, or 4 of 16)
+            constexpr int NP = CB / 2;
+            uint32_t l2w, meta, cw[4 * NP];
+            asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(l2w), "=r"(meta) : "r"(rec + CODE_BYTES + r * 8));
+            #pragma unroll
+            for (int p = 0; p < NP; ++p)
+                asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(cw[4 * p]), "=r"(cw[4 * p + 1]), "=r"(cw[4 * p + 2]), "=r"(cw[4 * p + 3])
+                             : "r"(rec + ((NP * hh + p) * PK_ROWS + r) * 16));
             const uint32_t sc = meta & 0xFFFFu, s2 = sc * 0x10001u, tb = (meta >> 16) & 1u;
             const uint32_t base2 = tb ? a.base2[1] : a.base2[0], step2 = tb ? a.step2[1] : a.step2[0];
             // a scale in fp16's top binade could overflow t*s where (level*t)*s stays finite: multiply in two steps there
@@ -293,7 +317,7 @@ gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const PkArgs a)
             const bool more = i + 2 < nst;
             const uint32_t ni = (uint32_t)i + 2u;
             const bool nxt_l = more && mbar_test(bar_lfull + 8 * (ni % nl), (ni / nl) & 1u);
-            const bool nxt_e = more && mbar_test(bar_eempty + 8 * (ni % PK_NE), ((ni / PK_NE) & 1u) ^ 1u);
+            const bool nxt_e = more && mbar_test(bar_eempty + 8 * (ni % ne), ((ni / ne) & 1u) ^ 1u);
             uint32_t t2 = 0u, ts2 = 0u;
             if (!two_step) {
                 #pragma unroll
@@ -304,7 +328,8 @@ gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const PkArgs a)
                         ts2 = h2_bits(__hmul2(bits_h2(t2), bits_h2(s2)));
                     }
                     uint32_t o[4];
-                    expand8<false>(cw[c], ts2, t2, s2, o);
+                    if (CB == 4) expand8<false>(cw[c], ts2, t2, s2, o);
+                    else expand8_bytes<false>(cw[(2 * c) % (4 * NP)], cw[(2 * c + 1) % (4 * NP)], ts2, t2, s2, o);
                     asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};"
                                  ::"r"(out ^ ((uint32_t)c << 4)), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
                 }
@@ -314,7 +339,8 @@ gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const PkArgs a)
                     const uint32_t idx = (l2q >> (2 * (c >> MS))) & 3u;
                     t2 = base2 + idx * step2;
                     uint32_t o[4];
-                    expand8<true>(cw[c], 0u, t2, s2, o);
+                    if (CB == 4) expand8<true>(cw[c], 0u, t2, s2, o);
+                    else expand8_bytes<true>(cw[(2 * c) % (4 * NP)], cw[(2 * c + 1) % (4 * NP)], 0u, t2, s2, o);
                     asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};"
                                  ::"r"(out ^ ((uint32_t)c << 4)), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
                 }
@@ -343,8 +369,11 @@ gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const PkArgs a)
             float* part = a.ws + ((int64_t)cta * 2 + (tile == (int)(g0 / a.nblk) ? 0 : 1)) * a.m_pad * PK_ROWS + nloc;
             const __half bv = a.bias ? a.bias[gn] : __float2half_rn(0.f);
             for (int c0 = 0; c0 < a.m_pad; c0 += 32) {
-                float v[32];
-                tc_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * a.acc_cols + c0, v);
+                float v[32], v1[32];
+                tc_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (2u * buf) * a.acc_cols + c0, v);
+                tc_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (2u * buf + 1u) * a.acc_cols + c0, v1);
+                #pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] += v1[i];             // first K tiles + second K tiles of the stages
                 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
                     const int m = c0 + i;
@@ -425,7 +454,7 @@ gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const PkArgs a)
     }
     if (warp == 5) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2u * a.acc_cols) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(4u * a.acc_cols) : "memory");
     }
 }
 
@@ -440,23 +469,41 @@ struct PrepackArgs {
     int K, nblk, l2_bytes;
 };
 
+template <int CB>
 __global__ void __launch_bounds__(256) gemm_w4_prepack_kernel(const PrepackArgs a)
 {
-    constexpr int SLOTS = PK_REC_BYTES / 16;                  // 576 per record: 512 of codes, 64 of side records
+    constexpr int CODE_SLOTS = pk_code_bytes(CB) / 16;        // 16-byte slots of codes per record: 512 or 1024
+    constexpr int SLOTS = pk_rec_bytes(CB) / 16;              // ... plus 64 of side records
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= a.total) return;
     const int slot = (int)(i % SLOTS);
     const int64_t rec = i / SLOTS;
     const int kb = (int)(rec % a.nblk);
     const int64_t tile = rec / a.nblk;
-    if (slot < 512) {
-        const int q = slot >> 7, r = slot & 127;
-        a.out[i] = *reinterpret_cast<const uint4*>(a.codes + (tile * PK_ROWS + r) * (int64_t)(a.K / 2) + kb * 64 + q * 16);
+    if (slot < CODE_SLOTS) {
+        const int q = slot >> 7, r = slot & 127;                                   // piece, row
+        const uint8_t* src = a.codes + (tile * PK_ROWS + r) * (int64_t)(a.K / 2) + kb * 64;
+        if (CB == 4) {
+            a.out[i] = *reinterpret_cast<const uint4*>(src + q * 16);             // 32 codes as they are
+        } else {
+            // 16 codes -> the top bytes of their E2M1 values 0, .5, 1, 1.5, 2, 3, 4, 6 as fp16, sign in bit 7
+            const uint2 nib = *reinterpret_cast<const uint2*>(src + q * 8);
+            const unsigned long long n64 = ((unsigned long long)nib.y << 32) | nib.x;
+            constexpr unsigned long long LUT = 0x464442403E3C3800ull;
+            uint32_t w[4] = {0u, 0u, 0u, 0u};
+            #pragma unroll
+            for (int e = 0; e < 16; ++e) {
+                const uint32_t c = (uint32_t)(n64 >> (4 * e)) & 0xFu;
+                const uint32_t b = (uint32_t)(LUT >> (8 * (c & 7u))) & 0xFFu;
+                w[e >> 2] |= (b | ((c & 8u) << 4)) << (8 * (e & 3));
+            }
+            a.out[i] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
     } else {
         uint32_t w[4];
         #pragma unroll
         for (int j = 0; j < 2; ++j) {
-            const int64_t blk = (tile * PK_ROWS + (slot - 512) * 2 + j) * a.nblk + kb;
+            const int64_t blk = (tile * PK_ROWS + (slot - CODE_SLOTS) * 2 + j) * a.nblk + kb;
             uint32_t l2w = 0;
             for (int b = 0; b < a.l2_bytes; ++b) l2w |= (uint32_t)a.l2[blk * a.l2_bytes + b] << (8 * b);
             w[2 * j] = l2w;
@@ -496,16 +543,19 @@ static bool w4_shape(int64_t M, int64_t N, int64_t K)
            N <= (1ll << 24) && K <= (1ll << 24);
 }
 
-int64_t gemm_w4_prepacked_bytes(int64_t N, int64_t K)
+static bool w4_container(int cb) { return cb == 4 || cb == 8; }
+
+int64_t gemm_w4_prepacked_bytes(int64_t N, int64_t K, int container_bits)
 {
-    if (N <= 0 || K <= 0 || (N % PK_ROWS) || (K % PK_KB)) return -1;
-    return (N / PK_ROWS) * (K / PK_KB) * (int64_t)PK_REC_BYTES;
+    if (N <= 0 || K <= 0 || (N % PK_ROWS) || (K % PK_KB) || !w4_container(container_bits)) return -1;
+    return (N / PK_ROWS) * (K / PK_KB) * (int64_t)pk_rec_bytes(container_bits);
 }
 
-int gemm_w4_prepack(const hbq_packed_out* in, int64_t N, int64_t K, const hbq_format* f, void* out, cudaStream_t stream)
+int gemm_w4_prepack(const hbq_packed_out* in, int64_t N, int64_t K, const hbq_format* f, int container_bits, void* out,
+                    cudaStream_t stream)
 {
     if (!in || !out || !in->codes || !in->scale_u8 || !in->l2_packed) return HBQ_ERR_ARG;
-    if (!w4_format(f, nullptr, nullptr) || !w4_shape(1, N, K)) return HBQ_ERR_UNSUPPORTED;
+    if (!w4_format(f, nullptr, nullptr) || !w4_shape(1, N, K) || !w4_container(container_bits)) return HBQ_ERR_UNSUPPORTED;
     if (f->l2_scheme == HBQ_L2_MIX && !in->scheme) return HBQ_ERR_ARG;
     if ((reinterpret_cast<uintptr_t>(in->codes) | reinterpret_cast<uintptr_t>(out)) & 15) return HBQ_ERR_ALIGN;
     PrepackArgs a;
@@ -513,8 +563,10 @@ int gemm_w4_prepack(const hbq_packed_out* in, int64_t N, int64_t K, const hbq_fo
     a.scheme = f->l2_scheme == HBQ_L2_MIX ? in->scheme : nullptr;
     a.out = (uint4*)out;
     a.K = (int)K; a.nblk = (int)(K / PK_KB); a.l2_bytes = (128 / f->l2_block_size) * 2 / 8;
-    a.total = gemm_w4_prepacked_bytes(N, K) / 16;
-    gemm_w4_prepack_kernel<<<(unsigned)((a.total + 255) / 256), 256, 0, stream>>>(a);
+    a.total = gemm_w4_prepacked_bytes(N, K, container_bits) / 16;
+    const unsigned grid = (unsigned)((a.total + 255) / 256);
+    if (container_bits == 4) gemm_w4_prepack_kernel<4><<<grid, 256, 0, stream>>>(a);
+    else gemm_w4_prepack_kernel<8><<<grid, 256, 0, stream>>>(a);
     HBQ_LAUNCH_CHECK("gemm_w4_prepack_kernel");
     return HBQ_OK;
 }
@@ -528,16 +580,25 @@ int64_t gemm_w4_workspace_bytes(int64_t M, int64_t N, int64_t K)
     return (int64_t)sms * 2 * m_pad * PK_ROWS * 4 + tiles * 4;        // two partial-sum slots per CTA, one counter per tile
 }
 
+template <int MS, int CB>
+static int launch_packed(const CUtensorMap& mx, const PkArgs& a, int grid, size_t smem, cudaStream_t stream)
+{
+    { const int rc = ensure_dynamic_smem(gemm_packed_kernel<MS, CB>, smem); if (rc) return rc; }
+    gemm_packed_kernel<MS, CB><<<grid, PK_THREADS, smem, stream>>>(mx, a);
+    HBQ_LAUNCH_CHECK("gemm_packed_kernel");
+    return HBQ_OK;
+}
+
 // workspace: gemm_w4_workspace_bytes() bytes, 16-byte aligned, zeroed once by the caller (the kernel leaves the tile
 // counters at zero again); one call at a time per workspace.
 int gemm_w4_launch(const void* X, const void* Wp, void* C, int64_t M, int64_t N, int64_t K, const hbq_format* f,
-                   const void* bias, void* workspace, cudaStream_t stream, uint32_t poll_limit)
+                   int container_bits, const void* bias, void* workspace, cudaStream_t stream, uint32_t poll_limit)
 {
     PkArgs a;
     memset(&a, 0, sizeof(a));
     int ms = 0;
     if (!X || !Wp || !C || !workspace) return HBQ_ERR_ARG;
-    if (!w4_format(f, &a, &ms) || !w4_shape(M, N, K)) return HBQ_ERR_UNSUPPORTED;
+    if (!w4_format(f, &a, &ms) || !w4_shape(M, N, K) || !w4_container(container_bits)) return HBQ_ERR_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(Wp) | reinterpret_cast<uintptr_t>(workspace)) & 15)
         return HBQ_ERR_ALIGN;
     if ((reinterpret_cast<uintptr_t>(C) | reinterpret_cast<uintptr_t>(bias)) & 1) return HBQ_ERR_ALIGN;
@@ -551,8 +612,11 @@ int gemm_w4_launch(const void* X, const void* Wp, void* C, int64_t M, int64_t N,
     const int grid = (int)(a.total < sms ? a.total : sms);
     a.ws = (float*)workspace;
     a.counters = (int*)((uint8_t*)workspace + (int64_t)sms * 2 * a.m_pad * PK_ROWS * 4);
-    const uint32_t LS = PK_REC_BYTES, ES = PK_EXP_BYTES + (uint32_t)a.m_pad * 256u;
-    const uint32_t avail = 227u * 1024u - 1024u - PK_NE * ES - PK_CTRL_BYTES;
+    const uint32_t LS = (uint32_t)pk_rec_bytes(container_bits), ES = PK_EXP_BYTES + (uint32_t)a.m_pad * 256u;
+    // three operand stages unless that leaves fewer than four record stages (many tokens and the 8-bit container)
+    a.ne = PK_NE;
+    uint32_t avail = 227u * 1024u - 1024u - (uint32_t)a.ne * ES - PK_CTRL_BYTES;
+    if (avail / LS < 4) { a.ne = 2; avail = 227u * 1024u - 1024u - 2u * ES - PK_CTRL_BYTES; }
     a.nl = (int)(avail / LS);
     if (a.nl > PK_NL_MAX) a.nl = PK_NL_MAX;
     // An even count: the two expansion groups take alternate stages, so with an even ring a slot always serves the same
@@ -565,16 +629,9 @@ int gemm_w4_launch(const void* X, const void* Wp, void* C, int64_t M, int64_t N,
     a.poll_limit = poll_limit ? poll_limit : (1u << 23);
     CUtensorMap mx;
     { const int rc = gemm_make_map(&mx, X, M, K, a.m_pad); if (rc) return rc; }
-    const size_t smem = 1024 + (size_t)PK_NE * ES + (size_t)a.nl * LS + PK_CTRL_BYTES;
-    if (ms == 0) {
-        { const int rc = ensure_dynamic_smem(gemm_packed_kernel<0>, smem); if (rc) return rc; }
-        gemm_packed_kernel<0><<<grid, PK_THREADS, smem, stream>>>(mx, a);
-    } else {
-        { const int rc = ensure_dynamic_smem(gemm_packed_kernel<2>, smem); if (rc) return rc; }
-        gemm_packed_kernel<2><<<grid, PK_THREADS, smem, stream>>>(mx, a);
-    }
-    HBQ_LAUNCH_CHECK("gemm_packed_kernel");
-    return HBQ_OK;
+    const size_t smem = 1024 + (size_t)a.ne * ES + (size_t)a.nl * LS + PK_CTRL_BYTES;
+    if (container_bits == 4) return ms == 0 ? launch_packed<0, 4>(mx, a, grid, smem, stream) : launch_packed<2, 4>(mx, a, grid, smem, stream);
+    return ms == 0 ? launch_packed<0, 8>(mx, a, grid, smem, stream) : launch_packed<2, 8>(mx, a, grid, smem, stream);
 }
 
 int gemm_w4_status(int* host_out)

@@ -21,8 +21,9 @@ MAX_ROWS = 128                      # tokens per call the kernel takes
 class W4Weight:
     """A quantised weight ``[N, K]`` prepacked for ``hbq_gemm_w4``."""
 
-    def __init__(self, data: torch.Tensor, fmt: "_lib.Format", shape: Tuple[int, int]):
+    def __init__(self, data: torch.Tensor, fmt: "_lib.Format", shape: Tuple[int, int], container_bits: int = 4):
         self.data, self.fmt, self.shape = data, fmt, (int(shape[0]), int(shape[1]))
+        self.container_bits = container_bits
         self._workspaces: Dict[Tuple[int, int], torch.Tensor] = {}
 
     @staticmethod
@@ -31,26 +32,31 @@ class W4Weight:
         if packed.codes is None or not packed.codes.is_cuda or len(packed.shape) != 2:
             return False
         N, K = packed.shape
-        return int(_lib.lib().hbq_gemm_w4_prepacked_bytes(N, K)) > 0 and packed.l2_packed is not None and \
+        return int(_lib.lib().hbq_gemm_w4_prepacked_bytes(N, K, 4)) > 0 and packed.l2_packed is not None and \
             packed.sign is None
 
     @classmethod
-    def from_packed(cls, packed: PackedTensor) -> "W4Weight":
-        """Rearrange the planes of ``quantize_packed`` (``hbq_gemm_w4_prepack``); raises for formats outside the kernel."""
+    def from_packed(cls, packed: PackedTensor, container_bits: int = 4) -> "W4Weight":
+        """Rearrange the planes of ``quantize_packed`` (``hbq_gemm_w4_prepack``); raises for formats outside the kernel.
+        ``container_bits``: 4 keeps the codes as nibbles (0.5625 B per weight); 8 stores each code as the top byte of its
+        value's fp16 pattern (1.0625 B per weight), which halves the expansion's instructions -- the faster form on B200,
+        where instruction issue and not bytes bounds the kernel."""
         N, K = packed.shape
         L = _lib.lib()
-        nbytes = int(L.hbq_gemm_w4_prepacked_bytes(N, K))
+        nbytes = int(L.hbq_gemm_w4_prepacked_bytes(N, K, container_bits))
         if nbytes <= 0:
-            raise _lib.HbqError(f"hbq_gemm_w4: weight shape {tuple(packed.shape)} is not a multiple of 128 x 128")
+            raise _lib.HbqError(f"hbq_gemm_w4: weight shape {tuple(packed.shape)} is not a multiple of 128 x 128 "
+                                f"(or container_bits {container_bits} is not 4 or 8)")
         dev = packed.codes.device
         out = torch.empty(nbytes, dtype=torch.uint8, device=dev)
         po = _lib.PackedOut(packed.codes.data_ptr(), None, packed.scale_u8.data_ptr(), None,
                             packed.l2_packed.data_ptr() if packed.l2_packed is not None else None, None,
                             packed.scheme.data_ptr() if packed.scheme is not None else None)
         with _lib.device_guard(dev):
-            rc = L.hbq_gemm_w4_prepack(ctypes.byref(po), N, K, ctypes.byref(packed.fmt), _ptr(out), _stream_ptr(dev))
+            rc = L.hbq_gemm_w4_prepack(ctypes.byref(po), N, K, ctypes.byref(packed.fmt), container_bits, _ptr(out),
+                                       _stream_ptr(dev))
         _lib.check(rc, "hbq_gemm_w4_prepack")
-        return cls(out, packed.fmt, (N, K))
+        return cls(out, packed.fmt, (N, K), container_bits)
 
     def nbytes(self) -> int:
         return self.data.numel()
@@ -82,7 +88,7 @@ class W4Weight:
             return c
         ws = self._workspace(M)
         with _lib.device_guard(x.device):
-            rc = _lib.lib().hbq_gemm_w4(_ptr(x), _ptr(self.data), _ptr(c), M, N, K, ctypes.byref(self.fmt), _ptr(bias),
+            rc = _lib.lib().hbq_gemm_w4(_ptr(x), _ptr(self.data), _ptr(c), M, N, K, ctypes.byref(self.fmt), self.container_bits, _ptr(bias),
                                         _ptr(ws), ws.numel(), _stream_ptr(x.device))
         _lib.check(rc, "hbq_gemm_w4")
         return c

@@ -248,9 +248,14 @@ int hbq_gemm_wait_selftest(const void* A, const void* W, void* C, int64_t M, int
  * 1 <= M <= 128.  HBQ_ERR_UNSUPPORTED otherwise (callers then use hbq_gemm on the fp16 tensor).
  *
  * hbq_gemm_w4_prepack turns the planes of hbq_quantize (codes, scale_u8, l2_packed, scheme; W is [N, K]) into the
- * kernel's operand, hbq_gemm_w4_prepacked_bytes(N, K) bytes, 16-byte aligned: one 9216-byte record per (128 rows,
+ * kernel's operand, hbq_gemm_w4_prepacked_bytes(N, K, container_bits) bytes, 16-byte aligned: one record per (128 rows,
  * 128 k) -- four 32-element pieces of every row's codes with the rows contiguous, then per row the 32 bits of
  * micro-scale indices, the block scale as fp16 and the table bit.  Done once per weight.
+ *
+ * container_bits: 4 -- codes as stored, {sign, e1, e0, m} per nibble, records of 9216 bytes (0.5625 B per weight);
+ * 8 -- each code as the top byte of its value's fp16 pattern (the low byte is zero for E2M1), records of 17408 bytes
+ * (1.0625 B per weight).  Same values either way; the 8-bit container halves the instructions of the expansion, which,
+ * not the bytes, is what bounds the 4-bit form on B200.  prepack and gemm must be given the same value.
  *
  * workspace: hbq_gemm_w4_workspace_bytes(M, N, K) bytes (-1: shape not served), 16-byte aligned, ZEROED ONCE by
  * the caller before its first use; the kernel leaves it usable for the next call on the same stream.  The work is
@@ -258,12 +263,13 @@ int hbq_gemm_wait_selftest(const void* A, const void* W, void* C, int64_t M, int
  * parts of a tile that different SMs computed meet here as fp32 partial sums (two slots per SM) and are added in a
  * fixed order, so results do not vary from run to run; one counter per tile tells which SM finishes it.  After a
  * call that hbq_gemm_status reports as failed, zero it again. */
-int64_t hbq_gemm_w4_prepacked_bytes(int64_t N, int64_t K);
-int hbq_gemm_w4_prepack(const hbq_packed_out* in, int64_t N, int64_t K, const hbq_format* fmt, void* out,
-                        void* stream);
+int64_t hbq_gemm_w4_prepacked_bytes(int64_t N, int64_t K, int container_bits);
+int hbq_gemm_w4_prepack(const hbq_packed_out* in, int64_t N, int64_t K, const hbq_format* fmt, int container_bits,
+                        void* out, void* stream);
 int64_t hbq_gemm_w4_workspace_bytes(int64_t M, int64_t N, int64_t K);
 int hbq_gemm_w4(const void* X, const void* Wp, void* C, int64_t M, int64_t N, int64_t K,
-                const hbq_format* fmt, const void* bias, void* workspace, int64_t workspace_bytes, void* stream);
+                const hbq_format* fmt, int container_bits, const void* bias, void* workspace,
+                int64_t workspace_bytes, void* stream);
 
 /* The tensor-core kernel is persistent: one CTA per SM, each holding most of an SM's shared
  * memory, with a fixed round-robin share of the tiles.  A kernel of another stream that already

@@ -33,8 +33,10 @@ def test_library_exports_every_declared_symbol():
     assert L.hbq_gemm_workspace_bytes(8, 64, 128, 1, 2, 64, 0) == 0
     assert L.hbq_absmax_scratch_bytes() > 0
     # packed-weight GEMM: one 9216-byte record per (128 rows, 128 k); other shapes are not served
-    assert L.hbq_gemm_w4_prepacked_bytes(14336, 4096) == 14336 * 4096 * 9216 // (128 * 128) == 33030144
-    assert L.hbq_gemm_w4_prepacked_bytes(14336, 4000) == -1 and L.hbq_gemm_w4_prepacked_bytes(100, 4096) == -1
+    assert L.hbq_gemm_w4_prepacked_bytes(14336, 4096, 4) == 14336 * 4096 * 9216 // (128 * 128) == 33030144
+    assert L.hbq_gemm_w4_prepacked_bytes(14336, 4096, 8) == 14336 * 4096 * 17408 // (128 * 128)
+    assert L.hbq_gemm_w4_prepacked_bytes(14336, 4000, 4) == -1 and L.hbq_gemm_w4_prepacked_bytes(100, 4096, 4) == -1
+    assert L.hbq_gemm_w4_prepacked_bytes(14336, 4096, 5) == -1
     assert L.hbq_gemm_w4_workspace_bytes(129, 4096, 4096) == -1 and L.hbq_gemm_w4_workspace_bytes(0, 4096, 4096) == -1
 
 

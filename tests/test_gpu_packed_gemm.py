@@ -1,4 +1,4 @@
-"""GPU: the GEMM on the packed 4-bit weight (hbq_gemm_w4) against the same product on the fp16 fake-quantised tensor
+"""GPU: the GEMM on the packed 4-bit weight (hbq_gemm_w4, both code containers) against the same product on the fp16 fake-quantised tensor
 the reference keeps (src/ptq.py:349, F.linear in src/module.py:64).
 
 Two bars.  (1) The values the kernel expands in shared memory are the fake-quantised weights BIT FOR BIT: one-hot rows
@@ -17,7 +17,7 @@ REL_TOL = 2.0 ** -9
 FAR_ULP_FRACTION = 0.01
 
 
-def _weight(name, N, K, seed):
+def _weight(name, N, K, seed, bits=4):
     import hbq_b200 as H
     from hbq_b200.packed_gemm import W4Weight
     q = make_quantizer(load_formats()[name])
@@ -27,7 +27,7 @@ def _weight(name, N, K, seed):
     packed, deq = q.quantize_packed(w, with_deq=True)
     assert W4Weight.supported(packed)
     assert torch.equal(H.dequantize_packed(packed).view(torch.int16), deq.view(torch.int16))
-    return W4Weight.from_packed(packed), deq
+    return W4Weight.from_packed(packed, container_bits=bits), deq
 
 
 def _ulps(a, b):
@@ -37,15 +37,16 @@ def _ulps(a, b):
     return (ia - ib).abs()
 
 
+@pytest.mark.parametrize("bits", [4, 8])
 @pytest.mark.parametrize("name", ["hbq_a_wgt", "hbq_e_wgt", "hbq_fp1", "hbq_fpm100"])
 @pytest.mark.parametrize("shape", [(256, 512), (1024, 4096)])
-def test_expanded_values_are_the_fake_quantised_weights(name, shape):
+def test_expanded_values_are_the_fake_quantised_weights(name, shape, bits):
     spec = load_formats()[name]
     if spec["mbit"] != 1 or spec["block_size"] != 128 or spec["l2_block_size"] not in (8, 32) or spec["l2_sc_bit"] != 2:
         pytest.skip("not a 4-bit block-128 weight format")
     N, K = shape
-    w4, deq = _weight(name, N, K, seed=N + K)
-    assert w4.nbytes() == N * K * 9216 // (128 * 128)
+    w4, deq = _weight(name, N, K, seed=N + K, bits=bits)
+    assert w4.nbytes() == N * K * (9216 if bits == 4 else 17408) // (128 * 128)
     for rows in (128, 16, 5):
         for off in range(0, K, 128 if K <= 512 else 1024):
             x = torch.zeros((rows, K), device="cuda", dtype=torch.float16)
@@ -59,12 +60,13 @@ def test_expanded_values_are_the_fake_quantised_weights(name, shape):
             assert bool((c[~nz] == 0).all())
 
 
+@pytest.mark.parametrize("bits", [4, 8])
 @pytest.mark.parametrize("name", ["hbq_a_wgt", "hbq_e_wgt"])
 @pytest.mark.parametrize("N,K", [(14336, 4096), (4096, 14336), (1024, 4096), (128, 128)])
-def test_against_the_fp16_operand_product(name, N, K):
+def test_against_the_fp16_operand_product(name, N, K, bits):
     import hbq_b200 as H
     from hbq_b200 import blockquant_ext as ext
-    w4, deq = _weight(name, N, K, seed=1)
+    w4, deq = _weight(name, N, K, seed=1, bits=bits)
     aq = make_quantizer(load_formats()["hbq_a_act" if name == "hbq_a_wgt" else "hbq_e_act"])
     g = torch.Generator(device="cuda").manual_seed(N)
     bias = torch.randn(N, device="cuda", generator=g).half()
