@@ -333,12 +333,12 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         one = llama_prefill_record(rank, world, dev, 2, 1, 1, layers=args.llama_layers, parallel=False)
         sub["llama_prefill"] = {"one_gpu": one}
         if world > 1:
-            tp = llama_prefill_record(rank, world, dev, 2, 1, args.llama_pieces, layers=args.llama_layers)
+            tp = llama_prefill_record(rank, world, dev, 3, 2, args.llama_pieces, layers=args.llama_layers)
             sub["llama_prefill"]["tensor_parallel"] = tp
             sub["llama_prefill"]["speedup_over_one_gpu"] = one["ms_per_forward"] / tp["ms_per_forward"]
             m1 = llama_prefill_record(rank, world, dev, 2, 1, 1, layers=args.llama_layers, batch=4, seq=4096, parallel=False,
                                       mixtral=True)
-            mp_ = llama_prefill_record(rank, world, dev, 2, 1, 1, layers=args.llama_layers, batch=4, seq=4096, mixtral=True)
+            mp_ = llama_prefill_record(rank, world, dev, 3, 2, 1, layers=args.llama_layers, batch=4, seq=4096, mixtral=True)
             sub["mixtral_prefill"] = {"one_gpu": m1, "expert_parallel": mp_,
                                       "speedup_over_one_gpu": m1["ms_per_forward"] / mp_["ms_per_forward"]}
             sa = argparse.Namespace(**vars(args))

@@ -122,26 +122,48 @@ class ExpertParallelMoE(nn.Module):
         return dequantize_packed(arrived)
 
     # ---- forward ---------------------------------------------------------------------------------
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    # The block needs one host read (the per-rank row counts size the all-to-all).  It is split in two so that a caller
+    # with several independent batches can put other launches between the exchange of the counts and the read:
+    # ``begin`` routes, exchanges the counts and starts their copy to pinned host memory; ``finish`` waits for that
+    # copy only, then dispatches, runs the local experts and combines.  ``forward`` is the two back to back.
+    def begin(self, x: torch.Tensor) -> dict:
         lead = x.shape[:-1]
         x2d = x.reshape(-1, self.hidden)
-        T = x2d.shape[0]
         w, idx = self.route(x2d)
         flat_e = idx.reshape(-1)                                       # expert of copy c = (token c // k, choice c % k)
         order = torch.sort(flat_e, stable=True).indices               # copies grouped by expert, hence by rank
         src_rows = torch.div(order, self.top_k, rounding_mode="floor")
         per_expert = torch.bincount(flat_e, minlength=self.num_experts)
-
         if self.world == 1:
-            recv_per_expert = per_expert.tolist()                      # the call's one host read
+            counts = per_expert.unsqueeze(0)
+        else:
+            # every rank's copies per expert, in one small all-gather: row r is what rank r sends
+            rows = [torch.empty_like(per_expert) for _ in range(self.world)]
+            dist.all_gather(rows, per_expert.contiguous(), group=self.group)
+            counts = torch.stack(rows)
+        st = dict(lead=lead, x2d=x2d, w=w, order=order, src_rows=src_rows)
+        if counts.is_cuda:
+            host = torch.empty(counts.shape, dtype=counts.dtype, pin_memory=True)
+            host.copy_(counts, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
+            st["counts"], st["event"] = host, ev
+        else:
+            st["counts"], st["event"] = counts, None
+        return st
+
+    def finish(self, st: dict) -> torch.Tensor:
+        lead, x2d, w, order, src_rows = st["lead"], st["x2d"], st["w"], st["order"], st["src_rows"]
+        T = x2d.shape[0]
+        if st["event"] is not None:
+            st["event"].synchronize()                                  # the call's one host read
+        tl = st["counts"].tolist()
+        if self.world == 1:
+            recv_per_expert = tl[0]
             xq = self._dispatch(x2d, src_rows, None, None)
             send_counts = recv_counts = None
         else:
-            # every rank's copies per expert, in one small all-gather and ONE host read: row r is what rank r sends,
-            # so my row gives the split sizes of what I send and my experts' columns those of what I receive
-            rows = [torch.empty_like(per_expert) for _ in range(self.world)]
-            dist.all_gather(rows, per_expert.contiguous(), group=self.group)
-            tl = torch.stack(rows).tolist()
+            # my row gives the split sizes of what I send and my experts' columns those of what I receive
             send_counts = [sum(tl[self.rank][d * self.per_rank:(d + 1) * self.per_rank]) for d in range(self.world)]
             got_l = [tl[s][self.e0:self.e0 + self.per_rank] for s in range(self.world)]
             recv_counts = [sum(g) for g in got_l]
@@ -177,3 +199,6 @@ class ExpertParallelMoE(nn.Module):
         y = torch.zeros((T, self.hidden), dtype=x2d.dtype, device=x2d.device)
         y.index_add_(0, src_rows, y_rows * wc)
         return y.reshape(*lead, self.hidden)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return self.finish(self.begin(x))

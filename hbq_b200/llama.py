@@ -423,10 +423,15 @@ class QLlamaModel(nn.Module):
             if layer.block_sparse_moe is not None:
                 # sparse MoE on this rank's own tokens: router on the normalised rows, copies to the experts' ranks
                 # and back by all-to-all (inside the block); no gather / scatter of rows in this half
+                # (two passes over the pieces: the host reads one piece's row counts while the next piece's kernels
+                # are already queued, so the read never leaves the GPU without work)
+                states = []
                 for p in pieces:
                     self._await(p)
                     h, p.x = rmsnorm_quantize(p.x, layer.post_attention_layernorm, a.eps, None, residual=p.branch)
-                    p.branch = layer.block_sparse_moe(h)
+                    states.append(layer.block_sparse_moe.begin(h))
+                for p, st in zip(pieces, states):
+                    p.branch = layer.block_sparse_moe.finish(st)
                 continue
             for p in pieces:
                 self._await(p)
