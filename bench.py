@@ -728,6 +728,9 @@ def run_llama(args, rank: int, world: int, local_rank: int):
     dev = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+    if args.tp_reserve_sms:
+        from hbq_b200.gemm import gemm_reserve_sms
+        gemm_reserve_sms(args.tp_reserve_sms)
     if args.mixtral:
         rec = llama_prefill_record(rank, world, dev, args.steps, args.warmup, args.llama_pieces, layers=args.llama_layers,
                                    batch=4, seq=4096, mixtral=True)
@@ -928,7 +931,7 @@ def main():
                     help="--tp-mlp: pieces the row-parallel layer cuts its rows into (1 = all-reduce after the whole GEMM; "
                          "default: chosen from the per-rank GEMM size)")
     ap.add_argument("--tp-reserve-sms", type=int, default=0,
-                    help="--tp-mlp: SMs the row-parallel GEMM leaves free for the all-reduce running beside it")
+                    help="--tp-mlp / --llama / --mixtral: SMs the tensor-core GEMMs leave free for the collective running beside them")
     args = ap.parse_args()
     if args.sweep is not None:
         run_sweep(args)
