@@ -6,7 +6,8 @@ Importing the package does not need a GPU; the CUDA library (``lib/libhbq_b200.s
 """
 from . import blockquant_ext  # noqa: F401
 from ._lib import HbqError, launch_count  # noqa: F401
-from .gemm import gemm, gemm_status, gemm_status_reset  # noqa: F401
+from .gemm import gemm, gemm_reserve_sms, gemm_status, gemm_status_reset  # noqa: F401
+from .packed_gemm import W4Weight  # noqa: F401
 from .fused import rmsnorm_quantize, softmax_quantize  # noqa: F401
 from .kvcache import swiglu_quantize, write_k_cache, write_v_cache  # noqa: F401
 from .llama import mixtral_8x7b, LlamaArch, QLlamaAttention, QLlamaDecoderLayer, QLlamaMLP, QLlamaModel  # noqa: F401
@@ -22,4 +23,4 @@ from .quantizer import (HBQQuantizer, MXExQuantizer, MXFPQuantizer, MXINTQuantiz
 __all__ = ["HBQQuantizer", "MXFPQuantizer", "MXINTQuantizer", "MXExQuantizer", "VSQQuantizer", "_QBase", "FP16AccumMatMul", "QLinear",
            "PTQConfig", "load_quant_config", "blockquant_ext", "gemm", "gemm_status", "gemm_status_reset", "PackedTensor",
            "dequantize_packed", "HbqError", "launch_count", "get_max_norm", "get_min_norm", "get_min_subnorm",
-           "write_k_cache", "write_v_cache", "swiglu_quantize", "rmsnorm_quantize", "softmax_quantize", "ColumnParallelQLinear", "RowParallelQLinear", "LlamaArch", "mixtral_8x7b", "FP32AccumMatMul", "QLlamaModel", "QLlamaAttention", "QLlamaMLP", "QLlamaDecoderLayer", "ExpertParallelMoE", "QuantExpert"]
+           "write_k_cache", "write_v_cache", "swiglu_quantize", "rmsnorm_quantize", "softmax_quantize", "ColumnParallelQLinear", "RowParallelQLinear", "LlamaArch", "mixtral_8x7b", "FP32AccumMatMul", "QLlamaModel", "QLlamaAttention", "QLlamaMLP", "QLlamaDecoderLayer", "ExpertParallelMoE", "QuantExpert", "W4Weight", "gemm_reserve_sms"]

@@ -163,3 +163,18 @@ def test_reciprocal_division_is_exact():
         fast = (x * (np.float32(1) / s)).astype(np.float16)
         keep = exact.astype(np.float64) >= 2.0 ** -14          # subnormal quotients always quantise to 0
         assert np.array_equal(bits(exact[keep]), bits(fast[keep])), s
+
+
+def test_packed_weight_wrapper_without_a_gpu():
+    """Host side of the packed-weight GEMM: CPU tensors and shapes outside the kernel are reported as not served, and
+    nothing falls back to a CPU product."""
+    torch = pytest.importorskip("torch")
+    import hbq_b200 as H
+    from hbq_b200 import _lib
+    fmt = _lib.Format(_lib.KIND_HBQ, 2, 1, 5, 3, 128, 0, 0, 0, 8, 2, _lib.L2_SCHEMES.index("Mix"), 0, 0)
+    u8 = lambda *shape: torch.zeros(shape, dtype=torch.uint8)
+    packed = H.PackedTensor(torch.Size((256, 256)), torch.float16, fmt, u8(256, 128), None, u8(256, 2), u8(256, 2, 4), u8(256, 2))
+    assert not H.W4Weight.supported(packed)                       # planes on the host
+    lin = H.QLinear(256, 256, bias=False)
+    assert not lin.prepare_decode() and lin.w4_weight is None     # CPU layer: unchanged
+
