@@ -148,3 +148,35 @@ def test_linear_layer_on_the_packed_weight():
     lin2 = H.QLinear(K, N, bias=False, device="cuda", dtype=torch.float16, ops=H.FP16AccumMatMul(group_size=128))
     lin2.wq = make_quantizer(fm["hbq_a_wgt"])
     assert not lin2.prepare_decode()
+
+
+def test_cuda_graph_capture_of_a_decode_step():
+    """A decode step on the packed weight (activation quantize + hbq_gemm_w4) allocates and synchronises nothing of its
+    own once warmed up, so a serving engine can capture it in a CUDA graph and replay it on new tokens."""
+    import hbq_b200 as H
+    fm = load_formats()
+    K, N, rows = 2048, 1024, 8
+    lin = H.QLinear(K, N, bias=True, device="cuda", dtype=torch.float16, check_finite=False)
+    g0 = torch.Generator(device="cuda").manual_seed(21)
+    lin.weight.data = (0.02 * torch.randn((N, K), device="cuda", generator=g0)).half()
+    lin.bias.data = torch.randn(N, device="cuda", generator=g0).half()
+    lin.wq, lin.aq = make_quantizer(fm["hbq_e_wgt"]), make_quantizer(fm["hbq_e_act"])
+    assert lin.prepare_decode(drop_fp16=True)
+    x_static = torch.randn((rows, K), device="cuda", generator=g0).half()
+    with torch.no_grad():
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                lin(x_static)
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            y_static = lin(x_static)
+        for seed in (22, 23, 24):
+            x_new = torch.randn((rows, K), device="cuda", generator=torch.Generator(device="cuda").manual_seed(seed)).half()
+            x_static.copy_(x_new)
+            graph.replay()
+            torch.cuda.synchronize()
+            assert torch.equal(y_static, lin(x_new))
+    assert H.gemm_status() == 0
