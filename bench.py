@@ -438,7 +438,7 @@ def decode_gemm_record(dev, rows: int = 16, copies: int = 8, reps: int = 6):
     weights): the GEMM on the packed 4-bit weight (hbq_gemm_w4, 0.5625 B per weight) beside the same product on the
     fp16 fake-quantised tensor by this library's tensor-core kernel and by F.linear (the reference's path,
     src/module.py:64).  Each variant walks `copies` separate weights back to back so that no call finds its weight in
-    L2; us per call from CUDA events around the whole walk (host launch gaps included: the calls are this short)."""
+    L2; the walk is replayed from a CUDA graph and timed with CUDA events: us per call on the device."""
     import torch
     import hbq_b200 as H
     from hbq_b200 import blockquant_ext as ext
@@ -448,20 +448,31 @@ def decode_gemm_record(dev, rows: int = 16, copies: int = 8, reps: int = 6):
            "note": "w4 = packed-weight kernel, codes as nibbles (0.5625 B per weight); w4_in_8bit_containers = the same codes one per byte (1.0625 B); fp16_tc = gemm_tc_kernel on the fp16 tensor; fp16_library = F.linear", "shapes": {}}
 
     def walk(fns):
-        for f in fns:
-            f()
+        # the walk over the copies is captured in a CUDA graph and replayed, so that the time per call is the device's
+        # (kernel plus the gap to the next kernel of the graph), not the host's launch path
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                for f in fns:
+                    f()
+        torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for f in fns:
+                f()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         best = None
         for _ in range(3):
             e0.record()
             for _ in range(reps):
-                for f in fns:
-                    f()
+                graph.replay()
             e1.record()
             torch.cuda.synchronize()
             t = e0.elapsed_time(e1) * 1e3 / (reps * len(fns))
             best = t if best is None else min(best, t)
+        del graph
         return best
 
     for N, Kd in ((14336, 4096), (4096, 14336)):

@@ -31,7 +31,7 @@ class QLinear(nn.Linear):
         self.packed_weight = None
         self.w4_weight = None          # the packed weight in the decode GEMM's tile order (prepare_decode)
         self.w4_max_rows = 0           # batches up to this many rows take it while the fp16 tensor is kept; 0: none --
-                                       # on B200 the packed kernel runs at about 0.8x the library fp16 GEMM for
+                                       # on B200 the packed kernel runs at about 0.65x the library fp16 GEMM for
                                        # 1..16 rows (its limit is instruction issue, not bytes), so what it buys is
                                        # the 3.6x smaller weight (prepare_decode(drop_fp16=True)), not time
 
