@@ -35,11 +35,13 @@
 //   warp 6      X producer: two TMA loads (128 k of every token) into the operand stage the expansion is filling
 //   warps 8-23  expansion, two groups of eight warps on alternate stages: thread (row r, half hh) turns 64 codes into
 //               the 8 swizzled 16-byte chunks of its row in one of the stage's two K-major 128 x 64 tiles
-// What bounds a stage (measured with per-role cycle stamps): the MMA thread's serial chain -- about 90 cycles per
-// issued MMA whatever its width, eight per stage -- and the expansion's ~25 half-rate instructions per 8 codes; so
-// the MMA thread waits on ONE barrier per stage (completed by the expansion warps' arrivals and the X tiles' bytes
-// together) and commits once, and the expansion warps issue the barrier tests of their next stage before the
-// arithmetic of the current one, because a test costs hundreds of cycles of latency even when it succeeds.
+// What bounds a stage (measured with per-role cycle stamps) is latency, not bytes or arithmetic: a record takes two to
+// three thousand cycles from its bulk copy to its barrier, an mbarrier test or arrival costs the issuing warp a few
+// hundred cycles even when it succeeds at once, an issued MMA about 90 cycles whatever its width.  Hence the MMA
+// threads wait on ONE barrier per stage (completed by the expansion warps' arrivals and the X tiles' bytes together)
+// and commit once, and the expansion warps issue the barrier tests of their next stage before the arithmetic of the
+// current one.  With container_bits = 8 each code is stored as the top byte of its value's fp16 pattern (17408-byte
+// records): the same values, half the expansion's instructions.
 #include "tc_dev.cuh"
 #include <math.h>
 #include <mutex>
