@@ -90,6 +90,8 @@ int gemm_w4_prepack(const hbq_packed_out*, int64_t, int64_t, const hbq_format*, 
 int64_t gemm_w4_workspace_bytes(int64_t, int64_t, int64_t);
 int gemm_w4_launch(const void*, const void*, void*, int64_t, int64_t, int64_t, const hbq_format*, int, const void*, void*,
                    cudaStream_t, uint32_t);
+bool gemm_w16_eligible(int64_t, int64_t, int64_t);
+int gemm_w16_launch(const void*, const void*, void*, int64_t, int64_t, int64_t, const void*, void*, cudaStream_t);
 
 // ------------------------------------------------------------------------------------------
 // Packed codes -> fake-quantised fp16/bf16 tensor.
@@ -313,10 +315,22 @@ int hbq_gemm_uses_tensor_cores(int64_t M, int64_t N, int64_t K, int b_is_nk, int
     return gemm_tc_eligible(M, N, K, mode, group_k, group_n) ? 1 : 0;
 }
 
+// Decode-sized fp32-accumulation products whose 128-column tiles would not fill the SMs run the stream-K pipeline
+// (gemm_packed.cu) when the caller hands over its workspace; without one they take the tile-per-CTA kernel.
+// Measured on B200 (16 tokens): [4096, 14336] 34 us against 63 us, [4096, 4096] 21 against 23; with 112 tiles
+// ([14336, 4096]) or more than 32 tokens the tile-per-CTA kernel is the faster one.
+static bool decode_stream_k(int64_t M, int64_t N, int64_t K, int mode)
+{
+    int sms = 0;
+    return mode == HBQ_ACC_FP32 && M <= 32 && gemm_w16_eligible(M, N, K) && device_sms(&sms) == HBQ_OK && (N / 128) * 2 <= sms;
+}
+
 int64_t hbq_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int b_is_nk, int mode, int group_k, int group_n)
 {
-    if (b_is_nk || !gemm_tc_eligible(M, N, K, mode, group_k, group_n)) return 0;
-    return N * K * 2;      // eligible operands have N, K <= 2^30: the product fits
+    if (!gemm_tc_eligible(M, N, K, mode, group_k, group_n)) return 0;
+    const int64_t sk = decode_stream_k(M, N, K, mode) ? gemm_w4_workspace_bytes(M, N, K) : 0;
+    const int64_t tr = b_is_nk ? 0 : N * K * 2;      // eligible operands have N, K <= 2^30: the product fits
+    return (tr + 15) / 16 * 16 + (sk > 0 ? sk : 0);
 }
 
 int hbq_gemm(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int b_is_nk, int mode,
@@ -329,11 +343,18 @@ int hbq_gemm(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_
     const bool aligned = (((uintptr_t)A | (uintptr_t)B | (uintptr_t)C | (uintptr_t)bias) & 15) == 0;
     if (K > 0 && aligned && gemm_tc_eligible(M, N, K, mode, group_k, group_n)) {
         const void* W = B;
+        int64_t used = 0;
         if (!b_is_nk) {
             if (!workspace || workspace_bytes < N * K * 2 || ((uintptr_t)workspace & 15)) return HBQ_ERR_WORKSPACE;
             rc = transpose_launch(B, workspace, K, N, st);
             if (rc) return rc;
             W = workspace;
+            used = (N * K * 2 + 15) / 16 * 16;
+        }
+        if (decode_stream_k(M, N, K, mode) && workspace && !((uintptr_t)workspace & 15)) {
+            const int64_t sk = gemm_w4_workspace_bytes(M, N, K);
+            if (sk > 0 && workspace_bytes >= used + sk)
+                return gemm_w16_launch(A, W, C, M, N, K, bias, (uint8_t*)workspace + used, st);
         }
         return gemm_tc_launch(A, W, C, M, N, K, mode, group_k, group_n, bias, st);
     }

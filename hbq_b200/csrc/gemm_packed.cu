@@ -59,7 +59,8 @@ constexpr int PK_SIDE_BYTES = PK_ROWS * 8;                    // 1024
 __host__ __device__ constexpr int pk_code_bytes(int cb) { return PK_ROWS * PK_KB * cb / 8; }
 __host__ __device__ constexpr int pk_rec_bytes(int cb) { return pk_code_bytes(cb) + PK_SIDE_BYTES; }
 constexpr int PK_EXP_BYTES = 2 * PK_ROWS * 128;               // two K-major 128 x 64 fp16 tiles
-constexpr int PK_NE = 3;                                      // expanded stages
+constexpr int PK_NE = 3;                                      // operand stages when the weight is expanded here
+constexpr int PK_NE_MAX = 6;                                  // ... when fp16 weight tiles come straight from TMA
 constexpr int PK_NL_MAX = 6;                                  // load stages (fewer when X tiles are large)
 constexpr int PK_EPI_WARPS = 4;
 constexpr int PK_EXP_WARPS = 16;
@@ -162,7 +163,7 @@ __device__ __forceinline__ void expand8_bytes(uint32_t w0, uint32_t w1, uint32_t
 // MS: log2(chunks of 8 per micro-block): 0 (micro-block 8) or 2 (micro-block 32); CB: bits of the code container
 template <int MS, int CB>
 __global__ void __launch_bounds__(PK_THREADS, 1)
-gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const PkArgs a)
+gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CUtensorMap mapW, const PkArgs a)
 {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
@@ -177,9 +178,10 @@ gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const PkArgs a)
     // control block: ld_full[6] ld_empty[6] ex_full[3] ex_empty[3] acc_full[2] acc_empty[2] (8 B each), then the
     // tensor-memory base, the abort flag and the "this CTA completes the tile" flag
     const uint32_t bar_lfull = ctrl_u, bar_lempty = ctrl_u + 8 * PK_NL_MAX;
-    const uint32_t bar_efull = ctrl_u + 16 * PK_NL_MAX, bar_eempty = bar_efull + 8 * PK_NE;
-    const uint32_t bar_afull = bar_eempty + 8 * PK_NE, bar_aempty = bar_afull + 16;
-    constexpr int CTRL_WORDS = 16 * PK_NL_MAX + 16 * PK_NE + 32;
+    const uint32_t bar_efull = ctrl_u + 16 * PK_NL_MAX, bar_eempty = bar_efull + 8 * PK_NE_MAX;
+    const uint32_t bar_afull = bar_eempty + 8 * PK_NE_MAX, bar_aempty = bar_afull + 16;
+    constexpr int CTRL_WORDS = 16 * PK_NL_MAX + 16 * PK_NE_MAX + 32;
+    static_assert(CTRL_WORDS + 16 <= PK_CTRL_BYTES, "control block");
     uint32_t* tmem_base_smem = reinterpret_cast<uint32_t*>(ctrl + CTRL_WORDS);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(ctrl + CTRL_WORDS + 8);
     volatile int* last_flag = reinterpret_cast<volatile int*>(ctrl + CTRL_WORDS + 12);
@@ -192,7 +194,8 @@ gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const PkArgs a)
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < PK_NL_MAX; ++s) { mbar_init(bar_lfull + 8 * s, 1); mbar_init(bar_lempty + 8 * s, PK_EXP_WARPS / 2); }
-        for (int s = 0; s < PK_NE; ++s) { mbar_init(bar_efull + 8 * s, PK_EXP_WARPS / 2 + 1); mbar_init(bar_eempty + 8 * s, 2); }
+        // operands ready: the expansion group's eight warps + the X tiles' bytes, or (fp16 weight) the two producers' bytes
+        for (int s = 0; s < PK_NE_MAX; ++s) { mbar_init(bar_efull + 8 * s, CB == 16 ? 2 : PK_EXP_WARPS / 2 + 1); mbar_init(bar_eempty + 8 * s, 2); }
         for (int b = 0; b < 2; ++b) { mbar_init(bar_afull + 8 * b, 2); mbar_init(bar_aempty + 8 * b, PK_EPI_WARPS); }
         *abort_flag = 0;
         *last_flag = 0;
@@ -210,7 +213,22 @@ gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const PkArgs a)
 
     if (warp == 4) {
         // ================= record producer =================
-        if (lane == 0) {
+        if (CB == 16) {
+            // fp16 weight: its two K-major 128 x 64 tiles go by TMA straight into the operand stage
+            if (lane == 0) {
+                uint32_t es = 0, eph = 0;
+                for (int i = 0; i < nst; ++i) {
+                    if (!mbar_wait(bar_eempty + 8 * es, eph ^ 1u, abort_flag, 1, a.poll_limit)) break;
+                    const uint32_t dst = exp0 + es * ES, bar = bar_efull + 8 * es;
+                    const int64_t g = g0 + i;
+                    const int kb = (int)(g % a.nblk), row0 = (int)(g / a.nblk) * PK_ROWS;
+                    mbar_expect_tx(bar, PK_EXP_BYTES);
+                    tma_load_2d(dst, &mapW, kb * PK_KB, row0, bar);
+                    tma_load_2d(dst + PK_ROWS * 128, &mapW, kb * PK_KB + 64, row0, bar);
+                    if (++es == ne) { es = 0; eph ^= 1u; }
+                }
+            }
+        } else if (lane == 0) {
             const uint8_t* src = a.wp + g0 * (int64_t)LS;            // the run's records are consecutive in memory
             uint32_t stage = 0, phase = 0;
             for (int i = 0; i < nst; ++i) {
@@ -275,7 +293,7 @@ gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const PkArgs a)
             }
             g += len;
         }
-    } else if (warp >= PK_EXP_WARP0) {
+    } else if (warp >= PK_EXP_WARP0 && CB != 16) {
         // ================= expansion =================
         // Two groups of eight warps take alternate stages, so that one group's arithmetic runs under the other's
         // stores, fence and barrier traffic; thread (row r, half hh) of a group turns 64 codes into the 8 chunks of its
@@ -583,12 +601,61 @@ int64_t gemm_w4_workspace_bytes(int64_t M, int64_t N, int64_t K)
 }
 
 template <int MS, int CB>
-static int launch_packed(const CUtensorMap& mx, const PkArgs& a, int grid, size_t smem, cudaStream_t stream)
+static int launch_packed(const CUtensorMap& mx, const CUtensorMap& mw, const PkArgs& a, int grid, size_t smem, cudaStream_t stream)
 {
     { const int rc = ensure_dynamic_smem(gemm_packed_kernel<MS, CB>, smem); if (rc) return rc; }
-    gemm_packed_kernel<MS, CB><<<grid, PK_THREADS, smem, stream>>>(mx, a);
+    gemm_packed_kernel<MS, CB><<<grid, PK_THREADS, smem, stream>>>(mx, mw, a);
     HBQ_LAUNCH_CHECK("gemm_packed_kernel");
     return HBQ_OK;
+}
+
+// The same pipeline on an fp16 weight [N, K] (no expansion: TMA puts the weight tiles straight into the operand
+// stages): the fp32-accumulation GEMM for decode-sized M, where giving a CTA whole 128-column tiles over the full K
+// would leave most SMs idle.  Equal runs of (tile, block) stages per SM; partial tiles meet in the workspace.
+// It takes as long as the packed forms (32-35 us for 16 tokens x [14336, 4096]), which shows that neither the
+// expansion nor the record stream bounds this pipeline: each MMA-issuing thread visits every stage, and a visit --
+// seeing the barrier, four MMAs, two commits -- is about a thousand cycles whatever the operands are.
+bool gemm_w16_eligible(int64_t M, int64_t N, int64_t K)
+{
+    int sms = 0;
+    return w4_shape(M, N, K) && device_sms(&sms) == HBQ_OK && N / PK_ROWS <= sms;
+}
+
+int gemm_w16_launch(const void* X, const void* W, void* C, int64_t M, int64_t N, int64_t K, const void* bias, void* workspace,
+                    cudaStream_t stream)
+{
+    if (!X || !W || !C || !workspace) return HBQ_ERR_ARG;
+    if (!gemm_w16_eligible(M, N, K)) return HBQ_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(workspace)) & 15)
+        return HBQ_ERR_ALIGN;
+    if ((reinterpret_cast<uintptr_t>(C) | reinterpret_cast<uintptr_t>(bias)) & 1) return HBQ_ERR_ALIGN;
+    PkArgs a;
+    memset(&a, 0, sizeof(a));
+    int sms = 0;
+    { const int rc = device_sms(&sms); if (rc) return rc; }
+    a.C = (__half*)C; a.bias = (const __half*)bias;
+    a.M = (int)M; a.N = (int)N; a.K = (int)K;
+    a.m_pad = (int)((M + 15) / 16 * 16);
+    a.nblk = (int)(K / PK_KB); a.tiles = (int)(N / PK_ROWS);
+    a.total = (int64_t)a.tiles * a.nblk;
+    const int grid = (int)(a.total < sms ? a.total : sms);
+    a.ws = (float*)workspace;
+    a.counters = (int*)((uint8_t*)workspace + (int64_t)sms * 2 * a.m_pad * PK_ROWS * 4);
+    const uint32_t ES = PK_EXP_BYTES + (uint32_t)a.m_pad * 256u;
+    const uint32_t budget = 227u * 1024u - 1024u - PK_CTRL_BYTES;
+    a.ne = (int)(budget / ES);
+    if (a.ne > PK_NE_MAX) a.ne = PK_NE_MAX;
+    if (a.ne < 2) return HBQ_ERR_UNSUPPORTED;
+    a.nl = 0;
+    a.acc_cols = a.m_pad <= 32 ? 32u : (a.m_pad <= 64 ? 64u : 128u);
+    a.poll_limit = 1u << 23;
+    CUtensorMap mx, mw;
+    { const int rc = gemm_make_map(&mx, X, M, K, a.m_pad); if (rc) return rc; }
+    { const int rc = gemm_make_map(&mw, W, N, K, PK_ROWS); if (rc) return rc; }
+    // the tile counters must read zero; the workspace is the caller's scratch, so they are cleared here
+    HBQ_CUDA_TRY(cudaMemsetAsync(a.counters, 0, (size_t)a.tiles * 4, stream));
+    const size_t smem = 1024 + (size_t)a.ne * ES + PK_CTRL_BYTES;
+    return launch_packed<0, 16>(mx, mw, a, grid, smem, stream);
 }
 
 // workspace: gemm_w4_workspace_bytes() bytes, 16-byte aligned, zeroed once by the caller (the kernel leaves the tile
@@ -632,8 +699,8 @@ int gemm_w4_launch(const void* X, const void* Wp, void* C, int64_t M, int64_t N,
     CUtensorMap mx;
     { const int rc = gemm_make_map(&mx, X, M, K, a.m_pad); if (rc) return rc; }
     const size_t smem = 1024 + (size_t)a.ne * ES + (size_t)a.nl * LS + PK_CTRL_BYTES;
-    if (container_bits == 4) return ms == 0 ? launch_packed<0, 4>(mx, a, grid, smem, stream) : launch_packed<2, 4>(mx, a, grid, smem, stream);
-    return ms == 0 ? launch_packed<0, 8>(mx, a, grid, smem, stream) : launch_packed<2, 8>(mx, a, grid, smem, stream);
+    if (container_bits == 4) return ms == 0 ? launch_packed<0, 4>(mx, mx, a, grid, smem, stream) : launch_packed<2, 4>(mx, mx, a, grid, smem, stream);
+    return ms == 0 ? launch_packed<0, 8>(mx, mx, a, grid, smem, stream) : launch_packed<2, 8>(mx, mx, a, grid, smem, stream);
 }
 
 int gemm_w4_status(int* host_out)

@@ -46,8 +46,9 @@ def gemm(a: torch.Tensor, b: torch.Tensor, mode: int, group_k: int = 0, group_n:
             rc = L.hbq_gemm_simt(_ptr(a), _ptr(b), _ptr(c), M, N, K, int(b_is_nk), mode, group_k, group_n,
                                  _ptr(bias), stream)
         else:
-            # only the [K,N] layout needs scratch (for the transposed operand)
-            ws_bytes = 0 if b_is_nk else int(L.hbq_gemm_workspace_bytes(M, N, K, 0, mode, group_k, group_n))
+            # scratch: the transposed operand of the [K,N] layout, and the partial sums of decode-sized fp32 products
+            # that run as equal runs of K blocks per SM
+            ws_bytes = int(L.hbq_gemm_workspace_bytes(M, N, K, int(b_is_nk), mode, group_k, group_n))
             ws = torch.empty(ws_bytes, dtype=torch.uint8, device=a.device) if ws_bytes else None
             rc = L.hbq_gemm(_ptr(a), _ptr(b), _ptr(c), M, N, K, int(b_is_nk), mode, group_k, group_n,
                             _ptr(bias), _ptr(ws), ws_bytes, stream)
