@@ -1,5 +1,5 @@
 // Decode-shape GEMM that reads the HBQ weight as packed 4-bit codes and scales (0.5625 B per weight instead of
-// the 2 B of the fp16 fake-quantised tensor) and expands them to fp16 in shared memory in front of the tensor core.
+// the 2 B of the fp16 fake-quantised tensor) and expands them to fp16 in tensor memory in front of the tensor core.
 //
 //   C[M,N] = X[M,K] * deq(Wp)[N,K]^T     M <= 128 tokens, fp32 accumulation, fp16 output
 //
@@ -11,8 +11,14 @@
 // like the quantizer's fp16(fp16(level * t) * s).
 //
 // Operands are swapped with respect to gemm_tc.cu: the 128 weight rows of a tile are the M side of the MMA
-// (A operand, expanded here), the tokens its N side (B operand, X through TMA, zero filled beyond M), so the MMA's
-// cost follows the token count.  The accumulator D^T[n, m] sits in tensor memory, lane = weight row.
+// (A operand), the tokens its N side (B operand, X through TMA, zero filled beyond M), so the MMA's cost follows the
+// token count.  The A operand is read from TENSOR MEMORY: lane = weight row, a 32-bit column = two consecutive k, 64
+// columns per stage of 128 k.  The expansion warps write it there with tcgen05.st (each warp the lane quarter it may
+// access), so the expanded weights never pass through shared memory: writing 32 KB per stage and having the tensor
+// core read it back was, with the record and the X tiles, some 90 KB of shared-memory traffic per 9 KB record and
+// the bound of the earlier design.  The accumulator D^T[n, m] sits in tensor memory as well; the SM's 512 columns
+// hold four accumulators (two issuers x two segments in flight) of 32 or 64 columns and six or four expanded stages.
+// More than 64 tokens are two launches.
 //
 // Prepacked weight (hbq_gemm_w4_prepack): one 9216-byte record per (tile of 128 rows, block of 128 k) -- what one
 // pipeline stage consumes, fetched with ONE bulk async copy:
@@ -20,28 +26,32 @@
 //                                32-bit word in nibble j as {sign, e1, e0, m}; rows are contiguous so that a warp's
 //                                16-byte reads (one row per lane) hit every bank once
 //   [128 rows][8 B]              micro-scale indices (2 bits each, 32 bits), the block scale as fp16, the table bit
+// A byte of two codes becomes an fp16 pair with one cvt.rn.f16x2.e2m1x2 (the codes ARE E2M1), then one multiply by the
+// packed scale.  With container_bits = 8 each code is stored as the top byte of its value's fp16 pattern
+// (17408-byte records): the same values through a byte permute instead of the conversion.
 //
-// Work split: the (tile, block) records form one sequence of tiles * K/128 stages; CTA c of G (one per SM) takes the
-// c-th of G equal runs of it, whatever tile boundaries fall inside ("stream-K"), so every SM streams the same number
-// of bytes.  A run is a sequence of segments (tile, blocks kb0..kb1); a segment that covers its tile's whole K goes
-// straight to C, the others leave fp32 partial sums in a workspace and the CTA that completes a tile adds its
-// segments in CTA order (deterministic) and writes C.
+// Work split: the (tile, block) records form one sequence of tiles * K/128 stages.  Either every CTA takes whole
+// tiles (nothing to fix up), or CTA c of G (one per SM) takes the c-th of G equal runs of the sequence, whatever tile
+// boundaries fall inside ("stream-K"), so that every SM streams the same number of bytes.  A shared tile costs a
+// chain of dependent round trips through memory (partial sums, fence, count, read back) that is worth about ten
+// stages, so the host takes equal runs only where they save more than that (few tiles, long K).  In a run, a segment
+// that covers its tile's whole K goes straight to C; the others leave fp32 partial sums in a workspace and the CTA
+// that completes a tile adds its segments in CTA order (deterministic) and writes C.  A run is processed head of the
+// next CTA's tile first and end of the previous CTA's tile last, so that the CTA ending a tile mostly finds the
+// partner's partial sums published and completes the tile straight from its accumulator.
 //
-// 768 threads:
-//   warps 0-3   epilogue: one per quarter of the tensor-memory lanes; two accumulators alternate between segments
-//   warp 4      record producer: one bulk copy of a packed record per stage, six stages ahead
-//   warps 5, 7  MMA issue (one lane each: first / second 64-wide K tile of every stage, an accumulator each);
-//               warp 5 owns the tensor-memory allocation
-//   warp 6      X producer: two TMA loads (128 k of every token) into the operand stage the expansion is filling
-//   warps 8-23  expansion, two groups of eight warps on alternate stages: thread (row r, half hh) turns 64 codes into
-//               the 8 swizzled 16-byte chunks of its row in one of the stage's two K-major 128 x 64 tiles
-// What bounds a stage (measured with per-role cycle stamps) is latency, not bytes or arithmetic: a record takes two to
-// three thousand cycles from its bulk copy to its barrier, an mbarrier test or arrival costs the issuing warp a few
-// hundred cycles even when it succeeds at once, an issued MMA about 90 cycles whatever its width.  Hence the MMA
-// threads wait on ONE barrier per stage (completed by the expansion warps' arrivals and the X tiles' bytes together)
-// and commit once, and the expansion warps issue the barrier tests of their next stage before the arithmetic of the
-// current one.  With container_bits = 8 each code is stored as the top byte of its value's fp16 pattern (17408-byte
-// records): the same values, half the expansion's instructions.
+// 896 threads:
+//   warps 0-3    epilogue: one per quarter of the tensor-memory lanes; two accumulator pairs alternate between segments
+//   warps 4, 6   record producers (one lane each) of the even / odd stages: one bulk copy of a packed record per stage
+//   warps 5, 7   MMA issue (one lane each) on the even / odd stages, an accumulator each; warp 5 owns the tensor-memory
+//                allocation
+//   warps 8-23   expansion, two groups of eight warps on alternate stages: thread (row r, half hh) turns 64 codes into
+//                32 columns of its lane; the groups touch no mbarrier (hardware barriers to their service warps)
+//   warps 24-27  waiters (see a stage's record landed and its slot free, release the group, issue the X tiles' TMA
+//                loads) and reporters (announce the stored stage to the MMA thread, free the record slot)
+// No thread visits every stage: a visit (seeing an mbarrier, arming it, issuing) costs several hundred cycles even
+// when nothing blocks, an issued MMA about 90 cycles whatever its width.  What a stage costs now, 0.4 us, is close to
+// both the eight MMAs of an issuer and the barrier skeleton alone (measured with the expansion and the MMAs left out).
 #include "tc_dev.cuh"
 #include <math.h>
 #include <mutex>
@@ -59,14 +69,16 @@ constexpr int PK_SIDE_BYTES = PK_ROWS * 8;                    // 1024
 __host__ __device__ constexpr int pk_code_bytes(int cb) { return PK_ROWS * PK_KB * cb / 8; }
 __host__ __device__ constexpr int pk_rec_bytes(int cb) { return pk_code_bytes(cb) + PK_SIDE_BYTES; }
 constexpr int PK_EXP_BYTES = 2 * PK_ROWS * 128;               // two K-major 128 x 64 fp16 tiles
-constexpr int PK_NE = 3;                                      // operand stages when the weight is expanded here
+constexpr int PK_NE = 6;                                      // operand stages when the weight is expanded here (even: two per lane)
 constexpr int PK_NE_MAX = 6;                                  // ... when fp16 weight tiles come straight from TMA
-constexpr int PK_NL_MAX = 6;                                  // load stages (fewer when X tiles are large)
+constexpr int PK_NL_MAX = 16;                                 // load stages (fewer when X tiles are large)
 constexpr int PK_EPI_WARPS = 4;
 constexpr int PK_EXP_WARPS = 16;
 constexpr int PK_EXP_WARP0 = PK_EPI_WARPS + 4;              // warps 4, 5, 6: record producer, MMA issue, X producer
-constexpr int PK_THREADS = (PK_EXP_WARP0 + PK_EXP_WARPS) * 32;
-constexpr int PK_CTRL_BYTES = 256;
+constexpr int PK_SERVICE0 = PK_EXP_WARP0 + PK_EXP_WARPS;       // warps 24, 25: waiters of expansion groups 0, 1; 26, 27: their reporters
+constexpr int PK_THREADS = (PK_SERVICE0 + 4) * 32;
+constexpr int PK_CTRL_BYTES = 512;
+constexpr int PK_FIXUP_STAGES = 10;                           // what sharing tiles between CTAs costs, in stages
 
 struct PkArgs {
     const uint8_t* wp;          // prepacked weight [tiles][nblk][record]
@@ -81,7 +93,9 @@ struct PkArgs {
     int64_t total;              // tiles * nblk stages
     uint32_t base2[2], step2[2];// micro-scale t = base + idx * step as packed fp16 pairs, per table
     uint32_t acc_cols;          // tensor-memory columns of one accumulator (32, 64 or 128); four are allocated
+    uint32_t tmem_cols;         // columns allocated: the accumulators, then (packed weight) `ne` expanded stages of 64
     uint32_t poll_limit;
+    int whole_tiles;            // 1: every CTA takes whole tiles (no tile is shared, nothing to fix up)
 };
 
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel)
@@ -97,17 +111,48 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel)
 template <bool TWO_STEP>
 __device__ __forceinline__ void expand8(uint32_t w, uint32_t ts2, uint32_t t2, uint32_t s2, uint32_t* o)
 {
-    constexpr uint32_t LUT0 = 0x3E3C3800u, LUT1 = 0x46444240u;
-    const uint32_t w7 = w & 0x77777777u, wl = w << 4;
-    uint32_t plo = prmt(LUT0, LUT1, w7), phi = prmt(LUT0, LUT1, w7 >> 16);
-    const uint32_t mlo = prmt(w, wl, 0x9D8Cu), mhi = prmt(w, wl, 0xBFAEu);
-    plo |= mlo & 0x80808080u;
-    phi |= mhi & 0x80808080u;
-    const uint32_t v[4] = {prmt(plo, 0u, 0x1404u), prmt(plo, 0u, 0x3424u), prmt(phi, 0u, 0x1404u), prmt(phi, 0u, 0x3424u)};
+    // the conversion unit turns a byte of two E2M1 codes into an fp16 pair (low nibble -> low half), signs included
+    uint32_t v[4];
+    asm("{ .reg .b8 b0, b1, b2, b3;\n"
+        "  mov.b32 {b0, b1, b2, b3}, %4;\n"
+        "  cvt.rn.f16x2.e2m1x2 %0, b0;\n"
+        "  cvt.rn.f16x2.e2m1x2 %1, b1;\n"
+        "  cvt.rn.f16x2.e2m1x2 %2, b2;\n"
+        "  cvt.rn.f16x2.e2m1x2 %3, b3; }"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]) : "r"(w));
     #pragma unroll
     for (int p = 0; p < 4; ++p)
         o[p] = TWO_STEP ? h2_bits(__hmul2(__hmul2(bits_h2(v[p]), bits_h2(t2)), bits_h2(s2)))
                         : h2_bits(__hmul2(bits_h2(v[p]), bits_h2(ts2)));
+}
+
+// The MMA with its A operand in tensor memory (lane = row, a 32-bit column = two consecutive k), B from shared memory.
+__device__ __forceinline__ void tc_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Four 32-bit columns of this thread's tensor-memory lane (warp-collective: every lane, the same columns).
+__device__ __forceinline__ void tc_st4(uint32_t taddr, const uint32_t* o)
+{
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};"
+                 ::"r"(taddr), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
+}
+
+// 16 consecutive fp32 columns of this thread's tensor-memory lane
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, float* v)
+{
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
+          "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    #pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar)
@@ -139,6 +184,27 @@ __device__ __forceinline__ bool mbar_wait_parked_warp(uint32_t bar, uint32_t par
 }
 
 
+// Bounded wait of a warp for TWO barriers at once: lane 0 polls (bar0, par0), lane 1 (bar1, par1), the other lanes
+// poll nothing; the result is warp-uniform.
+__device__ __forceinline__ bool mbar_wait_pair(uint32_t bar0, uint32_t par0, uint32_t bar1, uint32_t par1, volatile int* abort_flag,
+                                               int code, uint32_t limit)
+{
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t bar = lane == 1 ? bar1 : bar0, par = lane == 1 ? par1 : par0;
+    #pragma unroll 1
+    for (uint32_t it = 0; it < limit; ++it) {
+        const bool t = lane < 2 ? mbar_test(bar, par) : true;
+        if (__all_sync(0xFFFFFFFFu, t)) return true;
+        if ((it & 127u) == 127u && __any_sync(0xFFFFFFFFu, *abort_flag != 0)) return false;
+    }
+    if (lane == 0) {
+        *abort_flag = 1;
+        atomicCAS(&g_tc_status, 0, code);
+    }
+    __syncwarp();
+    return false;
+}
+
 // First stage of CTA c's run, and the CTA whose run holds stage g.
 __device__ __forceinline__ int64_t run_begin(int64_t total, int c, int G) { return total * c / G; }
 __device__ __forceinline__ int cta_of_stage(int64_t total, int64_t g, int G)
@@ -168,14 +234,17 @@ gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t exp0 = (raw + 1023u) & ~1023u;                    // expanded tiles (1024-byte aligned for the swizzle)
-    const uint32_t ES = PK_EXP_BYTES + (uint32_t)a.m_pad * 256u;     // operand stage: expanded weight tiles + two X tiles
+    // operand stage in shared memory: two X tiles, after (fp16 weight) the two weight tiles; the expanded stages of a
+    // packed weight live in tensor memory
+    constexpr uint32_t WB = CB == 16 ? PK_EXP_BYTES : 0;
+    const uint32_t ES = WB + (uint32_t)a.m_pad * 256u;
     constexpr uint32_t LS = pk_rec_bytes(CB);                        // load stage: one packed record
     constexpr uint32_t CODE_BYTES = pk_code_bytes(CB);
     const uint32_t ne = (uint32_t)a.ne;
     const uint32_t ld0 = exp0 + ne * ES;
     const uint32_t ctrl_u = ld0 + (uint32_t)a.nl * LS;
     uint8_t* ctrl = smem_raw + (ctrl_u - raw);
-    // control block: ld_full[6] ld_empty[6] ex_full[3] ex_empty[3] acc_full[2] acc_empty[2] (8 B each), then the
+    // control block: ld_full[16] ld_empty[16] ex_full[6] ex_empty[6] acc_full[2] acc_empty[2] (8 B each), then the
     // tensor-memory base, the abort flag and the "this CTA completes the tile" flag
     const uint32_t bar_lfull = ctrl_u, bar_lempty = ctrl_u + 8 * PK_NL_MAX;
     const uint32_t bar_efull = ctrl_u + 16 * PK_NL_MAX, bar_eempty = bar_efull + 8 * PK_NE_MAX;
@@ -188,22 +257,42 @@ gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = gridDim.x, cta = blockIdx.x;
-    const int64_t g0 = run_begin(a.total, cta, G), g1 = run_begin(a.total, cta + 1, G);
+    const int64_t g0 = a.whole_tiles ? (int64_t)a.tiles * cta / G * a.nblk : run_begin(a.total, cta, G);
+    const int64_t g1 = a.whole_tiles ? (int64_t)a.tiles * (cta + 1) / G * a.nblk : run_begin(a.total, cta + 1, G);
     const int nst = (int)(g1 - g0);
+    // The run's stages are taken in three pieces: the head of the tile that the NEXT CTA completes, the whole tiles, and
+    // last the end of the tile that the PREVIOUS CTA began.  A tile shared by two CTAs is thus begun early by one and
+    // ended late by the other, whose fix-up then finds the partner's partial sums already published.
+    const int64_t e1 = (g0 % a.nblk) == 0 ? g0 : min(g1, (g0 / a.nblk + 1) * a.nblk);
+    const int64_t hb = max(e1, g1 - g1 % a.nblk);
+    const int64_t pc_s[3] = {hb, e1, g0};
+    const int pc_n[3] = {(int)(g1 - hb), (int)(hb - e1), (int)(e1 - g0)};
+    // stage i of the run in processing order -> its global (tile, block) index
+    auto stage_g = [&](int i) -> int64_t {
+        if (i < pc_n[0]) return pc_s[0] + i;
+        i -= pc_n[0];
+        return i < pc_n[1] ? pc_s[1] + i : pc_s[2] + (i - pc_n[1]);
+    };
     const uint32_t park_limit = (a.poll_limit >> 6) + 64u;          // parked attempts last far longer than a poll
 
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < PK_NL_MAX; ++s) { mbar_init(bar_lfull + 8 * s, 1); mbar_init(bar_lempty + 8 * s, PK_EXP_WARPS / 2); }
-        // operands ready: the expansion group's eight warps + the X tiles' bytes, or (fp16 weight) the two producers' bytes
-        for (int s = 0; s < PK_NE_MAX; ++s) { mbar_init(bar_efull + 8 * s, CB == 16 ? 2 : PK_EXP_WARPS / 2 + 1); mbar_init(bar_eempty + 8 * s, 2); }
-        for (int b = 0; b < 2; ++b) { mbar_init(bar_afull + 8 * b, 2); mbar_init(bar_aempty + 8 * b, PK_EPI_WARPS); }
-        *abort_flag = 0;
-        *last_flag = 0;
+    if (threadIdx.x == 32) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&mapX) : "memory");
+        if (CB == 16) asm volatile("prefetch.tensormap [%0];" ::"l"(&mapW) : "memory");
+    }
+    if (threadIdx.x < 2 * PK_NL_MAX + 2 * PK_NE_MAX + 4) {
+        // one barrier per thread: ld_full / ld_empty (one arrival each), ex_full (two: the stage's reporter or weight
+        // bytes, and the X tiles' bytes), ex_empty (one commit), acc_full (both issuers), acc_empty (the epilogue warps)
+        const int t = threadIdx.x;
+        uint32_t count = 1;
+        if (t >= 2 * PK_NL_MAX && t < 2 * PK_NL_MAX + PK_NE_MAX) count = 2;
+        else if (t >= 2 * PK_NL_MAX + 2 * PK_NE_MAX) count = t < 2 * PK_NL_MAX + 2 * PK_NE_MAX + 2 ? 2 : PK_EPI_WARPS;
+        mbar_init(ctrl_u + 8 * t, count);
+        if (t == 0) { *abort_flag = 0; *last_flag = 0; }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 5) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(smem_u32(tmem_base_smem)), "r"(4u * a.acc_cols) : "memory");
+                     ::"r"(smem_u32(tmem_base_smem)), "r"(a.tmem_cols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
@@ -220,7 +309,7 @@ gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
                 for (int i = 0; i < nst; ++i) {
                     if (!mbar_wait(bar_eempty + 8 * es, eph ^ 1u, abort_flag, 1, a.poll_limit)) break;
                     const uint32_t dst = exp0 + es * ES, bar = bar_efull + 8 * es;
-                    const int64_t g = g0 + i;
+                    const int64_t g = stage_g(i);
                     const int kb = (int)(g % a.nblk), row0 = (int)(g / a.nblk) * PK_ROWS;
                     mbar_expect_tx(bar, PK_EXP_BYTES);
                     tma_load_2d(dst, &mapW, kb * PK_KB, row0, bar);
@@ -229,69 +318,147 @@ gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
                 }
             }
         } else if (lane == 0) {
-            const uint8_t* src = a.wp + g0 * (int64_t)LS;            // the run's records are consecutive in memory
-            uint32_t stage = 0, phase = 0;
-            for (int i = 0; i < nst; ++i) {
-                if (!mbar_wait_parked(bar_lempty + 8 * stage, phase ^ 1u, abort_flag, 1, park_limit)) break;
+            // packed weight: the records of the EVEN stages (warp 6 takes the odd ones).  One visit of a producing
+            // thread to a stage -- seeing the barrier, arming it, issuing the copy -- costs 600-700 cycles even when
+            // nothing blocks, so no thread of this kernel visits every stage.
+            const uint32_t nl = (uint32_t)a.nl;
+            for (int i = 0; i < nst; i += 2) {
+                const uint32_t stage = (uint32_t)i % nl, phase = ((uint32_t)i / nl) & 1u;
+                if (!mbar_wait(bar_lempty + 8 * stage, phase ^ 1u, abort_flag, 1, a.poll_limit)) break;
                 const uint32_t bar = bar_lfull + 8 * stage;
                 mbar_expect_tx(bar, LS);
-                bulk_load(ld0 + stage * LS, src + (int64_t)i * LS, LS, bar);
-                if (++stage == (uint32_t)a.nl) { stage = 0; phase ^= 1u; }
+                bulk_load(ld0 + stage * LS, a.wp + stage_g(i) * (int64_t)LS, LS, bar);
             }
         }
     } else if (warp == 6) {
-        // ================= X producer: the tokens' tiles travel with the operand stage =================
-        // They complete the same barrier as the expansion's arrivals, so the MMA warp waits once per stage and one
-        // commit hands the whole stage back.
-        if (lane == 0) {
-            uint32_t es = 0, eph = 0;
-            for (int i = 0; i < nst; ++i) {
-                if (!mbar_wait_parked(bar_eempty + 8 * es, eph ^ 1u, abort_flag, 8, park_limit)) break;
-                const uint32_t dst = exp0 + es * ES + PK_EXP_BYTES, bar = bar_efull + 8 * es;
-                const int kb = (int)((g0 + i) % a.nblk);
-                mbar_expect_tx(bar, (uint32_t)a.m_pad * 256u);
-                tma_load_2d(dst, &mapX, kb * PK_KB, 0, bar);
-                tma_load_2d(dst + (uint32_t)a.m_pad * 128u, &mapX, kb * PK_KB + 64, 0, bar);
-                if (++es == ne) { es = 0; eph ^= 1u; }
+        if (CB == 16) {
+            // ================= X producer (fp16 weight): the tokens' tiles travel with the operand stage =================
+            if (lane == 0) {
+                uint32_t es = 0, eph = 0;
+                for (int i = 0; i < nst; ++i) {
+                    if (!mbar_wait_parked(bar_eempty + 8 * es, eph ^ 1u, abort_flag, 8, park_limit)) break;
+                    const uint32_t dst = exp0 + es * ES + WB, bar = bar_efull + 8 * es;
+                    const int kb = (int)(stage_g(i) % a.nblk);
+                    mbar_expect_tx(bar, (uint32_t)a.m_pad * 256u);
+                    tma_load_2d(dst, &mapX, kb * PK_KB, 0, bar);
+                    tma_load_2d(dst + (uint32_t)a.m_pad * 128u, &mapX, kb * PK_KB + 64, 0, bar);
+                    if (++es == ne) { es = 0; eph ^= 1u; }
+                }
+            }
+        } else if (lane == 0) {
+            // ================= record producer of the ODD stages =================
+            const uint32_t nl = (uint32_t)a.nl;
+            for (int i = 1; i < nst; i += 2) {
+                const uint32_t stage = (uint32_t)i % nl, phase = ((uint32_t)i / nl) & 1u;
+                if (!mbar_wait(bar_lempty + 8 * stage, phase ^ 1u, abort_flag, 1, a.poll_limit)) break;
+                const uint32_t bar = bar_lfull + 8 * stage;
+                mbar_expect_tx(bar, LS);
+                bulk_load(ld0 + stage * LS, a.wp + stage_g(i) * (int64_t)LS, LS, bar);
             }
         }
     } else if (warp == 5 || warp == 7) {
         // ================= MMA issue =================
-        // Two issuing threads: the serial cost of issuing an MMA (about 90 cycles whatever its width) is what bounds a
-        // stage, so warp 5 issues the four MMAs of a stage's first 64-wide K tile and warp 7 those of the second, each
-        // into an accumulator of its own (MMAs of different threads are not ordered with each other); the epilogue
-        // adds the two.  Each thread's commit tracks its own MMAs, so the stage and accumulator barriers count two.
+        // A visit of an issuing thread to a stage -- seeing the barrier, the MMAs (about 90 cycles each whatever their
+        // width), the commits -- is a serial chain of about a thousand cycles, and it bounds the pipeline.  So the two
+        // issuers take ALTERNATE stages (issuer p the stages of parity p, all eight MMAs of each) into an accumulator
+        // of their own -- MMAs of different threads are not ordered with each other -- and the epilogue adds the two.
+        // The operand ring has an even length, so a slot always belongs to the same issuer and its barrier phases are
+        // seen one after the other; the test of the next stage's barrier is issued before this stage's MMAs.
         // kind::f16: D fp32, A/B fp16, both K-major, M = 128 weight rows, N = m_pad tokens
         const uint32_t idesc = (1u << 4) | ((uint32_t)(a.m_pad >> 3) << 17) | ((uint32_t)(PK_ROWS >> 4) << 24);
-        const uint32_t h = warp == 7 ? 1u : 0u;
+        const int p = warp == 7 ? 1 : 0;
         const bool leader = elect_one();
-        uint32_t es = 0, eph = 0;
         bool ok = true;
-        int j = 0;
-        for (int64_t g = g0; g < g1 && ok; ++j) {
+        bool pre = p < nst && mbar_test(bar_efull + 8 * ((uint32_t)p % ne), ((uint32_t)p / ne) & 1u);
+        int j = 0, first = 0;
+        for (int pc = 0; pc < 3 && ok; ++pc)
+        for (int64_t g = pc_s[pc], gend = pc_s[pc] + pc_n[pc]; g < gend && ok; ++j) {
             const int kb = (int)(g % a.nblk);
-            const int len = (int)min((int64_t)(a.nblk - kb), g1 - g);
+            const int len = (int)min((int64_t)(a.nblk - kb), gend - g);
             const uint32_t buf = (uint32_t)j & 1u;
             // the epilogue must have drained this accumulator pair's previous segment
             if (!(ok = mbar_wait_warp(bar_aempty + 8 * buf, (((uint32_t)j >> 1) & 1u) ^ 1u, abort_flag, 7, a.poll_limit))) break;
-            const uint32_t d_tmem = tmem_base + (2u * buf + h) * a.acc_cols;
-            for (int i = 0; i < len; ++i) {
-                // weights expanded and X tiles landed
-                if (!(ok = mbar_wait_warp(bar_efull + 8 * es, eph, abort_flag, 3, a.poll_limit))) break;
+            const uint32_t d_tmem = tmem_base + (2u * buf + (uint32_t)p) * a.acc_cols;
+            bool fresh = true;                                   // this issuer's first MMA of the segment overwrites
+            for (int i = first + ((p - first) & 1); i < first + len; i += 2) {
+                const uint32_t es = (uint32_t)i % ne, eph = ((uint32_t)i / ne) & 1u;
+                // weights expanded (or landed) and X tiles landed
+                if (!__all_sync(0xFFFFFFFFu, pre) && !(ok = mbar_wait_warp(bar_efull + 8 * es, eph, abort_flag, 3, a.poll_limit))) break;
                 tc_fence_after();
+                const uint32_t ni = (uint32_t)i + 2u;
+                const bool nxt = (int)ni < nst && mbar_test(bar_efull + 8 * (ni % ne), (ni / ne) & 1u);
                 if (leader) {
-                    const uint32_t wa = exp0 + es * ES + h * (PK_ROWS * 128);
-                    const uint32_t xa = exp0 + es * ES + PK_EXP_BYTES + h * ((uint32_t)a.m_pad * 128u);
+                    const uint32_t wa = exp0 + es * ES, xa = wa + WB;
+                    const uint32_t wt = tmem_base + 4u * a.acc_cols + es * 64u;      // the expanded stage in tensor memory
                     #pragma unroll
-                    for (int kk = 0; kk < 4; ++kk)
-                        tc_mma_f16(d_tmem, umma_desc(wa + kk * 32), umma_desc(xa + kk * 32), idesc, (i | kk) != 0 ? 1u : 0u);
+                    for (int h = 0; h < 2; ++h) {
+                        #pragma unroll
+                        for (int kk = 0; kk < 4; ++kk) {
+                            const uint64_t xd = umma_desc(xa + h * ((uint32_t)a.m_pad * 128u) + kk * 32);
+                            const uint32_t acc = (!fresh || (h | kk) != 0) ? 1u : 0u;
+                            if (CB == 16) tc_mma_f16(d_tmem, umma_desc(wa + h * (PK_ROWS * 128) + kk * 32), xd, idesc, acc);
+                            else tc_mma_f16_ts(d_tmem, wt + (uint32_t)(h * 4 + kk) * 8u, xd, idesc, acc);
+                        }
+                    }
                     tc_commit(bar_eempty + 8 * es);
-                    if (i + 1 == len) tc_commit(bar_afull + 8 * buf);
                 }
                 __syncwarp();
-                if (++es == ne) { es = 0; eph ^= 1u; }
+                fresh = false;
+                pre = nxt;
             }
+            if (!ok) break;
+            // both issuers report the segment, also the one that had no stage in it (its commit completes at once)
+            if (leader) tc_commit(bar_afull + 8 * buf);
+            __syncwarp();
+            first += len;
             g += len;
+        }
+    } else if (warp >= PK_SERVICE0) {
+        // ================= waiter / reporter of expansion group p =================
+        // Hardware barriers, three ids per purpose and group, taken in turn by the group's stages: 2 + p + 2k "stage
+        // released", 8 + p + 2k "stage stored" (k = 0, 1, 2).  A group owns at most three operand slots, so its waiter is
+        // at most two stages ahead of it (a slot frees only after the MMAs of a stage the group has finished) and the
+        // group at most two stages ahead of its reporter (the MMAs need the reporter's arrival): an early arrival never
+        // falls into a phase of the same barrier that is still open.
+        if (CB != 16) {
+            const int p = (warp - PK_SERVICE0) & 1;
+            const bool reporter = warp >= PK_SERVICE0 + 2;
+            const uint32_t nl = (uint32_t)a.nl, odd = (uint32_t)lane & 1u;
+            // every operand slot is free at the start: the X tiles of the group's first stages leave at once, under the
+            // flight of the first records
+            if (!reporter && lane == 0) {
+                for (int i = p; i < nst && i < (int)ne; i += 2) {
+                    const uint32_t dst = exp0 + (uint32_t)i * ES + WB, bar = bar_efull + 8 * (uint32_t)i;
+                    const int kb = (int)(stage_g(i) % a.nblk);
+                    mbar_expect_tx(bar, (uint32_t)a.m_pad * 256u);
+                    tma_load_2d(dst, &mapX, kb * PK_KB, 0, bar);
+                    tma_load_2d(dst + (uint32_t)a.m_pad * 128u, &mapX, kb * PK_KB + 64, 0, bar);
+                }
+            }
+            __syncwarp();
+            for (int i = p, k = 0; i < nst; i += 2, k = k == 2 ? 0 : k + 1) {
+                const uint32_t ls = (uint32_t)i % nl, lph = ((uint32_t)i / nl) & 1u, es = (uint32_t)i % ne, eph = ((uint32_t)i / ne) & 1u;
+                if (!reporter) {
+                    // lane 0 (and the idle lanes): record landed; lane 1: operand slot free -- one instruction, two addresses
+                    const bool ok = mbar_wait_pair(bar_lfull + 8 * ls, lph, bar_eempty + 8 * es, eph ^ 1u, abort_flag, 4, a.poll_limit);
+                    asm volatile("bar.arrive %0, 288;" ::"r"(2 + p + 2 * k) : "memory");   // (on failure: the group leaves)
+                    if (!ok) break;
+                    if (lane == 0 && i >= (int)ne) {
+                        // the slot is free: the tokens' two K tiles of this stage go into it; their bytes complete the same
+                        // barrier as the reporter's arrival, so an MMA thread waits once per stage
+                        const uint32_t dst = exp0 + es * ES + WB, bar = bar_efull + 8 * es;
+                        const int kb = (int)(stage_g(i) % a.nblk);
+                        mbar_expect_tx(bar, (uint32_t)a.m_pad * 256u);
+                        tma_load_2d(dst, &mapX, kb * PK_KB, 0, bar);
+                        tma_load_2d(dst + (uint32_t)a.m_pad * 128u, &mapX, kb * PK_KB + 64, 0, bar);
+                    }
+                    __syncwarp();
+                } else {
+                    asm volatile("bar.sync %0, 288;" ::"r"(8 + p + 2 * k) : "memory");
+                    if (*abort_flag) break;
+                    if (lane < 2) mbar_arrive(odd ? bar_lempty + 8 * ls : bar_efull + 8 * es);
+                }
+            }
         }
     } else if (warp >= PK_EXP_WARP0 && CB != 16) {
         // ================= expansion =================
@@ -301,17 +468,14 @@ gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
         const int te = threadIdx.x - PK_EXP_WARP0 * 32;
         const int grp = te >> 8, tg = te & 255;
         const int r = tg & (PK_ROWS - 1), hh = tg >> 7;
-        const uint32_t swz = (uint32_t)(r & 7);
         const uint32_t nl = (uint32_t)a.nl;
-        // A test of a barrier costs a few hundred cycles of latency even when it has completed, so the tests for the
-        // group's NEXT stage are issued before this stage's arithmetic and read after it; a wait loop runs only when
-        // one failed.
-        bool pre_l = grp < nst && mbar_test(bar_lfull + 8 * ((uint32_t)grp % nl), ((uint32_t)grp / nl) & 1u);
-        bool pre_e = grp < nst && mbar_test(bar_eempty + 8 * ((uint32_t)grp % ne), (((uint32_t)grp / ne) & 1u) ^ 1u);
-        for (int i = grp; i < nst; i += 2) {
-            const uint32_t ls = (uint32_t)i % nl, lph = ((uint32_t)i / nl) & 1u;
-            const uint32_t es = (uint32_t)i % ne, eph = ((uint32_t)i / ne) & 1u;
-            if (!__all_sync(0xFFFFFFFFu, pre_l) && !mbar_wait_warp(bar_lfull + 8 * ls, lph, abort_flag, 4, a.poll_limit)) break;
+        // The group touches no mbarrier: a test or an arrival costs the issuing warp several hundred cycles of latency,
+        // which with eight per stage was as much as the expansion itself.  Its waiter warp sees the stage's barriers and
+        // releases it through a hardware barrier, its reporter warp announces the finished stage.
+        for (int i = grp, k = 0; i < nst; i += 2, k = k == 2 ? 0 : k + 1) {
+            const uint32_t ls = (uint32_t)i % nl, es = (uint32_t)i % ne;
+            asm volatile("bar.sync %0, 288;" ::"r"(2 + grp + 2 * k) : "memory");
+            if (*abort_flag) { asm volatile("bar.arrive %0, 288;" ::"r"(8 + grp + 2 * k) : "memory"); break; }
             const uint32_t rec = ld0 + ls * LS;
             // this thread's 64 codes: 16-byte pieces, rows contiguous inside a piece (2 pieces of 32 codes, or 4 of 16)
             constexpr int NP = CB / 2;
@@ -325,97 +489,155 @@ gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
             const uint32_t sc = meta & 0xFFFFu, s2 = sc * 0x10001u, tb = (meta >> 16) & 1u;
             const uint32_t base2 = tb ? a.base2[1] : a.base2[0], step2 = tb ? a.step2[1] : a.step2[0];
             // a scale in fp16's top binade could overflow t*s where (level*t)*s stays finite: multiply in two steps there
+            // (the stores below are warp-collective, so the rare case is a select inside a warp-uniform branch)
             const bool two_step = sc >= 0x7800u;
+            const bool any_two = __any_sync(0xFFFFFFFFu, two_step);
             // this half's micro-scale indices: chunk 8hh + c of the block, one index per 2^MS chunks
             const uint32_t l2q = l2w >> (2 * ((8 * hh) >> MS));
-            const uint32_t out = (exp0 + es * ES + hh * (PK_ROWS * 128) + r * 128) ^ (swz << 4);
-            // the operand stage must have been read by the MMAs of its previous use
-            if (!__all_sync(0xFFFFFFFFu, pre_e) && !mbar_wait_warp(bar_eempty + 8 * es, eph ^ 1u, abort_flag, 5, a.poll_limit)) break;
-            // Only now: the parity test tells "completed" from "not yet" for the phase this group waits for next, but
-            // not from a phase two behind, and the MMAs of stage i - 3 having finished (the wait above) is what
-            // guarantees that the barrier of stage i + 2's slot is at most one phase behind.
-            const bool more = i + 2 < nst;
-            const uint32_t ni = (uint32_t)i + 2u;
-            const bool nxt_l = more && mbar_test(bar_lfull + 8 * (ni % nl), (ni / nl) & 1u);
-            const bool nxt_e = more && mbar_test(bar_eempty + 8 * (ni % ne), ((ni / ne) & 1u) ^ 1u);
+            // the stage in tensor memory: lane = weight row (this warp's quarter), 64 columns of two k each; this thread
+            // writes columns 32 hh + 4 c + {0..3} for its chunk c
+            const uint32_t out = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + 4u * a.acc_cols + es * 64u + (uint32_t)hh * 32u;
             uint32_t t2 = 0u, ts2 = 0u;
-            if (!two_step) {
-                #pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    if (MS == 0 || (c & 3) == 0) {
-                        const uint32_t idx = (l2q >> (2 * (c >> MS))) & 3u;
-                        t2 = base2 + idx * step2;
-                        ts2 = h2_bits(__hmul2(bits_h2(t2), bits_h2(s2)));
-                    }
-                    uint32_t o[4];
-                    if (CB == 4) expand8<false>(cw[c], ts2, t2, s2, o);
-                    else expand8_bytes<false>(cw[(2 * c) % (4 * NP)], cw[(2 * c + 1) % (4 * NP)], ts2, t2, s2, o);
-                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};"
-                                 ::"r"(out ^ ((uint32_t)c << 4)), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
-                }
-            } else {
-                #pragma unroll
-                for (int c = 0; c < 8; ++c) {
+            #pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                if (MS == 0 || (c & 3) == 0) {
                     const uint32_t idx = (l2q >> (2 * (c >> MS))) & 3u;
                     t2 = base2 + idx * step2;
-                    uint32_t o[4];
-                    if (CB == 4) expand8<true>(cw[c], 0u, t2, s2, o);
-                    else expand8_bytes<true>(cw[(2 * c) % (4 * NP)], cw[(2 * c + 1) % (4 * NP)], 0u, t2, s2, o);
-                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};"
-                                 ::"r"(out ^ ((uint32_t)c << 4)), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
+                    ts2 = h2_bits(__hmul2(bits_h2(t2), bits_h2(s2)));
                 }
+                uint32_t o[4];
+                if (CB == 4) expand8<false>(cw[c], ts2, t2, s2, o);
+                else expand8_bytes<false>(cw[(2 * c) % (4 * NP)], cw[(2 * c + 1) % (4 * NP)], ts2, t2, s2, o);
+                if (any_two) {
+                    uint32_t o2[4];
+                    if (CB == 4) expand8<true>(cw[c], 0u, t2, s2, o2);
+                    else expand8_bytes<true>(cw[(2 * c) % (4 * NP)], cw[(2 * c + 1) % (4 * NP)], 0u, t2, s2, o2);
+                    #pragma unroll
+                    for (int p = 0; p < 4; ++p) o[p] = two_step ? o2[p] : o[p];
+                }
+                tc_st4(out + 4u * (uint32_t)c, o);
             }
-            // the tensor core reads shared memory through the async proxy: order these generic-proxy stores before it
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) { mbar_arrive(bar_efull + 8 * es); mbar_arrive(bar_lempty + 8 * ls); }
-            pre_l = nxt_l; pre_e = nxt_e;
+            // the stores have landed in tensor memory, and are ordered before the arrival that the MMA thread will see
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            tc_fence_before();
+            asm volatile("bar.arrive %0, 288;" ::"r"(8 + grp + 2 * k) : "memory");
         }
     } else if (warp < PK_EPI_WARPS) {
         // ================= epilogue (warps 0-3: one per quarter of the tensor-memory lanes) =================
         const int quarter = warp, nloc = quarter * 32 + lane;          // this thread's weight row inside the tile
         bool ok = true;
-        int j = 0;
-        for (int64_t g = g0; g < g1; ++j) {
+        if (warp == 0 && lane < 12) {
+            // The fix-up is a chain of dependent round trips to memory this SM has not touched yet (counters, partial
+            // sums, C), and each first touch pays an address-translation miss of a few microseconds.  Touch those pages
+            // now, while the first stages are on their way; the values are not used.
+            const int64_t ta = g0 / a.nblk, tb = (g1 - 1) / a.nblk;
+            const char* pz = nullptr;
+            switch (lane) {
+            case 0: pz = (const char*)(a.counters + ta); break;
+            case 1: pz = (const char*)(a.counters + tb); break;
+            case 2: pz = (const char*)(a.ws + (int64_t)cta * 2 * a.m_pad * PK_ROWS); break;
+            case 3: pz = (const char*)(a.ws + ((int64_t)cta * 2 + 2) * a.m_pad * PK_ROWS - 1); break;
+            case 4: pz = (const char*)(a.ws + (int64_t)max(cta - 2, 0) * 2 * a.m_pad * PK_ROWS); break;
+            case 5: pz = (const char*)(a.ws + ((int64_t)min(cta + 2, G - 1) * 2 + 2) * a.m_pad * PK_ROWS - 1); break;
+            case 6: pz = (const char*)(a.C + ta * PK_ROWS); break;
+            case 7: pz = (const char*)(a.C + (int64_t)(a.M - 1) * a.N + ta * PK_ROWS + PK_ROWS - 1); break;
+            case 8: pz = (const char*)(a.C + tb * PK_ROWS); break;
+            case 9: pz = (const char*)(a.C + (int64_t)(a.M - 1) * a.N + tb * PK_ROWS + PK_ROWS - 1); break;
+            case 10: pz = a.bias ? (const char*)(a.bias + ta * PK_ROWS) : nullptr; break;
+            default: pz = a.bias ? (const char*)(a.bias + tb * PK_ROWS) : nullptr; break;
+            }
+            if (pz) {
+                uint32_t unused;
+                asm volatile("ld.global.cg.u8 %0, [%1];" : "=r"(unused) : "l"(pz) : "memory");
+            }
+        }
+        int j = 0, first = 0;
+        for (int pc = 0; pc < 3 && ok; ++pc)
+        for (int64_t g = pc_s[pc], gend = pc_s[pc] + pc_n[pc]; g < gend; ++j) {
             const int tile = (int)(g / a.nblk), kb = (int)(g % a.nblk);
-            const int len = (int)min((int64_t)(a.nblk - kb), g1 - g);
+            const int len = (int)min((int64_t)(a.nblk - kb), gend - g);
+            // issuer p accumulated the segment's stages of parity p: a one-stage segment has only one of the two
+            const bool has0 = len >= 2 || (first & 1) == 0, has1 = len >= 2 || (first & 1) == 1;
+            first += len;
             g += len;
             const uint32_t buf = (uint32_t)j & 1u;
+            const bool whole = len == a.nblk;
+            // the tile's segments sit in consecutive CTAs
+            int c_first = cta, c_last = cta;
+            bool closing = false;
+            if (!whole) {
+                c_first = cta_of_stage(a.total, (int64_t)tile * a.nblk, G);
+                c_last = cta_of_stage(a.total, (int64_t)tile * a.nblk + a.nblk - 1, G);
+                // This CTA ends the tile: while its MMAs still run, see whether every other CTA of the tile has already
+                // published its partial sums.  Then the tile is completed from the accumulator, with no partial sums of
+                // this CTA, no fence and no count on the way.
+                if (cta == c_last) {
+                    if (threadIdx.x == 0) {
+                        int seen;
+                        asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(a.counters + tile) : "memory");
+                        *last_flag = seen == c_last - c_first;
+                    }
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    closing = *last_flag != 0;
+                    asm volatile("bar.sync 1, 128;" ::: "memory");    // everyone has read the flag before its next use
+                    if (closing) __threadfence();
+                }
+            }
             ok = ok && mbar_wait_parked_warp(bar_afull + 8 * buf, ((uint32_t)j >> 1) & 1u, abort_flag, 6, park_limit);
             if (!ok) break;
             tc_fence_after();
-            const bool whole = len == a.nblk;
             const int gn = tile * PK_ROWS + nloc;
             float* part = a.ws + ((int64_t)cta * 2 + (tile == (int)(g0 / a.nblk) ? 0 : 1)) * a.m_pad * PK_ROWS + nloc;
             const __half bv = a.bias ? a.bias[gn] : __float2half_rn(0.f);
-            for (int c0 = 0; c0 < a.m_pad; c0 += 32) {
-                float v[32], v1[32];
-                tc_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (2u * buf) * a.acc_cols + c0, v);
-                tc_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (2u * buf + 1u) * a.acc_cols + c0, v1);
-                #pragma unroll
-                for (int i = 0; i < 32; ++i) v[i] += v1[i];             // first K tiles + second K tiles of the stages
-                #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const int m = c0 + i;
-                    if (m >= a.M) break;
-                    if (whole) {
+            for (int c0 = 0; c0 < a.m_pad; c0 += 16) {
+                float v[16];
+                {
+                    float v1[16];
+                    tc_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (2u * buf) * a.acc_cols + c0, v);
+                    tc_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (2u * buf + 1u) * a.acc_cols + c0, v1);
+                    #pragma unroll
+                    for (int i = 0; i < 16; ++i) v[i] = (has0 ? v[i] : 0.f) + (has1 ? v1[i] : 0.f);   // even + odd stages
+                }
+                if (closing) {
+                    // the other CTAs' partial sums in CTA order, this CTA's accumulator last: the order of the fix-up below
+                    float acc[16];
+                    #pragma unroll
+                    for (int i = 0; i < 16; ++i) acc[i] = 0.f;
+                    for (int cc = c_first; cc < c_last; ++cc) {
+                        const int slot = tile == (int)(run_begin(a.total, cc, G) / a.nblk) ? 0 : 1;
+                        const float* q = a.ws + ((int64_t)cc * 2 + slot) * a.m_pad * PK_ROWS + nloc;
+                        float w[16];
+                        #pragma unroll
+                        for (int i = 0; i < 16; ++i) w[i] = c0 + i < a.M ? __ldcg(q + (int64_t)(c0 + i) * PK_ROWS) : 0.f;
+                        #pragma unroll
+                        for (int i = 0; i < 16; ++i) acc[i] += w[i];
+                    }
+                    #pragma unroll
+                    for (int i = 0; i < 16; ++i) v[i] += acc[i];
+                }
+                if (whole || closing) {
+                    __half* cp = a.C + (int64_t)c0 * a.N + gn;
+                    #pragma unroll
+                    for (int i = 0; i < 16; ++i) {
                         __half o = __float2half_rn(v[i]);
                         if (a.bias) o = __hadd(o, bv);
-                        a.C[(int64_t)m * a.N + gn] = o;
-                    } else {
-                        part[(int64_t)m * PK_ROWS] = v[i];
+                        if (c0 + i < a.M) cp[(int64_t)i * a.N] = o;
                     }
+                } else {
+                    #pragma unroll
+                    for (int i = 0; i < 16; ++i)
+                        if (c0 + i < a.M) part[(int64_t)(c0 + i) * PK_ROWS] = v[i];
                 }
             }
             // the accumulator has been read: hand it back to the MMA warp
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_aempty + 8 * buf);
-            if (!whole) {
-                // the tile's segments sit in consecutive CTAs; the one that arrives last adds them in CTA order
-                const int c_first = cta_of_stage(a.total, (int64_t)tile * a.nblk, G);
-                const int c_last = cta_of_stage(a.total, (int64_t)tile * a.nblk + a.nblk - 1, G);
-                // every thread orders its own partial sums before the count (a fence by the counting thread alone, after
+            if (closing) {
+                if (threadIdx.x == 0) a.counters[tile] = 0;
+            } else if (!whole) {
+                // the CTA that arrives last adds the tile's partial sums in CTA order.
+                // Every thread orders its own partial sums before the count (a fence by the counting thread alone, after
                 // the barrier, was seen to let a reader on another SM run ahead of a warp's stores)
                 __threadfence();
                 asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -474,7 +696,7 @@ gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
     }
     if (warp == 5) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(4u * a.acc_cols) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(a.tmem_cols) : "memory");
     }
 }
 
@@ -591,13 +813,16 @@ int gemm_w4_prepack(const hbq_packed_out* in, int64_t N, int64_t K, const hbq_fo
     return HBQ_OK;
 }
 
+// The counters come first, so that launches of any token count find them (zeroed) at the same place.
+static int64_t w4_counter_bytes(int64_t tiles) { return (tiles * 4 + 255) / 256 * 256; }
+
 int64_t gemm_w4_workspace_bytes(int64_t M, int64_t N, int64_t K)
 {
     if (!w4_shape(M, N, K)) return -1;
     int sms = 0;
     if (device_sms(&sms) != HBQ_OK) return -1;
     const int64_t tiles = N / PK_ROWS, m_pad = (M + 15) / 16 * 16;
-    return (int64_t)sms * 2 * m_pad * PK_ROWS * 4 + tiles * 4;        // two partial-sum slots per CTA, one counter per tile
+    return w4_counter_bytes(tiles) + (int64_t)sms * 2 * m_pad * PK_ROWS * 4;   // one counter per tile, two partial-sum slots per CTA
 }
 
 template <int MS, int CB>
@@ -638,15 +863,17 @@ int gemm_w16_launch(const void* X, const void* W, void* C, int64_t M, int64_t N,
     a.nblk = (int)(K / PK_KB); a.tiles = (int)(N / PK_ROWS);
     a.total = (int64_t)a.tiles * a.nblk;
     const int grid = (int)(a.total < sms ? a.total : sms);
-    a.ws = (float*)workspace;
-    a.counters = (int*)((uint8_t*)workspace + (int64_t)sms * 2 * a.m_pad * PK_ROWS * 4);
+    a.counters = (int*)workspace;
+    a.ws = (float*)((uint8_t*)workspace + w4_counter_bytes(a.tiles));
     const uint32_t ES = PK_EXP_BYTES + (uint32_t)a.m_pad * 256u;
     const uint32_t budget = 227u * 1024u - 1024u - PK_CTRL_BYTES;
     a.ne = (int)(budget / ES);
     if (a.ne > PK_NE_MAX) a.ne = PK_NE_MAX;
+    a.ne &= ~1;                                            // even: a slot always belongs to the same issuer
     if (a.ne < 2) return HBQ_ERR_UNSUPPORTED;
     a.nl = 0;
     a.acc_cols = a.m_pad <= 32 ? 32u : (a.m_pad <= 64 ? 64u : 128u);
+    a.tmem_cols = 4u * a.acc_cols;
     a.poll_limit = 1u << 23;
     CUtensorMap mx, mw;
     { const int rc = gemm_make_map(&mx, X, M, K, a.m_pad); if (rc) return rc; }
@@ -659,6 +886,50 @@ int gemm_w16_launch(const void* X, const void* W, void* C, int64_t M, int64_t N,
 
 // workspace: gemm_w4_workspace_bytes() bytes, 16-byte aligned, zeroed once by the caller (the kernel leaves the tile
 // counters at zero again); one call at a time per workspace.
+// One launch: at most 64 tokens (four accumulators of up to 64 columns and the expanded stages share the SM's 512
+// tensor-memory columns).
+static int w4_launch_rows(const void* X, const void* Wp, void* C, int64_t M, int64_t N, int64_t K, PkArgs a, int ms,
+                          int container_bits, const void* bias, void* workspace, int sms, cudaStream_t stream)
+{
+    a.wp = (const uint8_t*)Wp; a.C = (__half*)C; a.bias = (const __half*)bias;
+    a.M = (int)M; a.N = (int)N; a.K = (int)K;
+    a.m_pad = (int)((M + 15) / 16 * 16);
+    a.nblk = (int)(K / PK_KB); a.tiles = (int)(N / PK_ROWS);
+    a.total = (int64_t)a.tiles * a.nblk;
+    // Equal runs of K blocks per SM share tiles between CTAs, and the fix-up of a shared tile is a chain of dependent
+    // round trips through memory worth about twenty stages.  Where whole tiles per CTA cost fewer stages than that on
+    // top, every CTA takes whole tiles and nothing is fixed up.
+    int grid = (int)(a.total < sms ? a.total : sms);
+    {
+        const int grid_w = a.tiles < sms ? a.tiles : sms;
+        const int64_t stages_w = (int64_t)((a.tiles + grid_w - 1) / grid_w) * a.nblk, stages_k = (a.total + grid - 1) / grid;
+        a.whole_tiles = stages_w - stages_k <= PK_FIXUP_STAGES;
+        if (a.whole_tiles) grid = grid_w;
+    }
+    a.counters = (int*)workspace;
+    a.ws = (float*)((uint8_t*)workspace + w4_counter_bytes(a.tiles));
+    const uint32_t LS = (uint32_t)pk_rec_bytes(container_bits), ES = (uint32_t)a.m_pad * 256u;
+    // tensor memory: four accumulators, then the expanded stages (64 columns each): six of them, four for 64 tokens
+    a.acc_cols = a.m_pad <= 32 ? 32u : 64u;
+    a.tmem_cols = 512u;
+    a.ne = (int)((a.tmem_cols - 4u * a.acc_cols) / 64u);
+    if (a.ne > PK_NE) a.ne = PK_NE;
+    const uint32_t avail = 227u * 1024u - 1024u - (uint32_t)a.ne * ES - PK_CTRL_BYTES;
+    a.nl = (int)(avail / LS);
+    if (a.nl > PK_NL_MAX) a.nl = PK_NL_MAX;
+    // An even count: the two expansion groups take alternate stages, so with an even ring a slot always serves the same
+    // group, and a group only ever waits for the fill that follows one it has consumed itself.  (A parity wait cannot
+    // tell "this fill has landed" from "the fill before it has not landed yet"; with an odd ring the fill before is the
+    // other group's and nothing orders it before the wait.)
+    a.nl &= ~1;
+    if (a.nl < 2) return HBQ_ERR_UNSUPPORTED;
+    CUtensorMap mx;
+    { const int rc = gemm_make_map(&mx, X, M, K, a.m_pad); if (rc) return rc; }
+    const size_t smem = 1024 + (size_t)a.ne * ES + (size_t)a.nl * LS + PK_CTRL_BYTES;
+    if (container_bits == 4) return ms == 0 ? launch_packed<0, 4>(mx, mx, a, grid, smem, stream) : launch_packed<2, 4>(mx, mx, a, grid, smem, stream);
+    return ms == 0 ? launch_packed<0, 8>(mx, mx, a, grid, smem, stream) : launch_packed<2, 8>(mx, mx, a, grid, smem, stream);
+}
+
 int gemm_w4_launch(const void* X, const void* Wp, void* C, int64_t M, int64_t N, int64_t K, const hbq_format* f,
                    int container_bits, const void* bias, void* workspace, cudaStream_t stream, uint32_t poll_limit)
 {
@@ -672,34 +943,15 @@ int gemm_w4_launch(const void* X, const void* Wp, void* C, int64_t M, int64_t N,
     if ((reinterpret_cast<uintptr_t>(C) | reinterpret_cast<uintptr_t>(bias)) & 1) return HBQ_ERR_ALIGN;
     int sms = 0;
     { const int rc = device_sms(&sms); if (rc) return rc; }
-    a.wp = (const uint8_t*)Wp; a.C = (__half*)C; a.bias = (const __half*)bias;
-    a.M = (int)M; a.N = (int)N; a.K = (int)K;
-    a.m_pad = (int)((M + 15) / 16 * 16);
-    a.nblk = (int)(K / PK_KB); a.tiles = (int)(N / PK_ROWS);
-    a.total = (int64_t)a.tiles * a.nblk;
-    const int grid = (int)(a.total < sms ? a.total : sms);
-    a.ws = (float*)workspace;
-    a.counters = (int*)((uint8_t*)workspace + (int64_t)sms * 2 * a.m_pad * PK_ROWS * 4);
-    const uint32_t LS = (uint32_t)pk_rec_bytes(container_bits), ES = PK_EXP_BYTES + (uint32_t)a.m_pad * 256u;
-    // three operand stages unless that leaves fewer than four record stages (many tokens and the 8-bit container)
-    a.ne = PK_NE;
-    uint32_t avail = 227u * 1024u - 1024u - (uint32_t)a.ne * ES - PK_CTRL_BYTES;
-    if (avail / LS < 4) { a.ne = 2; avail = 227u * 1024u - 1024u - 2u * ES - PK_CTRL_BYTES; }
-    a.nl = (int)(avail / LS);
-    if (a.nl > PK_NL_MAX) a.nl = PK_NL_MAX;
-    // An even count: the two expansion groups take alternate stages, so with an even ring a slot always serves the same
-    // group, and a group only ever waits for the fill that follows one it has consumed itself.  (A parity wait cannot
-    // tell "this fill has landed" from "the fill before it has not landed yet"; with an odd ring the fill before is the
-    // other group's and nothing orders it before the wait.)
-    a.nl &= ~1;
-    if (a.nl < 2) return HBQ_ERR_UNSUPPORTED;
-    a.acc_cols = a.m_pad <= 32 ? 32u : (a.m_pad <= 64 ? 64u : 128u);
     a.poll_limit = poll_limit ? poll_limit : (1u << 23);
-    CUtensorMap mx;
-    { const int rc = gemm_make_map(&mx, X, M, K, a.m_pad); if (rc) return rc; }
-    const size_t smem = 1024 + (size_t)a.ne * ES + (size_t)a.nl * LS + PK_CTRL_BYTES;
-    if (container_bits == 4) return ms == 0 ? launch_packed<0, 4>(mx, mx, a, grid, smem, stream) : launch_packed<2, 4>(mx, mx, a, grid, smem, stream);
-    return ms == 0 ? launch_packed<0, 8>(mx, mx, a, grid, smem, stream) : launch_packed<2, 8>(mx, mx, a, grid, smem, stream);
+    // more than 64 tokens: two launches, one after the other on the stream, over the same workspace
+    for (int64_t m0 = 0; m0 < M; m0 += 64) {
+        const int64_t rows = M - m0 < 64 ? M - m0 : 64;
+        const int rc = w4_launch_rows((const __half*)X + m0 * K, Wp, (__half*)C + m0 * N, rows, N, K, a, ms, container_bits, bias,
+                                      workspace, sms, stream);
+        if (rc) return rc;
+    }
+    return HBQ_OK;
 }
 
 int gemm_w4_status(int* host_out)

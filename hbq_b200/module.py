@@ -91,7 +91,7 @@ class QLinear(nn.Linear):
 
     def prepare_decode(self, wq=None, drop_fp16: bool = False) -> bool:
         """Keep the packed weight also in the tile order of ``hbq_gemm_w4`` so that batches of up to
-        ``w4_max_rows`` rows multiply against 4-bit codes and scales expanded in shared memory (same products as
+        ``w4_max_rows`` rows multiply against 4-bit codes and scales expanded on chip (same products as
         with the fp16 tensor: the expanded values are its values bit for bit).  ``drop_fp16`` frees the fp16 tensor:
         the layer then holds 0.56 B per weight and EVERY batch goes through the packed kernel, 128 rows per launch
         (a capacity mode: large batches are slower than on the fp16 tensor).  Returns False, and changes nothing, for

@@ -102,7 +102,7 @@ class HBQLinearMethod:
     def __init__(self, act_quantizer, wgt_quantizer, packed_weights: bool = False):
         """``packed_weights``: keep each weight ONLY as 4-bit codes and scales in the tile order of ``hbq_gemm_w4``
         (0.56 B per weight; formats and shapes outside that kernel keep the fp16 tensor) -- the engine then holds a
-        3.6x smaller model and every batch multiplies against codes expanded in shared memory."""
+        3.6x smaller model and every batch multiplies against codes expanded on chip."""
         self.act_quantizer = act_quantizer
         self.wgt_quantizer = wgt_quantizer
         self.packed_weights = packed_weights

@@ -237,7 +237,7 @@ int hbq_gemm_wait_selftest(const void* A, const void* W, void* C, int64_t M, int
 /* ---- GEMM on the packed weight (decode shapes) ---------------------------------------------- */
 
 /* C[M,N] = X[M,K] * deq(W)[N,K]^T for M <= 128 tokens, reading W as packed 4-bit codes, block scales and
- * micro-scale indices (0.5625 B per weight) and expanding it to the fp16 fake-quantised values in shared memory
+ * micro-scale indices (0.5625 B per weight) and expanding it to the fp16 fake-quantised values on chip (tensor memory)
  * in front of the tensor core; fp32 accumulation, fp16 output, bias as in hbq_gemm.  Replaces, for a statically
  * quantised HBQ weight (src/ptq.py:349, the fp16 tensor the reference keeps) under fp32 accumulation, the
  * F.linear of _QBaseLinear.forward (src/module.py:64) at decode-sized batches, where the time is the streaming
@@ -254,14 +254,17 @@ int hbq_gemm_wait_selftest(const void* A, const void* W, void* C, int64_t M, int
  *
  * container_bits: 4 -- codes as stored, {sign, e1, e0, m} per nibble, records of 9216 bytes (0.5625 B per weight);
  * 8 -- each code as the top byte of its value's fp16 pattern (the low byte is zero for E2M1), records of 17408 bytes
- * (1.0625 B per weight).  Same values either way; the 8-bit container halves the instructions of the expansion, which,
- * not the bytes, is what bounds the 4-bit form on B200.  prepack and gemm must be given the same value.
+ * (1.0625 B per weight).  Same values either way; the 4-bit form goes through the hardware's E2M1 conversion, the
+ * 8-bit form through a byte permute, and on B200 the 4-bit form is the faster one (fewer bytes, as few
+ * instructions).  prepack and gemm must be given the same value.
  *
  * workspace: hbq_gemm_w4_workspace_bytes(M, N, K) bytes (-1: shape not served), 16-byte aligned, ZEROED ONCE by
- * the caller before its first use; the kernel leaves it usable for the next call on the same stream.  The work is
- * cut into equal runs of (128 rows, 128 k) records, one run per SM, whatever tile boundaries fall inside a run; the
- * parts of a tile that different SMs computed meet here as fp32 partial sums (two slots per SM) and are added in a
- * fixed order, so results do not vary from run to run; one counter per tile tells which SM finishes it.  After a
+ * the caller before its first use; the kernel leaves it usable for the next call on the same stream, of any M up
+ * to the M it was sized for.  Where there are enough tiles every SM takes whole tiles and the workspace is not
+ * touched.  Otherwise the work is cut into equal runs of (128 rows, 128 k) records, one run per SM, whatever tile
+ * boundaries fall inside a run; the parts of a tile that different SMs computed meet here as fp32 partial sums
+ * (two slots per SM) and are added in a fixed order, so results do not vary from run to run; one counter per tile
+ * (at the start of the workspace) tells which SM finishes it.  More than 64 tokens run as two launches.  After a
  * call that hbq_gemm_status reports as failed, zero it again. */
 int64_t hbq_gemm_w4_prepacked_bytes(int64_t N, int64_t K, int container_bits);
 int hbq_gemm_w4_prepack(const hbq_packed_out* in, int64_t N, int64_t K, const hbq_format* fmt, int container_bits,

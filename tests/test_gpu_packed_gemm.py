@@ -1,7 +1,7 @@
 """GPU: the GEMM on the packed 4-bit weight (hbq_gemm_w4, both code containers) against the same product on the fp16 fake-quantised tensor
 the reference keeps (src/ptq.py:349, F.linear in src/module.py:64).
 
-Two bars.  (1) The values the kernel expands in shared memory are the fake-quantised weights BIT FOR BIT: one-hot rows
+Two bars.  (1) The values the kernel expands on chip are the fake-quantised weights BIT FOR BIT: one-hot rows
 of X make every output a single product 1 * w, so C spells out the expanded tile.  (2) With real activations the
 result is the fp32-accumulated product rounded to fp16: relative Frobenius error <= 2^-9 against an fp64 product of
 the same fp16 operands and at most 1 % of the outputs further than 2 fp16 ulps from it (the bound of the fp16-operand
