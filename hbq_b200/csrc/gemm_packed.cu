@@ -78,6 +78,7 @@ constexpr int PK_EXP_WARP0 = PK_EPI_WARPS + 4;              // warps 4, 5, 6: re
 constexpr int PK_SERVICE0 = PK_EXP_WARP0 + PK_EXP_WARPS;       // warps 24, 25: waiters of expansion groups 0, 1; 26, 27: their reporters
 constexpr int PK_THREADS = (PK_SERVICE0 + 4) * 32;
 constexpr int PK_CTRL_BYTES = 512;
+constexpr int PK_CLUSTER_STAGES = 2;                          // ... what meeting in a cluster's shared memory costs
 constexpr int PK_FIXUP_STAGES = 10;                           // what sharing tiles between CTAs costs, in stages
 
 struct PkArgs {
@@ -96,6 +97,7 @@ struct PkArgs {
     uint32_t tmem_cols;         // columns allocated: the accumulators, then (packed weight) `ne` expanded stages of 64
     uint32_t poll_limit;
     int whole_tiles;            // 1: every CTA takes whole tiles (no tile is shared, nothing to fix up)
+    int split;                  // S >= 2: a tile's K range is split over the S CTAs of a cluster; 0: no clusters
 };
 
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel)
@@ -257,8 +259,12 @@ gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = gridDim.x, cta = blockIdx.x;
-    const int64_t g0 = a.whole_tiles ? (int64_t)a.tiles * cta / G * a.nblk : run_begin(a.total, cta, G);
-    const int64_t g1 = a.whole_tiles ? (int64_t)a.tiles * (cta + 1) / G * a.nblk : run_begin(a.total, cta + 1, G);
+    // cluster split: CTA `rank` of the S in a cluster takes the rank-th of S equal parts of its tile's K blocks
+    const int split_tile = a.split ? cta / a.split : 0, split_rank = a.split ? cta % a.split : 0;
+    const int64_t g0 = a.split ? (int64_t)split_tile * a.nblk + a.nblk * split_rank / a.split
+                     : a.whole_tiles ? (int64_t)a.tiles * cta / G * a.nblk : run_begin(a.total, cta, G);
+    const int64_t g1 = a.split ? (int64_t)split_tile * a.nblk + a.nblk * (split_rank + 1) / a.split
+                     : a.whole_tiles ? (int64_t)a.tiles * (cta + 1) / G * a.nblk : run_begin(a.total, cta + 1, G);
     const int nst = (int)(g1 - g0);
     // The run's stages are taken in three pieces: the head of the tile that the NEXT CTA completes, the whole tiles, and
     // last the end of the tile that the PREVIOUS CTA began.  A tile shared by two CTAs is thus begun early by one and
@@ -565,7 +571,7 @@ gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
             // the tile's segments sit in consecutive CTAs
             int c_first = cta, c_last = cta;
             bool closing = false;
-            if (!whole) {
+            if (!whole && !a.split) {
                 c_first = cta_of_stage(a.total, (int64_t)tile * a.nblk, G);
                 c_last = cta_of_stage(a.total, (int64_t)tile * a.nblk + a.nblk - 1, G);
                 // This CTA ends the tile: while its MMAs still run, see whether every other CTA of the tile has already
@@ -615,7 +621,12 @@ gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
                     #pragma unroll
                     for (int i = 0; i < 16; ++i) v[i] += acc[i];
                 }
-                if (whole || closing) {
+                if (a.split) {
+                    // the cluster adds the parts of the tile from its CTAs' shared memory (teardown)
+                    #pragma unroll
+                    for (int i = 0; i < 16; ++i)
+                        asm volatile("st.shared.f32 [%0], %1;" ::"r"(ld0 + (uint32_t)((c0 + i) * PK_ROWS + nloc) * 4u), "f"(v[i]) : "memory");
+                } else if (whole || closing) {
                     __half* cp = a.C + (int64_t)c0 * a.N + gn;
                     #pragma unroll
                     for (int i = 0; i < 16; ++i) {
@@ -635,7 +646,7 @@ gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
             if (lane == 0) mbar_arrive(bar_aempty + 8 * buf);
             if (closing) {
                 if (threadIdx.x == 0) a.counters[tile] = 0;
-            } else if (!whole) {
+            } else if (!whole && !a.split) {
                 // the CTA that arrives last adds the tile's partial sums in CTA order.
                 // Every thread orders its own partial sums before the count (a fence by the counting thread alone, after
                 // the barrier, was seen to let a reader on another SM run ahead of a warp's stores)
@@ -693,6 +704,50 @@ gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
         const unsigned long long t0 = gtime_ns();
         while (gtime_ns() - t0 < 200000ull) { }          // copies that may still be in flight land before smem is released
         __syncthreads();
+    }
+    if (a.split) {
+        // Every CTA of the cluster has left its part of the tile (fp32, [token][row]) at the start of its record ring.
+        // Each CTA adds a share of the tokens, reading all parts in rank order through distributed shared memory, and
+        // writes C; the second barrier keeps every CTA's shared memory alive until all have read it.  Every thread of the
+        // cluster reaches both barriers.
+        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+        if (warp < PK_EPI_WARPS && !*abort_flag) {
+            // CTA `rank` adds the tokens of its share, reading every CTA's part in rank order
+            const int nloc = threadIdx.x, gn = split_tile * PK_ROWS + nloc;
+            const __half bv = a.bias ? a.bias[gn] : __float2half_rn(0.f);
+            const int m_lo = a.M * split_rank / a.split, m_hi = a.M * (split_rank + 1) / a.split;
+            for (int m0 = m_lo; m0 < m_hi; m0 += 8) {
+                float acc[8];
+                #pragma unroll
+                for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+                for (int r = 0; r < a.split; r += 2) {
+                    float w[2][8];
+                    #pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        uint32_t remote;
+                        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(ld0 + (uint32_t)nloc * 4u), "r"(min(r + u, a.split - 1)));
+                        #pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            w[u][i] = 0.f;
+                            if (r + u < a.split && m0 + i < m_hi)
+                                asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(w[u][i]) : "r"(remote + (uint32_t)((m0 + i) * PK_ROWS) * 4u) : "memory");
+                        }
+                    }
+                    #pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        #pragma unroll
+                        for (int i = 0; i < 8; ++i) acc[i] += w[u][i];
+                    }
+                }
+                #pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    __half o = __float2half_rn(acc[i]);
+                    if (a.bias) o = __hadd(o, bv);
+                    if (m0 + i < m_hi) a.C[(int64_t)(m0 + i) * a.N + gn] = o;
+                }
+            }
+        }
+        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
     }
     if (warp == 5) {
         tc_fence_after();
@@ -829,9 +884,49 @@ template <int MS, int CB>
 static int launch_packed(const CUtensorMap& mx, const CUtensorMap& mw, const PkArgs& a, int grid, size_t smem, cudaStream_t stream)
 {
     { const int rc = ensure_dynamic_smem(gemm_packed_kernel<MS, CB>, smem); if (rc) return rc; }
-    gemm_packed_kernel<MS, CB><<<grid, PK_THREADS, smem, stream>>>(mx, mw, a);
+    if (a.split) {
+        cudaLaunchConfig_t cfg;
+        memset(&cfg, 0, sizeof(cfg));
+        cfg.gridDim = dim3((unsigned)grid); cfg.blockDim = dim3(PK_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeClusterDimension;
+        at[0].val.clusterDim.x = (unsigned)a.split; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+        cfg.attrs = at; cfg.numAttrs = 1;
+        HBQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_packed_kernel<MS, CB>, mx, mw, a));
+    } else {
+        gemm_packed_kernel<MS, CB><<<grid, PK_THREADS, smem, stream>>>(mx, mw, a);
+    }
     HBQ_LAUNCH_CHECK("gemm_packed_kernel");
     return HBQ_OK;
+}
+
+// How many clusters of S CTAs of the kernel the device holds at once (0 on error); asked once per (kernel, S, smem).
+template <int MS, int CB>
+static int max_clusters_of(int S, size_t smem)
+{
+    static std::mutex mu;
+    static int cached[9];
+    static size_t cached_smem[9];
+    std::lock_guard<std::mutex> lock(mu);
+    if (cached_smem[S] == smem && cached[S] != 0) return cached[S] < 0 ? 0 : cached[S];
+    if (ensure_dynamic_smem(gemm_packed_kernel<MS, CB>, smem)) return 0;
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3((unsigned)(S * 64)); cfg.blockDim = dim3(PK_THREADS); cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = (unsigned)S; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_packed_kernel<MS, CB>, &cfg) != cudaSuccess) { (void)cudaGetLastError(); n = 0; }
+    cached[S] = n > 0 ? n : -1;
+    cached_smem[S] = smem;
+    return n;
+}
+static int max_clusters(int ms, int cb, int S, size_t smem)
+{
+    if (cb == 4) return ms == 0 ? max_clusters_of<0, 4>(S, smem) : max_clusters_of<2, 4>(S, smem);
+    return ms == 0 ? max_clusters_of<0, 8>(S, smem) : max_clusters_of<2, 8>(S, smem);
 }
 
 // The same pipeline on an fp16 weight [N, K] (no expansion: TMA puts the weight tiles straight into the operand
@@ -896,16 +991,6 @@ static int w4_launch_rows(const void* X, const void* Wp, void* C, int64_t M, int
     a.m_pad = (int)((M + 15) / 16 * 16);
     a.nblk = (int)(K / PK_KB); a.tiles = (int)(N / PK_ROWS);
     a.total = (int64_t)a.tiles * a.nblk;
-    // Equal runs of K blocks per SM share tiles between CTAs, and the fix-up of a shared tile is a chain of dependent
-    // round trips through memory worth about twenty stages.  Where whole tiles per CTA cost fewer stages than that on
-    // top, every CTA takes whole tiles and nothing is fixed up.
-    int grid = (int)(a.total < sms ? a.total : sms);
-    {
-        const int grid_w = a.tiles < sms ? a.tiles : sms;
-        const int64_t stages_w = (int64_t)((a.tiles + grid_w - 1) / grid_w) * a.nblk, stages_k = (a.total + grid - 1) / grid;
-        a.whole_tiles = stages_w - stages_k <= PK_FIXUP_STAGES;
-        if (a.whole_tiles) grid = grid_w;
-    }
     a.counters = (int*)workspace;
     a.ws = (float*)((uint8_t*)workspace + w4_counter_bytes(a.tiles));
     const uint32_t LS = (uint32_t)pk_rec_bytes(container_bits), ES = (uint32_t)a.m_pad * 256u;
@@ -926,6 +1011,27 @@ static int w4_launch_rows(const void* X, const void* Wp, void* C, int64_t M, int
     CUtensorMap mx;
     { const int rc = gemm_make_map(&mx, X, M, K, a.m_pad); if (rc) return rc; }
     const size_t smem = 1024 + (size_t)a.ne * ES + (size_t)a.nl * LS + PK_CTRL_BYTES;
+    // Three ways to cut the work, costed in stages per CTA:
+    //  - equal runs of (tile, block) records per SM: tiles are shared between CTAs, and the fix-up of a shared tile is a
+    //    chain of dependent round trips through memory worth about ten stages;
+    //  - whole tiles per CTA: nothing to fix up, but SMs idle where the tiles do not fill them;
+    //  - few tiles: a tile's K blocks split over the S CTAs of a thread-block cluster, whose parts meet in distributed
+    //    shared memory behind a cluster barrier (about two stages); S is the largest size whose clusters all fit on
+    //    the device at once and whose parts fit the record ring.
+    int grid = (int)(a.total < sms ? a.total : sms);
+    {
+        const int grid_w = a.tiles < sms ? a.tiles : sms;
+        const int64_t stages_w = (int64_t)((a.tiles + grid_w - 1) / grid_w) * a.nblk;
+        const int64_t stages_k = (a.total + grid - 1) / grid + PK_FIXUP_STAGES;
+        int S = sms / a.tiles;
+        if (S > 8) S = 8;
+        if (S > a.nblk) S = a.nblk;
+        if ((uint32_t)a.nl * LS < (uint32_t)a.m_pad * PK_ROWS * 4u) S = 0;
+        while (S >= 2 && max_clusters(ms, container_bits, S, smem) < a.tiles) --S;
+        const int64_t stages_c = S >= 2 ? (a.nblk + S - 1) / S + PK_CLUSTER_STAGES : (1ll << 40);
+        if (stages_c < stages_w && stages_c <= stages_k) { a.split = S; grid = a.tiles * S; }
+        else if (stages_w <= stages_k) { a.whole_tiles = 1; grid = grid_w; }
+    }
     if (container_bits == 4) return ms == 0 ? launch_packed<0, 4>(mx, mx, a, grid, smem, stream) : launch_packed<2, 4>(mx, mx, a, grid, smem, stream);
     return ms == 0 ? launch_packed<0, 8>(mx, mx, a, grid, smem, stream) : launch_packed<2, 8>(mx, mx, a, grid, smem, stream);
 }

@@ -39,7 +39,7 @@ def _ulps(a, b):
 
 @pytest.mark.parametrize("bits", [4, 8])
 @pytest.mark.parametrize("name", ["hbq_a_wgt", "hbq_e_wgt", "hbq_fp1", "hbq_fpm100"])
-@pytest.mark.parametrize("shape", [(256, 512), (1024, 4096)])
+@pytest.mark.parametrize("shape", [(256, 512), (1024, 4096), (19200, 2048)])
 def test_expanded_values_are_the_fake_quantised_weights(name, shape, bits):
     spec = load_formats()[name]
     if spec["mbit"] != 1 or spec["block_size"] != 128 or spec["l2_block_size"] not in (8, 32) or spec["l2_sc_bit"] != 2:
@@ -62,7 +62,9 @@ def test_expanded_values_are_the_fake_quantised_weights(name, shape, bits):
 
 @pytest.mark.parametrize("bits", [4, 8])
 @pytest.mark.parametrize("name", ["hbq_a_wgt", "hbq_e_wgt"])
-@pytest.mark.parametrize("N,K", [(14336, 4096), (4096, 14336), (1024, 4096), (128, 128)])
+# the three ways the work is cut: whole tiles per SM (14336 x 4096, 128 x 128), a tile's K split over a cluster
+# (4096 x 14336, 1024 x 4096), equal runs of records per SM with tiles shared between CTAs (19200 x 2048)
+@pytest.mark.parametrize("N,K", [(14336, 4096), (4096, 14336), (1024, 4096), (128, 128), (19200, 2048)])
 def test_against_the_fp16_operand_product(name, N, K, bits):
     import hbq_b200 as H
     from hbq_b200 import blockquant_ext as ext
