@@ -31,9 +31,10 @@ class QLinear(nn.Linear):
         self.packed_weight = None
         self.w4_weight = None          # the packed weight in the decode GEMM's tile order (prepare_decode)
         self.w4_max_rows = 0           # batches up to this many rows take it while the fp16 tensor is kept; 0: none --
-                                       # on B200 the packed kernel runs at about 0.65x the library fp16 GEMM for
-                                       # 1..16 rows (its limit is instruction issue, not bytes), so what it buys is
-                                       # the 3.6x smaller weight (prepare_decode(drop_fp16=True)), not time
+                                       # on B200 the packed kernel runs at 0.85-1.3x the library fp16 GEMM for
+                                       # 1..16 rows depending on the shape (faster on the MLP shapes, slower on
+                                       # the 4096 x 4096 projections), so it stays opt-in; what it always buys is
+                                       # the 3.6x smaller weight (prepare_decode(drop_fp16=True))
 
     def forward(self, x: torch.Tensor, input_quantized: bool = False):
         """``input_quantized``: ``x`` has been through ``self.aq`` already (a producer that fuses the
