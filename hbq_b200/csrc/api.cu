@@ -315,9 +315,10 @@ int hbq_gemm_uses_tensor_cores(int64_t M, int64_t N, int64_t K, int b_is_nk, int
     return gemm_tc_eligible(M, N, K, mode, group_k, group_n) ? 1 : 0;
 }
 
-// Decode-sized fp32-accumulation products whose 128-column tiles would not fill the SMs run the stream-K pipeline
-// (gemm_packed.cu) when the caller hands over its workspace; without one they take the tile-per-CTA kernel.
-// Measured on B200 (16 tokens): [4096, 14336] 34 us against 63 us, [4096, 4096] 21 against 23; with 112 tiles
+// Decode-sized fp32-accumulation products whose 128-column tiles would not fill the SMs run the pipeline of
+// gemm_packed.cu with fp16 weight tiles (a tile's K split over a thread-block cluster, or equal runs of K blocks per
+// SM) when the caller hands over its workspace; without one they take the tile-per-CTA kernel.
+// Measured on B200 (16 tokens): [4096, 14336] 28 us against 63 us, [4096, 4096] 15 against 23; with 112 tiles
 // ([14336, 4096]) or more than 32 tokens the tile-per-CTA kernel is the faster one.
 static bool decode_stream_k(int64_t M, int64_t N, int64_t K, int mode)
 {

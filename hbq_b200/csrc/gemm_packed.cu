@@ -245,6 +245,7 @@ gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
     const uint32_t ne = (uint32_t)a.ne;
     const uint32_t ld0 = exp0 + ne * ES;
     const uint32_t ctrl_u = ld0 + (uint32_t)a.nl * LS;
+    const uint32_t stg = CB == 16 ? exp0 : ld0;                      // where a cluster's CTAs leave their parts of a tile (free by then)
     uint8_t* ctrl = smem_raw + (ctrl_u - raw);
     // control block: ld_full[16] ld_empty[16] ex_full[6] ex_empty[6] acc_full[2] acc_empty[2] (8 B each), then the
     // tensor-memory base, the abort flag and the "this CTA completes the tile" flag
@@ -625,7 +626,7 @@ gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
                     // the cluster adds the parts of the tile from its CTAs' shared memory (teardown)
                     #pragma unroll
                     for (int i = 0; i < 16; ++i)
-                        asm volatile("st.shared.f32 [%0], %1;" ::"r"(ld0 + (uint32_t)((c0 + i) * PK_ROWS + nloc) * 4u), "f"(v[i]) : "memory");
+                        asm volatile("st.shared.f32 [%0], %1;" ::"r"(stg + (uint32_t)((c0 + i) * PK_ROWS + nloc) * 4u), "f"(v[i]) : "memory");
                 } else if (whole || closing) {
                     __half* cp = a.C + (int64_t)c0 * a.N + gn;
                     #pragma unroll
@@ -706,7 +707,8 @@ gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
         __syncthreads();
     }
     if (a.split) {
-        // Every CTA of the cluster has left its part of the tile (fp32, [token][row]) at the start of its record ring.
+        // Every CTA of the cluster has left its part of the tile (fp32, [token][row]) at the start of its record ring
+        // (fp16 weight: of its operand stages).
         // Each CTA adds a share of the tokens, reading all parts in rank order through distributed shared memory, and
         // writes C; the second barrier keeps every CTA's shared memory alive until all have read it.  Every thread of the
         // cluster reaches both barriers.
@@ -725,7 +727,7 @@ gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
                     #pragma unroll
                     for (int u = 0; u < 2; ++u) {
                         uint32_t remote;
-                        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(ld0 + (uint32_t)nloc * 4u), "r"(min(r + u, a.split - 1)));
+                        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(stg + (uint32_t)nloc * 4u), "r"(min(r + u, a.split - 1)));
                         #pragma unroll
                         for (int i = 0; i < 8; ++i) {
                             w[u][i] = 0.f;
@@ -929,6 +931,32 @@ static int max_clusters(int ms, int cb, int S, size_t smem)
     return ms == 0 ? max_clusters_of<0, 8>(S, smem) : max_clusters_of<2, 8>(S, smem);
 }
 
+// Three ways to cut the work, costed in stages per CTA; sets a.split / a.whole_tiles and returns the grid:
+//  - equal runs of (tile, block) records per SM: tiles are shared between CTAs, and the fix-up of a shared tile is a
+//    chain of dependent round trips through memory worth about ten stages;
+//  - whole tiles per CTA: nothing to fix up, but SMs idle where the tiles do not fill them;
+//  - few tiles: a tile's K blocks split over the S CTAs of a thread-block cluster, whose parts meet in distributed
+//    shared memory behind a cluster barrier (about two stages); S is the largest size whose clusters all fit on
+//    the device at once and whose parts (fp32, m_pad x 128) fit the `staging_bytes` that are free by then.
+static int choose_split(PkArgs& a, int sms, int ms, int cb, size_t smem, uint32_t staging_bytes)
+{
+    int grid = (int)(a.total < sms ? a.total : sms);
+    const int grid_w = a.tiles < sms ? a.tiles : sms;
+    const int64_t stages_w = (int64_t)((a.tiles + grid_w - 1) / grid_w) * a.nblk;
+    const int64_t stages_k = (a.total + grid - 1) / grid + PK_FIXUP_STAGES;
+    int S = sms / a.tiles;
+    if (S > 8) S = 8;
+    if (S > a.nblk) S = a.nblk;
+    if (staging_bytes < (uint32_t)a.m_pad * PK_ROWS * 4u) S = 0;
+    while (S >= 2 && (cb == 16 ? max_clusters_of<0, 16>(S, smem) : max_clusters(ms, cb, S, smem)) < a.tiles) --S;
+    const int64_t stages_c = S >= 2 ? (a.nblk + S - 1) / S + PK_CLUSTER_STAGES : (1ll << 40);
+    a.split = 0;
+    a.whole_tiles = 0;
+    if (stages_c < stages_w && stages_c <= stages_k) { a.split = S; grid = a.tiles * S; }
+    else if (stages_w <= stages_k) { a.whole_tiles = 1; grid = grid_w; }
+    return grid;
+}
+
 // The same pipeline on an fp16 weight [N, K] (no expansion: TMA puts the weight tiles straight into the operand
 // stages): the fp32-accumulation GEMM for decode-sized M, where giving a CTA whole 128-column tiles over the full K
 // would leave most SMs idle.  Equal runs of (tile, block) stages per SM; partial tiles meet in the workspace.
@@ -957,7 +985,6 @@ int gemm_w16_launch(const void* X, const void* W, void* C, int64_t M, int64_t N,
     a.m_pad = (int)((M + 15) / 16 * 16);
     a.nblk = (int)(K / PK_KB); a.tiles = (int)(N / PK_ROWS);
     a.total = (int64_t)a.tiles * a.nblk;
-    const int grid = (int)(a.total < sms ? a.total : sms);
     a.counters = (int*)workspace;
     a.ws = (float*)((uint8_t*)workspace + w4_counter_bytes(a.tiles));
     const uint32_t ES = PK_EXP_BYTES + (uint32_t)a.m_pad * 256u;
@@ -973,9 +1000,10 @@ int gemm_w16_launch(const void* X, const void* W, void* C, int64_t M, int64_t N,
     CUtensorMap mx, mw;
     { const int rc = gemm_make_map(&mx, X, M, K, a.m_pad); if (rc) return rc; }
     { const int rc = gemm_make_map(&mw, W, N, K, PK_ROWS); if (rc) return rc; }
-    // the tile counters must read zero; the workspace is the caller's scratch, so they are cleared here
-    HBQ_CUDA_TRY(cudaMemsetAsync(a.counters, 0, (size_t)a.tiles * 4, stream));
     const size_t smem = 1024 + (size_t)a.ne * ES + PK_CTRL_BYTES;
+    const int grid = choose_split(a, sms, 0, 16, smem, (uint32_t)a.ne * ES);
+    // equal runs: the tile counters must read zero; the workspace is the caller's scratch, so they are cleared here
+    if (!a.split && !a.whole_tiles) HBQ_CUDA_TRY(cudaMemsetAsync(a.counters, 0, (size_t)a.tiles * 4, stream));
     return launch_packed<0, 16>(mx, mw, a, grid, smem, stream);
 }
 
@@ -1011,27 +1039,7 @@ static int w4_launch_rows(const void* X, const void* Wp, void* C, int64_t M, int
     CUtensorMap mx;
     { const int rc = gemm_make_map(&mx, X, M, K, a.m_pad); if (rc) return rc; }
     const size_t smem = 1024 + (size_t)a.ne * ES + (size_t)a.nl * LS + PK_CTRL_BYTES;
-    // Three ways to cut the work, costed in stages per CTA:
-    //  - equal runs of (tile, block) records per SM: tiles are shared between CTAs, and the fix-up of a shared tile is a
-    //    chain of dependent round trips through memory worth about ten stages;
-    //  - whole tiles per CTA: nothing to fix up, but SMs idle where the tiles do not fill them;
-    //  - few tiles: a tile's K blocks split over the S CTAs of a thread-block cluster, whose parts meet in distributed
-    //    shared memory behind a cluster barrier (about two stages); S is the largest size whose clusters all fit on
-    //    the device at once and whose parts fit the record ring.
-    int grid = (int)(a.total < sms ? a.total : sms);
-    {
-        const int grid_w = a.tiles < sms ? a.tiles : sms;
-        const int64_t stages_w = (int64_t)((a.tiles + grid_w - 1) / grid_w) * a.nblk;
-        const int64_t stages_k = (a.total + grid - 1) / grid + PK_FIXUP_STAGES;
-        int S = sms / a.tiles;
-        if (S > 8) S = 8;
-        if (S > a.nblk) S = a.nblk;
-        if ((uint32_t)a.nl * LS < (uint32_t)a.m_pad * PK_ROWS * 4u) S = 0;
-        while (S >= 2 && max_clusters(ms, container_bits, S, smem) < a.tiles) --S;
-        const int64_t stages_c = S >= 2 ? (a.nblk + S - 1) / S + PK_CLUSTER_STAGES : (1ll << 40);
-        if (stages_c < stages_w && stages_c <= stages_k) { a.split = S; grid = a.tiles * S; }
-        else if (stages_w <= stages_k) { a.whole_tiles = 1; grid = grid_w; }
-    }
+    const int grid = choose_split(a, sms, ms, container_bits, smem, (uint32_t)a.nl * LS);
     if (container_bits == 4) return ms == 0 ? launch_packed<0, 4>(mx, mx, a, grid, smem, stream) : launch_packed<2, 4>(mx, mx, a, grid, smem, stream);
     return ms == 0 ? launch_packed<0, 8>(mx, mx, a, grid, smem, stream) : launch_packed<2, 8>(mx, mx, a, grid, smem, stream);
 }
