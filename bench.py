@@ -434,8 +434,8 @@ def act_quant_record(dev, peaks, steps: int = 30):
 
 
 def decode_gemm_record(dev, rows: int = 16, copies: int = 8, reps: int = 6):
-    """Decode-sized linear layers of configs[3] (Llama-3-8B MLP: 4096 -> 14336 and 14336 -> 4096, `rows` tokens, HBQ-A
-    weights): the GEMM on the packed 4-bit weight (hbq_gemm_w4, 0.5625 B per weight) beside the same product on the
+    """Decode-sized linear layers of configs[3] (the seven linears of a Llama-3-8B decoder layer, `rows` tokens, HBQ-A
+    weights; `llama3_8b_layer_linears` is their sum per layer): the GEMM on the packed 4-bit weight (hbq_gemm_w4, 0.5625 B per weight) beside the same product on the
     fp16 fake-quantised tensor by this library's tensor-core kernel and by F.linear (the reference's path,
     src/module.py:64).  Each variant walks `copies` separate weights back to back so that no call finds its weight in
     L2; the walk is replayed from a CUDA graph and timed with CUDA events: us per call on the device."""
@@ -475,22 +475,30 @@ def decode_gemm_record(dev, rows: int = 16, copies: int = 8, reps: int = 6):
         del graph
         return best
 
-    for N, Kd in ((14336, 4096), (4096, 14336)):
+    # the linear layers of one Llama-3-8B decoder layer: gate / up, down, q / o, k / v (times they occur)
+    layer = {(14336, 4096): 2, (4096, 14336): 1, (4096, 4096): 2, (1024, 4096): 2}
+    for (N, Kd) in layer:
         w = (0.02 * torch.randn(N, Kd, device=dev)).half()
         packed, deq = q.quantize_packed(w, with_deq=True)
-        w4s = [W4Weight.from_packed(packed) for _ in range(copies)]
-        w8s = [W4Weight.from_packed(packed, container_bits=8) for _ in range(copies)]
-        deqs = [deq.clone() for _ in range(copies)]
+        n_copies = max(copies, -(-300_000_000 // (N * Kd * 2)))       # the walk covers more than twice the L2
+        w4s = [W4Weight.from_packed(packed) for _ in range(n_copies)]
+        deqs = [deq.clone() for _ in range(n_copies)]
         x = torch.randn(rows, Kd, device=dev).half()
-        outs = [torch.empty(rows, N, device=dev, dtype=torch.float16) for _ in range(copies)]
+        outs = [torch.empty(rows, N, device=dev, dtype=torch.float16) for _ in range(n_copies)]
         t4 = walk([(lambda ww=ww, o=o: ww.matmul(x, out=o)) for ww, o in zip(w4s, outs)])
-        t8 = walk([(lambda ww=ww, o=o: ww.matmul(x, out=o)) for ww, o in zip(w8s, outs)])
         tt = walk([(lambda d=d, o=o: ext.gemm_fp32_accum(x, d, b_is_nk=True, out=o)) for d, o in zip(deqs, outs)])
         tl = walk([(lambda d=d, o=o: torch.mm(x, d.t(), out=o)) for d, o in zip(deqs, outs)])
-        rec["shapes"][f"N{N}_K{Kd}"] = {"w4": t4, "w4_in_8bit_containers": t8, "w8_bytes": w8s[0].nbytes(), "fp16_tc": tt, "fp16_library": tl, "w4_bytes": w4s[0].nbytes(),
-                                        "fp16_bytes": N * Kd * 2, "w4_GBs": w4s[0].nbytes() / t4 / 1e3,
-                                        "fp16_library_GBs": N * Kd * 2 / tl / 1e3}
-        del w4s, w8s, deqs, outs
+        one = {"w4": t4, "fp16_tc": tt, "fp16_library": tl, "w4_bytes": w4s[0].nbytes(), "fp16_bytes": N * Kd * 2,
+               "w4_GBs": w4s[0].nbytes() / t4 / 1e3, "fp16_library_GBs": N * Kd * 2 / tl / 1e3}
+        if Kd * N >= 4096 * 14336:
+            w8s = [W4Weight.from_packed(packed, container_bits=8) for _ in range(n_copies)]
+            one["w4_in_8bit_containers"] = walk([(lambda ww=ww, o=o: ww.matmul(x, out=o)) for ww, o in zip(w8s, outs)])
+            one["w8_bytes"] = w8s[0].nbytes()
+            del w8s
+        rec["shapes"][f"N{N}_K{Kd}"] = one
+        del w4s, deqs, outs
+    rec["llama3_8b_layer_linears"] = {k: sum(layer[(N, Kd)] * rec["shapes"][f"N{N}_K{Kd}"][k] for (N, Kd) in layer)
+                                      for k in ("w4", "fp16_tc", "fp16_library")}
     torch.cuda.empty_cache()
     return rec
 
