@@ -91,7 +91,8 @@ struct PkArgs {
     int m_pad;                  // tokens rounded up to 16: the MMA's N
     int nblk, tiles, nl;
     int ne;                     // operand stages: 3, or 2 when the tokens' tiles are large
-    int64_t total;              // tiles * nblk stages
+    int total;                  // tiles * nblk stages (below 2^31: a weight of that many records does not fit the device)
+    int run_q, run_r;           // equal runs: total / grid and total % grid -- CTA c takes run_q stages, one more if c < run_r
     uint32_t base2[2], step2[2];// micro-scale t = base + idx * step as packed fp16 pairs, per table
     uint32_t acc_cols;          // tensor-memory columns of one accumulator (32, 64 or 128); four are allocated
     uint32_t tmem_cols;         // columns allocated: the accumulators, then (packed weight) `ne` expanded stages of 64
@@ -208,13 +209,11 @@ __device__ __forceinline__ bool mbar_wait_pair(uint32_t bar0, uint32_t par0, uin
 }
 
 // First stage of CTA c's run, and the CTA whose run holds stage g.
-__device__ __forceinline__ int64_t run_begin(int64_t total, int c, int G) { return total * c / G; }
-__device__ __forceinline__ int cta_of_stage(int64_t total, int64_t g, int G)
+__device__ __forceinline__ int run_begin(const PkArgs& a, int c) { return c * a.run_q + min(c, a.run_r); }
+__device__ __forceinline__ int cta_of_stage(const PkArgs& a, int g)
 {
-    int c = (int)(g * G / total);
-    while (c + 1 < G && run_begin(total, c + 1, G) <= g) ++c;
-    while (c > 0 && run_begin(total, c, G) > g) --c;
-    return c;
+    const int edge = a.run_r * (a.run_q + 1);
+    return g < edge ? g / (a.run_q + 1) : a.run_r + (g - edge) / a.run_q;
 }
 
 // Eight element values given as the top bytes of their fp16 patterns (two words) times the packed scale.
@@ -262,20 +261,21 @@ gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
     const int G = gridDim.x, cta = blockIdx.x;
     // cluster split: CTA `rank` of the S in a cluster takes the rank-th of S equal parts of its tile's K blocks
     const int split_tile = a.split ? cta / a.split : 0, split_rank = a.split ? cta % a.split : 0;
-    const int64_t g0 = a.split ? (int64_t)split_tile * a.nblk + a.nblk * split_rank / a.split
-                     : a.whole_tiles ? (int64_t)a.tiles * cta / G * a.nblk : run_begin(a.total, cta, G);
-    const int64_t g1 = a.split ? (int64_t)split_tile * a.nblk + a.nblk * (split_rank + 1) / a.split
-                     : a.whole_tiles ? (int64_t)a.tiles * (cta + 1) / G * a.nblk : run_begin(a.total, cta + 1, G);
-    const int nst = (int)(g1 - g0);
+    // (32-bit index arithmetic throughout: a 64-bit division costs hundreds of cycles and several sat in every stage)
+    const int g0 = a.split ? split_tile * a.nblk + a.nblk * split_rank / a.split
+                 : a.whole_tiles ? a.tiles * cta / G * a.nblk : run_begin(a, cta);
+    const int g1 = a.split ? split_tile * a.nblk + a.nblk * (split_rank + 1) / a.split
+                 : a.whole_tiles ? a.tiles * (cta + 1) / G * a.nblk : run_begin(a, cta + 1);
+    const int nst = g1 - g0;
     // The run's stages are taken in three pieces: the head of the tile that the NEXT CTA completes, the whole tiles, and
     // last the end of the tile that the PREVIOUS CTA began.  A tile shared by two CTAs is thus begun early by one and
     // ended late by the other, whose fix-up then finds the partner's partial sums already published.
-    const int64_t e1 = (g0 % a.nblk) == 0 ? g0 : min(g1, (g0 / a.nblk + 1) * a.nblk);
-    const int64_t hb = max(e1, g1 - g1 % a.nblk);
-    const int64_t pc_s[3] = {hb, e1, g0};
-    const int pc_n[3] = {(int)(g1 - hb), (int)(hb - e1), (int)(e1 - g0)};
+    const int e1 = (g0 % a.nblk) == 0 ? g0 : min(g1, (g0 / a.nblk + 1) * a.nblk);
+    const int hb = max(e1, g1 - g1 % a.nblk);
+    const int pc_s[3] = {hb, e1, g0};
+    const int pc_n[3] = {g1 - hb, hb - e1, e1 - g0};
     // stage i of the run in processing order -> its global (tile, block) index
-    auto stage_g = [&](int i) -> int64_t {
+    auto stage_g = [&](int i) -> int {
         if (i < pc_n[0]) return pc_s[0] + i;
         i -= pc_n[0];
         return i < pc_n[1] ? pc_s[1] + i : pc_s[2] + (i - pc_n[1]);
@@ -316,8 +316,8 @@ gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
                 for (int i = 0; i < nst; ++i) {
                     if (!mbar_wait(bar_eempty + 8 * es, eph ^ 1u, abort_flag, 1, a.poll_limit)) break;
                     const uint32_t dst = exp0 + es * ES, bar = bar_efull + 8 * es;
-                    const int64_t g = stage_g(i);
-                    const int kb = (int)(g % a.nblk), row0 = (int)(g / a.nblk) * PK_ROWS;
+                    const int g = stage_g(i);
+                    const int kb = g % a.nblk, row0 = g / a.nblk * PK_ROWS;
                     mbar_expect_tx(bar, PK_EXP_BYTES);
                     tma_load_2d(dst, &mapW, kb * PK_KB, row0, bar);
                     tma_load_2d(dst + PK_ROWS * 128, &mapW, kb * PK_KB + 64, row0, bar);
@@ -345,7 +345,7 @@ gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
                 for (int i = 0; i < nst; ++i) {
                     if (!mbar_wait_parked(bar_eempty + 8 * es, eph ^ 1u, abort_flag, 8, park_limit)) break;
                     const uint32_t dst = exp0 + es * ES + WB, bar = bar_efull + 8 * es;
-                    const int kb = (int)(stage_g(i) % a.nblk);
+                    const int kb = stage_g(i) % a.nblk;
                     mbar_expect_tx(bar, (uint32_t)a.m_pad * 256u);
                     tma_load_2d(dst, &mapX, kb * PK_KB, 0, bar);
                     tma_load_2d(dst + (uint32_t)a.m_pad * 128u, &mapX, kb * PK_KB + 64, 0, bar);
@@ -379,9 +379,9 @@ gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
         bool pre = p < nst && mbar_test(bar_efull + 8 * ((uint32_t)p % ne), ((uint32_t)p / ne) & 1u);
         int j = 0, first = 0;
         for (int pc = 0; pc < 3 && ok; ++pc)
-        for (int64_t g = pc_s[pc], gend = pc_s[pc] + pc_n[pc]; g < gend && ok; ++j) {
-            const int kb = (int)(g % a.nblk);
-            const int len = (int)min((int64_t)(a.nblk - kb), gend - g);
+        for (int g = pc_s[pc], gend = pc_s[pc] + pc_n[pc]; g < gend && ok; ++j) {
+            const int kb = g % a.nblk;
+            const int len = min(a.nblk - kb, gend - g);
             const uint32_t buf = (uint32_t)j & 1u;
             // the epilogue must have drained this accumulator pair's previous segment
             if (!(ok = mbar_wait_warp(bar_aempty + 8 * buf, (((uint32_t)j >> 1) & 1u) ^ 1u, abort_flag, 7, a.poll_limit))) break;
@@ -436,7 +436,7 @@ gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
             if (!reporter && lane == 0) {
                 for (int i = p; i < nst && i < (int)ne; i += 2) {
                     const uint32_t dst = exp0 + (uint32_t)i * ES + WB, bar = bar_efull + 8 * (uint32_t)i;
-                    const int kb = (int)(stage_g(i) % a.nblk);
+                    const int kb = stage_g(i) % a.nblk;
                     mbar_expect_tx(bar, (uint32_t)a.m_pad * 256u);
                     tma_load_2d(dst, &mapX, kb * PK_KB, 0, bar);
                     tma_load_2d(dst + (uint32_t)a.m_pad * 128u, &mapX, kb * PK_KB + 64, 0, bar);
@@ -454,7 +454,7 @@ gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
                         // the slot is free: the tokens' two K tiles of this stage go into it; their bytes complete the same
                         // barrier as the reporter's arrival, so an MMA thread waits once per stage
                         const uint32_t dst = exp0 + es * ES + WB, bar = bar_efull + 8 * es;
-                        const int kb = (int)(stage_g(i) % a.nblk);
+                        const int kb = stage_g(i) % a.nblk;
                         mbar_expect_tx(bar, (uint32_t)a.m_pad * 256u);
                         tma_load_2d(dst, &mapX, kb * PK_KB, 0, bar);
                         tma_load_2d(dst + (uint32_t)a.m_pad * 128u, &mapX, kb * PK_KB + 64, 0, bar);
@@ -537,7 +537,7 @@ gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
             // The fix-up is a chain of dependent round trips to memory this SM has not touched yet (counters, partial
             // sums, C), and each first touch pays an address-translation miss of a few microseconds.  Touch those pages
             // now, while the first stages are on their way; the values are not used.
-            const int64_t ta = g0 / a.nblk, tb = (g1 - 1) / a.nblk;
+            const int ta = g0 / a.nblk, tb = (g1 - 1) / a.nblk;
             const char* pz = nullptr;
             switch (lane) {
             case 0: pz = (const char*)(a.counters + ta); break;
@@ -560,9 +560,9 @@ gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
         }
         int j = 0, first = 0;
         for (int pc = 0; pc < 3 && ok; ++pc)
-        for (int64_t g = pc_s[pc], gend = pc_s[pc] + pc_n[pc]; g < gend; ++j) {
-            const int tile = (int)(g / a.nblk), kb = (int)(g % a.nblk);
-            const int len = (int)min((int64_t)(a.nblk - kb), gend - g);
+        for (int g = pc_s[pc], gend = pc_s[pc] + pc_n[pc]; g < gend; ++j) {
+            const int tile = g / a.nblk, kb = g % a.nblk;
+            const int len = min(a.nblk - kb, gend - g);
             // issuer p accumulated the segment's stages of parity p: a one-stage segment has only one of the two
             const bool has0 = len >= 2 || (first & 1) == 0, has1 = len >= 2 || (first & 1) == 1;
             first += len;
@@ -573,8 +573,8 @@ gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
             int c_first = cta, c_last = cta;
             bool closing = false;
             if (!whole && !a.split) {
-                c_first = cta_of_stage(a.total, (int64_t)tile * a.nblk, G);
-                c_last = cta_of_stage(a.total, (int64_t)tile * a.nblk + a.nblk - 1, G);
+                c_first = cta_of_stage(a, tile * a.nblk);
+                c_last = cta_of_stage(a, tile * a.nblk + a.nblk - 1);
                 // This CTA ends the tile: while its MMAs still run, see whether every other CTA of the tile has already
                 // published its partial sums.  Then the tile is completed from the accumulator, with no partial sums of
                 // this CTA, no fence and no count on the way.
@@ -594,7 +594,7 @@ gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
             if (!ok) break;
             tc_fence_after();
             const int gn = tile * PK_ROWS + nloc;
-            float* part = a.ws + ((int64_t)cta * 2 + (tile == (int)(g0 / a.nblk) ? 0 : 1)) * a.m_pad * PK_ROWS + nloc;
+            float* part = a.ws + ((int64_t)cta * 2 + (tile == g0 / a.nblk ? 0 : 1)) * a.m_pad * PK_ROWS + nloc;
             const __half bv = a.bias ? a.bias[gn] : __float2half_rn(0.f);
             for (int c0 = 0; c0 < a.m_pad; c0 += 16) {
                 float v[16];
@@ -611,7 +611,7 @@ gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
                     #pragma unroll
                     for (int i = 0; i < 16; ++i) acc[i] = 0.f;
                     for (int cc = c_first; cc < c_last; ++cc) {
-                        const int slot = tile == (int)(run_begin(a.total, cc, G) / a.nblk) ? 0 : 1;
+                        const int slot = tile == run_begin(a, cc) / a.nblk ? 0 : 1;
                         const float* q = a.ws + ((int64_t)cc * 2 + slot) * a.m_pad * PK_ROWS + nloc;
                         float w[16];
                         #pragma unroll
@@ -672,7 +672,7 @@ gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
                             #pragma unroll
                             for (int u = 0; u < 2; ++u) {
                                 const int cu = cc + u <= c_last ? cc + u : c_last;
-                                const int slot = tile == (int)(run_begin(a.total, cu, G) / a.nblk) ? 0 : 1;
+                                const int slot = tile == run_begin(a, cu) / a.nblk ? 0 : 1;
                                 const float* p = a.ws + ((int64_t)cu * 2 + slot) * a.m_pad * PK_ROWS + nloc;
                                 #pragma unroll
                                 for (int i = 0; i < 16; ++i)
@@ -839,7 +839,7 @@ static bool w4_format(const hbq_format* f, PkArgs* a, int* micro_shift)
 static bool w4_shape(int64_t M, int64_t N, int64_t K)
 {
     return M >= 1 && M <= 128 && N >= PK_ROWS && (N % PK_ROWS) == 0 && K >= PK_KB && (K % PK_KB) == 0 &&
-           N <= (1ll << 24) && K <= (1ll << 24);
+           N <= (1ll << 24) && K <= (1ll << 24) && (N / PK_ROWS) * (K / PK_KB) < (1ll << 30);
 }
 
 static bool w4_container(int cb) { return cb == 4 || cb == 8; }
@@ -940,7 +940,9 @@ static int max_clusters(int ms, int cb, int S, size_t smem)
 //    the device at once and whose parts (fp32, m_pad x 128) fit the `staging_bytes` that are free by then.
 static int choose_split(PkArgs& a, int sms, int ms, int cb, size_t smem, uint32_t staging_bytes)
 {
-    int grid = (int)(a.total < sms ? a.total : sms);
+    int grid = a.total < sms ? a.total : sms;
+    a.run_q = a.total / grid;
+    a.run_r = a.total % grid;
     const int grid_w = a.tiles < sms ? a.tiles : sms;
     const int64_t stages_w = (int64_t)((a.tiles + grid_w - 1) / grid_w) * a.nblk;
     const int64_t stages_k = (a.total + grid - 1) / grid + PK_FIXUP_STAGES;
@@ -984,7 +986,7 @@ int gemm_w16_launch(const void* X, const void* W, void* C, int64_t M, int64_t N,
     a.M = (int)M; a.N = (int)N; a.K = (int)K;
     a.m_pad = (int)((M + 15) / 16 * 16);
     a.nblk = (int)(K / PK_KB); a.tiles = (int)(N / PK_ROWS);
-    a.total = (int64_t)a.tiles * a.nblk;
+    a.total = a.tiles * a.nblk;
     a.counters = (int*)workspace;
     a.ws = (float*)((uint8_t*)workspace + w4_counter_bytes(a.tiles));
     const uint32_t ES = PK_EXP_BYTES + (uint32_t)a.m_pad * 256u;
@@ -1018,7 +1020,7 @@ static int w4_launch_rows(const void* X, const void* Wp, void* C, int64_t M, int
     a.M = (int)M; a.N = (int)N; a.K = (int)K;
     a.m_pad = (int)((M + 15) / 16 * 16);
     a.nblk = (int)(K / PK_KB); a.tiles = (int)(N / PK_ROWS);
-    a.total = (int64_t)a.tiles * a.nblk;
+    a.total = a.tiles * a.nblk;
     a.counters = (int*)workspace;
     a.ws = (float*)((uint8_t*)workspace + w4_counter_bytes(a.tiles));
     const uint32_t LS = (uint32_t)pk_rec_bytes(container_bits), ES = (uint32_t)a.m_pad * 256u;
