@@ -38,9 +38,9 @@ class W4Weight:
     @classmethod
     def from_packed(cls, packed: PackedTensor, container_bits: int = 4) -> "W4Weight":
         """Rearrange the planes of ``quantize_packed`` (``hbq_gemm_w4_prepack``); raises for formats outside the kernel.
-        ``container_bits``: 4 keeps the codes as nibbles (0.5625 B per weight); 8 stores each code as the top byte of its
-        value's fp16 pattern (1.0625 B per weight), which halves the expansion's instructions -- the faster form on B200,
-        where instruction issue and not bytes bounds the kernel."""
+        ``container_bits``: 4 keeps the codes as nibbles (0.5625 B per weight), expanded by the hardware's E2M1
+        conversion -- the smaller and on B200 the faster form; 8 stores each code as the top byte of its value's fp16
+        pattern (1.0625 B per weight), expanded by a byte permute."""
         N, K = packed.shape
         L = _lib.lib()
         nbytes = int(L.hbq_gemm_w4_prepacked_bytes(N, K, container_bits))
