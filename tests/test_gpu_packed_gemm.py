@@ -63,8 +63,9 @@ def test_expanded_values_are_the_fake_quantised_weights(name, shape, bits):
 @pytest.mark.parametrize("bits", [4, 8])
 @pytest.mark.parametrize("name", ["hbq_a_wgt", "hbq_e_wgt"])
 # the three ways the work is cut: whole tiles per SM (14336 x 4096, 128 x 128), a tile's K split over a cluster
-# (4096 x 14336, 1024 x 4096), equal runs of records per SM with tiles shared between CTAs (19200 x 2048)
-@pytest.mark.parametrize("N,K", [(14336, 4096), (4096, 14336), (1024, 4096), (128, 128), (19200, 2048)])
+# (4096 x 14336, 1024 x 4096), equal runs of records per SM with tiles shared between CTAs (19200 x 2048); 19200 x 256 is
+# more whole tiles than SMs
+@pytest.mark.parametrize("N,K", [(14336, 4096), (4096, 14336), (1024, 4096), (128, 128), (19200, 2048), (19200, 256)])
 def test_against_the_fp16_operand_product(name, N, K, bits):
     import hbq_b200 as H
     from hbq_b200 import blockquant_ext as ext
