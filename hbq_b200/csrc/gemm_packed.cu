@@ -17,8 +17,8 @@
 // access), so the expanded weights never pass through shared memory: writing 32 KB per stage and having the tensor
 // core read it back was, with the record and the X tiles, some 90 KB of shared-memory traffic per 9 KB record and
 // the bound of the earlier design.  The accumulator D^T[n, m] sits in tensor memory as well; the SM's 512 columns
-// hold four accumulators (two issuers x two segments in flight) of 32 or 64 columns and six or four expanded stages.
-// More than 64 tokens are two launches.
+// hold four accumulators (two issuers x two segments in flight) of 32 or 64 columns and six or four expanded stages;
+// beyond 64 tokens two accumulators of 128 columns (one segment in flight) and four stages.
 //
 // Prepacked weight (hbq_gemm_w4_prepack): one 9216-byte record per (tile of 128 rows, block of 128 k) -- what one
 // pipeline stage consumes, fetched with ONE bulk async copy:
@@ -94,7 +94,8 @@ struct PkArgs {
     int total;                  // tiles * nblk stages (below 2^31: a weight of that many records does not fit the device)
     int run_q, run_r;           // equal runs: total / grid and total % grid -- CTA c takes run_q stages, one more if c < run_r
     uint32_t base2[2], step2[2];// micro-scale t = base + idx * step as packed fp16 pairs, per table
-    uint32_t acc_cols;          // tensor-memory columns of one accumulator (32, 64 or 128); four are allocated
+    uint32_t acc_cols;          // tensor-memory columns of one accumulator (32, 64 or 128)
+    uint32_t acc_bufs;          // accumulator pairs (one per issuer) in flight: 2 (segments alternate), 1 for 128 columns
     uint32_t tmem_cols;         // columns allocated: the accumulators, then (packed weight) `ne` expanded stages of 64
     uint32_t poll_limit;
     int whole_tiles;            // 1: every CTA takes whole tiles (no tile is shared, nothing to fix up)
@@ -382,9 +383,9 @@ gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
         for (int g = pc_s[pc], gend = pc_s[pc] + pc_n[pc]; g < gend && ok; ++j) {
             const int kb = g % a.nblk;
             const int len = min(a.nblk - kb, gend - g);
-            const uint32_t buf = (uint32_t)j & 1u;
+            const uint32_t buf = a.acc_bufs == 2u ? (uint32_t)j & 1u : 0u, use = a.acc_bufs == 2u ? (uint32_t)j >> 1 : (uint32_t)j;
             // the epilogue must have drained this accumulator pair's previous segment
-            if (!(ok = mbar_wait_warp(bar_aempty + 8 * buf, (((uint32_t)j >> 1) & 1u) ^ 1u, abort_flag, 7, a.poll_limit))) break;
+            if (!(ok = mbar_wait_warp(bar_aempty + 8 * buf, (use & 1u) ^ 1u, abort_flag, 7, a.poll_limit))) break;
             const uint32_t d_tmem = tmem_base + (2u * buf + (uint32_t)p) * a.acc_cols;
             bool fresh = true;                                   // this issuer's first MMA of the segment overwrites
             for (int i = first + ((p - first) & 1); i < first + len; i += 2) {
@@ -396,7 +397,7 @@ gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
                 const bool nxt = (int)ni < nst && mbar_test(bar_efull + 8 * (ni % ne), (ni / ne) & 1u);
                 if (leader) {
                     const uint32_t wa = exp0 + es * ES, xa = wa + WB;
-                    const uint32_t wt = tmem_base + 4u * a.acc_cols + es * 64u;      // the expanded stage in tensor memory
+                    const uint32_t wt = tmem_base + 2u * a.acc_bufs * a.acc_cols + es * 64u;      // the expanded stage in tensor memory
                     #pragma unroll
                     for (int h = 0; h < 2; ++h) {
                         #pragma unroll
@@ -503,7 +504,7 @@ gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
             const uint32_t l2q = l2w >> (2 * ((8 * hh) >> MS));
             // the stage in tensor memory: lane = weight row (this warp's quarter), 64 columns of two k each; this thread
             // writes columns 32 hh + 4 c + {0..3} for its chunk c
-            const uint32_t out = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + 4u * a.acc_cols + es * 64u + (uint32_t)hh * 32u;
+            const uint32_t out = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + 2u * a.acc_bufs * a.acc_cols + es * 64u + (uint32_t)hh * 32u;
             uint32_t t2 = 0u, ts2 = 0u;
             #pragma unroll
             for (int c = 0; c < 8; ++c) {
@@ -567,7 +568,7 @@ gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
             const bool has0 = len >= 2 || (first & 1) == 0, has1 = len >= 2 || (first & 1) == 1;
             first += len;
             g += len;
-            const uint32_t buf = (uint32_t)j & 1u;
+            const uint32_t buf = a.acc_bufs == 2u ? (uint32_t)j & 1u : 0u, use = a.acc_bufs == 2u ? (uint32_t)j >> 1 : (uint32_t)j;
             const bool whole = len == a.nblk;
             // the tile's segments sit in consecutive CTAs
             int c_first = cta, c_last = cta;
@@ -590,7 +591,7 @@ gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
                     if (closing) __threadfence();
                 }
             }
-            ok = ok && mbar_wait_parked_warp(bar_afull + 8 * buf, ((uint32_t)j >> 1) & 1u, abort_flag, 6, park_limit);
+            ok = ok && mbar_wait_parked_warp(bar_afull + 8 * buf, use & 1u, abort_flag, 6, park_limit);
             if (!ok) break;
             tc_fence_after();
             const int gn = tile * PK_ROWS + nloc;
@@ -997,6 +998,7 @@ int gemm_w16_launch(const void* X, const void* W, void* C, int64_t M, int64_t N,
     if (a.ne < 2) return HBQ_ERR_UNSUPPORTED;
     a.nl = 0;
     a.acc_cols = a.m_pad <= 32 ? 32u : (a.m_pad <= 64 ? 64u : 128u);
+    a.acc_bufs = 2u;
     a.tmem_cols = 4u * a.acc_cols;
     a.poll_limit = 1u << 23;
     CUtensorMap mx, mw;
@@ -1011,8 +1013,8 @@ int gemm_w16_launch(const void* X, const void* W, void* C, int64_t M, int64_t N,
 
 // workspace: gemm_w4_workspace_bytes() bytes, 16-byte aligned, zeroed once by the caller (the kernel leaves the tile
 // counters at zero again); one call at a time per workspace.
-// One launch: at most 64 tokens (four accumulators of up to 64 columns and the expanded stages share the SM's 512
-// tensor-memory columns).
+// One launch.  The accumulators and the expanded stages share the SM's 512 tensor-memory columns: up to 64 tokens two
+// accumulator pairs (segments alternate between them), beyond that one pair of 128 columns.
 static int w4_launch_rows(const void* X, const void* Wp, void* C, int64_t M, int64_t N, int64_t K, PkArgs a, int ms,
                           int container_bits, const void* bias, void* workspace, int sms, cudaStream_t stream)
 {
@@ -1024,10 +1026,11 @@ static int w4_launch_rows(const void* X, const void* Wp, void* C, int64_t M, int
     a.counters = (int*)workspace;
     a.ws = (float*)((uint8_t*)workspace + w4_counter_bytes(a.tiles));
     const uint32_t LS = (uint32_t)pk_rec_bytes(container_bits), ES = (uint32_t)a.m_pad * 256u;
-    // tensor memory: four accumulators, then the expanded stages (64 columns each): six of them, four for 64 tokens
-    a.acc_cols = a.m_pad <= 32 ? 32u : 64u;
+    // tensor memory: the accumulators, then the expanded stages (64 columns each): six of them, four beyond 32 tokens
+    a.acc_cols = a.m_pad <= 32 ? 32u : (a.m_pad <= 64 ? 64u : 128u);
+    a.acc_bufs = a.m_pad <= 64 ? 2u : 1u;
     a.tmem_cols = 512u;
-    a.ne = (int)((a.tmem_cols - 4u * a.acc_cols) / 64u);
+    a.ne = (int)((a.tmem_cols - 2u * a.acc_bufs * a.acc_cols) / 64u);
     if (a.ne > PK_NE) a.ne = PK_NE;
     const uint32_t avail = 227u * 1024u - 1024u - (uint32_t)a.ne * ES - PK_CTRL_BYTES;
     a.nl = (int)(avail / LS);
@@ -1060,14 +1063,7 @@ int gemm_w4_launch(const void* X, const void* Wp, void* C, int64_t M, int64_t N,
     int sms = 0;
     { const int rc = device_sms(&sms); if (rc) return rc; }
     a.poll_limit = poll_limit ? poll_limit : (1u << 23);
-    // more than 64 tokens: two launches, one after the other on the stream, over the same workspace
-    for (int64_t m0 = 0; m0 < M; m0 += 64) {
-        const int64_t rows = M - m0 < 64 ? M - m0 : 64;
-        const int rc = w4_launch_rows((const __half*)X + m0 * K, Wp, (__half*)C + m0 * N, rows, N, K, a, ms, container_bits, bias,
-                                      workspace, sms, stream);
-        if (rc) return rc;
-    }
-    return HBQ_OK;
+    return w4_launch_rows(X, Wp, C, M, N, K, a, ms, container_bits, bias, workspace, sms, stream);
 }
 
 int gemm_w4_status(int* host_out)

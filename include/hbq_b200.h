@@ -264,7 +264,7 @@ int hbq_gemm_wait_selftest(const void* A, const void* W, void* C, int64_t M, int
  * touched.  Otherwise the work is cut into equal runs of (128 rows, 128 k) records, one run per SM, whatever tile
  * boundaries fall inside a run; the parts of a tile that different SMs computed meet here as fp32 partial sums
  * (two slots per SM) and are added in a fixed order, so results do not vary from run to run; one counter per tile
- * (at the start of the workspace) tells which SM finishes it.  More than 64 tokens run as two launches.  After a
+ * (at the start of the workspace) tells which SM finishes it.  After a
  * call that hbq_gemm_status reports as failed, zero it again. */
 int64_t hbq_gemm_w4_prepacked_bytes(int64_t N, int64_t K, int container_bits);
 int hbq_gemm_w4_prepack(const hbq_packed_out* in, int64_t N, int64_t K, const hbq_format* fmt, int container_bits,
