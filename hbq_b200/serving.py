@@ -99,20 +99,24 @@ class HBQLinearMethod:
     activations and multiplies.  The product is the reference's ``F.linear`` (fp32 accumulation) on the tensor-core
     kernel, whose 128-column tile serves decode-sized batches."""
 
-    def __init__(self, act_quantizer, wgt_quantizer, packed_weights: bool = False):
+    def __init__(self, act_quantizer, wgt_quantizer, packed_weights: bool = False, packed_max_rows: int = 0):
         """``packed_weights``: keep each weight ONLY as 4-bit codes and scales in the tile order of ``hbq_gemm_w4``
         (0.56 B per weight; formats and shapes outside that kernel keep the fp16 tensor) -- the engine then holds a
-        3.6x smaller model and every batch multiplies against codes expanded on chip."""
+        3.6x smaller model and every batch multiplies against codes expanded on chip.
+        ``packed_max_rows`` (1..128, with ``packed_weights`` off): keep the packed weight BESIDE the fp16 tensor and
+        send batches of up to that many tokens -- decode steps -- through the packed kernel, which streams 3.6x fewer
+        bytes per step; larger batches multiply against the fp16 tensor."""
         self.act_quantizer = act_quantizer
         self.wgt_quantizer = wgt_quantizer
         self.packed_weights = packed_weights
+        self.packed_max_rows = 0 if packed_weights else max(0, min(int(packed_max_rows), 128))
 
     @torch.inference_mode()
     def process_weights_after_loading(self, layer: torch.nn.Module) -> None:
         if getattr(layer, "hbq_weight_quantized", False) or getattr(layer, "weight", None) is None:
             return
         w4 = None
-        if self.packed_weights and layer.weight.is_cuda and layer.weight.dtype == torch.float16 and \
+        if (self.packed_weights or self.packed_max_rows) and layer.weight.is_cuda and layer.weight.dtype == torch.float16 and \
                 hasattr(self.wgt_quantizer, "quantize_packed"):
             from ._lib import HbqError
             from .packed_gemm import W4Weight
@@ -124,6 +128,7 @@ class HBQLinearMethod:
                 w4 = None
         if w4 is not None:
             layer.hbq_w4_weight = w4
+        if w4 is not None and self.packed_weights:
             layer.weight.data = torch.empty(0, dtype=layer.weight.dtype, device=layer.weight.device)
         else:
             layer.weight.data = self.wgt_quantizer.q(layer.weight.data).to(layer.weight.dtype)
@@ -132,7 +137,7 @@ class HBQLinearMethod:
     def apply(self, layer: torch.nn.Module, x: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
         xq = self.act_quantizer.q(x)
         w4 = getattr(layer, "hbq_w4_weight", None)
-        if w4 is not None:
+        if w4 is not None and (layer.weight.numel() == 0 or xq.numel() // xq.shape[-1] <= self.packed_max_rows):
             x2d = xq.reshape(-1, xq.shape[-1])
             y = torch.empty((x2d.shape[0], w4.shape[0]), dtype=torch.float16, device=x2d.device)
             for r0 in range(0, x2d.shape[0], 128):

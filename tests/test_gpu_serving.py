@@ -109,3 +109,32 @@ def test_linear_method_on_packed_weights():
         assert outs[-1].shape == (3, 50, N)
     rel = float((outs[0].double() - outs[1].double()).norm() / outs[0].double().norm())
     assert rel <= 2.0 ** -9, rel
+
+
+def test_linear_method_decode_batches_on_the_packed_weight():
+    """``packed_max_rows``: the fp16 tensor stays, decode-sized batches take the packed kernel (one GEMM launch of this
+    library per call either way), larger ones the fp16 tensor; both agree with the plain method."""
+    import hbq_b200 as H
+    from hbq_b200 import serving
+    fm = load_formats()
+    K, N = 2048, 1024
+    g = torch.Generator(device="cuda").manual_seed(13)
+    w0 = (0.02 * torch.randn((N, K), device="cuda", generator=g)).half()
+    layers = []
+    for rows_max in (0, 16):
+        method = serving.HBQLinearMethod(make_quantizer(fm["hbq_a_act"]), make_quantizer(fm["hbq_a_wgt"]), packed_max_rows=rows_max)
+        layer = torch.nn.Linear(K, N, bias=False, device="cuda", dtype=torch.float16)
+        layer.weight.data = w0.clone()
+        method.process_weights_after_loading(layer)
+        assert layer.weight.numel() == N * K and (getattr(layer, "hbq_w4_weight", None) is not None) == (rows_max > 0)
+        layers.append((method, layer))
+    assert torch.equal(layers[0][1].weight.data, layers[1][1].weight.data)
+    for rows in (1, 16, 17, 200):
+        x = torch.randn((rows, K), device="cuda", generator=g).half()
+        y0 = layers[0][0].apply(layers[0][1], x)
+        y1 = layers[1][0].apply(layers[1][1], x)
+        rel = float((y0.double() - y1.double()).norm() / y0.double().norm())
+        assert y1.shape == (rows, N) and rel <= 2.0 ** -9, (rows, rel)
+        if rows > 16:
+            assert torch.equal(y0, y1)                 # the same kernel on the same fp16 tensor
+    assert H.gemm_status() == 0
