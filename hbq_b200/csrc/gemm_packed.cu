@@ -758,6 +758,110 @@ gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
     }
 }
 
+// ---- one or two tokens: no tensor core ---------------------------------------------------------------------
+// For M <= 2 the MMA path's cost per stage (eight MMAs of fixed cost, barriers) is several times the record's time on
+// HBM.  Here a warp owns 32 weight rows (lane = row) and every KS-th 128-k block of them: it reads its part of the
+// record with plain 16-byte loads (a warp's lanes cover 512 contiguous bytes of a piece), expands eight codes at a
+// time exactly as the MMA path does and multiplies with the tokens' values from shared memory (the same address in
+// every lane: a broadcast) in fma.rn.f32.f16 -- the product of two fp16 values is exact in fp32, the sum is fp32.
+// The KS warps of a CTA meet in shared memory and are added in warp order, so results do not vary from run to run;
+// nothing is shared between CTAs.
+struct GvArgs {
+    const uint8_t* wp;
+    const __half* x;            // [M, K]
+    __half* C;                  // [M, N]
+    const __half* bias;
+    int M, N, K, nblk, ks;
+    uint32_t base2[2], step2[2];
+};
+
+__device__ __forceinline__ void fma2_f32(float& acc, uint32_t w2, uint32_t x2)
+{
+    asm("{ .reg .b16 wl, wh, xl, xh;\n mov.b32 {wl, wh}, %1;\n mov.b32 {xl, xh}, %2;\n"
+        " fma.rn.f32.f16 %0, wl, xl, %0;\n fma.rn.f32.f16 %0, wh, xh, %0; }" : "+f"(acc) : "r"(w2), "r"(x2));
+}
+
+template <int MS, int MT>
+__global__ void __launch_bounds__(512) gemv_packed_kernel(const GvArgs a)
+{
+    extern __shared__ uint8_t gv_smem[];
+    uint4* xs = reinterpret_cast<uint4*>(gv_smem);                               // [MT][K] fp16
+    float* red = reinterpret_cast<float*>(gv_smem + (size_t)MT * a.K * 2);        // [ks][MT][32]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    {
+        const uint4* src = reinterpret_cast<const uint4*>(a.x);
+        const int n16 = a.M * a.K / 8;
+        for (int i = threadIdx.x; i < MT * a.K / 8; i += blockDim.x) xs[i] = i < n16 ? __ldg(src + i) : make_uint4(0u, 0u, 0u, 0u);
+    }
+    __syncthreads();
+    const int unit = blockIdx.x, tile = unit >> 2, r = (unit & 3) * 32 + lane;    // this lane's row inside the tile
+    const uint8_t* rec0 = a.wp + (int64_t)tile * a.nblk * pk_rec_bytes(4);
+    float acc[MT];
+    #pragma unroll
+    for (int m = 0; m < MT; ++m) acc[m] = 0.f;
+    uint4 cw[4], nw[4];
+    uint2 side, nside;
+    auto fetch = [&](int kb, uint4* c, uint2& sd) {
+        const uint8_t* rec = rec0 + (int64_t)kb * pk_rec_bytes(4);
+        #pragma unroll
+        for (int q = 0; q < 4; ++q)
+            asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(c[q].x), "=r"(c[q].y), "=r"(c[q].z), "=r"(c[q].w) : "l"(rec + (q * PK_ROWS + r) * 16));
+        asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0, %1}, [%2];" : "=r"(sd.x), "=r"(sd.y) : "l"(rec + pk_code_bytes(4) + r * 8));
+    };
+    int kb = warp;
+    if (kb < a.nblk) fetch(kb, nw, nside);
+    for (; kb < a.nblk; kb += a.ks) {
+        #pragma unroll
+        for (int q = 0; q < 4; ++q) cw[q] = nw[q];
+        side = nside;
+        if (kb + a.ks < a.nblk) fetch(kb + a.ks, nw, nside);                      // the next record is on its way under this one
+        const uint32_t l2w = side.x, meta = side.y;
+        const uint32_t sc = meta & 0xFFFFu, s2 = sc * 0x10001u, tb = (meta >> 16) & 1u;
+        const uint32_t base2 = tb ? a.base2[1] : a.base2[0], step2 = tb ? a.step2[1] : a.step2[0];
+        const bool two_step = sc >= 0x7800u;                                     // as in the MMA path's expansion
+        uint32_t t2 = 0u, ts2 = 0u;
+        #pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const uint32_t w4[4] = {cw[q].x, cw[q].y, cw[q].z, cw[q].w};
+            #pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int cb = 4 * q + j;                                        // chunk of 8 k inside the block
+                if (MS == 0 || (cb & 3) == 0) {
+                    const uint32_t idx = (l2w >> (2 * (cb >> MS))) & 3u;
+                    t2 = base2 + idx * step2;
+                    ts2 = h2_bits(__hmul2(bits_h2(t2), bits_h2(s2)));
+                }
+                uint32_t o[4];
+                if (!two_step) expand8<false>(w4[j], ts2, t2, s2, o);
+                else expand8<true>(w4[j], 0u, t2, s2, o);
+                #pragma unroll
+                for (int m = 0; m < MT; ++m) {
+                    const uint4 xv = xs[(m * a.K + kb * PK_KB + cb * 8) >> 3];
+                    fma2_f32(acc[m], o[0], xv.x);
+                    fma2_f32(acc[m], o[1], xv.y);
+                    fma2_f32(acc[m], o[2], xv.z);
+                    fma2_f32(acc[m], o[3], xv.w);
+                }
+            }
+        }
+    }
+    #pragma unroll
+    for (int m = 0; m < MT; ++m) red[(warp * MT + m) * 32 + lane] = acc[m];
+    __syncthreads();
+    if (warp == 0) {
+        const int gn = tile * PK_ROWS + r;
+        #pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            float sum = 0.f;
+            for (int w = 0; w < a.ks; ++w) sum += red[(w * MT + m) * 32 + lane];
+            __half o = __float2half_rn(sum);
+            if (a.bias) o = __hadd(o, a.bias[gn]);
+            if (m < a.M) a.C[(int64_t)m * a.N + gn] = o;
+        }
+    }
+}
+
 // ---- prepack: the planes of hbq_quantize -> the per-(tile, block) records above --------------------------
 struct PrepackArgs {
     const uint8_t* codes;       // [N, K/2]
@@ -1049,6 +1153,33 @@ static int w4_launch_rows(const void* X, const void* Wp, void* C, int64_t M, int
     return ms == 0 ? launch_packed<0, 8>(mx, mx, a, grid, smem, stream) : launch_packed<2, 8>(mx, mx, a, grid, smem, stream);
 }
 
+// One or two tokens on the nibble container: the kernel without the tensor core.
+static int w4_launch_gemv(const void* X, const void* Wp, void* C, int64_t M, int64_t N, int64_t K, const PkArgs& pa, int ms,
+                          const void* bias, int sms, cudaStream_t stream)
+{
+    GvArgs a;
+    memset(&a, 0, sizeof(a));
+    a.wp = (const uint8_t*)Wp; a.x = (const __half*)X; a.C = (__half*)C; a.bias = (const __half*)bias;
+    a.M = (int)M; a.N = (int)N; a.K = (int)K; a.nblk = (int)(K / PK_KB);
+    for (int i = 0; i < 2; ++i) { a.base2[i] = pa.base2[i]; a.step2[i] = pa.step2[i]; }
+    const int units = (int)(N / 32);                       // CTAs: 32 weight rows each
+    // warps per CTA: enough of them over the GPU to cover the memory latency (about twelve per SM), at most one per block
+    int ks = 4;
+    while (ks < 16 && (int64_t)units * ks < (int64_t)sms * 12) ks *= 2;
+    if (ks > a.nblk) ks = a.nblk;
+    a.ks = ks;
+    const int mt = M == 1 ? 1 : 2;
+    const size_t smem = (size_t)mt * K * 2 + (size_t)ks * mt * 32 * 4;
+    auto go = [&](auto kern) -> int {
+        { const int rc = ensure_dynamic_smem(kern, smem); if (rc) return rc; }
+        kern<<<units, ks * 32, smem, stream>>>(a);
+        HBQ_LAUNCH_CHECK("gemv_packed_kernel");
+        return HBQ_OK;
+    };
+    if (ms == 0) return mt == 1 ? go(gemv_packed_kernel<0, 1>) : go(gemv_packed_kernel<0, 2>);
+    return mt == 1 ? go(gemv_packed_kernel<2, 1>) : go(gemv_packed_kernel<2, 2>);
+}
+
 int gemm_w4_launch(const void* X, const void* Wp, void* C, int64_t M, int64_t N, int64_t K, const hbq_format* f,
                    int container_bits, const void* bias, void* workspace, cudaStream_t stream, uint32_t poll_limit)
 {
@@ -1063,6 +1194,8 @@ int gemm_w4_launch(const void* X, const void* Wp, void* C, int64_t M, int64_t N,
     int sms = 0;
     { const int rc = device_sms(&sms); if (rc) return rc; }
     a.poll_limit = poll_limit ? poll_limit : (1u << 23);
+    if (M <= 2 && container_bits == 4 && K * 2 * 2 <= 96 * 1024)
+        return w4_launch_gemv(X, Wp, C, M, N, K, a, ms, bias, sms, stream);
     return w4_launch_rows(X, Wp, C, M, N, K, a, ms, container_bits, bias, workspace, sms, stream);
 }
 

@@ -47,7 +47,7 @@ def test_expanded_values_are_the_fake_quantised_weights(name, shape, bits):
     N, K = shape
     w4, deq = _weight(name, N, K, seed=N + K, bits=bits)
     assert w4.nbytes() == N * K * (9216 if bits == 4 else 17408) // (128 * 128)
-    for rows in (128, 16, 5):
+    for rows in (128, 16, 5, 2, 1):                      # 2 and 1: the kernel without the tensor core (nibble container)
         for off in range(0, K, 128 if K <= 512 else 1024):
             x = torch.zeros((rows, K), device="cuda", dtype=torch.float16)
             cols = (off + torch.arange(rows, device="cuda") * 7) % K
@@ -73,7 +73,7 @@ def test_against_the_fp16_operand_product(name, N, K, bits):
     aq = make_quantizer(load_formats()["hbq_a_act" if name == "hbq_a_wgt" else "hbq_e_act"])
     g = torch.Generator(device="cuda").manual_seed(N)
     bias = torch.randn(N, device="cuda", generator=g).half()
-    for M in (1, 7, 16, 33, 64, 128):
+    for M in (1, 2, 7, 16, 33, 64, 128):
         x = aq.q(torch.randn((M, K), device="cuda", generator=g).half())
         for b in (None, bias):
             c = w4.matmul(x, bias=b)
