@@ -758,8 +758,8 @@ gemm_packed_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_consta
     }
 }
 
-// ---- one or two tokens: no tensor core ---------------------------------------------------------------------
-// For M <= 2 the MMA path's cost per stage (eight MMAs of fixed cost, barriers) is several times the record's time on
+// ---- one token: no tensor core --------------------------------------------------------------------------------
+// For M = 1 the MMA paths' cost per stage (eight MMAs of fixed cost, barriers) is several times the record's time on
 // HBM.  Here a warp owns 32 weight rows (lane = row) and every KS-th 128-k block of them: it reads its part of the
 // record with plain 16-byte loads (a warp's lanes cover 512 contiguous bytes of a piece), expands eight codes at a
 // time exactly as the MMA path does and multiplies with the tokens' values from shared memory (the same address in
@@ -781,9 +781,10 @@ __device__ __forceinline__ void fma2_f32(float& acc, uint32_t w2, uint32_t x2)
         " fma.rn.f32.f16 %0, wl, xl, %0;\n fma.rn.f32.f16 %0, wh, xh, %0; }" : "+f"(acc) : "r"(w2), "r"(x2));
 }
 
-template <int MS, int MT>
+template <int MS>
 __global__ void __launch_bounds__(512) gemv_packed_kernel(const GvArgs a)
 {
+    constexpr int MT = 1;                                                       // tokens
     extern __shared__ uint8_t gv_smem[];
     uint4* xs = reinterpret_cast<uint4*>(gv_smem);                               // [MT][K] fp16
     float* red = reinterpret_cast<float*>(gv_smem + (size_t)MT * a.K * 2);        // [ks][MT][32]
@@ -859,6 +860,139 @@ __global__ void __launch_bounds__(512) gemv_packed_kernel(const GvArgs a)
             if (a.bias) o = __hadd(o, a.bias[gn]);
             if (m < a.M) a.C[(int64_t)m * a.N + gn] = o;
         }
+    }
+}
+
+// ---- two to eight tokens: the warp-level MMA with the weights in registers -----------------------------------
+// tcgen05 pays per 128-k stage eight MMAs of fixed cost and a chain of barriers, about twice the record's time on HBM.
+// For M <= 8 the product also fits ONE mma.sync m16n8k16 per 16 x 16 weights (a second column tile for 9-16 tokens costs
+// more than the tcgen05 path: on B200 this MMA runs at a sixteenth of the tcgen05 rate) with the A operand straight from the expanding thread's
+// registers: no shared memory, no barrier, no hand-off between warps.  A warp owns 32 weight rows (two groups of 16)
+// and every ks-th 128-k block; lane (g, t) = (lane / 4, lane % 4) loads the 16-byte piece t (32 consecutive codes) of
+// rows g and g + 8, expands it as the tcgen05 path does, and uses the four pairs of each word as the A fragments of two
+// MMAs.  The MMA adds over its 16 columns whatever k they stand for, so columns (2t, 2t+1, 2t+8, 2t+9) of step s are
+// k = 32t + 4s + (0..3), and the B fragment of token n = g is X[n][those k]: one 16-byte load per word serves both steps.  Products are exact in fp32 and the sums are fp32.  The ks warps of a slab meet in shared memory
+// and are added in order (results do not vary from run to run); CTAs share nothing.
+struct RgArgs {
+    const uint8_t* wp;
+    const __half* x;            // [M, K]
+    __half* C;                  // [M, N]
+    const __half* bias;
+    int M, N, K, nblk, ks, slabs;
+    uint32_t base2[2], step2[2];
+};
+
+__device__ __forceinline__ void mma_16816(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1)
+{
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int MS>
+__global__ void __launch_bounds__(512) gemm_packed_reg_kernel(const RgArgs a)
+{
+    constexpr int NT = 1;                                                       // column tiles of 8 tokens
+    extern __shared__ float rg_red[];                                           // [ks][slabs][32 lanes][8 NT]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int slab = warp % a.slabs, ksp = warp / a.slabs;
+    const int row0 = (blockIdx.x * a.slabs + slab) * 32, tile = row0 >> 7, rt = row0 & (PK_ROWS - 1);
+    const uint8_t* rec0 = a.wp + (int64_t)tile * a.nblk * pk_rec_bytes(4);
+    float c[2][NT][4];
+    #pragma unroll
+    for (int G2 = 0; G2 < 2; ++G2)
+        #pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+            #pragma unroll
+            for (int i = 0; i < 4; ++i) c[G2][nt][i] = 0.f;
+    uint4 cw[2][2], nw[2][2];                                                   // [group][row g / g + 8]: piece t of the row
+    uint2 sd[2][2], nsd[2][2];
+    auto fetch = [&](int kb, uint4 (*w)[2], uint2 (*s)[2]) {
+        const uint8_t* rec = rec0 + (int64_t)kb * pk_rec_bytes(4);
+        #pragma unroll
+        for (int G2 = 0; G2 < 2; ++G2)
+            #pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int row = rt + 16 * G2 + g + 8 * h;
+                asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(w[G2][h].x), "=r"(w[G2][h].y), "=r"(w[G2][h].z), "=r"(w[G2][h].w) : "l"(rec + (t * PK_ROWS + row) * 16));
+                asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0, %1}, [%2];" : "=r"(s[G2][h].x), "=r"(s[G2][h].y) : "l"(rec + pk_code_bytes(4) + row * 8));
+            }
+    };
+    int kb = ksp;
+    if (kb < a.nblk) fetch(kb, nw, nsd);
+    for (; kb < a.nblk; kb += a.ks) {
+        #pragma unroll
+        for (int G2 = 0; G2 < 2; ++G2)
+            #pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                cw[G2][h] = nw[G2][h];
+                sd[G2][h] = nsd[G2][h];
+            }
+        if (kb + a.ks < a.nblk) fetch(kb + a.ks, nw, nsd);                        // the next record is on its way under this one
+        // token n = g (+ 8) of this lane: eight consecutive k per word (cached: the slabs of a CTA read the same lines)
+        uint4 xv[4][NT];
+        #pragma unroll
+        for (int q = 0; q < 4; ++q)
+            #pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const int n = g + 8 * nt;
+                xv[q][nt] = n < a.M ? __ldg(reinterpret_cast<const uint4*>(a.x + (int64_t)n * a.K + kb * PK_KB + 32 * t + 8 * q))
+                                    : make_uint4(0u, 0u, 0u, 0u);
+            }
+        #pragma unroll
+        for (int G2 = 0; G2 < 2; ++G2) {
+            uint32_t s2[2], base2[2], step2[2];
+            bool two_step[2];
+            #pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const uint32_t meta = sd[G2][h].y, sc = meta & 0xFFFFu, tb = (meta >> 16) & 1u;
+                s2[h] = sc * 0x10001u;
+                base2[h] = tb ? a.base2[1] : a.base2[0];
+                step2[h] = tb ? a.step2[1] : a.step2[0];
+                two_step[h] = sc >= 0x7800u;                                     // as in the tcgen05 path's expansion
+            }
+            #pragma unroll
+            for (int q = 0; q < 4; ++q) {                                        // word q of the lane's piece
+                const int cb = 4 * t + q;                                        // its chunk of 8 k inside the block
+                uint32_t o[2][4];
+                #pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const uint32_t word = q == 0 ? cw[G2][h].x : q == 1 ? cw[G2][h].y : q == 2 ? cw[G2][h].z : cw[G2][h].w;
+                    const uint32_t idx = (sd[G2][h].x >> (2 * (cb >> MS))) & 3u;
+                    const uint32_t t2 = base2[h] + idx * step2[h];
+                    if (!two_step[h]) expand8<false>(word, h2_bits(__hmul2(bits_h2(t2), bits_h2(s2[h]))), t2, s2[h], o[h]);
+                    else expand8<true>(word, 0u, t2, s2[h], o[h]);
+                }
+                #pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    mma_16816(c[G2][nt], o[0][0], o[1][0], o[0][1], o[1][1], xv[q][nt].x, xv[q][nt].y);
+                    mma_16816(c[G2][nt], o[0][2], o[1][2], o[0][3], o[1][3], xv[q][nt].z, xv[q][nt].w);
+                }
+            }
+        }
+    }
+    float* mine = rg_red + ((size_t)(ksp * a.slabs + slab) * 32 + lane) * (8 * NT);
+    #pragma unroll
+    for (int G2 = 0; G2 < 2; ++G2)
+        #pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+            #pragma unroll
+            for (int i = 0; i < 4; ++i) mine[(G2 * NT + nt) * 4 + i] = c[G2][nt][i];
+    __syncthreads();
+    if (ksp == 0) {
+        #pragma unroll
+        for (int G2 = 0; G2 < 2; ++G2)
+            #pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+                #pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    float sum = 0.f;
+                    for (int w = 0; w < a.ks; ++w) sum += rg_red[((size_t)(w * a.slabs + slab) * 32 + lane) * (8 * NT) + (G2 * NT + nt) * 4 + i];
+                    const int gn = row0 + 16 * G2 + g + (i >> 1) * 8, m = 8 * nt + 2 * t + (i & 1);
+                    __half o = __float2half_rn(sum);
+                    if (a.bias) o = __hadd(o, a.bias[gn]);
+                    if (m < a.M) a.C[(int64_t)m * a.N + gn] = o;
+                }
     }
 }
 
@@ -1153,7 +1287,7 @@ static int w4_launch_rows(const void* X, const void* Wp, void* C, int64_t M, int
     return ms == 0 ? launch_packed<0, 8>(mx, mx, a, grid, smem, stream) : launch_packed<2, 8>(mx, mx, a, grid, smem, stream);
 }
 
-// One or two tokens on the nibble container: the kernel without the tensor core.
+// One token on the nibble container: the kernel without the tensor core.
 static int w4_launch_gemv(const void* X, const void* Wp, void* C, int64_t M, int64_t N, int64_t K, const PkArgs& pa, int ms,
                           const void* bias, int sms, cudaStream_t stream)
 {
@@ -1168,16 +1302,38 @@ static int w4_launch_gemv(const void* X, const void* Wp, void* C, int64_t M, int
     while (ks < 16 && (int64_t)units * ks < (int64_t)sms * 12) ks *= 2;
     if (ks > a.nblk) ks = a.nblk;
     a.ks = ks;
-    const int mt = M == 1 ? 1 : 2;
-    const size_t smem = (size_t)mt * K * 2 + (size_t)ks * mt * 32 * 4;
+    const size_t smem = (size_t)K * 2 + (size_t)ks * 32 * 4;
     auto go = [&](auto kern) -> int {
         { const int rc = ensure_dynamic_smem(kern, smem); if (rc) return rc; }
         kern<<<units, ks * 32, smem, stream>>>(a);
         HBQ_LAUNCH_CHECK("gemv_packed_kernel");
         return HBQ_OK;
     };
-    if (ms == 0) return mt == 1 ? go(gemv_packed_kernel<0, 1>) : go(gemv_packed_kernel<0, 2>);
-    return mt == 1 ? go(gemv_packed_kernel<2, 1>) : go(gemv_packed_kernel<2, 2>);
+    return ms == 0 ? go(gemv_packed_kernel<0>) : go(gemv_packed_kernel<2>);
+}
+
+// Two to eight tokens on the nibble container: the warp-level MMA with the weights in registers.
+static int w4_launch_reg(const void* X, const void* Wp, void* C, int64_t M, int64_t N, int64_t K, const PkArgs& pa, int ms,
+                         const void* bias, int sms, cudaStream_t stream)
+{
+    RgArgs a;
+    memset(&a, 0, sizeof(a));
+    a.wp = (const uint8_t*)Wp; a.x = (const __half*)X; a.C = (__half*)C; a.bias = (const __half*)bias;
+    a.M = (int)M; a.N = (int)N; a.K = (int)K; a.nblk = (int)(K / PK_KB);
+    for (int i = 0; i < 2; ++i) { a.base2[i] = pa.base2[i]; a.step2[i] = pa.step2[i]; }
+    // warps of a CTA: slabs of 32 rows x splits of K.  The most slabs that still give every SM a CTA (the slabs of a CTA
+    // read the same lines of X), the rest of the warps split K: eight warps, sixteen where the CTAs do not fill the SMs.
+    int slabs = 4;
+    while (slabs > 1 && N / (32 * slabs) < sms) slabs >>= 1;
+    int ks = (N / (32 * slabs) < sms ? 16 : 8) / slabs;
+    if (ks > a.nblk) ks = a.nblk;
+    a.slabs = slabs; a.ks = ks;
+    const int grid = (int)(N / (32 * slabs));
+    const size_t smem = (size_t)ks * slabs * 32 * 8 * 4;
+    if (ms == 0) gemm_packed_reg_kernel<0><<<grid, ks * slabs * 32, smem, stream>>>(a);
+    else gemm_packed_reg_kernel<2><<<grid, ks * slabs * 32, smem, stream>>>(a);
+    HBQ_LAUNCH_CHECK("gemm_packed_reg_kernel");
+    return HBQ_OK;
 }
 
 int gemm_w4_launch(const void* X, const void* Wp, void* C, int64_t M, int64_t N, int64_t K, const hbq_format* f,
@@ -1194,8 +1350,12 @@ int gemm_w4_launch(const void* X, const void* Wp, void* C, int64_t M, int64_t N,
     int sms = 0;
     { const int rc = device_sms(&sms); if (rc) return rc; }
     a.poll_limit = poll_limit ? poll_limit : (1u << 23);
-    if (M <= 2 && container_bits == 4 && K * 2 * 2 <= 96 * 1024)
+    // the nibble container has two more kernels for the smallest batches (measured on B200, 16 / 8 / 1 tokens x
+    // [14336, 4096]: tcgen05 path 20.3 us, warp-level MMA 17.7 us, no tensor core 14.3 us)
+    if (M == 1 && container_bits == 4 && K * 2 <= 96 * 1024)
         return w4_launch_gemv(X, Wp, C, M, N, K, a, ms, bias, sms, stream);
+    if (M <= 8 && container_bits == 4)
+        return w4_launch_reg(X, Wp, C, M, N, K, a, ms, bias, sms, stream);
     return w4_launch_rows(X, Wp, C, M, N, K, a, ms, container_bits, bias, workspace, sms, stream);
 }
 
