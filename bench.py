@@ -499,6 +499,22 @@ def decode_gemm_record(dev, rows: int = 16, copies: int = 8, reps: int = 6):
         del w4s, deqs, outs
     rec["llama3_8b_layer_linears"] = {k: sum(layer[(N, Kd)] * rec["shapes"][f"N{N}_K{Kd}"][k] for (N, Kd) in layer)
                                       for k in ("w4", "fp16_tc", "fp16_library")}
+    # fewer tokens: the packed weight has a kernel without the tensor core for one token and a warp-level-MMA kernel
+    # (weights expanded into register fragments) for two to eight
+    rec["fewer_tokens"] = {}
+    for (N, Kd) in ((14336, 4096), (4096, 4096)):
+        w = (0.02 * torch.randn(N, Kd, device=dev)).half()
+        packed, deq = q.quantize_packed(w, with_deq=True)
+        n_copies = max(copies, -(-300_000_000 // (N * Kd * 2)))
+        w4s = [W4Weight.from_packed(packed) for _ in range(n_copies)]
+        deqs = [deq.clone() for _ in range(n_copies)]
+        for r in (1, 8):
+            x = torch.randn(r, Kd, device=dev).half()
+            outs = [torch.empty(r, N, device=dev, dtype=torch.float16) for _ in range(n_copies)]
+            rec["fewer_tokens"][f"N{N}_K{Kd}_rows{r}"] = {
+                "w4": walk([(lambda ww=ww, o=o: ww.matmul(x, out=o)) for ww, o in zip(w4s, outs)]),
+                "fp16_library": walk([(lambda d=d, o=o: torch.mm(x, d.t(), out=o)) for d, o in zip(deqs, outs)])}
+        del w4s, deqs, outs
     torch.cuda.empty_cache()
     return rec
 

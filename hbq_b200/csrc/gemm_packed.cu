@@ -10,6 +10,10 @@
 // significant bits), level * t is exact as well, so one multiply by the per-micro-block product t*s rounds exactly
 // like the quantizer's fp16(fp16(level * t) * s).
 //
+// Three kernels share the prepacked weight and its expansion.  One token: gemv_packed_kernel, no tensor core.  Two to
+// eight tokens (nibble container): gemm_packed_reg_kernel, mma.sync with the expanded weights as register fragments.
+// Everything else, described here: gemm_packed_kernel on tcgen05.
+//
 // Operands are swapped with respect to gemm_tc.cu: the 128 weight rows of a tile are the M side of the MMA
 // (A operand), the tokens its N side (B operand, X through TMA, zero filled beyond M), so the MMA's cost follows the
 // token count.  The A operand is read from TENSOR MEMORY: lane = weight row, a 32-bit column = two consecutive k, 64

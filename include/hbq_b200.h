@@ -243,6 +243,10 @@ int hbq_gemm_wait_selftest(const void* A, const void* W, void* C, int64_t M, int
  * F.linear of _QBaseLinear.forward (src/module.py:64) at decode-sized batches, where the time is the streaming
  * of W: the products are those of the fp16 tensor (each expanded value equals hbq_dequantize's bit for bit).
  *
+ * By token count the nibble container runs one of three kernels over the same prepacked weight: one token without the
+ * tensor core, two to eight tokens on the warp-level MMA with the expanded weights in registers, more on tcgen05 with
+ * the expanded weights in tensor memory.  All add in a fixed order (results do not vary from call to call).
+ *
  * Served: HBQ weights with E2M1 elements, block 128 with an E5M3 scale, 2-bit micro-scales per 8 or 32 with the
  * FPM1 / FP1 / FPM10 / FPM100 / Mix tables (every shipped HBQ weight format); N and K multiples of 128;
  * 1 <= M <= 128.  HBQ_ERR_UNSUPPORTED otherwise (callers then use hbq_gemm on the fp16 tensor).
