@@ -625,19 +625,21 @@ def run_sweep(args):
         from hbq_b200.packed_gemm import W4Weight
         packed = cls["hbq"](**dict(WGT, l2_block_size=8)).quantize_packed((0.02 * torch.randn(N, K, device="cuda")).half())
         w4 = W4Weight.from_packed(packed)
-        x16 = torch.randn(16, K, device="cuda", dtype=torch.float16)
-        for _ in range(max(args.warmup, 3)):
-            w4.matmul(x16)
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(args.steps):
-            w4.matmul(x16)
-        e1.record()
-        torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1) / args.steps
-        print(json.dumps({"case": "gemm on the packed weight (weight L2-resident after the first call)", "ms": ms, "shape": [16, K, N],
-                          "packed_bytes": w4.nbytes(), "status": H.gemm_status()}))
+        # 16 tokens: the tcgen05 kernel; 8: the warp-level-MMA kernel; 1: the kernel without the tensor core
+        for rows in (16, 8, 1):
+            xr = torch.randn(rows, K, device="cuda", dtype=torch.float16)
+            for _ in range(max(args.warmup, 3)):
+                w4.matmul(xr)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(args.steps):
+                w4.matmul(xr)
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / args.steps
+            print(json.dumps({"case": "gemm on the packed weight (weight L2-resident after the first call)", "ms": ms, "shape": [rows, K, N],
+                              "packed_bytes": w4.nbytes(), "status": H.gemm_status()}))
         del w4, packed
     if want in (None, "softmax", "rmsnorm"):  # the fused row kernels at configs[3]'s shapes (one batch row of the prefill)
         from hbq_b200 import fused
