@@ -30,11 +30,10 @@ class QLinear(nn.Linear):
         self.check_finite = check_finite
         self.packed_weight = None
         self.w4_weight = None          # the packed weight in the decode GEMM's tile order (prepare_decode)
-        self.w4_max_rows = 0           # batches up to this many rows take it while the fp16 tensor is kept; 0: none --
-                                       # on B200 the packed kernel runs at 0.85-1.3x the library fp16 GEMM for
-                                       # 1..16 rows depending on the shape (faster on the MLP shapes, slower on
-                                       # the 4096 x 4096 projections), so it stays opt-in; what it always buys is
-                                       # the 3.6x smaller weight (prepare_decode(drop_fp16=True))
+        self.w4_max_rows = 0           # batches up to this many rows take it while the fp16 tensor is kept.
+                                       # prepare_decode sets 8: up to there the packed kernels beat the library
+                                       # fp16 GEMM on every Llama-3-8B shape on B200 (1.2-2.2x); at 16 rows they are
+                                       # faster on the MLP shapes and slower on the 4096 x 4096 projections
 
     def forward(self, x: torch.Tensor, input_quantized: bool = False):
         """``input_quantized``: ``x`` has been through ``self.aq`` already (a producer that fuses the
@@ -92,7 +91,7 @@ class QLinear(nn.Linear):
 
     def prepare_decode(self, wq=None, drop_fp16: bool = False) -> bool:
         """Keep the packed weight also in the tile order of ``hbq_gemm_w4`` so that batches of up to
-        ``w4_max_rows`` rows multiply against 4-bit codes and scales expanded on chip (same products as
+        ``w4_max_rows`` rows (8 unless set before) multiply against 4-bit codes and scales expanded on chip (same products as
         with the fp16 tensor: the expanded values are its values bit for bit).  ``drop_fp16`` frees the fp16 tensor:
         the layer then holds 0.56 B per weight and EVERY batch goes through the packed kernel, 128 rows per launch
         (a capacity mode: large batches are slower than on the fp16 tensor).  Returns False, and changes nothing, for
@@ -120,6 +119,8 @@ class QLinear(nn.Linear):
         if drop_fp16:
             self.weight.data = torch.empty(0, dtype=self.weight.dtype, device=self.weight.device)
             self.packed_weight = None
+        elif self.w4_max_rows == 0:
+            self.w4_max_rows = 8
         return True
 
     def load_packed_weight(self, packed):

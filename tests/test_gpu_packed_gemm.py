@@ -127,7 +127,7 @@ def test_linear_layer_on_the_packed_weight():
     lin.bias.data = torch.randn(N, device="cuda", generator=g).half()
     lin.wq = make_quantizer(fm["hbq_a_wgt"])
     lin.aq = make_quantizer(fm["hbq_a_act"])
-    assert lin.prepare_decode() and lin.w4_max_rows == 0     # opt-in while the fp16 tensor is kept
+    assert lin.prepare_decode() and lin.w4_max_rows == 8     # the batch sizes where the packed kernels always win
     lin.w4_max_rows = 32
     wq = lin.weight.data.clone()
     for rows in (1, 20, 32, 33, 300):
