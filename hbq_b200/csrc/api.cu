@@ -318,12 +318,14 @@ int hbq_gemm_uses_tensor_cores(int64_t M, int64_t N, int64_t K, int b_is_nk, int
 // Decode-sized fp32-accumulation products whose 128-column tiles would not fill the SMs run the pipeline of
 // gemm_packed.cu with fp16 weight tiles (a tile's K split over a thread-block cluster, or equal runs of K blocks per
 // SM) when the caller hands over its workspace; without one they take the tile-per-CTA kernel.
-// Measured on B200 (16 tokens): [4096, 14336] 28 us against 63 us, [4096, 4096] 15 against 23; with 112 tiles
-// ([14336, 4096]) or more than 32 tokens the tile-per-CTA kernel is the faster one.
+// Measured on B200 (16 tokens): [4096, 14336] 28 us against 63 us, [4096, 4096] 15 against 23, [12288, 4096] 25 against
+// 32, one token x [14336, 4096] 27 against 39; beyond 128 MB of weight ([14336, 8192]: 51 against 47 us) or 32 tokens
+// the tile-per-CTA kernel is the faster one.
 static bool decode_stream_k(int64_t M, int64_t N, int64_t K, int mode)
 {
     int sms = 0;
-    return mode == HBQ_ACC_FP32 && M <= 32 && gemm_w16_eligible(M, N, K) && device_sms(&sms) == HBQ_OK && (N / 128) * 2 <= sms;
+    return mode == HBQ_ACC_FP32 && M <= 32 && gemm_w16_eligible(M, N, K) && device_sms(&sms) == HBQ_OK &&
+           ((N / 128) * 2 <= sms || (N / 128 <= sms && N * K * 2 <= (128ll << 20)));
 }
 
 int64_t hbq_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int b_is_nk, int mode, int group_k, int group_n)

@@ -37,7 +37,7 @@
 // Work split: the (tile, block) records form one sequence of tiles * K/128 stages.  Either every CTA takes whole
 // tiles (nothing to fix up), or CTA c of G (one per SM) takes the c-th of G equal runs of the sequence, whatever tile
 // boundaries fall inside ("stream-K"), so that every SM streams the same number of bytes.  A shared tile costs a
-// chain of dependent round trips through memory (partial sums, fence, count, read back) that is worth about ten
+// chain of dependent round trips through memory (partial sums, fence, count, read back) that is worth about fourteen
 // stages, so the host takes equal runs only where they save more than that (few tiles, long K).  In a run, a segment
 // that covers its tile's whole K goes straight to C; the others leave fp32 partial sums in a workspace and the CTA
 // that completes a tile adds its segments in CTA order (deterministic) and writes C.  A run is processed head of the
@@ -83,7 +83,7 @@ constexpr int PK_SERVICE0 = PK_EXP_WARP0 + PK_EXP_WARPS;       // warps 24, 25: 
 constexpr int PK_THREADS = (PK_SERVICE0 + 4) * 32;
 constexpr int PK_CTRL_BYTES = 512;
 constexpr int PK_CLUSTER_STAGES = 2;                          // ... what meeting in a cluster's shared memory costs
-constexpr int PK_FIXUP_STAGES = 10;                           // what sharing tiles between CTAs costs, in stages
+constexpr int PK_FIXUP_STAGES = 14;                           // what sharing tiles between CTAs costs, in stages
 
 struct PkArgs {
     const uint8_t* wp;          // prepacked weight [tiles][nblk][record]
@@ -1176,7 +1176,7 @@ static int max_clusters(int ms, int cb, int S, size_t smem)
 
 // Three ways to cut the work, costed in stages per CTA; sets a.split / a.whole_tiles and returns the grid:
 //  - equal runs of (tile, block) records per SM: tiles are shared between CTAs, and the fix-up of a shared tile is a
-//    chain of dependent round trips through memory worth about ten stages;
+//    chain of dependent round trips through memory worth about fourteen stages at 16 tokens, more with more tokens;
 //  - whole tiles per CTA: nothing to fix up, but SMs idle where the tiles do not fill them;
 //  - few tiles: a tile's K blocks split over the S CTAs of a thread-block cluster, whose parts meet in distributed
 //    shared memory behind a cluster barrier (about two stages); S is the largest size whose clusters all fit on
@@ -1188,7 +1188,7 @@ static int choose_split(PkArgs& a, int sms, int ms, int cb, size_t smem, uint32_
     a.run_r = a.total % grid;
     const int grid_w = a.tiles < sms ? a.tiles : sms;
     const int64_t stages_w = (int64_t)((a.tiles + grid_w - 1) / grid_w) * a.nblk;
-    const int64_t stages_k = (a.total + grid - 1) / grid + PK_FIXUP_STAGES;
+    const int64_t stages_k = (a.total + grid - 1) / grid + (int64_t)PK_FIXUP_STAGES * (a.m_pad / 16);   // partial sums grow with the tokens
     int S = sms / a.tiles;
     if (S > 8) S = 8;
     if (S > a.nblk) S = a.nblk;
